@@ -1,0 +1,306 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A * B (+bias) with
+//   * operands staged in shared memory by TMA (128-byte swizzle), a multi-stage
+//     mbarrier ring between one producer thread and one MMA-issuing thread,
+//   * tcgen05.mma (cta_group::1, 128 x BN x 16) accumulating in TMEM, two
+//     accumulator buffers so that the epilogue of tile i overlaps the main loop
+//     of tile i+1,
+//   * a persistent grid (one CTA per SM) walking tiles in an L2-friendly order.
+//
+// Operand layouts ("major" = which logical dimension is contiguous in memory):
+//   A K-major : A stored [M, K] (row stride lda)      -> y = x W^T, dx = dy W
+//   A MN-major: A stored [K, M]                        -> dW = dy^T x
+//   B K-major : B stored [N, K] (nn.Linear weight)     -> y = x W^T
+//   B MN-major: B stored [K, N]                        -> dx = dy W, dW = dy^T x
+// so all three GEMMs of a linear layer's forward/backward run without an
+// explicit transpose.
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace sb {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;  // warp0: TMA, warp1: MMA + TMEM alloc, warps 2-5: epilogue
+constexpr int kGroupM = 8;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+enum OutMode { kOutBf16 = 0, kOutF32 = 1, kOutF32Accum = 2 };
+
+struct TileMap {
+  int m_blocks, n_blocks;
+  __device__ __forceinline__ void get(int tile, int& pm, int& pn) const {
+    const int per_group = kGroupM * n_blocks;
+    const int group = tile / per_group;
+    const int first_m = group * kGroupM;
+    const int gsize = min(m_blocks - first_m, kGroupM);
+    const int r = tile - group * per_group;
+    pm = first_m + (r % gsize);
+    pn = r / gsize;
+  }
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
+                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc, int out_mode, int* status) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::kStages;
+  uint64_t* tfull = bars + 2 * Cfg::kStages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  TileMap tm{(M + kBM - 1) / kBM, (N + BN - 1) / BN};
+  const int tiles = tm.m_blocks * tm.n_blocks;
+  const int k_blocks = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        int pm, pn;
+        tm.get(tile, pm, pn);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, status, 0x101)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + s * Cfg::kStageBytes;
+          uint8_t* sB = sA + Cfg::kABytes;
+          mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, &full[s], kb * kBK, pm * kBM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, &full[s], pm * kBM + j * 64, kb * kBK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &tmB, &full[s], kb * kBK, pn * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, &full[s], pn * BN + j * 64, kb * kBK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+      int it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tcount) {
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], aph ^ 1, status, 0x201)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1;
+          if (!mbar_wait(&full[s], ph, status, 0x202)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint32_t b_base = a_base + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc =
+                A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024) : make_smem_desc(a_base + k * 32, 0, 1024);
+            const uint64_t bdesc =
+                B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024) : make_smem_desc(b_base + k * 32, 0, 1024);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // frees the smem stage once these MMAs retire
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue -----------------------------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may access
+    int tcount = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tcount) {
+      int pm, pn;
+      tm.get(tile, pm, pn);
+      const int acc = tcount & 1;
+      const uint32_t aph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], aph, status, 0x301)) break;
+      tc_fence_after();
+      const int row = pm * kBM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = pn * BN + c * 32;
+        if (row < M && col0 < N) {
+          const bool full_chunk = (col0 + 32 <= N);
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              const float b = (col < N) ? __bfloat162float(__ldg(bias + col)) : 0.f;
+              r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
+            }
+          }
+          if (out_mode == kOutBf16) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(C) + static_cast<long long>(row) * ldc + col0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                reinterpret_cast<uint4*>(crow)[v] = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          } else {
+            float* crow = reinterpret_cast<float*>(C) + static_cast<long long>(row) * ldc + col0;
+            const bool vec = full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
+            if (vec) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (out_mode == kOutF32Accum) {
+                  const float4 p = reinterpret_cast<float4*>(crow)[v];
+                  o.x += p.x;
+                  o.y += p.y;
+                  o.z += p.z;
+                  o.w += p.w;
+                }
+                reinterpret_cast<float4*>(crow)[v] = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) {
+                  float o = __uint_as_float(r[j]);
+                  if (out_mode == kOutF32Accum) o += crow[j];
+                  crow[j] = o;
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                       long long ldb, long long ldc, int out_mode, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  const CUtensorMap* ta = A_MN ? get_tmap_bf16_2d(A, K, M, lda, 64) : get_tmap_bf16_2d(A, M, K, lda, kBM);
+  const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN);
+  if (!ta || !tb) return SB_ERR_TMAP;
+  static bool attr_set = false;
+  auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+      return SB_ERR_CUDA;
+    attr_set = true;
+  }
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kfn<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N,
+                                                       K, ldc, out_mode, device_status_ptr());
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+template <bool A_MN, bool B_MN>
+static int dispatch_bn(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                       long long ldb, long long ldc, int out_mode, int bn_hint, cudaStream_t stream) {
+  int bn = bn_hint;
+  if (bn != 64 && bn != 128 && bn != 256) {
+    const long long mb = (M + kBM - 1) / kBM;
+    const int sms = sm_count();
+    if (mb * ((N + 255) / 256) >= sms || N >= 4096)
+      bn = 256;
+    else if (mb * ((N + 127) / 128) >= sms / 2)
+      bn = 128;
+    else
+      bn = 64;
+  }
+  if (bn == 256) return launch_gemm<256, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream);
+  if (bn == 128) return launch_gemm<128, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream);
+  return launch_gemm<64, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream);
+}
+
+}  // namespace sb
+
+extern "C" {
+
+// C[M,N] = op(A) * op(B) (+ bias[N]).  a_mn / b_mn select the operand layouts described at the
+// top of this file; out_mode: 0 = bf16 store, 1 = fp32 store, 2 = fp32 accumulate into C.
+// lda/ldb/ldc are row strides in elements of the stored matrices. bn_hint 0 = automatic tile width.
+int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                 long long ldb, long long ldc, int a_mn, int b_mn, int out_mode, int bn_hint, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return SB_ERR_ARG;
+  if ((lda & 7) || (ldb & 7)) return SB_ERR_ARG;
+  if (out_mode < 0 || out_mode > 2) return SB_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return sb::dispatch_bn<false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
+  if (!a_mn && b_mn) return sb::dispatch_bn<false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
+  if (a_mn && b_mn) return sb::dispatch_bn<true, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
+  return sb::dispatch_bn<true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
+}
+
+}  // extern "C"

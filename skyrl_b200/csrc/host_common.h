@@ -1,0 +1,27 @@
+// Host-side helpers shared by the kernel translation units: error codes, the
+// driver entry point for tensor-map encoding and a small tensor-map cache.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SB_OK 0
+#define SB_ERR_ARG 1        // unsupported shape / alignment
+#define SB_ERR_CUDA 2       // a CUDA runtime call failed
+#define SB_ERR_TMAP 3       // tensor-map encode failed
+#define SB_ERR_TOO_LARGE 4  // size beyond a stated maximum
+
+namespace sb {
+
+// 2-D bf16 row-major tensor [rows, cols] with row stride `ld` elements; box is
+// [box_rows, 64] elements with the 128-byte swizzle. Returns nullptr on failure.
+const CUtensorMap* get_tmap_bf16_2d(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                                    uint32_t box_cols = 64);
+// 3-D bf16 tensor [d2, d1, d0] (d0 innermost) with byte strides for d1 and d2.
+const CUtensorMap* get_tmap_bf16_3d(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                                    uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2);
+
+int* device_status_ptr();  // per-device status word (device address)
+int sm_count();
+
+}  // namespace sb

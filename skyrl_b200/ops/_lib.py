@@ -1,0 +1,88 @@
+"""ctypes bindings to the in-tree native libraries.
+
+``kernels()`` returns the handle of ``libsb_kernels.so`` (sm_100a CUDA kernels) and ``runtime()`` the
+handle of ``libsb_runtime.so`` (host C++ runtime).  On a machine with a CUDA device a missing kernel
+library is a hard error: the CUDA path is the product and silently running a PyTorch fallback on a GPU
+would hide a broken build.  On CPU-only machines the Python ops use their PyTorch reference
+implementations and never ask for the kernel library.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
+_lock = threading.Lock()
+_kernels = None
+_runtime = None
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def _load(name: str) -> ctypes.CDLL:
+    path = _LIB_DIR / name
+    if not path.exists():
+        if os.environ.get("SKYRL_B200_NO_AUTOBUILD", "0") != "1":
+            from skyrl_b200 import build
+
+            build.build_all()
+    if not path.exists():
+        raise NativeLibraryError(f"{path} is missing; run `python -m skyrl_b200.build`")
+    return ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+
+
+def kernels() -> ctypes.CDLL:
+    global _kernels
+    if _kernels is None:
+        with _lock:
+            if _kernels is None:
+                lib = _load("libsb_kernels.so")
+                lib.sb_version.restype = ctypes.c_char_p
+                _kernels = lib
+    return _kernels
+
+
+def runtime() -> ctypes.CDLL:
+    global _runtime
+    if _runtime is None:
+        with _lock:
+            if _runtime is None:
+                _runtime = _load("libsb_runtime.so")
+    return _runtime
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+_ERR = {1: "unsupported shape or alignment", 2: "CUDA runtime error", 3: "tensor-map encode failed", 4: "size beyond maximum"}
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeLibraryError(f"{what} failed: {_ERR.get(code, 'error')} (code {code})")
+
+
+def status_read_clear() -> int:
+    """Device status word: non-zero when a bounded device-side wait gave up. Synchronises."""
+    return int(kernels().sb_status_read_clear())
+
+
+def use_cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda

@@ -1,0 +1,169 @@
+"""bf16 GEMMs on the tcgen05 tensor-core kernel (``csrc/gemm_tcgen05.cu``) and the autograd
+``linear`` built from them.
+
+The three products of a linear layer map onto one kernel with different operand "major-ness", so
+no transposed copy of activations, gradients or weights is ever made:
+
+* ``y  = x  @ W^T``  -> ``gemm_nt``  (A K-major,  B K-major)
+* ``dx = dy @ W``    -> ``gemm_nn``  (A K-major,  B MN-major)
+* ``dW = dy^T @ x``  -> ``gemm_tn``  (A MN-major, B MN-major), optional fp32 accumulation
+
+CPU tensors take a PyTorch fp32 reference path (used by the CPU test-suite and the gloo plumbing
+runs).  Replaces the cuBLAS calls behind ``torch.nn.Linear`` in the reference's HF model forward
+(skyrl/backends/skyrl_train/workers/model_wrapper.py:329-333).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_configured = False
+
+
+def _fn():
+    global _configured
+    lib = _lib.kernels()
+    if not _configured:
+        lib.sb_gemm_bf16.restype = ctypes.c_int
+        lib.sb_gemm_bf16.argtypes = [
+            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+            ctypes.c_int, ctypes.c_int, ctypes.c_int,
+            ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong,
+            ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+        ]  # fmt: skip
+        _configured = True
+    return lib.sb_gemm_bf16
+
+
+def _as_2d_rowmajor(t: torch.Tensor) -> torch.Tensor:
+    assert t.dim() == 2
+    if t.stride(1) != 1 or (t.stride(0) % 8) != 0 or (t.data_ptr() % 16) != 0:
+        t = t.contiguous()
+        if (t.stride(0) % 8) != 0:
+            raise ValueError(f"GEMM operand row length {t.shape[1]} must be a multiple of 8")
+    return t
+
+
+def _launch(a, b, c, bias, M, N, K, a_mn, b_mn, out_mode, bn_hint=0):
+    code = _fn()(
+        a.data_ptr(), b.data_ptr(), c.data_ptr(), None if bias is None else bias.data_ptr(),
+        M, N, K, a.stride(0), b.stride(0), c.stride(0), int(a_mn), int(b_mn), out_mode, bn_hint,
+        _lib.stream_ptr(),
+    )  # fmt: skip
+    _lib.check(code, "sb_gemm_bf16")
+
+
+def gemm_nt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
+            out_dtype: torch.dtype = torch.bfloat16, bn_hint: int = 0) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T (+ bias[N])`` -> ``[M,N]``."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not x.is_cuda:
+        y = x.float() @ w.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        y = y.to(out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    x = _as_2d_rowmajor(x)
+    w = _as_2d_rowmajor(w)
+    if out is None:
+        out = torch.empty((M, N), device=x.device, dtype=out_dtype)
+    assert out.stride(1) == 1
+    mode = 0 if out.dtype == torch.bfloat16 else 1
+    _launch(x, w, out, bias, M, N, K, False, False, mode, bn_hint)
+    return out
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, bn_hint: int = 0) -> torch.Tensor:
+    """``a[M,K] @ b[K,N]`` -> bf16 ``[M,N]`` (b row-major, i.e. N contiguous)."""
+    M, K = a.shape
+    N = b.shape[1]
+    if not a.is_cuda:
+        y = (a.float() @ b.float()).to(torch.bfloat16 if a.dtype == torch.bfloat16 else a.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    a = _as_2d_rowmajor(a)
+    b = _as_2d_rowmajor(b)
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=torch.bfloat16)
+    _launch(a, b, out, None, M, N, K, False, True, 0, bn_hint)
+    return out
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+            out_dtype: torch.dtype = torch.bfloat16, bn_hint: int = 0) -> torch.Tensor:
+    """``a[K,M]^T @ b[K,N]`` -> ``[M,N]``; with ``accumulate`` the fp32 ``out`` is added to."""
+    K, M = a.shape
+    N = b.shape[1]
+    if not a.is_cuda:
+        y = a.float().t() @ b.float()
+        if out is not None:
+            if accumulate:
+                out.add_(y.to(out.dtype))
+            else:
+                out.copy_(y)
+            return out
+        return y.to(out_dtype)
+    a = _as_2d_rowmajor(a)
+    b = _as_2d_rowmajor(b)
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+    if accumulate:
+        assert out.dtype == torch.float32
+        mode = 2
+    else:
+        mode = 0 if out.dtype == torch.bfloat16 else 1
+    _launch(a, b, out, None, M, N, K, True, True, mode, bn_hint)
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T + b with all three GEMMs on the tcgen05 kernel.
+
+    If the weight carries a ``main_grad`` fp32 buffer (set by the sharded optimizer) the weight
+    gradient is accumulated straight into it by the GEMM epilogue and ``None`` is returned to autograd.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        y = gemm_nt(x2, w, bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.in_shape = shp
+        return y.reshape(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_nn(dy2, w).reshape(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(w, "main_grad", None)
+            if main_grad is not None:
+                gemm_tn(dy2, x2, out=main_grad, accumulate=True)
+            else:
+                dw = gemm_tn(dy2, x2, out_dtype=w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    return _LinearFn.apply(x, w, bias)
