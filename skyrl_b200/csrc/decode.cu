@@ -1,0 +1,359 @@
+// Generation-engine kernels: KV-cache scatter, paged-KV decode attention (split-KV with a
+// combine pass), Gumbel-max sampling with the chosen token's log-probability, and the
+// token-embedding gather.
+#include <curand_kernel.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace sb {
+
+// ------------------------------------------------------------------ KV cache write
+// qkv row t -> k_cache[slot[t]], v_cache[slot[t]]; caches are [num_slots, nkv, D] flattened.
+__global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ kc,
+                                      __nv_bfloat16* __restrict__ vc, const int* __restrict__ slots, int T, int nq,
+                                      int nkv, int D, long long row_stride) {
+  const int vec_per_row = nkv * D / 8;
+  const long long total = static_cast<long long>(T) * vec_per_row;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / vec_per_row);
+    const int v = static_cast<int>(idx - static_cast<long long>(t) * vec_per_row);
+    const int slot = slots[t];
+    if (slot < 0) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(t) * row_stride + nq * D);
+    reinterpret_cast<uint4*>(kc + static_cast<size_t>(slot) * nkv * D)[v] = src[v];
+    reinterpret_cast<uint4*>(vc + static_cast<size_t>(slot) * nkv * D)[v] = src[vec_per_row + v];
+  }
+}
+
+// ------------------------------------------------------------------ decode attention
+// grid (n_seq, nkv, splits), 128 threads. 16 lanes cooperate on one token (8 dims each), so a warp
+// covers 2 tokens per step and the CTA 8.  G = nq / nkv query heads share every K/V row read.
+constexpr int kDecMaxG = 8;
+constexpr int kDecThreads = 128;
+
+template <int G>
+__global__ void __launch_bounds__(kDecThreads)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ kc,
+                   const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_tables,
+                   const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int nq,
+                   int nkv, int block_size, int max_blocks, int splits, long long q_stride, float scale_log2) {
+  constexpr int D = 128;
+  const int seq = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+  const int ctx = ctx_lens[seq];
+  const int per_split = ((ctx + splits - 1) / splits + 7) & ~7;
+  const int t0 = split * per_split;
+  const int t1 = min(ctx, t0 + per_split);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 15, tok_in_warp = lane >> 4;
+
+  float q[G][8], o[G][8], m[G], l[G];
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    const uint4 v = *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(seq) * q_stride + (g * G + h) * D + sub * 8);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(p[i]);
+      q[h][2 * i] = f.x * scale_log2;
+      q[h][2 * i + 1] = f.y * scale_log2;
+    }
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[h][i] = 0.f;
+  }
+
+  const int* bt = block_tables + static_cast<size_t>(seq) * max_blocks;
+  // the trip count is uniform per warp (full-mask shuffles below); the second token of the pair
+  // may fall beyond the range and is then predicated off
+  for (int tb = t0 + warp * 2; tb < t1; tb += 8) {
+    const int t = tb + tok_in_warp;
+    const bool valid = t < t1;
+    uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) {
+      const int blk = bt[t / block_size];
+      const size_t slot = static_cast<size_t>(blk) * block_size + (t % block_size);
+      const size_t off = (slot * nkv + g) * D + sub * 8;
+      kv4 = *reinterpret_cast<const uint4*>(kc + off);
+      vv4 = *reinterpret_cast<const uint4*>(vc + off);
+    }
+    float kf[8], vf[8];
+    {
+      const __nv_bfloat162* pk = reinterpret_cast<const __nv_bfloat162*>(&kv4);
+      const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&vv4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(pk[i]);
+        const float2 b = __bfloat1622float2(pv[i]);
+        kf[2 * i] = a.x;
+        kf[2 * i + 1] = a.y;
+        vf[2 * i] = b.x;
+        vf[2 * i + 1] = b.y;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += q[h][i] * kf[i];
+#pragma unroll
+      for (int ofs = 8; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
+      if (!valid) s = -INFINITY;
+      const float mn = fmaxf(m[h], s);
+      if (mn == -INFINITY) continue;
+      const float alpha = exp2f(m[h] - mn);
+      const float p = exp2f(s - mn);
+      l[h] = l[h] * alpha + p;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[h][i] = o[h][i] * alpha + p * vf[i];
+      m[h] = mn;
+    }
+  }
+  // tokens beyond t1 simply did not iterate; lanes whose loop ended early hold (m=-inf, l=0)
+
+  // merge the 8 token-groups of the CTA through shared memory
+  __shared__ float s_m[8][G], s_l[8][G];
+  __shared__ float s_o[8][G][D];
+  const int grp = warp * 2 + tok_in_warp;
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    if (sub == 0) {
+      s_m[grp][h] = m[h];
+      s_l[grp][h] = l[h];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_o[grp][h][sub * 8 + i] = o[h][i];
+  }
+  __syncthreads();
+  // thread d (0..127) merges column d for every head
+  const int d = threadIdx.x;
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+    float mm = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) mm = fmaxf(mm, s_m[k][h]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float w = (s_m[k][h] == -INFINITY) ? 0.f : exp2f(s_m[k][h] - mm);
+      ll += s_l[k][h] * w;
+      oo += s_o[k][h][d] * w;
+    }
+    const int head = g * G + h;
+    if (splits == 1) {
+      out[(static_cast<size_t>(seq) * nq + head) * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+    } else {
+      float* w = ws + ((static_cast<size_t>(seq) * nq + head) * splits + split) * (D + 2);
+      w[d] = oo;
+      if (d == 0) {
+        w[D] = mm;
+        w[D + 1] = ll;
+      }
+    }
+  }
+}
+
+__global__ void attn_decode_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int splits) {
+  constexpr int D = 128;
+  const size_t row = blockIdx.x;  // seq * nq + head
+  const int d = threadIdx.x;
+  const float* base = ws + row * splits * (D + 2);
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, base[s * (D + 2) + D]);
+  float ll = 0.f, oo = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = base[s * (D + 2) + D];
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+    ll += base[s * (D + 2) + D + 1] * w;
+    oo += base[s * (D + 2) + d] * w;
+  }
+  out[row * D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+}
+
+// ------------------------------------------------------------------ sampling
+// One CTA per row. token = argmax_i (z_i / T + Gumbel_i) is an exact sample of softmax(z / T);
+// logprob = z_tok / T - logsumexp(z / T).  temperature <= 0 -> greedy.
+constexpr int kSampThreads = 512;
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(kSampThreads)
+sample_gumbel_kernel(const T* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temperature,
+                     unsigned long long seed, const long long* __restrict__ step_offsets, int* __restrict__ tokens,
+                     float* __restrict__ logprobs) {
+  const int row = blockIdx.x;
+  const T* z = logits + static_cast<size_t>(row) * row_stride;
+  const float temp = temperature[row];
+  const bool greedy = temp <= 0.f;
+  const float inv_t = greedy ? 1.f : 1.f / temp;
+  curandStatePhilox4_32_10_t rng;
+  curand_init(seed, static_cast<unsigned long long>(row) * kSampThreads + threadIdx.x,
+              step_offsets ? static_cast<unsigned long long>(step_offsets[0]) * 1024ull : 0ull, &rng);
+  float best = -INFINITY, m = -INFINITY, s = 0.f;
+  int best_i = 0x7fffffff;
+  for (int i0 = threadIdx.x * 4; i0 < V; i0 += kSampThreads * 4) {
+    float4 u4 = greedy ? make_float4(0.5f, 0.5f, 0.5f, 0.5f) : curand_uniform4(&rng);
+    const float u[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = i0 + e;
+      if (i < V) {
+        const float x = to_f<T>(z[i]) * inv_t;
+        const float mn = fmaxf(m, x);
+        s = s * __expf(m - mn) + __expf(x - mn);
+        m = mn;
+        const float gum = greedy ? 0.f : -__logf(-__logf(u[e]));
+        const float y = x + gum;
+        if (y > best || (y == best && i < best_i)) {
+          best = y;
+          best_i = i;
+        }
+      }
+    }
+  }
+  __shared__ float sh_best[kSampThreads / 32], sh_m[kSampThreads / 32], sh_s[kSampThreads / 32];
+  __shared__ int sh_i[kSampThreads / 32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ob > best || (ob == best && oi < best_i)) {
+      best = ob;
+      best_i = oi;
+    }
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const float os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mn = fmaxf(m, om);
+    s = (m == -INFINITY ? 0.f : s * __expf(m - mn)) + (om == -INFINITY ? 0.f : os * __expf(om - mn));
+    m = mn;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sh_best[warp] = best;
+    sh_i[warp] = best_i;
+    sh_m[warp] = m;
+    sh_s[warp] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kSampThreads / 32; ++w) {
+      if (sh_best[w] > best || (sh_best[w] == best && sh_i[w] < best_i)) {
+        best = sh_best[w];
+        best_i = sh_i[w];
+      }
+      const float mn = fmaxf(m, sh_m[w]);
+      s = (m == -INFINITY ? 0.f : s * __expf(m - mn)) + (sh_m[w] == -INFINITY ? 0.f : sh_s[w] * __expf(sh_m[w] - mn));
+      m = mn;
+    }
+    tokens[row] = best_i;
+    logprobs[row] = to_f<T>(z[best_i]) * inv_t - (m + __logf(s));
+  }
+}
+
+// ------------------------------------------------------------------ embedding gather
+__global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
+                                    __nv_bfloat16* __restrict__ out, int T, int H) {
+  const int vec = H / 8;
+  const long long total = static_cast<long long>(T) * vec;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(idx / vec);
+    const int v = static_cast<int>(idx - static_cast<long long>(t) * vec);
+    reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H)[v] =
+        reinterpret_cast<const uint4*>(table + static_cast<size_t>(ids[t]) * H)[v];
+  }
+}
+
+static inline int grid_1d(long long items, int threads) {
+  long long b = (items + threads - 1) / threads;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  if (b > cap) b = cap;
+  return static_cast<int>(b < 1 ? 1 : b);
+}
+
+}  // namespace sb
+
+extern "C" {
+
+int sb_kv_cache_write(const void* qkv, void* k_cache, void* v_cache, const int* slots, int T, int nq, int nkv, int D,
+                      long long row_stride, int reserved, void* stream) {
+  (void)reserved;
+  if (T <= 0) return SB_OK;
+  if ((nkv * D) % 8 != 0) return SB_ERR_ARG;
+  sb::kv_cache_write_kernel<<<sb::grid_1d(static_cast<long long>(T) * nkv * D / 8, 256), 256, 0,
+                              reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<__nv_bfloat16*>(k_cache),
+      reinterpret_cast<__nv_bfloat16*>(v_cache), slots, T, nq, nkv, D, row_stride);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+int sb_attn_decode_paged(const void* qkv, const void* k_cache, const void* v_cache, const int* block_tables,
+                         const int* ctx_lens, void* out, float* workspace, int n, int nq, int nkv, int D,
+                         int block_size, int max_blocks, int splits, long long q_stride, float scale, void* stream) {
+  if (D != 128 || nq % nkv != 0 || n <= 0 || splits < 1) return SB_ERR_ARG;
+  const int G = nq / nkv;
+  if (G > sb::kDecMaxG) return SB_ERR_ARG;
+  if (splits > 1 && !workspace) return SB_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid(n, nkv, splits);
+  const float sl2 = scale * 1.4426950408889634f;
+#define SB_DEC_CASE(GV)                                                                                              \
+  case GV:                                                                                                           \
+    sb::attn_decode_kernel<GV><<<grid, sb::kDecThreads, 0, st>>>(                                                    \
+        reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(k_cache),                \
+        reinterpret_cast<const __nv_bfloat16*>(v_cache), block_tables, ctx_lens, reinterpret_cast<__nv_bfloat16*>(out), \
+        workspace, nq, nkv, block_size, max_blocks, splits, q_stride, sl2);                                          \
+    break;
+  switch (G) {
+    SB_DEC_CASE(1)
+    SB_DEC_CASE(2)
+    SB_DEC_CASE(3)
+    SB_DEC_CASE(4)
+    SB_DEC_CASE(5)
+    SB_DEC_CASE(6)
+    SB_DEC_CASE(7)
+    SB_DEC_CASE(8)
+    default:
+      return SB_ERR_ARG;
+  }
+#undef SB_DEC_CASE
+  if (splits > 1)
+    sb::attn_decode_combine_kernel<<<n * nq, 128, 0, st>>>(workspace, reinterpret_cast<__nv_bfloat16*>(out), splits);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+// logits: [n, V] bf16 (is_bf16 = 1) or fp32; temperature: [n] fp32 on device; step_offsets: optional device
+// int64 counter that decorrelates successive calls made from a replayed CUDA graph.
+int sb_sample_gumbel(const void* logits, int is_bf16, long long row_stride, int n, int V, const float* temperature,
+                     unsigned long long seed, const long long* step_offsets, int* tokens, float* logprobs,
+                     void* stream) {
+  if (n <= 0 || V <= 0) return SB_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    sb::sample_gumbel_kernel<__nv_bfloat16><<<n, sb::kSampThreads, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V, temperature, seed, step_offsets, tokens, logprobs);
+  else
+    sb::sample_gumbel_kernel<float><<<n, sb::kSampThreads, 0, st>>>(reinterpret_cast<const float*>(logits), row_stride,
+                                                                    V, temperature, seed, step_offsets, tokens,
+                                                                    logprobs);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+int sb_embed_gather(const void* table, const int* ids, void* out, int T, int H, void* stream) {
+  if (T <= 0) return SB_OK;
+  if (H % 8 != 0) return SB_ERR_ARG;
+  sb::embed_gather_kernel<<<sb::grid_1d(static_cast<long long>(T) * H / 8, 256), 256, 0,
+                            reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(table), ids, reinterpret_cast<__nv_bfloat16*>(out), T, H);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+}  // extern "C"

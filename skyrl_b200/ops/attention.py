@@ -1,0 +1,194 @@
+"""Attention ops: packed variable-length causal attention for training / prefill, paged-KV decode
+attention for the generation engine, and the KV-cache scatter.
+
+The packed layout is the one the reference feeds flash-attn with after ``unpad_input``
+(skyrl/backends/skyrl_train/workers/model_wrapper.py:278-289,326-329): all sequences concatenated
+along one token axis plus ``cu_seqlens``.  Here the kernels read Q, K and V straight out of the
+fused-QKV projection output ``[T, (nq + 2 nkv) * D]`` through TMA, so no split/contiguous copy is made.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+_cfg_done = False
+
+
+def _k():
+    global _cfg_done
+    lib = _lib.kernels()
+    if not _cfg_done:
+        vp, ci, cf, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+        lib.sb_attn_fwd_varlen.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, cl, cf, vp]
+        lib.sb_attn_bwd_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cl, cf, vp]
+        lib.sb_kv_cache_write.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, cl, ci, vp]
+        lib.sb_attn_decode_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cl, cf, vp]
+        _cfg_done = True
+    return lib
+
+
+def _split(qkv, nq, nkv, D):
+    T = qkv.shape[0]
+    q = qkv[:, : nq * D].view(T, nq, D)
+    k = qkv[:, nq * D : (nq + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nq + nkv) * D :].view(T, nkv, D)
+    return q, k, v
+
+
+def attn_varlen_ref(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: int, D: int, scale: float):
+    """fp32 PyTorch reference: returns (out [T, nq*D], lse [nq, T])."""
+    T = qkv.shape[0]
+    q, k, v = _split(qkv.float(), nq, nkv, D)
+    rep = nq // nkv
+    out = torch.zeros(T, nq, D, dtype=torch.float32, device=qkv.device)
+    lse = torch.zeros(nq, T, dtype=torch.float32, device=qkv.device)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        s, e = cu[b], cu[b + 1]
+        if e <= s:
+            continue
+        qb = q[s:e].transpose(0, 1)  # [nq, L, D]
+        kb = k[s:e].transpose(0, 1).repeat_interleave(rep, dim=0)
+        vb = v[s:e].transpose(0, 1).repeat_interleave(rep, dim=0)
+        sc = qb @ kb.transpose(1, 2) * scale
+        L = e - s
+        mask = torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+        lse[:, s:e] = torch.logsumexp(sc, dim=-1)
+        out[s:e] = (torch.softmax(sc, dim=-1) @ vb).transpose(0, 1)
+    return out.reshape(T, nq * D).to(qkv.dtype), lse
+
+
+class _AttnVarlenFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cu_seqlens, nq, nkv, D, scale, max_seqlen):
+        T = qkv.shape[0]
+        B = cu_seqlens.numel() - 1
+        if qkv.is_cuda:
+            assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and cu_seqlens.dtype == torch.int32
+            out = torch.empty((T, nq * D), device=qkv.device, dtype=qkv.dtype)
+            lse = torch.empty((nq, T), device=qkv.device, dtype=torch.float32)
+            code = _k().sb_attn_fwd_varlen(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), cu_seqlens.data_ptr(), B, T,
+                                           nq, nkv, D, qkv.stride(0), scale, _lib.stream_ptr())
+            _lib.check(code, "sb_attn_fwd_varlen")
+        else:
+            out, lse = attn_varlen_ref(qkv, cu_seqlens, nq, nkv, D, scale)
+        ctx.save_for_backward(qkv, out, lse, cu_seqlens)
+        ctx.meta = (nq, nkv, D, scale, max_seqlen)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, cu = ctx.saved_tensors
+        nq, nkv, D, scale, max_seqlen = ctx.meta
+        T = qkv.shape[0]
+        B = cu.numel() - 1
+        if qkv.is_cuda:
+            dout = dout.contiguous()
+            dqkv = torch.empty_like(qkv)
+            delta = torch.empty(nq * T, device=qkv.device, dtype=torch.float32)
+            code = _k().sb_attn_bwd_varlen(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+                                           dqkv.data_ptr(), cu.data_ptr(), delta.data_ptr(), B, T, nq, nkv, D,
+                                           dqkv.stride(0),
+                                           scale, _lib.stream_ptr())
+            _lib.check(code, "sb_attn_bwd_varlen")
+            return dqkv, None, None, None, None, None, None
+        with torch.enable_grad():
+            x = qkv.detach().float().requires_grad_()
+            o, _ = attn_varlen_ref(x, cu, nq, nkv, D, scale)
+            (g,) = torch.autograd.grad(o, x, dout.float())
+        return g.to(qkv.dtype), None, None, None, None, None, None
+
+
+def attn_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: int, head_dim: int,
+                scale: float | None = None, max_seqlen: int = 0) -> torch.Tensor:
+    """Causal attention over packed sequences. ``qkv``: ``[T, (nq+2nkv)*D]`` -> ``[T, nq*D]``."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    return _AttnVarlenFn.apply(qkv, cu_seqlens, nq, nkv, head_dim, scale, max_seqlen)
+
+
+# ----------------------------------------------------------------------------- paged KV cache
+def kv_cache_write(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor, nq: int,
+                   nkv: int, D: int) -> None:
+    """Scatter the K and V heads of each row of ``qkv`` into cache slot ``slots[t]`` (negative = skip).
+
+    Caches are ``[num_blocks, block_size, nkv, D]``; a slot is ``block * block_size + offset``.
+    """
+    T = qkv.shape[0]
+    if qkv.is_cuda:
+        code = _k().sb_kv_cache_write(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slots.data_ptr(), T, nq,
+                                      nkv, D, qkv.stride(0), 0, _lib.stream_ptr())
+        _lib.check(code, "sb_kv_cache_write")
+        return
+    _, k, v = _split(qkv, nq, nkv, D)
+    kc = k_cache.view(-1, nkv, D)
+    vc = v_cache.view(-1, nkv, D)
+    ok = slots >= 0
+    kc[slots[ok].long()] = k[ok]
+    vc[slots[ok].long()] = v[ok]
+
+
+def attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale):
+    n, nq, D = q.shape
+    nkv = k_cache.shape[2]
+    bs = k_cache.shape[1]
+    rep = nq // nkv
+    out = torch.zeros_like(q, dtype=torch.float32)
+    for i in range(n):
+        L = int(ctx_lens[i])
+        if L == 0:
+            continue
+        nb = (L + bs - 1) // bs
+        blocks = block_tables[i, :nb].long()
+        kk = k_cache[blocks].reshape(-1, nkv, D)[:L].float().repeat_interleave(rep, dim=1)
+        vv = v_cache[blocks].reshape(-1, nkv, D)[:L].float().repeat_interleave(rep, dim=1)
+        s = torch.einsum("hd,lhd->hl", q[i].float(), kk) * scale
+        out[i] = torch.einsum("hl,lhd->hd", torch.softmax(s, dim=-1), vv)
+    return out.to(q.dtype)
+
+
+def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                      ctx_lens: torch.Tensor, nq: int, nkv: int, D: int, scale: float | None = None,
+                      out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                      max_ctx: int = 0) -> torch.Tensor:
+    """One query token per sequence against its paged KV (which already contains that token).
+
+    ``qkv``: ``[n, (nq+2nkv)*D]`` (only the q heads are read); ``block_tables``: ``[n, max_blocks]`` int32;
+    ``ctx_lens``: ``[n]`` int32.  Returns ``[n, nq*D]``.
+    """
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    n = qkv.shape[0]
+    if not qkv.is_cuda:
+        q = qkv[:, : nq * D].view(n, nq, D)
+        return attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale).reshape(n, nq * D)
+    if out is None:
+        out = torch.empty((n, nq * D), device=qkv.device, dtype=qkv.dtype)
+    bs = k_cache.shape[1]
+    splits = decode_num_splits(n, nkv, max_ctx if max_ctx > 0 else block_tables.shape[1] * bs)
+    if workspace is None:
+        workspace = torch.empty(decode_workspace_floats(n, nq, D, splits), device=qkv.device, dtype=torch.float32)
+    code = _k().sb_attn_decode_paged(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                                     ctx_lens.data_ptr(), out.data_ptr(), workspace.data_ptr(), n, nq, nkv, D, bs,
+                                     block_tables.shape[1], splits, qkv.stride(0), scale, _lib.stream_ptr())
+    _lib.check(code, "sb_attn_decode_paged")
+    return out
+
+
+def decode_num_splits(n: int, nkv: int, max_ctx: int) -> int:
+    """Split long contexts so that at least ~2 CTAs per SM are in flight."""
+    ctas = n * nkv
+    if ctas >= 296 or max_ctx <= 256:
+        return 1
+    want = (296 + ctas - 1) // ctas
+    return int(max(1, min(want, max_ctx // 256, 32)))
+
+
+def decode_workspace_floats(n: int, nq: int, D: int, splits: int) -> int:
+    return n * nq * splits * (D + 2)

@@ -1,0 +1,160 @@
+"""Elementwise, attention, decode, sampling and optimizer kernels against fp32 PyTorch references."""
+import math
+
+import pytest
+import torch
+
+from skyrl_b200.ops import _lib, attention, elementwise, optim, sampling
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("T,H", [(7, 256), (1000, 1536), (333, 3584)])
+def test_add_rmsnorm_fwd_bwd(T, H):
+    torch.manual_seed(0)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    d = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    xn, y = elementwise.add_rmsnorm(x, d, w, 1e-6)
+    g1, g2 = torch.randn_like(xn), torch.randn_like(y)
+    (xn * g1).sum().backward(retain_graph=True)
+    (y * g2).sum().backward()
+    xr, dr, wr = (t.detach().float().requires_grad_() for t in (x, d, w))
+    s = (xr + dr).to(torch.bfloat16).float() + 0 * (xr + dr)  # rounding point as in the kernel
+    s = xr + dr
+    yr = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    ((s * g1.float()).sum() + (yr * g2.float()).sum()).backward()
+    assert rel(xn, s) < 5e-3 and rel(y, yr) < 8e-3
+    assert rel(x.grad, xr.grad) < 1e-2 and rel(d.grad, dr.grad) < 1e-2 and rel(w.grad, wr.grad) < 1e-2
+
+
+def test_rope_roundtrip_and_ref():
+    torch.manual_seed(0)
+    T, nq, nkv, D = 300, 12, 2, 128
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 4096, (T,), device="cuda", dtype=torch.int32)
+    tab = elementwise.build_rope_table(4096, D, 1e6, "cuda")
+    ref = elementwise._rope_ref(qkv.cpu(), pos.cpu(), tab.cpu(), nq + nkv, D, 1.0)
+    got = elementwise.rope_(qkv.clone(), pos, tab, nq + nkv, D, 1.0)
+    assert rel(got.cpu(), ref) < 5e-3
+    back = elementwise.rope_(got.clone(), pos, tab, nq + nkv, D, -1.0)
+    assert rel(back, qkv) < 1e-2
+    assert torch.equal(got[:, (nq + nkv) * D:], qkv[:, (nq + nkv) * D:])
+
+
+def test_swiglu():
+    torch.manual_seed(0)
+    gu = torch.randn(513, 2 * 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = elementwise.swiglu(gu)
+    g = torch.randn_like(out)
+    out.backward(g)
+    r = gu.detach().float().requires_grad_()
+    o = torch.nn.functional.silu(r[:, :1024]) * r[:, 1024:]
+    o.backward(g.float())
+    assert rel(out, o) < 5e-3 and rel(gu.grad, r.grad) < 8e-3
+
+
+def _mk_qkv(lens, nq, nkv, D=128, seed=0):
+    torch.manual_seed(seed)
+    T = sum(lens)
+    qkv = (torch.randn(T, (nq + 2 * nkv) * D, device="cuda") * 0.7).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    return qkv, cu
+
+
+@pytest.mark.parametrize("lens,nq,nkv", [([128], 2, 1), ([64], 2, 2), ([300, 17, 129, 512], 12, 2), ([1000, 1], 4, 4)])
+def test_attn_fwd(lens, nq, nkv):
+    qkv, cu = _mk_qkv(lens, nq, nkv)
+    out = attention.attn_varlen(qkv, cu, nq, nkv, 128)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    ref, _ = attention.attn_varlen_ref(qkv, cu, nq, nkv, 128, 1 / math.sqrt(128))
+    assert rel(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("lens,nq,nkv", [([128], 2, 1), ([64], 2, 2), ([300, 17, 129, 512], 12, 2), ([700, 1], 4, 4)])
+def test_attn_bwd(lens, nq, nkv):
+    qkv, cu = _mk_qkv(lens, nq, nkv, seed=1)
+    qkv.requires_grad_()
+    out = attention.attn_varlen(qkv, cu, nq, nkv, 128)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    x = qkv.detach().float().requires_grad_()
+    ref, _ = attention.attn_varlen_ref(x, cu, nq, nkv, 128, 1 / math.sqrt(128))
+    ref.backward(g.float())
+    D = 128
+    for name, sl in (("dq", slice(0, nq * D)), ("dk", slice(nq * D, (nq + nkv) * D)), ("dv", slice((nq + nkv) * D, None))):
+        assert rel(qkv.grad[:, sl], x.grad[:, sl]) < 2e-2, name
+
+
+@pytest.mark.parametrize("nq,nkv,bs", [(12, 2, 16), (28, 4, 32), (4, 4, 16)])
+def test_decode_paged(nq, nkv, bs):
+    torch.manual_seed(0)
+    D, n = 128, 5
+    ctx = torch.tensor([1, 17, 300, 1025, 64], dtype=torch.int32)
+    max_blocks = (int(ctx.max()) + bs - 1) // bs
+    nblocks = n * max_blocks + 3
+    kc = torch.randn(nblocks, bs, nkv, D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(nblocks, bs, nkv, D, device="cuda").to(torch.bfloat16)
+    bt = torch.randperm(nblocks)[: n * max_blocks].view(n, max_blocks).to(torch.int32).cuda()
+    qkv = torch.randn(n, (nq + 2 * nkv) * D, device="cuda").to(torch.bfloat16)
+    ref = attention.attn_decode_paged_ref(qkv[:, : nq * D].view(n, nq, D), kc, vc, bt, ctx, 1 / math.sqrt(D))
+    for max_ctx in (0, 2048):
+        out = attention.attn_decode_paged(qkv, kc, vc, bt, ctx.cuda(), nq, nkv, D, max_ctx=max_ctx)
+        assert rel(out.view(n, nq, D), ref) < 1e-2
+
+
+def test_kv_cache_write():
+    nq, nkv, D, T = 4, 2, 128, 37
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device="cuda").to(torch.bfloat16)
+    kc = torch.zeros(8, 16, nkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(128)[:T].to(torch.int32).cuda()
+    slots[3] = -1
+    attention.kv_cache_write(qkv, kc, vc, slots, nq, nkv, D)
+    k = qkv[:, nq * D:(nq + nkv) * D].view(T, nkv, D)
+    for t in (0, 5, 36):
+        assert torch.equal(kc.view(-1, nkv, D)[slots[t]], k[t])
+    assert kc.view(-1, nkv, D).abs().sum(dim=(1, 2)).ne(0).sum() == T - 1
+
+
+def test_sampling_distribution_and_logprob():
+    torch.manual_seed(0)
+    V, n = 1000, 4096
+    base = torch.randn(V, device="cuda") * 2
+    logits = base.expand(n, V).contiguous().to(torch.bfloat16)
+    temp = torch.full((n,), 0.8, device="cuda")
+    tok, lp = sampling.sample(logits, temp, seed=123)
+    ref_lp = torch.log_softmax(logits[0].float() / 0.8, -1)
+    assert torch.allclose(lp, ref_lp[tok.long()], atol=2e-3)
+    emp = torch.bincount(tok.long(), minlength=V).float() / n
+    top = ref_lp.exp().topk(5).indices
+    assert torch.allclose(emp[top], ref_lp.exp()[top], atol=0.03)
+    tok2, _ = sampling.sample(logits, torch.zeros(n, device="cuda"), seed=1)
+    assert (tok2.long() == logits[0].float().argmax()).all()
+
+
+def test_adamw_flat_matches_torch():
+    torch.manual_seed(0)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    ref = p.clone().requires_grad_()
+    opt = torch.optim.AdamW([ref], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    master, m, v = p.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    bf = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        ref.grad = g.clone()
+        opt.step()
+        optim.adamw_flat(master, m, v, g, bf, 1e-3, 0.9, 0.95, 1e-8, 0.01, step)
+    assert torch.allclose(master, ref.detach(), atol=1e-5, rtol=1e-5)
+    assert rel(bf, master) < 5e-3
+    sq = torch.zeros(1, device="cuda")
+    optim.sqnorm_accum(g, sq)
+    assert abs(sq.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
