@@ -58,10 +58,12 @@ def _launch(a, b, c, bias, M, N, K, a_mn, b_mn, out_mode, bn_hint=0):
 
 
 def gemm_nt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
-            out_dtype: torch.dtype = torch.bfloat16, bn_hint: int = 0) -> torch.Tensor:
-    """``x[M,K] @ w[N,K]^T (+ bias[N])`` -> ``[M,N]``."""
+            out_dtype: torch.dtype | None = None, bn_hint: int = 0) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T (+ bias[N])`` -> ``[M,N]`` (dtype of ``x`` unless ``out_dtype`` is given)."""
     M, K = x.shape
     N = w.shape[0]
+    if out_dtype is None:
+        out_dtype = x.dtype
     if not x.is_cuda:
         y = x.float() @ w.float().t()
         if bias is not None:
@@ -87,7 +89,7 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, b
     M, K = a.shape
     N = b.shape[1]
     if not a.is_cuda:
-        y = (a.float() @ b.float()).to(torch.bfloat16 if a.dtype == torch.bfloat16 else a.dtype)
+        y = (a.float() @ b.float()).to(a.dtype)
         if out is not None:
             out.copy_(y)
             return out
@@ -101,10 +103,12 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, b
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
-            out_dtype: torch.dtype = torch.bfloat16, bn_hint: int = 0) -> torch.Tensor:
+            out_dtype: torch.dtype | None = None, bn_hint: int = 0) -> torch.Tensor:
     """``a[K,M]^T @ b[K,N]`` -> ``[M,N]``; with ``accumulate`` the fp32 ``out`` is added to."""
     K, M = a.shape
     N = b.shape[1]
+    if out_dtype is None:
+        out_dtype = a.dtype
     if not a.is_cuda:
         y = a.float().t() @ b.float()
         if out is not None:
@@ -142,6 +146,7 @@ class _LinearFn(torch.autograd.Function):
         y = gemm_nt(x2, w, bias)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
+        ctx.bias_ref = bias
         ctx.in_shape = shp
         return y.reshape(*shp[:-1], w.shape[0])
 
@@ -161,7 +166,11 @@ class _LinearFn(torch.autograd.Function):
             else:
                 dw = gemm_tn(dy2, x2, out_dtype=w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy2.dtype)
+            bias_main = getattr(ctx.bias_ref, "main_grad", None)
+            if bias_main is not None:
+                bias_main.add_(dy2.float().sum(0))
+            else:
+                db = dy2.float().sum(0).to(dy2.dtype)
         return dx, dw, db
 
 
