@@ -515,23 +515,24 @@ _KL_CODES = {"k1": 0, "abs": 1, "k2": 2, "k3": 3}
 class FusedPolicyObjective(torch.autograd.Function):
     """Clipped policy loss + KL penalty, value and gradient from one kernel pass (``sb_policy_loss``).
 
-    Returns ``(weighted_total, stats[8])`` where ``weighted_total = w_pol * L_policy + w_kl * KL_sum`` and
+    Returns ``(weighted_total, stats[8])`` where ``weighted_total = w_pol * L_policy + w_kl * sum(kl_weights * KL)`` and
     stats are the raw sums documented in ``csrc/rl_loss.cu``.  Only ``log_probs`` receives a gradient.
     """
 
     @staticmethod
-    def forward(ctx, log_probs, old_log_probs, advantages, loss_mask, ref_log_probs, tis, eps_low, eps_high, clip_c,
-                dual_clip, kl_type, w_pol, w_kl):
+    def forward(ctx, log_probs, old_log_probs, advantages, loss_mask, ref_log_probs, tis, kl_weights, eps_low, eps_high,
+                clip_c, dual_clip, kl_type, w_pol, w_kl):
         lib = _lib.kernels()
         vp, cf, ci = ctypes.c_void_p, ctypes.c_float, ctypes.c_int
-        lib.sb_policy_loss.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_longlong, cf, cf, cf, ci, ci, cf, cf, vp, vp, vp]
+        lib.sb_policy_loss.argtypes = [vp, vp, vp, vp, vp, vp, vp, ctypes.c_longlong, cf, cf, cf, ci, ci, cf, cf, vp, vp, vp]
         lp = log_probs.float().contiguous()
         args = [t.float().contiguous() if t is not None else None for t in (old_log_probs, advantages, loss_mask,
-                                                                            ref_log_probs, tis)]
+                                                                            ref_log_probs, tis, kl_weights)]
         dlogp = torch.empty_like(lp)
         stats = torch.zeros(8, device=lp.device, dtype=torch.float32)
         code = lib.sb_policy_loss(lp.data_ptr(), args[0].data_ptr(), args[1].data_ptr(), args[2].data_ptr(),
-                                  _lib.ptr(args[3]), _lib.ptr(args[4]), lp.numel(), eps_low, eps_high, clip_c,
+                                  _lib.ptr(args[3]), _lib.ptr(args[4]), _lib.ptr(args[5]), lp.numel(), eps_low, eps_high,
+                                  clip_c,
                                   1 if dual_clip else 0, _KL_CODES[kl_type], w_pol, w_kl, dlogp.data_ptr(),
                                   stats.data_ptr(), _lib.stream_ptr())
         _lib.check(code, "sb_policy_loss")
@@ -544,7 +545,7 @@ class FusedPolicyObjective(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g_total, _g_stats):
         (dlogp,) = ctx.saved_tensors
-        return ((dlogp * g_total).reshape(ctx.shape).to(ctx.dtype),) + (None,) * 12
+        return ((dlogp * g_total).reshape(ctx.shape).to(ctx.dtype),) + (None,) * 13
 
 
 def fused_objective_supported(config) -> bool:
@@ -553,3 +554,9 @@ def fused_objective_supported(config) -> bool:
                          and oc.outlier_token_is_threshold_high is None and oc.token_mask_is_threshold_low is None
                          and oc.tis_ratio_type is None)
     return config.policy_loss_type in ("regular", "dual_clip") and simple_off_policy
+
+
+def off_policy_correction_enabled_cfg(algorithm_cfg) -> bool:
+    from .off_policy import off_policy_correction_enabled
+
+    return off_policy_correction_enabled(algorithm_cfg.off_policy_correction)

@@ -272,6 +272,61 @@ __global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ table, con
   }
 }
 
+
+// ------------------------------------------------------------------ decode state advance
+// One thread per engine slot. Appends the sampled token / log-probability to the slot's output row,
+// decides termination (EOS after min_new tokens, or max_new reached) and prepares the next step's
+// input token, position, KV slot and context length, so that a decode step needs no host work.
+struct DecodeState {
+  int* cur_tokens;       // [S] input token of the next step
+  int* positions;        // [S]
+  int* slots;            // [S] KV slot of the next step's token (-1 = no write)
+  int* ctx_lens;         // [S]
+  const int* block_tables;  // [S, max_blocks]
+  int* active;           // [S]
+  int* finish_reason;    // [S] 0 = running, 1 = stop (EOS), 2 = length
+  int* gen_count;        // [S]
+  const int* max_new;    // [S]
+  const int* min_new;    // [S]
+  int* out_tokens;       // [S, out_stride]
+  float* out_logprobs;   // [S, out_stride]
+  const int* eos_ids;    // [n_eos]
+  long long* step_counter;  // [1] incremented once per call (decorrelates the sampler across graph replays)
+};
+
+__global__ void decode_advance_kernel(DecodeState st, const int* __restrict__ sampled,
+                                      const float* __restrict__ sampled_lp, int n, int max_blocks, int block_size,
+                                      int out_stride, int n_eos) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0 && st.step_counter) *st.step_counter += 1;
+  if (i >= n || !st.active[i]) return;
+  const int tok = sampled[i];
+  int gc = st.gen_count[i];
+  if (gc < out_stride) {
+    st.out_tokens[static_cast<size_t>(i) * out_stride + gc] = tok;
+    st.out_logprobs[static_cast<size_t>(i) * out_stride + gc] = sampled_lp[i];
+  }
+  ++gc;
+  st.gen_count[i] = gc;
+  int reason = 0;
+  if (gc >= st.min_new[i])
+    for (int e = 0; e < n_eos; ++e)
+      if (tok == st.eos_ids[e]) reason = 1;
+  if (!reason && gc >= st.max_new[i]) reason = 2;
+  if (reason) {
+    st.active[i] = 0;
+    st.finish_reason[i] = reason;
+    st.slots[i] = -1;
+    st.ctx_lens[i] = 0;
+    return;
+  }
+  const int p = st.positions[i] + 1;
+  st.positions[i] = p;
+  st.cur_tokens[i] = tok;
+  st.slots[i] = st.block_tables[static_cast<size_t>(i) * max_blocks + p / block_size] * block_size + p % block_size;
+  st.ctx_lens[i] = p + 1;
+}
+
 static inline int grid_1d(long long items, int threads) {
   long long b = (items + threads - 1) / threads;
   const long long cap = static_cast<long long>(sm_count()) * 8;
@@ -344,6 +399,30 @@ int sb_sample_gumbel(const void* logits, int is_bf16, long long row_stride, int 
     sb::sample_gumbel_kernel<float><<<n, sb::kSampThreads, 0, st>>>(reinterpret_cast<const float*>(logits), row_stride,
                                                                     V, temperature, seed, step_offsets, tokens,
                                                                     logprobs);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+// ptrs: the 14 device pointers of DecodeState in declaration order.
+int sb_decode_advance(void* const* ptrs, const int* sampled, const float* sampled_lp, int n, int max_blocks,
+                      int block_size, int out_stride, int n_eos, void* stream) {
+  if (n <= 0) return SB_OK;
+  sb::DecodeState st;
+  st.cur_tokens = static_cast<int*>(ptrs[0]);
+  st.positions = static_cast<int*>(ptrs[1]);
+  st.slots = static_cast<int*>(ptrs[2]);
+  st.ctx_lens = static_cast<int*>(ptrs[3]);
+  st.block_tables = static_cast<const int*>(ptrs[4]);
+  st.active = static_cast<int*>(ptrs[5]);
+  st.finish_reason = static_cast<int*>(ptrs[6]);
+  st.gen_count = static_cast<int*>(ptrs[7]);
+  st.max_new = static_cast<const int*>(ptrs[8]);
+  st.min_new = static_cast<const int*>(ptrs[9]);
+  st.out_tokens = static_cast<int*>(ptrs[10]);
+  st.out_logprobs = static_cast<float*>(ptrs[11]);
+  st.eos_ids = static_cast<const int*>(ptrs[12]);
+  st.step_counter = static_cast<long long*>(ptrs[13]);
+  sb::decode_advance_kernel<<<(n + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      st, sampled, sampled_lp, n, max_blocks, block_size, out_stride, n_eos);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

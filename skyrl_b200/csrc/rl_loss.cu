@@ -26,7 +26,8 @@ __device__ __forceinline__ float block_sum_f(float v, float* red) {
 // dlogp = w_pol * d(policy loss)/dlogp + w_kl * d(KL)/dlogp   (both already multiplied by the mask)
 __global__ void policy_loss_kernel(const float* __restrict__ logp, const float* __restrict__ old_logp,
                                    const float* __restrict__ adv, const float* __restrict__ mask,
-                                   const float* __restrict__ ref_logp, const float* __restrict__ tis, long long n,
+                                   const float* __restrict__ ref_logp, const float* __restrict__ tis,
+                                   const float* __restrict__ klw, long long n,
                                    float eps_low, float eps_high, float clip_c, int loss_type, int kl_type, float w_pol,
                                    float w_kl, float* __restrict__ dlogp, float* __restrict__ stats) {
   __shared__ float red[32];
@@ -81,10 +82,11 @@ __global__ void policy_loss_kernel(const float* __restrict__ logp, const float* 
         }
       }
     }
-    if (dlogp) dlogp[i] = mk * (w_pol * w * g + w_kl * dkl);
+    const float kw = klw ? klw[i] : 1.f;  // per-token weight of the KL term (e.g. 1 / tokens-in-sequence)
+    if (dlogp) dlogp[i] = mk * (w_pol * w * g + w_kl * kw * dkl);
     acc[0] += mk * w * loss;
     acc[1] += mk * (clipped ? 1.f : 0.f);
-    acc[2] += mk * kl;
+    acc[2] += mk * kw * kl;
     acc[3] += mk;
     acc[4] += mk * r;
     acc[5] += mk * (dual ? 1.f : 0.f);
@@ -158,14 +160,14 @@ __global__ void gae_kernel(const float* __restrict__ rewards, const float* __res
 extern "C" {
 
 int sb_policy_loss(const float* logp, const float* old_logp, const float* adv, const float* mask, const float* ref_logp,
-                   const float* tis, long long n, float eps_low, float eps_high, float clip_c, int loss_type,
+                   const float* tis, const float* klw, long long n, float eps_low, float eps_high, float clip_c, int loss_type,
                    int kl_type, float w_pol, float w_kl, float* dlogp, float* stats, void* stream) {
   if (n <= 0) return SB_OK;
   long long blocks = (n + 255) / 256;
   const long long cap = static_cast<long long>(sb::sm_count()) * 4;
   if (blocks > cap) blocks = cap;
   sb::policy_loss_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      logp, old_logp, adv, mask, ref_logp, tis, n, eps_low, eps_high, clip_c, loss_type, kl_type, w_pol, w_kl, dlogp,
+      logp, old_logp, adv, mask, ref_logp, tis, klw, n, eps_low, eps_high, clip_c, loss_type, kl_type, w_pol, w_kl, dlogp,
       stats);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }

@@ -1,0 +1,732 @@
+"""In-process generation engine: paged KV cache, continuous batching, device-resident decode state.
+
+What the reference gets from vLLM (skyrl/backends/skyrl_train/inference_servers/vllm_server_actor.py,
+the engine behind ``/inference/v1/generate``) is rebuilt here around three ideas:
+
+* **Admission on the host, stepping on the device.**  The C++ scheduler (``csrc/runtime``) admits
+  requests, owns the block pool and the prefix cache.  Once a request is admitted its whole decode
+  state (current token, position, KV slot, context length, block table, output row) lives in device
+  arrays indexed by an engine *slot*; a tiny kernel advances all slots after every sampled token, so a
+  decode step is a fixed launch sequence with no host input.
+* **CUDA graphs per batch bucket.**  That fixed sequence is captured once per bucket size and
+  replayed; the host only synchronises every ``sync_interval`` steps to harvest finished slots.
+* **Shared kernels with training.**  Prefill runs the same packed-varlen model forward as the
+  trainer (tcgen05 attention, fused projections) with a hook that scatters K/V into the cache, so
+  rollout and training log-probabilities come from the same arithmetic.
+
+The engine also runs on CPU tensors (PyTorch reference ops, no graphs) for the plumbing tests.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..models.decoder import CausalLM
+from ..ops import _lib
+from ..ops import attention as attn_ops
+from ..ops import elementwise as ew
+from ..ops import gemm, sampling
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 1024
+    min_tokens: int = 1
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    min_p: float = 0.0
+    stop: Optional[List[str]] = None
+    stop_token_ids: Optional[List[int]] = None
+    ignore_eos: bool = False
+    logprobs: Optional[int] = 1
+    prompt_logprobs: bool = False
+    include_stop_str_in_output: bool = True
+    skip_special_tokens: bool = True
+    seed: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, d: Optional[dict]) -> "SamplingParams":
+        d = dict(d or {})
+        if "max_generate_length" in d:
+            d["max_tokens"] = d.pop("max_generate_length")
+        extra = d.pop("additional_kwargs", None) or {}
+        d.update(extra)
+        known = {f for f in cls.__dataclass_fields__}
+        d.pop("repetition_penalty", None)
+        d.pop("n", None)
+        return cls(**{k: v for k, v in d.items() if k in known})
+
+    @property
+    def needs_mask(self) -> bool:
+        return (self.top_k is not None and self.top_k > 0) or (self.top_p is not None and self.top_p < 1.0) or (
+            self.min_p is not None and self.min_p > 0.0)
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: List[int]
+    token_ids: List[int]
+    logprobs: List[float]
+    finish_reason: str  # "stop" | "length" | "abort"
+    prompt_logprobs: Optional[List[float]] = None
+    num_cached_tokens: int = 0
+    weight_version: int = 0
+
+
+@dataclass
+class _Request:
+    rid: str
+    sid: int  # numeric id used by the C++ scheduler
+    prompt: List[int]
+    params: SamplingParams
+    salt: int
+    slot: int = -1
+    done: bool = False
+    prompt_logprobs: Optional[List[float]] = None
+    cached: int = 0
+    # tokens generated before a pause(abort)/preemption; the request is re-admitted with prompt+partial
+    partial_tokens: List[int] = field(default_factory=list)
+    partial_logprobs: List[float] = field(default_factory=list)
+
+
+@dataclass
+class EngineConfig:
+    block_size: int = 32
+    num_blocks: int = 0  # 0 = derive from gpu_memory_utilization
+    gpu_memory_utilization: float = 0.5
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 16384
+    max_model_len: int = 4096
+    enable_prefix_caching: bool = False
+    enforce_eager: bool = False
+    sync_interval: int = 16
+    seed: int = 0
+    graph_batch_sizes: Sequence[int] = (8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024)
+    reserve_full_length: bool = True
+
+
+def _rt():
+    lib = _lib.runtime()
+    if getattr(lib, "_sb_cfg", False):
+        return lib
+    vp, ci, cl, u64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint64
+    lib.sbrt_sched_create.restype = vp
+    lib.sbrt_sched_create.argtypes = [ci] * 6
+    lib.sbrt_sched_destroy.argtypes = [vp]
+    lib.sbrt_sched_add.argtypes = [vp, cl, vp, ci, ci, u64]
+    lib.sbrt_sched_plan.argtypes = [vp, vp, vp, vp, vp, ci]
+    lib.sbrt_sched_mark_prefilled.argtypes = [vp, cl]
+    lib.sbrt_sched_append.argtypes = [vp, cl, ci]
+    lib.sbrt_sched_finish.argtypes = [vp, cl, ci]
+    lib.sbrt_sched_seq_len.argtypes = [vp, cl]
+    lib.sbrt_sched_seq_cached.argtypes = [vp, cl]
+    lib.sbrt_sched_seq_blocks.argtypes = [vp, cl, vp, ci]
+    lib.sbrt_sched_seq_tokens.argtypes = [vp, cl, vp, ci]
+    lib.sbrt_sched_set_paused.argtypes = [vp, ci]
+    for f in ("num_running", "num_waiting", "num_free_blocks", "num_preemptions"):
+        getattr(lib, "sbrt_sched_" + f).argtypes = [vp]
+    lib.sbrt_sched_prefix_hit_rate.argtypes = [vp]
+    lib.sbrt_sched_prefix_hit_rate.restype = ctypes.c_double
+    lib.sbrt_sched_reset_prefix_cache.argtypes = [vp]
+    lib.sbrt_sched_invalidate_all_kv.argtypes = [vp]
+    lib.sbrt_sched_pop_failed.argtypes = [vp, vp, ci]
+    lib.sbrt_sched_list.argtypes = [vp, ci, vp, ci]
+    lib._sb_cfg = True
+    return lib
+
+
+class LLMEngine:
+    """Generation engine bound to one device and one ``CausalLM`` (whose weights it reads in place)."""
+
+    def __init__(self, model: CausalLM, config: Optional[EngineConfig] = None, eos_token_ids: Sequence[int] = (),
+                 detokenize: Optional[Callable[[List[int]], str]] = None):
+        self.model = model
+        self.cfg = config or EngineConfig()
+        self.device = model.flat_params.device
+        self.is_cuda = self.device.type == "cuda"
+        self.detokenize = detokenize
+        self.eos_token_ids = list(eos_token_ids)
+        a = model.args
+        c = self.cfg
+        self.max_blocks_per_seq = (c.max_model_len + c.block_size - 1) // c.block_size
+        self.num_blocks = c.num_blocks or self._derive_num_blocks()
+        self.rt = _rt()
+        self.sched = self.rt.sbrt_sched_create(self.num_blocks, c.block_size, c.max_num_seqs, c.max_num_batched_tokens,
+                                               int(c.enable_prefix_caching), int(c.reserve_full_length))
+        self.kv_dtype = model.flat_params.dtype
+        self.k_cache: List[torch.Tensor] = []
+        self.v_cache: List[torch.Tensor] = []
+        self._alloc_kv()
+        S = c.max_num_seqs
+        dev = self.device
+        i32 = dict(device=dev, dtype=torch.int32)
+        self.out_stride = c.max_model_len
+        self.cur_tokens = torch.zeros(S, **i32)
+        self.positions = torch.zeros(S, **i32)
+        self.slots = torch.full((S,), -1, **i32)
+        self.ctx_lens = torch.zeros(S, **i32)
+        self.block_tables = torch.zeros((S, self.max_blocks_per_seq), **i32)
+        self.active = torch.zeros(S, **i32)
+        self.finish_reason = torch.zeros(S, **i32)
+        self.gen_count = torch.zeros(S, **i32)
+        self.max_new = torch.zeros(S, **i32)
+        self.min_new = torch.ones(S, **i32)
+        self.out_tokens = torch.zeros((S, self.out_stride), **i32)
+        self.out_logprobs = torch.zeros((S, self.out_stride), device=dev, dtype=torch.float32)
+        self.eos_dev = torch.tensor(self.eos_token_ids or [-1], **i32)
+        self.step_counter = torch.zeros(1, device=dev, dtype=torch.int64)
+        self.temperature = torch.ones(S, device=dev, dtype=torch.float32)
+        self.top_k = torch.full((S,), -1, **i32)
+        self.top_p = torch.ones(S, device=dev, dtype=torch.float32)
+        self.min_p = torch.zeros(S, device=dev, dtype=torch.float32)
+        self.sampled = torch.zeros(S, **i32)
+        self.sampled_lp = torch.zeros(S, device=dev, dtype=torch.float32)
+        self._state_ptrs = None
+        self._graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
+        self._graph_pool = None
+        self._slot_req: List[Optional[_Request]] = [None] * S
+        self._free_slots = list(range(S - 1, -1, -1))
+        self._reqs: Dict[int, _Request] = {}
+        self._next_sid = 1
+        self._mask_slots = 0  # number of occupied slots that need top-k/top-p/min-p masking
+        self._cpu_gen = torch.Generator().manual_seed(c.seed)
+        self.weight_version = 0
+        self.paused = False
+        self.asleep = False
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_calls": 0,
+                      "graph_replays": 0, "preemptions": 0}
+        self._finished: List[RequestOutput] = []
+
+    # ------------------------------------------------------------------ memory
+    def _kv_block_bytes(self) -> int:
+        a = self.model.args
+        return 2 * a.num_layers * self.cfg.block_size * a.num_kv_heads * a.head_dim * self.model.flat_params.element_size()
+
+    def _derive_num_blocks(self) -> int:
+        c = self.cfg
+        if self.is_cuda:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(min(free * 0.9, total * c.gpu_memory_utilization))
+            n = budget // self._kv_block_bytes()
+        else:
+            n = 4 * c.max_num_seqs * self.max_blocks_per_seq // 4
+        need_all = c.max_num_seqs * self.max_blocks_per_seq
+        return int(max(16, min(n, need_all + 64)))
+
+    def _alloc_kv(self) -> None:
+        a = self.model.args
+        shape = (self.num_blocks, self.cfg.block_size, a.num_kv_heads, a.head_dim)
+        self.k_cache = [torch.zeros(shape, device=self.device, dtype=self.kv_dtype) for _ in range(a.num_layers)]
+        self.v_cache = [torch.zeros(shape, device=self.device, dtype=self.kv_dtype) for _ in range(a.num_layers)]
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, request_id: str, prompt_token_ids: Sequence[int], params: SamplingParams,
+                    cache_salt: Optional[str] = None) -> None:
+        prompt = [int(t) for t in prompt_token_ids]
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        room = self.cfg.max_model_len - len(prompt)
+        if room < 1:
+            self._finished.append(RequestOutput(request_id, prompt, [], [], "length", weight_version=self.weight_version))
+            return
+        sid = self._next_sid
+        self._next_sid += 1
+        salt = (hash(cache_salt) if cache_salt else 0) & ((1 << 64) - 1)
+        req = _Request(request_id, sid, prompt, params, salt)
+        self._reqs[sid] = req
+        self._enqueue(req)
+
+    def _enqueue(self, req: _Request) -> None:
+        toks = req.prompt + req.partial_tokens
+        max_new = max(1, min(req.params.max_tokens - len(req.partial_tokens), self.cfg.max_model_len - len(toks)))
+        arr = np.asarray(toks, dtype=np.int32)
+        self.rt.sbrt_sched_add(self.sched, req.sid, arr.ctypes.data, len(toks), int(max_new), req.salt)
+
+    def has_unfinished(self) -> bool:
+        return bool(self._reqs)
+
+    def abort_request(self, request_id: str) -> None:
+        for sid, r in list(self._reqs.items()):
+            if r.rid == request_id:
+                self._retire(r, "abort")
+
+    # ------------------------------------------------------------------ forward passes
+    def _layer_decode(self, i, x, delta, n):
+        m, a = self.model, self.model.args
+        pre = f"layers.{i}."
+        x, h = ew.add_rmsnorm(x, delta, m.p(pre + "ln1"), a.rms_norm_eps)
+        qkv = gemm.gemm_nt(h, m.p(pre + "wqkv"), m._p.get(pre + "bqkv"))
+        if a.qk_norm:
+            qkv = m._qk_norm(qkv, i)
+        qkv = ew.rope_(qkv, self.positions[:n], m.rope_table(self.device), a.num_heads + a.num_kv_heads, a.head_dim)
+        attn_ops.kv_cache_write(qkv, self.k_cache[i], self.v_cache[i], self.slots[:n], a.num_heads, a.num_kv_heads,
+                                a.head_dim)
+        att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], self.block_tables[:n], self.ctx_lens[:n],
+                                         a.num_heads, a.num_kv_heads, a.head_dim, max_ctx=self.cfg.max_model_len)
+        o = gemm.gemm_nt(att, m.p(pre + "wo"))
+        x, h = ew.add_rmsnorm(x, o, m.p(pre + "ln2"), a.rms_norm_eps)
+        if a.num_experts:
+            from ..models.moe import moe_ffn
+
+            d = moe_ffn(h, m.p(pre + "router"), m.p(pre + "experts_wgu"), m.p(pre + "experts_wd"),
+                        a.num_experts_per_tok, a.norm_topk_prob)
+        else:
+            gu = gemm.gemm_nt(h, m.p(pre + "wgu"))
+            d = gemm.gemm_nt(ew.swiglu(gu), m.p(pre + "wd"))
+        return x, d
+
+    @torch.no_grad()
+    def _decode_once(self, n: int, masked: bool) -> None:
+        m, a = self.model, self.model.args
+        x = sampling.embed(m.p("embed"), self.cur_tokens[:n])
+        delta = None
+        for i in range(a.num_layers):
+            x, delta = self._layer_decode(i, x, delta, n)
+        _, h = ew.add_rmsnorm(x, delta, m.p("final_norm"), a.rms_norm_eps)
+        logits = gemm.gemm_nt(h, m.lm_head_weight())
+        self._sample(logits, n, masked)
+        self._advance(n)
+
+    def _sample(self, logits: torch.Tensor, n: int, masked: bool, rows: Optional[torch.Tensor] = None) -> None:
+        """Samples into ``self.sampled[:n]`` / ``self.sampled_lp[:n]`` (rows = slot index of each logits row)."""
+        temp = self.temperature[:n] if rows is None else self.temperature[rows]
+        if masked:
+            tk = self.top_k[:n] if rows is None else self.top_k[rows]
+            tp = self.top_p[:n] if rows is None else self.top_p[rows]
+            mp = self.min_p[:n] if rows is None else self.min_p[rows]
+            logits = _mask_logits_rows(logits, temp, tk, tp, mp)
+        out_t = self.sampled[:n] if rows is None else torch.empty(logits.shape[0], device=self.device, dtype=torch.int32)
+        out_l = self.sampled_lp[:n] if rows is None else torch.empty(logits.shape[0], device=self.device)
+        if self.is_cuda:
+            sampling.sample(logits, temp.contiguous(), self.cfg.seed, self.step_counter, out_t, out_l)
+        else:
+            t, l = sampling.sample(logits, temp, self.cfg.seed, generator=self._cpu_gen)
+            out_t.copy_(t)
+            out_l.copy_(l)
+        if rows is not None:
+            self.sampled[rows] = out_t
+            self.sampled_lp[rows] = out_l
+
+    def _advance(self, n: int) -> None:
+        if self.is_cuda:
+            if self._state_ptrs is None:
+                ptrs = [self.cur_tokens, self.positions, self.slots, self.ctx_lens, self.block_tables, self.active,
+                        self.finish_reason, self.gen_count, self.max_new, self.min_new, self.out_tokens,
+                        self.out_logprobs, self.eos_dev, self.step_counter]
+                self._state_ptrs = (ctypes.c_void_p * len(ptrs))(*[p.data_ptr() for p in ptrs])
+                lib = _lib.kernels()
+                lib.sb_decode_advance.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                                  ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+            code = _lib.kernels().sb_decode_advance(self._state_ptrs, self.sampled.data_ptr(), self.sampled_lp.data_ptr(),
+                                                    n, self.max_blocks_per_seq, self.cfg.block_size, self.out_stride,
+                                                    len(self.eos_token_ids), _lib.stream_ptr())
+            _lib.check(code, "sb_decode_advance")
+            return
+        self._advance_rows(torch.arange(n, device=self.device))
+
+    def _advance_rows(self, rows: torch.Tensor) -> None:
+        """PyTorch mirror of ``decode_advance_kernel`` restricted to ``rows`` (CPU path, prefill install)."""
+        rows = rows[self.active[rows].bool()]
+        if rows.numel() == 0:
+            return
+        r = rows.long()
+        tok, lp = self.sampled[r], self.sampled_lp[r]
+        gc = self.gen_count[r].long()
+        ok = gc < self.out_stride
+        self.out_tokens[r[ok], gc[ok]] = tok[ok]
+        self.out_logprobs[r[ok], gc[ok]] = lp[ok]
+        gc = gc + 1
+        self.gen_count[r] = gc.to(torch.int32)
+        is_eos = torch.zeros_like(tok, dtype=torch.bool)
+        for e in self.eos_token_ids:
+            is_eos |= tok == e
+        reason = torch.where(is_eos & (gc >= self.min_new[r]), 1, 0)
+        reason = torch.where((reason == 0) & (gc >= self.max_new[r]), 2, reason).to(torch.int32)
+        fin = reason != 0
+        fr = r[fin]
+        self.active[fr] = 0
+        self.finish_reason[fr] = reason[fin]
+        self.slots[fr] = -1
+        self.ctx_lens[fr] = 0
+        go = r[~fin]
+        if go.numel():
+            p = self.positions[go] + 1
+            self.positions[go] = p
+            self.cur_tokens[go] = tok[~fin]
+            bs = self.cfg.block_size
+            blk = self.block_tables[go, (p // bs).long()]
+            self.slots[go] = blk * bs + p % bs
+            self.ctx_lens[go] = p + 1
+        if self.is_cuda:
+            self.step_counter += 1
+
+    @torch.no_grad()
+    def _prefill(self, reqs: List[_Request], starts: List[int]) -> None:
+        m, a = self.model, self.model.args
+        bs = self.cfg.block_size
+        dev = self.device
+        ids, pos, slot_list, cu = [], [], [], [0]
+        rows = []
+        for req in reqs:
+            toks = req.prompt + req.partial_tokens
+            L = len(toks)
+            bt = np.zeros(self.max_blocks_per_seq, dtype=np.int32)
+            nb = self.rt.sbrt_sched_seq_blocks(self.sched, req.sid, bt.ctypes.data, self.max_blocks_per_seq)
+            assert nb >= (L + bs - 1) // bs, "scheduler did not reserve enough blocks"
+            req.cached = self.rt.sbrt_sched_seq_cached(self.sched, req.sid)
+            slot = self._free_slots.pop()
+            req.slot = slot
+            self._slot_req[slot] = req
+            rows.append(slot)
+            self.block_tables[slot].copy_(torch.from_numpy(bt))
+            ids.extend(toks)
+            pos.extend(range(L))
+            slot_list.extend((bt[np.arange(L) // bs] * bs + np.arange(L) % bs).tolist())
+            cu.append(cu[-1] + L)
+        t_ids = torch.tensor(ids, device=dev, dtype=torch.int32)
+        t_pos = torch.tensor(pos, device=dev, dtype=torch.int32)
+        t_slots = torch.tensor(slot_list, device=dev, dtype=torch.int32)
+        t_cu = torch.tensor(cu, device=dev, dtype=torch.int32)
+
+        def sink(layer, qkv):
+            attn_ops.kv_cache_write(qkv, self.k_cache[layer], self.v_cache[layer], t_slots, a.num_heads,
+                                    a.num_kv_heads, a.head_dim)
+
+        max_len = max(len(r.prompt) + len(r.partial_tokens) for r in reqs)
+        h = m(t_ids, t_pos, t_cu, max_len, kv_sink=sink)
+        last = h[(t_cu[1:] - 1).long()]
+        if any(r.params.prompt_logprobs for r in reqs):
+            tgt = torch.roll(t_ids, -1)
+            plp, _ = m.token_logprobs(h, tgt)
+            plp = plp.float().cpu()
+            for k, r in enumerate(reqs):
+                if r.params.prompt_logprobs:
+                    r.prompt_logprobs = [None] + plp[cu[k] : cu[k + 1] - 1].tolist()
+        logits = gemm.gemm_nt(last.contiguous(), m.lm_head_weight())
+        rows_t = torch.tensor(rows, device=dev, dtype=torch.long)
+        # per-slot sampling parameters and counters
+        host = lambda f, dt: torch.tensor([f(r) for r in reqs], device=dev, dtype=dt)  # noqa: E731
+        self.temperature[rows_t] = host(lambda r: r.params.temperature, torch.float32)
+        self.top_k[rows_t] = host(lambda r: r.params.top_k if r.params.top_k else -1, torch.int32)
+        self.top_p[rows_t] = host(lambda r: r.params.top_p, torch.float32)
+        self.min_p[rows_t] = host(lambda r: r.params.min_p, torch.float32)
+        self.max_new[rows_t] = host(lambda r: max(1, min(r.params.max_tokens - len(r.partial_tokens),
+                                                         self.cfg.max_model_len - len(r.prompt) - len(r.partial_tokens))),
+                                    torch.int32)
+        self.min_new[rows_t] = host(lambda r: (1 << 30) if r.params.ignore_eos else max(0, r.params.min_tokens - len(r.partial_tokens)),
+                                    torch.int32)
+        self.gen_count[rows_t] = 0
+        self.finish_reason[rows_t] = 0
+        self.active[rows_t] = 1
+        self.positions[rows_t] = host(lambda r: len(r.prompt) + len(r.partial_tokens) - 1, torch.int32)
+        masked = any(r.params.needs_mask for r in reqs)
+        self._mask_slots += sum(1 for r in reqs if r.params.needs_mask)
+        self._sample(logits, len(reqs), masked, rows=rows_t)
+        self._advance_rows(rows_t)
+        for r in reqs:
+            self.rt.sbrt_sched_mark_prefilled(self.sched, r.sid)
+        self.stats["prefill_tokens"] += len(ids)
+        self.stats["prefill_calls"] += 1
+
+    # ------------------------------------------------------------------ stepping
+    def _bucket(self, n: int) -> int:
+        for b in self.cfg.graph_batch_sizes:
+            if b >= n and b <= self.cfg.max_num_seqs:
+                return b
+        return self.cfg.max_num_seqs
+
+    def _hi(self) -> int:
+        hi = 0
+        for s, r in enumerate(self._slot_req):
+            if r is not None:
+                hi = s + 1
+        return hi
+
+    def _run_decode(self, steps: int) -> None:
+        hi = self._hi()
+        if hi == 0:
+            return
+        masked = self._mask_slots > 0
+        n = self._bucket(hi)
+        use_graph = self.is_cuda and not self.cfg.enforce_eager and not masked and not self.model.args.num_experts
+        if use_graph:
+            g = self._graphs.get(n)
+            if g is None:
+                g = self._capture(n)
+            for _ in range(steps):
+                g.replay()
+            self.stats["graph_replays"] += steps
+        else:
+            for _ in range(steps):
+                self._decode_once(n, masked)
+        self.stats["decode_steps"] += steps
+
+    def _capture(self, n: int):
+        # warm up outside capture (lazy kernel attribute setup, tensor-map cache, workspace sizing)
+        saved = [t.clone() for t in (self.cur_tokens, self.positions, self.slots, self.ctx_lens, self.active,
+                                     self.finish_reason, self.gen_count, self.out_tokens, self.out_logprobs,
+                                     self.step_counter)]
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._decode_once(n, False)
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self._graph_pool):
+            self._decode_once(n, False)
+        if self._graph_pool is None:
+            self._graph_pool = g.pool()
+        for dst, src in zip((self.cur_tokens, self.positions, self.slots, self.ctx_lens, self.active,
+                             self.finish_reason, self.gen_count, self.out_tokens, self.out_logprobs,
+                             self.step_counter), saved):
+            dst.copy_(src)
+        self._graphs[n] = g
+        return g
+
+    def _harvest(self) -> None:
+        hi = self._hi()
+        if hi == 0:
+            return
+        fr = self.finish_reason[:hi].cpu()
+        gc = self.gen_count[:hi].cpu()
+        done = [s for s in range(hi) if self._slot_req[s] is not None and int(fr[s]) != 0]
+        stop_str = [s for s in range(hi) if self._slot_req[s] is not None and int(fr[s]) == 0
+                    and self._slot_req[s].params.stop and self.detokenize is not None]
+        fetch = done + stop_str
+        if not fetch:
+            return
+        idx = torch.tensor(fetch, device=self.device, dtype=torch.long)
+        toks = self.out_tokens[idx].cpu()
+        lps = self.out_logprobs[idx].cpu()
+        for k, s in enumerate(fetch):
+            req = self._slot_req[s]
+            n = int(gc[s])
+            t, l = toks[k, :n].tolist(), lps[k, :n].tolist()
+            if k < len(done):
+                self._retire(req, "stop" if int(fr[s]) == 1 else "length", t, l)
+            else:
+                cut = _find_stop(self.detokenize, t, req.params.stop)
+                if cut is not None:
+                    self._retire(req, "stop", t[:cut], l[:cut])
+
+    def _retire(self, req: _Request, reason: str, toks: Optional[List[int]] = None,
+                lps: Optional[List[float]] = None) -> None:
+        toks = req.partial_tokens + (toks or [])
+        lps = req.partial_logprobs + (lps or [])
+        if req.slot >= 0:
+            s = req.slot
+            self.active[s] = 0
+            self.finish_reason[s] = 0
+            self.slots[s] = -1
+            self.ctx_lens[s] = 0
+            self._slot_req[s] = None
+            self._free_slots.append(s)
+            self._free_slots.sort(reverse=True)
+            if req.params.needs_mask:
+                self._mask_slots -= 1
+            req.slot = -1
+        # keep the scheduler's copy of the sequence in sync so that its full blocks can be published
+        for t in (toks[len(req.partial_tokens):] if self.cfg.enable_prefix_caching else []):
+            self.rt.sbrt_sched_append(self.sched, req.sid, int(t))
+        self.rt.sbrt_sched_finish(self.sched, req.sid, int(self.cfg.enable_prefix_caching and reason != "abort"))
+        self._reqs.pop(req.sid, None)
+        self.stats["decode_tokens"] += len(toks)
+        self._finished.append(RequestOutput(req.rid, req.prompt, toks, lps, reason, req.prompt_logprobs, req.cached,
+                                            self.weight_version))
+
+    def step(self) -> List[RequestOutput]:
+        """One scheduling round: admit + prefill what fits, then ``sync_interval`` decode steps, then harvest."""
+        if self.paused or self.asleep:
+            out, self._finished = self._finished, []
+            return out
+        cap = self.cfg.max_num_seqs
+        ids = (ctypes.c_longlong * cap)()
+        starts = (ctypes.c_int * cap)()
+        counts = (ctypes.c_int * cap)()
+        mode = ctypes.c_int(0)
+        while self._free_slots and self.rt.sbrt_sched_num_waiting(self.sched) > 0:
+            n = self.rt.sbrt_sched_plan(self.sched, ctypes.byref(mode), ids, starts, counts, min(cap, len(self._free_slots)))
+            if mode.value != 1 or n == 0:
+                break
+            self._prefill([self._reqs[ids[i]] for i in range(n)], [starts[i] for i in range(n)])
+        failed = (ctypes.c_longlong * 64)()
+        nf = self.rt.sbrt_sched_pop_failed(self.sched, failed, 64)
+        for i in range(nf):
+            req = self._reqs.pop(failed[i], None)
+            if req is not None:
+                self._finished.append(RequestOutput(req.rid, req.prompt, [], [], "abort", weight_version=self.weight_version))
+        self._harvest()  # requests that finished on their very first token
+        if any(r is not None for r in self._slot_req):
+            self._run_decode(self.cfg.sync_interval)
+            self._harvest()
+        out, self._finished = self._finished, []
+        return out
+
+    def generate(self, prompts: Sequence[Sequence[int]], params, request_ids: Optional[Sequence[str]] = None,
+                 cache_salt: Optional[str] = None) -> List[RequestOutput]:
+        """Blocking convenience wrapper: run until every given prompt has finished; results in input order."""
+        if isinstance(params, SamplingParams):
+            params = [params] * len(prompts)
+        rids = list(request_ids) if request_ids is not None else [f"gen-{self._next_sid}-{i}" for i in range(len(prompts))]
+        for rid, p, sp in zip(rids, prompts, params):
+            self.add_request(rid, p, sp, cache_salt)
+        want = set(rids)
+        got: Dict[str, RequestOutput] = {}
+        while want - set(got):
+            if self.paused or self.asleep:
+                raise RuntimeError("generate() called on a paused or sleeping engine")
+            for o in self.step():
+                got[o.request_id] = o
+        return [got[r] for r in rids]
+
+    # ------------------------------------------------------------------ control plane
+    def pause(self, mode: str = "keep", clear_cache: bool = False) -> List[RequestOutput]:
+        """``keep``: freeze in-flight requests with their KV; ``abort``: return partial outputs; ``wait``: drain."""
+        out: List[RequestOutput] = []
+        if mode == "wait":
+            while self.has_unfinished():
+                out.extend(self.step())
+        elif mode == "abort":
+            self._harvest()
+            hi = self._hi()
+            gc = self.gen_count[:hi].cpu() if hi else []
+            for s in range(hi):
+                req = self._slot_req[s]
+                if req is None:
+                    continue
+                n = int(gc[s])
+                self._retire(req, "abort", self.out_tokens[s, :n].cpu().tolist(), self.out_logprobs[s, :n].cpu().tolist())
+            for req in list(self._reqs.values()):
+                self._retire(req, "abort")
+            out, self._finished = self._finished, []
+        elif mode != "keep":
+            raise ValueError(f"unknown pause mode '{mode}'")
+        self.paused = True
+        self.rt.sbrt_sched_set_paused(self.sched, 1)
+        if clear_cache:
+            self.reset_prefix_cache()
+        return out
+
+    def resume(self) -> None:
+        self.paused = False
+        self.rt.sbrt_sched_set_paused(self.sched, 0)
+
+    def reset_prefix_cache(self, reset_running_requests: bool = False) -> None:
+        if reset_running_requests:
+            self._requeue_running()
+            self.rt.sbrt_sched_invalidate_all_kv(self.sched)
+        else:
+            self.rt.sbrt_sched_reset_prefix_cache(self.sched)
+
+    def _requeue_running(self) -> None:
+        """Move every slot's request back to the waiting queue, keeping the tokens generated so far."""
+        hi = self._hi()
+        if hi == 0:
+            return
+        gc = self.gen_count[:hi].cpu()
+        for s in range(hi):
+            req = self._slot_req[s]
+            if req is None:
+                continue
+            n = int(gc[s])
+            req.partial_tokens = req.partial_tokens + self.out_tokens[s, :n].cpu().tolist()
+            req.partial_logprobs = req.partial_logprobs + self.out_logprobs[s, :n].cpu().tolist()
+            self.active[s] = 0
+            self.slots[s] = -1
+            self.ctx_lens[s] = 0
+            self._slot_req[s] = None
+            self._free_slots.append(s)
+            if req.params.needs_mask:
+                self._mask_slots -= 1
+            req.slot = -1
+            self.rt.sbrt_sched_finish(self.sched, req.sid, 0)
+            self._enqueue(req)
+        self._free_slots.sort(reverse=True)
+
+    def sleep(self, level: int = 1, tags: Optional[Sequence[str]] = None) -> None:
+        """Release the KV cache memory (level >= 1). Weights are shared with the trainer and stay put."""
+        if self.asleep:
+            return
+        if tags is None or "kv_cache" in tags:
+            self._requeue_running()
+            self.rt.sbrt_sched_invalidate_all_kv(self.sched)
+            self.k_cache, self.v_cache = [], []
+            self._graphs.clear()
+            self._graph_pool = None
+            if self.is_cuda:
+                torch.cuda.empty_cache()
+        self.asleep = True
+
+    def wake_up(self, tags: Optional[Sequence[str]] = None) -> None:
+        if tags is None or "kv_cache" in tags:
+            if not self.k_cache:
+                self._alloc_kv()
+            self.asleep = False
+        # tags == ["weights"]: nothing to map back; stay asleep until the KV cache returns
+
+    def on_weights_updated(self, clear_kv: bool = True) -> None:
+        """Called after the trainer pushed new weights into the model this engine reads."""
+        self.weight_version += 1
+        if clear_kv:
+            self.rt.sbrt_sched_reset_prefix_cache(self.sched)
+
+    def metrics(self) -> Dict[str, float]:
+        m = dict(self.stats)
+        m["num_running"] = sum(r is not None for r in self._slot_req)
+        m["num_waiting"] = self.rt.sbrt_sched_num_waiting(self.sched)
+        m["kv_free_blocks"] = self.rt.sbrt_sched_num_free_blocks(self.sched)
+        m["kv_usage"] = 1.0 - m["kv_free_blocks"] / max(1, self.num_blocks)
+        m["prefix_hit_rate"] = self.rt.sbrt_sched_prefix_hit_rate(self.sched)
+        m["weight_version"] = self.weight_version
+        return m
+
+    def __del__(self):
+        try:
+            if getattr(self, "sched", None):
+                self.rt.sbrt_sched_destroy(self.sched)
+                self.sched = None
+        except Exception:
+            pass
+
+
+def _find_stop(detok, tokens: List[int], stops: List[str]) -> Optional[int]:
+    """Smallest token count whose decoded text contains a stop string (the stop text is kept)."""
+    text = detok(tokens)
+    if not any(s in text for s in stops):
+        return None
+    lo, hi = 1, len(tokens)
+    while lo < hi:
+        mid = (lo + hi) // 2
+        if any(s in detok(tokens[:mid]) for s in stops):
+            hi = mid
+        else:
+            lo = mid + 1
+    return lo
+
+
+def _mask_logits_rows(logits, temp, top_k, top_p, min_p):
+    """Per-row top-k / top-p / min-p masking (fp32 result, -inf outside the kept set)."""
+    z = logits.float()
+    t = torch.where(temp > 0, temp, torch.ones_like(temp))[:, None]
+    zs, idx = torch.sort(z / t, dim=-1, descending=True)
+    V = z.shape[-1]
+    k = torch.where(top_k > 0, top_k, torch.full_like(top_k, V)).clamp(max=V).long()[:, None]
+    rank = torch.arange(V, device=z.device)[None, :]
+    remove = rank >= k
+    probs = torch.softmax(zs, dim=-1)
+    cum = probs.cumsum(-1)
+    remove |= (cum - probs) >= top_p[:, None]
+    remove |= probs < (min_p[:, None] * probs[:, :1])
+    remove[:, 0] = False
+    zs = zs.masked_fill(remove, float("-inf"))
+    out = torch.full_like(z, float("-inf")).scatter(-1, idx, zs * t)
+    return out

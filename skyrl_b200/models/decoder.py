@@ -187,7 +187,7 @@ class CausalLM(nn.Module):
                  flat_buffer: Optional[torch.Tensor] = None, seed: Optional[int] = 0):
         super().__init__()
         self.args = args
-        self.value_head = value_head
+        self.has_value_head = value_head
         self.specs = _param_specs(args, value_head=value_head)
         self.offsets: Dict[str, Tuple[int, int]] = {}
         off = 0
@@ -195,7 +195,7 @@ class CausalLM(nn.Module):
             n = math.prod(shape)
             self.offsets[name] = (off, n)
             off += _align(n)
-        self.flat_numel = off
+        self.flat_numel = _align(off, 8192)  # divisible by 8 * world for world <= 8 with 128-element shards
         if flat_buffer is None:
             flat_buffer = torch.zeros(self.flat_numel, device=device, dtype=dtype)
         assert flat_buffer.numel() >= self.flat_numel
@@ -312,7 +312,7 @@ class CausalLM(nn.Module):
         return gemm.gemm_nt(hidden, self.lm_head_weight())
 
     def values(self, hidden: torch.Tensor) -> torch.Tensor:
-        assert self.value_head
+        assert self.has_value_head
         return gemm.linear(hidden, self.p("value_head"))[:, 0].float()
 
     def num_parameters(self) -> int:

@@ -113,7 +113,7 @@ def to_hf_state_dict(model) -> Dict[str, torch.Tensor]:
     sd["model.norm.weight"] = model.p("final_norm").detach()
     if not a.tie_word_embeddings and "lm_head" in model._p:
         sd["lm_head.weight"] = model.p("lm_head").detach()
-    if model.value_head:
+    if model.has_value_head:
         sd["value_head.weight"] = model.p("value_head").detach()[:1]
     return sd
 

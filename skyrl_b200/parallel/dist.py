@@ -1,0 +1,96 @@
+"""Process-group bootstrap and mesh helpers: one process per GPU, NCCL for CUDA tensors and gloo for
+host objects (the reference initialises ``cpu:gloo,cuda:nccl`` the same way,
+skyrl/backends/skyrl_train/workers/worker.py:118-143).  Everything degrades to a single process when
+``WORLD_SIZE`` is unset, and to gloo-only on machines without a GPU.
+"""
+
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class DistEnv:
+    rank: int = 0
+    local_rank: int = 0
+    world_size: int = 1
+    device: torch.device = torch.device("cpu")
+
+    @property
+    def is_main(self) -> bool:
+        return self.rank == 0
+
+
+_ENV: Optional[DistEnv] = None
+
+
+def init_distributed(backend: Optional[str] = None, timeout_s: Optional[int] = None, device: Optional[str] = None) -> DistEnv:
+    """Initialise ``torch.distributed`` from the torchrun environment variables (idempotent)."""
+    global _ENV
+    if _ENV is not None:
+        return _ENV
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    use_cuda = torch.cuda.is_available() and device != "cpu"
+    dev = torch.device(f"cuda:{local}") if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(dev)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if backend is None:
+            backend = "cpu:gloo,cuda:nccl" if use_cuda else "gloo"
+        if timeout_s is None:
+            timeout_s = int(os.environ.get("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", "600"))
+        kw = {}
+        if use_cuda:
+            kw["device_id"] = dev
+        dist.init_process_group(backend=backend, rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kw)
+    _ENV = DistEnv(rank, local, world, dev)
+    return _ENV
+
+
+def get_env() -> DistEnv:
+    return _ENV if _ENV is not None else init_distributed()
+
+
+def reset_env_for_tests() -> None:
+    global _ENV
+    _ENV = None
+
+
+def barrier() -> None:
+    if dist.is_initialized():
+        dist.barrier()
+
+
+def all_reduce_max_scalar(x: float, device) -> float:
+    """MAX over ranks of a host scalar (used for device-timed step durations)."""
+    if not dist.is_initialized():
+        return x
+    t = torch.tensor([x], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def all_reduce_sum_scalar(x: float, device) -> float:
+    if not dist.is_initialized():
+        return x
+    t = torch.tensor([x], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def shutdown() -> None:
+    global _ENV
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    _ENV = None

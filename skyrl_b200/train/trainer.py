@@ -1,0 +1,453 @@
+"""Synchronous PPO / GRPO controller.
+
+One RL step (reference: ``RayPPOTrainer.train`` skyrl/train/trainer.py:271-601) is
+
+    generate -> postprocess rewards -> tensorise -> forward (old policy / ref / critic) ->
+    KL-in-reward -> advantages -> train critic + policy (mini-batches x epochs) -> checkpoint ->
+    weight sync -> log
+
+The process model is SPMD: every rank runs this controller on *its own shard* of the prompt batch
+with its colocated generation engine, so no batch ever crosses a process boundary.  Ranks meet only
+inside the sharded optimizer step (gradient reduce-scatter, parameter push) and when metrics are
+averaged.  With the engine reading the trainer's parameter buffer in place, "weight sync" after an
+update is the parameter push of the optimizer step itself plus a version bump that retires stale
+prefix-cache entries.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import math
+import os
+import time
+from typing import Any, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..algorithms import rl
+from ..engine.llm_engine import EngineConfig, LLMEngine
+from ..inference.local_client import LocalInferenceClient
+from ..parallel.dist import DistEnv, get_env
+from ..workers.worker import CriticWorker, PolicyWorker, RefWorker
+from . import utils as tutils
+from .batch import TrainingInputBatch, pad_training_input_batch
+from .dataset import PromptDataset, StatefulBatchIterator
+from .generators.base import GeneratorInput, GeneratorInterface, GeneratorOutput
+from .generators.skyrl_gym_generator import SkyRLGymGenerator
+from .generators.utils import compute_pass_at_n, get_metrics_from_generator_output, prepare_generator_input
+from .preprocess import (compute_prompt_boundaries, compute_prompt_mini_batch_boundaries,
+                         convert_prompts_responses_to_batch_tensors)
+from .tracking import Tracking
+from .utils import Timer
+
+
+class PPOTrainer:
+    def __init__(self, cfg, tracker: Optional[Tracking] = None, tokenizer=None, train_dataset: Optional[PromptDataset] = None,
+                 eval_dataset: Optional[PromptDataset] = None, inference_engine_client=None,
+                 generator: Optional[GeneratorInterface] = None, env: Optional[DistEnv] = None):
+        self.cfg = cfg
+        self.env = env or get_env()
+        self.tracker = tracker
+        self.tokenizer = tokenizer
+        self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
+        self.inference_engine_client = inference_engine_client
+        self.generator = generator
+        self.policy: Optional[PolicyWorker] = None
+        self.ref: Optional[RefWorker] = None
+        self.critic: Optional[CriticWorker] = None
+        self.engine: Optional[LLMEngine] = None
+        self.global_step = 0
+        self.all_metrics: Dict[str, float] = {}
+        self.all_timings: Dict[str, float] = {}
+        self.kl_controller = rl.get_kl_controller(cfg.trainer.algorithm) if cfg.trainer.algorithm.use_kl_in_reward else None
+        self.train_iter: Optional[StatefulBatchIterator] = None
+        self.callbacks: List[Any] = []
+        tutils.validate_cfg(cfg, self.env.world_size)
+        torch.manual_seed(cfg.trainer.seed + self.env.rank)
+        np.random.seed(cfg.trainer.seed + self.env.rank)
+
+    # ------------------------------------------------------------------ construction
+    def build_models(self, policy_model=None, peer_ctx=None) -> None:
+        """Create the policy (and optional ref / critic) workers and the colocated generation engine."""
+        t = self.cfg.trainer
+        a = t.algorithm
+        self.policy = PolicyWorker(t, model=policy_model, model_path=t.policy.model.path, env=self.env, peer_ctx=peer_ctx,
+                                   seed=t.seed)
+        if a.use_kl_loss or a.use_kl_in_reward:
+            self.ref = RefWorker(t, model_path=t.ref.model.path or t.policy.model.path, env=self.env, seed=t.seed)
+        if a.advantage_estimator == "gae" or t.critic.model.path is not None:
+            self.critic = CriticWorker(t, model_path=t.critic.model.path or t.policy.model.path, env=self.env,
+                                       seed=t.seed + 1)
+        if self.inference_engine_client is None:
+            self.engine = self._build_engine(self.policy.model)
+            self.inference_engine_client = LocalInferenceClient([self.engine], self.tokenizer)
+        if self.generator is None:
+            self.generator = SkyRLGymGenerator(self.cfg.generator, self.cfg.environment.skyrl_gym,
+                                               self.inference_engine_client, self.tokenizer)
+
+    def _build_engine(self, model) -> LLMEngine:
+        g, ie, b = self.cfg.generator, self.cfg.generator.inference_engine, self.cfg.trainer.b200
+        max_len = (g.max_input_length or self.cfg.trainer.max_prompt_length) + g.sampling_params.max_generate_length
+        ecfg = EngineConfig(block_size=b.kv_block_size, gpu_memory_utilization=ie.gpu_memory_utilization,
+                            max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=max(ie.max_num_batched_tokens, max_len),
+                            max_model_len=max_len, enable_prefix_caching=ie.enable_prefix_caching,
+                            enforce_eager=ie.enforce_eager or not b.cuda_graph_decode, seed=self.cfg.trainer.seed + self.env.rank)
+        for k, v in (ie.engine_init_kwargs or {}).items():
+            if hasattr(ecfg, k):
+                setattr(ecfg, k, v)
+        eos = [self.tokenizer.eos_token_id] if self.tokenizer is not None and self.tokenizer.eos_token_id is not None else []
+        detok = (lambda ids: self.tokenizer.decode(ids, skip_special_tokens=False)) if self.tokenizer is not None else None
+        return LLMEngine(model, ecfg, eos_token_ids=eos, detokenize=detok)
+
+    # ------------------------------------------------------------------ data
+    def _local_prompts(self, global_batch: List[Dict[str, Any]]) -> List[Dict[str, Any]]:
+        """This rank's contiguous share of the global prompt batch (tail prompts dropped to keep shares equal)."""
+        W, r = self.env.world_size, self.env.rank
+        per = len(global_batch) // W
+        return global_batch[r * per : (r + 1) * per]
+
+    # ------------------------------------------------------------------ rollout
+    async def generate(self, gen_input: GeneratorInput) -> GeneratorOutput:
+        out = await self.generator.generate(gen_input)
+        n = len(out["response_ids"])
+        for key in ("prompt_token_ids", "rewards", "loss_masks"):
+            if len(out[key]) != n:
+                raise ValueError(f"generator output field '{key}' has {len(out[key])} rows, expected {n}")
+        return out
+
+    def postprocess_generator_output(self, out: GeneratorOutput, uids: List[str]) -> GeneratorOutput:
+        """Scalar rewards -> last response token; metrics; optional zero-variance filter
+        (reference: trainer.py:1013-1121)."""
+        a = self.cfg.trainer.algorithm
+        rewards = out["rewards"]
+        per_token: List[List[float]] = []
+        for r, resp in zip(rewards, out["response_ids"]):
+            if isinstance(r, (list, tuple)):
+                per_token.append([float(x) for x in r])
+            else:
+                row = [0.0] * len(resp)
+                if row:
+                    row[-1] = float(r)
+                per_token.append(row)
+        scores = np.array([sum(r) for r in per_token], dtype=np.float64)
+        m = {"reward/avg_raw_reward": float(scores.mean()) if len(scores) else 0.0,
+             "reward/avg_pass_at_{}".format(self.cfg.generator.n_samples_per_prompt): compute_pass_at_n(per_token, uids),
+             "reward/mean_positive_reward": float(scores[scores > 0].mean()) if (scores > 0).any() else 0.0}
+        if a.zero_variance_filter:
+            groups: Dict[str, List[int]] = {}
+            for i, u in enumerate(uids):
+                groups.setdefault(u, []).append(i)
+            masks = [list(x) for x in out["loss_masks"]]
+            dropped = 0
+            for idxs in groups.values():
+                live = [i for i in idxs if any(masks[i])]
+                if len(live) > 1 and float(np.ptp(scores[live])) <= a.zero_variance_filter_tol:
+                    for i in live:
+                        masks[i] = [0] * len(masks[i])
+                    dropped += 1
+            out["loss_masks"] = masks
+            m["reward/zero_variance_groups"] = float(dropped)
+        out["rewards"] = per_token
+        self.all_metrics.update(m)
+        if out.get("rollout_metrics"):
+            self.all_metrics.update(out["rollout_metrics"])
+        return out
+
+    def convert_to_training_input(self, out: GeneratorOutput, uids: List[str]) -> TrainingInputBatch:
+        pad_id = self.tokenizer.pad_token_id if self.tokenizer is not None and self.tokenizer.pad_token_id is not None else 0
+        seq, att, rmask, rew, lmask, lps = convert_prompts_responses_to_batch_tensors(
+            pad_id, out["prompt_token_ids"], out["response_ids"], out["rewards"], out["loss_masks"],
+            out.get("rollout_logprobs"), max_seq_len=self.cfg.trainer.algorithm.max_seq_len)
+        batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "rewards": rew,
+                                    "loss_mask": lmask, "rollout_logprobs": lps})
+        batch.metadata = {"uids": list(uids), "response_length": rmask.shape[1],
+                          "is_last_step": out.get("is_last_step"),
+                          "avg_response_length": float(rmask.sum(1).float().mean()),
+                          "trajectory_ids": [t.to_string() for t in out["trajectory_ids"]] if out.get("trajectory_ids") else None}
+        self.all_metrics["generate/avg_response_length"] = batch.metadata["avg_response_length"]
+        return batch
+
+    # ------------------------------------------------------------------ forward passes
+    def _skip_policy_forward(self) -> bool:
+        a = self.cfg.trainer.algorithm
+        return a.policy_loss_type in rl.LOSSES_WITHOUT_OLD_LOGPROBS and not rl.off_policy_correction_enabled_cfg(a)
+
+    def fwd_logprobs_values_reward(self, batch: TrainingInputBatch) -> TrainingInputBatch:
+        if self.critic is not None:
+            batch["values"] = self.critic.forward(batch)["output"]
+        if self.ref is not None:
+            batch["base_action_log_probs"] = self.ref.forward(batch)["output"]
+        if self._skip_policy_forward() and batch.get("rollout_logprobs") is not None:
+            batch["action_log_probs"] = batch["rollout_logprobs"].clone()
+        else:
+            batch["action_log_probs"] = self.policy.forward(batch)["output"]
+        if batch.get("rollout_logprobs") is not None:
+            d = (batch["action_log_probs"] - batch["rollout_logprobs"]).abs()
+            mk = batch["loss_mask"]
+            denom = mk.sum().clamp(min=1)
+            mean = float((d * mk).sum() / denom)
+            self.all_metrics["policy/rollout_train_logprobs_abs_diff_mean"] = mean
+            self.all_metrics["policy/rollout_train_logprobs_abs_diff_std"] = float(
+                ((((d - mean) ** 2) * mk).sum() / denom).sqrt())
+        return batch
+
+    def apply_reward_kl_penalty(self, batch: TrainingInputBatch) -> TrainingInputBatch:
+        """reward_t -= beta * KL_t (reference: trainer.py:1409-1464)."""
+        a = self.cfg.trainer.algorithm
+        kl = rl.compute_approx_kl(batch["action_log_probs"], batch["base_action_log_probs"], loss_mask=batch["loss_mask"],
+                                  kl_estimator_type=a.kl_estimator_type)
+        mk = batch["loss_mask"]
+        kl_mean = float(((kl * mk).sum(-1) / mk.sum(-1).clamp(min=1)).mean())
+        beta = self.kl_controller.value
+        batch["rewards"] = batch["rewards"] - beta * kl
+        self.kl_controller.update(kl_mean, n_steps=batch.batch_size)
+        self.all_metrics.update({"loss/avg_kl": kl_mean, "loss/avg_kl_max": float(kl.max()), "loss/kl_loss_coef": beta})
+        return batch
+
+    def compute_advantages_and_returns(self, batch: TrainingInputBatch) -> TrainingInputBatch:
+        a = self.cfg.trainer.algorithm
+        uids = np.array(batch.metadata["uids"], dtype=object)
+        rew, rmask = batch["rewards"], batch["response_mask"].float()
+        last = batch.metadata.get("is_last_step")
+        dev = self.env.device if self.env.device.type == "cuda" else torch.device("cpu")
+        if last is not None and self.cfg.generator.step_wise_trajectories:
+            # step-wise: estimate on the last step of each trajectory, broadcast to its earlier steps
+            last_t = torch.tensor(last, dtype=torch.bool)
+            tids = batch.metadata["trajectory_ids"]
+            adv_l, ret_l = rl.compute_advantages_and_returns(
+                rew[last_t].to(dev), rmask[last_t].to(dev), uids[last_t.numpy()], a.advantage_estimator, a,
+                values=batch["values"][last_t].to(dev) if batch.get("values") is not None else None,
+                grpo_norm_by_std=a.grpo_norm_by_std, gamma=a.gamma, lambd=a.lambd)
+            adv_l, ret_l = adv_l.cpu(), ret_l.cpu()
+            scalar = {}
+            k = 0
+            for i, is_last in enumerate(last):
+                if is_last:
+                    live = rmask[i] > 0
+                    scalar[tids[i]] = (float(adv_l[k][live[-adv_l.shape[1]:]].mean()) if live.any() else 0.0)
+                    k += 1
+            adv = torch.stack([rmask[i] * scalar.get(tids[i], 0.0) for i in range(len(last))])
+            ret = adv.clone()
+        else:
+            adv, ret = rl.compute_advantages_and_returns(
+                rew.to(dev), rmask.to(dev), uids, a.advantage_estimator, a,
+                values=batch["values"].to(dev) if batch.get("values") is not None else None,
+                grpo_norm_by_std=a.grpo_norm_by_std, gamma=a.gamma, lambd=a.lambd)
+            adv, ret = adv.cpu(), ret.cpu()
+        batch["advantages"], batch["returns"] = adv, ret
+        mk = batch["loss_mask"]
+        scores = rew.sum(-1)
+        self.all_metrics.update({
+            "reward/avg_rewards": float(scores.mean()),
+            "loss/avg_advantages": float((adv * mk).sum() / mk.sum().clamp(min=1)),
+            "loss/avg_advantages_abs": float((adv.abs() * mk).sum() / mk.sum().clamp(min=1)),
+        })
+        return batch
+
+    # ------------------------------------------------------------------ training
+    def _normalize_advantages(self, mini: TrainingInputBatch, boundaries=None) -> TrainingInputBatch:
+        """Optional batch z-score, then bake the loss reduction into the advantages (reference: trainer.py:1467-1507)."""
+        a, t = self.cfg.trainer.algorithm, self.cfg.trainer
+        adv, mk = mini["advantages"], mini["loss_mask"]
+        if a.advantage_batch_normalize:
+            n = mk.sum().clamp(min=1)
+            mean = (adv * mk).sum() / n
+            var = (((adv - mean) ** 2) * mk).sum() / n
+            adv = (adv - mean) * torch.rsqrt(var + 1e-8)
+        # token counts are global quantities: sum them across data-parallel ranks
+        W = self.env.world_size
+        if a.loss_reduction == "token_mean":
+            tot = mk.sum()
+            if dist.is_initialized() and W > 1:
+                tt = tot.to(self.env.device).clone()
+                dist.all_reduce(tt)
+                tot = tt.cpu()
+            mini["advantages"] = adv / tot.clamp(min=1)
+        else:
+            scaled = rl.apply_loss_reduction_to_advantages_minibatch(
+                adv, mk, a.loss_reduction, t.micro_train_batch_size_per_gpu, a.max_seq_len or adv.shape[1], boundaries)
+            mini["advantages"] = scaled / W
+        return mini
+
+    def _execute_training_step(self, role: str, batch: TrainingInputBatch) -> Dict[str, float]:
+        t = self.cfg.trainer
+        worker = self.policy if role == "policy" else self.critic
+        mini_prompts = (t.policy_mini_batch_size if role == "policy" else t.critic_mini_batch_size) // self.env.world_size
+        mini_prompts = max(1, mini_prompts)
+        uids = batch.metadata["uids"]
+        bounds = compute_prompt_mini_batch_boundaries(uids, mini_prompts)
+        all_status: List[Dict[str, float]] = []
+        for _epoch in range(t.update_epochs_per_batch):
+            for (s, e) in bounds:
+                mini = batch.slice(s, e)
+                mini.metadata = dict(batch.metadata)
+                mini.metadata["uids"] = uids[s:e]
+                if role == "policy":
+                    pb = [(a - s, b - s) for a, b in compute_prompt_boundaries(uids[s:e])]
+                    mini = self._normalize_advantages(mini, pb)
+                status = worker.forward_backward(mini)
+                gn = worker.optim_step()
+                if gn is not None:
+                    status["grad_norm"] = float(gn)
+                all_status.append({k: v for k, v in status.items() if isinstance(v, (int, float))})
+        keys = set().union(*[s.keys() for s in all_status]) if all_status else set()
+        return {k: float(np.mean([s[k] for s in all_status if k in s])) for k in keys}
+
+    def train_critic_and_policy(self, batch: TrainingInputBatch) -> Dict[str, float]:
+        m: Dict[str, float] = {}
+        if self.critic is not None:
+            with Timer("critic_train", self.all_timings):
+                for k, v in self._execute_training_step("critic", batch).items():
+                    m[f"critic/{k}"] = v
+        with Timer("policy_train", self.all_timings):
+            for k, v in self._execute_training_step("policy", batch).items():
+                m[f"policy/{k}"] = v
+        return m
+
+    def sync_weights(self) -> None:
+        """Make the freshly trained weights visible to the generation engine(s)."""
+        c = self.inference_engine_client
+        if hasattr(c, "increment_weight_version"):
+            c.increment_weight_version()
+
+    # ------------------------------------------------------------------ one RL step
+    async def train_step_async(self, prompts: List[Dict[str, Any]], prompt_token_ids=None) -> Dict[str, float]:
+        cfg = self.cfg
+        self.all_metrics, self.all_timings = {}, {}
+        t_step = time.time()
+        gen_input, uids = prepare_generator_input(prompts, cfg.generator.n_samples_per_prompt, None,
+                                                  cfg.environment.env_class, "train", self.global_step, prompt_token_ids)
+        with Timer("generate", self.all_timings):
+            out = await self.generate(gen_input)
+        if out.get("trajectory_ids") and len(out["response_ids"]) != len(uids):
+            uids = [t.instance_id for t in out["trajectory_ids"]]  # step-wise outputs have one row per step
+        with Timer("postprocess", self.all_timings):
+            out = self.postprocess_generator_output(out, uids)
+            batch = self.convert_to_training_input(out, uids)
+        with Timer("fwd_logprobs_values_reward", self.all_timings):
+            batch = self.fwd_logprobs_values_reward(batch)
+        if cfg.trainer.algorithm.use_kl_in_reward and self.ref is not None:
+            batch = self.apply_reward_kl_penalty(batch)
+        with Timer("compute_advantages_and_returns", self.all_timings):
+            batch = self.compute_advantages_and_returns(batch)
+        with Timer("train_critic_and_policy", self.all_timings):
+            self.all_metrics.update(self.train_critic_and_policy(batch))
+        with Timer("sync_weights", self.all_timings):
+            self.sync_weights()
+        n_tokens = int(batch["attention_mask"].sum())
+        n_gen = int(batch["response_mask"].sum())
+        self.all_timings["step"] = time.time() - t_step
+        tt = max(1e-9, self.all_timings.get("train_critic_and_policy", 0.0))
+        self.all_metrics["trainer/tokens_per_second_per_gpu"] = n_tokens / tt
+        self.all_metrics["trainer/num_tokens"] = float(n_tokens)
+        self.all_metrics["trainer/num_generated_tokens"] = float(n_gen)
+        self.global_step += 1
+        self.all_metrics["trainer/global_step"] = float(self.global_step)
+        metrics = dict(self.all_metrics)
+        metrics.update({f"timing/{k}": v for k, v in self.all_timings.items()})
+        self._last_batch = batch
+        return metrics
+
+    def train_step(self, prompts: List[Dict[str, Any]], prompt_token_ids=None) -> Dict[str, float]:
+        return asyncio.run(self.train_step_async(prompts, prompt_token_ids))
+
+    # ------------------------------------------------------------------ full loop
+    def train(self) -> None:
+        asyncio.run(self.train_async())
+
+    async def train_async(self) -> None:
+        t = self.cfg.trainer
+        assert self.train_dataset is not None, "train() needs a train_dataset"
+        self.train_iter = StatefulBatchIterator(self.train_dataset, t.train_batch_size, shuffle=True, seed=t.seed)
+        self.load_checkpoints()
+        if t.eval_before_train and self.eval_dataset is not None and self.global_step == 0:
+            self._log(await self.eval_async(), self.global_step)
+        total = t.epochs * len(self.train_iter)
+        if t.max_training_steps is not None:
+            total = min(total, t.max_training_steps)
+        for cb in self.callbacks:
+            cb.on_train_begin(self)
+        done = False
+        while self.train_iter.epoch < t.epochs and not done:
+            for global_batch in self.train_iter:
+                metrics = await self.train_step_async(self._local_prompts(global_batch))
+                if t.eval_interval > 0 and self.eval_dataset is not None and self.global_step % t.eval_interval == 0:
+                    metrics.update(await self.eval_async())
+                self._log(metrics, self.global_step)
+                for cb in self.callbacks:
+                    cb.on_step_end(self, metrics)
+                if t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0:
+                    self.save_checkpoints()
+                if t.hf_save_interval > 0 and self.global_step % t.hf_save_interval == 0:
+                    self.save_models()
+                if self.global_step >= total:
+                    done = True
+                    break
+            if t.update_ref_every_epoch and self.ref is not None:
+                self.update_ref_with_policy()
+        if t.ckpt_interval > 0:
+            self.save_checkpoints()
+        for cb in self.callbacks:
+            cb.on_train_end(self)
+
+    def _log(self, metrics: Dict[str, float], step: int) -> None:
+        if self.tracker is not None and self.env.is_main:
+            self.tracker.log(metrics, step)
+
+    async def eval_async(self) -> Dict[str, float]:
+        from .evaluate import evaluate
+
+        return await evaluate(self.eval_dataset, self.generator, self.cfg, self.global_step, self.tokenizer, self.env)
+
+    def eval(self) -> Dict[str, float]:
+        return asyncio.run(self.eval_async())
+
+    def update_ref_with_policy(self) -> None:
+        self.ref.backload()
+        self.ref.model.flat_params.copy_(self.policy.model.flat_params)
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoints(self) -> None:
+        """``{ckpt_path}/global_step_N/{policy,critic}/`` + ``data.pt`` + ``trainer_state.pt``; pointer written last."""
+        t = self.cfg.trainer
+        d = os.path.join(t.ckpt_path, f"{tutils.GLOBAL_STEP_PREFIX}{self.global_step}")
+        os.makedirs(d, exist_ok=True)
+        self.policy.save_checkpoint(os.path.join(d, "policy"), tag=str(self.global_step))
+        if self.critic is not None:
+            self.critic.save_checkpoint(os.path.join(d, "critic"), tag=str(self.global_step))
+        if self.env.is_main:
+            if self.train_iter is not None:
+                torch.save(self.train_iter.state_dict(), os.path.join(d, "data.pt"))
+            torch.save({"global_step": self.global_step, "config": self.cfg.to_dict()}, os.path.join(d, "trainer_state.pt"))
+        if dist.is_initialized():
+            dist.barrier()
+        if self.env.is_main:
+            tutils.write_latest(t.ckpt_path, self.global_step)
+            tutils.cleanup_old_checkpoints(t.ckpt_path, t.max_ckpts_to_keep, self.global_step)
+
+    def load_checkpoints(self) -> int:
+        d = tutils.resolve_resume_path(self.cfg.trainer)
+        if d is None:
+            return 0
+        state = torch.load(os.path.join(d, "trainer_state.pt"), weights_only=False)
+        step_from_dir = int(os.path.basename(os.path.normpath(d))[len(tutils.GLOBAL_STEP_PREFIX):])
+        if state["global_step"] != step_from_dir:
+            raise ValueError(f"checkpoint {d} is inconsistent: trainer_state says step {state['global_step']}")
+        self.policy.load_checkpoint(os.path.join(d, "policy"))
+        if self.critic is not None and os.path.isdir(os.path.join(d, "critic")):
+            self.critic.load_checkpoint(os.path.join(d, "critic"))
+        if self.train_iter is not None and os.path.exists(os.path.join(d, "data.pt")):
+            self.train_iter.load_state_dict(torch.load(os.path.join(d, "data.pt"), weights_only=False))
+        self.global_step = int(state["global_step"])
+        self.sync_weights()
+        return self.global_step
+
+    def save_models(self) -> None:
+        d = os.path.join(self.cfg.trainer.export_path, f"{tutils.GLOBAL_STEP_PREFIX}{self.global_step}", "policy")
+        self.policy.save_hf_model(d, self.tokenizer)
+
+
+# familiar name for users of the reference
+RayPPOTrainer = PPOTrainer

@@ -1,0 +1,474 @@
+"""Training workers: policy, critic and reference model replicas running SPMD, one process per GPU.
+
+The verbs are the reference's (skyrl/backends/skyrl_train/workers/worker.py:831-1639):
+``forward`` (log-probs or values, no grad), ``forward_backward`` (micro-batch loop with gradient
+accumulation), ``optim_step``, ``set_lr``, checkpoint verbs, offload/backload.  What differs is
+where the work happens: a worker receives *its own shard* of the batch (built on the same rank by
+the controller), packs it to tokens, runs the packed model, and reads log-probabilities from the
+fused LM-head kernel only at the positions that predict response tokens.  Gradients accumulate into
+one flat fp32 buffer that the sharded optimizer reduces across ranks once per step, so there is no
+per-layer collective and no ``dp_size`` loss-scaling trick: ranks *sum* their pre-scaled losses.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..algorithms import rl
+from ..models.decoder import CausalLM, build_model
+from ..ops import _lib
+from ..parallel.dist import DistEnv, get_env
+from ..parallel.sharded_optimizer import ShardedAdamW, get_scheduler
+from ..train.batch import TrainingInputBatch, TrainingOutputBatch
+from ..train.preprocess import PackedView, pack_batch
+from ..utils.torch_utils import masked_mean
+
+
+# ----------------------------------------------------------------------------- micro-batching
+def microbatch_indices(seq_lens: Sequence[int], micro_batch_size: int, max_tokens: int) -> List[List[int]]:
+    """Row-index groups: by token budget (balanced bins, C++ runtime) when ``max_tokens > 0``, else by count.
+
+    Reference: ``max_tokens_per_microbatch`` / ``micro_*_batch_size_per_gpu`` handling in
+    skyrl/backends/skyrl_train/workers/worker_utils.py:248-444.
+    """
+    n = len(seq_lens)
+    if n == 0:
+        return []
+    if max_tokens is not None and max_tokens > 0:
+        lens = np.asarray(seq_lens, dtype=np.int32)
+        budget = max(int(max_tokens), int(lens.max()))
+        out = np.zeros(n, dtype=np.int32)
+        rt = _lib.runtime()
+        rt.sbrt_balanced_bins.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        bins = rt.sbrt_balanced_bins(lens.ctypes.data, n, budget, out.ctypes.data)
+        groups: List[List[int]] = [[] for _ in range(bins)]
+        for i, b in enumerate(out.tolist()):
+            groups[b].append(i)
+        return [g for g in groups if g]
+    mbs = max(1, micro_batch_size)
+    return [list(range(s, min(n, s + mbs))) for s in range(0, n, mbs)]
+
+
+def sync_num_microbatches(n_local: int, env: DistEnv) -> int:
+    """All ranks must run the same number of micro-batches (collectives inside the model); take the MAX."""
+    if not dist.is_initialized() or env.world_size == 1:
+        return n_local
+    t = torch.tensor([n_local], device=env.device, dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return int(t.item())
+
+
+def reduce_metrics(metrics_list: List[Dict[str, float]]) -> Dict[str, float]:
+    """Combine per-micro-batch metrics: ``*_loss`` / ``loss`` summed, ``*_min`` / ``*_max`` min/max, others averaged."""
+    if not metrics_list:
+        return {}
+    keys = set().union(*[m.keys() for m in metrics_list])
+    out = {}
+    for k in keys:
+        vals = [m[k] for m in metrics_list if k in m and isinstance(m[k], (int, float))]
+        if not vals:
+            continue
+        if k.endswith("_min"):
+            out[k] = min(vals)
+        elif k.endswith("_max"):
+            out[k] = max(vals)
+        elif k.endswith("loss") or k.endswith("_loss_sum"):
+            out[k] = float(sum(vals))
+        else:
+            out[k] = float(sum(vals) / len(vals))
+    return out
+
+
+def all_reduce_metrics(metrics: Dict[str, float], env: DistEnv) -> Dict[str, float]:
+    if not dist.is_initialized() or env.world_size == 1 or not metrics:
+        return metrics
+    keys = sorted(metrics)
+    sums = torch.tensor([metrics[k] for k in keys], device=env.device, dtype=torch.float64)
+    mins, maxs = sums.clone(), sums.clone()
+    dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    dist.all_reduce(mins, op=dist.ReduceOp.MIN)
+    dist.all_reduce(maxs, op=dist.ReduceOp.MAX)
+    out = {}
+    for i, k in enumerate(keys):
+        if k.endswith("_min"):
+            out[k] = float(mins[i])
+        elif k.endswith("_max"):
+            out[k] = float(maxs[i])
+        elif k.endswith("loss") or k.endswith("_loss_sum"):
+            out[k] = float(sums[i])
+        else:
+            out[k] = float(sums[i]) / env.world_size
+    return out
+
+
+# ----------------------------------------------------------------------------- worker
+class ModelWorker:
+    role = "model"
+
+    def __init__(self, cfg, model: Optional[CausalLM] = None, model_path: Optional[str] = None, env: Optional[DistEnv] = None,
+                 trainable: bool = True, value_head: bool = False, optimizer_cfg=None, peer_ctx=None,
+                 flat_buffer: Optional[torch.Tensor] = None, flat_grad: Optional[torch.Tensor] = None, seed: int = 0):
+        self.cfg = cfg  # TrainerConfig
+        self.env = env or get_env()
+        dev = self.env.device
+        dtype = torch.bfloat16 if (cfg.bf16 and dev.type == "cuda") else torch.float32
+        if model is None:
+            model = build_model(model_path, device=dev, dtype=dtype, value_head=value_head, seed=seed)
+        self.model = model
+        self.model.gradient_checkpointing = bool(cfg.gradient_checkpointing) and trainable
+        self.trainable = trainable
+        self.optimizer: Optional[ShardedAdamW] = None
+        self.scheduler = None
+        self._on_device = True
+        self._offloaded: Dict[str, torch.Tensor] = {}
+        self.num_microbatches_accumulated = 0
+        if trainable:
+            ocfg = optimizer_cfg
+            if flat_grad is None:
+                flat_grad = torch.zeros(model.flat_params.numel(), device=dev, dtype=torch.float32)
+            model.attach_main_grad(flat_grad)
+            self.flat_grad = flat_grad
+            self.optimizer = ShardedAdamW(model.flat_params, flat_grad, lr=ocfg.lr, betas=tuple(ocfg.adam_betas),
+                                          weight_decay=ocfg.weight_decay, max_grad_norm=ocfg.max_grad_norm,
+                                          peer_ctx=peer_ctx)
+            self.scheduler = get_scheduler(ocfg.scheduler, self.optimizer, ocfg.num_warmup_steps, base_lr=ocfg.lr)
+
+    # ------------------------------------------------------------------ helpers
+    def _max_tokens(self) -> int:
+        return int(self.cfg.max_tokens_per_microbatch or -1)
+
+    def _seq_lens(self, batch: TrainingInputBatch) -> List[int]:
+        return batch["attention_mask"].sum(1).tolist()
+
+    def _pack(self, batch: TrainingInputBatch, rows: List[int]) -> PackedView:
+        idx = torch.tensor(rows, dtype=torch.long)
+        return pack_batch(batch["sequences"][idx], batch["attention_mask"][idx], batch["response_mask"][idx],
+                          self.env.device)
+
+    def _rows_to_device(self, t: Optional[torch.Tensor], rows: List[int]) -> Optional[torch.Tensor]:
+        if t is None:
+            return None
+        return t[torch.tensor(rows, dtype=torch.long)].to(self.env.device, non_blocking=True)
+
+    def _hidden(self, pv: PackedView) -> torch.Tensor:
+        return self.model(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen)
+
+    # ------------------------------------------------------------------ forward (no grad)
+    @torch.no_grad()
+    def forward(self, batch: TrainingInputBatch) -> TrainingOutputBatch:
+        """Log-probabilities (policy/ref) or values (critic) on the right-aligned response grid ``[B, R]``."""
+        self.backload()
+        B, R = batch["response_mask"].shape
+        out = torch.zeros((B, R), dtype=torch.float32)
+        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_forward_batch_size_per_gpu, self._max_tokens())
+        n_mb = sync_num_microbatches(len(groups), self.env)
+        temp = float(self.cfg.algorithm.temperature or 1.0)
+        was_ckpt = self.model.gradient_checkpointing
+        self.model.gradient_checkpointing = False
+        for k in range(n_mb):
+            rows = groups[k] if k < len(groups) else groups[-1]  # padding micro-batch keeps collectives aligned
+            pv = self._pack(batch, rows)
+            h = self._hidden(pv)
+            if pv.pred_index.numel() == 0:
+                continue
+            hs = h[pv.pred_index]
+            vals = self.model.values(hs) if self.role == "critic" else self.model.token_logprobs(hs, pv.targets, temp)[0]
+            if k < len(groups):
+                grid = pv.scatter_to_grid(vals.float()).cpu()
+                out[torch.tensor(rows, dtype=torch.long)] = grid
+        self.model.gradient_checkpointing = was_ckpt
+        return TrainingOutputBatch({"output": out})
+
+    # ------------------------------------------------------------------ state movement (colocation)
+    def offload(self, include_optimizer: bool = True, include_params: bool = True) -> None:
+        """Move parameters / optimizer state to pinned host memory (colocated GPU sharing)."""
+        if self.env.device.type != "cuda":
+            return
+        if include_optimizer and self.optimizer is not None:
+            self.optimizer.offload()
+        if include_params and self._on_device and not self.trainable:
+            host = torch.empty(self.model.flat_params.shape, dtype=self.model.flat_params.dtype, pin_memory=True)
+            host.copy_(self.model.flat_params)
+            self._offloaded["params"] = host
+            # keep the storage object (views must stay valid): shrink it to zero bytes
+            self.model.flat_params.untyped_storage().resize_(0)
+            self._on_device = False
+        torch.cuda.empty_cache()
+
+    def backload(self, include_optimizer: bool = True) -> None:
+        if self.env.device.type != "cuda":
+            return
+        if not self._on_device:
+            host = self._offloaded.pop("params")
+            st = self.model.flat_params.untyped_storage()
+            st.resize_(host.numel() * host.element_size())
+            self.model.flat_params.copy_(host, non_blocking=True)
+            self._on_device = True
+        if include_optimizer and self.optimizer is not None:
+            self.optimizer.backload()
+
+    # ------------------------------------------------------------------ optimizer
+    def optim_step(self) -> Optional[float]:
+        """Reduce gradients across ranks, clip, AdamW, LR schedule, zero grads. Returns the gradient norm."""
+        assert self.optimizer is not None
+        self.backload()
+        scale = 1.0
+        if self.role == "critic" and self.num_microbatches_accumulated > 0:
+            scale = 1.0 / self.num_microbatches_accumulated  # reference: worker.py:1513-1537
+        norm = self.optimizer.step(grad_scale=scale)
+        self.scheduler.step()
+        self.optimizer.zero_grad()
+        self.num_microbatches_accumulated = 0
+        return norm
+
+    def set_lr(self, lr: float) -> None:
+        self.optimizer.set_lr(lr)
+
+    def get_lr(self) -> float:
+        return self.optimizer.lr
+
+    # ------------------------------------------------------------------ checkpoints (FSDP-style per-rank layout)
+    def save_checkpoint(self, ckpt_dir: str, tag: Optional[str] = None, client_state: Optional[dict] = None) -> None:
+        """Per-rank files ``{model,optim,extra_state}_world_size_{W}_rank_{r}.pt`` (+ ``huggingface/`` on rank 0).
+
+        File naming follows the reference layout (fsdp_strategy.py:391-444); the model file holds this rank's
+        contiguous slice of the flat parameter buffer instead of pickled DTensors.
+        """
+        os.makedirs(ckpt_dir, exist_ok=True)
+        W, r = self.env.world_size, self.env.rank
+        n = self.model.flat_params.numel()
+        shard = n // W
+        lo = r * shard
+        torch.save({"flat_shard": self.model.flat_params[lo : lo + shard].cpu(), "offset": lo, "numel": n,
+                    "specs": self.model.specs}, os.path.join(ckpt_dir, f"model_world_size_{W}_rank_{r}.pt"))
+        if self.optimizer is not None:
+            sd = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in self.optimizer.state_dict().items()}
+            torch.save(sd, os.path.join(ckpt_dir, f"optim_world_size_{W}_rank_{r}.pt"))
+        extra = {"lr_scheduler": self.scheduler.state_dict() if self.scheduler else None, "client_state": client_state or {},
+                 "tag": tag, "fsdp_strategy": "flat_zero", "world_size": W, "rank": r,
+                 "rng": {"torch": torch.get_rng_state(), "numpy": np.random.get_state(),
+                         "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None}}
+        torch.save(extra, os.path.join(ckpt_dir, f"extra_state_world_size_{W}_rank_{r}.pt"))
+        if r == 0:
+            import json
+
+            hf_dir = os.path.join(ckpt_dir, "huggingface")
+            os.makedirs(hf_dir, exist_ok=True)
+            with open(os.path.join(hf_dir, "config.json"), "w") as f:
+                json.dump(self.model.args.to_hf_config(), f, indent=1)
+            with open(os.path.join(ckpt_dir, "fsdp_config.json"), "w") as f:
+                json.dump({"FSDP_version": 2, "world_size": W, "layout": "flat_zero"}, f)
+        if dist.is_initialized():
+            dist.barrier()
+
+    def load_checkpoint(self, ckpt_dir: str, load_optimizer_states: bool = True, load_lr_scheduler_states: bool = True):
+        W, r = self.env.world_size, self.env.rank
+        path = os.path.join(ckpt_dir, f"model_world_size_{W}_rank_{r}.pt")
+        if not os.path.exists(path):
+            have = sorted(f for f in os.listdir(ckpt_dir) if f.startswith("model_world_size_"))
+            raise FileNotFoundError(f"{path} not found (checkpoint was written for a different world size? found: {have})")
+        n = self.model.flat_params.numel()
+        # every rank needs the full parameter buffer: read all ranks' slices
+        for rr in range(W):
+            d = torch.load(os.path.join(ckpt_dir, f"model_world_size_{W}_rank_{rr}.pt"), weights_only=False)
+            assert d["numel"] == n, "checkpoint parameter layout differs from the model"
+            self.model.flat_params[d["offset"] : d["offset"] + d["flat_shard"].numel()].copy_(d["flat_shard"])
+        if self.optimizer is not None and load_optimizer_states:
+            sd = torch.load(os.path.join(ckpt_dir, f"optim_world_size_{W}_rank_{r}.pt"), weights_only=False)
+            self.optimizer.load_state_dict(sd)
+        extra = torch.load(os.path.join(ckpt_dir, f"extra_state_world_size_{W}_rank_{r}.pt"), weights_only=False)
+        if self.scheduler is not None and load_lr_scheduler_states and extra.get("lr_scheduler"):
+            self.scheduler.load_state_dict(extra["lr_scheduler"])
+        rng = extra.get("rng") or {}
+        if rng.get("torch") is not None:
+            torch.set_rng_state(rng["torch"])
+        if rng.get("numpy") is not None:
+            np.random.set_state(rng["numpy"])
+        if rng.get("cuda") is not None and torch.cuda.is_available():
+            torch.cuda.set_rng_state(rng["cuda"])
+        return ckpt_dir, extra.get("client_state", {})
+
+    def save_hf_model(self, export_dir: str, tokenizer=None) -> None:
+        from ..models import hf_io
+
+        if self.env.rank == 0:
+            hf_io.save_hf_model(self.model, export_dir, tokenizer)
+        if dist.is_initialized():
+            dist.barrier()
+
+
+class RefWorker(ModelWorker):
+    role = "ref"
+
+    def __init__(self, cfg, **kw):
+        super().__init__(cfg, trainable=False, **kw)
+
+
+class PolicyWorker(ModelWorker):
+    role = "policy"
+
+    def __init__(self, cfg, **kw):
+        super().__init__(cfg, trainable=True, optimizer_cfg=cfg.policy.optimizer_config, **kw)
+
+    def forward_backward(self, batch: TrainingInputBatch, loss_fn: Optional[str] = None,
+                         loss_fn_config: Optional[dict] = None, return_per_token_outputs: bool = False) -> Dict[str, Any]:
+        """One mini-batch: micro-batch loop accumulating gradients. Advantages must already be reduction-scaled."""
+        self.backload()
+        algo = self.cfg.algorithm
+        if loss_fn_config:
+            import copy
+
+            algo = copy.deepcopy(algo)
+            for k, v in loss_fn_config.items():
+                setattr(algo, k, v)
+        loss_name = loss_fn or algo.policy_loss_type
+        loss_name = {"ppo": "regular"}.get(loss_name, loss_name)
+        if loss_name != algo.policy_loss_type:
+            import copy
+
+            algo = copy.deepcopy(algo)
+            algo.policy_loss_type = loss_name
+        loss_func = rl.PolicyLossRegistry.get(loss_name)
+        dev = self.env.device
+        B, R = batch["response_mask"].shape
+        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens())
+        n_mb = sync_num_microbatches(len(groups), self.env)
+        world = self.env.world_size
+        temp = float(algo.temperature or 1.0)
+        use_kl = bool(algo.use_kl_loss) and batch.get("base_action_log_probs") is not None and loss_name != "cross_entropy"
+        use_ent = bool(algo.use_entropy_loss) and loss_name != "cross_entropy"
+        fused = dev.type == "cuda" and rl.fused_objective_supported(algo) and loss_name in ("regular", "dual_clip") \
+            and not return_per_token_outputs
+        all_metrics: List[Dict[str, float]] = []
+        per_row_logprobs = torch.zeros((B, R), dtype=torch.float32) if return_per_token_outputs else None
+        for k in range(n_mb):
+            real = k < len(groups)
+            rows = groups[k] if real else groups[-1]
+            pv = self._pack(batch, rows)
+            h = self._hidden(pv)
+            hs = h[pv.pred_index]
+            lp, ent = self.model.token_logprobs(hs, pv.targets, temp, with_entropy=use_ent)
+            weight = len(rows) / max(1, B * world)  # KL / entropy terms: mean over the global mini-batch
+            g = lambda key: self._rows_to_device(batch.get(key), rows)  # noqa: E731
+            mask_g, adv_g = g("loss_mask"), g("advantages")
+            old_g, ref_g, roll_g = g("action_log_probs"), g("base_action_log_probs"), g("rollout_logprobs")
+            if old_g is None:
+                old_g = pv.scatter_to_grid(lp.detach().float())
+            m: Dict[str, float] = {}
+            if fused:
+                mask_f = pv.gather_from_grid(mask_g)
+                klw = None
+                if use_kl:
+                    per_seq = mask_g.sum(-1, keepdim=True).clamp(min=1.0) * len(rows)
+                    klw = pv.gather_from_grid((1.0 / per_seq).expand_as(mask_g))
+                total, stats = rl.FusedPolicyObjective.apply(
+                    lp.float(), pv.gather_from_grid(old_g), pv.gather_from_grid(adv_g), mask_f,
+                    pv.gather_from_grid(ref_g) if use_kl else None, None, klw, algo.eps_clip_low, algo.eps_clip_high,
+                    algo.clip_ratio_c, loss_name == "dual_clip", algo.kl_estimator_type, 1.0,
+                    algo.kl_loss_coef * weight if use_kl else 0.0)
+                loss = total
+                entropy_mean = None
+                if ent is not None:
+                    entropy_mean = (ent.float() * mask_f).sum() / mask_f.sum().clamp(min=1.0)
+                    if use_ent:
+                        loss = loss - algo.entropy_loss_coef * weight * entropy_mean
+                st = stats.detach()
+                m.update(policy_loss=float(st[0]), policy_kl=float(st[2]) if use_kl else 0.0,
+                         **{"loss_metrics/clip_ratio": float(st[1] / st[3].clamp(min=1.0))})
+                if entropy_mean is not None:
+                    m["policy_entropy"] = float(entropy_mean.detach())
+            else:
+                lp_grid = pv.scatter_to_grid(lp.float())
+                policy_loss, lm = loss_func(lp_grid, old_g, adv_g if adv_g is not None else torch.zeros_like(lp_grid),
+                                            algo, loss_mask=mask_g, rollout_logprobs=roll_g)
+                loss = policy_loss
+                m["policy_loss"] = float(policy_loss.detach())
+                m.update({"loss_metrics/" + kk: float(vv) for kk, vv in lm.items()})
+                if loss_name != "cross_entropy":
+                    if ent is not None:
+                        ent_grid = pv.scatter_to_grid(ent.float())
+                        entropy_mean = masked_mean(ent_grid, mask_g)
+                        m["policy_entropy"] = float(entropy_mean.detach())
+                        if use_ent:
+                            loss = loss - algo.entropy_loss_coef * weight * entropy_mean
+                    if use_kl:
+                        kl = rl.compute_approx_kl(lp_grid, ref_g, loss_mask=mask_g, kl_estimator_type=algo.kl_estimator_type)
+                        kl_mean = masked_mean(kl, mask_g, dim=-1).mean()
+                        loss = loss + algo.kl_loss_coef * weight * kl_mean
+                        m["policy_kl"] = float(kl_mean.detach())
+                if per_row_logprobs is not None and real:
+                    per_row_logprobs[torch.tensor(rows, dtype=torch.long)] = lp_grid.detach().cpu()
+            if not real:
+                loss = loss * 0.0
+            loss.backward()
+            if real:
+                m["final_loss"] = float(loss.detach())
+                if roll_g is not None:
+                    d = (pv.scatter_to_grid(lp.detach().float()) - roll_g).abs()
+                    m["rollout_train_logprobs_abs_diff_mean"] = float(masked_mean(d, mask_g))
+                all_metrics.append(m)
+            self.num_microbatches_accumulated += 1
+        status = reduce_metrics(all_metrics)
+        status = all_reduce_metrics(status, self.env)
+        status["policy_lr"] = self.optimizer.lr
+        status["response_length"] = R
+        if per_row_logprobs is not None:
+            rm = batch["response_mask"]
+            lm_ = batch.get("loss_mask")
+            outs = []
+            for i in range(B):
+                n = int(rm[i].sum())
+                row = per_row_logprobs[i, R - n:].tolist() if n else []
+                o = {"logprobs": row}
+                if loss_name == "cross_entropy":
+                    w = lm_[i, R - n:].tolist() if (lm_ is not None and n) else [1.0] * n
+                    o["elementwise_loss"] = [-a * b for a, b in zip(row, w)]
+                outs.append(o)
+            status["loss_fn_outputs"] = outs
+        return status
+
+
+class CriticWorker(ModelWorker):
+    role = "critic"
+
+    def __init__(self, cfg, **kw):
+        super().__init__(cfg, trainable=True, value_head=True, optimizer_cfg=cfg.critic.optimizer_config, **kw)
+
+    def forward_backward(self, batch: TrainingInputBatch, **_unused) -> Dict[str, Any]:
+        """Clipped value loss over the mini-batch; gradients are averaged over micro-batches at ``optim_step``."""
+        self.backload()
+        algo = self.cfg.algorithm
+        B, R = batch["response_mask"].shape
+        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens())
+        n_mb = sync_num_microbatches(len(groups), self.env)
+        all_metrics = []
+        for k in range(n_mb):
+            real = k < len(groups)
+            rows = groups[k] if real else groups[-1]
+            pv = self._pack(batch, rows)
+            h = self._hidden(pv)
+            v = self.model.values(h[pv.pred_index])
+            v_grid = pv.scatter_to_grid(v)
+            g = lambda key: self._rows_to_device(batch.get(key), rows)  # noqa: E731
+            loss, clipfrac = rl.ppo_critic_loss(v_grid, g("values"), g("returns"), algo, loss_mask=g("loss_mask"))
+            if not real:
+                loss = loss * 0.0
+            (loss / max(1, self.env.world_size)).backward()
+            if real:
+                mk = g("loss_mask")
+                all_metrics.append({"critic_loss": float(loss.detach()), "values_mean": float(masked_mean(v_grid.detach(), mk)),
+                                    "values_clipfrac": float(clipfrac or 0.0)})
+            self.num_microbatches_accumulated += 1
+        st = reduce_metrics(all_metrics)
+        if "critic_loss" in st and all_metrics:
+            st["critic_loss"] = st["critic_loss"] / len(all_metrics)
+        st = all_reduce_metrics(st, self.env)
+        st["critic_lr"] = self.optimizer.lr
+        return st

@@ -1,0 +1,108 @@
+"""Generation engine on CPU: paged decode must reproduce full-recompute greedy decoding and log-probs."""
+import torch
+
+from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine, SamplingParams
+from skyrl_b200.models.decoder import CausalLM, ModelArgs
+
+
+def _model():
+    args = ModelArgs(vocab_size=97, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16,
+                     intermediate_size=96, tie_word_embeddings=True, attention_bias=True, max_position_embeddings=256)
+    return CausalLM(args, dtype=torch.float32, seed=11)
+
+
+def _naive_greedy(m, prompt, n):
+    toks = list(prompt)
+    lps = []
+    for _ in range(n):
+        ids = torch.tensor(toks)
+        pos = torch.arange(len(toks), dtype=torch.int32)
+        cu = torch.tensor([0, len(toks)], dtype=torch.int32)
+        with torch.no_grad():
+            z = m.logits(m(ids, pos, cu, len(toks)))[-1].float()
+        t = int(z.argmax())
+        lps.append(float(torch.log_softmax(z, -1)[t]))
+        toks.append(t)
+    return toks[len(prompt):], lps
+
+
+def test_greedy_matches_full_recompute_and_slots_recycle():
+    m = _model()
+    eng = LLMEngine(m, EngineConfig(block_size=4, max_num_seqs=3, max_model_len=64, max_num_batched_tokens=64,
+                                    sync_interval=3, enforce_eager=True))
+    prompts = [[5, 6, 7, 8, 9], [10, 11], [3] * 9, [20, 21, 22], [40]]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=7, temperature=0.0))
+    for p, o in zip(prompts, outs):
+        ref_t, ref_l = _naive_greedy(m, p, 7)
+        assert o.token_ids == ref_t, (p, o.token_ids, ref_t)
+        assert torch.allclose(torch.tensor(o.logprobs), torch.tensor(ref_l), atol=1e-4)
+        assert o.finish_reason == "length"
+    assert not eng.has_unfinished()
+    assert eng.metrics()["kv_free_blocks"] == eng.num_blocks
+
+
+def test_eos_stops_and_per_request_lengths():
+    m = _model()
+    ref_t, _ = _naive_greedy(m, [1, 2, 3], 6)
+    eos = ref_t[3]
+    eng = LLMEngine(m, EngineConfig(block_size=4, max_num_seqs=4, max_model_len=64, sync_interval=2, enforce_eager=True),
+                    eos_token_ids=[eos])
+    o1, o2 = eng.generate([[1, 2, 3], [1, 2, 3]], [SamplingParams(max_tokens=6, temperature=0.0),
+                                                    SamplingParams(max_tokens=2, temperature=0.0)])
+    first = ref_t.index(eos)
+    assert o1.token_ids == ref_t[: first + 1] and o1.finish_reason == "stop"
+    assert o2.token_ids == ref_t[: min(2, first + 1)]
+    assert o2.finish_reason == ("stop" if first < 2 else "length")
+
+
+def test_sampling_is_seeded_and_logprobs_are_consistent():
+    m = _model()
+    cfg = EngineConfig(block_size=8, max_num_seqs=8, max_model_len=64, enforce_eager=True, seed=3)
+    a = LLMEngine(m, cfg).generate([[4, 5, 6]] * 4, SamplingParams(max_tokens=5, temperature=1.0))
+    b = LLMEngine(m, cfg).generate([[4, 5, 6]] * 4, SamplingParams(max_tokens=5, temperature=1.0))
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    assert len({tuple(o.token_ids) for o in a}) > 1
+    for o in a:  # the reported logprob is the model's logprob of the sampled token
+        toks = [4, 5, 6] + o.token_ids
+        ids = torch.tensor(toks)
+        with torch.no_grad():
+            z = m.logits(m(ids, torch.arange(len(toks), dtype=torch.int32), torch.tensor([0, len(toks)], dtype=torch.int32),
+                           len(toks))).float()
+        lp = torch.log_softmax(z, -1)
+        want = [float(lp[2 + i, t]) for i, t in enumerate(o.token_ids)]
+        assert torch.allclose(torch.tensor(o.logprobs), torch.tensor(want), atol=1e-4)
+
+
+def test_pause_keep_resume_and_abort():
+    m = _model()
+    eng = LLMEngine(m, EngineConfig(block_size=4, max_num_seqs=2, max_model_len=64, sync_interval=2, enforce_eager=True))
+    ref_t, _ = _naive_greedy(m, [9, 8, 7], 10)
+    eng.add_request("a", [9, 8, 7], SamplingParams(max_tokens=10, temperature=0.0))
+    eng.step()
+    eng.pause("keep")
+    assert eng.step() == [] and eng.has_unfinished()
+    eng.resume()
+    outs = []
+    while eng.has_unfinished():
+        outs += eng.step()
+    assert outs[0].token_ids == ref_t
+    eng.add_request("b", [9, 8, 7], SamplingParams(max_tokens=10, temperature=0.0))
+    eng.step()
+    part = eng.pause("abort")
+    assert part[0].finish_reason == "abort" and part[0].token_ids == ref_t[: len(part[0].token_ids)]
+    assert 0 < len(part[0].token_ids) < 10
+
+
+def test_top_k_one_equals_greedy_and_requeue_after_kv_reset():
+    m = _model()
+    eng = LLMEngine(m, EngineConfig(block_size=4, max_num_seqs=2, max_model_len=64, sync_interval=2, enforce_eager=True))
+    ref_t, _ = _naive_greedy(m, [2, 4, 6, 8], 8)
+    (o,) = eng.generate([[2, 4, 6, 8]], SamplingParams(max_tokens=8, temperature=1.0, top_k=1))
+    assert o.token_ids == ref_t
+    eng.add_request("x", [2, 4, 6, 8], SamplingParams(max_tokens=8, temperature=0.0))
+    eng.step()
+    eng.reset_prefix_cache(reset_running_requests=True)  # weights changed mid-flight: KV dropped, tokens kept
+    outs = []
+    while eng.has_unfinished():
+        outs += eng.step()
+    assert outs[0].token_ids == ref_t and len(outs[0].logprobs) == 8
