@@ -191,6 +191,7 @@ class LLMEngine:
         self.sampled_lp = torch.zeros(S, device=dev, dtype=torch.float32)
         self._state_ptrs = None
         self._graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
+        self._graph_launches: Dict[int, int] = {}
         self._graph_pool = None
         self._slot_req: List[Optional[_Request]] = [None] * S
         self._free_slots = list(range(S - 1, -1, -1))
@@ -386,15 +387,15 @@ class LLMEngine:
             req.slot = slot
             self._slot_req[slot] = req
             rows.append(slot)
-            self.block_tables[slot].copy_(torch.from_numpy(bt))
+            self.block_tables[slot].copy_(_lib.to_device(torch.from_numpy(bt), dev))
             ids.extend(toks)
             pos.extend(range(L))
             slot_list.extend((bt[np.arange(L) // bs] * bs + np.arange(L) % bs).tolist())
             cu.append(cu[-1] + L)
-        t_ids = torch.tensor(ids, device=dev, dtype=torch.int32)
-        t_pos = torch.tensor(pos, device=dev, dtype=torch.int32)
-        t_slots = torch.tensor(slot_list, device=dev, dtype=torch.int32)
-        t_cu = torch.tensor(cu, device=dev, dtype=torch.int32)
+        t_ids = _lib.to_device(torch.tensor(ids, dtype=torch.int32), dev)
+        t_pos = _lib.to_device(torch.tensor(pos, dtype=torch.int32), dev)
+        t_slots = _lib.to_device(torch.tensor(slot_list, dtype=torch.int32), dev)
+        t_cu = _lib.to_device(torch.tensor(cu, dtype=torch.int32), dev)
 
         def sink(layer, qkv):
             attn_ops.kv_cache_write(qkv, self.k_cache[layer], self.v_cache[layer], t_slots, a.num_heads,
@@ -463,6 +464,7 @@ class LLMEngine:
                 g = self._capture(n)
             for _ in range(steps):
                 g.replay()
+            _lib.LAUNCH_COUNT += steps * self._graph_launches.get(n, 0)
             self.stats["graph_replays"] += steps
         else:
             for _ in range(steps):
@@ -481,8 +483,11 @@ class LLMEngine:
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
+        before = _lib.LAUNCH_COUNT
         with torch.cuda.graph(g, pool=self._graph_pool):
             self._decode_once(n, False)
+        self._graph_launches[n] = _lib.LAUNCH_COUNT - before
+        _lib.LAUNCH_COUNT = before  # capture does not execute; replays are counted instead
         if self._graph_pool is None:
             self._graph_pool = g.pool()
         for dst, src in zip((self.cur_tokens, self.positions, self.slots, self.ctx_lens, self.active,
@@ -496,8 +501,8 @@ class LLMEngine:
         hi = self._hi()
         if hi == 0:
             return
-        fr = self.finish_reason[:hi].cpu()
-        gc = self.gen_count[:hi].cpu()
+        fr = _lib.to_host(self.finish_reason[:hi])
+        gc = _lib.to_host(self.gen_count[:hi])
         done = [s for s in range(hi) if self._slot_req[s] is not None and int(fr[s]) != 0]
         stop_str = [s for s in range(hi) if self._slot_req[s] is not None and int(fr[s]) == 0
                     and self._slot_req[s].params.stop and self.detokenize is not None]
@@ -505,8 +510,8 @@ class LLMEngine:
         if not fetch:
             return
         idx = torch.tensor(fetch, device=self.device, dtype=torch.long)
-        toks = self.out_tokens[idx].cpu()
-        lps = self.out_logprobs[idx].cpu()
+        toks = _lib.to_host(self.out_tokens[idx])
+        lps = _lib.to_host(self.out_logprobs[idx])
         for k, s in enumerate(fetch):
             req = self._slot_req[s]
             n = int(gc[s])

@@ -20,7 +20,10 @@ class SyntheticBernoulliEnv(BaseTextEnv):
         super().__init__()
         extras = extras or {}
         self.p = float(extras.get("p", 0.5))
-        self.rng = random.Random(extras.get("seed", None))
+        seed = extras.get("seed", None)
+        if seed is not None:  # distinct draws for the repetitions of one prompt
+            seed = int(seed) * 1000003 + int(extras.get("repetition_id", 0))
+        self.rng = random.Random(seed)
 
     def step(self, action: str) -> BaseTextEnvStepOutput:
         return BaseTextEnvStepOutput(observations=[], reward=1.0 if self.rng.random() < self.p else 0.0, done=True,

@@ -74,7 +74,13 @@ def ptr(t: torch.Tensor | None) -> int | None:
 _ERR = {1: "unsupported shape or alignment", 2: "CUDA runtime error", 3: "tensor-map encode failed", 4: "size beyond maximum"}
 
 
+LAUNCH_COUNT = 0  # kernel-launching library calls made by this process (a call may launch several kernels)
+_LAUNCHES_PER_CALL = {"sb_attn_bwd_varlen": 3, "sb_attn_decode_paged": 1}
+
+
 def check(code: int, what: str) -> None:
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += _LAUNCHES_PER_CALL.get(what, 1)
     if code != 0:
         raise NativeLibraryError(f"{what} failed: {_ERR.get(code, 'error')} (code {code})")
 
@@ -86,3 +92,26 @@ def status_read_clear() -> int:
 
 def use_cuda(t: torch.Tensor) -> bool:
     return t.is_cuda
+
+
+# ----------------------------------------------------------------------------- host<->device accounting
+H2D_BYTES = 0
+D2H_BYTES = 0
+
+
+def to_device(t: torch.Tensor, device, non_blocking: bool = True) -> torch.Tensor:
+    """Copy a host tensor to ``device`` through pinned memory and account the bytes."""
+    global H2D_BYTES
+    if torch.device(device).type != "cuda" or t.is_cuda:
+        return t.to(device)
+    H2D_BYTES += t.numel() * t.element_size()
+    if not t.is_pinned():
+        t = t.pin_memory()
+    return t.to(device, non_blocking=non_blocking)
+
+
+def to_host(t: torch.Tensor) -> torch.Tensor:
+    global D2H_BYTES
+    if t.is_cuda:
+        D2H_BYTES += t.numel() * t.element_size()
+    return t.cpu()

@@ -148,7 +148,7 @@ class _LinearFn(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.bias_ref = bias
         ctx.in_shape = shp
-        return y.reshape(*shp[:-1], w.shape[0])
+        return y if x.dim() == 2 else y.reshape(*shp[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):

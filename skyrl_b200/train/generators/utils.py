@@ -67,7 +67,9 @@ def prepare_generator_input(prompts: List[Any], n_samples_per_prompt: int, sampl
         for rep in range(n_samples_per_prompt):
             convs.append(item["prompt"])
             classes.append(item.get("env_class") or default_env_class)
-            extras.append(dict(item.get("env_extras") or {}))
+            ex = dict(item.get("env_extras") or {})
+            ex.setdefault("repetition_id", rep)
+            extras.append(ex)
             tids.append(TrajectoryID(uid, rep))
             uids.append(uid)
             if prompt_token_ids is not None:

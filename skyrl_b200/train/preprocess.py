@@ -125,6 +125,8 @@ def pack_batch(sequences: torch.Tensor, attention_mask: torch.Tensor, response_m
     else:
         grid_row = grid_col = pred_index = torch.zeros(0, dtype=torch.long)
     targets = ids[(pred_index + 1)] if pred_index.numel() else ids.new_zeros(0)
-    mv = lambda t: t.to(device, non_blocking=True)  # noqa: E731
+    from ..ops import _lib
+
+    mv = lambda t: _lib.to_device(t, device)  # noqa: E731
     return PackedView(mv(ids), mv(pos), mv(cu), int(lens.max()) if B else 0, mv(pred_index), mv(targets.to(torch.int32)),
                       mv(grid_row), mv(grid_col), B, R, int(ids.numel()))

@@ -155,7 +155,7 @@ class ModelWorker:
     def _rows_to_device(self, t: Optional[torch.Tensor], rows: List[int]) -> Optional[torch.Tensor]:
         if t is None:
             return None
-        return t[torch.tensor(rows, dtype=torch.long)].to(self.env.device, non_blocking=True)
+        return _lib.to_device(t[torch.tensor(rows, dtype=torch.long)], self.env.device)
 
     def _hidden(self, pv: PackedView) -> torch.Tensor:
         return self.model(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen)
@@ -181,7 +181,7 @@ class ModelWorker:
             hs = h[pv.pred_index]
             vals = self.model.values(hs) if self.role == "critic" else self.model.token_logprobs(hs, pv.targets, temp)[0]
             if k < len(groups):
-                grid = pv.scatter_to_grid(vals.float()).cpu()
+                grid = _lib.to_host(pv.scatter_to_grid(vals.float()))
                 out[torch.tensor(rows, dtype=torch.long)] = grid
         self.model.gradient_checkpointing = was_ckpt
         return TrainingOutputBatch({"output": out})
