@@ -28,6 +28,7 @@ def _k():
         lib.sb_attn_bwd_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cl, cf, vp]
         lib.sb_kv_cache_write.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, cl, ci, vp]
         lib.sb_attn_decode_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cl, cf, vp]
+        lib.sb_attn_decode_paged_tc.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, cl, cf, vp]
         _cfg_done = True
     return lib
 
@@ -156,7 +157,7 @@ def attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale):
 def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                       ctx_lens: torch.Tensor, nq: int, nkv: int, D: int, scale: float | None = None,
                       out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                      max_ctx: int = 0) -> torch.Tensor:
+                      max_ctx: int = 0, force_simt: bool = False) -> torch.Tensor:
     """One query token per sequence against its paged KV (which already contains that token).
 
     ``qkv``: ``[n, (nq+2nkv)*D]`` (only the q heads are read); ``block_tables``: ``[n, max_blocks]`` int32;
@@ -171,14 +172,33 @@ def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     if out is None:
         out = torch.empty((n, nq * D), device=qkv.device, dtype=qkv.dtype)
     bs = k_cache.shape[1]
-    splits = decode_num_splits(n, nkv, max_ctx if max_ctx > 0 else block_tables.shape[1] * bs)
-    if workspace is None:
+    G = nq // nkv
+    use_tc = (128 % bs == 0) and (bs % 8 == 0) and D == 128 and (G <= 8 or G in (12, 16)) and not force_simt
+    mc = max_ctx if max_ctx > 0 else block_tables.shape[1] * bs
+    splits = decode_num_splits_tc(n, nkv, mc) if use_tc else decode_num_splits(n, nkv, mc)
+    if workspace is None and splits > 1:
         workspace = torch.empty(decode_workspace_floats(n, nq, D, splits), device=qkv.device, dtype=torch.float32)
+    if use_tc:
+        code = _k().sb_attn_decode_paged_tc(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                            block_tables.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(),
+                                            _lib.ptr(workspace), n, nq, nkv, D, bs, k_cache.shape[0],
+                                            block_tables.shape[1], splits, qkv.stride(0), scale, _lib.stream_ptr())
+        _lib.check(code, "sb_attn_decode_paged_tc")
+        return out
     code = _k().sb_attn_decode_paged(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
-                                     ctx_lens.data_ptr(), out.data_ptr(), workspace.data_ptr(), n, nq, nkv, D, bs,
+                                     ctx_lens.data_ptr(), out.data_ptr(), _lib.ptr(workspace), n, nq, nkv, D, bs,
                                      block_tables.shape[1], splits, qkv.stride(0), scale, _lib.stream_ptr())
     _lib.check(code, "sb_attn_decode_paged")
     return out
+
+
+def decode_num_splits_tc(n: int, nkv: int, max_ctx: int) -> int:
+    """The tensor-core kernel runs one CTA per SM; split the context (128-token granularity) when few CTAs exist."""
+    ctas = n * nkv
+    if ctas >= 148 or max_ctx <= 256:
+        return 1
+    want = (148 + ctas - 1) // ctas
+    return int(max(1, min(want, max_ctx // 256, 32)))
 
 
 def decode_num_splits(n: int, nkv: int, max_ctx: int) -> int:

@@ -106,8 +106,11 @@ def test_decode_paged(nq, nkv, bs):
     qkv = torch.randn(n, (nq + 2 * nkv) * D, device="cuda").to(torch.bfloat16)
     ref = attention.attn_decode_paged_ref(qkv[:, : nq * D].view(n, nq, D), kc, vc, bt, ctx, 1 / math.sqrt(D))
     for max_ctx in (0, 2048):
-        out = attention.attn_decode_paged(qkv, kc, vc, bt, ctx.cuda(), nq, nkv, D, max_ctx=max_ctx)
-        assert rel(out.view(n, nq, D), ref) < 1e-2
+        for simt in (False, True):
+            out = attention.attn_decode_paged(qkv, kc, vc, bt, ctx.cuda(), nq, nkv, D, max_ctx=max_ctx, force_simt=simt)
+            torch.cuda.synchronize()
+            assert _lib.status_read_clear() == 0
+            assert rel(out.view(n, nq, D), ref) < 1e-2, (max_ctx, simt)
 
 
 def test_kv_cache_write():
