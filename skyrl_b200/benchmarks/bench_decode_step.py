@@ -1,0 +1,58 @@
+"""Decode-step micro-benchmark: fills the engine with ``--seqs`` sequences of ``--ctx`` context tokens and
+times decode steps (CUDA-graph replay or eager), reporting ms/step, tokens/s and the HBM roofline fraction
+(weights + KV bytes that a step must read, over the measured copy bandwidth).
+
+    python -m skyrl_b200.benchmarks.bench_decode_step --model qwen2.5-1.5b --seqs 256 --ctx 900 --steps 32
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine, SamplingParams
+from skyrl_b200.models.decoder import PRESETS, CausalLM
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="qwen2.5-1.5b")
+    ap.add_argument("--seqs", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=900)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--hbm-gbs", type=float, default=float(os.environ.get("SB_HBM_GBS", "6543.4")))
+    args = ap.parse_args()
+    a = PRESETS[args.model]
+    m = CausalLM(a, device="cuda", dtype=torch.bfloat16, seed=0)
+    max_len = args.ctx + args.steps * 3 + 64
+    eng = LLMEngine(m, EngineConfig(block_size=32, max_num_seqs=args.seqs, max_model_len=max_len,
+                                    max_num_batched_tokens=1 << 20, enforce_eager=args.eager, sync_interval=args.steps,
+                                    num_blocks=args.seqs * ((max_len + 31) // 32) + 8))
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(4, a.vocab_size, (args.seqs, args.ctx), generator=g).tolist()
+    sp = SamplingParams(max_tokens=args.steps * 3 + 8, temperature=1.0, ignore_eos=True)
+    for i, p in enumerate(prompts):
+        eng.add_request(f"r{i}", p, sp)
+    eng.step()  # prefill + first `steps` decode steps (also captures the graph)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    eng._run_decode(args.steps)
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / args.steps
+    ctx_now = args.ctx + args.steps * 1.5
+    kv_bytes = args.seqs * ctx_now * 2 * a.num_layers * a.num_kv_heads * a.head_dim * 2
+    w_bytes = (m.num_parameters()) * 2
+    ideal_ms = (kv_bytes + w_bytes) / (args.hbm_gbs * 1e9) * 1e3
+    print(json.dumps({"model": args.model, "seqs": args.seqs, "ctx": args.ctx, "mode": "eager" if args.eager else "graph",
+                      "ms_per_step": ms, "tokens_per_s": args.seqs / ms * 1e3, "hbm_bytes_per_step": kv_bytes + w_bytes,
+                      "roofline_ms": ideal_ms, "fraction_of_measured_hbm_roofline": ideal_ms / ms}))
+
+
+if __name__ == "__main__":
+    main()

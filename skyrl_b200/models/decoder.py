@@ -319,20 +319,37 @@ class CausalLM(nn.Module):
         return sum(math.prod(s) for _, s in self.specs)
 
 
+def flat_numel_for(args: ModelArgs, value_head: bool = False) -> int:
+    """Size (elements) of the flat parameter buffer ``CausalLM`` lays out for ``args``."""
+    off = 0
+    for _, shape in _param_specs(args, value_head=value_head):
+        off += _align(math.prod(shape))
+    return _align(off, 8192)
+
+
+def resolve_model_args(name_or_path: str, model_config_kwargs: Optional[dict] = None) -> ModelArgs:
+    import dataclasses
+
+    if name_or_path in PRESETS:
+        return dataclasses.replace(PRESETS[name_or_path], **(model_config_kwargs or {}))
+    with open(os.path.join(name_or_path, "config.json")) as f:
+        return ModelArgs.from_hf_config(json.load(f))
+
+
 def build_model(name_or_path: str, device="cpu", dtype=torch.bfloat16, value_head: bool = False, seed: int = 0,
-                model_config_kwargs: Optional[dict] = None) -> CausalLM:
+                model_config_kwargs: Optional[dict] = None, flat_buffer: Optional[torch.Tensor] = None) -> CausalLM:
     """Build from a preset name (random init) or from an HF checkpoint directory (weights loaded)."""
     if name_or_path in PRESETS:
         import dataclasses
 
         args = dataclasses.replace(PRESETS[name_or_path], **(model_config_kwargs or {}))
-        return CausalLM(args, device=device, dtype=dtype, value_head=value_head, seed=seed)
+        return CausalLM(args, device=device, dtype=dtype, value_head=value_head, seed=seed, flat_buffer=flat_buffer)
     cfg_path = os.path.join(name_or_path, "config.json")
     if not os.path.exists(cfg_path):
         raise FileNotFoundError(f"'{name_or_path}' is neither a preset ({sorted(PRESETS)}) nor a checkpoint directory")
     with open(cfg_path) as f:
         args = ModelArgs.from_hf_config(json.load(f))
-    model = CausalLM(args, device=device, dtype=dtype, value_head=value_head, seed=None)
+    model = CausalLM(args, device=device, dtype=dtype, value_head=value_head, seed=None, flat_buffer=flat_buffer)
     from . import hf_io
 
     hf_io.load_hf_weights(model, name_or_path)

@@ -39,7 +39,7 @@ class ShardedAdamW:
     def __init__(self, flat_params: torch.Tensor, flat_grads: torch.Tensor, lr: float = 1e-6, betas=(0.9, 0.999),
                  eps: float = 1e-8, weight_decay: float = 0.01, max_grad_norm: float = 1.0,
                  group: Optional[dist.ProcessGroup] = None, transport: str = "auto", peer_ctx=None,
-                 numel: Optional[int] = None):
+                 numel: Optional[int] = None, params_symm=None, grads_symm=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -62,8 +62,10 @@ class ShardedAdamW:
         self._skip = torch.zeros(1, device=dev, dtype=torch.int32)
         self._norm = torch.zeros(1, device=dev, dtype=torch.float32)
         self._grad_shard = torch.zeros(self.shard, device=dev, dtype=torch.float32) if self.world > 1 else None
+        self.params_symm, self.grads_symm = params_symm, grads_symm
         if transport == "auto":
-            transport = "peer" if (peer_ctx is not None and self.world > 1) else "nccl"
+            transport = "peer" if (peer_ctx is not None and self.world > 1 and params_symm is not None
+                                   and grads_symm is not None) else "nccl"
         self.transport = transport
         self.peer_ctx = peer_ctx
         self.last_grad_norm: Optional[torch.Tensor] = None
@@ -74,11 +76,17 @@ class ShardedAdamW:
         """Apply one update; returns the (pre-clip) global gradient norm as a device scalar."""
         self.step_count += 1
         b1, b2 = self.betas
+        if self.world > 1 and self.transport == "peer":
+            # peer-memory path: loads from every peer's gradient buffer, AdamW, stores into every peer's parameters
+            ctx = self.peer_ctx
+            ctx.reduce_scatter_and_norm(self.grads_symm, self._grad_shard, self.lo, self.shard)
+            norm, skipped = ctx.adamw_and_push(self.master, self.exp_avg, self.exp_avg_sq, self._grad_shard,
+                                               self.params_symm, self.lo, self.shard, self.lr, b1, b2, self.eps,
+                                               self.weight_decay, self.step_count, self.max_grad_norm, grad_scale)
+            self.last_grad_norm = norm.clone()
+            return self.last_grad_norm
         if self.world == 1:
             g = self.grads
-        elif self.transport == "peer":
-            self.peer_ctx.reduce_scatter_grads(self.grads, self._grad_shard, self.lo, self.shard)
-            g = self._grad_shard
         else:
             dist.reduce_scatter_tensor(self._grad_shard, self.grads, op=dist.ReduceOp.SUM, group=self.group)
             g = self._grad_shard
@@ -91,10 +99,7 @@ class ShardedAdamW:
         optim_ops.adamw_flat(self.master, self.exp_avg, self.exp_avg_sq, g, shard_params, self.lr, b1, b2, self.eps,
                              self.weight_decay, self.step_count, self._coef, self._skip)
         if self.world > 1:
-            if self.transport == "peer":
-                self.peer_ctx.push_params(self.params, self.lo, self.shard)
-            else:
-                dist.all_gather_into_tensor(self.params, shard_params.clone(), group=self.group)
+            dist.all_gather_into_tensor(self.params, shard_params.clone(), group=self.group)
         self.last_grad_norm = self._norm.clone()
         return self.last_grad_norm
 

@@ -73,6 +73,12 @@ class PPOTrainer:
         """Create the policy (and optional ref / critic) workers and the colocated generation engine."""
         t = self.cfg.trainer
         a = t.algorithm
+        if (peer_ctx is None and self.env.world_size > 1 and self.env.device.type == "cuda" and t.b200.fused_optimizer
+                and policy_model is None):
+            from ..parallel.peer import PeerContext
+
+            peer_ctx = PeerContext(self.env.device)
+        self.peer_ctx = peer_ctx
         self.policy = PolicyWorker(t, model=policy_model, model_path=t.policy.model.path, env=self.env, peer_ctx=peer_ctx,
                                    seed=t.seed)
         if a.use_kl_loss or a.use_kl_in_reward:

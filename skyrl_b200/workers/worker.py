@@ -119,8 +119,18 @@ class ModelWorker:
         self.env = env or get_env()
         dev = self.env.device
         dtype = torch.bfloat16 if (cfg.bf16 and dev.type == "cuda") else torch.float32
+        self.params_symm = self.grads_symm = None
+        use_peer = peer_ctx is not None and trainable and self.env.world_size > 1 and dev.type == "cuda"
         if model is None:
-            model = build_model(model_path, device=dev, dtype=dtype, value_head=value_head, seed=seed)
+            if use_peer:
+                from ..models.decoder import flat_numel_for, resolve_model_args
+
+                n = flat_numel_for(resolve_model_args(model_path), value_head)
+                self.params_symm = peer_ctx.alloc(n, dtype)
+                self.grads_symm = peer_ctx.alloc(n, torch.float32)
+                flat_buffer, flat_grad = self.params_symm.local, self.grads_symm.local
+            model = build_model(model_path, device=dev, dtype=dtype, value_head=value_head, seed=seed,
+                                flat_buffer=flat_buffer)
         self.model = model
         self.model.gradient_checkpointing = bool(cfg.gradient_checkpointing) and trainable
         self.trainable = trainable
@@ -137,7 +147,7 @@ class ModelWorker:
             self.flat_grad = flat_grad
             self.optimizer = ShardedAdamW(model.flat_params, flat_grad, lr=ocfg.lr, betas=tuple(ocfg.adam_betas),
                                           weight_decay=ocfg.weight_decay, max_grad_norm=ocfg.max_grad_norm,
-                                          peer_ctx=peer_ctx)
+                                          peer_ctx=peer_ctx, params_symm=self.params_symm, grads_symm=self.grads_symm)
             self.scheduler = get_scheduler(ocfg.scheduler, self.optimizer, ocfg.num_warmup_steps, base_lr=ocfg.lr)
 
     # ------------------------------------------------------------------ helpers
