@@ -550,6 +550,9 @@ class LLMEngine:
 
     def step(self) -> List[RequestOutput]:
         """One scheduling round: admit + prefill what fits, then ``sync_interval`` decode steps, then harvest."""
+        if self.is_cuda:
+            # the CUDA current device is per thread; callers may step the engine from worker threads
+            torch.cuda.set_device(self.device)
         if self.paused or self.asleep:
             out, self._finished = self._finished, []
             return out
