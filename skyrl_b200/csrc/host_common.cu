@@ -65,6 +65,14 @@ static const CUtensorMap* lookup_or_make(const Key& key, uint32_t rank, void* pt
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, ptr, dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // The driver entry point needs the primary context current on the calling thread; a thread that has made
+    // no runtime call yet (an autograd worker thread, say) binds it here and retries.  Never reached while a
+    // stream is capturing, because capture starts on a thread that has already launched work.
+    cudaFree(nullptr);
+    r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) {
     std::fprintf(stderr, "[skyrl_b200] cuTensorMapEncodeTiled failed: %d (rank %u ptr %p)\n", (int)r, rank, ptr);
     free(m);
