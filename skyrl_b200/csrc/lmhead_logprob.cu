@@ -338,3 +338,96 @@ int sb_lmhead_dlogits(void* logits, long long ld, int rows, int V, const int* ta
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in lmhead_noalloc.h).
+// ---------------------------------------------------------------------------------------------------------
+#include "lmhead_noalloc.h"
+
+namespace sb {
+
+// Scratch for the per-(row, split) records of the no-alloc entry point: lives in the device image of
+// every GPU that loads this library.  In host code this name is only a stand-in for the symbol; the
+// device address is obtained with cudaGetSymbolAddress below.
+static __device__ __align__(256) float4 g_lmhead_noalloc_scratch[SB_LMHEAD_NOALLOC_MAX_RECORDS];
+
+typedef CUresult (*NoAllocEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct NoAllocDeviceState {
+  float4* scratch = nullptr;
+  bool ready = false;
+};
+static NoAllocDeviceState g_noalloc_state[64];
+static NoAllocEncodeFn g_noalloc_encode = nullptr;
+
+// Once per device, with that device current: resolve the scratch address and configure the kernel.
+static int noalloc_setup(int dev) {
+  NoAllocDeviceState& st = g_noalloc_state[dev];
+  if (st.ready) return SB_OK;
+  cudaFree(nullptr);  // bind the primary context to this thread (frees nothing, allocates nothing)
+  float4* ptr = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_lmhead_noalloc_scratch) != cudaSuccess || ptr == nullptr)
+    return SB_ERR_CUDA;
+  if (cudaFuncSetAttribute(lmhead_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLmSmem) != cudaSuccess)
+    return SB_ERR_CUDA;
+  if (!g_noalloc_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !fn)
+      return SB_ERR_TMAP;
+    g_noalloc_encode = reinterpret_cast<NoAllocEncodeFn>(fn);
+  }
+  st.scratch = ptr;
+  st.ready = true;
+  return SB_OK;
+}
+
+// Tensor map built in caller-provided (stack) storage: no cache, no heap.
+static int noalloc_encode_2d(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                             uint32_t box_rows) {
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15)) return SB_ERR_ARG;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_noalloc_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SB_OK : SB_ERR_TMAP;
+}
+
+}  // namespace sb
+
+extern "C" int sb_lmhead_logprob_noalloc(const void* hidden, const void* W, const int* targets, int T, int V, int K,
+                                         long long ldh, long long ldw, float inv_temp, float* logprob, float* entropy,
+                                         float* lse, void* stream) {
+  if (T <= 0 || V <= 0 || K <= 0 || (ldh & 7) || (ldw & 7) || !hidden || !W || !targets) return SB_ERR_ARG;
+  const int splits = sb_lmhead_num_splits(T, V);
+  if (static_cast<long long>(T) * splits > SB_LMHEAD_NOALLOC_MAX_RECORDS) return SB_ERR_TOO_LARGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SB_ERR_CUDA;
+  int rc = sb::noalloc_setup(dev);
+  if (rc != SB_OK) return rc;
+  alignas(64) CUtensorMap ta, tb;
+  rc = sb::noalloc_encode_2d(&ta, hidden, T, K, ldh, sb::kLmBM);
+  if (rc != SB_OK) return rc;
+  rc = sb::noalloc_encode_2d(&tb, W, V, K, ldw, sb::kLmBN);
+  if (rc != SB_OK) return rc;
+  float4* scratch = sb::g_noalloc_state[dev].scratch;  // device address, not the host-side symbol
+  const int chunks = (V + sb::kLmBN - 1) / sb::kLmBN;
+  const int cps = (chunks + splits - 1) / splits;
+  const int m_blocks = (T + sb::kLmBM - 1) / sb::kLmBM;
+  const int items = m_blocks * splits;
+  const int grid = items < sb::sm_count() ? items : sb::sm_count();
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  sb::lmhead_fwd_kernel<<<grid, sb::kLmThreads, sb::kLmSmem, st>>>(ta, tb, targets, scratch, T, V, K, splits, cps, 0,
+                                                                  inv_temp, sb::device_status_ptr());
+  if (cudaGetLastError() != cudaSuccess) return SB_ERR_CUDA;
+  sb::PartialSources src;
+  for (int i = 0; i < 8; ++i) src.ptr[i] = i == 0 ? scratch : nullptr;
+  sb::lmhead_combine_kernel<<<(T + 255) / 256, 256, 0, st>>>(src, 1, splits, T, logprob, entropy, lse);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
