@@ -1,0 +1,108 @@
+"""Kernel micro-benchmarks with roofline fractions against the measured peaks of the machine.
+
+    python -m skyrl_b200.benchmarks.bench_kernels --which gemm --m 4096 --n 4096 --k 4096
+    python -m skyrl_b200.benchmarks.bench_kernels --which decode_attn --seqs 64 --ctx 1024
+    python -m skyrl_b200.benchmarks.bench_kernels --which attn --seqs 8 --seqlen 2048
+    python -m skyrl_b200.benchmarks.bench_kernels --which lmhead --tokens 4096
+
+Peaks default to the values measured on the B200 pool (copy bandwidth 6543.4 GB/s, bf16 GEMM 1668.8 TFLOP/s burst /
+1376.9 sustained) and can be overridden with --hbm-gbs / --peak-tflops.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from skyrl_b200.ops import attention, gemm, lm_head
+
+
+def timeit(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+    tot = 0.0
+    for _ in range(iters):
+        flush.zero_()  # evict L2 between timed iterations
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        tot += s.elapsed_time(e)
+    return tot / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--seqs", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1024)
+    ap.add_argument("--seqlen", type=int, default=2048)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--nq", type=int, default=12)
+    ap.add_argument("--nkv", type=int, default=2)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--hbm-gbs", type=float, default=6543.4)
+    ap.add_argument("--peak-tflops", type=float, default=1668.8)
+    a = ap.parse_args()
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    out = {"which": a.which}
+    if a.which == "gemm":
+        if a.layout == "nt":
+            x, w = torch.randn(a.m, a.k, **bf), torch.randn(a.n, a.k, **bf)
+            fn = lambda: gemm.gemm_nt(x, w)  # noqa: E731
+        elif a.layout == "nn":
+            x, w = torch.randn(a.m, a.k, **bf), torch.randn(a.k, a.n, **bf)
+            fn = lambda: gemm.gemm_nn(x, w)  # noqa: E731
+        else:
+            x, w = torch.randn(a.k, a.m, **bf), torch.randn(a.k, a.n, **bf)
+            fn = lambda: gemm.gemm_tn(x, w)  # noqa: E731
+        ms = timeit(fn, a.iters)
+        fl = 2.0 * a.m * a.n * a.k
+        out.update(m=a.m, n=a.n, k=a.k, layout=a.layout, ms=ms, tflops=fl / ms / 1e9,
+                   fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
+    elif a.which == "decode_attn":
+        bs, D = 32, 128
+        mb = (a.ctx + bs - 1) // bs
+        nb = a.seqs * mb
+        kc, vc = torch.randn(nb, bs, a.nkv, D, **bf), torch.randn(nb, bs, a.nkv, D, **bf)
+        bt = torch.arange(nb, device="cuda", dtype=torch.int32).view(a.seqs, mb)
+        cl = torch.full((a.seqs,), a.ctx, device="cuda", dtype=torch.int32)
+        qkv = torch.randn(a.seqs, (a.nq + 2 * a.nkv) * D, **bf)
+        ms = timeit(lambda: attention.attn_decode_paged(qkv, kc, vc, bt, cl, a.nq, a.nkv, D, max_ctx=a.ctx), a.iters)
+        by = 2.0 * a.seqs * a.ctx * a.nkv * D * 2
+        out.update(seqs=a.seqs, ctx=a.ctx, ms=ms, gbs=by / ms / 1e6, fraction_of_measured_hbm=by / ms / 1e6 / a.hbm_gbs)
+    elif a.which == "attn":
+        D = 128
+        T = a.seqs * a.seqlen
+        qkv = (torch.randn(T, (a.nq + 2 * a.nkv) * D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+        cu = torch.arange(0, T + 1, a.seqlen, device="cuda", dtype=torch.int32)
+        ms_f = timeit(lambda: attention.attn_varlen(qkv.detach(), cu, a.nq, a.nkv, D), a.iters)
+        o = attention.attn_varlen(qkv, cu, a.nq, a.nkv, D)
+        g = torch.randn_like(o)
+        ms_b = timeit(lambda: torch.autograd.grad(o, qkv, g, retain_graph=True), a.iters)
+        fl = 4.0 * a.seqs * a.nq * a.seqlen * a.seqlen * D / 2
+        out.update(tokens=T, seqlen=a.seqlen, fwd_ms=ms_f, fwd_tflops=fl / ms_f / 1e9, bwd_ms=ms_b,
+                   bwd_tflops=2.5 * fl / ms_b / 1e9, fwd_fraction_of_measured_bf16_burst=fl / ms_f / 1e9 / a.peak_tflops)
+    else:
+        V, H = 151936, 1536
+        h = (torch.randn(a.tokens, H, device="cuda") * 0.5).to(torch.bfloat16)
+        W = (torch.randn(V, H, device="cuda") * 0.02).to(torch.bfloat16)
+        tgt = torch.randint(0, V, (a.tokens,), device="cuda")
+        ms = timeit(lambda: lm_head.lm_head_logprobs(h, W, tgt, 1.0), a.iters)
+        fl = 2.0 * a.tokens * V * H
+        out.update(tokens=a.tokens, ms=ms, tflops=fl / ms / 1e9, fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
