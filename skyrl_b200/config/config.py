@@ -587,6 +587,9 @@ class B200Config(BaseConfig):
     peer_memory_weight_sync: bool = True
     nvls: bool = True
     lm_head_bwd_chunk: int = 8192
+    # With exactly one optimizer step per RL step the "old policy" is the policy being trained, so its
+    # log-probabilities are the (detached) ones of the training forward pass: no separate forward is run.
+    reuse_train_forward_for_old_logprobs: bool = True
 
 
 @dataclass

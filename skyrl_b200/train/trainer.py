@@ -180,6 +180,15 @@ class PPOTrainer:
         a = self.cfg.trainer.algorithm
         return a.policy_loss_type in rl.LOSSES_WITHOUT_OLD_LOGPROBS and not rl.off_policy_correction_enabled_cfg(a)
 
+    def _old_logprobs_from_train_forward(self) -> bool:
+        """True when pi_old == pi_theta at the only optimizer step of this RL step (and nothing else needs pi_old)."""
+        t = self.cfg.trainer
+        single_update = (t.update_epochs_per_batch == 1 and t.train_batch_size == t.policy_mini_batch_size)
+        a = t.algorithm
+        return (t.b200.reuse_train_forward_for_old_logprobs and single_update and not a.use_kl_in_reward
+                and not rl.off_policy_correction_enabled_cfg(a) and a.policy_loss_type in ("regular", "dual_clip", "gspo",
+                                                                                           "sapo", "cispo"))
+
     def fwd_logprobs_values_reward(self, batch: TrainingInputBatch) -> TrainingInputBatch:
         if self.critic is not None:
             batch["values"] = self.critic.forward(batch)["output"]
@@ -187,6 +196,9 @@ class PPOTrainer:
             batch["base_action_log_probs"] = self.ref.forward(batch)["output"]
         if self._skip_policy_forward() and batch.get("rollout_logprobs") is not None:
             batch["action_log_probs"] = batch["rollout_logprobs"].clone()
+        elif self._old_logprobs_from_train_forward():
+            batch["action_log_probs"] = None  # filled by the worker from its own forward (identical weights)
+            return batch
         else:
             batch["action_log_probs"] = self.policy.forward(batch)["output"]
         if batch.get("rollout_logprobs") is not None:
