@@ -92,6 +92,9 @@ def main() -> None:
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--prompts-per-gpu", type=int, default=PROMPTS_PER_GPU)
     ap.add_argument("--max-tokens-per-microbatch", type=int, default=32768)
+    ap.add_argument("--reuse-train-forward", action="store_true",
+                    help="take old log-probs from the training forward (exact with one optimizer update per step); "
+                         "off by default so the step runs the same separate old-policy forward the reference does")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -123,7 +126,8 @@ def main() -> None:
         "trainer.gradient_checkpointing=false", "environment.env_class=synthetic_bernoulli",
         f"generator.inference_engine.max_num_seqs={P * n}", "generator.inference_engine.gpu_memory_utilization=0.25",
         "generator.inference_engine.enable_prefix_caching=false", "trainer.resume_mode=none", "trainer.seed=0",
-        "trainer.logger=console"])
+        "trainer.logger=console",
+        f"trainer.b200.reuse_train_forward_for_old_logprobs={'true' if args.reuse_train_forward else 'false'}"])
     tok = SyntheticTokenizer(margs.vocab_size)
     trainer = PPOTrainer(cfg, tokenizer=tok, env=env)
     trainer.build_models()

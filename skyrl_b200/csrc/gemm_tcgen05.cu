@@ -51,7 +51,10 @@ struct TileMap {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
-                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc, int out_mode, int* status) {
+                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc, int out_mode, int splits,
+                 long long split_stride, int* status) {
+  // splits > 1: split-K. Work item = (output tile, k slice); slice ks writes its fp32 partial sum to
+  // C + ks * split_stride (the consumer kernel adds the partials), bias is applied by slice 0 only.
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -65,8 +68,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   TileMap tm{(M + kBM - 1) / kBM, (N + BN - 1) / BN};
-  const int tiles = tm.m_blocks * tm.n_blocks;
+  const int tiles_mn = tm.m_blocks * tm.n_blocks;
+  const int tiles = tiles_mn * splits;
   const int k_blocks = (K + kBK - 1) / kBK;
+  const int kpb = (k_blocks + splits - 1) / splits;  // k blocks per slice (host guarantees no empty slice)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -97,8 +102,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         int pm, pn;
-        tm.get(tile, pm, pn);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int ks = tile / tiles_mn;
+        tm.get(tile - ks * tiles_mn, pm, pn);
+        const int kb0 = ks * kpb, kb1 = min(k_blocks, kb0 + kpb);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % Cfg::kStages;
           const uint32_t ph = (it / Cfg::kStages) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, status, 0x101)) {
@@ -135,7 +142,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&tempty[acc], aph ^ 1, status, 0x201)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int ks = tile / tiles_mn;
+        const int kb0 = ks * kpb, kb1 = min(k_blocks, kb0 + kpb);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % Cfg::kStages;
           const uint32_t ph = (it / Cfg::kStages) & 1;
           if (!mbar_wait(&full[s], ph, status, 0x202)) {
@@ -151,7 +160,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024) : make_smem_desc(a_base + k * 32, 0, 1024);
             const uint64_t bdesc =
                 B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024) : make_smem_desc(b_base + k * 32, 0, 1024);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // frees the smem stage once these MMAs retire
         }
@@ -164,7 +173,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int tcount = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tcount) {
       int pm, pn;
-      tm.get(tile, pm, pn);
+      const int ks = tile / tiles_mn;
+      tm.get(tile - ks * tiles_mn, pm, pn);
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aph, status, 0x301)) break;
@@ -179,7 +189,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int col0 = pn * BN + c * 32;
         if (row < M && col0 < N) {
           const bool full_chunk = (col0 + 32 <= N);
-          if (bias != nullptr) {
+          if (bias != nullptr && ks == 0) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int col = col0 + j;
@@ -205,7 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < N) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
             }
           } else {
-            float* crow = reinterpret_cast<float*>(C) + static_cast<long long>(row) * ldc + col0;
+            float* crow = reinterpret_cast<float*>(C) + ks * split_stride + static_cast<long long>(row) * ldc + col0;
             const bool vec = full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
             if (vec) {
 #pragma unroll
@@ -246,7 +256,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
-                       long long ldb, long long ldc, int out_mode, cudaStream_t stream) {
+                       long long ldb, long long ldc, int out_mode, cudaStream_t stream, int splits = 1,
+                       long long split_stride = 0) {
   using Cfg = GemmCfg<BN>;
   const CUtensorMap* ta = A_MN ? get_tmap_bf16_2d(A, K, M, lda, 64) : get_tmap_bf16_2d(A, M, K, lda, kBM);
   const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN);
@@ -258,10 +269,10 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
       return SB_ERR_CUDA;
     attr_set = true;
   }
-  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kfn<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N,
-                                                       K, ldc, out_mode, device_status_ptr());
+                                                       K, ldc, out_mode, splits, split_stride, device_status_ptr());
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
@@ -301,6 +312,25 @@ int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M,
   if (!a_mn && b_mn) return sb::dispatch_bn<false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
   if (a_mn && b_mn) return sb::dispatch_bn<true, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
   return sb::dispatch_bn<true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
+}
+
+
+// Split-K product for skinny problems (decode: M <= a few hundred rows): x[M,K] * W[N,K]^T as `splits` fp32
+// partial sums, partial s at C + s * split_stride (row stride ldc).  `splits` is clamped so that no slice is
+// empty; the value used is returned through splits_used.  bias (optional) is added into partial 0.
+int sb_gemm_bf16_splitk(const void* A, const void* B, float* C, const void* bias, int M, int N, int K, long long lda,
+                        long long ldb, long long ldc, long long split_stride, int splits, int bn, int* splits_used,
+                        void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || splits < 1) return SB_ERR_ARG;
+  const int k_blocks = (K + sb::kBK - 1) / sb::kBK;
+  if (splits > k_blocks) splits = k_blocks;
+  int kpb = (k_blocks + splits - 1) / splits;
+  splits = (k_blocks + kpb - 1) / kpb;
+  if (splits_used) *splits_used = splits;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 256) return sb::launch_gemm<256, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
+  if (bn == 128) return sb::launch_gemm<128, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
+  return sb::launch_gemm<64, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
 }
 
 }  // extern "C"

@@ -111,6 +111,7 @@ class EngineConfig:
     seed: int = 0
     graph_batch_sizes: Sequence[int] = (8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024)
     reserve_full_length: bool = True
+    fused_decode: bool = True  # split-K projections with fused partial-sum consumers on the decode path
 
 
 def _rt():
@@ -284,9 +285,48 @@ class LLMEngine:
             d = gemm.gemm_nt(ew.swiglu(gu), m.p(pre + "wd"))
         return x, d
 
+    def _splitk_linear(self, h, w, bias, n):
+        """Skinny projection as fp32 split-K partials; returns (partials[P, n, N], n_written)."""
+        N, K = w.shape
+        splits, bn = gemm.plan_splitk(n, N, K)
+        part = torch.empty((splits, n, N), device=self.device, dtype=torch.float32)
+        return part, gemm.gemm_nt_splitk(h, w, bias, part, splits, bn)
+
+    @torch.no_grad()
+    def _decode_once_fused(self, n: int, masked: bool) -> None:
+        """Decode step for dense models on CUDA: every projection whose tile count cannot fill the SMs runs
+        split-K, and the partial sums are consumed by the next kernel (norm / RoPE + cache write)."""
+        m, a = self.model, self.model.args
+        x = sampling.embed(m.p("embed"), self.cur_tokens[:n])  # residual stream, updated in place
+        table = m.rope_table(self.device)
+        qkv = torch.empty((n, (a.num_heads + 2 * a.num_kv_heads) * a.head_dim), device=self.device, dtype=x.dtype)
+        pending = None
+        for i in range(a.num_layers):
+            pre = f"layers.{i}."
+            if pending is None:
+                _, h = ew.add_rmsnorm(x, None, m.p(pre + "ln1"), a.rms_norm_eps)
+            else:
+                h = ew.add_rmsnorm_partials_(x, pending[0], pending[1], m.p(pre + "ln1"), a.rms_norm_eps)
+            part, np_ = self._splitk_linear(h, m.p(pre + "wqkv"), m._p.get(pre + "bqkv"), n)
+            ew.qkv_finalize(part, np_, self.positions[:n], table, qkv, self.k_cache[i], self.v_cache[i], self.slots[:n],
+                            a.num_heads, a.num_kv_heads, a.head_dim)
+            att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], self.block_tables[:n],
+                                             self.ctx_lens[:n], a.num_heads, a.num_kv_heads, a.head_dim,
+                                             max_ctx=self.cfg.max_model_len)
+            part, np_ = self._splitk_linear(att, m.p(pre + "wo"), None, n)
+            h = ew.add_rmsnorm_partials_(x, part, np_, m.p(pre + "ln2"), a.rms_norm_eps)
+            gu = gemm.gemm_nt(h, m.p(pre + "wgu"))
+            pending = self._splitk_linear(ew.swiglu(gu), m.p(pre + "wd"), None, n)
+        h = ew.add_rmsnorm_partials_(x, pending[0], pending[1], m.p("final_norm"), a.rms_norm_eps)
+        logits = gemm.gemm_nt(h, m.lm_head_weight())
+        self._sample(logits, n, masked)
+        self._advance(n)
+
     @torch.no_grad()
     def _decode_once(self, n: int, masked: bool) -> None:
         m, a = self.model, self.model.args
+        if self.is_cuda and self.cfg.fused_decode and not a.num_experts and not a.qk_norm:
+            return self._decode_once_fused(n, masked)
         x = sampling.embed(m.p("embed"), self.cur_tokens[:n])
         delta = None
         for i in range(a.num_layers):

@@ -200,3 +200,61 @@ class _SwiGLUFn(torch.autograd.Function):
 def swiglu(gu: torch.Tensor) -> torch.Tensor:
     """``silu(gu[:, :F]) * gu[:, F:]`` for the fused gate/up projection output."""
     return _SwiGLUFn.apply(gu)
+
+
+# ----------------------------------------------------------------------------- split-K consumers (decode)
+def add_rmsnorm_partials_(x: torch.Tensor, partials: torch.Tensor, n_part: int, w: torch.Tensor, eps: float,
+                          out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x += sum(partials[:n_part])`` in place (bf16 residual stream), returns ``rmsnorm(x) * w``.
+
+    ``partials`` is the fp32 ``[P, T, H]`` output of ``gemm_nt_splitk``; summing it here saves the separate
+    reduction pass a split-K GEMM otherwise needs."""
+    T, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    if not x.is_cuda:
+        x.copy_((x.float() + partials[:n_part].sum(0)).to(x.dtype))
+        out.copy_(_rmsnorm_ref(x, None, w, eps)[1])
+        return out
+    lib = _lib.kernels()
+    f = lib.sb_add_rmsnorm_partials
+    if not getattr(f, "_configured", False):
+        vp, ci, cf, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+        f.argtypes = [vp, vp, ci, cl, vp, vp, ci, ci, cf, vp]
+        f._configured = True
+    assert x.is_contiguous() and partials.dtype == torch.float32 and partials.stride(1) == H
+    _lib.check(f(x.data_ptr(), partials.data_ptr(), n_part, partials.stride(0), w.data_ptr(), out.data_ptr(), T, H, eps,
+                 _lib.stream_ptr()), "sb_add_rmsnorm_partials")
+    return out
+
+
+def qkv_finalize(partials: torch.Tensor, n_part: int, pos: torch.Tensor, table: torch.Tensor, qkv: torch.Tensor,
+                 k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, slots: torch.Tensor | None, nq: int,
+                 nkv: int, head_dim: int) -> torch.Tensor:
+    """Sum the fp32 partials of the fused QKV projection, rotate q/k, write bf16 ``qkv`` and scatter k/v rows
+    into their paged-cache slot (one kernel for what was reduction + RoPE + cache write)."""
+    T = qkv.shape[0]
+    if not qkv.is_cuda:
+        full = partials[:n_part].sum(0).to(qkv.dtype)
+        full = _rope_ref(full, pos, table, nq + nkv, head_dim, 1.0)
+        qkv.copy_(full)
+        if k_cache is not None and slots is not None:
+            ok = slots >= 0
+            s = slots[ok].long()
+            kc = k_cache.view(-1, nkv * head_dim)
+            vc = v_cache.view(-1, nkv * head_dim)
+            kc[s] = full[ok, nq * head_dim:(nq + nkv) * head_dim]
+            vc[s] = full[ok, (nq + nkv) * head_dim:]
+        return qkv
+    lib = _lib.kernels()
+    f = lib.sb_qkv_finalize
+    if not getattr(f, "_configured", False):
+        vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        f.argtypes = [vp, ci, cl, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
+        f._configured = True
+    assert qkv.is_contiguous() and partials.stride(1) == qkv.shape[1] and pos.dtype == torch.int32
+    _lib.check(f(partials.data_ptr(), n_part, partials.stride(0), pos.data_ptr(), table.data_ptr(),
+                 None if slots is None else slots.data_ptr(), qkv.data_ptr(),
+                 None if k_cache is None else k_cache.data_ptr(), None if v_cache is None else v_cache.data_ptr(),
+                 T, nq, nkv, head_dim, _lib.stream_ptr()), "sb_qkv_finalize")
+    return qkv

@@ -132,6 +132,58 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, a
     return out
 
 
+def plan_splitk(M: int, N: int, K: int, n_sm: int = 148) -> tuple[int, int]:
+    """(splits, bn) for a skinny ``x[M,K] @ w[N,K]^T``: enough (tile, k-slice) work items to cover the SMs
+    once, with the widest N tile that still does (wide tiles re-read the activation block less often)."""
+    m_blocks = (M + 127) // 128
+    k_blocks = (K + 63) // 64
+    best = (1, 64)
+    for bn in (128, 64):
+        tiles = m_blocks * ((N + bn - 1) // bn)
+        if tiles >= n_sm:
+            return 1, bn
+        splits = max(1, min(n_sm // tiles, k_blocks // 4 if k_blocks >= 8 else 1))
+        best = (splits, bn)
+        if tiles * splits >= 0.75 * n_sm:
+            break
+    splits, bn = best
+    if splits > 1:  # no empty slice
+        kpb = (k_blocks + splits - 1) // splits
+        splits = (k_blocks + kpb - 1) // kpb
+    return splits, bn
+
+
+def gemm_nt_splitk(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, splits: int,
+                   bn: int = 64) -> int:
+    """``x @ w^T`` as ``splits`` fp32 partial sums written to ``out[s]`` (``out``: fp32 ``[>=splits, M, N]``);
+    the bias is folded into partial 0.  Returns the number of partials actually written (<= ``splits``);
+    a fused consumer (``add_rmsnorm_partials`` / ``qkv_finalize``) adds them up."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not x.is_cuda:
+        y = x.float() @ w.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        out[0].copy_(y)
+        return 1
+    lib = _lib.kernels()
+    f = lib.sb_gemm_bf16_splitk
+    if not getattr(f, "_configured", False):
+        f.restype = ctypes.c_int
+        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                      ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong,
+                      ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]
+        f._configured = True
+    assert out.dtype == torch.float32 and out.dim() == 3 and out.shape[0] >= splits and out.stride(2) == 1
+    x = _as_2d_rowmajor(x)
+    w = _as_2d_rowmajor(w)
+    used = ctypes.c_int(0)
+    code = f(x.data_ptr(), w.data_ptr(), out.data_ptr(), None if bias is None else bias.data_ptr(), M, N, K,
+             x.stride(0), w.stride(0), out.stride(1), out.stride(0), splits, bn, ctypes.byref(used), _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_bf16_splitk")
+    return used.value
+
+
 class _LinearFn(torch.autograd.Function):
     """y = x W^T + b with all three GEMMs on the tcgen05 kernel.
 

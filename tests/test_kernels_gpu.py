@@ -161,3 +161,82 @@ def test_adamw_flat_matches_torch():
     sq = torch.zeros(1, device="cuda")
     optim.sqnorm_accum(g, sq)
     assert abs(sq.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
+
+
+# ------------------------------------------------------------------ split-K GEMM + fused partial-sum consumers
+@pytest.mark.parametrize("M,N,K,splits,bn", [(256, 1536, 8960, 6, 128), (64, 2048, 1536, 4, 64), (200, 1536, 1536, 6, 128),
+                                             (8, 2048, 1536, 24, 64), (130, 520, 200, 3, 64)])
+def test_gemm_splitk_partials_sum_to_product(M, N, K, splits, bn):
+    from skyrl_b200.ops import gemm
+
+    torch.manual_seed(1)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, device="cuda").to(torch.bfloat16)
+    part = torch.full((splits, M, N), float("nan"), device="cuda")
+    used = gemm.gemm_nt_splitk(x, w, b, part, splits, bn)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    assert 1 <= used <= splits
+    ref = x.float() @ w.float().t() + b.float()
+    got = part[:used].sum(0)
+    assert torch.isfinite(got).all()
+    assert ((got - ref).norm() / ref.norm()).item() < 2e-3
+
+
+def test_plan_splitk_covers_the_machine_without_empty_slices():
+    from skyrl_b200.ops import gemm
+
+    for M, N, K in [(256, 2048, 1536), (256, 1536, 1536), (256, 1536, 8960), (64, 2048, 1536), (8, 1536, 8960),
+                    (256, 17920, 1536), (1024, 2048, 1536)]:
+        s, bn = gemm.plan_splitk(M, N, K)
+        kb = (K + 63) // 64
+        kpb = (kb + s - 1) // s
+        assert (s - 1) * kpb < kb  # the last slice is not empty
+        tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
+        assert tiles * s >= 96 or s == 1 and tiles >= 96 or kb < 8
+
+
+def test_add_rmsnorm_partials_matches_reference():
+    from skyrl_b200.ops import elementwise as ew
+
+    torch.manual_seed(2)
+    T, H, P = 77, 1536, 5
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    part = torch.randn(P + 1, T, H, device="cuda") * 0.3
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    x_ref = (x.float() + part[:P].sum(0)).to(torch.bfloat16)
+    xf = x_ref.float()
+    y_ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    y = ew.add_rmsnorm_partials_(x, part, P, w, 1e-6)
+    torch.cuda.synchronize()
+    assert (x.float() - x_ref.float()).abs().max() <= 2 ** -5  # one bf16 ulp at |x| < 8 (summation order)
+    assert ((y.float() - y_ref).norm() / y_ref.norm()).item() < 6e-3
+
+
+def test_qkv_finalize_matches_unfused_rope_and_cache_write():
+    from skyrl_b200.ops import attention as attn_ops
+    from skyrl_b200.ops import elementwise as ew
+
+    torch.manual_seed(3)
+    T, nq, nkv, D, P = 50, 12, 2, 128, 3
+    W = (nq + 2 * nkv) * D
+    part = torch.randn(P, T, W, device="cuda")
+    pos = torch.randint(0, 500, (T,), device="cuda", dtype=torch.int32)
+    table = ew.build_rope_table(512, D, 1e6, "cuda")
+    slots = torch.randperm(64 * 16, device="cuda")[:T].to(torch.int32)
+    slots[5] = -1
+    kc = torch.zeros(64, 16, nkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(kc)
+    qkv = torch.empty(T, W, device="cuda", dtype=torch.bfloat16)
+    ew.qkv_finalize(part, P, pos, table, qkv, kc, vc, slots, nq, nkv, D)
+    ref = part.sum(0).to(torch.bfloat16)
+    ref = ew.rope_(ref, pos, table, nq + nkv, D)
+    attn_ops.kv_cache_write(ref, kc2, vc2, slots, nq, nkv, D)
+    torch.cuda.synchronize()
+    assert (qkv.float() - ref.float()).abs().max() <= 0.0625  # summation order may move a value by one bf16 ulp
+    assert ((qkv.float() - ref.float()).norm() / ref.float().norm()).item() < 3e-3
+    assert ((kc.float() - kc2.float()).norm() / kc2.float().norm()).item() < 3e-3
+    assert ((vc.float() - vc2.float()).norm() / vc2.float().norm()).item() < 3e-3
+    assert kc.view(-1, nkv * D)[slots[6].item()].abs().sum() > 0
