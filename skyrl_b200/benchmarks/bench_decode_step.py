@@ -24,13 +24,14 @@ def main() -> None:
     ap.add_argument("--ctx", type=int, default=900)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="plain GEMMs instead of split-K + fused consumers")
     ap.add_argument("--hbm-gbs", type=float, default=float(os.environ.get("SB_HBM_GBS", "6543.4")))
     args = ap.parse_args()
     a = PRESETS[args.model]
     m = CausalLM(a, device="cuda", dtype=torch.bfloat16, seed=0)
     max_len = args.ctx + args.steps * 3 + 64
     eng = LLMEngine(m, EngineConfig(block_size=32, max_num_seqs=args.seqs, max_model_len=max_len,
-                                    max_num_batched_tokens=1 << 20, enforce_eager=args.eager, sync_interval=args.steps,
+                                    max_num_batched_tokens=1 << 20, enforce_eager=args.eager, sync_interval=args.steps, fused_decode=not args.no_fused,
                                     num_blocks=args.seqs * ((max_len + 31) // 32) + 8))
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(4, a.vocab_size, (args.seqs, args.ctx), generator=g).tolist()
@@ -49,7 +50,7 @@ def main() -> None:
     kv_bytes = args.seqs * ctx_now * 2 * a.num_layers * a.num_kv_heads * a.head_dim * 2
     w_bytes = (m.num_parameters()) * 2
     ideal_ms = (kv_bytes + w_bytes) / (args.hbm_gbs * 1e9) * 1e3
-    print(json.dumps({"model": args.model, "seqs": args.seqs, "ctx": args.ctx, "mode": "eager" if args.eager else "graph",
+    print(json.dumps({"model": args.model, "seqs": args.seqs, "ctx": args.ctx, "mode": "eager" if args.eager else "graph", "fused": not args.no_fused,
                       "ms_per_step": ms, "tokens_per_s": args.seqs / ms * 1e3, "hbm_bytes_per_step": kv_bytes + w_bytes,
                       "roofline_ms": ideal_ms, "fraction_of_measured_hbm_roofline": ideal_ms / ms}))
 
