@@ -1,0 +1,114 @@
+"""Stand-alone rollout serving: one engine + HTTP server per GPU and, on rank 0, a session-affine router in front
+(reference: skyrl/train/entrypoints/serve.py:33-124).  Trainers on another machine point
+``generator.inference_engine.external_proxy_url`` / ``external_server_urls`` at the printed addresses.
+
+    python -m skyrl_b200.launch --nproc-per-node 8 -m skyrl_b200.entrypoints.serve trainer.policy.model.path=... \\
+        generator.inference_engine.served_model_name=policy
+
+Every rank prints one JSON line ``{"rank", "server_url"}``; rank 0 also prints ``{"router_url", "server_urls"}``.
+"""
+
+from __future__ import annotations
+
+import json
+import signal
+import sys
+import threading
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config.config import ConfigError, SkyRLTrainConfig
+from ..parallel import dist as pdist
+from .main_base import BasePPOExp
+
+
+def _validate_serve_cfg(cfg: SkyRLTrainConfig) -> None:
+    ie = cfg.generator.inference_engine
+    if ie.external_proxy_url or ie.external_server_urls:
+        raise ConfigError("serve starts its own servers: unset generator.inference_engine.external_proxy_url / "
+                          "external_server_urls")
+    if not cfg.trainer.policy.model.path:
+        raise ConfigError("serve needs trainer.policy.model.path (the model to serve)")
+
+
+class InferenceOnlyEntrypoint(BasePPOExp):
+    def __init__(self, cfg: SkyRLTrainConfig, base_port: int = 0, host: str = "127.0.0.1"):
+        _validate_serve_cfg(cfg)
+        self.host, self.base_port = host, base_port
+        self._servers, self._router = [], None
+        self._stop = threading.Event()
+        super().__init__(cfg)
+
+    def get_train_dataset(self):
+        return None
+
+    def get_eval_dataset(self):
+        return None
+
+    def _teardown(self) -> None:
+        for s in self._servers:
+            s.stop()
+        if self._router is not None:
+            self._router.stop()
+        self._servers, self._router = [], None
+
+    def start(self) -> dict:
+        """Bring the servers up and return the address record (does not block)."""
+        from ..engine.llm_engine import LLMEngine
+        from ..inference.local_client import LocalInferenceClient
+        from ..inference.router import SessionRouter, build_router_app
+        from ..inference.server import ServerThread, build_app
+        from ..models.decoder import build_model
+        from ..train.trainer import PPOTrainer
+
+        t = self.cfg.trainer
+        model = build_model(t.policy.model.path, device=self.env.device,
+                            dtype=torch.bfloat16 if self.env.device.type == "cuda" else torch.float32, seed=t.seed)
+        shell = PPOTrainer.__new__(PPOTrainer)  # reuse the trainer's engine sizing rules without building workers
+        shell.cfg, shell.env, shell.tokenizer = self.cfg, self.env, self.tokenizer
+        engine: LLMEngine = shell._build_engine(model)
+        client = LocalInferenceClient([engine], self.tokenizer)
+        name = getattr(self.cfg.generator.inference_engine, "served_model_name", None) or t.policy.model.path
+        port = self.base_port + self.env.rank if self.base_port else 0
+        srv = ServerThread(build_app(client, model_name=name), host=self.host, port=port).start()
+        self._servers.append(srv)
+        rec = {"rank": self.env.rank, "server_url": srv.url}
+        urls = [srv.url]
+        if dist.is_initialized() and self.env.world_size > 1:
+            gathered: List[Optional[str]] = [None] * self.env.world_size
+            dist.all_gather_object(gathered, srv.url)
+            urls = [u for u in gathered if u]
+        if self.env.is_main:
+            self._router = ServerThread(build_router_app(SessionRouter(urls)), host=self.host,
+                                        port=(self.base_port + self.env.world_size) if self.base_port else 0).start()
+            rec.update({"router_url": self._router.url, "server_urls": urls})
+        print(json.dumps(rec), flush=True)
+        return rec
+
+    def run(self) -> None:
+        self.start()
+        for sig in (signal.SIGINT, signal.SIGTERM):
+            try:
+                signal.signal(sig, lambda *_: self._stop.set())
+            except ValueError:  # not the main thread
+                pass
+        try:
+            self._stop.wait()
+        finally:
+            self._teardown()
+            pdist.shutdown()
+
+
+def skyrl_entrypoint(cfg: SkyRLTrainConfig):
+    InferenceOnlyEntrypoint(cfg).run()
+
+
+def main(argv: Optional[List[str]] = None) -> None:
+    cfg = SkyRLTrainConfig.from_cli_overrides(sys.argv[1:] if argv is None else argv)
+    skyrl_entrypoint(cfg)
+
+
+if __name__ == "__main__":
+    main()
