@@ -35,6 +35,37 @@ struct GemmCfg {
 
 enum OutMode { kOutBf16 = 0, kOutF32 = 1, kOutF32Accum = 2 };
 
+// Tensor-parallel extensions of the kernel (both optional, selected by template flags):
+//  GATHER  - the A operand is sequence-sharded over n_ranks GPUs.  Four extra warps copy the remote shards into
+//            this GPU's full-size A buffer piece by piece (plain peer loads over NVLink, each byte crosses once)
+//            and publish a per-m-block counter; the TMA producer waits for an m-block's counter before loading
+//            it, and tiles are walked starting with the local shard so the copies hide behind the math.
+//  SCATTER - the epilogue stores each output tile straight into peer memory: to the rank that owns those rows
+//            (reduce-scatter layout, slot = this rank) or to every rank (all-reduce layout); the consumer kernel
+//            on the owning GPU adds the n_ranks slots.
+constexpr int kTpMaxRanks = 8;
+constexpr int kGatherWarps = 4;
+constexpr int kPiecesPerBlock = 8;  // an m-block (128 rows) is copied as 8 pieces of 16 rows
+
+struct TpArgs {
+  const void* src[kTpMaxRanks];  // GATHER: rank r's own shard (rows [r*rows_per_rank, ...) of the full matrix)
+  void* a_full;                  // GATHER: this GPU's full A buffer (the tensor map covers it)
+  unsigned int* flags;           // GATHER: [m_blocks] piece counters followed by one work ticket
+  void* dst[kTpMaxRanks];        // SCATTER: rank d's partial-sum buffer
+  long long lda;                 // GATHER: row stride of A in elements
+  long long slot_stride;         // SCATTER: elements between two source ranks' slots in a destination buffer
+  int n_ranks, my_rank;
+  int rows_per_rank;             // rows of the full matrix owned by each rank (A rows for GATHER, C rows for SCATTER)
+  int scatter_all;               // SCATTER: 0 = rows go to their owner only, 1 = every rank receives every row
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
 struct TileMap {
   int m_blocks, n_blocks;
   __device__ __forceinline__ void get(int tile, int& pm, int& pn) const {
@@ -48,11 +79,11 @@ struct TileMap {
   }
 };
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, bool A_MN, bool B_MN, bool GATHER = false, bool SCATTER = false>
+__global__ void __launch_bounds__(kGemmThreads + (GATHER ? kGatherWarps * 32 : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
                  const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc, int out_mode, int splits,
-                 long long split_stride, int* status) {
+                 long long split_stride, int* status, const __grid_constant__ TpArgs tp) {
   // splits > 1: split-K. Work item = (output tile, k slice); slice ks writes its fp32 partial sum to
   // C + ks * split_stride (the consumer kernel adds the partials), bias is applied by slice 0 only.
   using Cfg = GemmCfg<BN>;
@@ -72,6 +103,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles = tiles_mn * splits;
   const int k_blocks = (K + kBK - 1) / kBK;
   const int kpb = (k_blocks + splits - 1) / splits;  // k blocks per slice (host guarantees no empty slice)
+  // GATHER: logical m-block 0 is the first block of the local shard, then the next rank's, and so on
+  const int m_rot = GATHER ? tp.my_rank * (tp.rows_per_rank / kBM) : 0;
+  auto rot = [&](int pm) { return GATHER ? (pm + m_rot) % tm.m_blocks : pm; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -100,10 +134,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       int it = 0;
       bool ok = true;
+      unsigned long long ready_mask = 0;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         int pm, pn;
         const int ks = tile / tiles_mn;
         tm.get(tile - ks * tiles_mn, pm, pn);
+        pm = rot(pm);
+        if (GATHER) {
+          // rows of another rank: wait until the copy warps have landed every piece of this m-block
+          const int owner = (pm * kBM) / tp.rows_per_rank;
+          if (owner != tp.my_rank && !((ready_mask >> (pm & 63)) & 1ull)) {
+            const unsigned long long t0 = globaltimer_ns();
+            while (ld_acquire_gpu(tp.flags + pm) < static_cast<unsigned int>(kPiecesPerBlock)) {
+              if (*reinterpret_cast<volatile int*>(status) != 0 || globaltimer_ns() - t0 > kWaitTimeoutNs) {
+                atomicCAS(status, 0, 0x104);
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            fence_proxy_async_global();  // generic-proxy stores of the copy warps -> async-proxy (TMA) reads
+            if (tm.m_blocks <= 64) ready_mask |= 1ull << pm;
+          }
+        }
         const int kb0 = ks * kpb, kb1 = min(k_blocks, kb0 + kpb);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % Cfg::kStages;
@@ -167,7 +220,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (ok) umma_commit(&tfull[acc]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue -----------------------------------
     const int q = warp & 3;  // TMEM lane quadrant this warp may access
     int tcount = 0;
@@ -175,6 +228,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int pm, pn;
       const int ks = tile / tiles_mn;
       tm.get(tile - ks * tiles_mn, pm, pn);
+      pm = rot(pm);
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aph, status, 0x301)) break;
@@ -197,55 +251,119 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
             }
           }
-          if (out_mode == kOutBf16) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(C) + static_cast<long long>(row) * ldc + col0;
-            if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+          auto store_chunk = [&](void* cbase, long long elem_off) {
+            if (out_mode == kOutBf16) {
+              __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(cbase) + elem_off;
+              if (full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 o;
-                o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                reinterpret_cast<uint4*>(crow)[v] = o;
+                for (int v = 0; v < 4; ++v) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                  o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                  o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                  o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                  reinterpret_cast<uint4*>(crow)[v] = o;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < N) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
               }
             } else {
+              float* crow = reinterpret_cast<float*>(cbase) + elem_off;
+              const bool vec = full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
+              if (vec) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
+                for (int v = 0; v < 8; ++v) {
+                  float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                         __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                  if (out_mode == kOutF32Accum) {
+                    const float4 p = reinterpret_cast<float4*>(crow)[v];
+                    o.x += p.x;
+                    o.y += p.y;
+                    o.z += p.z;
+                    o.w += p.w;
+                  }
+                  reinterpret_cast<float4*>(crow)[v] = o;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < N) {
+                    float o = __uint_as_float(r[j]);
+                    if (out_mode == kOutF32Accum) o += crow[j];
+                    crow[j] = o;
+                  }
+              }
             }
+          };
+          if (!SCATTER) {
+            store_chunk(C, ks * split_stride + static_cast<long long>(row) * ldc + col0);
+          } else if (tp.scatter_all) {
+            // all-reduce layout: every rank receives this rank's partial rows in slot my_rank
+            const long long off = tp.my_rank * tp.slot_stride + static_cast<long long>(row) * ldc + col0;
+#pragma unroll 1
+            for (int d = 0; d < tp.n_ranks; ++d) store_chunk(tp.dst[(tp.my_rank + d) % tp.n_ranks], off);
           } else {
-            float* crow = reinterpret_cast<float*>(C) + ks * split_stride + static_cast<long long>(row) * ldc + col0;
-            const bool vec = full_chunk && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                if (out_mode == kOutF32Accum) {
-                  const float4 p = reinterpret_cast<float4*>(crow)[v];
-                  o.x += p.x;
-                  o.y += p.y;
-                  o.z += p.z;
-                  o.w += p.w;
-                }
-                reinterpret_cast<float4*>(crow)[v] = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) {
-                  float o = __uint_as_float(r[j]);
-                  if (out_mode == kOutF32Accum) o += crow[j];
-                  crow[j] = o;
-                }
-            }
+            // reduce-scatter layout: the rows' owner receives them, at its local row index, in slot my_rank
+            const int dest = row / tp.rows_per_rank;
+            store_chunk(tp.dst[dest], tp.my_rank * tp.slot_stride +
+                                          static_cast<long long>(row - dest * tp.rows_per_rank) * ldc + col0);
           }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  } else if (GATHER) {
+    // ------------------------------ copy warps (remote A shards -> local full buffer) ---------------
+    // Work is handed out by a ticket counter so that whichever CTAs are resident finish every piece.
+    const int bpr = tp.rows_per_rank / kBM;               // m-blocks per rank
+    const int total = (tp.n_ranks - 1) * bpr * kPiecesPerBlock;
+    const int vec_per_row = K >> 3;                        // 16-byte vectors per row
+    constexpr int kRowsPerPiece = kBM / kPiecesPerBlock;
+    unsigned int* ticket = tp.flags + tm.m_blocks;
+    while (true) {
+      int piece = 0;
+      if (lane == 0) piece = static_cast<int>(atomicAdd(ticket, 1u));
+      piece = __shfl_sync(0xffffffffu, piece, 0);
+      if (piece >= total) break;
+      const int bi = piece / kPiecesPerBlock, sub = piece - bi * kPiecesPerBlock;
+      const int src_rank = (tp.my_rank + 1 + bi / bpr) % tp.n_ranks;
+      const int mb = src_rank * bpr + bi % bpr;
+      const int row0 = mb * kBM + sub * kRowsPerPiece;     // row in the full matrix
+      const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(tp.src[src_rank]) +
+                                                        static_cast<long long>(row0 - src_rank * tp.rows_per_rank) * tp.lda);
+      uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tp.a_full) +
+                                           static_cast<long long>(row0) * tp.lda);
+      const int ld_vec = static_cast<int>(tp.lda >> 3);
+      const int n_vec = kRowsPerPiece * vec_per_row;
+      for (int base = 0; base < n_vec; base += 32 * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int idx = base + u * 32 + lane;
+          if (idx < n_vec) {
+            const int rr = idx / vec_per_row, cc = idx - rr * vec_per_row;
+            v[u] = sp[static_cast<long long>(rr) * ld_vec + cc];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int idx = base + u * 32 + lane;
+          if (idx < n_vec) {
+            const int rr = idx / vec_per_row, cc = idx - rr * vec_per_row;
+            dp[static_cast<long long>(rr) * ld_vec + cc] = v[u];
+          }
+        }
+      }
+      fence_proxy_async_global();
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        atomicAdd(tp.flags + mb, 1u);
+      }
     }
   }
 
@@ -272,7 +390,38 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kfn<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N,
-                                                       K, ldc, out_mode, splits, split_stride, device_status_ptr());
+                                                       K, ldc, out_mode, splits, split_stride, device_status_ptr(),
+                                                       TpArgs{});
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+// Tensor-parallel launch: x @ W^T (B_MN = false) or dy @ W (B_MN = true) with the A operand gathered from peers
+// and / or the output scattered to peers (see TpArgs).
+template <int BN, bool B_MN, bool GATHER, bool SCATTER>
+static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, int out_mode, const TpArgs& tp, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  const CUtensorMap* ta = get_tmap_bf16_2d(A, M, K, lda, kBM);
+  const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN);
+  if (!ta || !tb) return SB_ERR_TMAP;
+  static bool attr_set = false;
+  auto kfn = gemm_bf16_kernel<BN, false, B_MN, GATHER, SCATTER>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+      return SB_ERR_CUDA;
+    attr_set = true;
+  }
+  const int m_blocks = (M + kBM - 1) / kBM;
+  const int tiles = m_blocks * ((N + BN - 1) / BN);
+  if (GATHER) {
+    // piece counters and the ticket start at zero for every launch
+    if (cudaMemsetAsync(tp.flags, 0, sizeof(unsigned int) * (m_blocks + 1), stream) != cudaSuccess) return SB_ERR_CUDA;
+  }
+  // with GATHER every CTA also carries copy warps, so launch the full machine even for few tiles
+  const int grid = GATHER ? sm_count() : (tiles < sm_count() ? tiles : sm_count());
+  const int threads = kGemmThreads + (GATHER ? kGatherWarps * 32 : 0);
+  kfn<<<grid, threads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc,
+                                                  out_mode, 1, 0, device_status_ptr(), tp);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
@@ -331,6 +480,64 @@ int sb_gemm_bf16_splitk(const void* A, const void* B, float* C, const void* bias
   if (bn == 256) return sb::launch_gemm<256, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
   if (bn == 128) return sb::launch_gemm<128, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
   return sb::launch_gemm<64, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
+}
+
+
+// Tensor-parallel GEMM with the collective inside the kernel.
+//   gather != 0 : A is the full [M, K] buffer on this GPU whose rows [r*rows_per_rank, (r+1)*rows_per_rank) belong to
+//                 rank r; peers[r] points at rank r's own shard (in rank r's memory).  The kernel copies the remote
+//                 shards in while it computes (all-gather fused into the GEMM).  flags: (M/128 + 1) uint32 of scratch.
+//                 M must equal n_ranks * rows_per_rank and rows_per_rank must be a multiple of 128.
+//   scatter = 1 : C rows are stored to their owner rank's buffer outs[row / rows_per_rank] at slot my_rank
+//                 (reduce-scatter layout; the owner adds the n_ranks slots), scatter = 2: to every rank (all-reduce).
+//   b_mn selects W stored [N, K] (0) or [K, N] (1).  out_mode 0 = bf16, 1 = fp32.
+int sb_gemm_tp(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda, long long ldb,
+               long long ldc, int b_mn, int out_mode, int gather, int scatter, const void* const* peers,
+               void* const* outs, int n_ranks, int my_rank, int rows_per_rank, long long slot_stride,
+               unsigned int* flags, int bn, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (K & 7)) return SB_ERR_ARG;
+  if (n_ranks < 1 || n_ranks > sb::kTpMaxRanks || my_rank < 0 || my_rank >= n_ranks || rows_per_rank <= 0) return SB_ERR_ARG;
+  if (out_mode != 0 && out_mode != 1) return SB_ERR_ARG;
+  if (!gather && !scatter) return SB_ERR_ARG;
+  sb::TpArgs tp{};
+  tp.n_ranks = n_ranks;
+  tp.my_rank = my_rank;
+  tp.rows_per_rank = rows_per_rank;
+  tp.lda = lda;
+  tp.slot_stride = slot_stride;
+  tp.scatter_all = scatter == 2;
+  if (gather) {
+    if (!peers || !flags || rows_per_rank % sb::kBM != 0 || M != n_ranks * rows_per_rank) return SB_ERR_ARG;
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!peers[r] || (reinterpret_cast<uintptr_t>(peers[r]) & 15)) return SB_ERR_ARG;
+      tp.src[r] = peers[r];
+    }
+    tp.a_full = const_cast<void*>(A);
+    tp.flags = flags;
+  }
+  if (scatter) {
+    if (!outs) return SB_ERR_ARG;
+    if (scatter == 1 && M > n_ranks * rows_per_rank) return SB_ERR_ARG;
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!outs[r]) return SB_ERR_ARG;
+      tp.dst[r] = outs[r];
+    }
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn != 128 && bn != 256) bn = (static_cast<long long>((M + 127) / 128) * ((N + 255) / 256) >= sb::sm_count()) ? 256 : 128;
+#define SB_TP_CASE(BNV, BMN, G, S)                                                                                   \
+  if (bn == BNV && (b_mn != 0) == BMN && (gather != 0) == G && (scatter != 0) == S)                                  \
+    return sb::launch_gemm_tp<BNV, BMN, G, S>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, tp, st);
+  SB_TP_CASE(128, false, true, false)
+  SB_TP_CASE(256, false, true, false)
+  SB_TP_CASE(128, true, true, false)
+  SB_TP_CASE(256, true, true, false)
+  SB_TP_CASE(128, false, false, true)
+  SB_TP_CASE(256, false, false, true)
+  SB_TP_CASE(128, true, false, true)
+  SB_TP_CASE(256, true, false, true)
+#undef SB_TP_CASE
+  return SB_ERR_ARG;
 }
 
 }  // extern "C"

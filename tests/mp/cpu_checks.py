@@ -1,0 +1,77 @@
+"""Run under torchrun on CPU (gloo), world size 2: host-side logic of the multi-rank paths."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from skyrl_b200.parallel import dist as pdist  # noqa: E402
+from skyrl_b200.parallel import tensor_parallel as tpm  # noqa: E402
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def check_tp(env):
+    W, r = env.world_size, env.rank
+    tp = tpm.TPGroup(None)
+    assert not tp.fused and tp.size == W
+    T, H, F = 8 * W, 16, 32
+    g = torch.Generator().manual_seed(0)
+    x_full, w1, w2 = torch.randn(T, H, generator=g), torch.randn(F, H, generator=g) * 0.1, torch.randn(H, F, generator=g) * 0.1
+    dy = torch.randn(T, H, generator=g)
+    R, Fs = T // W, F // W
+    x = x_full[r * R : (r + 1) * R].clone().requires_grad_()
+    w1s = w1[r * Fs : (r + 1) * Fs].clone().requires_grad_()
+    w2s = w2[:, r * Fs : (r + 1) * Fs].clone().requires_grad_()
+    y = tpm.row_parallel_linear(tpm.column_parallel_linear(x, w1s, None, tp), w2s, tp)
+    y.backward(dy[r * R : (r + 1) * R])
+    xr, w1r, w2r = x_full.clone().requires_grad_(), w1.clone().requires_grad_(), w2.clone().requires_grad_()
+    yr = (xr @ w1r.t()) @ w2r.t()
+    yr.backward(dy)
+    assert rel(y, yr[r * R : (r + 1) * R]) < 1e-5
+    assert rel(x.grad, xr.grad[r * R : (r + 1) * R]) < 1e-5
+    assert rel(w1s.grad, w1r.grad[r * Fs : (r + 1) * Fs]) < 1e-5
+    assert rel(w2s.grad, w2r.grad[:, r * Fs : (r + 1) * Fs]) < 1e-5
+
+
+def check_sharded_optimizer(env):
+    from skyrl_b200.parallel.sharded_optimizer import ShardedAdamW
+
+    W, r = env.world_size, env.rank
+    N = 64 * W
+    torch.manual_seed(0)
+    p = torch.randn(N)
+    ref = p.clone().requires_grad_()
+    opt_ref = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    grads = torch.zeros(N)
+    opt = ShardedAdamW(p, grads, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1e9)
+    for step in range(3):
+        torch.manual_seed(10 * step + r)
+        g_local = torch.randn(N)
+        grads.copy_(g_local)
+        g_sum = g_local.clone()
+        dist.all_reduce(g_sum)
+        ref.grad = g_sum
+        opt.step()
+        opt.zero_grad()
+        opt_ref.step()
+        assert rel(p, ref.detach()) < 1e-5, (step, rel(p, ref.detach()))
+
+
+def main():
+    env = pdist.init_distributed()
+    assert env.world_size == 2 and env.device.type == "cpu"
+    check_tp(env)
+    check_sharded_optimizer(env)
+    dist.barrier()
+    if env.rank == 0:
+        print("CPU_CHECKS_OK", flush=True)
+    pdist.shutdown()
+
+
+if __name__ == "__main__":
+    main()

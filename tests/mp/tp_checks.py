@@ -1,0 +1,124 @@
+"""Run under torchrun with 2+ GPUs: tensor-parallel linears with the collective inside the GEMM kernel, against an
+unsharded fp32 reference, forward and backward; prints one timing line per rank 0."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from skyrl_b200.ops import _lib  # noqa: E402
+from skyrl_b200.parallel import dist as pdist  # noqa: E402
+from skyrl_b200.parallel import tensor_parallel as tpm  # noqa: E402
+from skyrl_b200.parallel.peer import PeerContext  # noqa: E402
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def main():
+    env = pdist.init_distributed()
+    dev, W, r = env.device, env.world_size, env.rank
+    ctx = PeerContext(dev, wait_seconds=5.0)
+    tp = tpm.TPGroup(ctx)
+    assert tp.fused
+    T, H, F = 128 * W * 2, 512, 1024  # tokens, hidden, ffn (full sizes)
+    R = T // W
+    g = torch.Generator().manual_seed(0)
+    x_full = (torch.randn(T, H, generator=g) * 0.5).to(torch.bfloat16)
+    w1 = (torch.randn(F, H, generator=g) * 0.05).to(torch.bfloat16)  # column-parallel: rows of w1 sharded
+    w2 = (torch.randn(H, F, generator=g) * 0.05).to(torch.bfloat16)  # row-parallel: columns of w2 sharded
+    dy_full = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    Fs = F // W
+    x = x_full[r * R : (r + 1) * R].to(dev).requires_grad_()
+    w1s = w1[r * Fs : (r + 1) * Fs].contiguous().to(dev).requires_grad_()
+    w2s = w2[:, r * Fs : (r + 1) * Fs].contiguous().to(dev).requires_grad_()
+    h = tpm.column_parallel_linear(x, w1s, None, tp)  # [T, F/W]
+    y = tpm.row_parallel_linear(h, w2s, tp)  # [T/W, H]
+    y.backward(dy_full[r * R : (r + 1) * R].to(dev))
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    xr = x_full.float().requires_grad_()
+    w1r, w2r = w1.float().requires_grad_(), w2.float().requires_grad_()
+    hr = (xr @ w1r.t()).to(torch.bfloat16).float()  # the sharded path rounds h to bf16 as well
+    hr.retain_grad()
+    yr = hr @ w2r.t()
+    yr.backward(dy_full.float())
+    assert rel(y.cpu(), yr[r * R : (r + 1) * R]) < 2e-2, rel(y.cpu(), yr[r * R : (r + 1) * R])
+    dh = dy_full.float() @ w2.float()
+    dx_ref = (dh.to(torch.bfloat16).float() @ w1.float())[r * R : (r + 1) * R]
+    assert rel(x.grad.cpu(), dx_ref) < 3e-2, rel(x.grad.cpu(), dx_ref)
+    dw1_ref = dh.t() @ x_full.float()
+    dw2_ref = dy_full.float().t() @ hr
+    assert rel(w1s.grad.cpu(), dw1_ref[r * Fs : (r + 1) * Fs]) < 3e-2
+    assert rel(w2s.grad.cpu(), dw2_ref[:, r * Fs : (r + 1) * Fs]) < 3e-2
+
+    # ---- timing: fused all-gather GEMM and GEMM reduce-scatter against NCCL + plain GEMM (device time, max over ranks)
+    from skyrl_b200.ops import gemm
+
+    T2, H2, F2 = 8192, 3584, 18944  # 7B-shaped MLP
+    R2, Fs2 = T2 // W, (F2 // W) // 128 * 128
+    buf = tp.gather_buffer(T2, H2, "bench_x")
+    buf.local.normal_()
+    wc = (torch.randn(Fs2, H2, device=dev) * 0.02).to(torch.bfloat16)
+    wr = (torch.randn(H2, Fs2, device=dev) * 0.02).to(torch.bfloat16)
+    hloc = (torch.randn(T2, Fs2, device=dev) * 0.5).to(torch.bfloat16)
+    slots = tp.slot_buffer(R2, H2, torch.bfloat16, "bench_y")
+    xs = buf.local.view(T2, H2)[r * R2 : (r + 1) * R2].clone()
+    outg = torch.empty(T2, Fs2, device=dev, dtype=torch.bfloat16)
+
+    def timed(fn, iters=5):
+        for _ in range(3):
+            fn()
+        ctx.barrier()
+        torch.cuda.synchronize()
+        dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def fused_ag():
+        ctx.barrier()
+        tpm.gemm_all_gather(tp, buf, R2, wc, out=outg)
+
+    def nccl_ag():
+        full = torch.empty(T2, H2, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full, xs)
+        gemm.gemm_nt(full, wc, out=outg)
+
+    def fused_rs():
+        tpm.gemm_reduce_scatter(tp, hloc, wr, slots, R2)
+        ctx.barrier()
+        tpm.reduce_slots(slots.local.view(W, R2, H2))
+        ctx.barrier(1)
+
+    def nccl_rs():
+        yfull = gemm.gemm_nt(hloc, wr)
+        out = torch.empty(R2, H2, device=dev, dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(out, yfull)
+
+    res = {"ag_gemm_fused_ms": timed(fused_ag), "ag_gemm_nccl_ms": timed(nccl_ag), "gemm_rs_fused_ms": timed(fused_rs),
+           "gemm_rs_nccl_ms": timed(nccl_rs), "world": W, "shape": [T2, H2, Fs2]}
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    fl = 2.0 * T2 * H2 * Fs2
+    res["ag_gemm_fused_tflops"] = fl / res["ag_gemm_fused_ms"] / 1e9
+    res["gemm_rs_fused_tflops"] = fl / res["gemm_rs_fused_ms"] / 1e9
+    if r == 0:
+        import json
+
+        print("TP_CHECKS " + json.dumps(res), flush=True)
+    dist.barrier()
+    pdist.shutdown()
+
+
+if __name__ == "__main__":
+    main()

@@ -71,3 +71,68 @@ def test_linear_autograd():
     assert _rel_err(x.grad, xr.grad) < 6e-3
     assert _rel_err(w.grad, wr.grad) < 6e-3
     assert _rel_err(b.grad, br.grad) < 6e-3
+
+
+# ------------------------------------------------------------------ tensor-parallel modes, ranks emulated on one GPU
+def _tp_call(A, B, C, M, N, K, b_mn, out_mode, gather, scatter, peers, outs, n_ranks, my_rank, rpr, slot_stride, flags, bn=0):
+    import ctypes
+
+    from skyrl_b200.ops import _lib
+    from skyrl_b200.parallel import tensor_parallel as tpm
+
+    lib = tpm._k()
+    pa = (ctypes.c_void_p * n_ranks)(*peers) if peers else None
+    oa = (ctypes.c_void_p * n_ranks)(*outs) if outs else None
+    code = lib.sb_gemm_tp(A.data_ptr(), B.data_ptr(), None if C is None else C.data_ptr(), None, M, N, K, A.stride(0),
+                          B.stride(0), N, int(b_mn), out_mode, gather, scatter, pa, oa, n_ranks, my_rank, rpr, slot_stride,
+                          None if flags is None else flags.data_ptr(), bn, _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_tp")
+
+
+@pytest.mark.parametrize("n_ranks,rpr,N,K,b_mn", [(2, 256, 384, 512, False), (4, 128, 1024, 1536, False), (2, 128, 256, 320, True)])
+def test_gemm_gather_mode_matches_full_product(n_ranks, rpr, N, K, b_mn):
+    """All-gather fused into the GEMM: every 'rank' is a separate local buffer here, launches run one after another
+    (the kernel only waits on flags that its own copy warps set)."""
+    from skyrl_b200.ops import _lib
+
+    torch.manual_seed(0)
+    M = n_ranks * rpr
+    shards = [(torch.randn(rpr, K, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(n_ranks)]
+    W = (torch.randn(K, N, device="cuda") * 0.05).to(torch.bfloat16) if b_mn else \
+        (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    x_all = torch.cat(shards, 0)
+    ref = x_all.float() @ (W.float() if b_mn else W.float().t())
+    flags = torch.zeros(M // 128 + 1, dtype=torch.int32, device="cuda")
+    for me in range(n_ranks):
+        a_full = torch.full((M, K), float("nan"), device="cuda", dtype=torch.bfloat16)
+        a_full[me * rpr : (me + 1) * rpr] = shards[me]
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        _tp_call(a_full, W, out, M, N, K, b_mn, 0, 1, 0, [s.data_ptr() for s in shards], None, n_ranks, me, rpr, 0, flags)
+        torch.cuda.synchronize()
+        assert _lib.status_read_clear() == 0
+        assert torch.equal(a_full, x_all)  # the gathered operand is left behind for the backward pass
+        assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
+
+
+@pytest.mark.parametrize("all_ranks", [False, True])
+def test_gemm_scatter_mode_slots_sum_to_product(all_ranks):
+    from skyrl_b200.ops import _lib
+
+    torch.manual_seed(1)
+    n_ranks, rpr, N, Kloc = 4, 96, 512, 256
+    M = n_ranks * rpr
+    xs = [(torch.randn(M, Kloc, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(n_ranks)]
+    ws = [(torch.randn(N, Kloc, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(n_ranks)]
+    ref = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
+    rows = M if all_ranks else rpr
+    dests = [torch.full((n_ranks, rows, N), float("nan"), device="cuda") for _ in range(n_ranks)]
+    for me in range(n_ranks):
+        _tp_call(xs[me], ws[me], None, M, N, Kloc, False, 1, 0, 2 if all_ranks else 1, None, [d.data_ptr() for d in dests],
+                 n_ranks, me, M if all_ranks else rpr, rows * N, None)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    for d in range(n_ranks):
+        got = dests[d].sum(0)
+        want = ref if all_ranks else ref[d * rpr : (d + 1) * rpr]
+        assert torch.isfinite(got).all()
+        assert ((got - want).norm() / want.norm()).item() < 2e-3

@@ -28,3 +28,9 @@ def test_bench_two_gpus_tiny():
     p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-d128",
               "--prompts-per-gpu", "4"], port=29618)
     assert p.returncode == 0 and '"n_gpus": 2' in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_fused_gemm_collectives():
+    p = _run([os.path.join(ROOT, "tests", "mp", "tp_checks.py")], port=29619)
+    assert p.returncode == 0 and "TP_CHECKS" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]

@@ -1,0 +1,24 @@
+"""Multi-process paths on CPU (gloo, world size 2): tensor-parallel layer logic, sharded optimizer, a 2-rank RL step."""
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script_args, nproc=2, timeout=900, port=29631):
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port)] + script_args
+    return subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+def test_gloo_tp_and_sharded_optimizer():
+    p = _run([os.path.join(ROOT, "tests", "mp", "cpu_checks.py")])
+    assert p.returncode == 0 and "CPU_CHECKS_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_gloo_two_rank_rl_step():
+    p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-d128",
+              "--prompts-per-gpu", "1"], port=29632)
+    assert p.returncode == 0 and '"n_gpus": 2' in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
