@@ -167,9 +167,52 @@ __global__ void qkv_finalize_kernel(const float* __restrict__ part, int n_part, 
   }
 }
 
+// out[i] = sum_s slots[s][i] (fp32 accumulation), 8 elements per thread.
+template <typename T>
+__global__ void reduce_slots_kernel(const T* __restrict__ slots, int n_slots, long long slot_stride,
+                                    __nv_bfloat16* __restrict__ out, long long n8) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_slots; ++s) {
+      if (sizeof(T) == 2) {
+        float v[8];
+        ld_bf16x8(reinterpret_cast<const __nv_bfloat16*>(slots) + s * slot_stride + i * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += v[j];
+      } else {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(slots) + s * slot_stride + i * 8);
+        const float4 a = p[0], b = p[1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      }
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = pack_bf16x8(acc);
+  }
+}
+
 }  // namespace sb
 
 extern "C" {
+
+// out (bf16, n elements) = sum over n_slots partial buffers (bf16 or fp32) spaced slot_stride elements apart.
+int sb_reduce_slots(const void* slots, int n_slots, long long slot_stride, int slots_fp32, void* out, long long n,
+                    void* stream) {
+  if (n <= 0 || (n & 7) || (slot_stride & 7) || n_slots < 1) return SB_ERR_ARG;
+  const long long n8 = n >> 3;
+  long long blocks = (n8 + 255) / 256;
+  const long long cap = static_cast<long long>(sb::sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (slots_fp32)
+    sb::reduce_slots_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(
+        reinterpret_cast<const float*>(slots), n_slots, slot_stride, reinterpret_cast<__nv_bfloat16*>(out), n8);
+  else
+    sb::reduce_slots_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(slots), n_slots, slot_stride, reinterpret_cast<__nv_bfloat16*>(out), n8);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
 
 // x[T,H] (bf16, in place) += sum of n_part fp32 partials [T,H]; y = rmsnorm(x) * w.
 int sb_add_rmsnorm_partials(void* x, const float* part, int n_part, long long part_stride, const void* w, void* y,

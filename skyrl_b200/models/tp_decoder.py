@@ -1,0 +1,200 @@
+"""Tensor-parallel decoder (Megatron-style TP with sequence-parallel activations) on the fused GEMM collectives.
+
+Each rank holds ``1/tp`` of the attention heads and of the FFN width; the residual stream, norms and the LM head
+work on ``1/tp`` of the packed tokens.  Per layer there are two all-gather+GEMM kernels (QKV, gate/up) and two
+GEMM+reduce-scatter kernels (o-proj, down-proj); see ``parallel/tensor_parallel.py``.  This is the training-side
+counterpart of what the reference configures through Megatron-Bridge
+(skyrl/backends/skyrl_train/workers/megatron/megatron_worker.py:377-545, parallel sizes :468-474) and executes in
+``MegatronModelWrapper.forward`` (megatron_model_wrapper.py:285-528) -- but the layer math is the same packed,
+varlen code as the unsharded model, instantiated with the local head / FFN counts.
+
+The packed token count must be a multiple of ``tp * 128`` (``pad_packed_for_tp``): the gather kernel moves whole
+128-row blocks.  Parameters that every rank replicates (embedding, norms, LM head) receive the sum of the ranks'
+gradients through ``reduce_replicated_grads`` before the optimizer step.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import attention as attn_ops
+from ..ops import elementwise as ew
+from ..parallel import tensor_parallel as tpm
+from .decoder import CausalLM, ModelArgs, _EmbeddingFn
+
+REPLICATED_LEAVES = ("embed", "ln1", "ln2", "final_norm", "lm_head", "q_norm", "k_norm", "value_head")
+
+
+def local_args(a: ModelArgs, tp: int) -> ModelArgs:
+    if a.num_heads % tp or a.intermediate_size % tp:
+        raise ValueError(f"num_heads={a.num_heads} and intermediate_size={a.intermediate_size} must divide by tp={tp}")
+    if a.num_kv_heads % tp:
+        raise ValueError(f"num_kv_heads={a.num_kv_heads} must divide by tp={tp} (KV-head replication is not supported)")
+    if a.num_experts:
+        raise ValueError("tensor parallelism of MoE layers is expert-parallel; use the EP path")
+    return dataclasses.replace(a, num_heads=a.num_heads // tp, num_kv_heads=a.num_kv_heads // tp,
+                               intermediate_size=a.intermediate_size // tp)
+
+
+def shard_param(name: str, full: torch.Tensor, a: ModelArgs, tp: int, r: int) -> torch.Tensor:
+    """Rank ``r``'s slice of a full parameter (fused QKV and gate/up are sliced per component)."""
+    leaf = name.split(".")[-1]
+    d = a.head_dim
+    if leaf in ("wqkv", "bqkv"):
+        q, k, v = full[: a.q_dim], full[a.q_dim : a.q_dim + a.kv_dim], full[a.q_dim + a.kv_dim :]
+        qs, ks = a.q_dim // tp, a.kv_dim // tp
+        return torch.cat([q[r * qs : (r + 1) * qs], k[r * ks : (r + 1) * ks], v[r * ks : (r + 1) * ks]], 0)
+    if leaf == "wo":
+        qs = a.q_dim // tp
+        return full[:, r * qs : (r + 1) * qs]
+    if leaf == "wgu":
+        F, fs = a.intermediate_size, a.intermediate_size // tp
+        return torch.cat([full[r * fs : (r + 1) * fs], full[F + r * fs : F + (r + 1) * fs]], 0)
+    if leaf == "wd":
+        fs = a.intermediate_size // tp
+        return full[:, r * fs : (r + 1) * fs]
+    return full
+
+
+def unshard_param(name: str, shards: List[torch.Tensor], a: ModelArgs) -> torch.Tensor:
+    """Inverse of ``shard_param`` (used for weight sync to the generation engine and for HF export)."""
+    leaf = name.split(".")[-1]
+    tp = len(shards)
+    if leaf in ("wqkv", "bqkv"):
+        qs, ks = a.q_dim // tp, a.kv_dim // tp
+        return torch.cat([s[:qs] for s in shards] + [s[qs : qs + ks] for s in shards] + [s[qs + ks :] for s in shards], 0)
+    if leaf in ("wo", "wd"):
+        return torch.cat(shards, 1)
+    if leaf == "wgu":
+        fs = a.intermediate_size // tp
+        return torch.cat([s[:fs] for s in shards] + [s[fs:] for s in shards], 0)
+    return shards[0]
+
+
+def pad_packed_for_tp(input_ids: torch.Tensor, positions: torch.Tensor, cu_seqlens: torch.Tensor, tp: int,
+                      pad_id: int = 0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]:
+    """Pad the packed batch to a multiple of ``tp * 128`` tokens with one extra dummy sequence. Returns the padded
+    tensors and the number of real tokens."""
+    T = input_ids.numel()
+    mult = tp * 128
+    Tp = (T + mult - 1) // mult * mult
+    if Tp == T:
+        return input_ids, positions, cu_seqlens, T
+    n = Tp - T
+    ids = torch.cat([input_ids, torch.full((n,), pad_id, dtype=input_ids.dtype, device=input_ids.device)])
+    pos = torch.cat([positions, torch.arange(n, dtype=positions.dtype, device=positions.device)])
+    cu = torch.cat([cu_seqlens, torch.tensor([Tp], dtype=cu_seqlens.dtype, device=cu_seqlens.device)])
+    return ids, pos, cu, T
+
+
+class _GatherRowsFn(torch.autograd.Function):
+    """All-gather of per-rank row shards of a small tensor (log-probs); backward keeps the local slice."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        W = dist.get_world_size(group) if dist.is_initialized() else 1
+        if W == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(W)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        W = dist.get_world_size(ctx.group) if dist.is_initialized() else 1
+        if W == 1:
+            return g, None
+        r = dist.get_rank(ctx.group)
+        n = g.shape[0] // W
+        return g[r * n : (r + 1) * n].contiguous(), None
+
+
+class TPCausalLM(CausalLM):
+    """Local shard of a tensor-parallel model; ``full_args`` describes the unsharded architecture."""
+
+    def __init__(self, full_args: ModelArgs, tp: tpm.TPGroup, device="cpu", dtype=torch.bfloat16, value_head: bool = False,
+                 flat_buffer: Optional[torch.Tensor] = None, seed: Optional[int] = 0):
+        self.full_args = full_args
+        self.tp = tp
+        super().__init__(local_args(full_args, tp.size), device=device, dtype=dtype, value_head=value_head,
+                         flat_buffer=flat_buffer, seed=None)
+        if seed is not None:
+            self.load_from_full(CausalLM(full_args, device="cpu", dtype=torch.float32, value_head=value_head, seed=seed))
+
+    @torch.no_grad()
+    def load_from_full(self, full: CausalLM) -> None:
+        for name, prm in self.named_flat_views():
+            prm.copy_(shard_param(name, full.p(name).detach(), self.full_args, self.tp.size, self.tp.rank).to(prm.dtype))
+
+    @torch.no_grad()
+    def gather_full_state(self) -> Dict[str, torch.Tensor]:
+        """Unsharded parameters on every rank (all-gather of the shards), keyed like the unsharded model."""
+        out = {}
+        for name, prm in self.named_flat_views():
+            leaf = name.split(".")[-1]
+            if leaf in REPLICATED_LEAVES or self.tp.size == 1:
+                out[name] = prm.detach()
+                continue
+            parts = [torch.empty_like(prm) for _ in range(self.tp.size)]
+            dist.all_gather(parts, prm.detach().contiguous(), group=self.tp.group)
+            out[name] = unshard_param(name, parts, self.full_args)
+        return out
+
+    def reduce_replicated_grads(self) -> None:
+        """Sum over the TP group of the gradients of replicated parameters (each rank saw different tokens)."""
+        if self.tp.size == 1:
+            return
+        for name, prm in self.named_flat_views():
+            if name.split(".")[-1] in REPLICATED_LEAVES:
+                g = getattr(prm, "main_grad", None)
+                if g is None:
+                    g = prm.grad
+                if g is not None:
+                    dist.all_reduce(g, group=self.tp.group)
+
+    # ------------------------------------------------------------------ forward
+    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None):
+        a, tp = self.args, self.tp
+        pre = f"layers.{i}."
+        x, h = ew.add_rmsnorm(x, delta, self.p(pre + "ln1"), a.rms_norm_eps)  # [T/tp, H]
+        qkv = tpm.column_parallel_linear(h, self.p(pre + "wqkv"), self._p.get(pre + "bqkv"), tp)  # [T, local heads]
+        if a.qk_norm:
+            qkv = self._qk_norm(qkv, i)
+        qkv = ew.rope(qkv, pos, self.rope_table(qkv.device), a.num_heads + a.num_kv_heads, a.head_dim)
+        att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen)
+        o = tpm.row_parallel_linear(att, self.p(pre + "wo"), tp)  # [T/tp, H]
+        x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
+        gu = tpm.column_parallel_linear(h, self.p(pre + "wgu"), None, tp)  # [T, 2F/tp]
+        d = tpm.row_parallel_linear(ew.swiglu(gu), self.p(pre + "wd"), tp)
+        return x, d
+
+    def forward(self, input_ids, positions, cu_seqlens, max_seqlen: int = 0, kv_sink=None) -> torch.Tensor:
+        """Inputs are the full packed batch (identical on every rank of the TP group, padded with
+        ``pad_packed_for_tp``); returns this rank's rows ``[T/tp, H]`` of the final hidden states."""
+        tp = self.tp
+        T = input_ids.numel()
+        if T % (tp.size * 128) != 0 and tp.fused:
+            raise ValueError(f"packed length {T} must be a multiple of tp*128 = {tp.size * 128}")
+        R = T // tp.size
+        x = _EmbeddingFn.apply(input_ids[tp.rank * R : (tp.rank + 1) * R], self.p("embed"))
+        delta = None
+        for i in range(self.args.num_layers):
+            x, delta = self._layer(i, x, delta, positions, cu_seqlens, max_seqlen)
+        _, h = ew.add_rmsnorm(x, delta, self.p("final_norm"), self.args.rms_norm_eps)
+        return h
+
+    def token_logprobs_full(self, hidden_shard: torch.Tensor, targets_full: torch.Tensor, temperature: float = 1.0,
+                            with_entropy: bool = False):
+        """Log-probs of all ``T`` targets on every rank: each rank scores its own rows, then the rows are gathered."""
+        tp = self.tp
+        R = hidden_shard.shape[0]
+        lp, ent = self.token_logprobs(hidden_shard, targets_full[tp.rank * R : (tp.rank + 1) * R], temperature, with_entropy)
+        lp = _GatherRowsFn.apply(lp, tp.group)
+        if ent is not None:
+            ent = _GatherRowsFn.apply(ent, tp.group)
+        return lp, ent

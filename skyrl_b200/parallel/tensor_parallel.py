@@ -120,7 +120,19 @@ def gemm_reduce_scatter(tp: TPGroup, x: torch.Tensor, w: torch.Tensor, slots: Sy
 
 
 def reduce_slots(slots: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """Sum over the leading (source-rank) dimension in fp32."""
+    """Sum over the leading (source-rank) dimension in fp32 (one kernel on CUDA)."""
+    n = slots[0].numel()
+    if slots.is_cuda and out_dtype == torch.bfloat16 and n % 8 == 0 and slots.stride(0) % 8 == 0 and slots[0].is_contiguous():
+        lib = _lib.kernels()
+        f = lib.sb_reduce_slots
+        if not getattr(f, "_configured", False):
+            f.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p,
+                          ctypes.c_longlong, ctypes.c_void_p]
+            f._configured = True
+        out = torch.empty(slots.shape[1:], device=slots.device, dtype=torch.bfloat16)
+        _lib.check(f(slots.data_ptr(), slots.shape[0], slots.stride(0), int(slots.dtype == torch.float32), out.data_ptr(), n,
+                     _lib.stream_ptr()), "sb_reduce_slots")
+        return out
     return slots.float().sum(0).to(out_dtype)
 
 

@@ -62,11 +62,50 @@ def check_sharded_optimizer(env):
         assert rel(p, ref.detach()) < 1e-5, (step, rel(p, ref.detach()))
 
 
+def check_tp_model(env):
+    """Sharded model == unsharded model: hidden states, log-probs, and gradients of sharded + replicated params."""
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+    from skyrl_b200.models.tp_decoder import TPCausalLM, pad_packed_for_tp, shard_param
+    import dataclasses
+
+    W, r = env.world_size, env.rank
+    a = dataclasses.replace(PRESETS["tiny-llama"], num_kv_heads=2, num_heads=4)
+    tp = tpm.TPGroup(None)
+    full = CausalLM(a, device="cpu", dtype=torch.float32, seed=3)
+    m = TPCausalLM(a, tp, device="cpu", dtype=torch.float32, seed=3)
+    lens = [37, 50, 20]
+    ids = torch.randint(4, a.vocab_size, (sum(lens),), generator=torch.Generator().manual_seed(1)).int()
+    pos = torch.cat([torch.arange(n) for n in lens]).int()
+    cu = torch.tensor([0, 37, 87, 107]).int()
+    ids_p, pos_p, cu_p, T = pad_packed_for_tp(ids, pos, cu, W)
+    assert ids_p.numel() % (W * 128) == 0 and cu_p[-1] == ids_p.numel()
+    tgt = torch.roll(ids_p.long(), -1)
+    h = m(ids_p, pos_p, cu_p, 128)
+    lp, _ = m.token_logprobs_full(h, tgt)
+    wts = torch.zeros(ids_p.numel())
+    wts[:T] = torch.linspace(0.5, 1.5, T)
+    (lp * wts).sum().backward()
+    m.reduce_replicated_grads()
+    hf = full(ids_p, pos_p, cu_p, 128)
+    lpf, _ = full.token_logprobs(hf, tgt)
+    (lpf * wts).sum().backward()
+    R = ids_p.numel() // W
+    assert rel(h, hf[r * R : (r + 1) * R]) < 1e-4, rel(h, hf[r * R : (r + 1) * R])
+    assert rel(lp[:T], lpf[:T]) < 1e-4
+    for name, prm in m.named_flat_views():
+        want = shard_param(name, full.p(name).grad, a, W, r)
+        assert rel(prm.grad, want) < 2e-3, (name, rel(prm.grad, want))
+    st = m.gather_full_state()
+    for name, _ in full.named_flat_views():
+        assert torch.equal(st[name], full.p(name).detach()), name
+
+
 def main():
     env = pdist.init_distributed()
     assert env.world_size == 2 and env.device.type == "cpu"
     check_tp(env)
     check_sharded_optimizer(env)
+    check_tp_model(env)
     dist.barrier()
     if env.rank == 0:
         print("CPU_CHECKS_OK", flush=True)

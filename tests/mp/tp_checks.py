@@ -55,6 +55,39 @@ def main():
     assert rel(w1s.grad.cpu(), dw1_ref[r * Fs : (r + 1) * Fs]) < 3e-2
     assert rel(w2s.grad.cpu(), dw2_ref[:, r * Fs : (r + 1) * Fs]) < 3e-2
 
+    # ---- whole model: sharded bf16 model on the fused kernels vs the unsharded bf16 model
+    import dataclasses
+
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+    from skyrl_b200.models.tp_decoder import TPCausalLM, pad_packed_for_tp, shard_param
+
+    a = dataclasses.replace(PRESETS["tiny-qwen2-d128"], num_heads=4, num_kv_heads=2, hidden_size=512, intermediate_size=1024)
+    fullm = CausalLM(a, device=dev, dtype=torch.bfloat16, seed=3)
+    m = TPCausalLM(a, tp, device=dev, dtype=torch.bfloat16, seed=3)
+    lens = [137, 250, 90]
+    ids = torch.randint(4, a.vocab_size, (sum(lens),), generator=torch.Generator().manual_seed(1)).int().to(dev)
+    pos = torch.cat([torch.arange(n) for n in lens]).int().to(dev)
+    cu = torch.tensor([0, 137, 387, 477]).int().to(dev)
+    ids_p, pos_p, cu_p, Tr = pad_packed_for_tp(ids, pos, cu, W)
+    tgt = torch.roll(ids_p.long(), -1)
+    hs = m(ids_p, pos_p, cu_p, 512)
+    lp, _ = m.token_logprobs_full(hs, tgt)
+    wts = torch.zeros(ids_p.numel(), device=dev)
+    wts[:Tr] = 1.0
+    (lp.float() * wts).sum().backward()
+    m.reduce_replicated_grads()
+    hf = fullm(ids_p, pos_p, cu_p, 512)
+    lpf, _ = fullm.token_logprobs(hf, tgt)
+    (lpf.float() * wts).sum().backward()
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    Rm = ids_p.numel() // W
+    assert rel(hs, hf[r * Rm : (r + 1) * Rm]) < 3e-2, rel(hs, hf[r * Rm : (r + 1) * Rm])
+    assert (lp[:Tr].float() - lpf[:Tr].float()).abs().max() < 0.1
+    for name, prm in m.named_flat_views():
+        want = shard_param(name, fullm.p(name).grad, a, W, r)
+        assert rel(prm.grad, want) < 8e-2, (name, rel(prm.grad, want))
+
     # ---- timing: fused all-gather GEMM and GEMM reduce-scatter against NCCL + plain GEMM (device time, max over ranks)
     from skyrl_b200.ops import gemm
 
