@@ -112,6 +112,9 @@ PRESETS: Dict[str, ModelArgs] = {
     "tiny-qwen2-d128": ModelArgs(vocab_size=2048, hidden_size=256, num_layers=2, num_heads=2, num_kv_heads=1,
                                  head_dim=128, intermediate_size=512, rope_theta=1e4, attention_bias=True,
                                  tie_word_embeddings=True, model_type="qwen2"),
+    "tiny-qwen2-tp": ModelArgs(vocab_size=2048, hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
+                               intermediate_size=1024, rope_theta=1e4, attention_bias=True, tie_word_embeddings=True,
+                               model_type="qwen2"),
     "qwen2.5-0.5b": ModelArgs(vocab_size=151936, hidden_size=896, num_layers=24, num_heads=14, num_kv_heads=2,
                               head_dim=64, intermediate_size=4864, rope_theta=1e6, attention_bias=True,
                               tie_word_embeddings=True, model_type="qwen2"),

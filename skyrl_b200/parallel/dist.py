@@ -58,6 +58,46 @@ def init_distributed(backend: Optional[str] = None, timeout_s: Optional[int] = N
     return _ENV
 
 
+@dataclass
+class ParallelMesh:
+    """(dp, tp) factorisation of the world: tensor-parallel groups are runs of ``tp`` consecutive ranks (they share
+    NVLink peers), data-parallel groups take every ``tp``-th rank."""
+
+    tp_size: int = 1
+    dp_size: int = 1
+    tp_rank: int = 0
+    dp_rank: int = 0
+    tp_group: Optional[object] = None
+    dp_group: Optional[object] = None
+
+
+_MESHES: dict = {}
+
+
+def build_mesh(tp: int, env: Optional[DistEnv] = None) -> ParallelMesh:
+    """Create (once per ``tp``) the process groups of a ``dp x tp`` mesh. Collective: every rank must call it."""
+    env = env or get_env()
+    if tp in _MESHES:
+        return _MESHES[tp]
+    W, r = env.world_size, env.rank
+    if tp < 1 or W % tp != 0:
+        raise ValueError(f"tensor parallel size {tp} does not divide the world size {W}")
+    mesh = ParallelMesh(tp, W // tp, r % tp, r // tp)
+    if W > 1 and dist.is_initialized():
+        for g in range(W // tp):  # every rank creates every group, in the same order
+            ranks = list(range(g * tp, (g + 1) * tp))
+            grp = dist.new_group(ranks)
+            if r in ranks:
+                mesh.tp_group = grp
+        for t in range(tp):
+            ranks = list(range(t, W, tp))
+            grp = dist.new_group(ranks)
+            if r in ranks:
+                mesh.dp_group = grp
+    _MESHES[tp] = mesh
+    return mesh
+
+
 def get_env() -> DistEnv:
     return _ENV if _ENV is not None else init_distributed()
 
@@ -94,3 +134,4 @@ def shutdown() -> None:
     if dist.is_initialized():
         dist.destroy_process_group()
     _ENV = None
+    _MESHES.clear()

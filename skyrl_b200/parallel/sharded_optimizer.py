@@ -39,8 +39,13 @@ class ShardedAdamW:
     def __init__(self, flat_params: torch.Tensor, flat_grads: torch.Tensor, lr: float = 1e-6, betas=(0.9, 0.999),
                  eps: float = 1e-8, weight_decay: float = 0.01, max_grad_norm: float = 1.0,
                  group: Optional[dist.ProcessGroup] = None, transport: str = "auto", peer_ctx=None,
-                 numel: Optional[int] = None, params_symm=None, grads_symm=None):
+                 numel: Optional[int] = None, params_symm=None, grads_symm=None, norm_group=None,
+                 dup_ranges=None, count_dups: bool = True):
+        """``norm_group`` / ``dup_ranges`` / ``count_dups`` serve tensor parallelism: the gradient norm is also summed
+        over ``norm_group`` (the TP group), and the flat-buffer ranges listed in ``dup_ranges`` (parameters replicated
+        across that group) enter the norm on one rank only (``count_dups``)."""
         self.group = group
+        self.norm_group, self.dup_ranges, self.count_dups = norm_group, list(dup_ranges or []), count_dups
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.params = flat_params
@@ -92,8 +97,21 @@ class ShardedAdamW:
             g = self._grad_shard
         self._sq.zero_()
         optim_ops.sqnorm_accum(g, self._sq)
+        if self.dup_ranges and not self.count_dups:
+            dup = torch.zeros_like(self._sq)
+            for a, b in self.dup_ranges:  # intersect with this rank's optimizer shard
+                a2, b2 = max(a, self.lo) - self.lo, min(b, self.lo + self.shard) - self.lo
+                if b2 > a2:
+                    a4 = (a2 + 3) // 4 * 4  # the norm kernel reads 16-byte vectors
+                    if a4 > a2:
+                        dup += g[a2 : min(a4, b2)].float().pow(2).sum()
+                    if b2 > a4:
+                        optim_ops.sqnorm_accum(g[a4:b2], dup)
+            self._sq -= dup
         if self.world > 1:
             dist.all_reduce(self._sq, op=dist.ReduceOp.SUM, group=self.group)
+        if self.norm_group is not None and dist.get_world_size(self.norm_group) > 1:
+            dist.all_reduce(self._sq, op=dist.ReduceOp.SUM, group=self.norm_group)
         optim_ops.clip_coef(self._sq, self.max_grad_norm, grad_scale, self._coef, self._skip, self._norm)
         shard_params = self.params[self.lo : self.lo + self.shard]
         optim_ops.adamw_flat(self.master, self.exp_avg, self.exp_avg_sq, g, shard_params, self.lr, b1, b2, self.eps,

@@ -43,10 +43,14 @@ def _k():
 class TPGroup:
     """Ranks of one tensor-parallel group plus their symmetric work buffers."""
 
-    def __init__(self, peer_ctx: Optional[PeerContext] = None, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, peer_ctx: Optional[PeerContext] = None, group: Optional[dist.ProcessGroup] = None,
+                 size: Optional[int] = None):
         self.group = group
-        self.size = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if size == 1:  # a trivial group inside a larger world
+            self.size, self.rank = 1, 0
+        else:
+            self.size = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.peer = peer_ctx
         self._gather_bufs = {}
         self._slot_bufs = {}

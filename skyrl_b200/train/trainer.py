@@ -87,7 +87,10 @@ class PPOTrainer:
             self.critic = CriticWorker(t, model_path=t.critic.model.path or t.policy.model.path, env=self.env,
                                        seed=t.seed + 1)
         if self.inference_engine_client is None:
-            self.engine = self._build_engine(self.policy.model)
+            engine_model = self.policy.model
+            if self.policy.tp_size > 1:  # the engine runs the unsharded model; weights are re-gathered after each update
+                engine_model = self._engine_model = self.policy.full_model_copy()
+            self.engine = self._build_engine(engine_model)
             self.inference_engine_client = LocalInferenceClient([self.engine], self.tokenizer)
         if self.generator is None:
             self.generator = SkyRLGymGenerator(self.cfg.generator, self.cfg.environment.skyrl_gym,
@@ -327,8 +330,27 @@ class PPOTrainer:
     def sync_weights(self) -> None:
         """Make the freshly trained weights visible to the generation engine(s)."""
         c = self.inference_engine_client
+        if self.policy is not None and self.policy.tp_size > 1 and getattr(self, "_engine_model", None) is not None:
+            self.policy.full_model_copy(into=self._engine_model)
         if hasattr(c, "increment_weight_version"):
             c.increment_weight_version()
+
+    def _gather_over_tp(self, out: GeneratorOutput, uids: List[str]):
+        """Every rank generated for its own prompts; ranks of one tensor-parallel group train on the same data, so
+        they exchange their rollouts and continue with the concatenation (in rank order, identical on each)."""
+        import torch.distributed as tdist
+
+        mesh = self.policy.mesh
+        parts: List[Any] = [None] * mesh.tp_size
+        tdist.all_gather_object(parts, (out, uids), group=mesh.tp_group)
+        merged: Dict[str, Any] = {}
+        for key in parts[0][0]:
+            vals = [p[0].get(key) for p in parts]
+            if all(isinstance(v, list) for v in vals):
+                merged[key] = [x for v in vals for x in v]
+            else:
+                merged[key] = vals[mesh.tp_rank]
+        return merged, [u for p in parts for u in p[1]]
 
     # ------------------------------------------------------------------ one RL step
     async def train_step_async(self, prompts: List[Dict[str, Any]], prompt_token_ids=None) -> Dict[str, float]:
@@ -339,6 +361,8 @@ class PPOTrainer:
                                                   cfg.environment.env_class, "train", self.global_step, prompt_token_ids)
         with Timer("generate", self.all_timings):
             out = await self.generate(gen_input)
+        if self.policy is not None and self.policy.tp_size > 1:
+            out, uids = self._gather_over_tp(out, uids)
         if out.get("trajectory_ids") and len(out["response_ids"]) != len(uids):
             uids = [t.instance_id for t in out["trajectory_ids"]]  # step-wise outputs have one row per step
         with Timer("postprocess", self.all_timings):

@@ -120,6 +120,27 @@ class ModelWorker:
         dev = self.env.device
         dtype = torch.bfloat16 if (cfg.bf16 and dev.type == "cuda") else torch.float32
         self.params_symm = self.grads_symm = None
+        self.mesh = None
+        tp_size = self._tp_size_from_cfg(cfg)
+        if tp_size > 1 and model is None:
+            # Megatron-style strategy: tensor-parallel shards inside groups of consecutive ranks, data parallel across
+            from ..models.decoder import resolve_model_args
+            from ..models.tp_decoder import TPCausalLM
+            from ..parallel.dist import build_mesh
+            from ..parallel.peer import PeerContext
+            from ..parallel.tensor_parallel import TPGroup
+
+            if value_head:
+                raise NotImplementedError("the critic runs data-parallel only; set tensor_model_parallel_size=1 for it")
+            self.mesh = build_mesh(tp_size, self.env)
+            tp_peer = PeerContext(dev, group=self.mesh.tp_group) if dev.type == "cuda" else None
+            self.tp = TPGroup(tp_peer, self.mesh.tp_group)
+            margs = resolve_model_args(model_path)
+            model = TPCausalLM(margs, self.tp, device=dev, dtype=dtype, seed=None)
+            full = build_model(model_path, device="cpu", dtype=torch.float32, seed=seed)
+            model.load_from_full(full)
+            del full
+            peer_ctx = None  # the flat-buffer peer optimizer spans the whole world; TP uses the DP group over NCCL
         use_peer = peer_ctx is not None and trainable and self.env.world_size > 1 and dev.type == "cuda"
         if model is None:
             if use_peer:
@@ -145,9 +166,17 @@ class ModelWorker:
                 flat_grad = torch.zeros(model.flat_params.numel(), device=dev, dtype=torch.float32)
             model.attach_main_grad(flat_grad)
             self.flat_grad = flat_grad
+            extra = {}
+            if self.mesh is not None:
+                from ..models.tp_decoder import REPLICATED_LEAVES
+
+                dups = [(o, o + n) for name, (o, n) in model.offsets.items() if name.split(".")[-1] in REPLICATED_LEAVES]
+                extra = dict(group=self.mesh.dp_group, transport="nccl", norm_group=self.mesh.tp_group, dup_ranges=dups,
+                             count_dups=self.mesh.tp_rank == 0)
             self.optimizer = ShardedAdamW(model.flat_params, flat_grad, lr=ocfg.lr, betas=tuple(ocfg.adam_betas),
                                           weight_decay=ocfg.weight_decay, max_grad_norm=ocfg.max_grad_norm,
-                                          peer_ctx=peer_ctx, params_symm=self.params_symm, grads_symm=self.grads_symm)
+                                          peer_ctx=peer_ctx, params_symm=self.params_symm, grads_symm=self.grads_symm,
+                                          **extra)
             self.scheduler = get_scheduler(ocfg.scheduler, self.optimizer, ocfg.num_warmup_steps, base_lr=ocfg.lr)
 
     # ------------------------------------------------------------------ helpers
@@ -170,6 +199,40 @@ class ModelWorker:
     def _hidden(self, pv: PackedView) -> torch.Tensor:
         return self.model(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen)
 
+    @staticmethod
+    def _tp_size_from_cfg(cfg) -> int:
+        if getattr(cfg, "strategy", "fsdp") != "megatron":
+            return 1
+        return int(getattr(cfg.policy.megatron_config, "tensor_model_parallel_size", 1) or 1)
+
+    def full_model_copy(self, into: Optional[CausalLM] = None) -> CausalLM:
+        """Unsharded copy of a tensor-parallel model (collective over the TP group); ``into`` is updated in place."""
+        state = self.model.gather_full_state()
+        if into is None:
+            into = CausalLM(self.model.full_args, device=self.env.device, dtype=self.model.flat_params.dtype, seed=None)
+        with torch.no_grad():
+            for name, prm in into.named_flat_views():
+                prm.copy_(state[name])
+        return into
+
+    @property
+    def tp_size(self) -> int:
+        return self.mesh.tp_size if self.mesh is not None else 1
+
+    def _pred_logprobs(self, pv: PackedView, temp: float, with_entropy: bool = False):
+        """Log-probs (and entropies) of the packed batch's prediction positions, ``[n_pred]`` each."""
+        if self.mesh is None:
+            h = self._hidden(pv)
+            return self.model.token_logprobs(h[pv.pred_index], pv.targets, temp, with_entropy=with_entropy)
+        from ..models.tp_decoder import pad_packed_for_tp
+
+        ids, pos, cu, T = pad_packed_for_tp(pv.ids, pv.positions, pv.cu_seqlens, self.mesh.tp_size)
+        h = self.model(ids, pos, cu, max(pv.max_seqlen, ids.numel() - T))
+        tgt = torch.zeros(ids.numel(), dtype=pv.targets.dtype, device=ids.device)
+        tgt[pv.pred_index] = pv.targets
+        lp, ent = self.model.token_logprobs_full(h, tgt, temp, with_entropy=with_entropy)
+        return lp[pv.pred_index], (ent[pv.pred_index] if ent is not None else None)
+
     # ------------------------------------------------------------------ forward (no grad)
     @torch.no_grad()
     def forward(self, batch: TrainingInputBatch) -> TrainingOutputBatch:
@@ -185,11 +248,16 @@ class ModelWorker:
         for k in range(n_mb):
             rows = groups[k] if k < len(groups) else groups[-1]  # padding micro-batch keeps collectives aligned
             pv = self._pack(batch, rows)
-            h = self._hidden(pv)
-            if pv.pred_index.numel() == 0:
-                continue
-            hs = h[pv.pred_index]
-            vals = self.model.values(hs) if self.role == "critic" else self.model.token_logprobs(hs, pv.targets, temp)[0]
+            if self.role == "critic":
+                h = self._hidden(pv)
+                if pv.pred_index.numel() == 0:
+                    continue
+                vals = self.model.values(h[pv.pred_index])
+            else:
+                if pv.pred_index.numel() == 0 and self.mesh is None:
+                    self._hidden(pv)
+                    continue
+                vals = self._pred_logprobs(pv, temp)[0]
             if k < len(groups):
                 grid = _lib.to_host(pv.scatter_to_grid(vals.float()))
                 out[torch.tensor(rows, dtype=torch.long)] = grid
@@ -232,6 +300,8 @@ class ModelWorker:
         scale = 1.0
         if self.role == "critic" and self.num_microbatches_accumulated > 0:
             scale = 1.0 / self.num_microbatches_accumulated  # reference: worker.py:1513-1537
+        if self.mesh is not None:
+            self.model.reduce_replicated_grads()
         norm = self.optimizer.step(grad_scale=scale)
         self.scheduler.step()
         self.optimizer.zero_grad()
@@ -254,10 +324,15 @@ class ModelWorker:
         os.makedirs(ckpt_dir, exist_ok=True)
         W, r = self.env.world_size, self.env.rank
         n = self.model.flat_params.numel()
-        shard = n // W
-        lo = r * shard
+        # with tensor parallelism each TP rank owns a different buffer, sliced over its data-parallel peers
+        dp = self.mesh.dp_size if self.mesh is not None else W
+        dpr = self.mesh.dp_rank if self.mesh is not None else r
+        shard = n // dp
+        lo = dpr * shard
         torch.save({"flat_shard": self.model.flat_params[lo : lo + shard].cpu(), "offset": lo, "numel": n,
-                    "specs": self.model.specs}, os.path.join(ckpt_dir, f"model_world_size_{W}_rank_{r}.pt"))
+                    "specs": self.model.specs, "tp_size": self.tp_size,
+                    "tp_rank": self.mesh.tp_rank if self.mesh is not None else 0},
+                   os.path.join(ckpt_dir, f"model_world_size_{W}_rank_{r}.pt"))
         if self.optimizer is not None:
             sd = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in self.optimizer.state_dict().items()}
             torch.save(sd, os.path.join(ckpt_dir, f"optim_world_size_{W}_rank_{r}.pt"))
@@ -274,7 +349,7 @@ class ModelWorker:
             with open(os.path.join(hf_dir, "config.json"), "w") as f:
                 json.dump(self.model.args.to_hf_config(), f, indent=1)
             with open(os.path.join(ckpt_dir, "fsdp_config.json"), "w") as f:
-                json.dump({"FSDP_version": 2, "world_size": W, "layout": "flat_zero"}, f)
+                json.dump({"FSDP_version": 2, "world_size": W, "layout": "flat_zero", "tensor_parallel_size": self.tp_size}, f)
         if dist.is_initialized():
             dist.barrier()
 
@@ -285,8 +360,9 @@ class ModelWorker:
             have = sorted(f for f in os.listdir(ckpt_dir) if f.startswith("model_world_size_"))
             raise FileNotFoundError(f"{path} not found (checkpoint was written for a different world size? found: {have})")
         n = self.model.flat_params.numel()
-        # every rank needs the full parameter buffer: read all ranks' slices
-        for rr in range(W):
+        # every rank needs its full parameter buffer: read the slices of all ranks that share it
+        tp = self.tp_size
+        for rr in (range(W) if self.mesh is None else range(self.mesh.tp_rank, W, tp)):
             d = torch.load(os.path.join(ckpt_dir, f"model_world_size_{W}_rank_{rr}.pt"), weights_only=False)
             assert d["numel"] == n, "checkpoint parameter layout differs from the model"
             self.model.flat_params[d["offset"] : d["offset"] + d["flat_shard"].numel()].copy_(d["flat_shard"])
@@ -308,8 +384,11 @@ class ModelWorker:
     def save_hf_model(self, export_dir: str, tokenizer=None) -> None:
         from ..models import hf_io
 
+        model = self.model
+        if self.mesh is not None:  # gather the TP shards into an unsharded model for the export
+            model = self.full_model_copy()
         if self.env.rank == 0:
-            hf_io.save_hf_model(self.model, export_dir, tokenizer)
+            hf_io.save_hf_model(model, export_dir, tokenizer)
         if dist.is_initialized():
             dist.barrier()
 
@@ -350,7 +429,7 @@ class PolicyWorker(ModelWorker):
         B, R = batch["response_mask"].shape
         groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens())
         n_mb = sync_num_microbatches(len(groups), self.env)
-        world = self.env.world_size
+        world = self.mesh.dp_size if self.mesh is not None else self.env.world_size  # number of distinct data shards
         temp = float(algo.temperature or 1.0)
         use_kl = bool(algo.use_kl_loss) and batch.get("base_action_log_probs") is not None and loss_name != "cross_entropy"
         use_ent = bool(algo.use_entropy_loss) and loss_name != "cross_entropy"
@@ -362,9 +441,7 @@ class PolicyWorker(ModelWorker):
             real = k < len(groups)
             rows = groups[k] if real else groups[-1]
             pv = self._pack(batch, rows)
-            h = self._hidden(pv)
-            hs = h[pv.pred_index]
-            lp, ent = self.model.token_logprobs(hs, pv.targets, temp, with_entropy=use_ent)
+            lp, ent = self._pred_logprobs(pv, temp, with_entropy=use_ent)
             weight = len(rows) / max(1, B * world)  # KL / entropy terms: mean over the global mini-batch
             g = lambda key: self._rows_to_device(batch.get(key), rows)  # noqa: E731
             mask_g, adv_g = g("loss_mask"), g("advantages")

@@ -34,3 +34,10 @@ def test_bench_two_gpus_tiny():
 def test_tensor_parallel_fused_gemm_collectives():
     p = _run([os.path.join(ROOT, "tests", "mp", "tp_checks.py")], port=29619)
     assert p.returncode == 0 and "TP_CHECKS" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_bench_two_gpus_tensor_parallel_tiny():
+    p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-tp",
+              "--prompts-per-gpu", "4", "--tp", "2"], port=29620)
+    assert p.returncode == 0 and "x tp2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]

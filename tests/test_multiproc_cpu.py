@@ -22,3 +22,9 @@ def test_gloo_two_rank_rl_step():
     p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-d128",
               "--prompts-per-gpu", "1"], port=29632)
     assert p.returncode == 0 and '"n_gpus": 2' in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_gloo_two_rank_tensor_parallel_rl_step():
+    p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-llama",
+              "--prompts-per-gpu", "1", "--tp", "2"], port=29633)
+    assert p.returncode == 0 and "x tp2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
