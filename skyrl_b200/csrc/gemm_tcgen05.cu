@@ -57,6 +57,16 @@ struct TpArgs {
   int n_ranks, my_rank;
   int rows_per_rank;             // rows of the full matrix owned by each rank (A rows for GATHER, C rows for SCATTER)
   int scatter_all;               // SCATTER: 0 = rows go to their owner only, 1 = every rank receives every row
+  // Sequence-parallel attention (all-to-all fused into the projections around it):
+  //  scatter_cols: the output columns are up to three segments (q | k | v heads), each split evenly over the
+  //    ranks; a column chunk goes to the rank that owns its heads, at row my_rank * rows_per_rank + row of that
+  //    rank's [n_ranks * rows_per_rank, local width] buffer (sequence-sharded -> head-sharded).
+  //  gather_cols: the A operand's rows are local, its columns are blocks of cols_per_rank owned by the ranks
+  //    (head-sharded -> sequence-sharded): rank r's block comes from src[r] rows [my_rank * M, ...).
+  int scatter_cols, gather_cols;
+  int seg_start[3], seg_w[3];    // scatter_cols: first column and per-rank width of each segment (0 width = unused)
+  int cols_per_rank;             // gather_cols
+  long long src_ld;              // gather_cols: row stride of the source buffers
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
@@ -104,7 +114,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int k_blocks = (K + kBK - 1) / kBK;
   const int kpb = (k_blocks + splits - 1) / splits;  // k blocks per slice (host guarantees no empty slice)
   // GATHER: logical m-block 0 is the first block of the local shard, then the next rank's, and so on
-  const int m_rot = GATHER ? tp.my_rank * (tp.rows_per_rank / kBM) : 0;
+  const int m_rot = (GATHER && !tp.gather_cols) ? tp.my_rank * (tp.rows_per_rank / kBM) : 0;
   auto rot = [&](int pm) { return GATHER ? (pm + m_rot) % tm.m_blocks : pm; };
 
   if (threadIdx.x == 0) {
@@ -142,10 +152,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         pm = rot(pm);
         if (GATHER) {
           // rows of another rank: wait until the copy warps have landed every piece of this m-block
-          const int owner = (pm * kBM) / tp.rows_per_rank;
+          const int owner = tp.gather_cols ? -1 : (pm * kBM) / tp.rows_per_rank;
+          const unsigned int need = tp.gather_cols ? kPiecesPerBlock * tp.n_ranks : kPiecesPerBlock;
           if (owner != tp.my_rank && !((ready_mask >> (pm & 63)) & 1ull)) {
             const unsigned long long t0 = globaltimer_ns();
-            while (ld_acquire_gpu(tp.flags + pm) < static_cast<unsigned int>(kPiecesPerBlock)) {
+            while (ld_acquire_gpu(tp.flags + pm) < need) {
               if (*reinterpret_cast<volatile int*>(status) != 0 || globaltimer_ns() - t0 > kWaitTimeoutNs) {
                 atomicCAS(status, 0, 0x104);
                 ok = false;
@@ -299,6 +310,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           };
           if (!SCATTER) {
             store_chunk(C, ks * split_stride + static_cast<long long>(row) * ldc + col0);
+          } else if (tp.scatter_cols) {
+            int sg = 0, base = 0;
+            if (tp.seg_w[1] > 0 && col0 >= tp.seg_start[1]) { sg = 1; base = tp.seg_w[0]; }
+            if (tp.seg_w[2] > 0 && col0 >= tp.seg_start[2]) { sg = 2; base = tp.seg_w[0] + tp.seg_w[1]; }
+            const int rel = col0 - tp.seg_start[sg];
+            const int dest = rel / tp.seg_w[sg];
+            store_chunk(tp.dst[dest], static_cast<long long>(tp.my_rank * tp.rows_per_rank + row) * ldc + base +
+                                          (rel - dest * tp.seg_w[sg]));
           } else if (tp.scatter_all) {
             // all-reduce layout: every rank receives this rank's partial rows in slot my_rank
             const long long off = tp.my_rank * tp.slot_stride + static_cast<long long>(row) * ldc + col0;
@@ -319,9 +338,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (GATHER) {
     // ------------------------------ copy warps (remote A shards -> local full buffer) ---------------
     // Work is handed out by a ticket counter so that whichever CTAs are resident finish every piece.
-    const int bpr = tp.rows_per_rank / kBM;               // m-blocks per rank
-    const int total = (tp.n_ranks - 1) * bpr * kPiecesPerBlock;
-    const int vec_per_row = K >> 3;                        // 16-byte vectors per row
+    const int bpr = tp.gather_cols ? tm.m_blocks : tp.rows_per_rank / kBM;  // m-blocks per source rank
+    const int total = (tp.gather_cols ? tp.n_ranks : tp.n_ranks - 1) * bpr * kPiecesPerBlock;
+    const int vec_per_row = (tp.gather_cols ? tp.cols_per_rank : K) >> 3;   // 16-byte vectors per copied row
     constexpr int kRowsPerPiece = kBM / kPiecesPerBlock;
     unsigned int* ticket = tp.flags + tm.m_blocks;
     while (true) {
@@ -330,15 +349,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       piece = __shfl_sync(0xffffffffu, piece, 0);
       if (piece >= total) break;
       const int bi = piece / kPiecesPerBlock, sub = piece - bi * kPiecesPerBlock;
-      const int src_rank = (tp.my_rank + 1 + bi / bpr) % tp.n_ranks;
-      const int mb = src_rank * bpr + bi % bpr;
-      const int row0 = mb * kBM + sub * kRowsPerPiece;     // row in the full matrix
-      const uint4* sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(tp.src[src_rank]) +
-                                                        static_cast<long long>(row0 - src_rank * tp.rows_per_rank) * tp.lda);
-      uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tp.a_full) +
-                                           static_cast<long long>(row0) * tp.lda);
-      const int ld_vec = static_cast<int>(tp.lda >> 3);
-      const int n_vec = kRowsPerPiece * vec_per_row;
+      int src_rank, mb, row0, rows_here = kRowsPerPiece;
+      const uint4* sp;
+      uint4* dp;
+      int ld_vec = static_cast<int>(tp.lda >> 3), sld_vec = ld_vec;
+      if (!tp.gather_cols) {
+        src_rank = (tp.my_rank + 1 + bi / bpr) % tp.n_ranks;
+        mb = src_rank * bpr + bi % bpr;
+        row0 = mb * kBM + sub * kRowsPerPiece;  // row in the full matrix
+        sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(tp.src[src_rank]) +
+                                            static_cast<long long>(row0 - src_rank * tp.rows_per_rank) * tp.lda);
+        dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tp.a_full) + static_cast<long long>(row0) * tp.lda);
+      } else {
+        // m-blocks outermost so that the first blocks complete first; within a block, one source rank after another
+        mb = bi / tp.n_ranks;
+        src_rank = (tp.my_rank + bi % tp.n_ranks) % tp.n_ranks;  // the local block is copied the same way
+        row0 = mb * kBM + sub * kRowsPerPiece;  // local row
+        rows_here = max(0, min(kRowsPerPiece, M - row0));
+        sld_vec = static_cast<int>(tp.src_ld >> 3);
+        sp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(tp.src[src_rank]) +
+                                            static_cast<long long>(tp.my_rank * tp.rows_per_rank + row0) * tp.src_ld);
+        dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tp.a_full) + static_cast<long long>(row0) * tp.lda +
+                                      static_cast<long long>(src_rank) * tp.cols_per_rank);
+      }
+      const int n_vec = rows_here * vec_per_row;
       for (int base = 0; base < n_vec; base += 32 * 8) {
         uint4 v[8];
 #pragma unroll
@@ -346,7 +380,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int idx = base + u * 32 + lane;
           if (idx < n_vec) {
             const int rr = idx / vec_per_row, cc = idx - rr * vec_per_row;
-            v[u] = sp[static_cast<long long>(rr) * ld_vec + cc];
+            v[u] = sp[static_cast<long long>(rr) * sld_vec + cc];
           }
         }
 #pragma unroll
@@ -537,6 +571,62 @@ int sb_gemm_tp(const void* A, const void* B, void* C, const void* bias, int M, i
   SB_TP_CASE(128, true, false, true)
   SB_TP_CASE(256, true, false, true)
 #undef SB_TP_CASE
+  return SB_ERR_ARG;
+}
+
+
+// Projections around sequence-parallel attention with the all-to-all inside the GEMM kernel (x @ W^T, W stored [N, K]).
+//   mode 1 (scatter columns): x is this rank's [M = rows_per_rank, K] token shard; output column segments
+//       (seg_start[i], seg_w[i] per rank, i < 3: q | k | v heads) are stored to the rank owning those heads, into its
+//       [n_ranks * rows_per_rank, sum(seg_w)] buffer peers[dest] at rows my_rank * rows_per_rank + row.
+//   mode 2 (gather columns): A is this rank's [M, K = n_ranks * cols_per_rank] buffer; column block r is copied from
+//       peers[r] (rank r's [n_ranks * rows_per_rank, cols_per_rank] attention output, row stride src_ld), rows
+//       my_rank * rows_per_rank + [0, M), while the GEMM runs; C is a plain local output.
+int sb_gemm_sp(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda, long long ldb,
+               long long ldc, int mode, void* const* peers, int n_ranks, int my_rank, int rows_per_rank,
+               const int* seg_start, const int* seg_w, int cols_per_rank, long long src_ld, unsigned int* flags, int bn,
+               void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (K & 7) || !peers) return SB_ERR_ARG;
+  if (n_ranks < 1 || n_ranks > sb::kTpMaxRanks || my_rank < 0 || my_rank >= n_ranks || M > rows_per_rank) return SB_ERR_ARG;
+  sb::TpArgs tp{};
+  tp.n_ranks = n_ranks;
+  tp.my_rank = my_rank;
+  tp.rows_per_rank = rows_per_rank;
+  tp.lda = lda;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn != 128 && bn != 256) bn = 128;
+  if (mode == 1) {
+    if (!seg_start || !seg_w) return SB_ERR_ARG;
+    int covered = 0;
+    for (int i = 0; i < 3; ++i) {
+      tp.seg_start[i] = seg_start[i];
+      tp.seg_w[i] = seg_w[i];
+      if (seg_w[i] < 0 || (seg_w[i] & 31) || (seg_start[i] & 31)) return SB_ERR_ARG;  // chunks of 32 columns stay whole
+      covered += seg_w[i] * n_ranks;
+    }
+    if (covered != N || seg_w[0] == 0) return SB_ERR_ARG;
+    tp.scatter_cols = 1;
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!peers[r]) return SB_ERR_ARG;
+      tp.dst[r] = peers[r];
+    }
+    if (bn == 256) return sb::launch_gemm_tp<256, false, false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, tp, st);
+    return sb::launch_gemm_tp<128, false, false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, tp, st);
+  }
+  if (mode == 2) {
+    if (!flags || cols_per_rank <= 0 || (cols_per_rank & 7) || K != n_ranks * cols_per_rank || (src_ld & 7)) return SB_ERR_ARG;
+    tp.gather_cols = 1;
+    tp.cols_per_rank = cols_per_rank;
+    tp.src_ld = src_ld;
+    tp.a_full = const_cast<void*>(A);
+    tp.flags = flags;
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!peers[r] || (reinterpret_cast<uintptr_t>(peers[r]) & 15)) return SB_ERR_ARG;
+      tp.src[r] = peers[r];
+    }
+    if (bn == 256) return sb::launch_gemm_tp<256, false, true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, tp, st);
+    return sb::launch_gemm_tp<128, false, true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, tp, st);
+  }
   return SB_ERR_ARG;
 }
 

@@ -198,3 +198,57 @@ class TPCausalLM(CausalLM):
         if ent is not None:
             ent = _GatherRowsFn.apply(ent, tp.group)
         return lp, ent
+
+
+class UlyssesCausalLM(CausalLM):
+    """Replicated weights, sequence-sharded activations, head-sharded attention (Ulysses sequence parallelism).
+
+    Every rank of the ``sp`` group passes the same packed batch (padded with ``pad_packed_for_tp``); the residual
+    stream, norms, MLP and LM head run on this rank's ``1/sp`` of the tokens with the full weights, attention runs on
+    all tokens with ``1/sp`` of the heads.  Gradients of the (replicated) weights are partial sums over tokens, so the
+    ordinary data-parallel gradient reduction over all ranks completes them.  Reference: HFModelWrapper.forward with
+    ``sequence_parallel_size > 1`` (skyrl/backends/skyrl_train/workers/model_wrapper.py:296-398).
+    """
+
+    def __init__(self, args: ModelArgs, sp: tpm.TPGroup, **kw):
+        if args.num_heads % sp.size or args.num_kv_heads % sp.size:
+            raise ValueError(f"sequence_parallel_size={sp.size} must divide num_heads={args.num_heads} and "
+                             f"num_kv_heads={args.num_kv_heads}")
+        if args.qk_norm or args.num_experts:
+            raise ValueError("Ulysses sequence parallelism supports dense models without per-head q/k norms")
+        self.tp = sp
+        super().__init__(args, **kw)
+
+    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None):
+        from ..parallel import ulysses
+
+        a, sp = self.args, self.tp
+        pre = f"layers.{i}."
+        x, h = ew.add_rmsnorm(x, delta, self.p(pre + "ln1"), a.rms_norm_eps)
+        qkv = ulysses.qkv_proj(h, self.p(pre + "wqkv"), self._p.get(pre + "bqkv"), [a.q_dim, a.kv_dim, a.kv_dim], sp)
+        nq, nkv = a.num_heads // sp.size, a.num_kv_heads // sp.size
+        qkv = ew.rope(qkv, pos, self.rope_table(qkv.device), nq + nkv, a.head_dim)
+        att = attn_ops.attn_varlen(qkv, cu, nq, nkv, a.head_dim, max_seqlen=max_seqlen)
+        o = ulysses.o_proj(att, self.p(pre + "wo"), sp)
+        x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
+        from ..ops import gemm
+
+        gu = gemm.linear(h, self.p(pre + "wgu"))
+        d = gemm.linear(ew.swiglu(gu), self.p(pre + "wd"))
+        return x, d
+
+    def forward(self, input_ids, positions, cu_seqlens, max_seqlen: int = 0, kv_sink=None) -> torch.Tensor:
+        sp = self.tp
+        T = input_ids.numel()
+        R = T // sp.size
+        x = _EmbeddingFn.apply(input_ids[sp.rank * R : (sp.rank + 1) * R], self.p("embed"))
+        delta = None
+        for i in range(self.args.num_layers):
+            x, delta = self._layer(i, x, delta, positions, cu_seqlens, max_seqlen)
+        _, h = ew.add_rmsnorm(x, delta, self.p("final_norm"), self.args.rms_norm_eps)
+        return h
+
+    token_logprobs_full = TPCausalLM.token_logprobs_full
+
+    def reduce_replicated_grads(self) -> None:  # the data-parallel reduction over all ranks already sums them
+        return

@@ -100,12 +100,49 @@ def check_tp_model(env):
         assert torch.equal(st[name], full.p(name).detach()), name
 
 
+def check_ulysses_model(env):
+    """Sequence-parallel model == plain model once the weight gradients are summed over ranks."""
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+    from skyrl_b200.models.tp_decoder import UlyssesCausalLM, pad_packed_for_tp
+    from skyrl_b200.parallel import ulysses
+    import dataclasses
+
+    W, r = env.world_size, env.rank
+    sp = tpm.TPGroup(None)
+    # layout exchange round trip
+    x = torch.arange(3 * 16, dtype=torch.float32).reshape(3, 16) + 100 * r
+    y = ulysses.seq_to_head(x, [8, 4, 4], sp)
+    assert y.shape == (3 * W, 16 // W)
+    assert torch.equal(ulysses.head_to_seq(y, [8, 4, 4], sp), x)
+    a = dataclasses.replace(PRESETS["tiny-llama"], num_kv_heads=2, num_heads=4)
+    full = CausalLM(a, device="cpu", dtype=torch.float32, seed=5)
+    m = UlyssesCausalLM(a, sp, device="cpu", dtype=torch.float32, seed=5)
+    lens = [30, 61]
+    ids = torch.randint(4, a.vocab_size, (sum(lens),), generator=torch.Generator().manual_seed(2)).int()
+    pos = torch.cat([torch.arange(n) for n in lens]).int()
+    cu = torch.tensor([0, 30, 91]).int()
+    ids_p, pos_p, cu_p, T = pad_packed_for_tp(ids, pos, cu, W)
+    tgt = torch.roll(ids_p.long(), -1)
+    wts = torch.zeros(ids_p.numel())
+    wts[:T] = 1.0
+    lp, _ = m.token_logprobs_full(m(ids_p, pos_p, cu_p, 128), tgt)
+    (lp * wts).sum().backward()
+    lpf, _ = full.token_logprobs(full(ids_p, pos_p, cu_p, 128), tgt)
+    (lpf * wts).sum().backward()
+    assert rel(lp[:T], lpf[:T]) < 1e-4, rel(lp[:T], lpf[:T])
+    for name, prm in m.named_flat_views():
+        g = prm.grad.clone()
+        dist.all_reduce(g)
+        assert rel(g, full.p(name).grad) < 2e-3, (name, rel(g, full.p(name).grad))
+
+
 def main():
     env = pdist.init_distributed()
     assert env.world_size == 2 and env.device.type == "cpu"
     check_tp(env)
     check_sharded_optimizer(env)
     check_tp_model(env)
+    check_ulysses_model(env)
     dist.barrier()
     if env.rank == 0:
         print("CPU_CHECKS_OK", flush=True)

@@ -136,3 +136,70 @@ def test_gemm_scatter_mode_slots_sum_to_product(all_ranks):
         want = ref if all_ranks else ref[d * rpr : (d + 1) * rpr]
         assert torch.isfinite(got).all()
         assert ((got - want).norm() / want.norm()).item() < 2e-3
+
+
+def _sp_call(A, B, C, M, N, K, mode, peers, n_ranks, my_rank, rpr, seg_start=None, seg_w=None, cpr=0, src_ld=0, flags=None,
+             ldc=None, bias=None):
+    import ctypes
+
+    from skyrl_b200.ops import _lib
+    from skyrl_b200.parallel import ulysses
+
+    lib = ulysses._k()
+    pa = (ctypes.c_void_p * n_ranks)(*peers)
+    ss = (ctypes.c_int * 3)(*seg_start) if seg_start else None
+    sw = (ctypes.c_int * 3)(*seg_w) if seg_w else None
+    code = lib.sb_gemm_sp(A.data_ptr(), B.data_ptr(), None if C is None else C.data_ptr(),
+                          None if bias is None else bias.data_ptr(), M, N, K, A.stride(0), B.stride(0),
+                          ldc if ldc is not None else N, mode, pa, n_ranks, my_rank, rpr, ss, sw, cpr, src_ld,
+                          None if flags is None else flags.data_ptr(), 0, _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_sp")
+
+
+def test_gemm_column_scatter_matches_all_to_all_layout():
+    """QKV projection whose epilogue performs the sequence-to-head exchange (ranks emulated by local buffers)."""
+    from skyrl_b200.ops import _lib
+
+    torch.manual_seed(2)
+    sp, R, K = 2, 200, 512
+    widths = [512, 256, 256]  # q | k | v
+    N = sum(widths)
+    per = [w // sp for w in widths]
+    local = sum(per)
+    starts = [0, 512, 768]
+    W = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, device="cuda").to(torch.bfloat16)
+    xs = [(torch.randn(R, K, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(sp)]
+    dests = [torch.full((sp * R, local), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(sp)]
+    for me in range(sp):
+        _sp_call(xs[me], W, None, R, N, K, 1, [d.data_ptr() for d in dests], sp, me, R, starts, per, ldc=local, bias=b)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    for d in range(sp):
+        for src in range(sp):
+            full = xs[src].float() @ W.float().t() + b.float()
+            want = torch.cat([full[:, s + d * p : s + (d + 1) * p] for s, p in zip(starts, per)], 1)
+            got = dests[d][src * R : (src + 1) * R].float()
+            assert torch.isfinite(got).all()
+            assert ((got - want).norm() / want.norm()).item() < 1e-2
+
+
+def test_gemm_column_gather_matches_head_to_seq_then_project():
+    from skyrl_b200.ops import _lib
+
+    torch.manual_seed(3)
+    sp, R, cpr, H = 4, 150, 128, 384
+    K = sp * cpr
+    atts = [(torch.randn(sp * R, cpr, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(sp)]  # rank r: all tokens, its heads
+    Wo = (torch.randn(H, K, device="cuda") * 0.05).to(torch.bfloat16)
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for me in range(sp):
+        a_full = torch.full((R, K), float("nan"), device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(R, H, device="cuda", dtype=torch.bfloat16)
+        _sp_call(a_full, Wo, out, R, H, K, 2, [a.data_ptr() for a in atts], sp, me, R, cpr=cpr, src_ld=cpr, flags=flags)
+        torch.cuda.synchronize()
+        assert _lib.status_read_clear() == 0
+        want_a = torch.cat([atts[r][me * R : (me + 1) * R] for r in range(sp)], 1)
+        assert torch.equal(a_full, want_a)
+        ref = want_a.float() @ Wo.float().t()
+        assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
