@@ -98,10 +98,6 @@ def main():
     torch.cuda.synchronize()
     assert _lib.status_read_clear() == 0
     assert (lpu[:Tr].float() - lpf[:Tr].float()).abs().max() < 0.1
-    for name, prm in um.named_flat_views():
-        g = prm.grad.float().clone()
-        dist.all_reduce(g)
-        assert rel(g, fullm.p(name).grad) < 8e-2 or True, name  # compared below against the unsharded gradients
     (fullm.token_logprobs(fullm(ids_p, pos_p, cu_p, 512), tgt)[0].float() * wts).sum().backward()
     for name, prm in um.named_flat_views():
         g = prm.grad.float().clone()
