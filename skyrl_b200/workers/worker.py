@@ -142,6 +142,10 @@ class ModelWorker:
             del full
             peer_ctx = None  # the flat-buffer peer optimizer spans the whole world; TP uses the DP group over NCCL
         use_peer = peer_ctx is not None and trainable and self.env.world_size > 1 and dev.type == "cuda"
+        sp_size = self._sp_size_from_cfg(cfg) if model is None and tp_size == 1 else 1
+        self.sequence_parallel = sp_size > 1
+        if self.sequence_parallel and value_head:
+            raise NotImplementedError("sequence parallelism of the critic is not supported; use sequence_parallel_size=1")
         if model is None:
             if use_peer:
                 from ..models.decoder import flat_numel_for, resolve_model_args
@@ -152,6 +156,18 @@ class ModelWorker:
                 flat_buffer, flat_grad = self.params_symm.local, self.grads_symm.local
             model = build_model(model_path, device=dev, dtype=dtype, value_head=value_head, seed=seed,
                                 flat_buffer=flat_buffer)
+            if self.sequence_parallel:
+                # Ulysses: same (replicated) parameters, sequence-sharded forward; groups of consecutive ranks
+                from ..models.tp_decoder import UlyssesCausalLM
+                from ..parallel.dist import build_mesh
+                from ..parallel.peer import PeerContext
+                from ..parallel.tensor_parallel import TPGroup
+
+                self.mesh = build_mesh(sp_size, self.env)
+                sp_peer = PeerContext(dev, group=self.mesh.tp_group) if dev.type == "cuda" else None
+                self.tp = TPGroup(sp_peer, self.mesh.tp_group)
+                self._plain_model = model
+                model = UlyssesCausalLM(model.args, self.tp, device=dev, dtype=dtype, flat_buffer=model.flat_params, seed=None)
         self.model = model
         self.model.gradient_checkpointing = bool(cfg.gradient_checkpointing) and trainable
         self.trainable = trainable
@@ -199,6 +215,17 @@ class ModelWorker:
     def _hidden(self, pv: PackedView) -> torch.Tensor:
         return self.model(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen)
 
+    def _sp_size_from_cfg(self, cfg) -> int:
+        if getattr(cfg, "strategy", "fsdp") == "megatron":
+            return 1
+        node = {"policy": cfg.policy, "ref": cfg.ref, "critic": cfg.critic}.get(self.role, cfg.policy)
+        return int(getattr(node, "sequence_parallel_size", 1) or 1)
+
+    def engine_model(self) -> CausalLM:
+        """The model object a colocated generation engine should run: the plain (unsharded-forward) view of the
+        same parameter buffer when training is sequence parallel, the training model itself otherwise."""
+        return getattr(self, "_plain_model", None) or self.model
+
     @staticmethod
     def _tp_size_from_cfg(cfg) -> int:
         if getattr(cfg, "strategy", "fsdp") != "megatron":
@@ -217,6 +244,7 @@ class ModelWorker:
 
     @property
     def tp_size(self) -> int:
+        """Ranks that jointly process one data shard (tensor- or sequence-parallel group size)."""
         return self.mesh.tp_size if self.mesh is not None else 1
 
     def _pred_logprobs(self, pv: PackedView, temp: float, with_entropy: bool = False):
