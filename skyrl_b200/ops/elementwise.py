@@ -62,6 +62,8 @@ class _AddRMSNormFn(torch.autograd.Function):
         else:
             x_out, y, rstd = _rmsnorm_ref(x, delta, w, eps)
         ctx.save_for_backward(x_out, w, rstd)
+        # taken here, not from the saved tensor: activation checkpointing hands backward a detached alias of w
+        ctx.main_grad = getattr(w, "main_grad", None)
         ctx.has_delta = delta is not None
         ctx.mark_non_differentiable(rstd)
         return x_out, y
@@ -70,7 +72,7 @@ class _AddRMSNormFn(torch.autograd.Function):
     def backward(ctx, dx_out, dy):
         x, w, rstd = ctx.saved_tensors
         T, H = x.shape
-        main_grad = getattr(w, "main_grad", None)
+        main_grad = ctx.main_grad
         if x.is_cuda:
             dy = dy.contiguous()
             dres = dx_out.contiguous() if dx_out is not None else None

@@ -198,7 +198,10 @@ class _LinearFn(torch.autograd.Function):
         y = gemm_nt(x2, w, bias)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
-        ctx.bias_ref = bias
+        # fp32 gradient buffers are looked up on the live parameters now: under activation checkpointing the tensors
+        # handed back by ``saved_tensors`` are detached aliases without the attribute
+        ctx.w_main_grad = getattr(w, "main_grad", None)
+        ctx.b_main_grad = getattr(bias, "main_grad", None) if bias is not None else None
         ctx.in_shape = shp
         return y if x.dim() == 2 else y.reshape(*shp[:-1], w.shape[0])
 
@@ -212,13 +215,13 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm_nn(dy2, w).reshape(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            main_grad = getattr(w, "main_grad", None)
+            main_grad = ctx.w_main_grad
             if main_grad is not None:
                 gemm_tn(dy2, x2, out=main_grad, accumulate=True)
             else:
                 dw = gemm_tn(dy2, x2, out_dtype=w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            bias_main = getattr(ctx.bias_ref, "main_grad", None)
+            bias_main = ctx.b_main_grad
             if bias_main is not None:
                 bias_main.add_(dy2.float().sum(0))
             else:

@@ -97,6 +97,7 @@ class _LMHeadLogprobFn(torch.autograd.Function):
             t32 = targets.to(torch.int32)
             lp, ent, lse = _ref_forward(hidden, W, targets, inv_temp, True, vocab_offset)
         ctx.save_for_backward(hidden, W, t32, lse, ent)
+        ctx.main_grad = getattr(W, "main_grad", None)  # see ops/gemm.py: not recoverable from the saved alias
         ctx.inv_temp = inv_temp
         ctx.vocab_offset = vocab_offset
         ctx.with_entropy = with_entropy
@@ -113,7 +114,7 @@ class _LMHeadLogprobFn(torch.autograd.Function):
         V = W.shape[0]
         use_ent = ctx.with_entropy and g_ent is not None
         need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        main_grad = getattr(W, "main_grad", None)
+        main_grad = ctx.main_grad
         if not hidden.is_cuda:
             with torch.enable_grad():
                 h = hidden.detach().float().requires_grad_()

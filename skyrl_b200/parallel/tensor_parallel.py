@@ -179,6 +179,7 @@ class _ColumnParallelFn(torch.autograd.Function):
             y = gemm.gemm_nt(x_full, w, bias)
         ctx.save_for_backward(x_full, w)
         ctx.has_bias = bias is not None
+        ctx.w_main_grad = getattr(w, "main_grad", None)
         return y
 
     @staticmethod
@@ -197,7 +198,7 @@ class _ColumnParallelFn(torch.autograd.Function):
             tp.peer.barrier(1)  # the slots may be overwritten only after every rank has read its own
         else:
             dx = ref_reduce_scatter_rows(gemm.gemm_nn(dy, w), tp.group)
-        mg = getattr(w, "main_grad", None)
+        mg = ctx.w_main_grad
         if mg is not None:
             gemm.gemm_tn(dy, x_full, out=mg.view(w.shape), accumulate=True)
             dw = None
@@ -227,6 +228,7 @@ class _RowParallelFn(torch.autograd.Function):
         else:
             y = ref_reduce_scatter_rows(gemm.gemm_nt(x_local, w), tp.group)
         ctx.save_for_backward(x_local, w)
+        ctx.w_main_grad = getattr(w, "main_grad", None)
         return y
 
     @staticmethod
@@ -245,7 +247,7 @@ class _RowParallelFn(torch.autograd.Function):
         else:
             dy_full = ref_all_gather_rows(dy_shard.contiguous(), tp.group)
             dx = gemm.gemm_nn(dy_full, w)
-        mg = getattr(w, "main_grad", None)
+        mg = ctx.w_main_grad
         if mg is not None:
             gemm.gemm_tn(dy_full, x_local, out=mg.view(w.shape), accumulate=True)
             dw = None

@@ -90,6 +90,7 @@ class _QKVProjFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, w, bias, widths, sp: TPGroup):
         ctx.sp, ctx.widths, ctx.has_bias = sp, tuple(widths), bias is not None
+        ctx.w_main_grad = getattr(w, "main_grad", None)
         ctx.save_for_backward(h, w)
         R, K = h.shape
         N = w.shape[0]
@@ -114,7 +115,7 @@ class _QKVProjFn(torch.autograd.Function):
         h, w = ctx.saved_tensors
         dqkv = head_to_seq(dqkv_local.contiguous(), ctx.widths, ctx.sp)  # [R, N]
         dh = gemm.gemm_nn(dqkv, w)
-        mg = getattr(w, "main_grad", None)
+        mg = ctx.w_main_grad
         if mg is not None:
             gemm.gemm_tn(dqkv, h, out=mg.view(w.shape), accumulate=True)
             dw = None
@@ -128,6 +129,7 @@ class _OProjFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, att_local, w, sp: TPGroup):
         ctx.sp = sp
+        ctx.w_main_grad = getattr(w, "main_grad", None)
         T, cpr = att_local.shape
         R = T // sp.size
         H, K = w.shape
@@ -155,7 +157,7 @@ class _OProjFn(torch.autograd.Function):
         att_seq, w = ctx.saved_tensors
         dout = dout.contiguous()
         datt_seq = gemm.gemm_nn(dout, w)  # [R, K]
-        mg = getattr(w, "main_grad", None)
+        mg = ctx.w_main_grad
         if mg is not None:
             gemm.gemm_tn(dout, att_seq, out=mg.view(w.shape), accumulate=True)
             dw = None

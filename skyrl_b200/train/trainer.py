@@ -87,11 +87,7 @@ class PPOTrainer:
             self.critic = CriticWorker(t, model_path=t.critic.model.path or t.policy.model.path, env=self.env,
                                        seed=t.seed + 1)
         if self.inference_engine_client is None:
-            engine_model = self.policy.engine_model()
-            if self.policy.tp_size > 1 and not self.policy.sequence_parallel:
-                # the engine runs the unsharded model; weights are re-gathered after each update
-                engine_model = self._engine_model = self.policy.full_model_copy()
-            self.engine = self._build_engine(engine_model)
+            self.engine = self._build_engine(self.policy.engine_model())
             self.inference_engine_client = LocalInferenceClient([self.engine], self.tokenizer)
         if self.generator is None:
             self.generator = SkyRLGymGenerator(self.cfg.generator, self.cfg.environment.skyrl_gym,
@@ -331,9 +327,8 @@ class PPOTrainer:
     def sync_weights(self) -> None:
         """Make the freshly trained weights visible to the generation engine(s)."""
         c = self.inference_engine_client
-        if (self.policy is not None and self.policy.tp_size > 1 and not self.policy.sequence_parallel
-                and getattr(self, "_engine_model", None) is not None):
-            self.policy.full_model_copy(into=self._engine_model)
+        if self.policy is not None:
+            self.policy.refresh_engine_model()  # TP shards / LoRA adapters -> the engine's full weights
         if hasattr(c, "increment_weight_version"):
             c.increment_weight_version()
 

@@ -154,8 +154,23 @@ class ModelWorker:
                 self.params_symm = peer_ctx.alloc(n, dtype)
                 self.grads_symm = peer_ctx.alloc(n, torch.float32)
                 flat_buffer, flat_grad = self.params_symm.local, self.grads_symm.local
+            lora_cfg = getattr(getattr(cfg, self.role, cfg.policy).model, "lora", None) if self.role in ("policy", "critic") else None
+            use_lora = trainable and not value_head and lora_cfg is not None and lora_cfg.rank > 0
+            if use_lora and use_peer:
+                use_peer, flat_buffer, flat_grad = False, None, None  # adapter buffers are small: plain NCCL reduction
+                self.params_symm = self.grads_symm = None
+                peer_ctx = None
             model = build_model(model_path, device=dev, dtype=dtype, value_head=value_head, seed=seed,
                                 flat_buffer=flat_buffer)
+            if use_lora:
+                from ..models.lora import LoRACausalLM
+
+                if sp_size > 1:
+                    raise NotImplementedError("LoRA together with sequence parallelism is not supported")
+                model = LoRACausalLM(model.args, rank=lora_cfg.rank, alpha=lora_cfg.alpha, dropout=lora_cfg.dropout,
+                                     target_modules=lora_cfg.target_modules, exclude_modules=lora_cfg.exclude_modules,
+                                     init_method=lora_cfg.init_method, device=dev, dtype=dtype,
+                                     flat_buffer=model.flat_params, seed=None, lora_seed=seed + 1)
             if self.sequence_parallel:
                 # Ulysses: same (replicated) parameters, sequence-sharded forward; groups of consecutive ranks
                 from ..models.tp_decoder import UlyssesCausalLM
@@ -222,9 +237,34 @@ class ModelWorker:
         return int(getattr(node, "sequence_parallel_size", 1) or 1)
 
     def engine_model(self) -> CausalLM:
-        """The model object a colocated generation engine should run: the plain (unsharded-forward) view of the
-        same parameter buffer when training is sequence parallel, the training model itself otherwise."""
+        """The model object a colocated generation engine should run.  Shared with training whenever the training
+        parameters are the full weights (plain or sequence-parallel); a separate full copy when they are not
+        (tensor-parallel shards, LoRA adapters over a frozen base) -- ``refresh_engine_model`` then re-derives it."""
+        from ..models.lora import LoRACausalLM
+
+        if getattr(self, "_engine_copy", None) is not None:
+            return self._engine_copy
+        if isinstance(self.model, LoRACausalLM):
+            self._engine_copy = CausalLM(self.model.args, device=self.env.device, dtype=self.model.base_flat_params.dtype,
+                                         seed=None)
+            self.model.merge_into(self._engine_copy)
+            return self._engine_copy
+        if self.mesh is not None and not self.sequence_parallel:
+            self._engine_copy = self.full_model_copy()
+            return self._engine_copy
         return getattr(self, "_plain_model", None) or self.model
+
+    def refresh_engine_model(self) -> None:
+        """Bring a separate engine copy up to date with the trained parameters (no-op when the buffer is shared)."""
+        from ..models.lora import LoRACausalLM
+
+        ec = getattr(self, "_engine_copy", None)
+        if ec is None:
+            return
+        if isinstance(self.model, LoRACausalLM):
+            self.model.merge_into(ec)
+        else:
+            self.full_model_copy(into=ec)
 
     @staticmethod
     def _tp_size_from_cfg(cfg) -> int:
@@ -412,8 +452,16 @@ class ModelWorker:
     def save_hf_model(self, export_dir: str, tokenizer=None) -> None:
         from ..models import hf_io
 
+        from ..models.lora import LoRACausalLM
+
         model = self.model
-        if self.mesh is not None:  # gather the TP shards into an unsharded model for the export
+        if isinstance(model, LoRACausalLM):  # merged weights + the adapter itself
+            if self.env.rank == 0:
+                model.save_adapter(os.path.join(export_dir, "lora_adapter"))
+            merged = CausalLM(model.args, device=self.env.device, dtype=model.base_flat_params.dtype, seed=None)
+            model.merge_into(merged)
+            model = merged
+        elif self.mesh is not None and not self.sequence_parallel:  # gather the TP shards for the export
             model = self.full_model_copy()
         if self.env.rank == 0:
             hf_io.save_hf_model(model, export_dir, tokenizer)

@@ -96,3 +96,28 @@ def test_hf_export_roundtrip(tmp_path):
 
     m2 = build_model(str(tmp_path / "export"))
     assert torch.equal(m.flat_params, m2.flat_params)
+
+
+def test_gradient_checkpointing_accumulates_into_main_grad():
+    """Recomputation must route weight gradients into the fp32 flat buffer exactly like the plain backward."""
+    import torch
+
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+
+    a = PRESETS["tiny-llama"]
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(4, a.vocab_size, (33,), generator=g).int()
+    pos = torch.cat([torch.arange(13), torch.arange(20)]).int()
+    cu = torch.tensor([0, 13, 33]).int()
+    grads = []
+    for ck in (False, True):
+        m = CausalLM(a, device="cpu", dtype=torch.float32, seed=0)
+        fg = torch.zeros(m.flat_params.numel())
+        m.attach_main_grad(fg)
+        m.gradient_checkpointing = ck
+        lp, _ = m.token_logprobs(m(ids, pos, cu, 32), torch.roll(ids.long(), -1))
+        lp.sum().backward()
+        assert all(p.grad is None for p in m.parameters())
+        grads.append(fg)
+    assert torch.allclose(grads[0], grads[1], atol=1e-5, rtol=1e-4)
+    assert grads[0].abs().sum() > 0
