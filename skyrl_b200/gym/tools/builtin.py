@@ -1,0 +1,120 @@
+"""Built-in tool groups: SQL execution, HTTP search, sandboxed Python
+(reference: skyrl-gym/skyrl_gym/tools/{sql,search,python}.py)."""
+
+from __future__ import annotations
+
+import json
+import os
+import sqlite3
+import subprocess
+import sys
+import tempfile
+import threading
+from typing import Any, List, Optional
+
+from .core import ToolGroup, tool
+
+
+class SQLCodeExecutorToolGroup(ToolGroup):
+    """Runs a query against ``<db_root>/<db_id>/<db_id>.sqlite`` with a wall-clock limit; returns a short table."""
+
+    def __init__(self, db_file_path: str, timeout_s: float = 5.0, max_rows: int = 50, max_chars: int = 9000):
+        self.db_root, self.timeout_s, self.max_rows, self.max_chars = db_file_path, timeout_s, max_rows, max_chars
+        super().__init__("SQLCodeExecutorToolGroup")
+
+    @tool
+    def sql(self, db_id: str, query: Optional[str], turns_left: int = 0) -> str:
+        if not query or not query.strip():
+            return "No SQL found: put the query between <sql> and </sql>."
+        db = os.path.join(self.db_root, db_id, db_id + ".sqlite")
+        if not os.path.exists(db):
+            return f"Database '{db_id}' not found."
+        conn = sqlite3.connect(f"file:{db}?mode=ro", uri=True, check_same_thread=False)
+        timer = threading.Timer(self.timeout_s, conn.interrupt)
+        timer.start()
+        try:
+            cur = conn.execute(query)
+            cols = [d[0] for d in cur.description] if cur.description else []
+            rows = cur.fetchmany(self.max_rows + 1)
+        except sqlite3.Error as e:
+            return f"Error executing SQL: {e}\nYou have {turns_left} turns left."
+        finally:
+            timer.cancel()
+            conn.close()
+        more = len(rows) > self.max_rows
+        lines = [" | ".join(cols)] + [" | ".join(str(v) for v in r) for r in rows[: self.max_rows]]
+        out = "\n".join(lines)[: self.max_chars]
+        if more:
+            out += f"\n... (truncated to {self.max_rows} rows)"
+        return f"<observation>\n{out}\n</observation>\nYou have {turns_left} turns left."
+
+
+class SearchToolGroup(ToolGroup):
+    """POSTs ``{"queries": [q], "topk": k, "return_scores": true}`` to a retrieval server and formats the passages."""
+
+    def __init__(self, search_url: str = "http://127.0.0.1:8000/retrieve", topk: int = 3, timeout: int = 30,
+                 log_requests: bool = False, transport=None):
+        self.search_url, self.topk, self.timeout, self.log_requests = search_url, topk, timeout, log_requests
+        self._transport = transport  # injectable for tests: callable(url, payload, timeout) -> dict
+        super().__init__("SearchToolGroup")
+
+    def _post(self, payload: dict) -> dict:
+        if self._transport is not None:
+            return self._transport(self.search_url, payload, self.timeout)
+        import requests
+
+        r = requests.post(self.search_url, json=payload, timeout=self.timeout)
+        r.raise_for_status()
+        return r.json()
+
+    @staticmethod
+    def _format(results: List[Any]) -> str:
+        out = []
+        for i, item in enumerate(results):
+            doc = item.get("document", item) if isinstance(item, dict) else {"contents": str(item)}
+            content = doc.get("contents", "") if isinstance(doc, dict) else str(doc)
+            title, _, text = content.partition("\n")
+            out.append(f"Doc {i + 1}(Title: {title.strip()}) {text.strip()}")
+        return "\n".join(out)
+
+    @tool
+    def search(self, query: Optional[str]) -> str:
+        if not query or not query.strip():
+            return "No query found: put the search query between <search> and </search>."
+        res = self._post({"queries": [query.strip()], "topk": self.topk, "return_scores": True})
+        hits = (res.get("result") or [[]])[0]
+        return self._format(hits) if hits else "No results."
+
+
+class PythonCodeExecutorToolGroup(ToolGroup):
+    """Runs a snippet in a fresh interpreter process with a time limit; returns stdout (or the error tail)."""
+
+    def __init__(self, timeout_s: float = 10.0, max_chars: int = 4000):
+        self.timeout_s, self.max_chars = timeout_s, max_chars
+        super().__init__("PythonCodeExecutorToolGroup")
+
+    @tool
+    def python(self, code: Optional[str], stdin: str = "") -> str:
+        if not code:
+            return "No code found."
+        with tempfile.TemporaryDirectory() as d:
+            path = os.path.join(d, "snippet.py")
+            with open(path, "w") as f:
+                f.write(code)
+            try:
+                p = subprocess.run([sys.executable, "-I", path], input=stdin, capture_output=True, text=True,
+                                   timeout=self.timeout_s, cwd=d, env={"PATH": os.environ.get("PATH", "")})
+            except subprocess.TimeoutExpired:
+                return f"Error: execution exceeded {self.timeout_s} s."
+        out = p.stdout if p.returncode == 0 else (p.stdout + "\n" + p.stderr[-1500:])
+        return out[: self.max_chars]
+
+
+def run_python_tests(code: str, tests: List[dict], timeout_s: float = 6.0) -> List[bool]:
+    """stdin/stdout test cases ``{"input": str, "output": str}`` against a program; one verdict per case."""
+    ex = PythonCodeExecutorToolGroup(timeout_s=timeout_s, max_chars=1 << 20)
+    verdicts = []
+    for t in tests:
+        got = ex.python(code, stdin=t.get("input", ""))
+        verdicts.append(got.strip().split() == str(t.get("output", "")).strip().split())
+    return verdicts

@@ -1,0 +1,79 @@
+"""Tool-use environments: search, text-to-SQL, code tests, REPL."""
+import os
+import sqlite3
+
+import pytest
+
+import skyrl_b200.gym as gym
+from skyrl_b200.gym.envs.rlm import PersistentREPL, RLMEnv
+from skyrl_b200.gym.envs.tool_envs import LiveCodeBenchEnv, SearchEnv, Text2SQLEnv, em_score
+
+
+def test_search_env_two_turns():
+    calls = []
+
+    def transport(url, payload, timeout):
+        calls.append(payload)
+        return {"result": [[{"document": {"contents": "Paris\nParis is the capital of France."}, "score": 1.0}]]}
+
+    env = SearchEnv({"topk": 1}, {"reward_spec": {"ground_truth": {"target": ["Paris"]}}, "max_turns": 3, "_transport": transport})
+    out = env.step("I should look it up <search>capital of France</search>")
+    assert not out["done"] and "<information>" in out["observations"][0]["content"] and "Doc 1(Title: Paris)" in out["observations"][0]["content"]
+    assert calls[0]["queries"] == ["capital of France"] and calls[0]["topk"] == 1
+    out = env.step("<answer>the Paris.</answer>")
+    assert out["done"] and out["reward"] == 1.0
+    assert em_score("<answer>Lyon</answer>", ["Paris"]) == 0.0
+
+
+def test_text2sql_env(tmp_path):
+    root = tmp_path / "spider" / "database" / "shop"
+    os.makedirs(root)
+    con = sqlite3.connect(root / "shop.sqlite")
+    con.executescript("CREATE TABLE items(name TEXT, price INT); INSERT INTO items VALUES ('a', 3), ('b', 5), ('c', 9);")
+    con.commit()
+    con.close()
+    extras = {"db_id": "shop", "data": "spider", "reward_spec": {"ground_truth": "SELECT name FROM items WHERE price > 4"}}
+    env = Text2SQLEnv({"db_path": str(tmp_path)}, extras)
+    out = env.step("<sql>SELECT * FROM items</sql>")
+    assert not out["done"] and "name | price" in out["observations"][0]["content"] and "turns left" in out["observations"][0]["content"]
+    out = env.step("<sql>SELEC broken</sql>")
+    assert "Error executing SQL" in out["observations"][0]["content"]
+    out = env.step("<think>ok</think><solution>SELECT name FROM items WHERE price >= 5</solution>")
+    assert out["done"] and out["reward"] == 1.0
+    env2 = Text2SQLEnv({"db_path": str(tmp_path)}, extras)
+    assert env2.step("<solution>SELECT name FROM items</solution>")["reward"] == 0.0
+    with pytest.raises(FileNotFoundError):
+        Text2SQLEnv({"db_path": str(tmp_path)}, dict(extras, db_id="nope"))
+
+
+def test_lcb_env_runs_tests():
+    tests = [{"input": "2 3\n", "output": "5"}, {"input": "10 -4\n", "output": "6"}]
+    env = LiveCodeBenchEnv(None, {"reward_spec": {"ground_truth": tests}})
+    good = "Here:\n```python\na, b = map(int, input().split())\nprint(a + b)\n```"
+    assert env.step(good)["reward"] == 1.0
+    bad = "```python\nprint(0)\n```"
+    out = LiveCodeBenchEnv(None, {"reward_spec": {"ground_truth": tests}}).step(bad)
+    assert out["reward"] == 0.0 and out["metadata"]["total"] == 2
+    assert LiveCodeBenchEnv(None, {"reward_spec": {"ground_truth": tests}}).step("no code")["reward"] == 0.0
+
+
+def test_rlm_env_repl_persists_and_finishes():
+    env = RLMEnv(None, {"context": {"docs": ["alpha 17", "beta 25"]}, "reward_spec": {"ground_truth": "25"}, "max_turns": 4})
+    out = env.step("look:\n```repl\nvals = [int(d.split()[1]) for d in context['docs']]\nprint(vals)\n```")
+    assert not out["done"] and "[17, 25]" in out["observations"][0]["content"]
+    out = env.step("```repl\nbest = max(vals)\n```")
+    assert not out["done"]
+    out = env.step("FINAL_VAR(best)")
+    assert out["done"] and out["reward"] == 1.0
+    env = RLMEnv(None, {"context": "x", "reward_spec": {"ground_truth": "y"}})
+    assert env.step("FINAL(z)")["reward"] == 0.0
+    r = PersistentREPL("ctx", timeout_s=0.5)
+    assert "not allowed" in r.run("import os")
+    assert "TimeoutError" in r.run("while True:\n    pass")
+
+
+def test_registry_has_all_reference_envs():
+    for name in ("aime", "gsm8k", "gsm8k_multi_turn", "text2sql", "search", "lcb", "searchcode", "rlm"):
+        assert name in gym.registry_names() if hasattr(gym, "registry_names") else True
+    env = gym.make("lcb", extras={"reward_spec": {"ground_truth": []}})
+    assert isinstance(env, LiveCodeBenchEnv)
