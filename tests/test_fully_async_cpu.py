@@ -94,3 +94,35 @@ def test_fully_async_end_to_end(tmp_path):
     tr.staleness.check_invariant()
     st = torch.load(f"{tmp_path}/ckpt/global_step_2/fully_async_state.pt", weights_only=False)
     assert len(st["consumed_uids"]) == 4
+
+
+def test_one_step_off_trainer_overlaps_generation_and_training(tmp_path):
+    """Batch k+1 is generated from the weights of step k-1 while step k trains; the engine has its own weight copy."""
+    import torch
+
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.parallel.dist import get_env
+    from skyrl_b200.train.async_trainer import OneStepOffPPOTrainer
+    from skyrl_b200.train.dataset import PromptDataset
+    from skyrl_b200.utils.tokenizer import SyntheticTokenizer
+
+    cfg = SkyRLTrainConfig.from_cli_overrides([
+        "trainer.policy.model.path=tiny-qwen2-d128", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+        "generator.n_samples_per_prompt=4", "trainer.max_prompt_length=32", "generator.sampling_params.max_generate_length=8",
+        "environment.env_class=synthetic_bernoulli", "trainer.bf16=false", "trainer.policy.optimizer_config.lr=1e-3",
+        "generator.inference_engine.max_num_seqs=8", "generator.inference_engine.enforce_eager=true",
+        "generator.inference_engine.engine_init_kwargs={num_blocks: 64}", "trainer.resume_mode=none", "trainer.ckpt_interval=-1",
+        "trainer.algorithm.use_kl_loss=false", "trainer.logger=console", "trainer.eval_interval=-1", "trainer.epochs=1",
+        f"trainer.ckpt_path={tmp_path}"])
+    tok = SyntheticTokenizer(2048)
+    rows = [{"prompt": [{"role": "user", "content": f"q{i}"}], "env_class": "synthetic_bernoulli",
+             "env_extras": {"p": 0.5, "seed": i}} for i in range(6)]
+    ds = PromptDataset(rows, tok, 32)
+    tr = OneStepOffPPOTrainer(cfg, tokenizer=tok, train_dataset=ds, env=get_env())
+    tr.build_models()
+    assert tr.engine.model is not tr.policy.model
+    before = tr.policy.model.flat_params.clone()
+    tr.train()
+    assert tr.global_step == 3
+    assert not torch.equal(tr.policy.model.flat_params, before)
+    assert torch.equal(tr.engine.model.flat_params, tr.policy.model.flat_params)  # last sync published the weights
