@@ -279,7 +279,7 @@ class LLMEngine:
             from ..models.moe import moe_ffn
 
             d = moe_ffn(h, m.p(pre + "router"), m.p(pre + "experts_wgu"), m.p(pre + "experts_wd"),
-                        a.num_experts_per_tok, a.norm_topk_prob)
+                        a.num_experts_per_tok, a.norm_topk_prob, layer=i)
         else:
             gu = gemm.gemm_nt(h, m.p(pre + "wgu"))
             d = gemm.gemm_nt(ew.swiglu(gu), m.p(pre + "wd"))

@@ -26,11 +26,16 @@ def route_topk(h: torch.Tensor, router_w: torch.Tensor, top_k: int, norm_topk_pr
 
 
 def moe_ffn(h: torch.Tensor, router_w: torch.Tensor, wgu: torch.Tensor, wd: torch.Tensor, top_k: int,
-            norm_topk_prob: bool = True, routed_indices: torch.Tensor | None = None) -> torch.Tensor:
-    """``h``: [T, H]; ``wgu``: [E, 2F, H]; ``wd``: [E, H, F].  ``routed_indices`` replays rollout-time routing."""
+            norm_topk_prob: bool = True, routed_indices: torch.Tensor | None = None, layer: int | None = None, qat=None) -> torch.Tensor:
+    """``h``: [T, H]; ``wgu``: [E, 2F, H]; ``wd``: [E, H, F].  ``routed_indices`` replays rollout-time routing;
+    with ``layer`` given, an active ``router_replay`` context records or overrides the choice."""
     T, H = h.shape
     E = wgu.shape[0]
     w, idx = route_topk(h, router_w, top_k, norm_topk_prob)
+    if layer is not None and routed_indices is None:
+        from . import router_replay
+
+        routed_indices = router_replay.on_route(layer, idx)
     if routed_indices is not None:
         probs = torch.softmax(h.float() @ router_w.float().t(), dim=-1)
         idx = routed_indices.long()
@@ -49,8 +54,14 @@ def moe_ffn(h: torch.Tensor, router_w: torch.Tensor, wgu: torch.Tensor, wd: torc
         if n == 0:
             continue
         xe = x[s : s + n]
-        gu = gemm.linear(xe, wgu[e])
-        out_rows.append(gemm.linear(ew.swiglu(gu), wd[e]))
+        w1, w2 = wgu[e], wd[e]
+        if qat is not None and qat.enabled and torch.is_grad_enabled():  # fake-INT4 expert weights, straight-through
+            from .qat import fake_int4
+
+            w1 = fake_int4(w1, qat.group_size, True, qat.scale_divisor, qat.q_min)
+            w2 = fake_int4(w2, qat.group_size, True, qat.scale_divisor, qat.q_min)
+        gu = gemm.linear(xe, w1)
+        out_rows.append(gemm.linear(ew.swiglu(gu), w2))
         s += n
     y = torch.cat(out_rows, dim=0) if out_rows else x.new_zeros((0, H))
     wf = w.reshape(-1)[order].to(y.dtype)

@@ -115,8 +115,11 @@ def parse_prometheus_text(text: str) -> Dict[str, float]:
 class ServerMetricsScraper:
     """Polls ``/metrics`` of each rollout server; ``delta()`` turns counters into rates between two scrapes."""
 
+    # counter name on the server -> rate reported (both this engine's names and the conventional *_total ones)
     RATES = {"generation_tokens_total": "gen_tokens_per_s", "prompt_tokens_total": "prompt_tokens_per_s",
-             "requests_finished_total": "requests_per_s"}
+             "requests_finished_total": "requests_per_s", "decode_tokens": "gen_tokens_per_s",
+             "prefill_tokens": "prompt_tokens_per_s", "decode_steps": "decode_steps_per_s"}
+    COUNTERS = frozenset(RATES)
 
     def __init__(self, urls: List[str], fetch: Optional[Callable[[str], str]] = None, prefix: str = "skyrl_b200_"):
         self.urls, self.prefix = [u.rstrip("/") for u in urls], prefix
@@ -143,7 +146,7 @@ class ServerMetricsScraper:
 
     def delta(self) -> Dict[str, float]:
         now, cur = time.time(), self.scrape()
-        out = {f"inference/{k}": v for k, v in cur.items() if not k.endswith("_total")}
+        out = {f"inference/{k}": v for k, v in cur.items() if not k.endswith("_total") and k not in self.COUNTERS}
         if self._last is not None and now > self._last_t:
             dt = now - self._last_t
             for k, name in self.RATES.items():

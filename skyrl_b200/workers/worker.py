@@ -184,6 +184,9 @@ class ModelWorker:
                 self._plain_model = model
                 model = UlyssesCausalLM(model.args, self.tp, device=dev, dtype=dtype, flat_buffer=model.flat_params, seed=None)
         self.model = model
+        qcfg = getattr(cfg.policy.model, "fake_int4_qat", None)
+        if trainable and qcfg is not None and qcfg.enabled:
+            self.model.fake_int4_qat = qcfg  # MoE expert weights are fake-quantised in the training forward
         self.model.gradient_checkpointing = bool(cfg.gradient_checkpointing) and trainable
         self.trainable = trainable
         self.optimizer: Optional[ShardedAdamW] = None

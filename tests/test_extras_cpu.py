@@ -1,0 +1,110 @@
+"""Wire packing, router replay, fake INT4 QAT, MTP soft cross-entropy, multi-tenant adapter store."""
+import numpy as np
+import pytest
+import torch
+
+from skyrl_b200.algorithms import mtp
+from skyrl_b200.inference import wire
+from skyrl_b200.models import qat, router_replay
+from skyrl_b200.models.moe import moe_ffn
+
+
+def test_wire_round_trip_and_rejections():
+    c, n = wire.build_logprobs_content([-0.5, None, float("nan"), float("-inf")])
+    assert n == 3 and c[1]["logprob"] == wire.CLAMPED_LOGPROB and c[0]["logprob"] == -0.5
+    a = np.random.default_rng(0).integers(0, 128, size=(5, 3, 8))
+    p = wire.pack_routed_experts(a)
+    assert p["dtype"] == "uint8" and np.array_equal(wire.decode_packed_routed_experts(p), a)
+    assert wire.pack_routed_experts(a + 300)["dtype"] == "uint16"
+    with pytest.raises(TypeError):
+        wire.pack_routed_experts(a.tolist())
+    bad = dict(p, shape=[5, 3])
+    with pytest.raises(ValueError):
+        wire.decode_packed_routed_experts(bad)
+    with pytest.raises(ValueError):
+        wire.decode_packed_routed_experts(dict(p, dtype="int32"))  # wrong byte count for the claimed dtype
+
+
+def test_router_replay_forces_recorded_experts():
+    torch.manual_seed(0)
+    T, H, E, F, k = 12, 16, 6, 8, 2
+    h = torch.randn(T, H)
+    router = torch.randn(E, H)
+    wgu, wd = torch.randn(E, 2 * F, H) * 0.1, torch.randn(E, H, F) * 0.1
+    with router_replay.record_routing() as store:
+        y0 = moe_ffn(h, router, wgu, wd, k, layer=0)
+    idx = router_replay.stack_recorded(store)
+    assert idx.shape == (T, 1, k)
+    h2 = h + 0.8 * torch.randn(T, H)  # perturbed activations would route differently on their own
+    free = moe_ffn(h2, router, wgu, wd, k, layer=0)
+    with router_replay.replay_routing(idx):
+        forced = moe_ffn(h2, router, wgu, wd, k, layer=0)
+    manual = moe_ffn(h2, router, wgu, wd, k, routed_indices=idx[:, 0])
+    assert torch.allclose(forced, manual) and not torch.allclose(forced, free)
+    with router_replay.replay_routing(idx):
+        assert torch.allclose(moe_ffn(h, router, wgu, wd, k, layer=0), y0, atol=1e-6)
+    al = router_replay.align_to_packed([idx[:4], idx[4:7]], [5, 3])
+    assert al.shape[0] == 8 and torch.equal(al[4], idx[3])
+
+
+def test_fake_int4_levels_and_straight_through():
+    w = torch.randn(8, 64, requires_grad=True)
+    q = qat.fake_int4(w, 32)
+    lv = (q.detach().reshape(8, 2, 32) / (w.detach().reshape(8, 2, 32).abs().amax(-1, keepdim=True) / 7)).round()
+    assert lv.abs().max() <= 7 and torch.unique(lv).numel() <= 15
+    q.sum().backward()
+    assert torch.equal(w.grad, torch.ones_like(w))
+    assert 0 < qat.quantization_error(w.detach()) < 0.2
+    with pytest.raises(ValueError):
+        qat.fake_int4_quant_dequant(torch.randn(4, 30))
+
+
+def test_mtp_soft_ce_trains_draft_head_only():
+    torch.manual_seed(0)
+    T, H, V = 40, 16, 50
+    hidden = torch.randn(T, H, requires_grad=True)
+    lm = torch.randn(V, H, requires_grad=True)
+    cu = torch.tensor([0, 15, 40])
+    head = mtp.DraftHead(H)
+    same = mtp.soft_cross_entropy(torch.randn(5, V), torch.randn(5, V))
+    assert same > 0
+    loss0 = mtp.mtp_draft_loss(head, hidden, lm, cu)
+    loss0.backward()
+    assert hidden.grad is None and lm.grad is None  # trunk and LM head are detached from the draft loss
+    assert head.down.weight.grad.abs().sum() > 0
+    norm, coef = mtp.clip_grad_norm_separately(head.parameters(), 1e-3)
+    assert coef < 1.0 and norm > 0
+    opt = torch.optim.Adam(head.parameters(), lr=3e-2)
+    for _ in range(60):
+        opt.zero_grad()
+        l = mtp.mtp_draft_loss(head, hidden, lm, cu)
+        l.backward()
+        opt.step()
+    assert float(l) < float(loss0)
+
+
+def test_adapter_store_swaps_tenants():
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.parallel.dist import get_env
+    from skyrl_b200.workers.adapter_store import AdapterStore
+    from skyrl_b200.workers.worker import PolicyWorker
+
+    cfg = SkyRLTrainConfig.from_cli_overrides(["trainer.policy.model.path=tiny-llama", "trainer.policy.model.lora.rank=4",
+                                               "trainer.bf16=false"])
+    w = PolicyWorker(cfg.trainer, model_path="tiny-llama", env=get_env(), seed=0)
+    store = AdapterStore(w, max_slots=2)
+    store.create("a", seed=1)
+    w.model.flat_params.add_(1.0)
+    w.optimizer.exp_avg.fill_(0.5)
+    w.optimizer.step_count = 7
+    pa = w.model.flat_params.clone()
+    store.create("b", seed=2)
+    assert w.optimizer.step_count == 0 and w.optimizer.exp_avg.abs().sum() == 0
+    assert not torch.equal(w.model.flat_params, pa)
+    pb = w.model.flat_params.clone()
+    store.swap_to("a")
+    assert torch.equal(w.model.flat_params, pa) and w.optimizer.step_count == 7 and float(w.optimizer.exp_avg[0]) == 0.5
+    store.swap_to("b")
+    assert torch.equal(w.model.flat_params, pb)
+    with pytest.raises(RuntimeError):
+        store.create("c")
