@@ -21,6 +21,71 @@ TRAINING_INPUT_KEYS = (
 )  # fmt: skip
 
 
+class TensorList:
+    """A batch column whose rows are tensors of different shapes (image patches per sample): supports the same
+    batch-dimension operations as a tensor column (reference: ``TensorList`` in training_batch.py:40-118)."""
+
+    def __init__(self, tensors: Sequence[torch.Tensor]):
+        self.tensors: List[torch.Tensor] = list(tensors)
+
+    @property
+    def shape(self):
+        return (len(self.tensors),)
+
+    def __len__(self) -> int:
+        return len(self.tensors)
+
+    def __iter__(self):
+        return iter(self.tensors)
+
+    def __getitem__(self, idx):
+        if isinstance(idx, int):
+            return self.tensors[idx]
+        if isinstance(idx, slice):
+            return TensorList(self.tensors[idx])
+        if isinstance(idx, torch.Tensor):
+            idx = idx.tolist()
+        return TensorList([self.tensors[int(i)] for i in idx])
+
+    @property
+    def is_cuda(self) -> bool:
+        return bool(self.tensors) and self.tensors[0].is_cuda
+
+    @property
+    def device(self):
+        return self.tensors[0].device if self.tensors else torch.device("cpu")
+
+    def is_floating_point(self) -> bool:
+        return bool(self.tensors) and self.tensors[0].is_floating_point()
+
+    def to(self, *a, **k) -> "TensorList":
+        return TensorList([t.to(*a, **k) for t in self.tensors])
+
+    def cpu(self) -> "TensorList":
+        return TensorList([t.cpu() for t in self.tensors])
+
+    def contiguous(self) -> "TensorList":
+        return TensorList([t.contiguous() for t in self.tensors])
+
+    def pin_memory(self) -> "TensorList":
+        return TensorList([t.pin_memory() for t in self.tensors])
+
+    def repeat_interleave(self, times: int, dim: int = 0) -> "TensorList":
+        return TensorList([t for t in self.tensors for _ in range(times)])
+
+    @staticmethod
+    def cat(lists: Sequence["TensorList"]) -> "TensorList":
+        return TensorList([t for l in lists for t in l.tensors])
+
+    def flat(self) -> torch.Tensor:
+        """All rows concatenated along dim 0 (what a vision tower consumes)."""
+        return torch.cat(self.tensors, 0) if self.tensors else torch.empty(0)
+
+
+def _batched(v) -> bool:
+    return isinstance(v, (torch.Tensor, TensorList))
+
+
 class TensorBatch(dict):
     """dict[str, Tensor | None] with batch-dimension operations. ``None`` values are carried through."""
 
@@ -31,14 +96,14 @@ class TensorBatch(dict):
 
     # ------------------------------------------------------------------ invariants
     def _check(self) -> None:
-        sizes = {k: v.shape[0] for k, v in self.items() if isinstance(v, torch.Tensor)}
+        sizes = {k: v.shape[0] for k, v in self.items() if _batched(v)}
         if len(set(sizes.values())) > 1:
             raise ValueError(f"batch size mismatch across keys: {sizes}")
 
     @property
     def batch_size(self) -> int:
         for v in self.values():
-            if isinstance(v, torch.Tensor):
+            if _batched(v):
                 return v.shape[0]
         return 0
 
@@ -53,14 +118,14 @@ class TensorBatch(dict):
         return None
 
     def __setitem__(self, key, value):
-        if isinstance(value, torch.Tensor) and self.batch_size and len(self.keys() - {key}) and \
+        if _batched(value) and self.batch_size and len(self.keys() - {key}) and \
                 value.shape[0] != self.batch_size:
             raise ValueError(f"'{key}' has batch size {value.shape[0]}, expected {self.batch_size}")
         super().__setitem__(key, value)
 
     # ------------------------------------------------------------------ batch ops
     def _map(self, fn) -> "TensorBatch":
-        out = type(self)({k: (fn(v) if isinstance(v, torch.Tensor) else v) for k, v in self.items()},
+        out = type(self)({k: (fn(v) if _batched(v) else v) for k, v in self.items()},
                          metadata=dict(self.metadata))
         return out
 
@@ -111,18 +176,20 @@ class TensorBatch(dict):
                 out[k] = None
             elif any(v is None for v in vals):
                 raise ValueError(f"key '{k}' is None in some batches but not all")
+            elif isinstance(vals[0], TensorList):
+                out[k] = TensorList.cat(vals)
             else:
                 out[k] = torch.cat(vals, dim=0)
         return cls(out, metadata=dict(batches[0].metadata))
 
     def iter_rows(self) -> Iterator[Dict[str, Any]]:
         for i in range(self.batch_size):
-            yield {k: (v[i] if isinstance(v, torch.Tensor) else v) for k, v in self.items()}
+            yield {k: (v[i] if _batched(v) else v) for k, v in self.items()}
 
     # ------------------------------------------------------------------ serialisation
     def to_bytes(self) -> bytes:
         buf = io.BytesIO()
-        torch.save({"tensors": {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in self.items()},
+        torch.save({"tensors": {k: (v.cpu() if _batched(v) else v) for k, v in self.items()},
                     "metadata": self.metadata}, buf)
         return buf.getvalue()
 
