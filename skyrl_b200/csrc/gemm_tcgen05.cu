@@ -66,7 +66,13 @@ struct TpArgs {
   int scatter_cols, gather_cols;
   int seg_start[3], seg_w[3];    // scatter_cols: first column and per-rank width of each segment (0 width = unused)
   int cols_per_rank;             // gather_cols
-  long long src_ld;              // gather_cols: row stride of the source buffers
+  long long src_ld;              // gather_cols / gather_idx: row stride of the source buffers
+  // Expert-parallel MoE (token dispatch / combine fused into the expert GEMMs):
+  //  gather_idx:  A row r is row idx_row[r] of rank idx_rank[r]'s token buffer src[rank] (dispatch).
+  //  scatter_idx: C row r is stored to row idx_row[r] of rank idx_rank[r]'s buffer dst[rank] (combine).
+  int gather_idx, scatter_idx;
+  const int* idx_rank;
+  const int* idx_row;
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
@@ -114,7 +120,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int k_blocks = (K + kBK - 1) / kBK;
   const int kpb = (k_blocks + splits - 1) / splits;  // k blocks per slice (host guarantees no empty slice)
   // GATHER: logical m-block 0 is the first block of the local shard, then the next rank's, and so on
-  const int m_rot = (GATHER && !tp.gather_cols) ? tp.my_rank * (tp.rows_per_rank / kBM) : 0;
+  const int m_rot = (GATHER && !tp.gather_cols && !tp.gather_idx) ? tp.my_rank * (tp.rows_per_rank / kBM) : 0;
   auto rot = [&](int pm) { return GATHER ? (pm + m_rot) % tm.m_blocks : pm; };
 
   if (threadIdx.x == 0) {
@@ -152,7 +158,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         pm = rot(pm);
         if (GATHER) {
           // rows of another rank: wait until the copy warps have landed every piece of this m-block
-          const int owner = tp.gather_cols ? -1 : (pm * kBM) / tp.rows_per_rank;
+          const int owner = (tp.gather_cols || tp.gather_idx) ? -1 : (pm * kBM) / tp.rows_per_rank;
           const unsigned int need = tp.gather_cols ? kPiecesPerBlock * tp.n_ranks : kPiecesPerBlock;
           if (owner != tp.my_rank && !((ready_mask >> (pm & 63)) & 1ull)) {
             const unsigned long long t0 = globaltimer_ns();
@@ -310,6 +316,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           };
           if (!SCATTER) {
             store_chunk(C, ks * split_stride + static_cast<long long>(row) * ldc + col0);
+          } else if (tp.scatter_idx) {
+            const int dest = __ldg(tp.idx_rank + row);
+            store_chunk(tp.dst[dest], static_cast<long long>(__ldg(tp.idx_row + row)) * ldc + col0);
           } else if (tp.scatter_cols) {
             int sg = 0, base = 0;
             if (tp.seg_w[1] > 0 && col0 >= tp.seg_start[1]) { sg = 1; base = tp.seg_w[0]; }
@@ -338,8 +347,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (GATHER) {
     // ------------------------------ copy warps (remote A shards -> local full buffer) ---------------
     // Work is handed out by a ticket counter so that whichever CTAs are resident finish every piece.
-    const int bpr = tp.gather_cols ? tm.m_blocks : tp.rows_per_rank / kBM;  // m-blocks per source rank
-    const int total = (tp.gather_cols ? tp.n_ranks : tp.n_ranks - 1) * bpr * kPiecesPerBlock;
+    const int bpr = (tp.gather_cols || tp.gather_idx) ? tm.m_blocks : tp.rows_per_rank / kBM;  // m-blocks per source rank
+    const int total = (tp.gather_idx ? 1 : (tp.gather_cols ? tp.n_ranks : tp.n_ranks - 1)) * bpr * kPiecesPerBlock;
     const int vec_per_row = (tp.gather_cols ? tp.cols_per_rank : K) >> 3;   // 16-byte vectors per copied row
     constexpr int kRowsPerPiece = kBM / kPiecesPerBlock;
     unsigned int* ticket = tp.flags + tm.m_blocks;
@@ -353,6 +362,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint4* sp;
       uint4* dp;
       int ld_vec = static_cast<int>(tp.lda >> 3), sld_vec = ld_vec;
+      if (tp.gather_idx) {
+        // one table lookup per row: (rank, row) of the token routed to this expert slot
+        mb = bi;
+        row0 = mb * kBM + sub * kRowsPerPiece;
+        rows_here = max(0, min(kRowsPerPiece, M - row0));
+        sld_vec = static_cast<int>(tp.src_ld >> 3);
+        for (int rr = 0; rr < rows_here; ++rr) {
+          const int r = row0 + rr;
+          const int sr = __ldg(tp.idx_rank + r);
+          const uint4* srow = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(tp.src[sr]) +
+                                                             static_cast<long long>(__ldg(tp.idx_row + r)) * tp.src_ld);
+          uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tp.a_full) + static_cast<long long>(r) * tp.lda);
+          for (int base = 0; base < vec_per_row; base += 32 * 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int c = base + u * 32 + lane;
+              if (c < vec_per_row) v[u] = srow[c];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int c = base + u * 32 + lane;
+              if (c < vec_per_row) drow[c] = v[u];
+            }
+          }
+        }
+        fence_proxy_async_global();
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          atomicAdd(tp.flags + mb, 1u);
+        }
+        continue;
+      }
       if (!tp.gather_cols) {
         src_rank = (tp.my_rank + 1 + bi / bpr) % tp.n_ranks;
         mb = src_rank * bpr + bi % bpr;
@@ -626,6 +669,58 @@ int sb_gemm_sp(const void* A, const void* B, void* C, const void* bias, int M, i
     }
     if (bn == 256) return sb::launch_gemm_tp<256, false, true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, tp, st);
     return sb::launch_gemm_tp<128, false, true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, tp, st);
+  }
+  return SB_ERR_ARG;
+}
+
+
+// Expert GEMM with the token exchange inside the kernel (x @ W^T with W [N, K], or x @ W with W [K, N] when b_mn).
+//   mode 1 (dispatch): A row r is fetched from row idx_row[r] of peers[idx_rank[r]] (row stride src_ld) into the local
+//       buffer A while the GEMM runs; C is a plain local output.  flags: (M/128 + 2) uint32 of scratch.
+//   mode 2 (combine): A is local; C row r is stored to row idx_row[r] of peers[idx_rank[r]] (row stride ldc).
+int sb_gemm_ep(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+               int b_mn, int mode, void* const* peers, int n_ranks, int my_rank, const int* idx_rank, const int* idx_row,
+               long long src_ld, unsigned int* flags, int bn, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (K & 7) || !peers || !idx_rank || !idx_row) return SB_ERR_ARG;
+  if (n_ranks < 1 || n_ranks > sb::kTpMaxRanks || my_rank < 0 || my_rank >= n_ranks) return SB_ERR_ARG;
+  sb::TpArgs tp{};
+  tp.n_ranks = n_ranks;
+  tp.my_rank = my_rank;
+  tp.rows_per_rank = M;
+  tp.lda = lda;
+  tp.idx_rank = idx_rank;
+  tp.idx_row = idx_row;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn != 128 && bn != 256) bn = 128;
+  if (mode == 1) {
+    if (!flags || (src_ld & 7)) return SB_ERR_ARG;
+    tp.gather_idx = 1;
+    tp.src_ld = src_ld;
+    tp.a_full = const_cast<void*>(A);
+    tp.flags = flags;
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!peers[r] || (reinterpret_cast<uintptr_t>(peers[r]) & 15)) return SB_ERR_ARG;
+      tp.src[r] = peers[r];
+    }
+    if (b_mn) {
+      if (bn == 256) return sb::launch_gemm_tp<256, true, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+      return sb::launch_gemm_tp<128, true, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+    }
+    if (bn == 256) return sb::launch_gemm_tp<256, false, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+    return sb::launch_gemm_tp<128, false, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+  }
+  if (mode == 2) {
+    tp.scatter_idx = 1;
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!peers[r]) return SB_ERR_ARG;
+      tp.dst[r] = peers[r];
+    }
+    if (b_mn) {
+      if (bn == 256) return sb::launch_gemm_tp<256, true, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+      return sb::launch_gemm_tp<128, true, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+    }
+    if (bn == 256) return sb::launch_gemm_tp<256, false, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+    return sb::launch_gemm_tp<128, false, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
   }
   return SB_ERR_ARG;
 }

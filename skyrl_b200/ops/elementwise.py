@@ -204,6 +204,12 @@ def swiglu(gu: torch.Tensor) -> torch.Tensor:
     return _SwiGLUFn.apply(gu)
 
 
+def swiglu_backward(gu: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
+    """Gradient of ``swiglu`` w.r.t. ``gu`` (for hand-written backward passes)."""
+    ctx = type("_Ctx", (), {"saved_tensors": (gu,)})()
+    return _SwiGLUFn.backward(ctx, dout)
+
+
 # ----------------------------------------------------------------------------- split-K consumers (decode)
 def add_rmsnorm_partials_(x: torch.Tensor, partials: torch.Tensor, n_part: int, w: torch.Tensor, eps: float,
                           out: torch.Tensor | None = None) -> torch.Tensor:

@@ -136,6 +136,42 @@ def check_ulysses_model(env):
         assert rel(g, full.p(name).grad) < 2e-3, (name, rel(g, full.p(name).grad))
 
 
+def check_expert_parallel(env):
+    """Experts sharded over ranks == all experts on every rank (forward, input / router-weight / expert grads)."""
+    from skyrl_b200.models.moe import moe_ffn
+    from skyrl_b200.parallel.expert_parallel import moe_ffn_ep
+
+    W, r = env.world_size, env.rank
+    ep = tpm.TPGroup(None)
+    T, H, E, F, k = 24, 16, 4 * W, 8, 2
+    g = torch.Generator().manual_seed(7)
+    router = torch.randn(E, H, generator=g)
+    wgu, wd = torch.randn(E, 2 * F, H, generator=g) * 0.2, torch.randn(E, H, F, generator=g) * 0.2
+    hs = [torch.randn(T, H, generator=g) for _ in range(W)]
+    El = E // W
+    h = hs[r].clone().requires_grad_()
+    wgu_l = wgu[r * El : (r + 1) * El].clone().requires_grad_()
+    wd_l = wd[r * El : (r + 1) * El].clone().requires_grad_()
+    rt = router.clone().requires_grad_()
+    y = moe_ffn_ep(h, rt, wgu_l, wd_l, k, True, ep, E)
+    gy = torch.randn(T, H, generator=torch.Generator().manual_seed(100 + r))
+    y.backward(gy)
+    # reference: every rank's tokens through the unsharded layer
+    wgu_f, wd_f = wgu.clone().requires_grad_(), wd.clone().requires_grad_()
+    tot_gu, tot_d = torch.zeros_like(wgu), torch.zeros_like(wd)
+    for rr in range(W):
+        hr = hs[rr].clone().requires_grad_()
+        rtr = router.clone().requires_grad_()
+        yr = moe_ffn(hr, rtr, wgu_f, wd_f, k, True)
+        yr.backward(torch.randn(T, H, generator=torch.Generator().manual_seed(100 + rr)))
+        if rr == r:
+            assert rel(y, yr) < 1e-5, rel(y, yr)
+            assert rel(h.grad, hr.grad) < 1e-4, rel(h.grad, hr.grad)
+            assert rel(rt.grad, rtr.grad) < 1e-4, rel(rt.grad, rtr.grad)
+    assert rel(wgu_l.grad, wgu_f.grad[r * El : (r + 1) * El]) < 1e-4
+    assert rel(wd_l.grad, wd_f.grad[r * El : (r + 1) * El]) < 1e-4
+
+
 def main():
     env = pdist.init_distributed()
     assert env.world_size == 2 and env.device.type == "cpu"
@@ -143,6 +179,7 @@ def main():
     check_sharded_optimizer(env)
     check_tp_model(env)
     check_ulysses_model(env)
+    check_expert_parallel(env)
     dist.barrier()
     if env.rank == 0:
         print("CPU_CHECKS_OK", flush=True)

@@ -104,6 +104,39 @@ def main():
         dist.all_reduce(g)
         assert rel(g, fullm.p(name).grad) < 8e-2, (name, rel(g, fullm.p(name).grad))
 
+    # ---- expert-parallel MoE layer on the fused dispatch / combine GEMMs vs the unsharded layer
+    from skyrl_b200.models.moe import moe_ffn
+    from skyrl_b200.parallel.expert_parallel import moe_ffn_ep
+
+    Tm, Hm, Em, Fm, km = 192, 256, 4 * W, 128, 2
+    ge = torch.Generator().manual_seed(7)
+    router = (torch.randn(Em, Hm, generator=ge) * 0.5).to(torch.bfloat16)
+    wgu_f = (torch.randn(Em, 2 * Fm, Hm, generator=ge) * 0.05).to(torch.bfloat16)
+    wd_f = (torch.randn(Em, Hm, Fm, generator=ge) * 0.05).to(torch.bfloat16)
+    hs_all = [(torch.randn(Tm, Hm, generator=ge) * 0.5).to(torch.bfloat16) for _ in range(W)]
+    El = Em // W
+    he = hs_all[r].to(dev).requires_grad_()
+    wgu_l = wgu_f[r * El : (r + 1) * El].contiguous().to(dev).requires_grad_()
+    wd_l = wd_f[r * El : (r + 1) * El].contiguous().to(dev).requires_grad_()
+    rt = router.to(dev).requires_grad_()
+    ye = moe_ffn_ep(he, rt, wgu_l, wd_l, km, True, tp, Em)
+    gy = torch.randn(Tm, Hm, generator=torch.Generator().manual_seed(100 + r)).to(torch.bfloat16).to(dev)
+    ye.backward(gy)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    wgu_r, wd_r = wgu_f.to(dev).requires_grad_(), wd_f.to(dev).requires_grad_()
+    for rr in range(W):
+        hr = hs_all[rr].to(dev).requires_grad_()
+        rtr = router.to(dev).requires_grad_()
+        yr = moe_ffn(hr, rtr, wgu_r, wd_r, km, True)
+        yr.backward(torch.randn(Tm, Hm, generator=torch.Generator().manual_seed(100 + rr)).to(torch.bfloat16).to(dev))
+        if rr == r:
+            assert rel(ye, yr) < 3e-2, rel(ye, yr)
+            assert rel(he.grad, hr.grad) < 5e-2, rel(he.grad, hr.grad)
+            assert rel(rt.grad, rtr.grad) < 8e-2, rel(rt.grad, rtr.grad)
+    assert rel(wgu_l.grad, wgu_r.grad[r * El : (r + 1) * El]) < 5e-2
+    assert rel(wd_l.grad, wd_r.grad[r * El : (r + 1) * El]) < 5e-2
+
     # ---- timing: fused all-gather GEMM and GEMM reduce-scatter against NCCL + plain GEMM (device time, max over ranks)
     from skyrl_b200.ops import gemm
 

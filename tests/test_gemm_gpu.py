@@ -203,3 +203,53 @@ def test_gemm_column_gather_matches_head_to_seq_then_project():
         assert torch.equal(a_full, want_a)
         ref = want_a.float() @ Wo.float().t()
         assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
+
+
+def test_gemm_indexed_dispatch_and_combine():
+    """Expert GEMMs with token dispatch (indexed row gather from 'peer' buffers) and combine (indexed row scatter)."""
+    import ctypes
+
+    from skyrl_b200.ops import _lib
+    from skyrl_b200.parallel import expert_parallel as epm
+
+    torch.manual_seed(4)
+    n_ranks, T, H, F2, n = 3, 40, 256, 512, 150
+    hid = [(torch.randn(T, H, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(n_ranks)]
+    W1 = (torch.randn(F2, H, device="cuda") * 0.05).to(torch.bfloat16)
+    src_rank = torch.randint(0, n_ranks, (n,), device="cuda", dtype=torch.int32)
+    src_row = torch.randint(0, T, (n,), device="cuda", dtype=torch.int32)
+    a_full = torch.full((n, H), float("nan"), device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(n, F2, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    peers = (ctypes.c_void_p * n_ranks)(*[h.data_ptr() for h in hid])
+    lib = epm._k()
+    _lib.check(lib.sb_gemm_ep(a_full.data_ptr(), W1.data_ptr(), out.data_ptr(), n, F2, H, H, H, F2, 0, 1, peers, n_ranks, 1,
+                              src_rank.data_ptr(), src_row.data_ptr(), H, flags.data_ptr(), 0, _lib.stream_ptr()), "dispatch")
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    want_rows = torch.stack(hid)[src_rank.long(), src_row.long()]
+    assert torch.equal(a_full, want_rows)
+    ref = want_rows.float() @ W1.float().t()
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
+    # combine: rows go to (rank, slot) of zero-initialised buffers; slots are unique per destination
+    W2 = (torch.randn(H, F2, device="cuda") * 0.05).to(torch.bfloat16)
+    x = (torch.randn(n, F2, device="cuda") * 0.5).to(torch.bfloat16)
+    dst_rank = torch.randint(0, n_ranks, (n,), device="cuda", dtype=torch.int32)
+    dst_row = torch.empty(n, device="cuda", dtype=torch.int32)
+    for d in range(n_ranks):
+        sel = (dst_rank == d).nonzero(as_tuple=True)[0]
+        dst_row[sel] = torch.randperm(200, device="cuda")[: sel.numel()].to(torch.int32)
+    bufs = [torch.zeros(200, H, device="cuda", dtype=torch.bfloat16) for _ in range(n_ranks)]
+    pc = (ctypes.c_void_p * n_ranks)(*[b.data_ptr() for b in bufs])
+    _lib.check(lib.sb_gemm_ep(x.data_ptr(), W2.data_ptr(), None, n, H, F2, F2, F2, H, 0, 2, pc, n_ranks, 0,
+                              dst_rank.data_ptr(), dst_row.data_ptr(), 0, None, 0, _lib.stream_ptr()), "combine")
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    y = x.float() @ W2.float().t()
+    for d in range(n_ranks):
+        sel = (dst_rank == d).nonzero(as_tuple=True)[0]
+        got = bufs[d][dst_row[sel].long()].float()
+        assert ((got - y[sel]).norm() / y[sel].norm()).item() < 1e-2
+        untouched = torch.ones(200, dtype=torch.bool, device="cuda")
+        untouched[dst_row[sel].long()] = False
+        assert bufs[d][untouched].abs().sum() == 0
