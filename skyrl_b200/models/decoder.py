@@ -55,6 +55,7 @@ class ModelArgs:
     norm_topk_prob: bool = True
     model_type: str = "qwen2"
     init_std: float = 0.02
+    ep_size: int = 1  # expert parallelism: this rank stores num_experts / ep_size experts (routing stays global)
 
     @property
     def q_dim(self) -> int:
@@ -115,6 +116,9 @@ PRESETS: Dict[str, ModelArgs] = {
     "tiny-qwen2-tp": ModelArgs(vocab_size=2048, hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
                                intermediate_size=1024, rope_theta=1e4, attention_bias=True, tie_word_embeddings=True,
                                model_type="qwen2"),
+    "tiny-moe": ModelArgs(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=2, num_kv_heads=1, head_dim=128,
+                          intermediate_size=512, rope_theta=1e4, num_experts=8, num_experts_per_tok=2,
+                          moe_intermediate_size=128, model_type="qwen3_moe", qk_norm=True),
     "qwen2.5-0.5b": ModelArgs(vocab_size=151936, hidden_size=896, num_layers=24, num_heads=14, num_kv_heads=2,
                               head_dim=64, intermediate_size=4864, rope_theta=1e6, attention_bias=True,
                               tie_word_embeddings=True, model_type="qwen2"),
@@ -146,8 +150,9 @@ def _param_specs(a: ModelArgs, with_lm_head: bool = True, value_head: bool = Fal
         specs.append((p + "ln2", (a.hidden_size,)))
         if a.num_experts:
             specs.append((p + "router", (a.num_experts, a.hidden_size)))
-            specs.append((p + "experts_wgu", (a.num_experts, 2 * a.moe_intermediate_size, a.hidden_size)))
-            specs.append((p + "experts_wd", (a.num_experts, a.hidden_size, a.moe_intermediate_size)))
+            el = a.num_experts // max(1, a.ep_size)
+            specs.append((p + "experts_wgu", (el, 2 * a.moe_intermediate_size, a.hidden_size)))
+            specs.append((p + "experts_wd", (el, a.hidden_size, a.moe_intermediate_size)))
         else:
             specs.append((p + "wgu", (2 * a.intermediate_size, a.hidden_size)))
             specs.append((p + "wd", (a.hidden_size, a.intermediate_size)))
@@ -277,7 +282,12 @@ class CausalLM(nn.Module):
         att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen)
         o = gemm.linear(att, self.p(pre + "wo"))
         x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
-        if a.num_experts:
+        if a.num_experts and getattr(self, "ep", None) is not None:
+            from ..parallel.expert_parallel import moe_ffn_ep
+
+            d = moe_ffn_ep(h, self.p(pre + "router"), self.p(pre + "experts_wgu"), self.p(pre + "experts_wd"),
+                           a.num_experts_per_tok, a.norm_topk_prob, self.ep, a.num_experts, layer=i)
+        elif a.num_experts:
             from .moe import moe_ffn
 
             d = moe_ffn(h, self.p(pre + "router"), self.p(pre + "experts_wgu"), self.p(pre + "experts_wd"),

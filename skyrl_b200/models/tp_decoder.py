@@ -252,3 +252,61 @@ class UlyssesCausalLM(CausalLM):
 
     def reduce_replicated_grads(self) -> None:  # the data-parallel reduction over all ranks already sums them
         return
+
+
+EXPERT_LEAVES = ("experts_wgu", "experts_wd")
+
+
+class EPCausalLM(CausalLM):
+    """MoE model whose experts are sharded over the ``ep`` group; everything else is replicated and every rank works
+    on its own tokens (data parallel).  Expert gradients are complete on the rank that owns the expert; gradients of
+    the replicated parameters are partial over tokens and are summed by ``reduce_replicated_grads``."""
+
+    def __init__(self, full_args: ModelArgs, ep: tpm.TPGroup, device="cpu", dtype=torch.bfloat16, seed: Optional[int] = 0,
+                 flat_buffer: Optional[torch.Tensor] = None):
+        if not full_args.num_experts or full_args.num_experts % ep.size:
+            raise ValueError(f"num_experts={full_args.num_experts} must be a positive multiple of ep={ep.size}")
+        self.full_args = full_args
+        self.tp = ep
+        super().__init__(dataclasses.replace(full_args, ep_size=ep.size), device=device, dtype=dtype, flat_buffer=flat_buffer,
+                         seed=None)
+        self.ep = ep
+        if seed is not None:
+            self.load_from_full(CausalLM(full_args, device="cpu", dtype=torch.float32, seed=seed))
+
+    def _shard(self, name: str, full: torch.Tensor) -> torch.Tensor:
+        if name.split(".")[-1] in EXPERT_LEAVES:
+            el = self.full_args.num_experts // self.ep.size
+            return full[self.ep.rank * el : (self.ep.rank + 1) * el]
+        return full
+
+    @torch.no_grad()
+    def load_from_full(self, full: CausalLM) -> None:
+        for name, prm in self.named_flat_views():
+            prm.copy_(self._shard(name, full.p(name).detach()).to(prm.dtype))
+
+    @torch.no_grad()
+    def gather_full_state(self) -> Dict[str, torch.Tensor]:
+        out = {}
+        for name, prm in self.named_flat_views():
+            if name.split(".")[-1] in EXPERT_LEAVES and self.ep.size > 1:
+                parts = [torch.empty_like(prm) for _ in range(self.ep.size)]
+                dist.all_gather(parts, prm.detach().contiguous(), group=self.ep.group)
+                out[name] = torch.cat(parts, 0)
+            else:
+                out[name] = prm.detach()
+        return out
+
+    def replicated_ranges(self) -> List[Tuple[int, int]]:
+        return [(o, o + n) for name, (o, n) in self.offsets.items() if name.split(".")[-1] not in EXPERT_LEAVES]
+
+    def reduce_replicated_grads(self) -> None:
+        if self.ep.size == 1:
+            return
+        for name, prm in self.named_flat_views():
+            if name.split(".")[-1] not in EXPERT_LEAVES:
+                g = getattr(prm, "main_grad", None)
+                if g is None:
+                    g = prm.grad
+                if g is not None:
+                    dist.all_reduce(g, group=self.ep.group)

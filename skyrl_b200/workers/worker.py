@@ -121,6 +121,7 @@ class ModelWorker:
         dtype = torch.bfloat16 if (cfg.bf16 and dev.type == "cuda") else torch.float32
         self.params_symm = self.grads_symm = None
         self.mesh = None
+        self.expert_parallel = self.sequence_parallel = False
         tp_size = self._tp_size_from_cfg(cfg)
         if tp_size > 1 and model is None:
             # Megatron-style strategy: tensor-parallel shards inside groups of consecutive ranks, data parallel across
@@ -141,6 +142,26 @@ class ModelWorker:
             model.load_from_full(full)
             del full
             peer_ctx = None  # the flat-buffer peer optimizer spans the whole world; TP uses the DP group over NCCL
+        ep_size = self._ep_size_from_cfg(cfg) if (model is None and tp_size == 1) else 1
+        self.expert_parallel = ep_size > 1
+        if self.expert_parallel:
+            # experts sharded over groups of consecutive ranks; tokens stay data parallel on every rank
+            from ..models.decoder import resolve_model_args
+            from ..models.tp_decoder import EPCausalLM
+            from ..parallel.dist import build_mesh
+            from ..parallel.peer import PeerContext
+            from ..parallel.tensor_parallel import TPGroup
+
+            if value_head:
+                raise NotImplementedError("the critic runs without expert parallelism")
+            self.mesh = build_mesh(ep_size, self.env)
+            ep_peer = PeerContext(dev, group=self.mesh.tp_group) if dev.type == "cuda" else None
+            self.tp = TPGroup(ep_peer, self.mesh.tp_group)
+            model = EPCausalLM(resolve_model_args(model_path), self.tp, device=dev, dtype=dtype, seed=None)
+            full = build_model(model_path, device="cpu", dtype=torch.float32, seed=seed)
+            model.load_from_full(full)
+            del full
+            peer_ctx = None
         use_peer = peer_ctx is not None and trainable and self.env.world_size > 1 and dev.type == "cuda"
         sp_size = self._sp_size_from_cfg(cfg) if model is None and tp_size == 1 else 1
         self.sequence_parallel = sp_size > 1
@@ -204,7 +225,10 @@ class ModelWorker:
             if self.mesh is not None:
                 from ..models.tp_decoder import REPLICATED_LEAVES
 
-                dups = [(o, o + n) for name, (o, n) in model.offsets.items() if name.split(".")[-1] in REPLICATED_LEAVES]
+                if self.expert_parallel:
+                    dups = model.replicated_ranges()
+                else:
+                    dups = [(o, o + n) for name, (o, n) in model.offsets.items() if name.split(".")[-1] in REPLICATED_LEAVES]
                 extra = dict(group=self.mesh.dp_group, transport="nccl", norm_group=self.mesh.tp_group, dup_ranges=dups,
                              count_dups=self.mesh.tp_rank == 0)
             self.optimizer = ShardedAdamW(model.flat_params, flat_grad, lr=ocfg.lr, betas=tuple(ocfg.adam_betas),
@@ -270,6 +294,12 @@ class ModelWorker:
             self.full_model_copy(into=ec)
 
     @staticmethod
+    def _ep_size_from_cfg(cfg) -> int:
+        if getattr(cfg, "strategy", "fsdp") != "megatron":
+            return 1
+        return int(getattr(cfg.policy.megatron_config, "expert_model_parallel_size", 1) or 1)
+
+    @staticmethod
     def _tp_size_from_cfg(cfg) -> int:
         if getattr(cfg, "strategy", "fsdp") != "megatron":
             return 1
@@ -287,8 +317,9 @@ class ModelWorker:
 
     @property
     def tp_size(self) -> int:
-        """Ranks that jointly process one data shard (tensor- or sequence-parallel group size)."""
-        return self.mesh.tp_size if self.mesh is not None else 1
+        """Ranks that jointly process one data shard (tensor- or sequence-parallel group size; expert-parallel ranks
+        each keep their own data)."""
+        return self.mesh.tp_size if (self.mesh is not None and not getattr(self, "expert_parallel", False)) else 1
 
     def _pred_logprobs(self, pv: PackedView, temp: float, with_entropy: bool = False):
         """Log-probs (and entropies) of the packed batch's prediction positions, ``[n_pred]`` each."""
@@ -296,6 +327,23 @@ class ModelWorker:
             h = self._hidden(pv)
             return self.model.token_logprobs(h[pv.pred_index], pv.targets, temp, with_entropy=with_entropy)
         from ..models.tp_decoder import pad_packed_for_tp
+
+        if self.expert_parallel:
+            # every rank routes its own tokens, but the routing tables are exchanged as equal-sized blocks: pad this
+            # rank's packed batch to the longest one in the expert-parallel group
+            T = pv.ids.numel()
+            tmax = torch.tensor([T], device=pv.ids.device, dtype=torch.int64)
+            if dist.is_initialized() and self.mesh.tp_size > 1:
+                dist.all_reduce(tmax, op=dist.ReduceOp.MAX, group=self.mesh.tp_group)
+            target = (int(tmax) + 7) // 8 * 8
+            ids, pos, cu = pv.ids, pv.positions, pv.cu_seqlens
+            if target > T:
+                n = target - T
+                ids = torch.cat([ids, torch.zeros(n, dtype=ids.dtype, device=ids.device)])
+                pos = torch.cat([pos, torch.arange(n, dtype=pos.dtype, device=pos.device)])
+                cu = torch.cat([cu, torch.tensor([target], dtype=cu.dtype, device=cu.device)])
+            h = self.model(ids, pos, cu, max(pv.max_seqlen, target - T))
+            return self.model.token_logprobs(h[pv.pred_index], pv.targets, temp, with_entropy=with_entropy)
 
         ids, pos, cu, T = pad_packed_for_tp(pv.ids, pv.positions, pv.cu_seqlens, self.mesh.tp_size)
         h = self.model(ids, pos, cu, max(pv.max_seqlen, ids.numel() - T))
@@ -508,7 +556,8 @@ class PolicyWorker(ModelWorker):
         B, R = batch["response_mask"].shape
         groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens())
         n_mb = sync_num_microbatches(len(groups), self.env)
-        world = self.mesh.dp_size if self.mesh is not None else self.env.world_size  # number of distinct data shards
+        # number of distinct data shards (expert-parallel ranks each hold their own)
+        world = self.mesh.dp_size if (self.mesh is not None and not self.expert_parallel) else self.env.world_size
         temp = float(algo.temperature or 1.0)
         use_kl = bool(algo.use_kl_loss) and batch.get("base_action_log_probs") is not None and loss_name != "cross_entropy"
         use_ent = bool(algo.use_entropy_loss) and loss_name != "cross_entropy"
