@@ -164,6 +164,124 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 }
 
 // ---------------------------------------------------------------------------
+// Warp-per-row variants (H = NV * 256, NV <= 8): no block-level synchronisation in the row loop, eight rows in flight
+// per CTA.  The row statistics are warp shuffles; the weight gradient is kept per lane and reduced once per CTA.
+// ---------------------------------------------------------------------------
+constexpr int kWarpNormThreads = 256;
+
+template <int NV>
+__global__ void __launch_bounds__(kWarpNormThreads)
+rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ x_out,
+                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int T, float eps) {
+  constexpr int H = NV * 256;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4 wq[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) wq[i] = reinterpret_cast<const uint4*>(w)[i * 32 + lane];
+  for (int row = blockIdx.x * 8 + warp; row < T; row += gridDim.x * 8) {
+    const size_t off = static_cast<size_t>(row) * H;
+    float vals[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = i * 32 + lane;
+      bf16x8_to_float(reinterpret_cast<const uint4*>(x + off)[v], vals[i]);
+      if (delta) {
+        float d[8];
+        bf16x8_to_float(reinterpret_cast<const uint4*>(delta + off)[v], d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] += d[j];
+        const uint4 rounded = float_to_bf16x8(vals[i]);  // the residual stream is stored in bf16: use those values
+        if (x_out) reinterpret_cast<uint4*>(x_out + off)[v] = rounded;
+        bf16x8_to_float(rounded, vals[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+    const float rs = rsqrtf(warp_sum(ss) / static_cast<float>(H) + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rs;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float wv[8], o[8];
+      bf16x8_to_float(wq[i], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rs * wv[j];
+      reinterpret_cast<uint4*>(y + off)[i * 32 + lane] = float_to_bf16x8(o);
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kWarpNormThreads)
+rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                        int T) {
+  constexpr int H = NV * 256;
+  extern __shared__ float sred[];  // [8 warps][H] for the final weight-gradient reduction
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4 wq[NV];
+  float dw_acc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    wq[i] = reinterpret_cast<const uint4*>(w)[i * 32 + lane];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw_acc[i][j] = 0.f;
+  }
+  for (int row = blockIdx.x * 8 + warp; row < T; row += gridDim.x * 8) {
+    const size_t off = static_cast<size_t>(row) * H;
+    const float rs = rstd[row];
+    uint4 dq[NV], xq[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      dq[i] = reinterpret_cast<const uint4*>(dy + off)[i * 32 + lane];
+      xq[i] = reinterpret_cast<const uint4*>(x + off)[i * 32 + lane];
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float d[8], xh[8], wv[8];
+      bf16x8_to_float(dq[i], d);
+      bf16x8_to_float(xq[i], xh);
+      bf16x8_to_float(wq[i], wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[j] *= rs;
+        dw_acc[i][j] += d[j] * xh[j];
+        dot += d[j] * wv[j] * xh[j];
+      }
+    }
+    const float mean = warp_sum(dot) / static_cast<float>(H);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float d[8], xh[8], wv[8], o[8];
+      float r[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      bf16x8_to_float(dq[i], d);
+      bf16x8_to_float(xq[i], xh);
+      bf16x8_to_float(wq[i], wv);
+      if (dres) bf16x8_to_float(reinterpret_cast<const uint4*>(dres + off)[i * 32 + lane], r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = r[j] + rs * (d[j] * wv[j] - xh[j] * rs * mean);
+      reinterpret_cast<uint4*>(dx + off)[i * 32 + lane] = float_to_bf16x8(o);
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sred[warp * H + (i * 32 + lane) * 8 + j] = dw_acc[i][j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < H; c += kWarpNormThreads) {
+      float t = 0.f;
+#pragma unroll
+      for (int wq_ = 0; wq_ < 8; ++wq_) t += sred[wq_ * H + c];
+      atomicAdd(dw + c, t);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // RoPE (rotate-half convention: pairs (i, i + D/2)) in place on the q and k heads
 // of a packed [T, (nq + 2 nkv) * D] buffer. cos_sin is a [max_pos, D] fp32 table:
 // cos in [:, :D/2], sin in [:, D/2:].  sign = +1 forward, -1 inverse (backward).
@@ -344,6 +462,22 @@ extern "C" {
 int sb_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_out, void* y, float* rstd, int T, int H,
                    float eps, void* stream) {
   if (H % 8 != 0 || H > sb::kNormThreads * 8 * sb::kNormMaxVec || T <= 0) return SB_ERR_ARG;
+  if (H % 256 == 0 && H <= 2048) {
+    const int blocks = (T + 7) / 8;
+    const int wgrid = blocks < sb::sm_count() * 8 ? blocks : sb::sm_count() * 8;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define SB_NORM_FWD(NVV)                                                                                              \
+  case NVV:                                                                                                           \
+    sb::rmsnorm_fwd_warp_kernel<NVV><<<wgrid, sb::kWarpNormThreads, 0, st>>>(                                         \
+        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(delta),                     \
+        reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(x_out),                           \
+        reinterpret_cast<__nv_bfloat16*>(y), rstd, T, eps);                                                           \
+    return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+    switch (H / 256) {
+      SB_NORM_FWD(1) SB_NORM_FWD(2) SB_NORM_FWD(3) SB_NORM_FWD(4) SB_NORM_FWD(5) SB_NORM_FWD(6) SB_NORM_FWD(7) SB_NORM_FWD(8)
+    }
+#undef SB_NORM_FWD
+  }
   const int grid = T < sb::sm_count() * 8 ? T : sb::sm_count() * 8;
   sb::rmsnorm_fwd_kernel<<<grid, sb::kNormThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(delta),
@@ -355,6 +489,29 @@ int sb_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_out,
 int sb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
                    float* dw, int T, int H, void* stream) {
   if (H % 8 != 0 || H > sb::kNormThreads * 8 * sb::kNormMaxVec || T <= 0) return SB_ERR_ARG;
+  if (H % 256 == 0 && H <= 2048) {
+    const int blocks = (T + 7) / 8;
+    const int wgrid = blocks < sb::sm_count() * 2 ? blocks : sb::sm_count() * 2;
+    const int smem = 8 * H * static_cast<int>(sizeof(float));
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define SB_NORM_BWD(NVV)                                                                                              \
+  case NVV: {                                                                                                         \
+    static bool attr = false;                                                                                         \
+    if (!attr) {                                                                                                      \
+      cudaFuncSetAttribute(sb::rmsnorm_bwd_warp_kernel<NVV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2048 * 4); \
+      attr = true;                                                                                                    \
+    }                                                                                                                 \
+    sb::rmsnorm_bwd_warp_kernel<NVV><<<wgrid, sb::kWarpNormThreads, smem, st>>>(                                      \
+        reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),                        \
+        reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<const __nv_bfloat16*>(dres),                \
+        reinterpret_cast<__nv_bfloat16*>(dx), dw, T);                                                                 \
+    return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;                                                   \
+  }
+    switch (H / 256) {
+      SB_NORM_BWD(1) SB_NORM_BWD(2) SB_NORM_BWD(3) SB_NORM_BWD(4) SB_NORM_BWD(5) SB_NORM_BWD(6) SB_NORM_BWD(7) SB_NORM_BWD(8)
+    }
+#undef SB_NORM_BWD
+  }
   const int grid = T < sb::sm_count() * 2 ? T : sb::sm_count() * 2;
   sb::rmsnorm_bwd_kernel<<<grid, sb::kNormThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),

@@ -13,7 +13,7 @@ def rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
-@pytest.mark.parametrize("T,H", [(7, 256), (1000, 1536), (333, 3584)])
+@pytest.mark.parametrize("T,H", [(7, 256), (1000, 1536), (333, 3584), (4099, 2048), (65, 768), (513, 264)])
 def test_add_rmsnorm_fwd_bwd(T, H):
     torch.manual_seed(0)
     x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
