@@ -172,6 +172,55 @@ def check_expert_parallel(env):
     assert rel(wd_l.grad, wd_f.grad[r * El : (r + 1) * El]) < 1e-4
 
 
+def check_pipeline(env):
+    """Two pipeline stages reproduce the single-model loss and gradients over several micro-batches."""
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+    from skyrl_b200.parallel.pipeline import PipelineStage, broadcast_from_last_stage, pipeline_forward_backward
+
+    W, r = env.world_size, env.rank
+    a = PRESETS["tiny-llama"]
+    full = CausalLM(a, device="cpu", dtype=torch.float32, seed=9)
+    stage = PipelineStage(a, r, W, device="cpu", dtype=torch.float32, seed=9)
+    g = torch.Generator().manual_seed(4)
+    mbs = []
+    for lens in ([11, 20], [7], [16, 5, 9]):
+        ids = torch.randint(4, a.vocab_size, (sum(lens),), generator=g).int()
+        pos = torch.cat([torch.arange(n) for n in lens]).int()
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0))).int()
+        mbs.append({"ids": ids, "pos": pos, "cu": cu, "max_seqlen": 32, "tgt": torch.roll(ids.long(), -1)})
+
+    def loss_fn(model):
+        return lambda h, mb: -model.token_logprobs(h, mb["tgt"])[0].sum()
+
+    res = pipeline_forward_backward(stage, mbs, loss_fn(stage))
+    ref_losses = []
+    for mb in mbs:
+        l = loss_fn(full)(full(mb["ids"], mb["pos"], mb["cu"], 32), mb)
+        l.backward()
+        ref_losses.append(l.detach())
+    if stage.is_last:
+        for a_, b_ in zip(res, ref_losses):
+            assert abs(float(a_) - float(b_)) < 1e-3 * abs(float(b_)), (float(a_), float(b_))
+    tot = broadcast_from_last_stage(torch.stack(res) if stage.is_last else None, (3,), torch.float32, stage)
+    assert torch.allclose(tot, torch.stack(ref_losses), rtol=1e-3)
+    for name, prm in stage.named_flat_views():
+        fn = stage._full_name(name)
+        ref = full.p(fn).grad
+        if name == "embed" and not (stage.is_first or (stage.is_last and a.tie_word_embeddings)):
+            assert prm.grad is None or prm.grad.abs().sum() == 0
+            continue
+        if name in ("final_norm", "lm_head") and not stage.is_last:
+            assert prm.grad is None or prm.grad.abs().sum() == 0
+            continue
+        if name == "embed" and not a.tie_word_embeddings and stage.is_last and not stage.is_first:
+            continue
+        assert prm.grad is not None, name
+        assert rel(prm.grad, ref) < 2e-3, (name, rel(prm.grad, ref))
+    out = pipeline_forward_backward(stage, mbs[:1], None, forward_only=True)
+    if stage.is_last:
+        assert rel(out[0], full(mbs[0]["ids"], mbs[0]["pos"], mbs[0]["cu"], 32).detach()) < 1e-4
+
+
 def main():
     env = pdist.init_distributed()
     assert env.world_size == 2 and env.device.type == "cpu"
@@ -180,6 +229,7 @@ def main():
     check_tp_model(env)
     check_ulysses_model(env)
     check_expert_parallel(env)
+    check_pipeline(env)
     dist.barrier()
     if env.rank == 0:
         print("CPU_CHECKS_OK", flush=True)
