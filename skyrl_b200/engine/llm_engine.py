@@ -416,6 +416,10 @@ class LLMEngine:
         dev = self.device
         ids, pos, slot_list, cu = [], [], [], [0]
         rows = []
+        full_slots: List[int] = []  # cache slot of every token (cached prefix + new), per sequence, for the prefix path
+        new_rows_in_full: List[int] = []
+        cu_full = [0]
+        any_cached = False
         for req in reqs:
             toks = req.prompt + req.partial_tokens
             L = len(toks)
@@ -423,15 +427,25 @@ class LLMEngine:
             nb = self.rt.sbrt_sched_seq_blocks(self.sched, req.sid, bt.ctypes.data, self.max_blocks_per_seq)
             assert nb >= (L + bs - 1) // bs, "scheduler did not reserve enough blocks"
             req.cached = self.rt.sbrt_sched_seq_cached(self.sched, req.sid)
+            # tokens whose key/value blocks are already in the cache are not recomputed (at least one token is)
+            c = min(int(req.cached), L - 1) if self.cfg.enable_prefix_caching else 0
+            if req.params.prompt_logprobs:
+                c = 0  # prompt log-probs need every position's hidden state
+            c = (c // bs) * bs
+            any_cached = any_cached or c > 0
             slot = self._free_slots.pop()
             req.slot = slot
             self._slot_req[slot] = req
             rows.append(slot)
             self.block_tables[slot].copy_(_lib.to_device(torch.from_numpy(bt), dev))
-            ids.extend(toks)
-            pos.extend(range(L))
-            slot_list.extend((bt[np.arange(L) // bs] * bs + np.arange(L) % bs).tolist())
-            cu.append(cu[-1] + L)
+            all_slots = (bt[np.arange(L) // bs] * bs + np.arange(L) % bs).tolist()
+            ids.extend(toks[c:])
+            pos.extend(range(c, L))
+            slot_list.extend(all_slots[c:])
+            cu.append(cu[-1] + (L - c))
+            new_rows_in_full.extend(range(cu_full[-1] + c, cu_full[-1] + L))
+            full_slots.extend(all_slots)
+            cu_full.append(cu_full[-1] + L)
         t_ids = _lib.to_device(torch.tensor(ids, dtype=torch.int32), dev)
         t_pos = _lib.to_device(torch.tensor(pos, dtype=torch.int32), dev)
         t_slots = _lib.to_device(torch.tensor(slot_list, dtype=torch.int32), dev)
@@ -442,7 +456,26 @@ class LLMEngine:
                                     a.num_kv_heads, a.head_dim)
 
         max_len = max(len(r.prompt) + len(r.partial_tokens) for r in reqs)
-        h = m(t_ids, t_pos, t_cu, max_len, kv_sink=sink)
+        attn_fn = None
+        if any_cached:
+            # Prefix path: the projections and the MLP run on the new tokens only; attention runs over rows that hold
+            # the cached prefix's keys/values (gathered from the paged cache) followed by the new tokens' q, k, v.
+            t_full_slots = _lib.to_device(torch.tensor(full_slots, dtype=torch.long), dev)
+            t_new_rows = _lib.to_device(torch.tensor(new_rows_in_full, dtype=torch.long), dev)
+            t_cu_full = _lib.to_device(torch.tensor(cu_full, dtype=torch.int32), dev)
+            qd, kvd = a.num_heads * a.head_dim, a.num_kv_heads * a.head_dim
+            Tf = len(full_slots)
+
+            def attn_fn(layer, qkv):  # noqa: F811 - runs after sink() has written the new keys/values
+                full = torch.zeros((Tf, qd + 2 * kvd), device=dev, dtype=qkv.dtype)
+                full[:, qd : qd + kvd] = self.k_cache[layer].view(-1, kvd)[t_full_slots]
+                full[:, qd + kvd :] = self.v_cache[layer].view(-1, kvd)[t_full_slots]
+                full[t_new_rows, :qd] = qkv[:, :qd]
+                att = attn_ops.attn_varlen(full, t_cu_full, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_len)
+                return att[t_new_rows].contiguous()
+
+            self.stats["prefix_cached_tokens"] = self.stats.get("prefix_cached_tokens", 0) + (Tf - len(ids))
+        h = m(t_ids, t_pos, t_cu, max_len, kv_sink=sink, attn_fn=attn_fn)
         last = h[(t_cu[1:] - 1).long()]
         if any(r.params.prompt_logprobs for r in reqs):
             tgt = torch.roll(t_ids, -1)

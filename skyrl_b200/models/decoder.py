@@ -269,7 +269,7 @@ class CausalLM(nn.Module):
         k = ew.rmsnorm(k, self.p(f"layers.{i}.k_norm"), a.rms_norm_eps).reshape(T, a.kv_dim)
         return torch.cat([q, k, qkv[:, a.q_dim + a.kv_dim :]], dim=-1)
 
-    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None):
+    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None, attn_fn=None):
         a = self.args
         pre = f"layers.{i}."
         x, h = ew.add_rmsnorm(x, delta, self.p(pre + "ln1"), a.rms_norm_eps)
@@ -279,7 +279,10 @@ class CausalLM(nn.Module):
         qkv = ew.rope(qkv, pos, self.rope_table(qkv.device), a.num_heads + a.num_kv_heads, a.head_dim)
         if kv_sink is not None:
             kv_sink(i, qkv)
-        att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen)
+        if attn_fn is not None:  # the caller supplies attention (e.g. over cached key/value prefixes)
+            att = attn_fn(i, qkv)
+        else:
+            att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen)
         o = gemm.linear(att, self.p(pre + "wo"))
         x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
         if a.num_experts and getattr(self, "ep", None) is not None:
@@ -298,7 +301,7 @@ class CausalLM(nn.Module):
         return x, d
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, cu_seqlens: torch.Tensor,
-                max_seqlen: int = 0, kv_sink=None) -> torch.Tensor:
+                max_seqlen: int = 0, kv_sink=None, attn_fn=None) -> torch.Tensor:
         """``input_ids`` / ``positions``: ``[T]``; ``cu_seqlens``: int32 ``[B+1]``. Returns hidden ``[T, H]``."""
         x = _EmbeddingFn.apply(input_ids, self.p("embed"))
         delta = None
@@ -309,7 +312,7 @@ class CausalLM(nn.Module):
                 x, delta = torch.utils.checkpoint.checkpoint(self._layer, i, x, delta, positions, cu_seqlens,
                                                              max_seqlen, use_reentrant=False)
             else:
-                x, delta = self._layer(i, x, delta, positions, cu_seqlens, max_seqlen, kv_sink)
+                x, delta = self._layer(i, x, delta, positions, cu_seqlens, max_seqlen, kv_sink, attn_fn)
         _, h = ew.add_rmsnorm(x, delta, self.p("final_norm"), self.args.rms_norm_eps)
         return h
 

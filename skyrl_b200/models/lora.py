@@ -138,7 +138,7 @@ class LoRACausalLM(CausalLM):
             y = y + self.scale * z
         return y
 
-    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None):
+    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None, attn_fn=None):
         a = self.args
         pre = f"layers.{i}."
         x, h = ew.add_rmsnorm(x, delta, self.p(pre + "ln1"), a.rms_norm_eps)
@@ -148,7 +148,10 @@ class LoRACausalLM(CausalLM):
         qkv = ew.rope(qkv, pos, self.rope_table(qkv.device), a.num_heads + a.num_kv_heads, a.head_dim)
         if kv_sink is not None:
             kv_sink(i, qkv)
-        att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen)
+        if attn_fn is not None:
+            att = attn_fn(i, qkv)
+        else:
+            att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen)
         o = self._lin(i, "o", att)
         x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
         d = self._lin(i, "down", ew.swiglu(self._lin(i, "gate_up", h)))

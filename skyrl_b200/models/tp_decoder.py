@@ -158,7 +158,7 @@ class TPCausalLM(CausalLM):
                     dist.all_reduce(g, group=self.tp.group)
 
     # ------------------------------------------------------------------ forward
-    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None):
+    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None, attn_fn=None):
         a, tp = self.args, self.tp
         pre = f"layers.{i}."
         x, h = ew.add_rmsnorm(x, delta, self.p(pre + "ln1"), a.rms_norm_eps)  # [T/tp, H]
@@ -219,7 +219,7 @@ class UlyssesCausalLM(CausalLM):
         self.tp = sp
         super().__init__(args, **kw)
 
-    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None):
+    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None, attn_fn=None):
         from ..parallel import ulysses
 
         a, sp = self.args, self.tp

@@ -106,3 +106,32 @@ def test_top_k_one_equals_greedy_and_requeue_after_kv_reset():
     while eng.has_unfinished():
         outs += eng.step()
     assert outs[0].token_ids == ref_t and len(outs[0].logprobs) == 8
+
+
+def test_prefix_cached_prefill_skips_cached_tokens_and_matches_full_prefill():
+    """A second request that shares a prompt prefix reuses the cached key/value blocks: only the new tokens go through
+    the projections, and the continuation is identical to a full prefill."""
+    import torch
+
+    from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine, SamplingParams
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+
+    m = CausalLM(PRESETS["tiny-llama"], device="cpu", dtype=torch.float32, seed=3)
+    g = torch.Generator().manual_seed(0)
+    shared = torch.randint(4, 1024, (70,), generator=g).tolist()
+    p1 = shared + torch.randint(4, 1024, (9,), generator=g).tolist()
+    p2 = shared + torch.randint(4, 1024, (13,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    outs = {}
+    for caching in (False, True):
+        eng = LLMEngine(m, EngineConfig(block_size=16, max_num_seqs=4, max_model_len=128, enforce_eager=True, num_blocks=64,
+                                        enable_prefix_caching=caching))
+        a = eng.generate([p1], sp)[0]
+        b = eng.generate([p2], sp)[0]
+        c = eng.generate([p1], sp)[0]
+        outs[caching] = (a.token_ids, b.token_ids, c.token_ids, eng.stats.get("prefix_cached_tokens", 0),
+                         eng.stats["prefill_tokens"])
+    assert outs[True][:3] == outs[False][:3]
+    assert outs[False][3] == 0
+    assert outs[True][3] >= 64 + 64  # p2 reuses 4 shared blocks, the repeat of p1 reuses 4 (79 tokens -> 64 cached)
+    assert outs[True][4] == outs[False][4] - outs[True][3]
