@@ -408,6 +408,9 @@ class PPOTrainer:
             total = min(total, t.max_training_steps)
         for cb in self.callbacks:
             cb.on_train_begin(self)
+        self.policy.start_profile()
+        if getattr(t.policy, "record_memory", False):
+            self.policy.record_memory_history(True)
         done = False
         while self.train_iter.epoch < t.epochs and not done:
             for global_batch in self.train_iter:
@@ -415,6 +418,7 @@ class PPOTrainer:
                 if t.eval_interval > 0 and self.eval_dataset is not None and self.global_step % t.eval_interval == 0:
                     metrics.update(await self.eval_async())
                 self._log(metrics, self.global_step)
+                self.policy.profile_step()  # one profiler step per RL step
                 for cb in self.callbacks:
                     cb.on_step_end(self, metrics)
                 if t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0:
@@ -428,6 +432,11 @@ class PPOTrainer:
                 self.update_ref_with_policy()
         if t.ckpt_interval > 0:
             self.save_checkpoints()
+        summary = self.policy.stop_profile()
+        if summary and self.env.is_main:
+            print(summary)
+        if getattr(t.policy, "record_memory", False):
+            self.policy.dump_memory_snapshot(os.path.join(t.log_path, "memory_snapshots"), f"step{self.global_step}")
         for cb in self.callbacks:
             cb.on_train_end(self)
 

@@ -257,6 +257,43 @@ class ModelWorker:
     def _hidden(self, pv: PackedView) -> torch.Tensor:
         return self.model(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen)
 
+    # ------------------------------------------------------------------ profiling verbs (reference: worker.py:361-457)
+    def start_profile(self) -> None:
+        from ..utils.profiler import Profiler
+
+        node = {"policy": self.cfg.policy, "critic": self.cfg.critic, "ref": self.cfg.ref}.get(self.role, self.cfg.policy)
+        pcfg = getattr(node, "torch_profiler_config", None)
+        if pcfg is None or not pcfg.enable:
+            self._profiler = None
+            return
+        self._profiler = Profiler(pcfg, self.env.rank)
+        self._profiler.start()
+
+    def profile_step(self) -> None:
+        p = getattr(self, "_profiler", None)
+        if p is not None:
+            p.step()
+
+    def stop_profile(self) -> Optional[str]:
+        p = getattr(self, "_profiler", None)
+        if p is None:
+            return None
+        p.stop()
+        return p.kernel_summary()
+
+    def record_memory_history(self, enabled: bool = True) -> None:
+        if torch.cuda.is_available():
+            torch.cuda.memory._record_memory_history(max_entries=100000 if enabled else None)
+
+    def dump_memory_snapshot(self, out_dir: str, tag: str = "") -> Optional[str]:
+        """Pickled allocator snapshot of this rank (viewable with pytorch.org/memory_viz)."""
+        if not torch.cuda.is_available():
+            return None
+        os.makedirs(out_dir, exist_ok=True)
+        path = os.path.join(out_dir, f"memory_{self.role}_rank{self.env.rank}{('_' + tag) if tag else ''}.pickle")
+        torch.cuda.memory._dump_snapshot(path)
+        return path
+
     def _sp_size_from_cfg(self, cfg) -> int:
         if getattr(cfg, "strategy", "fsdp") == "megatron":
             return 1
@@ -460,6 +497,8 @@ class ModelWorker:
                  "rng": {"torch": torch.get_rng_state(), "numpy": np.random.get_state(),
                          "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None}}
         torch.save(extra, os.path.join(ckpt_dir, f"extra_state_world_size_{W}_rank_{r}.pt"))
+        if r == 0 and hasattr(self.model, "save_adapter"):
+            self.model.save_adapter(os.path.join(ckpt_dir, "lora_adapter"))  # PEFT layout, as the reference writes
         if r == 0:
             import json
 
