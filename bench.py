@@ -167,6 +167,15 @@ def main() -> None:
             k += n
         trainer.generator._per_sample_max_tokens = per_item
         m = trainer.train_step(items)
+        if env.is_main:
+            import sys
+
+            print("[bench] step %d: " % s + ", ".join(f"{k[7:]}={v:.3f}" for k, v in m.items() if k.startswith("timing/")) +
+                  f", gen_tokens={m['trainer/num_generated_tokens']:.0f}" +
+                  (f", alloc_retries={torch.cuda.memory_stats().get('num_alloc_retries', 0)}"
+                   f", max_alloc_gb={torch.cuda.max_memory_allocated() / 2**30:.1f}"
+                   f", reserved_gb={torch.cuda.memory_reserved() / 2**30:.1f}" if torch.cuda.is_available() else ""),
+                  file=sys.stderr, flush=True)
         return m
 
     # per-sample lengths are passed through env_extras["sampling_params"], one entry per repetition

@@ -590,6 +590,9 @@ class B200Config(BaseConfig):
     # With exactly one optimizer step per RL step the "old policy" is the policy being trained, so its
     # log-probabilities are the (detached) ones of the training forward pass: no separate forward is run.
     reuse_train_forward_for_old_logprobs: bool = True
+    # packed micro-batches are padded (one dummy sequence) to a multiple of this many tokens so that activation
+    # tensors repeat in size from step to step; 0 disables
+    pack_pad_multiple: int = 512
 
 
 @dataclass

@@ -98,8 +98,13 @@ class PackedView:
         return grid[self.grid_row, self.grid_col]
 
 
-def pack_batch(sequences: torch.Tensor, attention_mask: torch.Tensor, response_mask: torch.Tensor, device) -> PackedView:
-    """Build the packed view of left-padded ``sequences`` (host-side index arithmetic, one H2D per tensor)."""
+def pack_batch(sequences: torch.Tensor, attention_mask: torch.Tensor, response_mask: torch.Tensor, device,
+               pad_multiple: int = 0) -> PackedView:
+    """Build the packed view of left-padded ``sequences`` (host-side index arithmetic, one H2D per tensor).
+
+    ``pad_multiple`` > 0 appends one dummy sequence so that the packed length is a multiple of it: activations then
+    come in a few repeating sizes, which keeps the caching allocator from growing and flushing its pool step after
+    step (the dummy tokens predict nothing and receive no gradient)."""
     seq = sequences.cpu()
     att = attention_mask.cpu().bool()
     B, S = seq.shape
@@ -125,8 +130,14 @@ def pack_batch(sequences: torch.Tensor, attention_mask: torch.Tensor, response_m
     else:
         grid_row = grid_col = pred_index = torch.zeros(0, dtype=torch.long)
     targets = ids[(pred_index + 1)] if pred_index.numel() else ids.new_zeros(0)
+    n_real = int(ids.numel())
+    if pad_multiple and pad_multiple > 1 and n_real % pad_multiple:
+        n_pad = pad_multiple - n_real % pad_multiple
+        ids = torch.cat([ids, torch.zeros(n_pad, dtype=ids.dtype)])
+        pos = torch.cat([pos, torch.arange(n_pad, dtype=torch.int32)])
+        cu = torch.cat([cu, torch.tensor([n_real + n_pad], dtype=torch.int32)])
     from ..ops import _lib
 
     mv = lambda t: _lib.to_device(t, device)  # noqa: E731
-    return PackedView(mv(ids), mv(pos), mv(cu), int(lens.max()) if B else 0, mv(pred_index), mv(targets.to(torch.int32)),
-                      mv(grid_row), mv(grid_col), B, R, int(ids.numel()))
+    return PackedView(mv(ids), mv(pos), mv(cu), max(int(lens.max()) if B else 0, int(ids.numel()) - n_real), mv(pred_index), mv(targets.to(torch.int32)),
+                      mv(grid_row), mv(grid_col), B, R, n_real)

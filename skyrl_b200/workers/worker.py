@@ -247,7 +247,7 @@ class ModelWorker:
     def _pack(self, batch: TrainingInputBatch, rows: List[int]) -> PackedView:
         idx = torch.tensor(rows, dtype=torch.long)
         return pack_batch(batch["sequences"][idx], batch["attention_mask"][idx], batch["response_mask"][idx],
-                          self.env.device)
+                          self.env.device, pad_multiple=int(getattr(self.cfg.b200, "pack_pad_multiple", 0) or 0))
 
     def _rows_to_device(self, t: Optional[torch.Tensor], rows: List[int]) -> Optional[torch.Tensor]:
         if t is None:
