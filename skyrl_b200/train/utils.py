@@ -163,9 +163,41 @@ def validate_cfg(cfg, world_size: int = 1) -> None:
         if not (B <= fa.num_parallel_generation_workers <= B * (fa.max_staleness_steps + 1)):
             raise ValueError("fully_async.num_parallel_generation_workers must lie in "
                              f"[{B}, {B * (fa.max_staleness_steps + 1)}] (mini-batch size .. mini-batch * (staleness+1))")
-    if t.policy.model.lora.rank > 0 and t.strategy == "megatron" and not t.policy.megatron_config.lora_config.merge_lora:
-        pass  # adapter-only sync is supported by the engine
+    validate_parallel_cfg(cfg, world_size)
     validate_batch_sizes(cfg, world_size)
+
+
+def validate_parallel_cfg(cfg, world_size: int = 1) -> None:
+    """Model-parallel settings that this build supports (reference: validate_megatron_cfg, train/utils/utils.py:194-232)."""
+    t = cfg.trainer
+    mc = t.policy.megatron_config
+    tp, pp, cp, ep = (int(getattr(mc, k, 1) or 1) for k in ("tensor_model_parallel_size", "pipeline_model_parallel_size",
+                                                              "context_parallel_size", "expert_model_parallel_size"))
+    sp = int(t.policy.sequence_parallel_size or 1)
+    if t.strategy != "megatron":
+        if max(tp, pp, cp, ep) > 1:
+            raise ValueError("tensor / pipeline / context / expert parallel sizes need trainer.strategy=megatron")
+    else:
+        if sp > 1:
+            raise ValueError("policy.sequence_parallel_size (Ulysses) belongs to strategy=fsdp; with strategy=megatron "
+                             "sequence parallelism is implied by tensor_model_parallel_size > 1")
+        if pp > 1:
+            raise ValueError("pipeline_model_parallel_size > 1 is not selectable from the trainer yet "
+                             "(skyrl_b200.parallel.pipeline provides the stage model and schedule)")
+        if cp > 1:
+            raise ValueError("context_parallel_size > 1 is not supported; use Ulysses sequence parallelism (strategy=fsdp)")
+        if tp > 1 and ep > 1:
+            raise ValueError("tensor and expert parallelism cannot be combined in this build")
+        if t.policy.model.lora.rank > 0 and (tp > 1 or ep > 1):
+            raise ValueError("LoRA is supported with the data-parallel strategy only")
+    for name, size in (("tensor_model_parallel_size", tp), ("expert_model_parallel_size", ep),
+                       ("policy.sequence_parallel_size", sp)):
+        if size > 1 and world_size % size != 0:
+            raise ValueError(f"{name}={size} does not divide the number of ranks ({world_size})")
+        if size > 8:
+            raise ValueError(f"{name}={size}: model-parallel groups span at most the 8 GPUs of one NVSwitch domain")
+    if sp > 1 and t.policy.model.lora.rank > 0:
+        raise ValueError("LoRA together with sequence parallelism is not supported")
 
 
 # ----------------------------------------------------------------------------- checkpoints
