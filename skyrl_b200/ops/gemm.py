@@ -231,3 +231,25 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     return _LinearFn.apply(x, w, bias)
+
+
+def gemm_2cta(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None, a_mn: bool = False,
+              b_mn: bool = False, accumulate: bool = False, bn: int = 256) -> torch.Tensor:
+    """Low-level entry to the CTA-pair kernel (``csrc/gemm_2cta.cu``): ``out = op(a) op(b) (+ bias)`` with the same
+    operand-layout flags as the one-CTA kernel.  ``out`` decides the output mode (bf16 / fp32 / fp32 accumulate)."""
+    lib = _lib.kernels()
+    f = lib.sb_gemm_bf16_2cta
+    if not getattr(f, "_configured", False):
+        f.restype = ctypes.c_int
+        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                      ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                      ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        f._configured = True
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
+    code = f(a.data_ptr(), b.data_ptr(), out.data_ptr(), None if bias is None else bias.data_ptr(), M, N, K, a.stride(0),
+             b.stride(0), out.stride(0), int(a_mn), int(b_mn), mode, bn, _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_bf16_2cta")
+    return out

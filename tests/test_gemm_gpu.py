@@ -253,3 +253,29 @@ def test_gemm_indexed_dispatch_and_combine():
         untouched = torch.ones(200, dtype=torch.bool, device="cuda")
         untouched[dst_row[sel].long()] = False
         assert bufs[d][untouched].abs().sum() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (300, 384, 200), (1000, 520, 1536), (128, 256, 320)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("bn", [256, 128])
+def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn, bn):
+    from skyrl_b200.ops import _lib, gemm
+
+    torch.manual_seed(0)
+    M8, N8 = (M + 7) // 8 * 8, (N + 7) // 8 * 8
+    A = (torch.randn(K, M8, device="cuda") * 0.5).to(torch.bfloat16) if a_mn else (torch.randn(M8, K + (-K) % 8, device="cuda") * 0.5).to(torch.bfloat16)
+    Kp = K if a_mn else A.shape[1]
+    B = (torch.randn(Kp, N8, device="cuda") * 0.1).to(torch.bfloat16) if b_mn else (torch.randn(N8, Kp, device="cuda") * 0.1).to(torch.bfloat16)
+    Af = A.float().t() if a_mn else A.float()
+    Bf = B.float() if b_mn else B.float().t()
+    ref = Af @ Bf
+    out = torch.full((M8, N8), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm.gemm_2cta(A, B, out, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    assert torch.isfinite(out.float()).all()
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
+    acc = torch.ones((M8, N8), device="cuda", dtype=torch.float32)
+    gemm.gemm_2cta(A, B, acc, a_mn=a_mn, b_mn=b_mn, accumulate=True, bn=bn)
+    torch.cuda.synchronize()
+    assert ((acc - 1 - ref).norm() / ref.norm()).item() < 2e-3
