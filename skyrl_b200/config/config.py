@@ -593,6 +593,9 @@ class B200Config(BaseConfig):
     # packed micro-batches are padded (one dummy sequence) to a multiple of this many tokens so that activation
     # tensors repeat in size from step to step; 0 disables
     pack_pad_multiple: int = 512
+    # "full": token-budget micro-batches are filled to the budget (first-fit decreasing) and padded to exactly the
+    # budget, so activation sizes repeat; "balanced": equal-load bins (the reference's packer)
+    microbatch_packing: str = "full"
 
 
 @dataclass

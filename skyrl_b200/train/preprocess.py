@@ -99,12 +99,13 @@ class PackedView:
 
 
 def pack_batch(sequences: torch.Tensor, attention_mask: torch.Tensor, response_mask: torch.Tensor, device,
-               pad_multiple: int = 0) -> PackedView:
+               pad_multiple: int = 0, pad_to: int = 0) -> PackedView:
     """Build the packed view of left-padded ``sequences`` (host-side index arithmetic, one H2D per tensor).
 
     ``pad_multiple`` > 0 appends one dummy sequence so that the packed length is a multiple of it: activations then
     come in a few repeating sizes, which keeps the caching allocator from growing and flushing its pool step after
-    step (the dummy tokens predict nothing and receive no gradient)."""
+    step (the dummy tokens predict nothing and receive no gradient).  ``pad_to`` > 0: a batch that fills at least
+    ``pad_to - 2 * pad_multiple`` tokens is padded to exactly ``pad_to`` (bins packed to a token budget)."""
     seq = sequences.cpu()
     att = attention_mask.cpu().bool()
     B, S = seq.shape
@@ -131,8 +132,12 @@ def pack_batch(sequences: torch.Tensor, attention_mask: torch.Tensor, response_m
         grid_row = grid_col = pred_index = torch.zeros(0, dtype=torch.long)
     targets = ids[(pred_index + 1)] if pred_index.numel() else ids.new_zeros(0)
     n_real = int(ids.numel())
-    if pad_multiple and pad_multiple > 1 and n_real % pad_multiple:
+    n_pad = 0
+    if pad_to and n_real < pad_to and n_real >= pad_to - 2 * max(pad_multiple, 256):
+        n_pad = pad_to - n_real
+    elif pad_multiple and pad_multiple > 1 and n_real % pad_multiple:
         n_pad = pad_multiple - n_real % pad_multiple
+    if n_pad:
         ids = torch.cat([ids, torch.zeros(n_pad, dtype=ids.dtype)])
         pos = torch.cat([pos, torch.arange(n_pad, dtype=torch.int32)])
         cu = torch.cat([cu, torch.tensor([n_real + n_pad], dtype=torch.int32)])

@@ -32,8 +32,11 @@ from ..utils.torch_utils import masked_mean
 
 
 # ----------------------------------------------------------------------------- micro-batching
-def microbatch_indices(seq_lens: Sequence[int], micro_batch_size: int, max_tokens: int) -> List[List[int]]:
-    """Row-index groups: by token budget (balanced bins, C++ runtime) when ``max_tokens > 0``, else by count.
+def microbatch_indices(seq_lens: Sequence[int], micro_batch_size: int, max_tokens: int, packing: str = "balanced") -> List[List[int]]:
+    """Row-index groups: by token budget (C++ runtime) when ``max_tokens > 0``, else by count.  ``packing``:
+    ``balanced`` = equal-load bins; ``full`` = first-fit-decreasing, i.e. every bin but the last is filled to the
+    budget, which makes the packed length -- and with it every activation size -- the same from micro-batch to
+    micro-batch and from step to step.
 
     Reference: ``max_tokens_per_microbatch`` / ``micro_*_batch_size_per_gpu`` handling in
     skyrl/backends/skyrl_train/workers/worker_utils.py:248-444.
@@ -46,8 +49,9 @@ def microbatch_indices(seq_lens: Sequence[int], micro_batch_size: int, max_token
         budget = max(int(max_tokens), int(lens.max()))
         out = np.zeros(n, dtype=np.int32)
         rt = _lib.runtime()
-        rt.sbrt_balanced_bins.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
-        bins = rt.sbrt_balanced_bins(lens.ctypes.data, n, budget, out.ctypes.data)
+        fn = rt.sbrt_ffd_pack if packing == "full" else rt.sbrt_balanced_bins
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        bins = fn(lens.ctypes.data, n, budget, out.ctypes.data)
         groups: List[List[int]] = [[] for _ in range(bins)]
         for i, b in enumerate(out.tolist()):
             groups[b].append(i)
@@ -246,8 +250,10 @@ class ModelWorker:
 
     def _pack(self, batch: TrainingInputBatch, rows: List[int]) -> PackedView:
         idx = torch.tensor(rows, dtype=torch.long)
+        b2 = self.cfg.b200
         return pack_batch(batch["sequences"][idx], batch["attention_mask"][idx], batch["response_mask"][idx],
-                          self.env.device, pad_multiple=int(getattr(self.cfg.b200, "pack_pad_multiple", 0) or 0))
+                          self.env.device, pad_multiple=int(getattr(b2, "pack_pad_multiple", 0) or 0),
+                          pad_to=self._max_tokens() if getattr(b2, "microbatch_packing", "balanced") == "full" else 0)
 
     def _rows_to_device(self, t: Optional[torch.Tensor], rows: List[int]) -> Optional[torch.Tensor]:
         if t is None:
@@ -396,7 +402,8 @@ class ModelWorker:
         self.backload()
         B, R = batch["response_mask"].shape
         out = torch.zeros((B, R), dtype=torch.float32)
-        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_forward_batch_size_per_gpu, self._max_tokens())
+        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_forward_batch_size_per_gpu, self._max_tokens(),
+                                    getattr(self.cfg.b200, "microbatch_packing", "balanced"))
         n_mb = sync_num_microbatches(len(groups), self.env)
         temp = float(self.cfg.algorithm.temperature or 1.0)
         was_ckpt = self.model.gradient_checkpointing
@@ -593,7 +600,8 @@ class PolicyWorker(ModelWorker):
         loss_func = rl.PolicyLossRegistry.get(loss_name)
         dev = self.env.device
         B, R = batch["response_mask"].shape
-        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens())
+        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens(),
+                                    getattr(self.cfg.b200, "microbatch_packing", "balanced"))
         n_mb = sync_num_microbatches(len(groups), self.env)
         # number of distinct data shards (expert-parallel ranks each hold their own)
         world = self.mesh.dp_size if (self.mesh is not None and not self.expert_parallel) else self.env.world_size
@@ -700,7 +708,8 @@ class CriticWorker(ModelWorker):
         self.backload()
         algo = self.cfg.algorithm
         B, R = batch["response_mask"].shape
-        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens())
+        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens(),
+                                    getattr(self.cfg.b200, "microbatch_packing", "balanced"))
         n_mb = sync_num_microbatches(len(groups), self.env)
         all_metrics = []
         for k in range(n_mb):
