@@ -189,6 +189,8 @@ __global__ void __launch_bounds__(kSampThreads)
 sample_gumbel_kernel(const T* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temperature,
                      unsigned long long seed, const long long* __restrict__ step_offsets, int* __restrict__ tokens,
                      float* __restrict__ logprobs) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const T* z = logits + static_cast<size_t>(row) * row_stride;
   const float temp = temperature[row];
@@ -261,6 +263,8 @@ sample_gumbel_kernel(const T* __restrict__ logits, long long row_stride, int V, 
 // ------------------------------------------------------------------ embedding gather
 __global__ void embed_gather_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
                                     __nv_bfloat16* __restrict__ out, int T, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int vec = H / 8;
   const long long total = static_cast<long long>(T) * vec;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -297,6 +301,8 @@ struct DecodeState {
 __global__ void decode_advance_kernel(DecodeState st, const int* __restrict__ sampled,
                                       const float* __restrict__ sampled_lp, int n, int max_blocks, int block_size,
                                       int out_stride, int n_eos) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i == 0 && st.step_counter) *st.step_counter += 1;
   if (i >= n || !st.active[i]) return;
@@ -393,12 +399,12 @@ int sb_sample_gumbel(const void* logits, int is_bf16, long long row_stride, int 
   if (n <= 0 || V <= 0) return SB_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (is_bf16)
-    sb::sample_gumbel_kernel<__nv_bfloat16><<<n, sb::kSampThreads, 0, st>>>(
-        reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V, temperature, seed, step_offsets, tokens, logprobs);
+    sb::launch_pdl(sb::sample_gumbel_kernel<__nv_bfloat16>, dim3(n), dim3(sb::kSampThreads), 0, st,
+                   reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V, temperature, seed, step_offsets, tokens,
+                   logprobs);
   else
-    sb::sample_gumbel_kernel<float><<<n, sb::kSampThreads, 0, st>>>(reinterpret_cast<const float*>(logits), row_stride,
-                                                                    V, temperature, seed, step_offsets, tokens,
-                                                                    logprobs);
+    sb::launch_pdl(sb::sample_gumbel_kernel<float>, dim3(n), dim3(sb::kSampThreads), 0, st,
+                   reinterpret_cast<const float*>(logits), row_stride, V, temperature, seed, step_offsets, tokens, logprobs);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
@@ -421,17 +427,18 @@ int sb_decode_advance(void* const* ptrs, const int* sampled, const float* sample
   st.out_logprobs = static_cast<float*>(ptrs[11]);
   st.eos_ids = static_cast<const int*>(ptrs[12]);
   st.step_counter = static_cast<long long*>(ptrs[13]);
-  sb::decode_advance_kernel<<<(n + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      st, sampled, sampled_lp, n, max_blocks, block_size, out_stride, n_eos);
-  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+  const cudaError_t e = sb::launch_pdl(sb::decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0,
+                                       reinterpret_cast<cudaStream_t>(stream), st, sampled, sampled_lp, n, max_blocks, block_size,
+                                       out_stride, n_eos);
+  return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
 int sb_embed_gather(const void* table, const int* ids, void* out, int T, int H, void* stream) {
   if (T <= 0) return SB_OK;
   if (H % 8 != 0) return SB_ERR_ARG;
-  sb::embed_gather_kernel<<<sb::grid_1d(static_cast<long long>(T) * H / 8, 256), 256, 0,
-                            reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(table), ids, reinterpret_cast<__nv_bfloat16*>(out), T, H);
+  sb::launch_pdl(sb::embed_gather_kernel, dim3(sb::grid_1d(static_cast<long long>(T) * H / 8, 256)), dim3(256), 0,
+                 reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(table), ids,
+                 reinterpret_cast<__nv_bfloat16*>(out), T, H);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -52,6 +52,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
   const int seq = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();  // q, the cache rows of this step and ctx_lens come from the preceding kernels
   const int ctx = ctx_lens[seq];
   const int per_split = (((ctx + splits - 1) / splits) + 127) & ~127;
   const int t0 = split * per_split;
@@ -277,6 +279,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 }
 
 __global__ void attn_decode_tc_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const int d = threadIdx.x;
   const float* base = ws + row * splits * 130;
@@ -325,10 +329,10 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
         return SB_ERR_CUDA;                                                                                         \
       attr = true;                                                                                                  \
     }                                                                                                               \
-    sb::attn_decode_tc_kernel<GV><<<grid, sb::kDtThreads, sb::kDtSmem, st>>>(                                       \
-        *tk, *tv, reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                              \
-        reinterpret_cast<__nv_bfloat16*>(out), workspace, nq, nkv, block_size, max_blocks, splits, q_stride, sl2,   \
-        sb::device_status_ptr());                                                                                   \
+    sb::launch_pdl(sb::attn_decode_tc_kernel<GV>, grid, dim3(sb::kDtThreads), sb::kDtSmem, st, *tk, *tv,             \
+                   reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                             \
+                   reinterpret_cast<__nv_bfloat16*>(out), workspace, nq, nkv, block_size, max_blocks, splits,       \
+                   q_stride, sl2, sb::device_status_ptr());                                                         \
   } break;
   switch (G) {
     SB_DT_CASE(1)
@@ -346,7 +350,8 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
   }
 #undef SB_DT_CASE
   if (splits > 1)
-    sb::attn_decode_tc_combine_kernel<<<n * nq, 128, 0, st>>>(workspace, reinterpret_cast<__nv_bfloat16*>(out), splits);
+    sb::launch_pdl(sb::attn_decode_tc_combine_kernel, dim3(n * nq), dim3(128), 0, st, workspace,
+                   reinterpret_cast<__nv_bfloat16*>(out), splits);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -54,6 +54,8 @@ add_rmsnorm_partials_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
                             __nv_bfloat16* __restrict__ y, int T, int H, float eps) {
   __shared__ float red[32];
   const int nvec = H >> 3;
+  pdl_launch_dependents();
+  pdl_wait();
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     float vals[kFMaxVec][8];
     float ss = 0.f;
@@ -105,6 +107,8 @@ __global__ void qkv_finalize_kernel(const float* __restrict__ part, int n_part, 
                                     const int* __restrict__ slots, __nv_bfloat16* __restrict__ qkv,
                                     __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, int T, int nq,
                                     int nkv, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int half = D >> 1;
   const int units_per_head = D >> 3;  // 8 output elements per unit
   const int heads = nq + 2 * nkv;
@@ -221,10 +225,11 @@ int sb_add_rmsnorm_partials(void* x, const float* part, int n_part, long long pa
   if ((reinterpret_cast<uintptr_t>(part) & 15) || (part_stride & 3)) return SB_ERR_ARG;
   const int cap = sb::sm_count() * 8;
   const int grid = T < cap ? T : cap;
-  sb::add_rmsnorm_partials_kernel<<<grid, sb::kFThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<__nv_bfloat16*>(x), part, n_part, part_stride, reinterpret_cast<const __nv_bfloat16*>(w),
-      reinterpret_cast<__nv_bfloat16*>(y), T, H, eps);
-  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+  const cudaError_t e = sb::launch_pdl(sb::add_rmsnorm_partials_kernel, dim3(grid), dim3(sb::kFThreads), 0,
+                                       reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<__nv_bfloat16*>(x), part, n_part,
+                                       part_stride, reinterpret_cast<const __nv_bfloat16*>(w),
+                                       reinterpret_cast<__nv_bfloat16*>(y), T, H, eps);
+  return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
 // partials [n_part][T, (nq+2nkv)*D] fp32 -> qkv bf16 [T, (nq+2nkv)*D] with rotary embedding on q,k;
@@ -238,10 +243,11 @@ int sb_qkv_finalize(const float* part, int n_part, long long part_stride, const 
   long long blocks = (total + 255) / 256;
   const long long cap = static_cast<long long>(sb::sm_count()) * 16;
   if (blocks > cap) blocks = cap;
-  sb::qkv_finalize_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      part, n_part, part_stride, pos, cos_sin, slots, reinterpret_cast<__nv_bfloat16*>(qkv),
-      reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, D);
-  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+  const cudaError_t e = sb::launch_pdl(sb::qkv_finalize_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0,
+                                       reinterpret_cast<cudaStream_t>(stream), part, n_part, part_stride, pos, cos_sin, slots,
+                                       reinterpret_cast<__nv_bfloat16*>(qkv), reinterpret_cast<__nv_bfloat16*>(k_cache),
+                                       reinterpret_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, D);
+  return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
 }  // extern "C"

@@ -176,6 +176,8 @@ rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int T, float eps) {
   constexpr int H = NV * 256;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait();
   uint4 wq[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) wq[i] = reinterpret_cast<const uint4*>(w)[i * 32 + lane];
@@ -318,6 +320,8 @@ __global__ void rope_inplace_kernel(__nv_bfloat16* __restrict__ qkv, const int* 
 // ---------------------------------------------------------------------------
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T,
                                   int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int fv = F >> 3;
   const long long total = T * fv;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -468,10 +472,10 @@ int sb_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_out,
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define SB_NORM_FWD(NVV)                                                                                              \
   case NVV:                                                                                                           \
-    sb::rmsnorm_fwd_warp_kernel<NVV><<<wgrid, sb::kWarpNormThreads, 0, st>>>(                                         \
-        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(delta),                     \
-        reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(x_out),                           \
-        reinterpret_cast<__nv_bfloat16*>(y), rstd, T, eps);                                                           \
+    sb::launch_pdl(sb::rmsnorm_fwd_warp_kernel<NVV>, dim3(wgrid), dim3(sb::kWarpNormThreads), 0, st,                  \
+                   reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(delta),          \
+                   reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(x_out),                \
+                   reinterpret_cast<__nv_bfloat16*>(y), rstd, T, eps);                                                \
     return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
     switch (H / 256) {
       SB_NORM_FWD(1) SB_NORM_FWD(2) SB_NORM_FWD(3) SB_NORM_FWD(4) SB_NORM_FWD(5) SB_NORM_FWD(6) SB_NORM_FWD(7) SB_NORM_FWD(8)
@@ -531,8 +535,9 @@ int sb_rope_inplace(void* qkv, const int* pos, const float* cos_sin, int T, int 
 
 int sb_swiglu_fwd(const void* gu, void* out, long long T, int F, void* stream) {
   if (F % 8 != 0 || T <= 0) return SB_ERR_ARG;
-  sb::swiglu_fwd_kernel<<<sb::grid_for(T * (F / 8), 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(gu), reinterpret_cast<__nv_bfloat16*>(out), T, F);
+  sb::launch_pdl(sb::swiglu_fwd_kernel, dim3(sb::grid_for(T * (F / 8), 256)), dim3(256), 0,
+                 reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(gu),
+                 reinterpret_cast<__nv_bfloat16*>(out), T, F);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -144,6 +144,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  // everything above (barriers, tensor memory) is private to this CTA and may overlap the previous kernel's tail;
+  // operands and outputs may belong to that kernel, so all roles wait for it here
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -468,10 +472,10 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   }
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kfn<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N,
-                                                       K, ldc, out_mode, splits, split_stride, device_status_ptr(),
-                                                       TpArgs{});
-  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+  const cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, *ta, *tb, C,
+                                   reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, out_mode, splits, split_stride,
+                                   device_status_ptr(), TpArgs{});
+  return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
 // Tensor-parallel launch: x @ W^T (B_MN = false) or dy @ W (B_MN = true) with the A operand gathered from peers

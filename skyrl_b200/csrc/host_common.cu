@@ -2,6 +2,7 @@
 #include "host_common.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -118,6 +119,15 @@ int* device_status_ptr() {
     ptrs[dev] = p;
   }
   return ptrs[dev];
+}
+
+bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SB_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 int sm_count() {

@@ -23,5 +23,30 @@ const CUtensorMap* get_tmap_bf16_3d(const void* ptr, uint64_t d0, uint64_t d1, u
 
 int* device_status_ptr();  // per-device status word (device address)
 int sm_count();
+bool pdl_enabled();  // programmatic dependent launch of the decode-chain kernels (SB_PDL=0 turns it off)
+
+#ifdef __CUDACC__
+// Programmatic dependent launch: a kernel started with the attribute below may begin (block scheduling, prologue)
+// while its predecessor in the stream is still draining; ``pdl_wait`` blocks until the predecessor grid has completed
+// and its writes are visible, so every access to memory that a predecessor may have produced -- or may still be
+// reading -- comes after it.  Without the launch attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 }  // namespace sb
