@@ -101,7 +101,9 @@ template <int BN, bool A_MN, bool B_MN, bool GATHER = false, bool SCATTER = fals
 __global__ void __launch_bounds__(kGemmThreads + (GATHER ? kGatherWarps * 32 : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
                  const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc, int out_mode, int splits,
-                 long long split_stride, int* status, const __grid_constant__ TpArgs tp) {
+                 long long split_stride, int* status, const __grid_constant__ TpArgs tp, int prefetch_b) {
+  // prefetch_b: the B operand is constant data (weights) that no kernel earlier in the stream writes, so its first
+  // tiles may be requested before waiting for the predecessor grid (programmatic dependent launch).
   // splits > 1: split-K. Work item = (output tile, k slice); slice ks writes its fp32 partial sum to
   // C + ks * split_stride (the consumer kernel adds the partials), bias is applied by slice 0 only.
   using Cfg = GemmCfg<BN>;
@@ -147,6 +149,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // everything above (barriers, tensor memory) is private to this CTA and may overlap the previous kernel's tail;
   // operands and outputs may belong to that kernel, so all roles wait for it here
   pdl_launch_dependents();
+  int b_ahead = 0;  // stages of the first tile whose B half is already in flight (producer thread only)
+  if (prefetch_b && !GATHER && threadIdx.x == 0 && blockIdx.x < tiles) {
+    int pm, pn;
+    const int ks = blockIdx.x / tiles_mn;
+    tm.get(blockIdx.x - ks * tiles_mn, pm, pn);
+    const int kb0 = ks * kpb, kb1 = min(k_blocks, kb0 + kpb);
+    b_ahead = min(Cfg::kStages, kb1 - kb0);
+    for (int j = 0; j < b_ahead; ++j) {
+      uint8_t* sB = smem + j * Cfg::kStageBytes + Cfg::kABytes;
+      mbar_arrive_expect_tx(&full[j], Cfg::kStageBytes);
+      if (!B_MN) {
+        tma_load_2d(sB, &tmB, &full[j], (kb0 + j) * kBK, pn * BN);
+      } else {
+#pragma unroll
+        for (int q2 = 0; q2 < BN / 64; ++q2) tma_load_2d(sB + q2 * 8192, &tmB, &full[j], pn * BN + q2 * 64, (kb0 + j) * kBK);
+      }
+    }
+  }
   pdl_wait();
 
   if (warp == 0) {
@@ -190,13 +210,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           uint8_t* sA = smem + s * Cfg::kStageBytes;
           uint8_t* sB = sA + Cfg::kABytes;
-          mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+          const bool b_done = it < b_ahead;  // this stage's B half was requested before the dependency wait
+          if (!b_done) mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
           if (!A_MN) {
             tma_load_2d(sA, &tmA, &full[s], kb * kBK, pm * kBM);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, &full[s], pm * kBM + j * 64, kb * kBK);
           }
+          if (b_done) continue;
           if (!B_MN) {
             tma_load_2d(sB, &tmB, &full[s], kb * kBK, pn * BN);
           } else {
@@ -458,7 +480,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                        long long ldb, long long ldc, int out_mode, cudaStream_t stream, int splits = 1,
-                       long long split_stride = 0) {
+                       long long split_stride = 0, int prefetch_b = 0) {
   using Cfg = GemmCfg<BN>;
   const CUtensorMap* ta = A_MN ? get_tmap_bf16_2d(A, K, M, lda, 64) : get_tmap_bf16_2d(A, M, K, lda, kBM);
   const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN);
@@ -474,7 +496,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   const int grid = tiles < sm_count() ? tiles : sm_count();
   const cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, *ta, *tb, C,
                                    reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, out_mode, splits, split_stride,
-                                   device_status_ptr(), TpArgs{});
+                                   device_status_ptr(), TpArgs{}, prefetch_b);
   return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
@@ -504,13 +526,13 @@ static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bia
   const int grid = GATHER ? sm_count() : (tiles < sm_count() ? tiles : sm_count());
   const int threads = kGemmThreads + (GATHER ? kGatherWarps * 32 : 0);
   kfn<<<grid, threads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc,
-                                                  out_mode, 1, 0, device_status_ptr(), tp);
+                                                  out_mode, 1, 0, device_status_ptr(), tp, 0);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
 template <bool A_MN, bool B_MN>
 static int dispatch_bn(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
-                       long long ldb, long long ldc, int out_mode, int bn_hint, cudaStream_t stream) {
+                       long long ldb, long long ldc, int out_mode, int bn_hint, cudaStream_t stream, int prefetch_b = 0) {
   int bn = bn_hint;
   if (bn != 64 && bn != 128 && bn != 256) {
     const long long mb = (M + kBM - 1) / kBM;
@@ -522,9 +544,9 @@ static int dispatch_bn(const void* A, const void* B, void* C, const void* bias, 
     else
       bn = 64;
   }
-  if (bn == 256) return launch_gemm<256, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream);
-  if (bn == 128) return launch_gemm<128, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream);
-  return launch_gemm<64, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream);
+  if (bn == 256) return launch_gemm<256, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream, 1, 0, prefetch_b);
+  if (bn == 128) return launch_gemm<128, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream, 1, 0, prefetch_b);
+  return launch_gemm<64, A_MN, B_MN>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, stream, 1, 0, prefetch_b);
 }
 
 }  // namespace sb
@@ -562,10 +584,14 @@ int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M,
   if (M <= 0 || N <= 0 || K <= 0) return SB_ERR_ARG;
   if ((lda & 7) || (ldb & 7)) return SB_ERR_ARG;
   if (out_mode < 0 || out_mode > 2) return SB_ERR_ARG;
+  // bit 12 of bn_hint: the B operand is constant data (weights), its first tiles may be fetched ahead of the
+  // dependency wait of a programmatic dependent launch
+  const int prefetch_b = (bn_hint >> 12) & 1;
+  bn_hint &= 0xFFF;
   if (sb::use_pair_kernel(M, N, K, bn_hint))
     return sb_gemm_bf16_2cta(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, 256, stream);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!a_mn && !b_mn) return sb::dispatch_bn<false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
+  if (!a_mn && !b_mn) return sb::dispatch_bn<false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st, prefetch_b);
   if (!a_mn && b_mn) return sb::dispatch_bn<false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
   if (a_mn && b_mn) return sb::dispatch_bn<true, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
   return sb::dispatch_bn<true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
@@ -585,9 +611,10 @@ int sb_gemm_bf16_splitk(const void* A, const void* B, float* C, const void* bias
   splits = (k_blocks + kpb - 1) / kpb;
   if (splits_used) *splits_used = splits;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (bn == 256) return sb::launch_gemm<256, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
-  if (bn == 128) return sb::launch_gemm<128, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
-  return sb::launch_gemm<64, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride);
+  // B is a weight matrix here by contract (decode projections): its first tiles are prefetched ahead of the wait
+  if (bn == 256) return sb::launch_gemm<256, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride, 1);
+  if (bn == 128) return sb::launch_gemm<128, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride, 1);
+  return sb::launch_gemm<64, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, 1, st, splits, split_stride, 1);
 }
 
 

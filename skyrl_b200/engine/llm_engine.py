@@ -315,10 +315,10 @@ class LLMEngine:
                                              max_ctx=self.cfg.max_model_len)
             part, np_ = self._splitk_linear(att, m.p(pre + "wo"), None, n)
             h = ew.add_rmsnorm_partials_(x, part, np_, m.p(pre + "ln2"), a.rms_norm_eps)
-            gu = gemm.gemm_nt(h, m.p(pre + "wgu"))
+            gu = gemm.gemm_nt(h, m.p(pre + "wgu"), static_w=True)
             pending = self._splitk_linear(ew.swiglu(gu), m.p(pre + "wd"), None, n)
         h = ew.add_rmsnorm_partials_(x, pending[0], pending[1], m.p("final_norm"), a.rms_norm_eps)
-        logits = gemm.gemm_nt(h, m.lm_head_weight())
+        logits = gemm.gemm_nt(h, m.lm_head_weight(), static_w=True)
         self._sample(logits, n, masked)
         self._advance(n)
 

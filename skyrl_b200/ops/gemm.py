@@ -58,8 +58,10 @@ def _launch(a, b, c, bias, M, N, K, a_mn, b_mn, out_mode, bn_hint=0):
 
 
 def gemm_nt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
-            out_dtype: torch.dtype | None = None, bn_hint: int = 0) -> torch.Tensor:
-    """``x[M,K] @ w[N,K]^T (+ bias[N])`` -> ``[M,N]`` (dtype of ``x`` unless ``out_dtype`` is given)."""
+            out_dtype: torch.dtype | None = None, bn_hint: int = 0, static_w: bool = False) -> torch.Tensor:
+    """``x[M,K] @ w[N,K]^T (+ bias[N])`` -> ``[M,N]`` (dtype of ``x`` unless ``out_dtype`` is given).
+    ``static_w``: ``w`` is not written by any kernel queued before this call (inference weights); its first tiles are
+    then fetched while the preceding kernel is still finishing."""
     M, K = x.shape
     N = w.shape[0]
     if out_dtype is None:
@@ -80,7 +82,7 @@ def gemm_nt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
         out = torch.empty((M, N), device=x.device, dtype=out_dtype)
     assert out.stride(1) == 1
     mode = 0 if out.dtype == torch.bfloat16 else 1
-    _launch(x, w, out, bias, M, N, K, False, False, mode, bn_hint)
+    _launch(x, w, out, bias, M, N, K, False, False, mode, bn_hint | (0x1000 if static_w else 0))
     return out
 
 
