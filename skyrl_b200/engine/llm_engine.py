@@ -596,6 +596,39 @@ class LLMEngine:
                 if cut is not None:
                     self._retire(req, "stop", t[:cut], l[:cut])
 
+    _SLOT_STATE = ("cur_tokens", "positions", "slots", "ctx_lens", "block_tables", "active", "finish_reason", "gen_count",
+                   "max_new", "min_new", "out_tokens", "out_logprobs", "temperature", "top_k", "top_p", "min_p", "sampled",
+                   "sampled_lp")
+
+    def _compact_slots(self) -> None:
+        """Move running sequences from high slots into free low slots when that lets the decode batch drop to a
+        smaller bucket: the decode step is launched over slots ``[0, bucket(hi))``, so stragglers parked in high
+        slots would otherwise keep every step at the full batch size while most rows are idle."""
+        live = [s for s, r in enumerate(self._slot_req) if r is not None]
+        if not live:
+            return
+        target = self._bucket(len(live))
+        if target >= self._bucket(live[-1] + 1):
+            return
+        movers = [s for s in live if s >= len(live)]
+        holes = [s for s in range(len(live)) if self._slot_req[s] is None]
+        src = torch.tensor(movers, device=self.device, dtype=torch.long)
+        dst = torch.tensor(holes[: len(movers)], device=self.device, dtype=torch.long)
+        for name in self._SLOT_STATE:
+            t = getattr(self, name)
+            t[dst] = t[src]
+        self.active[src] = 0
+        self.finish_reason[src] = 0
+        self.slots[src] = -1
+        self.ctx_lens[src] = 0
+        for a, b in zip(movers, holes):
+            req = self._slot_req[a]
+            self._slot_req[b], self._slot_req[a] = req, None
+            req.slot = b
+        used = {s for s, r in enumerate(self._slot_req) if r is not None}
+        self._free_slots = [s for s in range(self.cfg.max_num_seqs - 1, -1, -1) if s not in used]
+        self.stats["slot_compactions"] = self.stats.get("slot_compactions", 0) + 1
+
     def _retire(self, req: _Request, reason: str, toks: Optional[List[int]] = None,
                 lps: Optional[List[float]] = None) -> None:
         toks = req.partial_tokens + (toks or [])
@@ -647,6 +680,7 @@ class LLMEngine:
                 self._finished.append(RequestOutput(req.rid, req.prompt, [], [], "abort", weight_version=self.weight_version))
         self._harvest()  # requests that finished on their very first token
         if any(r is not None for r in self._slot_req):
+            self._compact_slots()
             self._run_decode(self.cfg.sync_interval)
             self._harvest()
         out, self._finished = self._finished, []

@@ -135,3 +135,28 @@ def test_prefix_cached_prefill_skips_cached_tokens_and_matches_full_prefill():
     assert outs[False][3] == 0
     assert outs[True][3] >= 64 + 64  # p2 reuses 4 shared blocks, the repeat of p1 reuses 4 (79 tokens -> 64 cached)
     assert outs[True][4] == outs[False][4] - outs[True][3]
+
+
+def test_slot_compaction_keeps_outputs_and_shrinks_the_decode_batch():
+    """Sequences of very different lengths: stragglers are moved to low slots, results are unchanged."""
+    import torch
+
+    from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine, SamplingParams
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+
+    m = CausalLM(PRESETS["tiny-llama"], device="cpu", dtype=torch.float32, seed=1)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(4, 1024, (10 + i,), generator=g).tolist() for i in range(24)]
+    lens = [3] * 20 + [40, 44, 48, 52]  # the long ones sit in the highest slots
+    params = [SamplingParams(max_tokens=n, temperature=0.0, ignore_eos=True) for n in lens]
+    cfgs = dict(block_size=16, max_model_len=128, enforce_eager=True, num_blocks=256, sync_interval=4)
+    eng = LLMEngine(m, EngineConfig(max_num_seqs=32, graph_batch_sizes=(8, 16, 32), **cfgs))
+    out = eng.generate(prompts, params)
+    assert eng.stats.get("slot_compactions", 0) >= 1
+    assert [len(o.token_ids) for o in out] == lens
+    ref_eng = LLMEngine(m, EngineConfig(max_num_seqs=32, graph_batch_sizes=(32,), **cfgs))  # one bucket: never compacts
+    ref = ref_eng.generate(prompts, params)
+    assert ref_eng.stats.get("slot_compactions", 0) == 0
+    for a, b in zip(out, ref):
+        assert a.token_ids == b.token_ids
+    assert eng.metrics()["kv_free_blocks"] == 256 and sorted(eng._free_slots) == list(range(32))
