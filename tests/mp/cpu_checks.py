@@ -172,6 +172,41 @@ def check_expert_parallel(env):
     assert rel(wd_l.grad, wd_f.grad[r * El : (r + 1) * El]) < 1e-4
 
 
+def check_ep_model(env):
+    """Expert-parallel model over both ranks' tokens == unsharded model over the union of the data."""
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+    from skyrl_b200.models.tp_decoder import EPCausalLM
+
+    W, r = env.world_size, env.rank
+    a = PRESETS["tiny-moe"]
+    ep = tpm.TPGroup(None)
+    full = CausalLM(a, device="cpu", dtype=torch.float32, seed=11)
+    m = EPCausalLM(a, ep, device="cpu", dtype=torch.float32, seed=11)
+    data = []
+    for rr in range(W):
+        g = torch.Generator().manual_seed(50 + rr)
+        ids = torch.randint(4, a.vocab_size, (48,), generator=g).int()  # equal packed length on every rank
+        pos = torch.cat([torch.arange(20), torch.arange(28)]).int()
+        cu = torch.tensor([0, 20, 48]).int()
+        data.append((ids, pos, cu))
+    ids, pos, cu = data[r]
+    lp, _ = m.token_logprobs(m(ids, pos, cu, 32), torch.roll(ids.long(), -1))
+    lp.sum().backward()
+    m.reduce_replicated_grads()
+    for rr in range(W):
+        i2, p2, c2 = data[rr]
+        l2, _ = full.token_logprobs(full(i2, p2, c2, 32), torch.roll(i2.long(), -1))
+        l2.sum().backward()
+        if rr == r:
+            assert rel(lp, l2) < 1e-4, rel(lp, l2)
+    for name, prm in m.named_flat_views():
+        want = m._shard(name, full.p(name).grad)
+        assert prm.grad is not None and rel(prm.grad, want) < 3e-3, (name, rel(prm.grad, want))
+    st = m.gather_full_state()
+    for name, _ in full.named_flat_views():
+        assert torch.equal(st[name], full.p(name).detach()), name
+
+
 def check_pipeline(env):
     """Two pipeline stages reproduce the single-model loss and gradients over several micro-batches."""
     from skyrl_b200.models.decoder import PRESETS, CausalLM
@@ -230,6 +265,7 @@ def main():
     check_ulysses_model(env)
     check_expert_parallel(env)
     check_pipeline(env)
+    check_ep_model(env)
     dist.barrier()
     if env.rank == 0:
         print("CPU_CHECKS_OK", flush=True)

@@ -187,7 +187,37 @@ def main():
         out = torch.empty(R2, H2, device=dev, dtype=torch.bfloat16)
         dist.reduce_scatter_tensor(out, yfull)
 
-    res = {"ag_gemm_fused_ms": timed(fused_ag), "ag_gemm_nccl_ms": timed(nccl_ag), "gemm_rs_fused_ms": timed(fused_rs),
+    # Ulysses projections: fused exchange vs all_to_all + GEMM (7B attention shapes, T tokens over W ranks)
+    from skyrl_b200.parallel import ulysses
+
+    nq_, nkv_, d_ = 28, 4, 128
+    widths = [nq_ * d_, nkv_ * d_, nkv_ * d_]
+    Ru = T2 // W
+    hq = (torch.randn(Ru, H2, device=dev) * 0.5).to(torch.bfloat16)
+    wqkv = (torch.randn(sum(widths), H2, device=dev) * 0.02).to(torch.bfloat16)
+    wo = (torch.randn(H2, nq_ * d_, device=dev) * 0.02).to(torch.bfloat16)
+    att_loc = (torch.randn(T2, nq_ * d_ // W, device=dev) * 0.5).to(torch.bfloat16)
+    ref_tp = tpm.TPGroup(None, tp.group)  # same ranks, no peer context -> all_to_all reference path
+
+    with torch.no_grad():
+        t_qkv_f = timed(lambda: ulysses.qkv_proj(hq, wqkv, None, widths, tp))
+        t_qkv_r = timed(lambda: ulysses.qkv_proj(hq, wqkv, None, widths, ref_tp))
+        t_o_f = timed(lambda: ulysses.o_proj(att_loc, wo, tp))
+        t_o_r = timed(lambda: ulysses.o_proj(att_loc, wo, ref_tp))
+
+    # expert-parallel MoE layer forward (30B-A3B expert shapes, 16 local experts per rank at W=8 -> Em/W here)
+    Tm2, Hm2, Em2, Fm2, km2 = 8192, 2048, 16 * W, 768, 8
+    rt2 = (torch.randn(Em2, Hm2, device=dev) * 0.5).to(torch.bfloat16)
+    wgu2 = (torch.randn(Em2 // W, 2 * Fm2, Hm2, device=dev) * 0.02).to(torch.bfloat16)
+    wd2 = (torch.randn(Em2 // W, Hm2, Fm2, device=dev) * 0.02).to(torch.bfloat16)
+    he2 = (torch.randn(Tm2, Hm2, device=dev) * 0.5).to(torch.bfloat16)
+    with torch.no_grad():
+        t_ep_f = timed(lambda: moe_ffn_ep(he2, rt2, wgu2, wd2, km2, True, tp, Em2), iters=3)
+        t_ep_r = timed(lambda: moe_ffn_ep(he2, rt2, wgu2, wd2, km2, True, ref_tp, Em2), iters=3)
+
+    res = {"ulysses_qkv_fused_ms": t_qkv_f, "ulysses_qkv_a2a_ms": t_qkv_r, "ulysses_o_fused_ms": t_o_f, "ulysses_o_a2a_ms": t_o_r,
+           "ep_moe_fused_ms": t_ep_f, "ep_moe_gather_ref_ms": t_ep_r,
+           "ag_gemm_fused_ms": timed(fused_ag), "ag_gemm_nccl_ms": timed(nccl_ag), "gemm_rs_fused_ms": timed(fused_rs),
            "gemm_rs_nccl_ms": timed(nccl_rs), "world": W, "shape": [T2, H2, Fs2]}
     torch.cuda.synchronize()
     assert _lib.status_read_clear() == 0
