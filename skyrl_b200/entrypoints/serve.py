@@ -72,7 +72,12 @@ class InferenceOnlyEntrypoint(BasePPOExp):
         client = LocalInferenceClient([engine], self.tokenizer)
         name = getattr(self.cfg.generator.inference_engine, "served_model_name", None) or t.policy.model.path
         port = self.base_port + self.env.rank if self.base_port else 0
-        srv = ServerThread(build_app(client, model_name=name), host=self.host, port=port).start()
+        from ..weight_sync.remote import make_weight_loader
+
+        dcfg = self.cfg.generator.inference_engine.delta_weight_sync
+        loader = make_weight_loader(model, engine, sync_dir=getattr(dcfg, "sync_dir", "") or None,
+                                    local_dir=getattr(dcfg, "local_checkpoint_dir", None))
+        srv = ServerThread(build_app(client, model_name=name, weight_loader=loader), host=self.host, port=port).start()
         self._servers.append(srv)
         rec = {"rank": self.env.rank, "server_url": srv.url}
         urls = [srv.url]

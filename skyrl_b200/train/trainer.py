@@ -327,6 +327,18 @@ class PPOTrainer:
     def sync_weights(self) -> None:
         """Make the freshly trained weights visible to the generation engine(s)."""
         c = self.inference_engine_client
+        if self.engine is None and self.policy is not None and hasattr(c, "fetch_weights"):
+            # stand-alone rollout servers: publish the weights and have every server load them
+            from ..weight_sync.remote import RemoteWeightSync
+
+            if getattr(self, "_remote_sync", None) is None:
+                ie = self.cfg.generator.inference_engine
+                transport = "delta" if ie.weight_sync_backend == "delta" else "path"
+                sd = getattr(ie.delta_weight_sync, "sync_dir", "") or None
+                self._remote_sync = RemoteWeightSync(c, self.policy.engine_model(), transport, sd, is_main=self.env.is_main)
+            self.policy.refresh_engine_model()
+            asyncio.run(self._remote_sync.sync()) if not self._in_event_loop() else None
+            return
         if self.policy is not None:
             self.policy.refresh_engine_model()  # TP shards / LoRA adapters -> the engine's full weights
         if hasattr(c, "increment_weight_version"):
@@ -348,6 +360,23 @@ class PPOTrainer:
             else:
                 merged[key] = vals[mesh.tp_rank]
         return merged, [u for p in parts for u in p[1]]
+
+    @staticmethod
+    def _in_event_loop() -> bool:
+        try:
+            asyncio.get_running_loop()
+            return True
+        except RuntimeError:
+            return False
+
+    async def sync_weights_async(self) -> None:
+        """``sync_weights`` for callers already inside an event loop (remote servers need awaited HTTP calls)."""
+        c = self.inference_engine_client
+        if self.engine is None and self.policy is not None and hasattr(c, "fetch_weights"):
+            self.sync_weights()  # builds the helper; the transfer itself is awaited here
+            await self._remote_sync.sync()
+        else:
+            self.sync_weights()
 
     # ------------------------------------------------------------------ one RL step
     async def train_step_async(self, prompts: List[Dict[str, Any]], prompt_token_ids=None) -> Dict[str, float]:
@@ -374,7 +403,7 @@ class PPOTrainer:
         with Timer("train_critic_and_policy", self.all_timings):
             self.all_metrics.update(self.train_critic_and_policy(batch))
         with Timer("sync_weights", self.all_timings):
-            self.sync_weights()
+            await self.sync_weights_async()
         n_tokens = int(batch["attention_mask"].sum())
         n_gen = int(batch["response_mask"].sum())
         self.all_timings["step"] = time.time() - t_step
@@ -400,7 +429,8 @@ class PPOTrainer:
         t = self.cfg.trainer
         assert self.train_dataset is not None, "train() needs a train_dataset"
         self.train_iter = StatefulBatchIterator(self.train_dataset, t.train_batch_size, shuffle=True, seed=t.seed)
-        self.load_checkpoints()
+        if self.load_checkpoints() > 0:
+            await self.sync_weights_async()  # remote servers learn about the restored weights before the first rollout
         if t.eval_before_train and self.eval_dataset is not None and self.global_step == 0:
             self._log(await self.eval_async(), self.global_step)
         total = t.epochs * len(self.train_iter)

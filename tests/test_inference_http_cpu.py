@@ -91,3 +91,49 @@ def test_router_proxies_to_servers():
 
 def test_logprob_clamping():
     assert clamp_logprobs([-1.0, None, float("nan"), float("-inf")]) == [-1.0, -9999.0, -9999.0, -9999.0]
+
+
+@pytest.mark.parametrize("transport", ["delta", "path"])
+def test_trainer_syncs_weights_to_stand_alone_server(tmp_path, transport):
+    """Disaggregated set-up in one test process: the rollout engine lives behind HTTP with its *own* weights; after an
+    RL step the server has loaded the trainer's new weights (delta replay or safetensors export) and kept serving."""
+    import torch
+
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_b200.inference.local_client import LocalInferenceClient
+    from skyrl_b200.inference.remote_client import RemoteInferenceClient
+    from skyrl_b200.inference.server import ServerThread, build_app
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+    from skyrl_b200.parallel.dist import get_env
+    from skyrl_b200.train.trainer import PPOTrainer
+    from skyrl_b200.utils.tokenizer import SyntheticTokenizer
+    from skyrl_b200.weight_sync.remote import make_weight_loader
+
+    tok = SyntheticTokenizer(2048)
+    server_model = CausalLM(PRESETS["tiny-qwen2-d128"], device="cpu", dtype=torch.float32, seed=123)  # not the trainer's
+    eng = LLMEngine(server_model, EngineConfig(block_size=16, max_num_seqs=8, max_model_len=64, enforce_eager=True, num_blocks=64),
+                    eos_token_ids=[tok.eos_token_id])
+    local = LocalInferenceClient([eng], tok)
+    srv = ServerThread(build_app(local, weight_loader=make_weight_loader(server_model, eng, local_dir=str(tmp_path / "local")))).start()
+    try:
+        cfg = SkyRLTrainConfig.from_cli_overrides([
+            "trainer.policy.model.path=tiny-qwen2-d128", "trainer.train_batch_size=2", "trainer.policy_mini_batch_size=2",
+            "generator.n_samples_per_prompt=4", "trainer.max_prompt_length=16", "generator.sampling_params.max_generate_length=8",
+            "environment.env_class=synthetic_bernoulli", "trainer.bf16=false", "trainer.policy.optimizer_config.lr=1e-3",
+            "trainer.policy.optimizer_config.num_warmup_steps=0", "trainer.resume_mode=none", "trainer.algorithm.use_kl_loss=false",
+            "trainer.placement.colocate_all=false", "generator.inference_engine.external_server_urls=['" + srv.url + "']",
+            f"generator.inference_engine.weight_sync_backend={'delta' if transport == 'delta' else 'broadcast'}",
+            f"generator.inference_engine.delta_weight_sync.sync_dir={tmp_path}/sync", "trainer.logger=console"])
+        client = RemoteInferenceClient([srv.url], tokenizer=tok)
+        tr = PPOTrainer(cfg, tokenizer=tok, inference_engine_client=client, env=get_env())
+        tr.build_models()
+        assert tr.engine is None
+        prompts = [{"prompt": [{"role": "user", "content": f"q{i}"}], "uid": f"u{i}", "env_extras": {"p": 0.5, "seed": i}}
+                   for i in range(2)]
+        for _ in range(2):  # first sync publishes the base, the second one a delta
+            tr.train_step(prompts)
+            assert torch.equal(server_model.flat_params[: tr.policy.model.flat_numel], tr.policy.model.flat_params[: tr.policy.model.flat_numel])
+        assert eng.weight_version >= 2 and not eng.paused
+    finally:
+        srv.stop()
