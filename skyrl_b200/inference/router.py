@@ -101,14 +101,14 @@ def build_router_app(router: SessionRouter):
                     router.mark(u, False)
             await asyncio.sleep(2.0)
 
-    @app.on_event("startup")
     async def _start():
         holder["probe"] = asyncio.create_task(probe_loop())
 
-    @app.on_event("shutdown")
     async def _stop():
         holder["probe"].cancel()
         if "s" in holder:
             await holder["s"].close()
 
+    app.router.on_startup.append(_start)
+    app.router.on_shutdown.append(_stop)
     return app
