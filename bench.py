@@ -266,6 +266,9 @@ def main() -> None:
             "e2e": {"value": e2e_all / wall, "timed_with": "host clock over %d further steps" % K, "unit": "tokens/s", "h2d_bytes_per_step": (_lib.H2D_BYTES - h0) / K,
                     "d2h_bytes_per_step": (_lib.D2H_BYTES - d0) / K},
             "gpu_launches": launches, "device_status": status, "impl": "ours",
+            # trainer -> rollout weight sync: the colocated engine reads the parameter buffer the optimizer's fused
+            # push just wrote, so the separate sync phase only bumps the weight version
+            "weight_sync_ms": 1e3 * float(last.get("timing/sync_weights", 0.0)),
         }
         print(json.dumps(out), flush=True)
     pdist.shutdown()
