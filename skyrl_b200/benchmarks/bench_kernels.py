@@ -39,7 +39,7 @@ def timeit(fn, iters, warmup=3):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead"])
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -93,6 +93,39 @@ def main() -> None:
         fl = 4.0 * a.seqs * a.nq * a.seqlen * a.seqlen * D / 2
         out.update(tokens=T, seqlen=a.seqlen, fwd_ms=ms_f, fwd_tflops=fl / ms_f / 1e9, bwd_ms=ms_b,
                    bwd_tflops=2.5 * fl / ms_b / 1e9, fwd_fraction_of_measured_bf16_burst=fl / ms_f / 1e9 / a.peak_tflops)
+    elif a.which in ("tp_gather", "tp_scatter"):
+        # Tensor-parallel GEMM modes with the ranks emulated by separate buffers of this GPU (the kernel code path --
+        # copy warps reading "peer" shards, epilogue storing into "peer" slots -- is the one used across GPUs; only
+        # the link is missing, so this measures kernel overhead, not NVLink).
+        import ctypes
+
+        from skyrl_b200.ops import _lib
+        from skyrl_b200.parallel import tensor_parallel as tpm
+
+        R = 4  # emulated ranks
+        M, K, N = a.m, a.k, a.n
+        rpr = M // R
+        lib = tpm._k()
+        w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+        if a.which == "tp_gather":
+            shards = [(torch.randn(rpr, K, device="cuda") * 0.5).to(torch.bfloat16) for _ in range(R)]
+            a_full = torch.zeros(M, K, **bf)
+            a_full[:rpr] = shards[0]
+            outp = torch.empty(M, N, **bf)
+            flags = torch.zeros(M // 128 + 2, dtype=torch.int32, device="cuda")
+            peers = (ctypes.c_void_p * R)(*[t.data_ptr() for t in shards])
+            fn = lambda: _lib.check(lib.sb_gemm_tp(a_full.data_ptr(), w.data_ptr(), outp.data_ptr(), None, M, N, K, K, K, N, 0, 0, 1, 0,  # noqa: E731
+                                                   peers, None, R, 0, rpr, 0, flags.data_ptr(), 0, _lib.stream_ptr()), "tp")
+        else:
+            x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+            dests = [torch.empty(R, rpr, N, **bf) for _ in range(R)]
+            outs = (ctypes.c_void_p * R)(*[t.data_ptr() for t in dests])
+            fn = lambda: _lib.check(lib.sb_gemm_tp(x.data_ptr(), w.data_ptr(), None, None, M, N, K, K, K, N, 0, 0, 0, 1, None,  # noqa: E731
+                                                   outs, R, 0, rpr, rpr * N, None, 0, _lib.stream_ptr()), "tp")
+        ms = timeit(fn, a.iters)
+        fl = 2.0 * M * N * K
+        out.update(m=M, n=N, k=K, emulated_ranks=R, ms=ms, tflops=fl / ms / 1e9,
+                   fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
     else:
         V, H = 151936, 1536
         h = (torch.randn(a.tokens, H, device="cuda") * 0.5).to(torch.bfloat16)
