@@ -94,6 +94,7 @@ def main() -> None:
     ap.add_argument("--max-tokens-per-microbatch", type=int, default=32768)
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size of the training model (1 = sharded data parallel)")
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel size (MoE models)")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size of the training model")
     ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size of the training model")
     ap.add_argument("--reuse-train-forward", action="store_true",
                     help="take old log-probs from the training forward (exact with one optimizer update per step); "
@@ -133,6 +134,8 @@ def main() -> None:
                                     f"trainer.policy.megatron_config.tensor_model_parallel_size={args.tp}"] if args.tp > 1 else []),
         *(["trainer.strategy=megatron", f"trainer.policy.megatron_config.expert_model_parallel_size={args.ep}"]
           if args.ep > 1 else []),
+        *(["trainer.strategy=megatron", f"trainer.policy.megatron_config.pipeline_model_parallel_size={args.pp}"]
+          if args.pp > 1 else []),
         *([f"trainer.policy.sequence_parallel_size={args.sp}", f"trainer.ref.sequence_parallel_size={args.sp}"]
           if args.sp > 1 else []),
         f"trainer.b200.reuse_train_forward_for_old_logprobs={'true' if args.reuse_train_forward else 'false'}"])
@@ -254,6 +257,7 @@ def main() -> None:
             "random-init weights)",
             "config": {"model": args.model, "global_batch": P * n * world, "seq_len": PROMPT_LEN + RESP_MAX,
                        "parallelism": (f"dp{world} x ep{args.ep} (fused expert dispatch/combine)" if args.ep > 1 else
+                                       f"dp{world // args.pp} x pp{args.pp} (layer stages)" if args.pp > 1 else
                                        f"dp{world // args.sp} x sp{args.sp} (Ulysses, fused projections)" if args.sp > 1 else
                                        f"dp{world} (sharded optimizer, colocated engine per GPU)" if args.tp == 1 else
                                        f"dp{world // args.tp} x tp{args.tp} (fused GEMM collectives, colocated engine per GPU)"),

@@ -61,6 +61,26 @@ class PipelineStage(CausalLM):
         for name, prm in self.named_flat_views():
             prm.copy_(full.p(self._full_name(name)).detach().to(prm.dtype))
 
+    def replicated_ranges(self) -> List[Tuple[int, int]]:
+        """Flat-buffer ranges whose gradient is identical on every stage after ``reduce_replicated_grads`` (the tied
+        embedding table); they count once in the global gradient norm."""
+        if not self.full_args.tie_word_embeddings:
+            return []
+        o, n = self.offsets["embed"]
+        return [(o, o + n)]
+
+    def reduce_replicated_grads(self) -> None:
+        """Tied embeddings: the first stage's lookup gradient and the last stage's LM-head gradient are summed (the
+        stages in between contribute zeros), so that every copy of the table takes the same update."""
+        fg = getattr(self, "flat_main_grad", None)
+        if self.pp_size == 1 or not self.full_args.tie_word_embeddings or fg is None:
+            return
+        o, n = self.offsets["embed"]
+        dist.all_reduce(fg[o : o + n], group=self.group)
+
+    def gather_full_state(self) -> Dict[str, torch.Tensor]:
+        return PipelinedCausalLM(self).gather_full_state()
+
     def stage_forward(self, input_ids, positions, cu_seqlens, max_seqlen: int, x_in: Optional[torch.Tensor]) -> torch.Tensor:
         """First stage: embeds ``input_ids``. Others: continue from ``x_in`` (the residual stream with every pending
         update already added).  Last stage returns final-normed hidden states, others the residual stream."""
@@ -136,3 +156,96 @@ def broadcast_from_last_stage(t: Optional[torch.Tensor], shape, dtype, stage: Pi
     buf = t.contiguous() if stage.is_last else torch.empty(shape, device=dev, dtype=dtype)
     dist.broadcast(buf, src=_peer(stage.group, stage.pp_size - 1), group=stage.group)
     return buf
+
+
+# ----------------------------------------------------------------------------- worker-facing wrapper
+class _RelayFn(torch.autograd.Function):
+    """Non-last stages: ship this stage's output to the next stage; in backward, receive its gradient from there.
+    The value returned to the caller is a placeholder that carries the autograd edge (it has no numeric meaning)."""
+
+    @staticmethod
+    def forward(ctx, out, next_rank, group):
+        ctx.next_rank, ctx.group, ctx.shape, ctx.dtype = next_rank, group, out.shape, out.dtype
+        dist.send(out.detach().contiguous(), dst=next_rank, group=group)
+        return out.new_zeros(())
+
+    @staticmethod
+    def backward(ctx, _g):
+        gout = torch.empty(ctx.shape, dtype=ctx.dtype, device=_g.device)
+        dist.recv(gout, src=ctx.next_rank, group=ctx.group)
+        return gout, None, None
+
+
+class PipelinedCausalLM:
+    """What a worker needs from a pipeline-parallel policy: per-token log-probs of a packed batch on *every* rank of
+    the pipeline group, with a backward pass that runs through all stages.
+
+    One micro-batch travels through the stages at a time (activations forward, gradients backward, both by send/recv);
+    the last stage scores the tokens and broadcasts the log-probs, so the loss code runs identically on every stage.
+    On the last stage the log-probs are attached to the graph; on the others a zero-valued relay term carries the
+    autograd edge, so that calling ``backward()`` on the (identical) loss of every rank drives the whole chain.
+    Micro-batches are not interleaved by this wrapper: ``pipeline_forward_backward`` is the overlapped schedule for
+    callers that own the micro-batch loop."""
+
+    def __init__(self, stage: PipelineStage):
+        self.stage = stage
+
+    def pred_logprobs(self, ids, pos, cu, max_seqlen, pred_index, targets, temp: float = 1.0, with_entropy: bool = False):
+        st = self.stage
+        g = st.group
+        H = st.args.hidden_size
+        dev, dt = st.flat_params.device, st.flat_params.dtype
+        grad_on = torch.is_grad_enabled()
+        x_in = None
+        if not st.is_first:
+            x_in = torch.empty((ids.numel(), H), device=dev, dtype=dt)
+            dist.recv(x_in, src=_peer(g, st.pp_rank - 1), group=g)
+            if grad_on:
+                x_in.requires_grad_()
+                prev = _peer(g, st.pp_rank - 1)
+                x_in.register_hook(lambda gr: dist.send(gr.contiguous(), dst=prev, group=g))
+        out = st.stage_forward(ids, pos, cu, max_seqlen, x_in)
+        n = pred_index.numel()
+        last = _peer(g, st.pp_size - 1)
+        if st.is_last:
+            lp, ent = st.token_logprobs(out[pred_index], targets, temp, with_entropy=with_entropy)
+            pack = torch.stack([lp.detach().float(), (ent.detach().float() if ent is not None else torch.zeros_like(lp.float()))])
+            dist.broadcast(pack, src=last, group=g)
+            return lp, ent
+        relay = _RelayFn.apply(out, _peer(g, st.pp_rank + 1), g) if grad_on else None
+        if not grad_on:
+            dist.send(out.detach().contiguous(), dst=_peer(g, st.pp_rank + 1), group=g)
+        pack = torch.empty((2, n), device=dev, dtype=torch.float32)
+        dist.broadcast(pack, src=last, group=g)
+        lp = pack[0]
+        ent = pack[1] if with_entropy else None
+        if relay is not None:
+            lp = lp + relay  # numerically a no-op; gives this rank's loss a path into its stage
+        return lp, ent
+
+    @torch.no_grad()
+    def gather_full_state(self) -> Dict[str, torch.Tensor]:
+        """Every stage's parameters on every rank, keyed by the unsharded model's names."""
+        st = self.stage
+        out: Dict[str, torch.Tensor] = {}
+        for r in range(st.pp_size):
+            names = [None]
+            if r == st.pp_rank:
+                names = [[(st._full_name(n), tuple(p.shape)) for n, p in st.named_flat_views()]]
+            dist.broadcast_object_list(names, src=_peer(st.group, r), group=st.group)
+            own = dict(st.named_flat_views()) if r == st.pp_rank else {}
+            lo, _ = stage_layer_range(st.full_args.num_layers, st.pp_size, r)
+            for full_name, shape in names[0]:
+                if r == st.pp_rank:
+                    parts = full_name.split(".")
+                    local = full_name if parts[0] != "layers" else ".".join(["layers", str(int(parts[1]) - lo)] + parts[2:])
+                    t = own[local].detach().contiguous()
+                else:
+                    t = torch.empty(shape, device=st.flat_params.device, dtype=st.flat_params.dtype)
+                dist.broadcast(t, src=_peer(st.group, r), group=st.group)
+                is_layer = full_name.startswith("layers.")
+                first_owner = full_name == "embed" and r == 0
+                last_owner = full_name in ("final_norm", "lm_head") and r == st.pp_size - 1
+                if is_layer or first_owner or last_owner:
+                    out[full_name] = t
+        return out

@@ -181,17 +181,16 @@ def validate_parallel_cfg(cfg, world_size: int = 1) -> None:
         if sp > 1:
             raise ValueError("policy.sequence_parallel_size (Ulysses) belongs to strategy=fsdp; with strategy=megatron "
                              "sequence parallelism is implied by tensor_model_parallel_size > 1")
-        if pp > 1:
-            raise ValueError("pipeline_model_parallel_size > 1 is not selectable from the trainer yet "
-                             "(skyrl_b200.parallel.pipeline provides the stage model and schedule)")
+        if pp > 1 and (tp > 1 or ep > 1):
+            raise ValueError("pipeline parallelism cannot be combined with tensor or expert parallelism in this build")
         if cp > 1:
             raise ValueError("context_parallel_size > 1 is not supported; use Ulysses sequence parallelism (strategy=fsdp)")
         if tp > 1 and ep > 1:
             raise ValueError("tensor and expert parallelism cannot be combined in this build")
-        if t.policy.model.lora.rank > 0 and (tp > 1 or ep > 1):
+        if t.policy.model.lora.rank > 0 and (tp > 1 or ep > 1 or pp > 1):
             raise ValueError("LoRA is supported with the data-parallel strategy only")
     for name, size in (("tensor_model_parallel_size", tp), ("expert_model_parallel_size", ep),
-                       ("policy.sequence_parallel_size", sp)):
+                       ("pipeline_model_parallel_size", pp), ("policy.sequence_parallel_size", sp)):
         if size > 1 and world_size % size != 0:
             raise ValueError(f"{name}={size} does not divide the number of ranks ({world_size})")
         if size > 8:

@@ -146,6 +146,24 @@ class ModelWorker:
             model.load_from_full(full)
             del full
             peer_ctx = None  # the flat-buffer peer optimizer spans the whole world; TP uses the DP group over NCCL
+        pp_size = self._pp_size_from_cfg(cfg) if (model is None and tp_size == 1) else 1
+        self.pipe = None
+        if pp_size > 1:
+            # consecutive ranks hold consecutive layer ranges; one data shard per pipeline group
+            from ..models.decoder import resolve_model_args
+            from ..parallel.dist import build_mesh
+            from ..parallel.pipeline import PipelinedCausalLM, PipelineStage
+
+            if value_head:
+                raise NotImplementedError("the critic runs without pipeline parallelism")
+            self.mesh = build_mesh(pp_size, self.env)
+            model = PipelineStage(resolve_model_args(model_path), self.mesh.tp_rank, pp_size, group=self.mesh.tp_group,
+                                  device=dev, dtype=dtype, seed=None)
+            full = build_model(model_path, device="cpu", dtype=torch.float32, seed=seed)
+            model.load_from_full(full)
+            del full
+            self.pipe = PipelinedCausalLM(model)
+            peer_ctx = None
         ep_size = self._ep_size_from_cfg(cfg) if (model is None and tp_size == 1) else 1
         self.expert_parallel = ep_size > 1
         if self.expert_parallel:
@@ -229,7 +247,7 @@ class ModelWorker:
             if self.mesh is not None:
                 from ..models.tp_decoder import REPLICATED_LEAVES
 
-                if self.expert_parallel:
+                if self.expert_parallel or self.pipe is not None:
                     dups = model.replicated_ranges()
                 else:
                     dups = [(o, o + n) for name, (o, n) in model.offsets.items() if name.split(".")[-1] in REPLICATED_LEAVES]
@@ -343,6 +361,12 @@ class ModelWorker:
         return int(getattr(cfg.policy.megatron_config, "expert_model_parallel_size", 1) or 1)
 
     @staticmethod
+    def _pp_size_from_cfg(cfg) -> int:
+        if getattr(cfg, "strategy", "fsdp") != "megatron":
+            return 1
+        return int(getattr(cfg.policy.megatron_config, "pipeline_model_parallel_size", 1) or 1)
+
+    @staticmethod
     def _tp_size_from_cfg(cfg) -> int:
         if getattr(cfg, "strategy", "fsdp") != "megatron":
             return 1
@@ -371,6 +395,9 @@ class ModelWorker:
             return self.model.token_logprobs(h[pv.pred_index], pv.targets, temp, with_entropy=with_entropy)
         from ..models.tp_decoder import pad_packed_for_tp
 
+        if self.pipe is not None:
+            return self.pipe.pred_logprobs(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen, pv.pred_index, pv.targets,
+                                           temp, with_entropy=with_entropy)
         if self.expert_parallel:
             # every rank routes its own tokens, but the routing tables are exchanged as equal-sized blocks: pad this
             # rank's packed batch to the longest one in the expert-parallel group

@@ -172,6 +172,42 @@ def check_expert_parallel(env):
     assert rel(wd_l.grad, wd_f.grad[r * El : (r + 1) * El]) < 1e-4
 
 
+def check_pipelined_wrapper(env):
+    """Worker-facing pipeline wrapper: identical log-probs on every stage, backward through the chain, full-state gather."""
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+    from skyrl_b200.parallel.pipeline import PipelinedCausalLM, PipelineStage
+
+    W, r = env.world_size, env.rank
+    a = PRESETS["tiny-llama"]
+    full = CausalLM(a, device="cpu", dtype=torch.float32, seed=21)
+    stage = PipelineStage(a, r, W, device="cpu", dtype=torch.float32, seed=21)
+    pm = PipelinedCausalLM(stage)
+    g = torch.Generator().manual_seed(8)
+    ids = torch.randint(4, a.vocab_size, (40,), generator=g).int()
+    pos = torch.cat([torch.arange(15), torch.arange(25)]).int()
+    cu = torch.tensor([0, 15, 40]).int()
+    pred = torch.tensor([3, 4, 5, 20, 21, 38])
+    tgt = ids[pred + 1].int()
+    wts = torch.linspace(0.5, 1.5, pred.numel())
+    lp, _ = pm.pred_logprobs(ids, pos, cu, 32, pred, tgt)
+    (lp * wts).sum().backward()
+    h = full(ids, pos, cu, 32)
+    lpf, _ = full.token_logprobs(h[pred], tgt)
+    (lpf * wts).sum().backward()
+    assert rel(lp.detach(), lpf.detach()) < 1e-4, rel(lp.detach(), lpf.detach())
+    for name, prm in stage.named_flat_views():
+        ref = full.p(stage._full_name(name)).grad
+        used = name.startswith("layers.") or (name == "embed" and stage.is_first) or (name in ("final_norm", "lm_head") and stage.is_last)
+        if used:
+            assert prm.grad is not None and rel(prm.grad, ref) < 2e-3, (name, rel(prm.grad, ref))
+    with torch.no_grad():
+        lp2, _ = pm.pred_logprobs(ids, pos, cu, 32, pred, tgt)
+    assert rel(lp2, lpf.detach()) < 1e-4
+    st = pm.gather_full_state()
+    for name, _ in full.named_flat_views():
+        assert torch.equal(st[name], full.p(name).detach()), name
+
+
 def check_ep_model(env):
     """Expert-parallel model over both ranks' tokens == unsharded model over the union of the data."""
     from skyrl_b200.models.decoder import PRESETS, CausalLM
@@ -266,6 +302,7 @@ def main():
     check_expert_parallel(env)
     check_pipeline(env)
     check_ep_model(env)
+    check_pipelined_wrapper(env)
     dist.barrier()
     if env.rank == 0:
         print("CPU_CHECKS_OK", flush=True)

@@ -40,3 +40,9 @@ def test_gloo_two_rank_expert_parallel_rl_step():
     p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-moe",
               "--prompts-per-gpu", "1", "--ep", "2"], port=29635)
     assert p.returncode == 0 and "x ep2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_gloo_two_rank_pipeline_parallel_rl_step():
+    p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-llama",
+              "--prompts-per-gpu", "1", "--pp", "2"], port=29636)
+    assert p.returncode == 0 and "x pp2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
