@@ -209,16 +209,21 @@ class PipelinedCausalLM:
         last = _peer(g, st.pp_size - 1)
         if st.is_last:
             lp, ent = st.token_logprobs(out[pred_index], targets, temp, with_entropy=with_entropy)
-            pack = torch.stack([lp.detach().float(), (ent.detach().float() if ent is not None else torch.zeros_like(lp.float()))])
+            # row 0: log-probs, row 1: entropies; the extra column says whether entropies were computed at all
+            pack = torch.zeros((2, n + 1), device=dev, dtype=torch.float32)
+            pack[0, :n] = lp.detach().float()
+            if ent is not None:
+                pack[1, :n] = ent.detach().float()
+                pack[1, n] = 1.0
             dist.broadcast(pack, src=last, group=g)
             return lp, ent
         relay = _RelayFn.apply(out, _peer(g, st.pp_rank + 1), g) if grad_on else None
         if not grad_on:
             dist.send(out.detach().contiguous(), dst=_peer(g, st.pp_rank + 1), group=g)
-        pack = torch.empty((2, n), device=dev, dtype=torch.float32)
+        pack = torch.empty((2, n + 1), device=dev, dtype=torch.float32)
         dist.broadcast(pack, src=last, group=g)
-        lp = pack[0]
-        ent = pack[1] if with_entropy else None
+        lp = pack[0, :n]
+        ent = pack[1, :n] if bool(pack[1, n] > 0) else None
         if relay is not None:
             lp = lp + relay  # numerically a no-op; gives this rank's loss a path into its stage
         return lp, ent

@@ -51,3 +51,10 @@ def test_bench_two_gpus_sequence_parallel_and_expert_parallel_tiny():
     p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-moe",
               "--prompts-per-gpu", "4", "--ep", "2"], port=29622)
     assert p.returncode == 0 and "x ep2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_bench_two_gpus_pipeline_parallel_tiny():
+    p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-tp",
+              "--prompts-per-gpu", "4", "--pp", "2"], port=29623)
+    assert p.returncode == 0 and "x pp2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
