@@ -39,7 +39,11 @@ def timeit(fn, iters, warmup=3):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter"])
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe"])
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--ffn", type=int, default=768)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -126,6 +130,28 @@ def main() -> None:
         fl = 2.0 * M * N * K
         out.update(m=M, n=N, k=K, emulated_ranks=R, ms=ms, tflops=fl / ms / 1e9,
                    fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
+    elif a.which == "moe":
+        # one mixture-of-experts FFN layer (router, grouped gate/up GEMM, SwiGLU, grouped down GEMM, weighted combine)
+        from skyrl_b200.models.moe import moe_ffn
+        from skyrl_b200.ops import grouped_gemm as gg
+
+        T, H, E, F, k = a.tokens, a.hidden, a.experts, a.ffn, a.topk
+        h = (torch.randn(T, H, device="cuda") * 0.5).to(torch.bfloat16)
+        rt = (torch.randn(E, H, device="cuda") * 0.5).to(torch.bfloat16)
+        wgu = (torch.randn(E, 2 * F, H, device="cuda") * 0.02).to(torch.bfloat16)
+        wd = (torch.randn(E, H, F, device="cuda") * 0.02).to(torch.bfloat16)
+        with torch.no_grad():
+            ms_layer = timeit(lambda: moe_ffn(h, rt, wgu, wd, k, True), a.iters)
+            ids = torch.randint(0, E, (T * k,), device="cuda")
+            plan = gg.plan_groups(ids, E)
+            x = torch.zeros((plan.m_cap, H), **bf)
+            ms_gu = timeit(lambda: gg.grouped_nt(x, wgu, plan), a.iters)
+            act = torch.zeros((plan.m_cap, F), **bf)
+            ms_dn = timeit(lambda: gg.grouped_nt(act, wd, plan), a.iters)
+        fl_gu, fl_dn = 2.0 * T * k * 2 * F * H, 2.0 * T * k * F * H
+        out.update(tokens=T, hidden=H, experts=E, ffn=F, topk=k, padded_rows=plan.m_cap, layer_fwd_ms=ms_layer,
+                   gate_up_ms=ms_gu, gate_up_tflops=fl_gu / ms_gu / 1e9, down_ms=ms_dn, down_tflops=fl_dn / ms_dn / 1e9,
+                   layer_tflops=(fl_gu + fl_dn) / ms_layer / 1e9)
     else:
         V, H = 151936, 1536
         h = (torch.randn(a.tokens, H, device="cuda") * 0.5).to(torch.bfloat16)

@@ -75,6 +75,17 @@ struct TpArgs {
   int gather_idx, scatter_idx;
   const int* idx_rank;
   const int* idx_row;
+  // Grouped (per-expert) products; the tables live on the device, so no expert count ever visits the host.
+  //  group_mode 1: the rows of A / C are grouped in blocks of 128: m-block pm belongs to expert tile_expert[pm]
+  //    (< 0: unused block, skipped) and multiplies that expert's B matrix, which starts group_b_rows * expert rows
+  //    further down the B tensor map.
+  //  group_mode 2 (weight gradients): work item = (expert, output tile); the contraction runs over the row range
+  //    [k_off[e], k_off[e + 1]) of both operands (multiples of 64; an empty range skips the item) and the result
+  //    goes to C + e * split_stride.
+  int group_mode;
+  int group_b_rows;
+  const int* tile_expert;
+  const int* k_off;
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
@@ -123,6 +134,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles = tiles_mn * splits;
   const int k_blocks = (K + kBK - 1) / kBK;
   const int kpb = (k_blocks + splits - 1) / splits;  // k blocks per slice (host guarantees no empty slice)
+  auto krange = [&](int ks, int& kb0, int& kb1) {
+    if (tp.group_mode == 2) {
+      kb0 = __ldg(tp.k_off + ks) / kBK;
+      kb1 = __ldg(tp.k_off + ks + 1) / kBK;
+    } else {
+      kb0 = ks * kpb;
+      kb1 = min(k_blocks, kb0 + kpb);
+    }
+  };
   // GATHER: logical m-block 0 is the first block of the local shard, then the next rank's, and so on
   const int m_rot = (GATHER && !tp.gather_cols && !tp.gather_idx) ? tp.my_rank * (tp.rows_per_rank / kBM) : 0;
   auto rot = [&](int pm) { return GATHER ? (pm + m_rot) % tm.m_blocks : pm; };
@@ -200,7 +220,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (tm.m_blocks <= 64) ready_mask |= 1ull << pm;
           }
         }
-        const int kb0 = ks * kpb, kb1 = min(k_blocks, kb0 + kpb);
+        int kb0, kb1, b_off = 0;
+        krange(ks, kb0, kb1);
+        if (tp.group_mode == 1) {
+          const int e = __ldg(tp.tile_expert + pm);
+          if (e < 0) continue;
+          b_off = e * tp.group_b_rows;
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % Cfg::kStages;
           const uint32_t ph = (it / Cfg::kStages) & 1;
@@ -220,10 +246,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (b_done) continue;
           if (!B_MN) {
-            tma_load_2d(sB, &tmB, &full[s], kb * kBK, pn * BN);
+            tma_load_2d(sB, &tmB, &full[s], kb * kBK, pn * BN + b_off);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, &full[s], pn * BN + j * 64, kb * kBK);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, &full[s], pn * BN + j * 64, kb * kBK + b_off);
           }
         }
       }
@@ -234,14 +260,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
       int it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int ks = tile / tiles_mn;
+        int kb0, kb1;
+        krange(ks, kb0, kb1);
+        if (tp.group_mode == 1) {
+          int pm, pn;
+          tm.get(tile - ks * tiles_mn, pm, pn);
+          if (__ldg(tp.tile_expert + pm) < 0) continue;
+        }
+        if (tp.group_mode && kb1 <= kb0) continue;
         const int acc = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
+        ++tcount;
         if (!mbar_wait(&tempty[acc], aph ^ 1, status, 0x201)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const int ks = tile / tiles_mn;
-        const int kb0 = ks * kpb, kb1 = min(k_blocks, kb0 + kpb);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % Cfg::kStages;
           const uint32_t ph = (it / Cfg::kStages) & 1;
@@ -269,13 +303,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------ epilogue -----------------------------------
     const int q = warp & 3;  // TMEM lane quadrant this warp may access
     int tcount = 0;
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tcount) {
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
       int pm, pn;
       const int ks = tile / tiles_mn;
       tm.get(tile - ks * tiles_mn, pm, pn);
       pm = rot(pm);
+      if (tp.group_mode) {
+        int kb0, kb1;
+        krange(ks, kb0, kb1);
+        if (kb1 <= kb0 || (tp.group_mode == 1 && __ldg(tp.tile_expert + pm) < 0)) continue;
+      }
       const int acc = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
+      ++tcount;
       if (!mbar_wait(&tfull[acc], aph, status, 0x301)) break;
       tc_fence_after();
       const int row = pm * kBM + q * 32 + lane;
@@ -530,6 +570,47 @@ static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bia
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
+// Grouped launch (see TpArgs::group_mode).  mode 1: A [M, K] with row blocks owned by experts, B = n_groups stacked
+// matrices ([N, K] each when !B_MN, [K, N] each when B_MN).  mode 2: A [rows, M] and B [rows, N], both MN-major,
+// C = n_groups stacked [M, N] results.
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm_grouped(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                               long long ldc, int out_mode, int mode, int n_groups, const int* tile_expert,
+                               const int* k_off, long long group_c_stride, int rows_total, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  const CUtensorMap* ta;
+  const CUtensorMap* tb;
+  TpArgs tp{};
+  tp.group_mode = mode;
+  tp.tile_expert = tile_expert;
+  tp.k_off = k_off;
+  int splits = 1;
+  if (mode == 1) {
+    ta = get_tmap_bf16_2d(A, M, K, lda, kBM);
+    tb = B_MN ? get_tmap_bf16_2d(B, static_cast<long long>(n_groups) * K, N, ldb, 64)
+              : get_tmap_bf16_2d(B, static_cast<long long>(n_groups) * N, K, ldb, BN);
+    tp.group_b_rows = B_MN ? K : N;
+  } else {
+    ta = get_tmap_bf16_2d(A, rows_total, M, lda, 64);
+    tb = get_tmap_bf16_2d(B, rows_total, N, ldb, 64);
+    splits = n_groups;
+  }
+  if (!ta || !tb) return SB_ERR_TMAP;
+  static bool attr_set = false;
+  auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
+      return SB_ERR_CUDA;
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) * splits;
+  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+  const cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, *ta, *tb, C,
+                                   static_cast<const __nv_bfloat16*>(nullptr), M, N, K, ldc, out_mode, splits,
+                                   group_c_stride, device_status_ptr(), tp, 0);
+  return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
 template <bool A_MN, bool B_MN>
 static int dispatch_bn(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                        long long ldb, long long ldc, int out_mode, int bn_hint, cudaStream_t stream, int prefetch_b = 0) {
@@ -597,6 +678,41 @@ int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M,
   return sb::dispatch_bn<true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_mode, bn_hint, st);
 }
 
+
+// Grouped products for mixture-of-experts layers; every table is device memory.
+//   mode 1, b_mn = 0: C[r, :] = A[r, :] * B[e(r)]^T   A [M, K], B [n_groups, N, K], C [M, N]; tile_expert[M / 128]
+//   mode 1, b_mn = 1: C[r, :] = A[r, :] * B[e(r)]     A [M, K], B [n_groups, K, N], C [M, N]
+//   mode 2:           C[e] (+)= A[rows_e, :]^T * B[rows_e, :]   A [rows, M], B [rows, N], C [n_groups, M, N];
+//                     rows_e = [k_off[e], k_off[e + 1]), multiples of 64; experts without rows leave C[e] untouched.
+// M of mode 1 must be a multiple of 128 (whole row blocks).
+int sb_gemm_grouped(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                    int b_mn, int out_mode, int mode, int n_groups, const int* tile_expert, const int* k_off,
+                    long long group_c_stride, int rows_total, void* stream) {
+  if (M <= 0 || N <= 0 || n_groups <= 0 || (lda & 7) || (ldb & 7) || out_mode < 0 || out_mode > 2) return SB_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (mode == 1) {
+    if (K <= 0 || (M % sb::kBM) != 0 || !tile_expert) return SB_ERR_ARG;
+    const bool wide = N >= 256;
+    if (!b_mn) {
+      return wide ? sb::launch_gemm_grouped<256, false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_mode, 1, n_groups,
+                                                               tile_expert, nullptr, 0, 0, st)
+                  : sb::launch_gemm_grouped<128, false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_mode, 1, n_groups,
+                                                               tile_expert, nullptr, 0, 0, st);
+    }
+    return wide ? sb::launch_gemm_grouped<256, false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_mode, 1, n_groups,
+                                                            tile_expert, nullptr, 0, 0, st)
+                : sb::launch_gemm_grouped<128, false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_mode, 1, n_groups,
+                                                            tile_expert, nullptr, 0, 0, st);
+  }
+  if (mode == 2) {
+    if (!k_off || rows_total <= 0 || (rows_total % sb::kBK) != 0) return SB_ERR_ARG;
+    return N >= 256 ? sb::launch_gemm_grouped<256, true, true>(A, B, C, M, N, rows_total, lda, ldb, ldc, out_mode, 2,
+                                                               n_groups, nullptr, k_off, group_c_stride, rows_total, st)
+                    : sb::launch_gemm_grouped<128, true, true>(A, B, C, M, N, rows_total, lda, ldb, ldc, out_mode, 2,
+                                                               n_groups, nullptr, k_off, group_c_stride, rows_total, st);
+  }
+  return SB_ERR_ARG;
+}
 
 // Split-K product for skinny problems (decode: M <= a few hundred rows): x[M,K] * W[N,K]^T as `splits` fp32
 // partial sums, partial s at C + s * split_stride (row stride ldc).  `splits` is clamped so that no slice is

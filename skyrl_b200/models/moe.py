@@ -12,7 +12,8 @@ from __future__ import annotations
 import torch
 
 from ..ops import elementwise as ew
-from ..ops import gemm
+from ..ops import gemm  # noqa: F401
+from ..ops import grouped_gemm as gg
 
 
 def route_topk(h: torch.Tensor, router_w: torch.Tensor, top_k: int, norm_topk_prob: bool):
@@ -43,28 +44,26 @@ def moe_ffn(h: torch.Tensor, router_w: torch.Tensor, wgu: torch.Tensor, wd: torc
         if norm_topk_prob:
             w = w / w.sum(dim=-1, keepdim=True)
     flat_e = idx.reshape(-1)
-    order = torch.argsort(flat_e, stable=True)
-    tok = torch.arange(T, device=h.device).repeat_interleave(top_k)[order]
-    counts = torch.bincount(flat_e, minlength=E).tolist()
-    x = h[tok]  # rows grouped by expert
-    out_rows = []
-    s = 0
-    for e in range(E):
-        n = counts[e]
-        if n == 0:
-            continue
-        xe = x[s : s + n]
-        w1, w2 = wgu[e], wd[e]
-        if qat is not None and qat.enabled and torch.is_grad_enabled():  # fake-INT4 expert weights, straight-through
-            from .qat import fake_int4
+    plan = gg.plan_groups(flat_e, E)
+    tok = torch.arange(T, device=h.device).repeat_interleave(top_k)[plan.order]
+    # rows grouped by expert, every expert's range padded to whole 128-row tiles; padding rows are zero whenever a
+    # weight gradient will be formed from them
+    alloc = torch.zeros if torch.is_grad_enabled() else torch.empty
+    x = alloc((plan.m_cap, H), device=h.device, dtype=h.dtype).index_copy(0, plan.dst_row, h[tok])
+    w1, w2 = wgu, wd
+    if qat is not None and qat.enabled and torch.is_grad_enabled():  # fake-INT4 expert weights, straight-through
+        from .qat import fake_int4
 
-            w1 = fake_int4(w1, qat.group_size, True, qat.scale_divisor, qat.q_min)
-            w2 = fake_int4(w2, qat.group_size, True, qat.scale_divisor, qat.q_min)
-        gu = gemm.linear(xe, w1)
-        out_rows.append(gemm.linear(ew.swiglu(gu), w2))
-        s += n
-    y = torch.cat(out_rows, dim=0) if out_rows else x.new_zeros((0, H))
-    wf = w.reshape(-1)[order].to(y.dtype)
+        w1 = fake_int4(w1, qat.group_size, True, qat.scale_divisor, qat.q_min)
+        w2 = fake_int4(w2, qat.group_size, True, qat.scale_divisor, qat.q_min)
+        # the fp32 gradient buffers belong to the parameters, not to the quantised copies
+        for q, prm in ((w1, wgu), (w2, wd)):
+            mg = getattr(prm, "main_grad", None)
+            if mg is not None:
+                q.main_grad = mg
+    gu = gg.grouped_linear(x, w1, plan)
+    y = gg.grouped_linear(ew.swiglu(gu), w2, plan)[plan.dst_row]
+    wf = w.reshape(-1)[plan.order].to(y.dtype)
     out = torch.zeros((T, H), device=h.device, dtype=torch.float32)
     out.index_add_(0, tok, (y * wf[:, None]).float())
     return out.to(h.dtype)

@@ -1,0 +1,168 @@
+"""Grouped (per-expert) linear layers for mixture-of-experts FFNs: one kernel launch for all experts.
+
+Rows routed to the same expert are laid out contiguously, each expert's range padded to a multiple of 128 rows, so
+that every 128-row tile of the tcgen05 GEMM belongs to exactly one expert.  The plan (row offsets, tile -> expert
+table) is computed with device ops and read by the kernel from device memory: no expert count ever reaches the host,
+so a layer costs three launches instead of three per expert and can be captured in a CUDA graph.
+
+Reference behaviour: Megatron-core's grouped expert GEMM, enabled with ``moe_grouped_gemm``
+(skyrl/backends/skyrl_train/workers/megatron/megatron_worker.py:472-473).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+ROW_ALIGN = 128
+
+
+@dataclass
+class GroupPlan:
+    """Layout of ``n`` routed rows over ``E`` experts in a padded ``[M_cap, *]`` buffer."""
+
+    order: torch.Tensor        # [n] routed entries sorted by expert (stable)
+    dst_row: torch.Tensor      # [n] padded-buffer row of sorted entry i
+    k_off: torch.Tensor        # [E + 1] int32 first padded row of each expert (multiples of 128)
+    tile_expert: torch.Tensor  # [M_cap / 128] int32 owner of each row block, -1 = unused
+    m_cap: int
+    num_experts: int
+
+
+def padded_rows(n: int, num_experts: int) -> int:
+    """Static upper bound of the padded row count for ``n`` routed rows."""
+    cap = n + min(num_experts, n) * (ROW_ALIGN - 1)
+    return max(ROW_ALIGN, (cap + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN)
+
+
+def plan_groups(expert_ids: torch.Tensor, num_experts: int) -> GroupPlan:
+    """``expert_ids``: [n] expert of every routed (token, slot) entry."""
+    n = expert_ids.numel()
+    dev = expert_ids.device
+    flat = expert_ids.reshape(-1).long()
+    counts = torch.bincount(flat, minlength=num_experts)
+    pad = (counts + (ROW_ALIGN - 1)) // ROW_ALIGN * ROW_ALIGN
+    ends = torch.cumsum(pad, 0)
+    off = ends - pad
+    order = torch.argsort(flat, stable=True)
+    se = flat[order]
+    ustart = torch.cumsum(counts, 0) - counts
+    dst_row = off[se] + (torch.arange(n, device=dev) - ustart[se])
+    m_cap = padded_rows(n, num_experts)
+    starts = torch.arange(m_cap // ROW_ALIGN, device=dev) * ROW_ALIGN
+    te = torch.searchsorted(ends, starts, right=True)
+    te = torch.where(starts < ends[-1], te, torch.full_like(te, -1))
+    k_off = torch.cat([torch.zeros(1, dtype=ends.dtype, device=dev), ends]).to(torch.int32)
+    return GroupPlan(order, dst_row, k_off, te.to(torch.int32), m_cap, num_experts)
+
+
+def _fn():
+    lib = _lib.kernels()
+    f = lib.sb_gemm_grouped
+    if not getattr(f, "_configured", False):
+        vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        f.restype = ci
+        f.argtypes = [vp, vp, vp, ci, ci, ci, cl, cl, cl, ci, ci, ci, ci, vp, vp, cl, ci, vp]
+        f._configured = True
+    return f
+
+
+def _out_mode(out: torch.Tensor, accumulate: bool) -> int:
+    return 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
+
+
+def _expert_ranges(plan: GroupPlan):
+    k = plan.k_off.tolist()
+    return [(e, k[e], k[e + 1]) for e in range(plan.num_experts) if k[e + 1] > k[e]]
+
+
+def grouped_nt(x: torch.Tensor, w: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
+    """``x`` [M_cap, K] (rows grouped by expert), ``w`` [E, N, K] -> [M_cap, N] with row r times its expert's ``w^T``.
+    Rows of unused blocks are left unwritten."""
+    M, K = x.shape
+    E, N, _ = w.shape
+    if not x.is_cuda:
+        out = x.new_zeros((M, N))
+        for e, lo, hi in _expert_ranges(plan):
+            out[lo:hi] = x[lo:hi] @ w[e].t()
+        return out
+    x, w = x.contiguous(), w.contiguous()
+    out = torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+    code = _fn()(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, K, K, N, 0, 0, 1, E, plan.tile_expert.data_ptr(), None, 0,
+                 0, _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_grouped(nt)")
+    return out
+
+
+def grouped_nn(dy: torch.Tensor, w: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
+    """``dy`` [M_cap, N], ``w`` [E, N, K] -> [M_cap, K] with row r times its expert's ``w``."""
+    M, N = dy.shape
+    E, _, K = w.shape
+    if not dy.is_cuda:
+        out = dy.new_zeros((M, K))
+        for e, lo, hi in _expert_ranges(plan):
+            out[lo:hi] = dy[lo:hi] @ w[e]
+        return out
+    dy, w = dy.contiguous(), w.contiguous()
+    out = torch.empty((M, K), device=dy.device, dtype=torch.bfloat16)
+    # contraction length N (rows of each expert's matrix), output width K
+    code = _fn()(dy.data_ptr(), w.data_ptr(), out.data_ptr(), M, K, N, N, K, K, 1, 0, 1, E, plan.tile_expert.data_ptr(), None, 0,
+                 0, _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_grouped(nn)")
+    return out
+
+
+def grouped_tn(dy: torch.Tensor, x: torch.Tensor, plan: GroupPlan, out: torch.Tensor, accumulate: bool) -> torch.Tensor:
+    """``out[e] (+)= dy[rows_e]^T x[rows_e]``; ``dy`` [M_cap, N], ``x`` [M_cap, K], ``out`` [E, N, K].  Padding rows of
+    both operands must be zero (or finite in one and zero in the other).  Experts without rows keep ``out[e]``."""
+    M, N = dy.shape
+    K = x.shape[1]
+    E = out.shape[0]
+    if not dy.is_cuda:
+        for e, lo, hi in _expert_ranges(plan):
+            g = dy[lo:hi].float().t() @ x[lo:hi].float()
+            if accumulate:
+                out[e] += g.to(out.dtype)
+            else:
+                out[e] = g.to(out.dtype)
+        return out
+    dy, x = dy.contiguous(), x.contiguous()
+    assert out.is_contiguous()
+    code = _fn()(dy.data_ptr(), x.data_ptr(), out.data_ptr(), N, K, 0, N, K, K, 1, _out_mode(out, accumulate), 2, E, None,
+                 plan.k_off.data_ptr(), N * K, M, _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_grouped(tn)")
+    return out
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, plan: GroupPlan):
+        ctx.plan = plan
+        ctx.w_main_grad = getattr(w, "main_grad", None)
+        ctx.save_for_backward(x, w)
+        return grouped_nt(x, w, plan)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        plan = ctx.plan
+        dy = dy.contiguous()
+        dx = grouped_nn(dy, w, plan) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = ctx.w_main_grad
+            if mg is not None:
+                grouped_tn(dy, x, plan, mg.view(w.shape), accumulate=True)
+            else:
+                dw = grouped_tn(dy, x, plan, torch.zeros_like(w), accumulate=False)
+        return dx, dw, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
+    """Differentiable ``x[r] @ w[expert(r)]^T`` over a padded, expert-grouped row buffer.  For the weight gradient the
+    padding rows of ``x`` and of the incoming gradient must be zero (``torch.zeros`` + ``index_copy`` gives that)."""
+    return _GroupedLinearFn.apply(x, w, plan)
