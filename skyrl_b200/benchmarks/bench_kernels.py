@@ -55,6 +55,7 @@ def main() -> None:
     ap.add_argument("--nq", type=int, default=12)
     ap.add_argument("--nkv", type=int, default=2)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--graph", action="store_true", help="decode_attn: time a CUDA-graph replay of several calls")
     ap.add_argument("--hbm-gbs", type=float, default=6543.4)
     ap.add_argument("--peak-tflops", type=float, default=1668.8)
     a = ap.parse_args()
@@ -82,7 +83,23 @@ def main() -> None:
         bt = torch.arange(nb, device="cuda", dtype=torch.int32).view(a.seqs, mb)
         cl = torch.full((a.seqs,), a.ctx, device="cuda", dtype=torch.int32)
         qkv = torch.randn(a.seqs, (a.nq + 2 * a.nkv) * D, **bf)
-        ms = timeit(lambda: attention.attn_decode_paged(qkv, kc, vc, bt, cl, a.nq, a.nkv, D, max_ctx=a.ctx), a.iters)
+        if a.graph:
+            # GPU time without host launch gaps: `reps` calls captured in one CUDA graph, each on its own cache copy
+            # (together larger than L2) so that no call finds its K/V in cache
+            reps = max(2, int(300e6 // (2 * nb * bs * a.nkv * D * 2)) + 1)
+            caches = [(kc, vc)] + [(torch.randn_like(kc), torch.randn_like(vc)) for _ in range(reps - 1)]
+            outb = torch.empty(a.seqs, a.nq * D, **bf)
+            ws = torch.empty(attention.decode_workspace_floats(a.seqs, a.nq, D, 32), device="cuda", dtype=torch.float32)
+            run = lambda: [attention.attn_decode_paged(qkv, k_, v_, bt, cl, a.nq, a.nkv, D, max_ctx=a.ctx, out=outb,  # noqa: E731
+                                                       workspace=ws) for k_, v_ in caches]
+            run()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                run()
+            ms = timeit(gr.replay, a.iters) / reps
+        else:
+            ms = timeit(lambda: attention.attn_decode_paged(qkv, kc, vc, bt, cl, a.nq, a.nkv, D, max_ctx=a.ctx), a.iters)
         by = 2.0 * a.seqs * a.ctx * a.nkv * D * 2
         out.update(seqs=a.seqs, ctx=a.ctx, ms=ms, gbs=by / ms / 1e6, fraction_of_measured_hbm=by / ms / 1e6 / a.hbm_gbs)
     elif a.which == "attn":

@@ -43,13 +43,9 @@ def moe_ffn(h: torch.Tensor, router_w: torch.Tensor, wgu: torch.Tensor, wd: torc
         w = probs.gather(-1, idx)
         if norm_topk_prob:
             w = w / w.sum(dim=-1, keepdim=True)
-    flat_e = idx.reshape(-1)
-    plan = gg.plan_groups(flat_e, E)
-    tok = torch.arange(T, device=h.device).repeat_interleave(top_k)[plan.order]
-    # rows grouped by expert, every expert's range padded to whole 128-row tiles; padding rows are zero whenever a
-    # weight gradient will be formed from them
-    alloc = torch.zeros if torch.is_grad_enabled() else torch.empty
-    x = alloc((plan.m_cap, H), device=h.device, dtype=h.dtype).index_copy(0, plan.dst_row, h[tok])
+    plan = gg.plan_groups(idx.reshape(-1), E, top_k)
+    # rows grouped by expert, every expert's range padded to whole 128-row tiles (padding rows are zero)
+    x = gg.dispatch_rows(h, plan)
     w1, w2 = wgu, wd
     if qat is not None and qat.enabled and torch.is_grad_enabled():  # fake-INT4 expert weights, straight-through
         from .qat import fake_int4
@@ -62,8 +58,5 @@ def moe_ffn(h: torch.Tensor, router_w: torch.Tensor, wgu: torch.Tensor, wd: torc
             if mg is not None:
                 q.main_grad = mg
     gu = gg.grouped_linear(x, w1, plan)
-    y = gg.grouped_linear(ew.swiglu(gu), w2, plan)[plan.dst_row]
-    wf = w.reshape(-1)[plan.order].to(y.dtype)
-    out = torch.zeros((T, H), device=h.device, dtype=torch.float32)
-    out.index_add_(0, tok, (y * wf[:, None]).float())
-    return out.to(h.dtype)
+    y = gg.grouped_linear(ew.swiglu(gu), w2, plan)
+    return gg.combine_rows(y, w, plan)

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -193,11 +194,22 @@ def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
 
 
 def decode_num_splits_tc(n: int, nkv: int, max_ctx: int) -> int:
-    """The tensor-core kernel runs one CTA per SM; split the context (128-token granularity) when few CTAs exist."""
+    """The tensor-core kernel keeps one CTA per SM.  Its persistent form walks a list of (sequence, kv head, split)
+    items per CTA, so the context is split (128-token granularity, at least two tiles per item) until every SM has
+    about six items and the last round of items leaves few SMs idle; the one-item-per-CTA form
+    (``SB_DECODE_ATTN_PERSIST=0``) only splits when there are fewer items than SMs."""
     ctas = n * nkv
-    if ctas >= 148 or max_ctx <= 256:
+    forced = os.environ.get("SB_DECODE_ATTN_SPLITS")
+    if forced:  # tuning knob
+        return int(max(1, min(int(forced), max(1, max_ctx // 128), 32)))
+    if max_ctx <= 256:
         return 1
-    want = (148 + ctas - 1) // ctas
+    if os.environ.get("SB_DECODE_ATTN_PERSIST", "1") == "0":
+        if ctas >= 148:
+            return 1
+        want = (148 + ctas - 1) // ctas
+    else:
+        want = (6 * 148 + ctas - 1) // ctas
     return int(max(1, min(want, max_ctx // 256, 32)))
 
 

@@ -31,6 +31,9 @@ class GroupPlan:
     tile_expert: torch.Tensor  # [M_cap / 128] int32 owner of each row block, -1 = unused
     m_cap: int
     num_experts: int
+    top_k: int = 1
+    row_src: torch.Tensor | None = None   # [M_cap] int32 token whose hidden row fills padded row r, -1 = padding
+    slot_row: torch.Tensor | None = None  # [n] int32 padded row of routed entry (token * top_k + slot)
 
 
 def padded_rows(n: int, num_experts: int) -> int:
@@ -39,8 +42,8 @@ def padded_rows(n: int, num_experts: int) -> int:
     return max(ROW_ALIGN, (cap + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN)
 
 
-def plan_groups(expert_ids: torch.Tensor, num_experts: int) -> GroupPlan:
-    """``expert_ids``: [n] expert of every routed (token, slot) entry."""
+def plan_groups(expert_ids: torch.Tensor, num_experts: int, top_k: int = 1) -> GroupPlan:
+    """``expert_ids``: [n] expert of every routed entry; entry ``i`` belongs to token ``i // top_k``."""
     n = expert_ids.numel()
     dev = expert_ids.device
     flat = expert_ids.reshape(-1).long()
@@ -57,7 +60,11 @@ def plan_groups(expert_ids: torch.Tensor, num_experts: int) -> GroupPlan:
     te = torch.searchsorted(ends, starts, right=True)
     te = torch.where(starts < ends[-1], te, torch.full_like(te, -1))
     k_off = torch.cat([torch.zeros(1, dtype=ends.dtype, device=dev), ends]).to(torch.int32)
-    return GroupPlan(order, dst_row, k_off, te.to(torch.int32), m_cap, num_experts)
+    row_src = torch.full((m_cap,), -1, dtype=torch.int32, device=dev)
+    row_src[dst_row] = (order // top_k).to(torch.int32)
+    slot_row = torch.empty(n, dtype=torch.int32, device=dev)
+    slot_row[order] = dst_row.to(torch.int32)
+    return GroupPlan(order, dst_row, k_off, te.to(torch.int32), m_cap, num_experts, top_k, row_src, slot_row)
 
 
 def _fn():
@@ -166,3 +173,104 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, plan: GroupPlan) -> torch.T
     """Differentiable ``x[r] @ w[expert(r)]^T`` over a padded, expert-grouped row buffer.  For the weight gradient the
     padding rows of ``x`` and of the incoming gradient must be zero (``torch.zeros`` + ``index_copy`` gives that)."""
     return _GroupedLinearFn.apply(x, w, plan)
+
+
+# ----------------------------------------------------------------------------- token movement around the expert GEMMs
+def _moe_fns():
+    lib = _lib.kernels()
+    if not getattr(lib.sb_moe_gather_rows, "_configured", False):
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        lib.sb_moe_gather_rows.argtypes = [vp, vp, vp, ci, ci, vp]
+        lib.sb_moe_combine.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp]
+        lib.sb_moe_combine_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, vp]
+        for f in (lib.sb_moe_gather_rows, lib.sb_moe_combine, lib.sb_moe_combine_bwd):
+            f.restype = ci
+        lib.sb_moe_gather_rows._configured = True
+    return lib
+
+
+def _gather_rows(h: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
+    if not h.is_cuda:
+        out = h.new_zeros((plan.m_cap, h.shape[1]))
+        valid = plan.row_src >= 0
+        out[valid] = h[plan.row_src[valid].long()]
+        return out
+    h = h.contiguous()
+    out = torch.empty((plan.m_cap, h.shape[1]), device=h.device, dtype=h.dtype)
+    code = _moe_fns().sb_moe_gather_rows(h.data_ptr(), plan.row_src.data_ptr(), out.data_ptr(), plan.m_cap, h.shape[1],
+                                         _lib.stream_ptr())
+    _lib.check(code, "sb_moe_gather_rows")
+    return out
+
+
+def _combine(y: torch.Tensor, plan: GroupPlan, w: torch.Tensor | None, T: int) -> torch.Tensor:
+    k, H = plan.top_k, y.shape[1]
+    if not y.is_cuda:
+        rows = y[plan.slot_row.long()].view(T, k, H).float()
+        if w is not None:
+            rows = rows * w.float().view(T, k, 1)
+        return rows.sum(1).to(y.dtype)
+    out = torch.empty((T, H), device=y.device, dtype=y.dtype)
+    code = _moe_fns().sb_moe_combine(y.data_ptr(), plan.slot_row.data_ptr(), None if w is None else w.data_ptr(),
+                                     out.data_ptr(), T, k, H, _lib.stream_ptr())
+    _lib.check(code, "sb_moe_combine")
+    return out
+
+
+def _combine_bwd(y: torch.Tensor | None, plan: GroupPlan, w: torch.Tensor | None, dout: torch.Tensor, want_dw: bool):
+    T, H = dout.shape
+    k = plan.top_k
+    if not dout.is_cuda:
+        dy = dout.new_zeros((plan.m_cap, H))
+        g = dout.float().view(T, 1, H).expand(T, k, H)
+        if w is not None:
+            g = g * w.float().view(T, k, 1)
+        dy[plan.slot_row.long()] = g.reshape(T * k, H).to(dout.dtype)
+        dw = (y[plan.slot_row.long()].view(T, k, H).float() * dout.float().view(T, 1, H)).sum(-1) if want_dw else None
+        return dy, dw
+    dout = dout.contiguous()
+    dy = torch.zeros((plan.m_cap, H), device=dout.device, dtype=dout.dtype)
+    dw = torch.empty((T, k), device=dout.device, dtype=torch.float32) if want_dw else None
+    code = _moe_fns().sb_moe_combine_bwd(None if y is None else y.data_ptr(), plan.slot_row.data_ptr(),
+                                         None if w is None else w.data_ptr(), dout.data_ptr(), dy.data_ptr(),
+                                         None if dw is None else dw.data_ptr(), T, k, H, _lib.stream_ptr())
+    _lib.check(code, "sb_moe_combine_bwd")
+    return dy, dw
+
+
+class _DispatchFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, plan: GroupPlan):
+        ctx.plan, ctx.T = plan, h.shape[0]
+        return _gather_rows(h, plan)
+
+    @staticmethod
+    def backward(ctx, dx):
+        return _combine(dx.contiguous(), ctx.plan, None, ctx.T), None
+
+
+class _CombineFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, w, plan: GroupPlan):
+        ctx.plan = plan
+        w32 = w.float().contiguous()
+        ctx.w_dtype = w.dtype
+        ctx.save_for_backward(y, w32)
+        return _combine(y, plan, w32, w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, w32 = ctx.saved_tensors
+        dy, dw = _combine_bwd(y, ctx.plan, w32, dout, ctx.needs_input_grad[1])
+        return dy, (dw.to(ctx.w_dtype) if dw is not None else None), None
+
+
+def dispatch_rows(h: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
+    """``[T, H]`` hidden rows -> padded expert-grouped buffer ``[M_cap, H]`` (padding rows zero); the gradient sums
+    each token's ``top_k`` rows."""
+    return _DispatchFn.apply(h, plan)
+
+
+def combine_rows(y: torch.Tensor, w: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
+    """``out[t] = sum_s w[t, s] * y[row of (t, s)]`` with ``w`` ``[T, top_k]``; differentiable in ``y`` and ``w``."""
+    return _CombineFn.apply(y, w, plan)

@@ -110,3 +110,65 @@ def test_grouped_weight_gradient_accumulates_into_main_grad():
         ref = 0.25 + (gy[m].float().t() @ rows[m].float() if m.any() else 0.0)
         err = (w.main_grad[e] - ref).abs().max() / (ref.abs().max() if m.any() else 1.0)
         assert err < 2e-2, (e, float(err))
+
+
+def _moe_reference(h, rt, wgu, wd, k):
+    """Plain fp32 mixture-of-experts FFN: softmax router, top-k, renormalised weights, per-expert SwiGLU FFN."""
+    T, H = h.shape
+    E, F2, _ = wgu.shape
+    F = F2 // 2
+    probs = torch.softmax(h.float() @ rt.float().t(), -1)
+    w, idx = torch.topk(probs, k, -1)
+    w = w / w.sum(-1, keepdim=True)
+    out = torch.zeros(T, H, dtype=torch.float32, device=h.device)
+    for e in range(E):
+        t, s = torch.nonzero(idx == e, as_tuple=True)
+        if t.numel() == 0:
+            continue
+        gu = h[t].float() @ wgu[e].float().t()
+        act = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+        out.index_add_(0, t, (act @ wd[e].float().t()) * w[t, s][:, None])
+    return out
+
+
+def test_moe_layer_cpu_matches_reference_with_gradients():
+    from skyrl_b200.models.moe import moe_ffn
+
+    g = torch.Generator().manual_seed(3)
+    T, H, E, F, k = 50, 32, 6, 24, 2
+    h = torch.randn(T, H, generator=g).requires_grad_()
+    rt = torch.randn(E, H, generator=g).requires_grad_()
+    wgu = (torch.randn(E, 2 * F, H, generator=g) * 0.2).requires_grad_()
+    wd = (torch.randn(E, H, F, generator=g) * 0.2).requires_grad_()
+    out = moe_ffn(h, rt, wgu, wd, k, True)
+    ref_in = [t.detach().clone().requires_grad_() for t in (h, rt, wgu, wd)]
+    ref = _moe_reference(*ref_in, k)
+    assert torch.allclose(out, ref, atol=1e-4), float((out - ref).abs().max())
+    gy = torch.randn(T, H, generator=g)
+    out.backward(gy)
+    ref.backward(gy)
+    for a, b, name in zip((h, rt, wgu, wd), ref_in, ("h", "router", "wgu", "wd")):
+        assert torch.allclose(a.grad, b.grad, atol=2e-4), (name, float((a.grad - b.grad).abs().max()))
+
+
+@pytest.mark.gpu
+def test_moe_layer_gpu_matches_fp32_reference():
+    from skyrl_b200.models.moe import moe_ffn
+
+    torch.manual_seed(0)
+    T, H, E, F, k = 1500, 512, 16, 256, 4
+    h = (torch.randn(T, H, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    rt = (torch.randn(E, H, device="cuda") * 0.1).to(torch.bfloat16)
+    wgu = (torch.randn(E, 2 * F, H, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    wd = (torch.randn(E, H, F, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    out = moe_ffn(h, rt, wgu, wd, k, True)
+    ref_in = [t.detach().clone().float().requires_grad_() for t in (h, wgu, wd)]
+    ref = _moe_reference(ref_in[0], rt, ref_in[1], ref_in[2], k)
+    err = (out.float() - ref).abs().max() / ref.abs().max()
+    assert err < 3e-2, float(err)
+    gy = (torch.randn(T, H, device="cuda") * 0.5).to(torch.bfloat16)
+    out.backward(gy)
+    ref.backward(gy.float())
+    for a, b, name in zip((h, wgu, wd), ref_in, ("h", "wgu", "wd")):
+        e = (a.grad.float() - b.grad).abs().max() / b.grad.abs().max().clamp_min(1e-6)
+        assert e < 5e-2, (name, float(e))
