@@ -18,6 +18,7 @@
 namespace sb {
 
 constexpr int kDtThreads = 192;
+constexpr int kDtThreadsPersist = 224;  // + one warp streaming the V tiles
 constexpr int kDtStages = 3;
 constexpr int kDtTile = 128 * 128 * 2;                 // one K or V tile: 32 KB (two 16 KB halves)
 constexpr int kDtStageBytes = 2 * kDtTile;             // K + V
@@ -289,7 +290,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 // last S^T product of the item complete, no MMA reads sQ any more and they store the next item's query rows (already
 // fetched into registers) before they continue with that tile.
 template <int G>
-__global__ void __launch_bounds__(kDtThreads, 1)
+__global__ void __launch_bounds__(kDtThreadsPersist, 1)
 attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                               const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ block_tables,
                               const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ ws,
@@ -302,13 +303,17 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
   // P and the O^T accumulator are double-buffered: the softmax warps store P(j) without waiting for the product of
   // tile j-1, whose result they fold afterwards
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kDtPBytes);
-  uint64_t* full = bars;               // [3]
-  uint64_t* empty = bars + 3;          // [3]
-  uint64_t* s_full = bars + 6;         // [2]
-  uint64_t* p_ready = bars + 8;        // [2] (two barriers: the softmax warps may be a whole tile ahead of the issuer)
-  uint64_t* o_full = bars + 10;        // [2]
-  uint64_t* q_ready = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  // K and V tiles travel through rings of their own: a K tile is free again as soon as its S^T product has completed,
+  // a whole tile period before the V tile of the same step, so its refill starts that much earlier
+  uint64_t* kfull = bars;              // [3]
+  uint64_t* kempty = bars + 3;         // [3]
+  uint64_t* vfull = bars + 6;          // [3]
+  uint64_t* vempty = bars + 9;         // [3]
+  uint64_t* s_full = bars + 12;        // [2]
+  uint64_t* p_ready = bars + 14;       // [2] (two barriers: the softmax warps may be a whole tile ahead of the issuer)
+  uint64_t* o_full = bars + 16;        // [2]
+  uint64_t* q_ready = bars + 18;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   __shared__ float s_red[4][16];
   __shared__ float s_lsum[4][16];
 
@@ -317,8 +322,10 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kDtStages; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+      mbar_init(&kfull[i], 1);
+      mbar_init(&kempty[i], 1);
+      mbar_init(&vfull[i], 1);
+      mbar_init(&vempty[i], 1);
     }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
@@ -333,7 +340,7 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
     tmem_alloc(tmem_slot, 64);
     tmem_relinquish();
   }
-  if (warp >= 2) {
+  if (warp >= 2 && warp < 6) {
     const int t = threadIdx.x - 64;  // rows of heads >= G stay zero for the whole kernel
     for (int i = t; i < (kDtQBytes + 2 * kDtPBytes) / 16; i += 128) reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0, 0, 0, 0);
   }
@@ -365,8 +372,13 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
   };
   const int pages_per_tile = 128 / block_size;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 6) {
+    // warp 0 streams the K tiles, warp 6 the V tiles (one thread each)
     if (lane == 0) {
+      const bool is_v = warp == 6;
+      uint64_t* fullb = is_v ? vfull : kfull;
+      uint64_t* emptyb = is_v ? vempty : kempty;
+      const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
       int jt = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -375,23 +387,20 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
         const int* bt = block_tables + static_cast<size_t>(seq) * max_blocks;
         for (int j = 0; j < n_tiles; ++j, ++jt) {
           const int s = jt % kDtStages;
-          if (!mbar_wait(&empty[s], ((jt / kDtStages) & 1) ^ 1, status, 0x831)) {
+          if (!mbar_wait(&emptyb[s], ((jt / kDtStages) & 1) ^ 1, status, is_v ? 0x832 : 0x831)) {
             ok = false;
             break;
           }
-          uint8_t* sK = smem + s * kDtStageBytes;
-          uint8_t* sV = sK + kDtTile;
-          mbar_arrive_expect_tx(&full[s], kDtStageBytes);
+          uint8_t* dst = smem + s * kDtStageBytes + (is_v ? kDtTile : 0);
+          mbar_arrive_expect_tx(&fullb[s], kDtTile);
           const int tok0 = t0 + j * 128;
           for (int p = 0; p < pages_per_tile; ++p) {
             int pi = (tok0 + p * block_size) / block_size;
             pi = pi < max_blocks ? pi : max_blocks - 1;
             const int slot0 = __ldg(bt + pi) * block_size;
             const int off = p * block_size * 128;
-            tma_load_3d(sK + off, &tm_k, &full[s], 0, g, slot0);
-            tma_load_3d(sK + 16384 + off, &tm_k, &full[s], 64, g, slot0);
-            tma_load_3d(sV + off, &tm_v, &full[s], 0, g, slot0);
-            tma_load_3d(sV + 16384 + off, &tm_v, &full[s], 64, g, slot0);
+            tma_load_3d(dst + off, tm, &fullb[s], 0, g, slot0);
+            tma_load_3d(dst + 16384 + off, tm, &fullb[s], 64, g, slot0);
           }
         }
       }
@@ -403,7 +412,7 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
       const uint32_t q_base = smem_u32(sQ), p_base = smem_u32(sP);
       auto issue_s = [&](int jt) -> bool {
         const int s = jt % kDtStages;
-        if (!mbar_wait(&full[s], (jt / kDtStages) & 1, status, 0x841)) return false;
+        if (!mbar_wait(&kfull[s], (jt / kDtStages) & 1, status, 0x841)) return false;
         tc_fence_after();
         const uint32_t k_base = smem_u32(smem + s * kDtStageBytes);
 #pragma unroll
@@ -411,6 +420,7 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
           umma_f16(tmem_base + (jt & 1) * 16, make_smem_desc(k_base + (k >> 2) * 16384 + (k & 3) * 32, 0, 1024),
                    make_smem_desc(q_base + (k >> 2) * 2048 + (k & 3) * 32, 0, 1024), idesc_s, k != 0);
         umma_commit(&s_full[jt & 1]);
+        umma_commit(&kempty[s]);  // the K tile is free once these products retire
         return true;
       };
       int jt = 0, qi = 0;
@@ -445,8 +455,12 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
             ok = false;
             break;
           }
-          tc_fence_after();
           const int s = jt % kDtStages;
+          if (!mbar_wait(&vfull[s], (jt / kDtStages) & 1, status, 0x845)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
           const uint32_t v_base = smem_u32(smem + s * kDtStageBytes + kDtTile);
 #pragma unroll
           for (int k = 0; k < 8; ++k)
@@ -454,13 +468,13 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
                      make_smem_desc(p_base + (jt & 1) * kDtPBytes + (k >> 2) * 2048 + (k & 3) * 32, 0, 1024), idesc_o,
                      k != 0);
           umma_commit(&o_full[jt & 1]);
-          umma_commit(&empty[s]);
+          umma_commit(&vempty[s]);
         }
         ++qi;
         item = nxt;
       }
     }
-  } else {
+  } else if (warp < 6) {
     const int q = warp & 3;
     const int sw = warp - 2;
     const int tid = threadIdx.x - 64;  // 0..127
@@ -700,7 +714,7 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
       attr_p = true;                                                                                                \
     }                                                                                                               \
     if (persist)                                                                                                    \
-      sb::launch_pdl(sb::attn_decode_tc_persist_kernel<GV>, dim3(pgrid), dim3(sb::kDtThreads), sb::kDtSmemPersist,  \
+      sb::launch_pdl(sb::attn_decode_tc_persist_kernel<GV>, dim3(pgrid), dim3(sb::kDtThreadsPersist), sb::kDtSmemPersist,  \
                      st,                                                                                            \
                      *tk, *tv, reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                 \
                      reinterpret_cast<__nv_bfloat16*>(out), workspace, n, nq, nkv, block_size, max_blocks, splits,  \

@@ -82,6 +82,26 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
+// Fused SwiGLU epilogues of the MLP GEMMs (BN = 256 only).
+//  mode 1 (gate/up projection, NT): B is the stacked [2F, K] weight; the leader CTA loads 128 gate rows, its partner
+//    the matching 128 up rows, so accumulator columns 0-127 / 128-255 hold gate / up of the same F-columns.  The
+//    epilogue stores both to C ([M, 2F], kept for the backward pass) and silu(gate) * up to c2 ([M, F], row stride ld2).
+//  mode 2 (input gradient of the down projection, NN): the accumulator is d(act); the epilogue reads gate / up from
+//    aux ([M, 2F]) and stores d(gate) | d(up) to C ([M, 2F]) -- d(act) never reaches memory.
+struct EpiArgs {
+  int mode;
+  int F;
+  void* c2;
+  const void* aux;
+  long long ld2;
+};
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct TileMap2 {
   int m_blocks, n_blocks;
   __device__ __forceinline__ void get(int tile, int& pm, int& pn) const {
@@ -98,7 +118,8 @@ struct TileMap2 {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(k2Threads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ C,
-                  const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc, int out_mode, int* status) {
+                  const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc, int out_mode, int* status,
+                  const EpiArgs epi) {
   using Cfg = Gemm2Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -150,7 +171,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         int pm, pn;
         tm.get(tile, pm, pn);
         const int row0 = pm * k2BM + static_cast<int>(rank) * k2HalfM;     // this CTA's rows of A
-        const int col0 = pn * BN + static_cast<int>(rank) * (BN / 2);      // this CTA's half of the B tile
+        // this CTA's half of the B tile (fused gate/up projection: gate rows for the leader, up rows for the partner)
+        const int col0 = (!B_MN && epi.mode == 1) ? pn * (BN / 2) + static_cast<int>(rank) * epi.F
+                                                  : pn * BN + static_cast<int>(rank) * (BN / 2);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % Cfg::kStages;
           const uint32_t ph = (it / Cfg::kStages) & 1;
@@ -224,6 +247,103 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       const int row = pm * k2BM + static_cast<int>(rank) * k2HalfM + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (BN == 256 && epi.mode == 1) {
+        // gate | up of the same 128 F-columns: store both, and silu(gate) * up computed from the rounded values.
+        // One epilogue warp per scheduler has nothing to hide latency with, so the arithmetic is kept short:
+        // bf16 pairs are packed once (the packed words are what gets stored) and unpacked by shifts, and
+        // sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5 costs a single special-function instruction.
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, rg);
+          tmem_ld_32x32b_x32(t_row + 128 + c * 32, ru);
+          tmem_ld_wait();
+          const int col = pn * 128 + c * 32;
+          if (row < M && col < epi.F) {
+            uint32_t pg[16], pu[16], pa[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              pg[j] = pack_bf16x2(__uint_as_float(rg[2 * j]), __uint_as_float(rg[2 * j + 1]));
+              pu[j] = pack_bf16x2(__uint_as_float(ru[2 * j]), __uint_as_float(ru[2 * j + 1]));
+              const float g0 = __uint_as_float(pg[j] << 16), g1 = __uint_as_float(pg[j] & 0xFFFF0000u);
+              const float u0 = __uint_as_float(pu[j] << 16), u1 = __uint_as_float(pu[j] & 0xFFFF0000u);
+              pa[j] = pack_bf16x2(g0 * fmaf(0.5f, tanh_approx(0.5f * g0), 0.5f) * u0,
+                                  g1 * fmaf(0.5f, tanh_approx(0.5f * g1), 0.5f) * u1);
+            }
+            if (C != nullptr) {  // forward-only callers do not keep gate / up
+              uint4* crow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(C) + static_cast<long long>(row) * ldc + col);
+              uint4* urow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(C) + static_cast<long long>(row) * ldc + col + epi.F);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                crow[v] = make_uint4(pg[4 * v], pg[4 * v + 1], pg[4 * v + 2], pg[4 * v + 3]);
+                urow[v] = make_uint4(pu[4 * v], pu[4 * v + 1], pu[4 * v + 2], pu[4 * v + 3]);
+              }
+            }
+            uint4* arow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(epi.c2) + static_cast<long long>(row) * epi.ld2 + col);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) arow[v] = make_uint4(pa[4 * v], pa[4 * v + 1], pa[4 * v + 2], pa[4 * v + 3]);
+          }
+        }
+      } else if (BN == 256 && epi.mode == 2) {
+        // d(act) -> d(gate) | d(up); the gate / up values of the next chunk are requested before this chunk's arithmetic
+        const bool live = row < M;
+        const uint4* gsrc = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(epi.aux) +
+                                                           static_cast<long long>(live ? row : 0) * epi.ld2 + pn * BN);
+        const int f_vec = epi.F >> 3;  // uint4 between the gate and the up value of a column
+        uint4 ng[4], nu[4];
+        auto fetch = [&](int c) {
+          if (live && pn * BN + c * 32 < epi.F) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              ng[v] = __ldg(gsrc + c * 4 + v);
+              nu[v] = __ldg(gsrc + f_vec + c * 4 + v);
+            }
+          }
+        };
+        fetch(0);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, r);
+          uint4 cg[4], cu[4];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            cg[v] = ng[v];
+            cu[v] = nu[v];
+          }
+          if (c + 1 < BN / 32) fetch(c + 1);
+          tmem_ld_wait();
+          const int col = pn * BN + c * 32;
+          if (live && col < epi.F) {
+            const uint32_t* wg = reinterpret_cast<const uint32_t*>(cg);
+            const uint32_t* wu = reinterpret_cast<const uint32_t*>(cu);
+            uint32_t pg[16], pu[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float dg2[2], du2[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const float g = __uint_as_float(e ? (wg[j] & 0xFFFF0000u) : (wg[j] << 16));
+                const float u = __uint_as_float(e ? (wu[j] & 0xFFFF0000u) : (wu[j] << 16));
+                const float d = __uint_as_float(r[2 * j + e]);
+                const float sig = fmaf(0.5f, tanh_approx(0.5f * g), 0.5f);
+                const float silu = g * sig;
+                du2[e] = d * silu;
+                dg2[e] = d * u * fmaf(silu, 1.f - sig, sig);
+              }
+              pg[j] = pack_bf16x2(dg2[0], dg2[1]);
+              pu[j] = pack_bf16x2(du2[0], du2[1]);
+            }
+            uint4* crow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(C) + static_cast<long long>(row) * ldc + col);
+            uint4* urow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(C) + static_cast<long long>(row) * ldc + col + epi.F);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              crow[v] = make_uint4(pg[4 * v], pg[4 * v + 1], pg[4 * v + 2], pg[4 * v + 3]);
+              urow[v] = make_uint4(pu[4 * v], pu[4 * v + 1], pu[4 * v + 2], pu[4 * v + 3]);
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -300,7 +420,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm2(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
-                        long long ldb, long long ldc, int out_mode, cudaStream_t stream) {
+                        long long ldb, long long ldc, int out_mode, cudaStream_t stream, EpiArgs epi = EpiArgs{}) {
   using Cfg = Gemm2Cfg<BN>;
   const CUtensorMap* ta = A_MN ? get_tmap_bf16_2d(A, K, M, lda, 64) : get_tmap_bf16_2d(A, M, K, lda, k2HalfM);
   const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN / 2);
@@ -316,7 +436,7 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* bias,
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   kfn<<<2 * pairs, k2Threads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
-                                                         ldc, out_mode, device_status_ptr());
+                                                         ldc, out_mode, device_status_ptr(), epi);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
@@ -339,6 +459,27 @@ int sb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, i
   SB_G2(128, false, false) SB_G2(128, false, true) SB_G2(128, true, true) SB_G2(128, true, false)
 #undef SB_G2
   return SB_ERR_ARG;
+}
+
+// Fused MLP products on CTA pairs (see EpiArgs).  F must be a multiple of 128, every pointer 16-byte aligned and
+// every row stride a multiple of 8 elements.
+//   sb_mlp_gate_up_swiglu: gu[M, 2F] = x[M, K] * W[2F, K]^T and act[M, F] = silu(gu[:, :F]) * gu[:, F:]
+//                          (gu may be null: only act is stored)
+//   sb_mlp_down_dgrad:     dgu[M, 2F] = d swiglu(gu) applied to (dy[M, H] * Wd[H, F]) without storing the product
+int sb_mlp_gate_up_swiglu(const void* x, const void* w, void* gu, void* act, int M, int F, int K, long long ldx,
+                          long long ldw, void* stream) {
+  if (M <= 0 || F <= 0 || K <= 0 || (F % 128) != 0 || (ldx & 7) || (ldw & 7)) return SB_ERR_ARG;
+  sb::EpiArgs epi{1, F, act, nullptr, F};
+  return sb::launch_gemm2<256, false, false>(x, w, gu, nullptr, M, 2 * F, K, ldx, ldw, 2LL * F, 0,
+                                             reinterpret_cast<cudaStream_t>(stream), epi);
+}
+
+int sb_mlp_down_dgrad(const void* dy, const void* wd, const void* gu, void* dgu, int M, int F, int H, long long lddy,
+                      long long ldwd, void* stream) {
+  if (M <= 0 || F <= 0 || H <= 0 || (F % 32) != 0 || (lddy & 7) || (ldwd & 7)) return SB_ERR_ARG;
+  sb::EpiArgs epi{2, F, nullptr, gu, 2LL * F};
+  return sb::launch_gemm2<256, false, true>(dy, wd, dgu, nullptr, M, F, H, lddy, ldwd, 2LL * F, 0,
+                                            reinterpret_cast<cudaStream_t>(stream), epi);
 }
 
 }  // extern "C"

@@ -296,8 +296,7 @@ class CausalLM(nn.Module):
             d = moe_ffn(h, self.p(pre + "router"), self.p(pre + "experts_wgu"), self.p(pre + "experts_wd"),
                         a.num_experts_per_tok, a.norm_topk_prob, layer=i, qat=getattr(self, "fake_int4_qat", None))
         else:
-            gu = gemm.linear(h, self.p(pre + "wgu"))
-            d = gemm.linear(ew.swiglu(gu), self.p(pre + "wd"))
+            d = gemm.swiglu_mlp(h, self.p(pre + "wgu"), self.p(pre + "wd"))
         return x, d
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor, cu_seqlens: torch.Tensor,

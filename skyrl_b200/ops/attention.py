@@ -194,13 +194,15 @@ def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
 
 
 def decode_num_splits_tc(n: int, nkv: int, max_ctx: int) -> int:
-    """The tensor-core kernel keeps one CTA per SM.  Its persistent form walks a list of (sequence, kv head, split)
-    items per CTA, so the context is split (128-token granularity, at least two tiles per item) until every SM has
-    about six items and the last round of items leaves few SMs idle; the one-item-per-CTA form
-    (``SB_DECODE_ATTN_PERSIST=0``) only splits when there are fewer items than SMs."""
+    """Context splits for the tensor-core decode kernel (one CTA per SM, 128-token tiles).
+
+    The persistent kernel walks ``n * nkv * splits`` items round-robin over the SMs; a small cost model (measured on
+    B200: about 1.8 us per tile, 1.5 us per item, 3 us for the combine pass that splits need) picks the split count
+    with the least idle SM time in the last round.  ``SB_DECODE_ATTN_PERSIST=0`` selects the one-item-per-CTA kernel,
+    which only splits when there are fewer items than SMs; ``SB_DECODE_ATTN_SPLITS`` forces a value (tuning)."""
     ctas = n * nkv
     forced = os.environ.get("SB_DECODE_ATTN_SPLITS")
-    if forced:  # tuning knob
+    if forced:
         return int(max(1, min(int(forced), max(1, max_ctx // 128), 32)))
     if max_ctx <= 256:
         return 1
@@ -208,9 +210,15 @@ def decode_num_splits_tc(n: int, nkv: int, max_ctx: int) -> int:
         if ctas >= 148:
             return 1
         want = (148 + ctas - 1) // ctas
-    else:
-        want = (6 * 148 + ctas - 1) // ctas
-    return int(max(1, min(want, max_ctx // 256, 32)))
+        return int(max(1, min(want, max_ctx // 256, 32)))
+    best, best_cost = 1, float("inf")
+    for s in range(1, min(32, max_ctx // 256) + 1):
+        tiles = (-(-max_ctx // s) + 127) // 128
+        rounds = -(-ctas * s // 148)
+        cost = rounds * (tiles * 1.8 + 1.5) + (3.0 if s > 1 else 0.0)
+        if cost < best_cost - 0.5:  # ties go to fewer splits
+            best, best_cost = s, cost
+    return best
 
 
 def decode_num_splits(n: int, nkv: int, max_ctx: int) -> int:

@@ -16,6 +16,7 @@ runs).  Replaces the cuBLAS calls behind ``torch.nn.Linear`` in the reference's 
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -255,3 +256,94 @@ def gemm_2cta(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bias: torch.T
              b.stride(0), out.stride(0), int(a_mn), int(b_mn), mode, bn, _lib.stream_ptr())
     _lib.check(code, "sb_gemm_bf16_2cta")
     return out
+
+
+# ----------------------------------------------------------------------------- fused SwiGLU MLP
+def _mlp_fns():
+    lib = _lib.kernels()
+    f = lib.sb_mlp_gate_up_swiglu
+    if not getattr(f, "_configured", False):
+        vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        f.restype = ci
+        f.argtypes = [vp, vp, vp, vp, ci, ci, ci, cl, cl, vp]
+        lib.sb_mlp_down_dgrad.restype = ci
+        lib.sb_mlp_down_dgrad.argtypes = [vp, vp, vp, vp, ci, ci, ci, cl, cl, vp]
+        f._configured = True
+    return lib
+
+
+def mlp_fusable(x: torch.Tensor, wgu: torch.Tensor, wd: torch.Tensor) -> bool:
+    """The fused epilogues need CUDA bf16 operands, ``F`` a multiple of 128 and enough rows to fill the CTA pairs."""
+    F = wd.shape[1]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] >= 512 and F % 128 == 0
+            and wgu.shape[0] == 2 * F and x.shape[1] % 8 == 0 and os.environ.get("SB_FUSED_MLP", "1") != "0")
+
+
+def gate_up_swiglu(x: torch.Tensor, wgu: torch.Tensor, need_gu: bool = True):
+    """``gu = x @ wgu^T`` and ``act = silu(gu[:, :F]) * gu[:, F:]`` from one GEMM (SwiGLU in the epilogue).  With
+    ``need_gu=False`` (forward-only) ``gu`` is neither stored nor returned (``None``)."""
+    M, K = x.shape
+    F = wgu.shape[0] // 2
+    x = _as_2d_rowmajor(x)
+    wgu = _as_2d_rowmajor(wgu)
+    gu = torch.empty((M, 2 * F), device=x.device, dtype=torch.bfloat16) if need_gu else None
+    act = torch.empty((M, F), device=x.device, dtype=torch.bfloat16)
+    code = _mlp_fns().sb_mlp_gate_up_swiglu(x.data_ptr(), wgu.data_ptr(), None if gu is None else gu.data_ptr(),
+                                            act.data_ptr(), M, F, K, x.stride(0), wgu.stride(0), _lib.stream_ptr())
+    _lib.check(code, "sb_mlp_gate_up_swiglu")
+    return gu, act
+
+
+def down_dgrad_swiglu(dy: torch.Tensor, wd: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+    """``d(gu)`` of ``swiglu(gu) @ wd^T`` given ``dy``: the product ``dy @ wd`` is consumed in the GEMM epilogue."""
+    M, H = dy.shape
+    F = wd.shape[1]
+    dy = _as_2d_rowmajor(dy)
+    wd = _as_2d_rowmajor(wd)
+    dgu = torch.empty((M, 2 * F), device=dy.device, dtype=torch.bfloat16)
+    code = _mlp_fns().sb_mlp_down_dgrad(dy.data_ptr(), wd.data_ptr(), gu.data_ptr(), dgu.data_ptr(), M, F, H, dy.stride(0),
+                                        wd.stride(0), _lib.stream_ptr())
+    _lib.check(code, "sb_mlp_down_dgrad")
+    return dgu
+
+
+class _SwiGLUMLPFn(torch.autograd.Function):
+    """``swiglu(x Wgu^T) Wd^T`` with the activation fused into the GEMM epilogues in both directions: the forward
+    writes ``gu`` and ``act`` from the gate/up GEMM, the backward turns ``dy Wd`` into ``d(gu)`` without storing it."""
+
+    @staticmethod
+    def forward(ctx, x, wgu, wd):
+        need = any(ctx.needs_input_grad)
+        gu, act = gate_up_swiglu(x, wgu, need_gu=need)
+        y = gemm_nt(act, wd)
+        if need:
+            ctx.save_for_backward(x, wgu, wd, gu, act)
+        ctx.wgu_main, ctx.wd_main = getattr(wgu, "main_grad", None), getattr(wd, "main_grad", None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wgu, wd, gu, act = ctx.saved_tensors
+        dy = dy.contiguous()
+        dwd = dwgu = None
+        if ctx.wd_main is not None:
+            gemm_tn(dy, act, out=ctx.wd_main, accumulate=True)
+        else:
+            dwd = gemm_tn(dy, act, out_dtype=wd.dtype)
+        dgu = down_dgrad_swiglu(dy, wd, gu)
+        dx = gemm_nn(dgu, wgu) if ctx.needs_input_grad[0] else None
+        if ctx.wgu_main is not None:
+            gemm_tn(dgu, x, out=ctx.wgu_main, accumulate=True)
+        else:
+            dwgu = gemm_tn(dgu, x, out_dtype=wgu.dtype)
+        return dx, dwgu, dwd
+
+
+def swiglu_mlp(x: torch.Tensor, wgu: torch.Tensor, wd: torch.Tensor) -> torch.Tensor:
+    """Dense SwiGLU feed-forward block.  Large CUDA batches take the fused-epilogue path; everything else is the plain
+    composition (``linear`` -> ``swiglu`` -> ``linear``)."""
+    if mlp_fusable(x, wgu, wd):
+        return _SwiGLUMLPFn.apply(x, wgu, wd)
+    from . import elementwise as ew
+
+    return linear(ew.swiglu(linear(x, wgu)), wd)

@@ -279,3 +279,46 @@ def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn, bn):
     gemm.gemm_2cta(A, B, acc, a_mn=a_mn, b_mn=b_mn, accumulate=True, bn=bn)
     torch.cuda.synchronize()
     assert ((acc - 1 - ref).norm() / ref.norm()).item() < 2e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,H,F", [(1024, 512, 1280), (2304, 1536, 8960), (777 + 256, 256, 384)])
+def test_fused_swiglu_mlp_matches_unfused(M, H, F):
+    """SwiGLU fused into the gate/up GEMM epilogue (forward) and into the down-projection input gradient (backward)
+    against the plain composition and an fp32 reference."""
+    import os
+
+    from skyrl_b200.ops import elementwise as ew
+
+    torch.manual_seed(M)
+    x = (torch.randn(M, H, device="cuda") * 0.5).to(torch.bfloat16)
+    wgu = (torch.randn(2 * F, H, device="cuda") * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(H, F, device="cuda") * 0.05).to(torch.bfloat16)
+    gy = (torch.randn(M, H, device="cuda") * 0.5).to(torch.bfloat16)
+
+    def run(fn):
+        xs, a, b = x.clone().requires_grad_(), wgu.clone().requires_grad_(), wd.clone().requires_grad_()
+        y = fn(xs, a, b)
+        y.backward(gy)
+        return y.detach().float(), xs.grad.float(), a.grad.float(), b.grad.float()
+
+    assert gemm.mlp_fusable(x, wgu, wd)
+    fused = run(gemm.swiglu_mlp)
+    plain = run(lambda xs, a, b: gemm.linear(ew.swiglu(gemm.linear(xs, a)), b))
+
+    def ref(xs, a, b):
+        gu = xs.float() @ a.float().t()
+        return (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ b.float().t()
+
+    xs, a, b = x.float().requires_grad_(), wgu.float().requires_grad_(), wd.float().requires_grad_()
+    yr = ref(xs, a, b)
+    yr.backward(gy.float())
+    refs = (yr.detach(), xs.grad, a.grad, b.grad)
+    for name, f, p_, r in zip(("y", "dx", "dwgu", "dwd"), fused, plain, refs):
+        scale = r.abs().max().clamp_min(1e-6)
+        assert (f - r).abs().max() / scale < 3e-2, (name, float((f - r).abs().max() / scale))
+        assert (f - p_).abs().max() / scale < 2e-2, (name, "vs unfused", float((f - p_).abs().max() / scale))
+    # forward-only callers skip the gate/up store
+    with torch.no_grad():
+        y2 = gemm.swiglu_mlp(x, wgu, wd).float()
+    assert torch.equal(y2, fused[0])
