@@ -159,6 +159,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive / copy completion
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  // barriers and tensor memory are private to the pair: with a programmatic dependent launch they are set up while
+  // the previous kernel drains; operands and outputs may belong to that kernel, so every role waits for it here
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -435,9 +439,10 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* bias,
   const int tiles = ((M + k2BM - 1) / k2BM) * ((N + BN - 1) / BN);
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kfn<<<2 * pairs, k2Threads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
-                                                         ldc, out_mode, device_status_ptr(), epi);
-  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+  const cudaError_t e = launch_pdl(kfn, dim3(2 * pairs), dim3(k2Threads), Cfg::kSmemBytes, stream, *ta, *tb, C,
+                                   reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, out_mode, device_status_ptr(),
+                                   epi);
+  return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
 }  // namespace sb

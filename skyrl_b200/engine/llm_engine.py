@@ -20,6 +20,7 @@ The engine also runs on CPU tensors (PyTorch reference ops, no graphs) for the p
 from __future__ import annotations
 
 import ctypes
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
@@ -301,6 +302,7 @@ class LLMEngine:
         table = m.rope_table(self.device)
         qkv = torch.empty((n, (a.num_heads + 2 * a.num_kv_heads) * a.head_dim), device=self.device, dtype=x.dtype)
         pending = None
+        fused_mlp = a.intermediate_size % 128 == 0 and n >= 32 and os.environ.get("SB_DECODE_FUSED_MLP", "1") != "0"
         for i in range(a.num_layers):
             pre = f"layers.{i}."
             if pending is None:
@@ -315,8 +317,11 @@ class LLMEngine:
                                              max_ctx=self.cfg.max_model_len)
             part, np_ = self._splitk_linear(att, m.p(pre + "wo"), None, n)
             h = ew.add_rmsnorm_partials_(x, part, np_, m.p(pre + "ln2"), a.rms_norm_eps)
-            gu = gemm.gemm_nt(h, m.p(pre + "wgu"), static_w=True)
-            pending = self._splitk_linear(ew.swiglu(gu), m.p(pre + "wd"), None, n)
+            if fused_mlp:  # SwiGLU in the epilogue of the CTA-pair gate/up GEMM
+                act = gemm.gate_up_swiglu(h, m.p(pre + "wgu"), need_gu=False)[1]
+            else:
+                act = ew.swiglu(gemm.gemm_nt(h, m.p(pre + "wgu"), static_w=True))
+            pending = self._splitk_linear(act, m.p(pre + "wd"), None, n)
         h = ew.add_rmsnorm_partials_(x, pending[0], pending[1], m.p("final_norm"), a.rms_norm_eps)
         logits = gemm.gemm_nt(h, m.lm_head_weight(), static_w=True)
         self._sample(logits, n, masked)
