@@ -184,59 +184,103 @@ __device__ __forceinline__ float to_f<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// One block per (row, vocabulary part).  Each part keeps the running maximum of logit + Gumbel noise (the sampled
+// token) and an online log-sum-exp (for the token's log-probability); the part that finishes last for a row merges
+// the parts (a per-row counter that it resets, so nothing has to be cleared between launches).
+struct SamplePart {
+  float best;
+  int best_i;
+  float m, s;
+};
+
+__device__ __forceinline__ void sample_merge(float& best, int& best_i, float& m, float& s, float ob, int oi, float om,
+                                             float os) {
+  if (ob > best || (ob == best && oi < best_i)) {
+    best = ob;
+    best_i = oi;
+  }
+  const float mn = fmaxf(m, om);
+  s = (m == -INFINITY ? 0.f : s * __expf(m - mn)) + (om == -INFINITY ? 0.f : os * __expf(om - mn));
+  m = mn;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads)
 sample_gumbel_kernel(const T* __restrict__ logits, long long row_stride, int V, const float* __restrict__ temperature,
                      unsigned long long seed, const long long* __restrict__ step_offsets, int* __restrict__ tokens,
-                     float* __restrict__ logprobs) {
+                     float* __restrict__ logprobs, SamplePart* __restrict__ parts, unsigned int* __restrict__ counters) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
+  const int n_parts = gridDim.y, part = blockIdx.y;
   const T* z = logits + static_cast<size_t>(row) * row_stride;
   const float temp = temperature[row];
   const bool greedy = temp <= 0.f;
   const float inv_t = greedy ? 1.f : 1.f / temp;
   curandStatePhilox4_32_10_t rng;
-  curand_init(seed, static_cast<unsigned long long>(row) * kSampThreads + threadIdx.x,
+  curand_init(seed, (static_cast<unsigned long long>(row) * n_parts + part) * kSampThreads + threadIdx.x,
               step_offsets ? static_cast<unsigned long long>(step_offsets[0]) * 1024ull : 0ull, &rng);
+  // this part's range, in whole groups of 8 elements
+  const int groups = (V + 7) / 8;
+  const int g_per = (groups + n_parts - 1) / n_parts;
+  const int g0 = part * g_per, g1 = min(groups, g0 + g_per);
+  const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(z) & 15) == 0);
   float best = -INFINITY, m = -INFINITY, s = 0.f;
   int best_i = 0x7fffffff;
-  for (int i0 = threadIdx.x * 4; i0 < V; i0 += kSampThreads * 4) {
-    float4 u4 = greedy ? make_float4(0.5f, 0.5f, 0.5f, 0.5f) : curand_uniform4(&rng);
-    const float u[4] = {u4.x, u4.y, u4.z, u4.w};
+  for (int g = g0 + threadIdx.x; g < g1; g += kSampThreads) {
+    const int i0 = g * 8;
+    float x[8];
+    if (vec_ok && i0 + 8 <= V) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(z + i0);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = i0 + e;
-      if (i < V) {
-        const float x = to_f<T>(z[i]) * inv_t;
-        const float mn = fmaxf(m, x);
-        s = s * __expf(m - mn) + __expf(x - mn);
-        m = mn;
-        const float gum = greedy ? 0.f : -__logf(-__logf(u[e]));
-        const float y = x + gum;
-        if (y > best || (y == best && i < best_i)) {
+      for (int e = 0; e < 4; ++e) {
+        x[2 * e] = __uint_as_float(w[e] << 16) * inv_t;
+        x[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u) * inv_t;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = (i0 + e < V) ? to_f<T>(z[i0 + e]) * inv_t : -INFINITY;
+    }
+    // log-sum-exp: one rescale per group instead of one per element
+    float gm = x[0];
+#pragma unroll
+    for (int e = 1; e < 8; ++e) gm = fmaxf(gm, x[e]);
+    if (gm > -INFINITY) {
+      const float mn = fmaxf(m, gm);
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += __expf(x[e] - mn);
+      s = s * __expf(m - mn) + acc;
+      m = mn;
+    }
+    if (greedy) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (x[e] > best) {  // ascending index within a thread: ties keep the first
+          best = x[e];
+          best_i = i0 + e;
+        }
+    } else {
+      const float4 ua = curand_uniform4(&rng), ub = curand_uniform4(&rng);
+      const float u[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float y = x[e] - __logf(-__logf(u[e]));
+        if (y > best) {
           best = y;
-          best_i = i;
+          best_i = i0 + e;
         }
       }
     }
   }
   __shared__ float sh_best[kSampThreads / 32], sh_m[kSampThreads / 32], sh_s[kSampThreads / 32];
   __shared__ int sh_i[kSampThreads / 32];
+  __shared__ bool is_last;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ob > best || (ob == best && oi < best_i)) {
-      best = ob;
-      best_i = oi;
-    }
-    const float om = __shfl_xor_sync(0xffffffffu, m, o);
-    const float os = __shfl_xor_sync(0xffffffffu, s, o);
-    const float mn = fmaxf(m, om);
-    s = (m == -INFINITY ? 0.f : s * __expf(m - mn)) + (om == -INFINITY ? 0.f : os * __expf(om - mn));
-    m = mn;
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    sample_merge(best, best_i, m, s, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, best_i, o),
+                 __shfl_xor_sync(0xffffffffu, m, o), __shfl_xor_sync(0xffffffffu, s, o));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (lane == 0) {
     sh_best[warp] = best;
@@ -246,17 +290,31 @@ sample_gumbel_kernel(const T* __restrict__ logits, long long row_stride, int V, 
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < kSampThreads / 32; ++w) {
-      if (sh_best[w] > best || (sh_best[w] == best && sh_i[w] < best_i)) {
-        best = sh_best[w];
-        best_i = sh_i[w];
+    for (int w = 1; w < kSampThreads / 32; ++w) sample_merge(best, best_i, m, s, sh_best[w], sh_i[w], sh_m[w], sh_s[w]);
+    if (n_parts > 1) {
+      parts[static_cast<size_t>(row) * n_parts + part] = SamplePart{best, best_i, m, s};
+      __threadfence();
+      is_last = atomicAdd(counters + row, 1u) == static_cast<unsigned int>(n_parts - 1);
+      if (is_last) {
+        __threadfence();
+        best = -INFINITY;
+        best_i = 0x7fffffff;
+        m = -INFINITY;
+        s = 0.f;
+        for (int p = 0; p < n_parts; ++p) {
+          const volatile SamplePart* sp = parts + static_cast<size_t>(row) * n_parts + p;
+          sample_merge(best, best_i, m, s, sp->best, sp->best_i, sp->m, sp->s);
+        }
+        counters[row] = 0;
       }
-      const float mn = fmaxf(m, sh_m[w]);
-      s = (m == -INFINITY ? 0.f : s * __expf(m - mn)) + (sh_m[w] == -INFINITY ? 0.f : sh_s[w] * __expf(sh_m[w] - mn));
-      m = mn;
+    } else {
+      is_last = true;
     }
-    tokens[row] = best_i;
-    logprobs[row] = to_f<T>(z[best_i]) * inv_t - (m + __logf(s));
+    if (is_last) {
+      best_i = best_i < V ? best_i : V - 1;
+      tokens[row] = best_i;
+      logprobs[row] = to_f<T>(z[best_i]) * inv_t - (m + __logf(s));
+    }
   }
 }
 
@@ -398,13 +456,47 @@ int sb_sample_gumbel(const void* logits, int is_bf16, long long row_stride, int 
                      void* stream) {
   if (n <= 0 || V <= 0) return SB_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // Rows are split into vocabulary parts until the grid has a few blocks per SM.  The partial records live in a
+  // library-owned buffer of kSlots regions used round-robin, so that launches in flight on different streams (or
+  // baked into different CUDA graphs) do not share a region.  The buffer is created by the first call (outside any
+  // stream capture: engines run one eager step before they capture).
+  constexpr int kSlots = 16, kMaxRows = 4096, kMaxParts = 8;
+  static sb::SamplePart* part_buf = nullptr;
+  static unsigned int* counter_buf = nullptr;
+  static unsigned int next_slot = 0;
+  int n_parts = 1;
+  if (n <= kMaxRows && V >= 32768) {
+    const int want = (4 * sb::sm_count() + n - 1) / n;
+    n_parts = want < 1 ? 1 : (want > kMaxParts ? kMaxParts : want);
+  }
+  if (n_parts > 1 && part_buf == nullptr) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cs);
+    if (cs != cudaStreamCaptureStatusNone) {
+      n_parts = 1;  // cannot allocate while capturing
+    } else {
+      if (cudaMalloc(&part_buf, sizeof(sb::SamplePart) * kSlots * kMaxRows * kMaxParts) != cudaSuccess ||
+          cudaMalloc(&counter_buf, sizeof(unsigned int) * kSlots * kMaxRows) != cudaSuccess ||
+          cudaMemset(counter_buf, 0, sizeof(unsigned int) * kSlots * kMaxRows) != cudaSuccess)
+        return SB_ERR_CUDA;
+    }
+  }
+  sb::SamplePart* parts = nullptr;
+  unsigned int* counters = nullptr;
+  if (n_parts > 1) {
+    const unsigned int slot = next_slot++ % kSlots;
+    parts = part_buf + static_cast<size_t>(slot) * kMaxRows * kMaxParts;
+    counters = counter_buf + static_cast<size_t>(slot) * kMaxRows;
+  }
+  const dim3 grid(n, n_parts);
   if (is_bf16)
-    sb::launch_pdl(sb::sample_gumbel_kernel<__nv_bfloat16>, dim3(n), dim3(sb::kSampThreads), 0, st,
+    sb::launch_pdl(sb::sample_gumbel_kernel<__nv_bfloat16>, grid, dim3(sb::kSampThreads), 0, st,
                    reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V, temperature, seed, step_offsets, tokens,
-                   logprobs);
+                   logprobs, parts, counters);
   else
-    sb::launch_pdl(sb::sample_gumbel_kernel<float>, dim3(n), dim3(sb::kSampThreads), 0, st,
-                   reinterpret_cast<const float*>(logits), row_stride, V, temperature, seed, step_offsets, tokens, logprobs);
+    sb::launch_pdl(sb::sample_gumbel_kernel<float>, grid, dim3(sb::kSampThreads), 0, st,
+                   reinterpret_cast<const float*>(logits), row_stride, V, temperature, seed, step_offsets, tokens, logprobs,
+                   parts, counters);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

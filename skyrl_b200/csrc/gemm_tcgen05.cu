@@ -386,7 +386,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             store_chunk(C, ks * split_stride + static_cast<long long>(row) * ldc + col0);
           } else if (tp.scatter_idx) {
             const int dest = __ldg(tp.idx_rank + row);
-            store_chunk(tp.dst[dest], static_cast<long long>(__ldg(tp.idx_row + row)) * ldc + col0);
+            if (dest >= 0) store_chunk(tp.dst[dest], static_cast<long long>(__ldg(tp.idx_row + row)) * ldc + col0);
           } else if (tp.scatter_cols) {
             int sg = 0, base = 0;
             if (tp.seg_w[1] > 0 && col0 >= tp.seg_start[1]) { sg = 1; base = tp.seg_w[0]; }
@@ -439,9 +439,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int rr = 0; rr < rows_here; ++rr) {
           const int r = row0 + rr;
           const int sr = __ldg(tp.idx_rank + r);
+          uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tp.a_full) + static_cast<long long>(r) * tp.lda);
+          if (sr < 0) {  // padding row of an expert's last tile
+            for (int c = lane; c < vec_per_row; c += 32) drow[c] = make_uint4(0, 0, 0, 0);
+            continue;
+          }
           const uint4* srow = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(tp.src[sr]) +
                                                              static_cast<long long>(__ldg(tp.idx_row + r)) * tp.src_ld);
-          uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tp.a_full) + static_cast<long long>(r) * tp.lda);
           for (int base = 0; base < vec_per_row; base += 32 * 8) {
             uint4 v[8];
 #pragma unroll
@@ -544,10 +548,12 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
 // and / or the output scattered to peers (see TpArgs).
 template <int BN, bool B_MN, bool GATHER, bool SCATTER>
 static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
-                          long long ldb, long long ldc, int out_mode, const TpArgs& tp, cudaStream_t stream) {
+                          long long ldb, long long ldc, int out_mode, const TpArgs& tp, cudaStream_t stream,
+                          int b_groups = 1) {
   using Cfg = GemmCfg<BN>;
   const CUtensorMap* ta = get_tmap_bf16_2d(A, M, K, lda, kBM);
-  const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN);
+  const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, static_cast<long long>(K) * b_groups, N, ldb, 64)
+                               : get_tmap_bf16_2d(B, static_cast<long long>(N) * b_groups, K, ldb, BN);
   if (!ta || !tb) return SB_ERR_TMAP;
   static bool attr_set = false;
   auto kfn = gemm_bf16_kernel<BN, false, B_MN, GATHER, SCATTER>;
@@ -852,12 +858,22 @@ int sb_gemm_sp(const void* A, const void* B, void* C, const void* bias, int M, i
 //   mode 1 (dispatch): A row r is fetched from row idx_row[r] of peers[idx_rank[r]] (row stride src_ld) into the local
 //       buffer A while the GEMM runs; C is a plain local output.  flags: (M/128 + 2) uint32 of scratch.
 //   mode 2 (combine): A is local; C row r is stored to row idx_row[r] of peers[idx_rank[r]] (row stride ldc).
-int sb_gemm_ep(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
-               int b_mn, int mode, void* const* peers, int n_ranks, int my_rank, const int* idx_rank, const int* idx_row,
-               long long src_ld, unsigned int* flags, int bn, void* stream) {
+// n_groups > 0: the rows are grouped by expert in 128-row tiles (tile_expert[M / 128], -1 = unused tile), B holds
+// n_groups stacked matrices and rows whose idx_rank is negative are padding (zero on dispatch, not stored on combine).
+int sb_gemm_ep_grouped(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                       long long ldc, int b_mn, int mode, void* const* peers, int n_ranks, int my_rank,
+                       const int* idx_rank, const int* idx_row, long long src_ld, unsigned int* flags, int bn,
+                       int n_groups, const int* tile_expert, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (K & 7) || !peers || !idx_rank || !idx_row) return SB_ERR_ARG;
   if (n_ranks < 1 || n_ranks > sb::kTpMaxRanks || my_rank < 0 || my_rank >= n_ranks) return SB_ERR_ARG;
+  if (n_groups > 0 && (!tile_expert || (M % sb::kBM) != 0)) return SB_ERR_ARG;
+  const int bg = n_groups > 0 ? n_groups : 1;
   sb::TpArgs tp{};
+  if (n_groups > 0) {
+    tp.group_mode = 1;
+    tp.tile_expert = tile_expert;
+    tp.group_b_rows = b_mn ? K : N;
+  }
   tp.n_ranks = n_ranks;
   tp.my_rank = my_rank;
   tp.rows_per_rank = M;
@@ -877,11 +893,11 @@ int sb_gemm_ep(const void* A, const void* B, void* C, int M, int N, int K, long 
       tp.src[r] = peers[r];
     }
     if (b_mn) {
-      if (bn == 256) return sb::launch_gemm_tp<256, true, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
-      return sb::launch_gemm_tp<128, true, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+      if (bn == 256) return sb::launch_gemm_tp<256, true, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
+      return sb::launch_gemm_tp<128, true, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
     }
-    if (bn == 256) return sb::launch_gemm_tp<256, false, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
-    return sb::launch_gemm_tp<128, false, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+    if (bn == 256) return sb::launch_gemm_tp<256, false, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
+    return sb::launch_gemm_tp<128, false, true, false>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
   }
   if (mode == 2) {
     tp.scatter_idx = 1;
@@ -890,13 +906,20 @@ int sb_gemm_ep(const void* A, const void* B, void* C, int M, int N, int K, long 
       tp.dst[r] = peers[r];
     }
     if (b_mn) {
-      if (bn == 256) return sb::launch_gemm_tp<256, true, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
-      return sb::launch_gemm_tp<128, true, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+      if (bn == 256) return sb::launch_gemm_tp<256, true, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
+      return sb::launch_gemm_tp<128, true, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
     }
-    if (bn == 256) return sb::launch_gemm_tp<256, false, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
-    return sb::launch_gemm_tp<128, false, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st);
+    if (bn == 256) return sb::launch_gemm_tp<256, false, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
+    return sb::launch_gemm_tp<128, false, false, true>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, tp, st, bg);
   }
   return SB_ERR_ARG;
+}
+
+int sb_gemm_ep(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+               int b_mn, int mode, void* const* peers, int n_ranks, int my_rank, const int* idx_rank, const int* idx_row,
+               long long src_ld, unsigned int* flags, int bn, void* stream) {
+  return sb_gemm_ep_grouped(A, B, C, M, N, K, lda, ldb, ldc, b_mn, mode, peers, n_ranks, my_rank, idx_rank, idx_row, src_ld,
+                            flags, bn, 0, nullptr, stream);
 }
 
 }  // extern "C"

@@ -36,6 +36,7 @@ def _k():
     if not _cfg:
         vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         lib.sb_gemm_ep.argtypes = [vp, vp, vp, ci, ci, ci, cl, cl, cl, ci, ci, vp, ci, ci, vp, vp, cl, vp, ci, vp]
+        lib.sb_gemm_ep_grouped.argtypes = [vp, vp, vp, ci, ci, ci, cl, cl, cl, ci, ci, vp, ci, ci, vp, vp, cl, vp, ci, ci, vp, vp]
         _cfg = True
     return lib
 
@@ -57,8 +58,15 @@ def build_routing_tables(idx: torch.Tensor, ep: TPGroup, num_experts: int) -> Tu
     e = full[r, t, s] - ep.rank * E_local
     order = torch.argsort(e, stable=True)
     r, t, s, e = r[order], t[order], s[order], e[order]
-    counts = torch.bincount(e, minlength=E_local).tolist()
+    counts = _Counts(torch.bincount(e, minlength=E_local).tolist())
+    counts.expert_of_row = e  # [n] local expert of every row (sorted), for the grouped launch
     return r.to(torch.int32).contiguous(), t.to(torch.int32).contiguous(), (t * k + s).to(torch.int32).contiguous(), counts
+
+
+class _Counts(list):
+    """Per-local-expert row counts; also carries the per-row expert ids as an attribute."""
+
+    expert_of_row: Optional[torch.Tensor] = None
 
 
 class _ExpertParallelFFN(torch.autograd.Function):
@@ -80,30 +88,31 @@ class _ExpertParallelFFN(torch.autograd.Function):
             ep.peer.barrier()
             peers_h = (ctypes.c_void_p * ep.size)(*hbuf.ptrs)
             peers_c = (ctypes.c_void_p * ep.size)(*comb.ptrs)
-            x_rows = torch.empty((max(n, 1), H), device=h.device, dtype=h.dtype)
-            gu = torch.empty((max(n, 1), F2), device=h.device, dtype=h.dtype)
-            flags = ep.flags((max(n, 1) + 127) // 128 + 1)
-            s = 0
-            for e in range(E_local):
-                c = counts[e]
-                if c == 0:
-                    continue
-                code = _k().sb_gemm_ep(x_rows[s:].data_ptr(), wgu[e].data_ptr(), gu[s:].data_ptr(), c, F2, H, H, H, F2, 0, 1,
-                                       peers_h, ep.size, ep.rank, src_rank[s:].data_ptr(), src_row[s:].data_ptr(), H,
-                                       flags.data_ptr(), 0, _lib.stream_ptr())
-                _lib.check(code, "sb_gemm_ep(dispatch)")
-                s += c
-            act = ew.swiglu(gu[:n]) if n else gu.new_zeros((0, F2 // 2))
-            s = 0
-            for e in range(E_local):
-                c = counts[e]
-                if c == 0:
-                    continue
-                code = _k().sb_gemm_ep(act[s:].data_ptr(), wd[e].data_ptr(), None, c, H, F2 // 2, F2 // 2, F2 // 2, H, 0, 2,
-                                       peers_c, ep.size, ep.rank, src_rank[s:].data_ptr(), dst_row[s:].data_ptr(), 0, None, 0,
-                                       _lib.stream_ptr())
-                _lib.check(code, "sb_gemm_ep(combine)")
-                s += c
+            # one grouped launch per projection: rows padded so that every 128-row tile belongs to one expert
+            from ..ops import grouped_gemm as gg
+
+            plan = gg.plan_groups(counts.expert_of_row, E_local)
+            Mc = plan.m_cap
+            pad_rank = torch.full((Mc,), -1, dtype=torch.int32, device=h.device)
+            pad_srow = torch.zeros((Mc,), dtype=torch.int32, device=h.device)
+            pad_drow = torch.zeros((Mc,), dtype=torch.int32, device=h.device)
+            pad_rank[plan.dst_row] = src_rank
+            pad_srow[plan.dst_row] = src_row
+            pad_drow[plan.dst_row] = dst_row
+            x_rows = torch.empty((Mc, H), device=h.device, dtype=h.dtype)
+            gu = torch.empty((Mc, F2), device=h.device, dtype=h.dtype)
+            flags = ep.flags(Mc // 128 + 2)
+            wgu_c, wd_c = wgu.contiguous(), wd.contiguous()
+            code = _k().sb_gemm_ep_grouped(x_rows.data_ptr(), wgu_c.data_ptr(), gu.data_ptr(), Mc, F2, H, H, H, F2, 0, 1,
+                                           peers_h, ep.size, ep.rank, pad_rank.data_ptr(), pad_srow.data_ptr(), H,
+                                           flags.data_ptr(), 256, E_local, plan.tile_expert.data_ptr(), _lib.stream_ptr())
+            _lib.check(code, "sb_gemm_ep_grouped(dispatch)")
+            act = ew.swiglu(gu)
+            code = _k().sb_gemm_ep_grouped(act.data_ptr(), wd_c.data_ptr(), None, Mc, H, F2 // 2, F2 // 2, F2 // 2, H, 0, 2,
+                                           peers_c, ep.size, ep.rank, pad_rank.data_ptr(), pad_drow.data_ptr(), 0, None,
+                                           256, E_local, plan.tile_expert.data_ptr(), _lib.stream_ptr())
+            _lib.check(code, "sb_gemm_ep_grouped(combine)")
+            ctx.plan = plan
             ep.peer.barrier()
             y_slots = comb.local[: T * k * H].view(T, k, H).clone()
         else:
@@ -111,8 +120,12 @@ class _ExpertParallelFFN(torch.autograd.Function):
             y_slots = _reference_combine(y_rows, ep, src_rank, dst_row, T, k, H)
         out = (y_slots.float() * w.float().unsqueeze(-1)).sum(1).to(h.dtype)
         ctx.ep, ctx.num_experts, ctx.counts, ctx.fused = ep, num_experts, counts, fused
-        ctx.save_for_backward(w, x_rows[:n] if n else x_rows[:0], gu[:n] if n else gu[:0], act, y_slots, wgu, wd, src_rank,
-                              src_row, dst_row)
+        if fused:
+            ctx.save_for_backward(w, x_rows, gu, act, y_slots, wgu, wd, src_rank, src_row, dst_row)
+        else:
+            ctx.plan = None
+            ctx.save_for_backward(w, x_rows[:n] if n else x_rows[:0], gu[:n] if n else gu[:0], act, y_slots, wgu, wd,
+                                  src_rank, src_row, dst_row)
         ctx.wgu_main, ctx.wd_main = getattr(wgu, "main_grad", None), getattr(wd, "main_grad", None)
         ctx.shape = (T, H, k)
         return out
@@ -130,9 +143,25 @@ class _ExpertParallelFFN(torch.autograd.Function):
         dy_slots = (dout.float().unsqueeze(1) * w.float().unsqueeze(-1)).to(dout.dtype).reshape(T * k, H).contiguous()
         # "dispatch" the slot gradients to the experts (rows indexed by dst_row on the owner), then mirror the forward
         dy_rows = _exchange_rows_to_experts(dy_slots, ep, src_rank, dst_row, n, H, ctx.fused, "ep_dy")
-        dact = torch.empty((max(n, 1), F), device=dout.device, dtype=dout.dtype)[:n]
         dwd = ctx.wd_main if ctx.wd_main is not None else torch.zeros(wd.shape, device=wd.device, dtype=torch.float32)
         dwgu = ctx.wgu_main if ctx.wgu_main is not None else torch.zeros(wgu.shape, device=wgu.device, dtype=torch.float32)
+        if ctx.plan is not None:
+            # grouped launches over the padded layout saved by the forward pass (padding rows are zero)
+            from ..ops import grouped_gemm as gg
+
+            plan = ctx.plan
+            dy_pad = torch.zeros((plan.m_cap, H), device=dout.device, dtype=dout.dtype).index_copy(0, plan.dst_row, dy_rows)
+            dact = gg.grouped_nn(dy_pad, wd, plan)
+            gg.grouped_tn(dy_pad, act, plan, dwd.view(wd.shape), accumulate=True)
+            dgu = ew.swiglu_backward(gu, dact)
+            dx_pad = gg.grouped_nn(dgu, wgu, plan)
+            gg.grouped_tn(dgu, x_rows, plan, dwgu.view(wgu.shape), accumulate=True)
+            dx_rows = dx_pad[plan.dst_row]
+            dh_slots = _fused_combine_rows(dx_rows, ep, src_rank, dst_row, T, k, H)
+            dh = dh_slots.float().sum(1).to(dout.dtype)
+            return (dh, dw, None, None if ctx.wgu_main is not None else dwgu.to(wgu.dtype),
+                    None if ctx.wd_main is not None else dwd.to(wd.dtype), None, None)
+        dact = torch.empty((max(n, 1), F), device=dout.device, dtype=dout.dtype)[:n]
         s = 0
         for e in range(E_local):
             c = counts[e]
