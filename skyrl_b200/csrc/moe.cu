@@ -118,6 +118,156 @@ __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ y, cons
   }
 }
 
+
+// Router: softmax over the experts, top-k, optional renormalisation of the k weights.  One warp per token; lane l
+// holds experts l, l + 32, ...  (E <= 1024, k <= 16).  Ties go to the lower expert index.
+constexpr int kRouteMaxPerLane = 32;
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ w, int* __restrict__ idx, int T, int E,
+                                 int k, int norm) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int per = (E + 31) >> 5;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_block) {
+    const float* z = logits + static_cast<size_t>(t) * E;
+    float p[kRouteMaxPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      if (j < per) {
+        const int e = j * 32 + lane;
+        p[j] = e < E ? __ldg(z + e) : -INFINITY;
+        mx = fmaxf(mx, p[j]);
+      }
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      if (j < per) {
+        p[j] = __expf(p[j] - mx);
+        sum += p[j];
+      }
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    float sel_sum = 0.f;
+    float my_w = 0.f;  // lane s keeps the s-th selected weight
+    int my_i = 0;
+    for (int s = 0; s < k; ++s) {
+      float best = -1.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < kRouteMaxPerLane; ++j) {
+        if (j < per && p[j] > best) {  // ascending expert index within a lane: ties keep the lower one
+          best = p[j];
+          best_e = j * 32 + lane;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) {
+          best = ob;
+          best_e = oe;
+        }
+      }
+      if ((best_e & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < kRouteMaxPerLane; ++j)
+          if (j == (best_e >> 5)) p[j] = -1.f;  // taken
+      }
+      const float pv = best * inv;
+      sel_sum += pv;
+      if (lane == s) {
+        my_w = pv;
+        my_i = best_e;
+      }
+    }
+    if (lane < k) {
+      w[static_cast<size_t>(t) * k + lane] = norm ? my_w / sel_sum : my_w;
+      idx[static_cast<size_t>(t) * k + lane] = my_i;
+    }
+  }
+}
+
+// d(logits) from d(w): w_j = p_j / S (S = sum of the selected p) when norm, else w_j = p_j, and p = softmax(logits).
+__global__ void moe_route_bwd_kernel(const float* __restrict__ logits, const float* __restrict__ w, const int* __restrict__ idx,
+                                     const float* __restrict__ dw, float* __restrict__ dlogits, int T, int E, int k, int norm) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int per = (E + 31) >> 5;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_block) {
+    const float* z = logits + static_cast<size_t>(t) * E;
+    float p[kRouteMaxPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      if (j < per) {
+        const int e = j * 32 + lane;
+        p[j] = e < E ? __ldg(z + e) : -INFINITY;
+        mx = fmaxf(mx, p[j]);
+      }
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      if (j < per) {
+        p[j] = __expf(p[j] - mx);
+        sum += p[j];
+      }
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    // lane s < k owns selected slot s
+    const int my_e = lane < k ? __ldg(idx + static_cast<size_t>(t) * k + lane) : -1;
+    const float my_dw = lane < k ? __ldg(dw + static_cast<size_t>(t) * k + lane) : 0.f;
+    const float my_wt = lane < k ? __ldg(w + static_cast<size_t>(t) * k + lane) : 0.f;
+    float dp_sel = my_dw;  // d/dp of the selected probability
+    float p_sel = 0.f;
+    if (norm) {
+      const float dot = warp_sum(my_dw * my_wt);
+      // S = p_j / w_j for any selected j with w_j > 0; recompute it from the probabilities instead
+      float ps = 0.f;
+      for (int s = 0; s < k; ++s) {
+        const int e = __shfl_sync(0xffffffffu, my_e, s);
+        float v = 0.f;
+#pragma unroll
+        for (int j = 0; j < kRouteMaxPerLane; ++j)
+          if (j < per && j == (e >> 5) && (e & 31) == lane) v = p[j] * inv;
+        v = warp_sum(v);
+        ps += v;
+        if (lane == s) p_sel = v;
+      }
+      dp_sel = (my_dw - dot) / ps;
+    } else {
+      for (int s = 0; s < k; ++s) {
+        const int e = __shfl_sync(0xffffffffu, my_e, s);
+        float v = 0.f;
+#pragma unroll
+        for (int j = 0; j < kRouteMaxPerLane; ++j)
+          if (j < per && j == (e >> 5) && (e & 31) == lane) v = p[j] * inv;
+        v = warp_sum(v);
+        if (lane == s) p_sel = v;
+      }
+    }
+    const float inner = warp_sum(lane < k ? p_sel * dp_sel : 0.f);  // sum_m p_m dp_m
+    // dlogits_i = p_i * (dp_i - inner)
+    float* out = dlogits + static_cast<size_t>(t) * E;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      if (j < per) {
+        const int e = j * 32 + lane;
+        if (e < E) out[e] = -p[j] * inv * inner;
+      }
+    }
+    __syncwarp();
+    if (lane < k) out[my_e] = p_sel * (dp_sel - inner);
+  }
+}
+
 }  // namespace sb
 
 extern "C" {
@@ -150,6 +300,23 @@ int sb_moe_combine_bwd(const void* y, const int* slot_row, const float* w, const
                                reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(y), slot_row, w, reinterpret_cast<const __nv_bfloat16*>(dout),
       reinterpret_cast<__nv_bfloat16*>(dy), dw, n, k, H);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+int sb_moe_route(const float* logits, float* w, int* idx, int T, int E, int k, int norm, void* stream) {
+  if (T <= 0 || E <= 0 || E > 32 * sb::kRouteMaxPerLane || k <= 0 || k > 16 || k > E) return SB_ERR_ARG;
+  const int blocks = (T + 7) / 8;
+  sb::moe_route_kernel<<<blocks < 148 * 8 ? blocks : 148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, w, idx, T,
+                                                                                                            E, k, norm);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+int sb_moe_route_bwd(const float* logits, const float* w, const int* idx, const float* dw, float* dlogits, int T, int E, int k,
+                     int norm, void* stream) {
+  if (T <= 0 || E <= 0 || E > 32 * sb::kRouteMaxPerLane || k <= 0 || k > 16 || k > E) return SB_ERR_ARG;
+  const int blocks = (T + 7) / 8;
+  sb::moe_route_bwd_kernel<<<blocks < 148 * 8 ? blocks : 148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      logits, w, idx, dw, dlogits, T, E, k, norm);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -16,9 +16,52 @@ from ..ops import gemm  # noqa: F401
 from ..ops import grouped_gemm as gg
 
 
+class _RouteFn(torch.autograd.Function):
+    """softmax -> top-k -> (re)normalise in one kernel per direction (``csrc/moe.cu``)."""
+
+    @staticmethod
+    def forward(ctx, logits, top_k, norm):
+        import ctypes
+
+        from ..ops import _lib
+
+        lib = _lib.kernels()
+        if not getattr(lib.sb_moe_route, "_configured", False):
+            vp, ci = ctypes.c_void_p, ctypes.c_int
+            lib.sb_moe_route.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
+            lib.sb_moe_route_bwd.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp]
+            lib.sb_moe_route.restype = lib.sb_moe_route_bwd.restype = ci
+            lib.sb_moe_route._configured = True
+        T, E = logits.shape
+        logits = logits.contiguous()
+        w = torch.empty((T, top_k), device=logits.device, dtype=torch.float32)
+        idx = torch.empty((T, top_k), device=logits.device, dtype=torch.int32)
+        _lib.check(lib.sb_moe_route(logits.data_ptr(), w.data_ptr(), idx.data_ptr(), T, E, top_k, int(norm), _lib.stream_ptr()),
+                   "sb_moe_route")
+        ctx.save_for_backward(logits, w, idx)
+        ctx.norm, ctx.lib = bool(norm), lib
+        ctx.mark_non_differentiable(idx)
+        return w, idx
+
+    @staticmethod
+    def backward(ctx, dw, _didx):
+        from ..ops import _lib
+
+        logits, w, idx = ctx.saved_tensors
+        T, E = logits.shape
+        dlogits = torch.empty_like(logits)
+        dw = dw.float().contiguous()
+        _lib.check(ctx.lib.sb_moe_route_bwd(logits.data_ptr(), w.data_ptr(), idx.data_ptr(), dw.data_ptr(), dlogits.data_ptr(),
+                                            T, E, idx.shape[1], int(ctx.norm), _lib.stream_ptr()), "sb_moe_route_bwd")
+        return dlogits, None, None
+
+
 def route_topk(h: torch.Tensor, router_w: torch.Tensor, top_k: int, norm_topk_prob: bool):
     """Returns (weights [T, k] fp32, expert ids [T, k]); router math in fp32 like the reference config."""
     logits = h.float() @ router_w.float().t()
+    if logits.is_cuda and logits.shape[1] <= 1024 and top_k <= 16:
+        w, idx = _RouteFn.apply(logits, top_k, norm_topk_prob)
+        return w, idx.long()
     probs = torch.softmax(logits, dim=-1)
     w, idx = torch.topk(probs, top_k, dim=-1)
     if norm_topk_prob:

@@ -274,3 +274,17 @@ def dispatch_rows(h: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
 def combine_rows(y: torch.Tensor, w: torch.Tensor, plan: GroupPlan) -> torch.Tensor:
     """``out[t] = sum_s w[t, s] * y[row of (t, s)]`` with ``w`` ``[T, top_k]``; differentiable in ``y`` and ``w``."""
     return _CombineFn.apply(y, w, plan)
+
+
+def weighted_slot_sum(y_slots: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``out[t] = sum_s w[t, s] * y_slots[t, s]`` for ``y_slots`` ``[T, k, H]`` (fp32 accumulation, no autograd)."""
+    T, k, H = y_slots.shape
+    if not y_slots.is_cuda or k > 16 or H % 8 != 0:
+        return (y_slots.float() * w.float().unsqueeze(-1)).sum(1).to(y_slots.dtype)
+    y = y_slots.contiguous().view(T * k, H)
+    rows = torch.arange(T * k, device=y.device, dtype=torch.int32)
+    w32 = w.float().contiguous()
+    out = torch.empty((T, H), device=y.device, dtype=y.dtype)
+    code = _moe_fns().sb_moe_combine(y.data_ptr(), rows.data_ptr(), w32.data_ptr(), out.data_ptr(), T, k, H, _lib.stream_ptr())
+    _lib.check(code, "sb_moe_combine")
+    return out

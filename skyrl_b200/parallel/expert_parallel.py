@@ -118,7 +118,9 @@ class _ExpertParallelFFN(torch.autograd.Function):
         else:
             x_rows, gu, act, y_rows = _reference_expert_rows(h, wgu, wd, ep, src_rank, src_row, counts)
             y_slots = _reference_combine(y_rows, ep, src_rank, dst_row, T, k, H)
-        out = (y_slots.float() * w.float().unsqueeze(-1)).sum(1).to(h.dtype)
+        from ..ops.grouped_gemm import weighted_slot_sum
+
+        out = weighted_slot_sum(y_slots, w)
         ctx.ep, ctx.num_experts, ctx.counts, ctx.fused = ep, num_experts, counts, fused
         if fused:
             ctx.save_for_backward(w, x_rows, gu, act, y_slots, wgu, wd, src_rank, src_row, dst_row)

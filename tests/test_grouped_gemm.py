@@ -172,3 +172,28 @@ def test_moe_layer_gpu_matches_fp32_reference():
     for a, b, name in zip((h, wgu, wd), ref_in, ("h", "wgu", "wd")):
         e = (a.grad.float() - b.grad).abs().max() / b.grad.abs().max().clamp_min(1e-6)
         assert e < 5e-2, (name, float(e))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,E,k,norm", [(1000, 128, 8, True), (333, 60, 4, False), (64, 8, 2, True), (500, 256, 1, True)])
+def test_router_kernel_matches_torch(T, E, k, norm):
+    from skyrl_b200.models.moe import _RouteFn
+
+    torch.manual_seed(E + k)
+    logits = (torch.randn(T, E, device="cuda") * 2.0).requires_grad_()
+    w, idx = _RouteFn.apply(logits, k, norm)
+    ref_l = logits.detach().clone().requires_grad_()
+    probs = torch.softmax(ref_l, -1)
+    wr, ir = torch.topk(probs, k, -1)
+    if norm:
+        wr = wr / wr.sum(-1, keepdim=True)
+    assert torch.equal(idx.long().sort(-1).values, ir.sort(-1).values)
+    order = idx.long().argsort(-1)
+    order_r = ir.argsort(-1)
+    assert torch.allclose(w.gather(-1, order), wr.gather(-1, order_r), atol=1e-5, rtol=1e-4)
+    g = torch.randn(T, k, device="cuda")
+    # same gradient per selected expert on both sides (the two orders of the k slots may differ)
+    g_ref = torch.zeros(T, E, device="cuda").scatter(-1, idx.long(), g).gather(-1, ir)
+    w.backward(g)
+    wr.backward(g_ref)
+    assert torch.allclose(logits.grad, ref_l.grad, atol=2e-5, rtol=1e-3), float((logits.grad - ref_l.grad).abs().max())
