@@ -268,6 +268,83 @@ __global__ void moe_route_bwd_kernel(const float* __restrict__ logits, const flo
   }
 }
 
+
+// Layout plan of a grouped expert launch, one CTA: histogram of the routed entries per expert, every expert's row
+// range padded to whole 128-row tiles, and a *stable* placement of the entries (entry order is kept inside an expert,
+// so the row order -- and with it the summation order of the weight gradients -- does not change from run to run).
+// Each warp owns a contiguous segment of the entries: pass A counts its segment per expert, a scan over the warps
+// turns the counts into per-warp cursors, pass B walks the segment again and places the entries.
+//   k_off[E + 1]        first padded row of each expert
+//   tile_expert[tiles]  owner of every 128-row tile, -1 = unused
+//   row_src[m_cap]      token (entry / top_k) whose hidden row fills a padded row, -1 = padding
+//   slot_row[n]         padded row of every entry
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanWarps = kPlanThreads / 32;
+
+template <typename IdT>
+__global__ void __launch_bounds__(kPlanThreads, 1)
+moe_plan_kernel(const IdT* __restrict__ ids, int n, int E, int top_k, int m_cap, int* __restrict__ k_off,
+                int* __restrict__ tile_expert, int* __restrict__ row_src, int* __restrict__ slot_row) {
+  extern __shared__ int plan_smem[];
+  int* cnt = plan_smem;                 // [kPlanWarps][E] counts, then cursors
+  int* off = plan_smem + kPlanWarps * E;  // [E + 1]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kPlanWarps * E; i += kPlanThreads) cnt[i] = 0;
+  for (int i = threadIdx.x; i < m_cap; i += kPlanThreads) row_src[i] = -1;
+  for (int i = threadIdx.x; i < m_cap / 128; i += kPlanThreads) tile_expert[i] = -1;
+  __syncthreads();
+  const int seg = (n + kPlanWarps - 1) / kPlanWarps;
+  const int lo = min(n, warp * seg), hi = min(n, lo + seg);
+  for (int i = lo + lane; i < hi; i += 32) {
+    const int e = static_cast<int>(ids[i]);
+    if (e >= 0 && e < E) atomicAdd(&cnt[warp * E + e], 1);
+  }
+  __syncthreads();
+  // per expert: total, padded total (thread e), then a serial scan over the experts by thread 0
+  for (int e = threadIdx.x; e < E; e += kPlanThreads) {
+    int tot = 0;
+    for (int w = 0; w < kPlanWarps; ++w) {
+      const int c = cnt[w * E + e];
+      cnt[w * E + e] = tot;  // entries of this expert in earlier warps
+      tot += c;
+    }
+    off[e + 1] = (tot + 127) & ~127;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    off[0] = 0;
+    for (int e = 0; e < E; ++e) off[e + 1] += off[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += kPlanThreads) k_off[e] = off[e];
+  for (int e = threadIdx.x; e < E; e += kPlanThreads)
+    for (int t = off[e] / 128; t < off[e + 1] / 128; ++t) tile_expert[t] = e;
+  // pass B: stable placement; only this warp touches its row of cursors
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const bool live = i < hi;
+    const int e = live ? static_cast<int>(ids[i]) : -1;
+    const bool ok = live && e >= 0 && e < E;
+    const unsigned int peers = __match_any_sync(0xffffffffu, ok ? e : -1 - lane);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const int leader = __ffs(peers) - 1;
+    int start = 0;
+    if (ok && lane == leader) {
+      start = cnt[warp * E + e];
+      cnt[warp * E + e] = start + __popc(peers);
+    }
+    start = __shfl_sync(0xffffffffu, start, leader);
+    if (ok) {
+      const int row = off[e] + start + rank;
+      slot_row[i] = row;
+      row_src[row] = i / top_k;
+    } else if (live) {
+      slot_row[i] = 0;
+    }
+    __syncwarp();
+  }
+}
+
 }  // namespace sb
 
 extern "C" {
@@ -317,6 +394,36 @@ int sb_moe_route_bwd(const float* logits, const float* w, const int* idx, const 
   const int blocks = (T + 7) / 8;
   sb::moe_route_bwd_kernel<<<blocks < 148 * 8 ? blocks : 148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       logits, w, idx, dw, dlogits, T, E, k, norm);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+// ids: [n] expert of every routed entry (int32 when ids_are_i64 == 0, else int64); E <= 1024; m_cap a multiple of 128
+// and at least the padded row total.
+int sb_moe_plan(const void* ids, int ids_are_i64, int n, int E, int top_k, int m_cap, int* k_off, int* tile_expert,
+                int* row_src, int* slot_row, void* stream) {
+  if (n < 0 || E <= 0 || E > 1024 || top_k <= 0 || m_cap <= 0 || (m_cap % 128) != 0) return SB_ERR_ARG;
+  const size_t smem = sizeof(int) * (static_cast<size_t>(sb::kPlanWarps) * E + E + 1);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (ids_are_i64) {
+    static bool attr = false;
+    if (!attr) {
+      if (cudaFuncSetAttribute(sb::moe_plan_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, 140 * 1024) !=
+          cudaSuccess)
+        return SB_ERR_CUDA;
+      attr = true;
+    }
+    sb::moe_plan_kernel<long long><<<1, sb::kPlanThreads, smem, st>>>(static_cast<const long long*>(ids), n, E, top_k, m_cap,
+                                                                      k_off, tile_expert, row_src, slot_row);
+  } else {
+    static bool attr = false;
+    if (!attr) {
+      if (cudaFuncSetAttribute(sb::moe_plan_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, 140 * 1024) != cudaSuccess)
+        return SB_ERR_CUDA;
+      attr = true;
+    }
+    sb::moe_plan_kernel<int><<<1, sb::kPlanThreads, smem, st>>>(static_cast<const int*>(ids), n, E, top_k, m_cap, k_off,
+                                                                tile_expert, row_src, slot_row);
+  }
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -12,7 +12,6 @@ Reference behaviour: Megatron-core's grouped expert GEMM, enabled with ``moe_gro
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass
 
 import torch
 
@@ -21,19 +20,32 @@ from . import _lib
 ROW_ALIGN = 128
 
 
-@dataclass
 class GroupPlan:
     """Layout of ``n`` routed rows over ``E`` experts in a padded ``[M_cap, *]`` buffer."""
 
-    order: torch.Tensor        # [n] routed entries sorted by expert (stable)
-    dst_row: torch.Tensor      # [n] padded-buffer row of sorted entry i
-    k_off: torch.Tensor        # [E + 1] int32 first padded row of each expert (multiples of 128)
-    tile_expert: torch.Tensor  # [M_cap / 128] int32 owner of each row block, -1 = unused
-    m_cap: int
-    num_experts: int
-    top_k: int = 1
-    row_src: torch.Tensor | None = None   # [M_cap] int32 token whose hidden row fills padded row r, -1 = padding
-    slot_row: torch.Tensor | None = None  # [n] int32 padded row of routed entry (token * top_k + slot)
+    def __init__(self, k_off, tile_expert, m_cap, num_experts, top_k, row_src, slot_row, ids, order=None, dst_row=None):
+        self.k_off = k_off              # [E + 1] int32 first padded row of each expert (multiples of 128)
+        self.tile_expert = tile_expert  # [M_cap / 128] int32 owner of each row block, -1 = unused
+        self.m_cap = m_cap
+        self.num_experts = num_experts
+        self.top_k = top_k
+        self.row_src = row_src          # [M_cap] int32 token whose hidden row fills padded row r, -1 = padding
+        self.slot_row = slot_row        # [n] int32 padded row of routed entry (token * top_k + slot)
+        self._ids, self._order, self._dst_row = ids, order, dst_row
+
+    @property
+    def order(self) -> torch.Tensor:
+        """[n] routed entries sorted by expert (stable); derived on demand when the plan came from the kernel."""
+        if self._order is None:
+            self._order = torch.argsort(self._ids.reshape(-1).long(), stable=True)
+        return self._order
+
+    @property
+    def dst_row(self) -> torch.Tensor:
+        """[n] padded-buffer row of sorted entry i."""
+        if self._dst_row is None:
+            self._dst_row = self.slot_row.long()[self.order]
+        return self._dst_row
 
 
 def padded_rows(n: int, num_experts: int) -> int:
@@ -43,9 +55,27 @@ def padded_rows(n: int, num_experts: int) -> int:
 
 
 def plan_groups(expert_ids: torch.Tensor, num_experts: int, top_k: int = 1) -> GroupPlan:
-    """``expert_ids``: [n] expert of every routed entry; entry ``i`` belongs to token ``i // top_k``."""
+    """``expert_ids``: [n] expert of every routed entry; entry ``i`` belongs to token ``i // top_k``.  On CUDA the whole
+    plan is one single-CTA kernel (histogram, padded offsets, stable placement); the CPU path spells it out."""
     n = expert_ids.numel()
     dev = expert_ids.device
+    m_cap = padded_rows(n, num_experts)
+    if expert_ids.is_cuda and num_experts <= 1024 and expert_ids.dtype in (torch.int32, torch.int64):
+        ids = expert_ids.reshape(-1).contiguous()
+        k_off = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+        te = torch.empty(m_cap // ROW_ALIGN, dtype=torch.int32, device=dev)
+        row_src = torch.empty(m_cap, dtype=torch.int32, device=dev)
+        slot_row = torch.empty(max(n, 1), dtype=torch.int32, device=dev)[:n]
+        lib = _lib.kernels()
+        if not getattr(lib.sb_moe_plan, "_configured", False):
+            vp, ci = ctypes.c_void_p, ctypes.c_int
+            lib.sb_moe_plan.restype = ci
+            lib.sb_moe_plan.argtypes = [vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp]
+            lib.sb_moe_plan._configured = True
+        code = lib.sb_moe_plan(ids.data_ptr(), int(ids.dtype == torch.int64), n, num_experts, top_k, m_cap, k_off.data_ptr(),
+                               te.data_ptr(), row_src.data_ptr(), slot_row.data_ptr(), _lib.stream_ptr())
+        _lib.check(code, "sb_moe_plan")
+        return GroupPlan(k_off, te, m_cap, num_experts, top_k, row_src, slot_row, ids)
     flat = expert_ids.reshape(-1).long()
     counts = torch.bincount(flat, minlength=num_experts)
     pad = (counts + (ROW_ALIGN - 1)) // ROW_ALIGN * ROW_ALIGN
@@ -55,7 +85,6 @@ def plan_groups(expert_ids: torch.Tensor, num_experts: int, top_k: int = 1) -> G
     se = flat[order]
     ustart = torch.cumsum(counts, 0) - counts
     dst_row = off[se] + (torch.arange(n, device=dev) - ustart[se])
-    m_cap = padded_rows(n, num_experts)
     starts = torch.arange(m_cap // ROW_ALIGN, device=dev) * ROW_ALIGN
     te = torch.searchsorted(ends, starts, right=True)
     te = torch.where(starts < ends[-1], te, torch.full_like(te, -1))
@@ -64,7 +93,7 @@ def plan_groups(expert_ids: torch.Tensor, num_experts: int, top_k: int = 1) -> G
     row_src[dst_row] = (order // top_k).to(torch.int32)
     slot_row = torch.empty(n, dtype=torch.int32, device=dev)
     slot_row[order] = dst_row.to(torch.int32)
-    return GroupPlan(order, dst_row, k_off, te.to(torch.int32), m_cap, num_experts, top_k, row_src, slot_row)
+    return GroupPlan(k_off, te.to(torch.int32), m_cap, num_experts, top_k, row_src, slot_row, flat, order, dst_row)
 
 
 def _fn():

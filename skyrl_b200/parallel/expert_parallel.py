@@ -96,9 +96,11 @@ class _ExpertParallelFFN(torch.autograd.Function):
             pad_rank = torch.full((Mc,), -1, dtype=torch.int32, device=h.device)
             pad_srow = torch.zeros((Mc,), dtype=torch.int32, device=h.device)
             pad_drow = torch.zeros((Mc,), dtype=torch.int32, device=h.device)
-            pad_rank[plan.dst_row] = src_rank
-            pad_srow[plan.dst_row] = src_row
-            pad_drow[plan.dst_row] = dst_row
+            rows_of = plan.slot_row.long()  # the tables are sorted by expert already: entry i sits in padded row slot_row[i]
+            pad_rank[rows_of] = src_rank
+            pad_srow[rows_of] = src_row
+            pad_drow[rows_of] = dst_row
+            ctx.rows_of = rows_of
             x_rows = torch.empty((Mc, H), device=h.device, dtype=h.dtype)
             gu = torch.empty((Mc, F2), device=h.device, dtype=h.dtype)
             flags = ep.flags(Mc // 128 + 2)
@@ -152,13 +154,13 @@ class _ExpertParallelFFN(torch.autograd.Function):
             from ..ops import grouped_gemm as gg
 
             plan = ctx.plan
-            dy_pad = torch.zeros((plan.m_cap, H), device=dout.device, dtype=dout.dtype).index_copy(0, plan.dst_row, dy_rows)
+            dy_pad = torch.zeros((plan.m_cap, H), device=dout.device, dtype=dout.dtype).index_copy(0, ctx.rows_of, dy_rows)
             dact = gg.grouped_nn(dy_pad, wd, plan)
             gg.grouped_tn(dy_pad, act, plan, dwd.view(wd.shape), accumulate=True)
             dgu = ew.swiglu_backward(gu, dact)
             dx_pad = gg.grouped_nn(dgu, wgu, plan)
             gg.grouped_tn(dgu, x_rows, plan, dwgu.view(wgu.shape), accumulate=True)
-            dx_rows = dx_pad[plan.dst_row]
+            dx_rows = dx_pad[ctx.rows_of]
             dh_slots = _fused_combine_rows(dx_rows, ep, src_rank, dst_row, T, k, H)
             dh = dh_slots.float().sum(1).to(dout.dtype)
             return (dh, dw, None, None if ctx.wgu_main is not None else dwgu.to(wgu.dtype),

@@ -197,3 +197,19 @@ def test_router_kernel_matches_torch(T, E, k, norm):
     w.backward(g)
     wr.backward(g_ref)
     assert torch.allclose(logits.grad, ref_l.grad, atol=2e-5, rtol=1e-3), float((logits.grad - ref_l.grad).abs().max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,E,k", [(7, 5, 1), (4096, 8, 2), (65536, 128, 8), (1000, 300, 4), (33, 1024, 1)])
+def test_plan_kernel_matches_reference_plan(n, E, k):
+    g = torch.Generator().manual_seed(n + E)
+    ids = torch.randint(0, E, (n,), generator=g)
+    ref = gg.plan_groups(ids, E, k)  # CPU path
+    for dt in (torch.int64, torch.int32):
+        got = gg.plan_groups(ids.to("cuda", dt), E, k)
+        assert got.m_cap == ref.m_cap
+        assert torch.equal(got.k_off.cpu(), ref.k_off)
+        assert torch.equal(got.tile_expert.cpu(), ref.tile_expert)
+        assert torch.equal(got.slot_row.cpu(), ref.slot_row)
+        assert torch.equal(got.row_src.cpu(), ref.row_src)
+        assert torch.equal(got.order.cpu(), ref.order) and torch.equal(got.dst_row.cpu(), ref.dst_row)
