@@ -535,7 +535,11 @@ class LLMEngine:
             return
         masked = self._mask_slots > 0
         n = self._bucket(hi)
-        use_graph = self.is_cuda and not self.cfg.enforce_eager and not masked and not self.model.args.num_experts
+        # mixture-of-experts layers build their routing plan on the device (no host reads), so they replay from a graph
+        # like dense layers -- except while the routing is being recorded or replayed (those tensors live on the host side)
+        from ..models import router_replay
+
+        use_graph = self.is_cuda and not self.cfg.enforce_eager and not masked and router_replay._get().mode is None
         if use_graph:
             g = self._graphs.get(n)
             if g is None:
