@@ -1,28 +1,81 @@
-"""Environment-variable knobs (names kept from the reference, skyrl/env_vars.py:13-106)."""
+"""Every environment variable the framework reads, in one place (reference: ``skyrl/env_vars.py:13-106``).
+
+Two families: ``SKYRL_*`` knobs carried over from the reference where the concept still exists in a
+one-process-per-GPU runtime, and ``SB_*`` switches of the native kernels (mostly A/B toggles for measurements).
+``describe()`` returns the table (name, current value, default, meaning); ``python -m skyrl_b200.env_vars`` prints it.
+Variables that configure an actor cluster in the reference (placement-group timeout, LD_LIBRARY_PATH / PYTHONPATH
+export to remote workers, data-parallel port offsets of the external engine) have no counterpart here: ranks are local
+processes started by ``skyrl_b200.launch`` and inherit the launching environment.
+"""
 
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass
+from typing import Callable, Dict, List
 
 
-def _int(name: str, default: int) -> int:
-    return int(os.environ.get(name, str(default)))
+def _flag(v: str) -> bool:
+    return str(v).strip().lower() in ("1", "true", "yes", "on")
 
 
-def _bool(name: str, default: bool = False) -> bool:
-    return os.environ.get(name, "1" if default else "0").lower() in ("1", "true", "yes")
+@dataclass(frozen=True)
+class EnvVar:
+    name: str
+    default: str
+    parse: Callable[[str], object]
+    doc: str
+
+    def get(self):
+        return self.parse(os.environ.get(self.name, self.default))
 
 
-SKYRL_RAY_PG_TIMEOUT_IN_S = _int("SKYRL_RAY_PG_TIMEOUT_IN_S", 180)  # kept for launch-time rendezvous timeouts
-SKYRL_WORKER_NCCL_TIMEOUT_IN_S = _int("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", 600)
-SKYRL_GENERATE_CONCURRENCY_PER_ENGINE = _int("SKYRL_GENERATE_CONCURRENCY_PER_ENGINE", 512)
-SKYRL_HTTP_CONNECTION_LIMIT = _int("SKYRL_HTTP_CONNECTION_LIMIT", 4096)
-SKYRL_DUMP_INFRA_LOG_TO_STDOUT = _bool("SKYRL_DUMP_INFRA_LOG_TO_STDOUT")
-SKYRL_LD_LIBRARY_PATH_EXPORT = _bool("SKYRL_LD_LIBRARY_PATH_EXPORT")
-SKYRL_PYTHONPATH_EXPORT = _bool("SKYRL_PYTHONPATH_EXPORT")
-SKYRL_WAIT_UNTIL_INFERENCE_SERVER_HEALTHY_TIMEOUT_S = _int("SKYRL_WAIT_UNTIL_INFERENCE_SERVER_HEALTHY_TIMEOUT_S", 600)
-SKYRL_INCLUDE_PYTHONPATH_IN_RUNTIME_ENV = _bool("SKYRL_INCLUDE_PYTHONPATH_IN_RUNTIME_ENV")
-# knobs of this implementation
-SKYRL_B200_NO_AUTOBUILD = _bool("SKYRL_B200_NO_AUTOBUILD")
-SKYRL_B200_PEER_WAIT_S = float(os.environ.get("SKYRL_B200_PEER_WAIT_S", "10"))
-SKYRL_B200_DISABLE_PEER = _bool("SKYRL_B200_DISABLE_PEER")
+_VARS: List[EnvVar] = [
+    # ---- carried over from the reference
+    EnvVar("SKYRL_WORKER_NCCL_TIMEOUT_IN_S", "600", int,
+           "timeout of the NCCL / gloo process groups created by the workers (seconds)"),
+    EnvVar("SKYRL_WAIT_UNTIL_INFERENCE_SERVER_HEALTHY_TIMEOUT_S", "600", int,
+           "how long clients wait for a generation server's /health before giving up (seconds)"),
+    EnvVar("SKYRL_HTTP_CONNECTION_LIMIT", "50000", int, "connection-pool limit of the HTTP inference client"),
+    EnvVar("SKYRL_GENERATE_CONCURRENCY_PER_ENGINE", "512", int,
+           "trajectories a generator keeps in flight per generation engine"),
+    EnvVar("SKYRL_DUMP_INFRA_LOG_TO_STDOUT", "False", _flag, "print infrastructure logs of all ranks instead of rank 0 only"),
+    EnvVar("SKYRL_LOG_LEVEL", "INFO", str, "log level of the ``skyrl_b200`` logger"),
+    # ---- this runtime
+    EnvVar("SKYRL_B200_NO_AUTOBUILD", "0", _flag, "do not compile the native libraries on first import (CI images ship them)"),
+    EnvVar("SKYRL_B200_NUMA_PIN", "1", _flag, "bind each rank's host threads to the CPUs of its GPU's NUMA node"),
+    EnvVar("SKYRL_B200_PEER_WAIT_S", "2.0", float, "upper bound of every wait on a peer flag inside the NVLink kernels (seconds)"),
+    # ---- kernel switches (A/B measurements; defaults are the fast paths)
+    EnvVar("SB_PDL", "1", _flag, "programmatic dependent launch between the kernels of a decode step / training layer"),
+    EnvVar("SB_GEMM_PAIR", "1", _flag, "CTA-pair (cta_group::2) GEMM for large problems"),
+    EnvVar("SB_FUSED_MLP", "1", _flag, "SwiGLU inside the gate/up and down-gradient GEMM epilogues (training)"),
+    EnvVar("SB_DECODE_FUSED_MLP", "1", _flag, "SwiGLU inside the gate/up GEMM epilogue (decode)"),
+    EnvVar("SB_DECODE_ATTN_PERSIST", "1", _flag, "persistent paged decode attention (one CTA per SM walking a work list)"),
+    EnvVar("SB_DECODE_ATTN_SPLITS", "", str, "force the context split count of decode attention (empty = cost model)"),
+    EnvVar("SB_BF16_TFLOPS", "1376.9", float, "bf16 GEMM peak used as roofline denominator by the benchmarks (TFLOP/s)"),
+    EnvVar("SB_HBM_GBS", "6543.4", float, "HBM copy bandwidth used as roofline denominator by the benchmarks (GB/s)"),
+]
+
+_BY_NAME: Dict[str, EnvVar] = {v.name: v for v in _VARS}
+
+
+def get(name: str):
+    """Parsed value of a registered variable (its default when unset)."""
+    return _BY_NAME[name].get()
+
+
+def describe() -> List[Dict[str, str]]:
+    return [{"name": v.name, "value": os.environ.get(v.name, v.default), "default": v.default, "doc": v.doc} for v in _VARS]
+
+
+# module-level constants for the names the reference exposes the same way
+SKYRL_WORKER_NCCL_TIMEOUT_IN_S = get("SKYRL_WORKER_NCCL_TIMEOUT_IN_S")
+SKYRL_WAIT_UNTIL_INFERENCE_SERVER_HEALTHY_TIMEOUT_S = get("SKYRL_WAIT_UNTIL_INFERENCE_SERVER_HEALTHY_TIMEOUT_S")
+SKYRL_HTTP_CONNECTION_LIMIT = get("SKYRL_HTTP_CONNECTION_LIMIT")
+SKYRL_GENERATE_CONCURRENCY_PER_ENGINE = get("SKYRL_GENERATE_CONCURRENCY_PER_ENGINE")
+SKYRL_DUMP_INFRA_LOG_TO_STDOUT = get("SKYRL_DUMP_INFRA_LOG_TO_STDOUT")
+
+
+if __name__ == "__main__":
+    for row in describe():
+        print(f"{row['name']:<52} {row['value']!s:<10} (default {row['default']!s})  {row['doc']}")

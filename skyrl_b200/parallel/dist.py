@@ -42,6 +42,13 @@ def init_distributed(backend: Optional[str] = None, timeout_s: Optional[int] = N
     dev = torch.device(f"cuda:{local}") if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(dev)
+        if os.environ.get("SKYRL_B200_NUMA_PIN", "1") not in ("0", "false", "False"):
+            try:  # host threads (input staging, scheduler) next to the GPU; silently skipped without sysfs topology
+                from ..utils.numa import pin_to_gpu_numa_node
+
+                pin_to_gpu_numa_node(local)
+            except Exception:
+                pass
     if world > 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")

@@ -108,3 +108,43 @@ def test_adapter_store_swaps_tenants():
     assert torch.equal(w.model.flat_params, pb)
     with pytest.raises(RuntimeError):
         store.create("c")
+
+
+def test_numa_pinning_reads_sysfs_topology(tmp_path):
+    from skyrl_b200.utils import numa
+
+    assert numa.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    root = tmp_path / "sys"
+    dev = root / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = root / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("16-19,48\n")
+    assert numa.gpu_numa_node("0000:1B:00.0", str(root)) == 1
+    applied = {}
+    cpus = numa.pin_to_gpu_numa_node(0, str(root), bus_id="0000:1b:00.0", setaffinity=lambda pid, s: applied.update(pid=pid, cpus=s))
+    assert cpus == [16, 17, 18, 19, 48] and applied == {"pid": 0, "cpus": {16, 17, 18, 19, 48}}
+    # unknown device or node -1: nothing is changed
+    (dev / "numa_node").write_text("-1\n")
+    assert numa.pin_to_gpu_numa_node(0, str(root), bus_id="0000:1b:00.0", setaffinity=lambda *a: applied.update(bad=1)) == []
+    assert numa.pin_to_gpu_numa_node(0, str(root), bus_id="0000:ff:00.0", setaffinity=lambda *a: applied.update(bad=1)) == []
+    assert "bad" not in applied
+
+
+def test_env_var_registry_lists_every_variable_the_code_reads():
+    import os
+    import re
+
+    from skyrl_b200 import env_vars
+
+    names = {r["name"] for r in env_vars.describe()}
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    found = set()
+    for dirpath, _, files in os.walk(os.path.join(root, "skyrl_b200")):
+        for fn in files:
+            if fn.endswith((".py", ".cu", ".cpp", ".h", ".cuh")) and fn != "env_vars.py":
+                text = open(os.path.join(dirpath, fn), errors="ignore").read()
+                found |= set(re.findall(r'(?:environ\.get|getenv)\(\s*"((?:SB|SKYRL)_[A-Z0-9_]+)"', text))
+    assert found <= names, sorted(found - names)
+    assert env_vars.get("SB_PDL") is True and isinstance(env_vars.SKYRL_WORKER_NCCL_TIMEOUT_IN_S, int)
