@@ -55,6 +55,7 @@ def main() -> None:
     ap.add_argument("--nq", type=int, default=12)
     ap.add_argument("--nkv", type=int, default=2)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--block-size", type=int, default=32, help="decode_attn: tokens per KV-cache page")
     ap.add_argument("--graph", action="store_true", help="decode_attn: time a CUDA-graph replay of several calls")
     ap.add_argument("--hbm-gbs", type=float, default=6543.4)
     ap.add_argument("--peak-tflops", type=float, default=1668.8)
@@ -76,7 +77,7 @@ def main() -> None:
         out.update(m=a.m, n=a.n, k=a.k, layout=a.layout, ms=ms, tflops=fl / ms / 1e9,
                    fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
     elif a.which == "decode_attn":
-        bs, D = 32, 128
+        bs, D = a.block_size, 128
         mb = (a.ctx + bs - 1) // bs
         nb = a.seqs * mb
         kc, vc = torch.randn(nb, bs, a.nkv, D, **bf), torch.randn(nb, bs, a.nkv, D, **bf)

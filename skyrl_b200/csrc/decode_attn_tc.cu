@@ -295,7 +295,10 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
                               const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ block_tables,
                               const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ ws,
                               int n_seqs, int nq, int nkv, int block_size, int max_blocks, int splits, long long q_stride,
-                              float scale_log2, int* status) {
+                              float scale_log2, int* status, int tail_start, int tail_splits) {
+  // Work list: the first tail_start (sequence, kv head) pairs are cut into `splits` parts each, the remaining pairs
+  // into `tail_splits` parts.  With more pairs than SMs the host leaves whole rounds unsplit (results go straight to
+  // `out`) and cuts only the pairs of the last, partly filled round, so that this round costs a fraction of a pair.
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem + kDtStages * kDtStageBytes;
@@ -318,7 +321,8 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
   __shared__ float s_lsum[4][16];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_items = n_seqs * nkv * splits;
+  const int tail_items0 = tail_start * splits;
+  const int n_items = tail_items0 + (n_seqs * nkv - tail_start) * tail_splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kDtStages; ++i) {
@@ -353,12 +357,21 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
 
   // item -> (sequence, kv head, split) and its token range; identical arithmetic in every role
   auto item_range = [&](int item, int& seq, int& g, int& split, int& t0, int& t1) -> int {
-    split = item % splits;
-    const int sg = item / splits;
+    int sg, nsp;
+    if (item < tail_items0) {
+      nsp = splits;
+      sg = item / splits;
+      split = item - sg * splits;
+    } else {
+      nsp = tail_splits;
+      const int jj = item - tail_items0;
+      sg = tail_start + jj / tail_splits;
+      split = jj - (sg - tail_start) * tail_splits;
+    }
     g = sg % nkv;
     seq = sg / nkv;
     const int ctx = __ldg(ctx_lens + seq);
-    const int per_split = (((ctx + splits - 1) / splits) + 127) & ~127;
+    const int per_split = (((ctx + nsp - 1) / nsp) + 127) & ~127;
     t0 = split * per_split;
     t1 = min(ctx, t0 + per_split);
     return (t1 > t0) ? (t1 - t0 + 127) / 128 : 0;
@@ -371,6 +384,13 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
     return n_items;
   };
   const int pages_per_tile = 128 / block_size;
+  // where an item's result goes: nullptr = the item covers its whole context, write `out` directly
+  auto part_slot = [&](int item, int seq, int g, int h, int split) -> float* {
+    const int sg = seq * nkv + g;
+    if (item < tail_items0)
+      return splits == 1 ? nullptr : ws + (static_cast<size_t>(sg * G + h) * splits + split) * 130;
+    return tail_splits == 1 ? nullptr : ws + (static_cast<size_t>((sg - tail_start) * G + h) * tail_splits + split) * 130;
+  };
 
   if (warp == 0 || warp == 6) {
     // warp 0 streams the K tiles, warp 6 the V tiles (one thread each)
@@ -529,10 +549,10 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
       const int d = tid;
       for (int h = 0; h < G; ++h) {
         const size_t head = static_cast<size_t>(seq) * nq + g * G + h;
-        if (splits == 1) {
+        float* w = part_slot(it, seq, g, h, split);
+        if (w == nullptr) {
           out[head * 128 + d] = __float2bfloat16(0.f);
         } else {
-          float* w = ws + (head * splits + split) * 130;
           w[d] = 0.f;
           if (d == 0) {
             w[128] = -INFINITY;
@@ -625,10 +645,10 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
         for (int h = 0; h < G; ++h) {
           const float l = s_lsum[0][h] + s_lsum[1][h] + s_lsum[2][h] + s_lsum[3][h];
           const size_t head = static_cast<size_t>(seq) * nq + g * G + h;
-          if (splits == 1) {
+          float* w = part_slot(item, seq, g, h, split);
+          if (w == nullptr) {
             out[head * 128 + d] = __float2bfloat16(l > 0.f ? O[h] / l : 0.f);
           } else {
-            float* w = ws + (head * splits + split) * 130;
             w[d] = O[h];
             if (d == 0) {
               w[128] = m[h];
@@ -695,7 +715,25 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
     const char* e = getenv("SB_DECODE_ATTN_PERSIST");
     persist = (e && e[0] == '0') ? 0 : 1;
   }
-  const int n_items = n * nkv * splits;
+  // Tail mode (persistent kernel, no uniform split, more pairs than SMs): the pairs of the last, partly filled round
+  // are cut into tail_splits parts (needs the workspace for their partial results).
+  // Measured on B200 the kernel is bound by HBM efficiency rather than by SM time (a half-empty last round streams as
+  // fast as a full one), so the extra parts only add the combine pass: off unless SB_DECODE_ATTN_TAIL=1.
+  int tail_start = n * nkv, tail_splits = 1;
+  const char* tail_env = getenv("SB_DECODE_ATTN_TAIL");
+  if (persist && splits == 1 && workspace != nullptr && tail_env && tail_env[0] == '1') {
+    const int sms = sb::sm_count(), pairs = n * nkv;
+    const int rem = pairs % sms;
+    if (pairs > sms && rem != 0 && 2 * rem <= sms + sms / 4) {
+      int s2 = sms / rem;
+      if (s2 > 4) s2 = 4;
+      if (s2 >= 2) {
+        tail_start = pairs - rem;
+        tail_splits = s2;
+      }
+    }
+  }
+  const int n_items = tail_start * splits + (n * nkv - tail_start) * tail_splits;
   const int pgrid = n_items < sb::sm_count() ? n_items : sb::sm_count();
 #define SB_DT_CASE(GV)                                                                                              \
   case GV: {                                                                                                        \
@@ -718,7 +756,7 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
                      st,                                                                                            \
                      *tk, *tv, reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                 \
                      reinterpret_cast<__nv_bfloat16*>(out), workspace, n, nq, nkv, block_size, max_blocks, splits,  \
-                     q_stride, sl2, sb::device_status_ptr());                                                       \
+                     q_stride, sl2, sb::device_status_ptr(), tail_start, tail_splits);                              \
     else                                                                                                            \
       sb::launch_pdl(sb::attn_decode_tc_kernel<GV>, grid, dim3(sb::kDtThreads), sb::kDtSmem, st, *tk, *tv,          \
                      reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                           \
@@ -740,9 +778,14 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
       return SB_ERR_ARG;
   }
 #undef SB_DT_CASE
-  if (splits > 1)
+  if (splits > 1) {
     sb::launch_pdl(sb::attn_decode_tc_combine_kernel, dim3(n * nq), dim3(128), 0, st, workspace,
                    reinterpret_cast<__nv_bfloat16*>(out), splits);
+  } else if (tail_splits > 1) {
+    // heads are numbered pair * G + h: the tail pairs' heads are the last (pairs - tail_start) * G rows of `out`
+    sb::launch_pdl(sb::attn_decode_tc_combine_kernel, dim3((n * nkv - tail_start) * G), dim3(128), 0, st, workspace,
+                   reinterpret_cast<__nv_bfloat16*>(out) + static_cast<size_t>(tail_start) * G * 128, tail_splits);
+  }
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

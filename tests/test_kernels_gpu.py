@@ -113,6 +113,31 @@ def test_decode_paged(nq, nkv, bs):
             assert rel(out.view(n, nq, D), ref) < 1e-2, (max_ctx, simt)
 
 
+@pytest.mark.parametrize("n,nkv,nq", [(100, 2, 12), (160, 2, 4), (75, 4, 8)])
+def test_decode_paged_many_sequences_tail_split(n, nkv, nq, monkeypatch):
+    """More (sequence, kv head) pairs than SMs with a partly filled last round: the persistent kernel cuts only the
+    pairs of that round (partial results + combine) and writes the others directly; inactive slots included."""
+    monkeypatch.setenv("SB_DECODE_ATTN_TAIL", "1")
+    torch.manual_seed(n)
+    D, bs = 128, 32
+    ctx = torch.randint(1, 700, (n,), dtype=torch.int32)
+    ctx[3] = 0  # an inactive slot
+    ctx[-1] = 1
+    max_blocks = (int(ctx.max()) + bs - 1) // bs
+    nblocks = n * max_blocks + 1
+    kc = torch.randn(nblocks, bs, nkv, D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(nblocks, bs, nkv, D, device="cuda").to(torch.bfloat16)
+    bt = torch.randperm(nblocks)[: n * max_blocks].view(n, max_blocks).to(torch.int32).cuda()
+    qkv = torch.randn(n, (nq + 2 * nkv) * D, device="cuda").to(torch.bfloat16)
+    ref = attention.attn_decode_paged_ref(qkv[:, : nq * D].view(n, nq, D), kc, vc, bt, ctx, 1 / math.sqrt(D))
+    out = attention.attn_decode_paged(qkv, kc, vc, bt, ctx.cuda(), nq, nkv, D, max_ctx=int(ctx.max()))
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    live = ctx > 0
+    assert rel(out.view(n, nq, D)[live.cuda()], ref[live]) < 1e-2
+    assert out.view(n, nq, D)[3].abs().max() == 0
+
+
 def test_kv_cache_write():
     nq, nkv, D, T = 4, 2, 128, 37
     qkv = torch.randn(T, (nq + 2 * nkv) * D, device="cuda").to(torch.bfloat16)
