@@ -39,7 +39,7 @@ def timeit(fn, iters, warmup=3):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe"])
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "hbm"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -148,6 +148,17 @@ def main() -> None:
         fl = 2.0 * M * N * K
         out.update(m=M, n=N, k=K, emulated_ranks=R, ms=ms, tflops=fl / ms / 1e9,
                    fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
+    elif a.which == "hbm":
+        # what the memory system delivers to library kernels: copy (read + write bytes) and read-only reductions
+        nbytes = 4 << 30
+        x = torch.empty(nbytes // 4, device="cuda", dtype=torch.float32).normal_()
+        y = torch.empty_like(x)
+        ms_copy = timeit(lambda: y.copy_(x), a.iters)
+        ms_sum = timeit(lambda: x.sum(), a.iters)
+        xb = x.view(torch.bfloat16)
+        ms_max = timeit(lambda: xb.amax(), a.iters)
+        out.update(bytes=nbytes, copy_gbs=2 * nbytes / ms_copy / 1e6, read_sum_fp32_gbs=nbytes / ms_sum / 1e6,
+                   read_amax_bf16_gbs=nbytes / ms_max / 1e6)
     elif a.which == "moe":
         # one mixture-of-experts FFN layer (router, grouped gate/up GEMM, SwiGLU, grouped down GEMM, weighted combine)
         from skyrl_b200.models.moe import moe_ffn

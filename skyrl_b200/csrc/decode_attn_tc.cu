@@ -18,6 +18,7 @@
 namespace sb {
 
 constexpr int kDtThreads = 192;
+constexpr int kDtL2Ahead = 6;           // tiles the L2 prefetch cursor runs ahead of the shared-memory loads
 constexpr int kDtThreadsPersist = 224;  // + one warp streaming the V tiles
 constexpr int kDtStages = 3;
 constexpr int kDtTile = 128 * 128 * 2;                 // one K or V tile: 32 KB (two 16 KB halves)
@@ -295,7 +296,8 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
                               const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ block_tables,
                               const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ ws,
                               int n_seqs, int nq, int nkv, int block_size, int max_blocks, int splits, long long q_stride,
-                              float scale_log2, int* status, int tail_start, int tail_splits) {
+                              float scale_log2, int* status, int tail_start, int tail_splits,
+                              const void* __restrict__ k_cache, const void* __restrict__ v_cache) {
   // Work list: the first tail_start (sequence, kv head) pairs are cut into `splits` parts each, the remaining pairs
   // into `tail_splits` parts.  With more pairs than SMs the host leaves whole rounds unsplit (results go straight to
   // `out`) and cuts only the pairs of the last, partly filled round, so that this round costs a fraction of a pair.
@@ -393,35 +395,84 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
   };
 
   if (warp == 0 || warp == 6) {
-    // warp 0 streams the K tiles, warp 6 the V tiles (one thread each)
-    if (lane == 0) {
+    // Warp 0 streams the K tiles, warp 6 the V tiles: lane 0 waits for a free stage and issues the TMA copies.
+    // Optional (SB_DECODE_ATTN_L2_AHEAD=1, off by default): a second cursor runs kDtL2Ahead tiles ahead and the whole
+    // warp touches those cache lines with prefetch.global.L2.  Measured on B200 this, like a TMA prefetch of the same
+    // boxes, slows the stream down (61 -> 85 us at 256 x 1000): the kernel is kept as the plain TMA stream.
+    {
       const bool is_v = warp == 6;
       uint64_t* fullb = is_v ? vfull : kfull;
       uint64_t* emptyb = is_v ? vempty : kempty;
       const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
-      int jt = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        int seq, g, split, t0, t1;
-        const int n_tiles = item_range(item, seq, g, split, t0, t1);
-        const int* bt = block_tables + static_cast<size_t>(seq) * max_blocks;
-        for (int j = 0; j < n_tiles; ++j, ++jt) {
-          const int s = jt % kDtStages;
-          if (!mbar_wait(&emptyb[s], ((jt / kDtStages) & 1) ^ 1, status, is_v ? 0x832 : 0x831)) {
-            ok = false;
-            break;
+      const uint8_t* cache = reinterpret_cast<const uint8_t*>(is_v ? v_cache : k_cache);
+      struct Cursor {
+        int item, j, n, g, t0;
+        const int* bt;
+      };
+      auto seek = [&](Cursor& c) {  // first item at or after c.item (in this CTA's list) that has tiles
+        for (; c.item < n_items; c.item += gridDim.x) {
+          int seq, g, split, t0, t1;
+          c.n = item_range(c.item, seq, g, split, t0, t1);
+          if (c.n > 0) {
+            c.g = g;
+            c.t0 = t0;
+            c.bt = block_tables + static_cast<size_t>(seq) * max_blocks;
+            c.j = 0;
+            return;
           }
-          uint8_t* dst = smem + s * kDtStageBytes + (is_v ? kDtTile : 0);
-          mbar_arrive_expect_tx(&fullb[s], kDtTile);
-          const int tok0 = t0 + j * 128;
-          for (int p = 0; p < pages_per_tile; ++p) {
-            int pi = (tok0 + p * block_size) / block_size;
-            pi = pi < max_blocks ? pi : max_blocks - 1;
-            const int slot0 = __ldg(bt + pi) * block_size;
-            const int off = p * block_size * 128;
-            tma_load_3d(dst + off, tm, &fullb[s], 0, g, slot0);
-            tma_load_3d(dst + 16384 + off, tm, &fullb[s], 64, g, slot0);
+        }
+      };
+      auto step = [&](Cursor& c) {
+        if (++c.j >= c.n) {
+          c.item += gridDim.x;
+          seek(c);
+        }
+      };
+      auto page_slot = [&](const Cursor& c, int p) -> int {
+        int pi = (c.t0 + c.j * 128 + p * block_size) / block_size;
+        pi = pi < max_blocks ? pi : max_blocks - 1;
+        return __ldg(c.bt + pi) * block_size;
+      };
+      // a token's row of one kv head is 256 bytes = two 128-byte lines; lane l touches lines l, l + 32, ...
+      auto prefetch_tile = [&](const Cursor& c) {
+        if (cache == nullptr) return;
+        for (int p = 0; p < pages_per_tile; ++p) {
+          const size_t slot0 = static_cast<size_t>(page_slot(c, p));
+          for (int ln = lane; ln < block_size * 2; ln += 32) {
+            const uint8_t* a = cache + ((slot0 + (ln >> 1)) * nkv + c.g) * 256 + (ln & 1) * 128;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
           }
+        }
+      };
+      Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0, 0, nullptr};
+      seek(cur);
+      Cursor ahead = cur;
+      for (int d = 0; d < kDtL2Ahead && ahead.item < n_items; ++d) {
+        prefetch_tile(ahead);
+        step(ahead);
+      }
+      for (int jt = 0; cur.item < n_items; ++jt) {
+        const int s = jt % kDtStages;
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(&emptyb[s], ((jt / kDtStages) & 1) ^ 1, status, is_v ? 0x832 : 0x831) ? 1 : 0;
+          if (ok) {
+            uint8_t* dst = smem + s * kDtStageBytes + (is_v ? kDtTile : 0);
+            mbar_arrive_expect_tx(&fullb[s], kDtTile);
+            for (int p = 0; p < pages_per_tile; ++p) {
+              const int slot0 = page_slot(cur, p);
+              const int off = p * block_size * 128;
+              tma_load_3d(dst + off, tm, &fullb[s], 0, cur.g, slot0);
+              tma_load_3d(dst + 16384 + off, tm, &fullb[s], 64, cur.g, slot0);
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        step(cur);
+        if (ahead.item < n_items) {
+          prefetch_tile(ahead);
+          step(ahead);
         }
       }
     }
@@ -733,6 +784,8 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
       }
     }
   }
+  const char* l2_env = getenv("SB_DECODE_ATTN_L2_AHEAD");
+  const bool l2_ahead = l2_env && l2_env[0] == '1';  // measured slower on B200 (see the kernel comment): opt-in
   const int n_items = tail_start * splits + (n * nkv - tail_start) * tail_splits;
   const int pgrid = n_items < sb::sm_count() ? n_items : sb::sm_count();
 #define SB_DT_CASE(GV)                                                                                              \
@@ -756,7 +809,8 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
                      st,                                                                                            \
                      *tk, *tv, reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                 \
                      reinterpret_cast<__nv_bfloat16*>(out), workspace, n, nq, nkv, block_size, max_blocks, splits,  \
-                     q_stride, sl2, sb::device_status_ptr(), tail_start, tail_splits);                              \
+                     q_stride, sl2, sb::device_status_ptr(), tail_start, tail_splits, l2_ahead ? k_cache : nullptr, \
+                     l2_ahead ? v_cache : nullptr);                                                                 \
     else                                                                                                            \
       sb::launch_pdl(sb::attn_decode_tc_kernel<GV>, grid, dim3(sb::kDtThreads), sb::kDtSmem, st, *tk, *tv,          \
                      reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                           \
