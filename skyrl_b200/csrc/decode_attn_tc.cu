@@ -835,7 +835,7 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
   if (splits > 1) {
     sb::launch_pdl(sb::attn_decode_tc_combine_kernel, dim3(n * nq), dim3(128), 0, st, workspace,
                    reinterpret_cast<__nv_bfloat16*>(out), splits);
-  } else if (tail_splits > 1) {
+  } else if (tail_splits > 1 && n * nkv > tail_start) {
     // heads are numbered pair * G + h: the tail pairs' heads are the last (pairs - tail_start) * G rows of `out`
     sb::launch_pdl(sb::attn_decode_tc_combine_kernel, dim3((n * nkv - tail_start) * G), dim3(128), 0, st, workspace,
                    reinterpret_cast<__nv_bfloat16*>(out) + static_cast<size_t>(tail_start) * G * 128, tail_splits);
