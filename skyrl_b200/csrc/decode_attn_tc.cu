@@ -18,7 +18,6 @@
 namespace sb {
 
 constexpr int kDtThreads = 192;
-constexpr int kDtL2Ahead = 6;           // tiles the L2 prefetch cursor runs ahead of the shared-memory loads
 constexpr int kDtThreadsPersist = 224;  // + one warp streaming the V tiles
 constexpr int kDtStages = 3;
 constexpr int kDtTile = 128 * 128 * 2;                 // one K or V tile: 32 KB (two 16 KB halves)
@@ -296,11 +295,7 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
                               const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ block_tables,
                               const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ ws,
                               int n_seqs, int nq, int nkv, int block_size, int max_blocks, int splits, long long q_stride,
-                              float scale_log2, int* status, int tail_start, int tail_splits,
-                              const void* __restrict__ k_cache, const void* __restrict__ v_cache) {
-  // Work list: the first tail_start (sequence, kv head) pairs are cut into `splits` parts each, the remaining pairs
-  // into `tail_splits` parts.  With more pairs than SMs the host leaves whole rounds unsplit (results go straight to
-  // `out`) and cuts only the pairs of the last, partly filled round, so that this round costs a fraction of a pair.
+                              float scale_log2, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem + kDtStages * kDtStageBytes;
@@ -323,8 +318,7 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
   __shared__ float s_lsum[4][16];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tail_items0 = tail_start * splits;
-  const int n_items = tail_items0 + (n_seqs * nkv - tail_start) * tail_splits;
+  const int n_items = n_seqs * nkv * splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kDtStages; ++i) {
@@ -359,21 +353,12 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
 
   // item -> (sequence, kv head, split) and its token range; identical arithmetic in every role
   auto item_range = [&](int item, int& seq, int& g, int& split, int& t0, int& t1) -> int {
-    int sg, nsp;
-    if (item < tail_items0) {
-      nsp = splits;
-      sg = item / splits;
-      split = item - sg * splits;
-    } else {
-      nsp = tail_splits;
-      const int jj = item - tail_items0;
-      sg = tail_start + jj / tail_splits;
-      split = jj - (sg - tail_start) * tail_splits;
-    }
+    split = item % splits;
+    const int sg = item / splits;
     g = sg % nkv;
     seq = sg / nkv;
     const int ctx = __ldg(ctx_lens + seq);
-    const int per_split = (((ctx + nsp - 1) / nsp) + 127) & ~127;
+    const int per_split = (((ctx + splits - 1) / splits) + 127) & ~127;
     t0 = split * per_split;
     t1 = min(ctx, t0 + per_split);
     return (t1 > t0) ? (t1 - t0 + 127) / 128 : 0;
@@ -386,93 +371,37 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
     return n_items;
   };
   const int pages_per_tile = 128 / block_size;
-  // where an item's result goes: nullptr = the item covers its whole context, write `out` directly
-  auto part_slot = [&](int item, int seq, int g, int h, int split) -> float* {
-    const int sg = seq * nkv + g;
-    if (item < tail_items0)
-      return splits == 1 ? nullptr : ws + (static_cast<size_t>(sg * G + h) * splits + split) * 130;
-    return tail_splits == 1 ? nullptr : ws + (static_cast<size_t>((sg - tail_start) * G + h) * tail_splits + split) * 130;
-  };
 
   if (warp == 0 || warp == 6) {
-    // Warp 0 streams the K tiles, warp 6 the V tiles: lane 0 waits for a free stage and issues the TMA copies.
-    // Optional (SB_DECODE_ATTN_L2_AHEAD=1, off by default): a second cursor runs kDtL2Ahead tiles ahead and the whole
-    // warp touches those cache lines with prefetch.global.L2.  Measured on B200 this, like a TMA prefetch of the same
-    // boxes, slows the stream down (61 -> 85 us at 256 x 1000): the kernel is kept as the plain TMA stream.
-    {
+    // warp 0 streams the K tiles, warp 6 the V tiles (one thread each)
+    if (lane == 0) {
       const bool is_v = warp == 6;
       uint64_t* fullb = is_v ? vfull : kfull;
       uint64_t* emptyb = is_v ? vempty : kempty;
       const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
-      const uint8_t* cache = reinterpret_cast<const uint8_t*>(is_v ? v_cache : k_cache);
-      struct Cursor {
-        int item, j, n, g, t0;
-        const int* bt;
-      };
-      auto seek = [&](Cursor& c) {  // first item at or after c.item (in this CTA's list) that has tiles
-        for (; c.item < n_items; c.item += gridDim.x) {
-          int seq, g, split, t0, t1;
-          c.n = item_range(c.item, seq, g, split, t0, t1);
-          if (c.n > 0) {
-            c.g = g;
-            c.t0 = t0;
-            c.bt = block_tables + static_cast<size_t>(seq) * max_blocks;
-            c.j = 0;
-            return;
+      int jt = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        int seq, g, split, t0, t1;
+        const int n_tiles = item_range(item, seq, g, split, t0, t1);
+        const int* bt = block_tables + static_cast<size_t>(seq) * max_blocks;
+        for (int j = 0; j < n_tiles; ++j, ++jt) {
+          const int s = jt % kDtStages;
+          if (!mbar_wait(&emptyb[s], ((jt / kDtStages) & 1) ^ 1, status, is_v ? 0x832 : 0x831)) {
+            ok = false;
+            break;
           }
-        }
-      };
-      auto step = [&](Cursor& c) {
-        if (++c.j >= c.n) {
-          c.item += gridDim.x;
-          seek(c);
-        }
-      };
-      auto page_slot = [&](const Cursor& c, int p) -> int {
-        int pi = (c.t0 + c.j * 128 + p * block_size) / block_size;
-        pi = pi < max_blocks ? pi : max_blocks - 1;
-        return __ldg(c.bt + pi) * block_size;
-      };
-      // a token's row of one kv head is 256 bytes = two 128-byte lines; lane l touches lines l, l + 32, ...
-      auto prefetch_tile = [&](const Cursor& c) {
-        if (cache == nullptr) return;
-        for (int p = 0; p < pages_per_tile; ++p) {
-          const size_t slot0 = static_cast<size_t>(page_slot(c, p));
-          for (int ln = lane; ln < block_size * 2; ln += 32) {
-            const uint8_t* a = cache + ((slot0 + (ln >> 1)) * nkv + c.g) * 256 + (ln & 1) * 128;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+          uint8_t* dst = smem + s * kDtStageBytes + (is_v ? kDtTile : 0);
+          mbar_arrive_expect_tx(&fullb[s], kDtTile);
+          const int tok0 = t0 + j * 128;
+          for (int p = 0; p < pages_per_tile; ++p) {
+            int pi = (tok0 + p * block_size) / block_size;
+            pi = pi < max_blocks ? pi : max_blocks - 1;
+            const int slot0 = __ldg(bt + pi) * block_size;
+            const int off = p * block_size * 128;
+            tma_load_3d(dst + off, tm, &fullb[s], 0, g, slot0);
+            tma_load_3d(dst + 16384 + off, tm, &fullb[s], 64, g, slot0);
           }
-        }
-      };
-      Cursor cur{static_cast<int>(blockIdx.x), 0, 0, 0, 0, nullptr};
-      seek(cur);
-      Cursor ahead = cur;
-      for (int d = 0; d < kDtL2Ahead && ahead.item < n_items; ++d) {
-        prefetch_tile(ahead);
-        step(ahead);
-      }
-      for (int jt = 0; cur.item < n_items; ++jt) {
-        const int s = jt % kDtStages;
-        int ok = 1;
-        if (lane == 0) {
-          ok = mbar_wait(&emptyb[s], ((jt / kDtStages) & 1) ^ 1, status, is_v ? 0x832 : 0x831) ? 1 : 0;
-          if (ok) {
-            uint8_t* dst = smem + s * kDtStageBytes + (is_v ? kDtTile : 0);
-            mbar_arrive_expect_tx(&fullb[s], kDtTile);
-            for (int p = 0; p < pages_per_tile; ++p) {
-              const int slot0 = page_slot(cur, p);
-              const int off = p * block_size * 128;
-              tma_load_3d(dst + off, tm, &fullb[s], 0, cur.g, slot0);
-              tma_load_3d(dst + 16384 + off, tm, &fullb[s], 64, cur.g, slot0);
-            }
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        step(cur);
-        if (ahead.item < n_items) {
-          prefetch_tile(ahead);
-          step(ahead);
         }
       }
     }
@@ -600,10 +529,10 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
       const int d = tid;
       for (int h = 0; h < G; ++h) {
         const size_t head = static_cast<size_t>(seq) * nq + g * G + h;
-        float* w = part_slot(it, seq, g, h, split);
-        if (w == nullptr) {
+        if (splits == 1) {
           out[head * 128 + d] = __float2bfloat16(0.f);
         } else {
+          float* w = ws + (head * splits + split) * 130;
           w[d] = 0.f;
           if (d == 0) {
             w[128] = -INFINITY;
@@ -696,10 +625,10 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
         for (int h = 0; h < G; ++h) {
           const float l = s_lsum[0][h] + s_lsum[1][h] + s_lsum[2][h] + s_lsum[3][h];
           const size_t head = static_cast<size_t>(seq) * nq + g * G + h;
-          float* w = part_slot(item, seq, g, h, split);
-          if (w == nullptr) {
+          if (splits == 1) {
             out[head * 128 + d] = __float2bfloat16(l > 0.f ? O[h] / l : 0.f);
           } else {
+            float* w = ws + (head * splits + split) * 130;
             w[d] = O[h];
             if (d == 0) {
               w[128] = m[h];
@@ -766,27 +695,7 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
     const char* e = getenv("SB_DECODE_ATTN_PERSIST");
     persist = (e && e[0] == '0') ? 0 : 1;
   }
-  // Tail mode (persistent kernel, no uniform split, more pairs than SMs): the pairs of the last, partly filled round
-  // are cut into tail_splits parts (needs the workspace for their partial results).
-  // Measured on B200 the kernel is bound by HBM efficiency rather than by SM time (a half-empty last round streams as
-  // fast as a full one), so the extra parts only add the combine pass: off unless SB_DECODE_ATTN_TAIL=1.
-  int tail_start = n * nkv, tail_splits = 1;
-  const char* tail_env = getenv("SB_DECODE_ATTN_TAIL");
-  if (persist && splits == 1 && workspace != nullptr && tail_env && tail_env[0] == '1') {
-    const int sms = sb::sm_count(), pairs = n * nkv;
-    const int rem = pairs % sms;
-    if (pairs > sms && rem != 0 && 2 * rem <= sms + sms / 4) {
-      int s2 = sms / rem;
-      if (s2 > 4) s2 = 4;
-      if (s2 >= 2) {
-        tail_start = pairs - rem;
-        tail_splits = s2;
-      }
-    }
-  }
-  const char* l2_env = getenv("SB_DECODE_ATTN_L2_AHEAD");
-  const bool l2_ahead = l2_env && l2_env[0] == '1';  // measured slower on B200 (see the kernel comment): opt-in
-  const int n_items = tail_start * splits + (n * nkv - tail_start) * tail_splits;
+  const int n_items = n * nkv * splits;
   const int pgrid = n_items < sb::sm_count() ? n_items : sb::sm_count();
 #define SB_DT_CASE(GV)                                                                                              \
   case GV: {                                                                                                        \
@@ -809,8 +718,7 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
                      st,                                                                                            \
                      *tk, *tv, reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                 \
                      reinterpret_cast<__nv_bfloat16*>(out), workspace, n, nq, nkv, block_size, max_blocks, splits,  \
-                     q_stride, sl2, sb::device_status_ptr(), tail_start, tail_splits, l2_ahead ? k_cache : nullptr, \
-                     l2_ahead ? v_cache : nullptr);                                                                 \
+                     q_stride, sl2, sb::device_status_ptr());                                                       \
     else                                                                                                            \
       sb::launch_pdl(sb::attn_decode_tc_kernel<GV>, grid, dim3(sb::kDtThreads), sb::kDtSmem, st, *tk, *tv,          \
                      reinterpret_cast<const __nv_bfloat16*>(qkv), block_tables, ctx_lens,                           \
@@ -832,14 +740,9 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
       return SB_ERR_ARG;
   }
 #undef SB_DT_CASE
-  if (splits > 1) {
+  if (splits > 1)
     sb::launch_pdl(sb::attn_decode_tc_combine_kernel, dim3(n * nq), dim3(128), 0, st, workspace,
                    reinterpret_cast<__nv_bfloat16*>(out), splits);
-  } else if (tail_splits > 1 && n * nkv > tail_start) {
-    // heads are numbered pair * G + h: the tail pairs' heads are the last (pairs - tail_start) * G rows of `out`
-    sb::launch_pdl(sb::attn_decode_tc_combine_kernel, dim3((n * nkv - tail_start) * G), dim3(128), 0, st, workspace,
-                   reinterpret_cast<__nv_bfloat16*>(out) + static_cast<size_t>(tail_start) * G * 128, tail_splits);
-  }
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -51,8 +51,6 @@ _VARS: List[EnvVar] = [
     EnvVar("SB_FUSED_MLP", "1", _flag, "SwiGLU inside the gate/up and down-gradient GEMM epilogues (training)"),
     EnvVar("SB_DECODE_FUSED_MLP", "1", _flag, "SwiGLU inside the gate/up GEMM epilogue (decode)"),
     EnvVar("SB_DECODE_ATTN_PERSIST", "1", _flag, "persistent paged decode attention (one CTA per SM walking a work list)"),
-    EnvVar("SB_DECODE_ATTN_TAIL", "0", _flag, "cut only the (sequence, kv head) pairs of the last, partly filled round of decode attention"),
-    EnvVar("SB_DECODE_ATTN_L2_AHEAD", "0", _flag, "decode attention: producer warps touch the next tiles' cache lines with prefetch.global.L2 (measured slower)"),
     EnvVar("SB_DECODE_ATTN_SPLITS", "", str, "force the context split count of decode attention (empty = cost model)"),
     EnvVar("SB_BF16_TFLOPS", "1376.9", float, "bf16 GEMM peak used as roofline denominator by the benchmarks (TFLOP/s)"),
     EnvVar("SB_HBM_GBS", "6543.4", float, "HBM copy bandwidth used as roofline denominator by the benchmarks (GB/s)"),

@@ -177,12 +177,8 @@ def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     use_tc = (128 % bs == 0) and (bs % 8 == 0) and D == 128 and (G <= 8 or G in (12, 16)) and not force_simt
     mc = max_ctx if max_ctx > 0 else block_tables.shape[1] * bs
     splits = decode_num_splits_tc(n, nkv, mc) if use_tc else decode_num_splits(n, nkv, mc)
-    # the tensor-core kernel may cut the (sequence, kv head) pairs of its last round into up to four parts even when
-    # no uniform split was asked for, so it always gets room for partial results
-    ws_splits = max(splits, 4) if use_tc else splits
-    need = decode_workspace_floats(n, nq, D, ws_splits)
-    if ws_splits > 1 and (workspace is None or workspace.numel() < need):
-        workspace = torch.empty(need, device=qkv.device, dtype=torch.float32)
+    if workspace is None and splits > 1:
+        workspace = torch.empty(decode_workspace_floats(n, nq, D, splits), device=qkv.device, dtype=torch.float32)
     if use_tc:
         code = _k().sb_attn_decode_paged_tc(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                                             block_tables.data_ptr(), ctx_lens.data_ptr(), out.data_ptr(),

@@ -114,10 +114,8 @@ def test_decode_paged(nq, nkv, bs):
 
 
 @pytest.mark.parametrize("n,nkv,nq", [(100, 2, 12), (160, 2, 4), (75, 4, 8)])
-def test_decode_paged_many_sequences_tail_split(n, nkv, nq, monkeypatch):
-    """More (sequence, kv head) pairs than SMs with a partly filled last round: the persistent kernel cuts only the
-    pairs of that round (partial results + combine) and writes the others directly; inactive slots included."""
-    monkeypatch.setenv("SB_DECODE_ATTN_TAIL", "1")
+def test_decode_paged_many_sequences(n, nkv, nq):
+    """More (sequence, kv head) pairs than SMs (several items per persistent CTA), ragged contexts, inactive slots."""
     torch.manual_seed(n)
     D, bs = 128, 32
     ctx = torch.randint(1, 700, (n,), dtype=torch.int32)
