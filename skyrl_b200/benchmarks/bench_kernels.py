@@ -39,7 +39,7 @@ def timeit(fn, iters, warmup=3):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "hbm"])
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "hbm", "membench", "elementwise"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -159,6 +159,72 @@ def main() -> None:
         ms_max = timeit(lambda: xb.amax(), a.iters)
         out.update(bytes=nbytes, copy_gbs=2 * nbytes / ms_copy / 1e6, read_sum_fp32_gbs=nbytes / ms_sum / 1e6,
                    read_amax_bf16_gbs=nbytes / ms_max / 1e6)
+    elif a.which == "elementwise":
+        # the bandwidth-bound kernels of a step: achieved bytes / s against the measured copy bandwidth
+        from skyrl_b200.ops import elementwise as ew, optim, sampling
+
+        T, H, F, V = a.tokens, 1536, 8960, 151936
+        x = torch.randn(T, H, **bf)
+        d = torch.randn(T, H, **bf)
+        w = torch.ones(H, **bf)
+        gu = torch.randn(T, 2 * F, **bf)
+        rows = []
+
+        def rec(name, nbytes, fn):
+            ms = timeit(fn, a.iters)
+            rows.append({"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+                         "fraction_of_measured_hbm": round(nbytes / ms / 1e6 / a.hbm_gbs, 3)})
+
+        with torch.no_grad():
+            rec("add_rmsnorm fwd (residual add + norm)", 4 * T * H * 2, lambda: ew.add_rmsnorm(x, d, w, 1e-6))
+            rec("swiglu fwd", 3 * T * F * 2, lambda: ew.swiglu(gu))
+            dact = torch.randn(T, F, **bf)
+            rec("swiglu bwd", 5 * T * F * 2, lambda: ew.swiglu_backward(gu, dact))
+            qkv = torch.randn(T, 16 * 128, **bf)
+            pos = torch.arange(T, device="cuda", dtype=torch.int32) % 2048
+            table = ew.build_rope_table(4096, 128, 1e6, "cuda")
+            rec("rope in place (12 q + 2 k heads)", 2 * T * 14 * 128 * 2, lambda: ew.rope_(qkv, pos, table, 14, 128))
+            n = 1_543_000_000 // 8  # one rank's optimizer shard of a 1.5B model at 8 GPUs
+            master, m_, v_ = (torch.zeros(n, device="cuda") for _ in range(3))
+            grad = torch.randn(n, device="cuda")
+            param = torch.zeros(n, **bf)
+            rec("adamw_flat (fp32 master/m/v, bf16 param out)", n * (4 * 4 + 3 * 4 + 2),
+                lambda: optim.adamw_flat(master, m_, v_, grad, param, 1e-5, 0.9, 0.999, 1e-8, 0.01, 1))
+            logits = torch.randn(256, V, **bf)
+            temp = torch.ones(256, device="cuda")
+            rec("sample (gumbel + log-prob, 256 x 151936 bf16 logits)", 256 * V * 2, lambda: sampling.sample(logits, temp, 1))
+        out.update(tokens=T, rows=rows)
+    elif a.which == "membench":
+        # ceiling of the TMA read stream (stages per CTA x CTAs per SM) against plain 16-byte loads, 2 GB buffer
+        import ctypes
+
+        from skyrl_b200.ops import _lib
+
+        lib = _lib.kernels()
+        vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        lib.sb_membench_tma_stream.argtypes = [vp, cl, ci, ci, ci, ci, ci, vp]
+        lib.sb_membench_ld_stream.argtypes = [vp, cl, ci, vp, vp]
+        nbytes = 2 << 30
+        buf = torch.empty(nbytes // 2, **bf).normal_()
+        sink = torch.zeros(4, device="cuda", dtype=torch.int32)
+        rows = []
+        # (stages, CTAs per SM, rows per box, 128-byte columns per matrix row, boxes of a stage issued by parallel lanes)
+        for stages, ctas, box_rows, slices, lanes in ((1, 1, 256, 1, 0), (2, 1, 256, 1, 0), (3, 1, 256, 1, 0), (6, 1, 256, 1, 0),
+                                                      (1, 2, 256, 1, 0), (2, 3, 256, 1, 0), (6, 1, 32, 1, 0), (6, 1, 32, 4, 0),
+                                                      (6, 1, 128, 4, 0), (6, 1, 256, 4, 0), (3, 2, 32, 4, 0), (6, 1, 32, 4, 1),
+                                                      (6, 1, 16, 4, 1), (3, 1, 32, 4, 1), (6, 1, 64, 4, 1)):
+            def run(stages=stages, ctas=ctas, box_rows=box_rows, slices=slices, lanes=lanes):
+                _lib.check(lib.sb_membench_tma_stream(buf.data_ptr(), nbytes, stages, ctas, box_rows, slices, lanes,
+                                                      _lib.stream_ptr()), "membench tma")
+            ms = timeit(run, a.iters)
+            rows.append({"path": "tma", "stages": stages, "ctas_per_sm": ctas, "box_rows": box_rows, "columns": slices,
+                         "lane_issue": lanes, "gbs": round(nbytes / ms / 1e6, 1)})
+        for ctas in (2, 8):
+            def run(ctas=ctas):
+                _lib.check(lib.sb_membench_ld_stream(buf.data_ptr(), nbytes, ctas, sink.data_ptr(), _lib.stream_ptr()), "membench ld")
+            ms = timeit(run, a.iters)
+            rows.append({"path": "ld.global.v4", "ctas_per_sm": ctas, "gbs": round(nbytes / ms / 1e6, 1)})
+        out.update(bytes=nbytes, rows=rows, device_status=_lib.status_read_clear())
     elif a.which == "moe":
         # one mixture-of-experts FFN layer (router, grouped gate/up GEMM, SwiGLU, grouped down GEMM, weighted combine)
         from skyrl_b200.models.moe import moe_ffn

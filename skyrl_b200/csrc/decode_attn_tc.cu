@@ -373,12 +373,16 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
   const int pages_per_tile = 128 / block_size;
 
   if (warp == 0 || warp == 6) {
-    // warp 0 streams the K tiles, warp 6 the V tiles (one thread each)
-    if (lane == 0) {
+    // Warp 0 streams the K tiles, warp 6 the V tiles.  Lane 0 waits for a free stage; the boxes of the tile (one per
+    // cache page and head-dim half, 4 KB each with 32-token pages) are then issued by as many lanes in one warp
+    // instruction: a single thread issuing 4 KB boxes one after the other sustains only about half of the HBM
+    // bandwidth (benchmarks/bench_kernels.py --which membench).
+    {
       const bool is_v = warp == 6;
       uint64_t* fullb = is_v ? vfull : kfull;
       uint64_t* emptyb = is_v ? vempty : kempty;
       const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+      const int n_boxes = pages_per_tile * 2;  // <= 32 (pages of at least 8 tokens)
       int jt = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -387,21 +391,25 @@ attn_decode_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_k, const __
         const int* bt = block_tables + static_cast<size_t>(seq) * max_blocks;
         for (int j = 0; j < n_tiles; ++j, ++jt) {
           const int s = jt % kDtStages;
-          if (!mbar_wait(&emptyb[s], ((jt / kDtStages) & 1) ^ 1, status, is_v ? 0x832 : 0x831)) {
+          int go = 1;
+          if (lane == 0) {
+            go = mbar_wait(&emptyb[s], ((jt / kDtStages) & 1) ^ 1, status, is_v ? 0x832 : 0x831) ? 1 : 0;
+            if (go) mbar_arrive_expect_tx(&fullb[s], kDtTile);
+          }
+          go = __shfl_sync(0xffffffffu, go, 0);
+          if (!go) {
             ok = false;
             break;
           }
-          uint8_t* dst = smem + s * kDtStageBytes + (is_v ? kDtTile : 0);
-          mbar_arrive_expect_tx(&fullb[s], kDtTile);
-          const int tok0 = t0 + j * 128;
-          for (int p = 0; p < pages_per_tile; ++p) {
-            int pi = (tok0 + p * block_size) / block_size;
+          if (lane < n_boxes) {
+            const int p = lane >> 1, half = lane & 1;
+            int pi = (t0 + j * 128 + p * block_size) / block_size;
             pi = pi < max_blocks ? pi : max_blocks - 1;
             const int slot0 = __ldg(bt + pi) * block_size;
-            const int off = p * block_size * 128;
-            tma_load_3d(dst + off, tm, &fullb[s], 0, g, slot0);
-            tma_load_3d(dst + 16384 + off, tm, &fullb[s], 64, g, slot0);
+            uint8_t* dst = smem + s * kDtStageBytes + (is_v ? kDtTile : 0) + half * 16384 + p * block_size * 128;
+            tma_load_3d(dst, tm, &fullb[s], half * 64, g, slot0);
           }
+          __syncwarp();
         }
       }
     }

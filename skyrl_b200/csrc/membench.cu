@@ -1,0 +1,132 @@
+// Read-stream micro-benchmarks: how fast can one B200 pull a buffer that is larger than L2, and through which path?
+//
+//   tma_stream   : every CTA copies 32 KB boxes (256 rows x 128 bytes, the row width of a 128-byte-swizzled operand
+//                  tile) into a ring of shared-memory stages with TMA; a second thread frees each stage as soon as it is
+//                  full.  Knobs: stages per CTA and CTAs per SM (shared memory per CTA = stages x 32 KB).
+//   ld_stream    : plain 16-byte loads from every thread (grid-stride, eight in flight per thread), reduced to one
+//                  word per thread so that the loads are not optimised away.
+//
+// The decode-time kernels of this library (paged attention, weight-streaming GEMMs, grouped expert GEMMs) are TMA
+// streams; this file measures the ceiling of that path against the load/store path on the same buffer.
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace sb {
+
+constexpr int kMbBoxRows = 256;
+constexpr int kMbBoxBytes = kMbBoxRows * 128;  // 32 KB
+
+// A stage is filled by `boxes_per_stage` boxes of `box_rows` rows x 128 bytes.  With slices == 1 the rows are contiguous
+// (pitch 128 bytes); with slices > 1 the buffer is a matrix whose rows hold `slices` 128-byte columns (pitch
+// slices x 128 bytes, the shape of a paged KV cache: token rows of several heads / head halves side by side) and
+// consecutive boxes take neighbouring columns of the same rows.
+__global__ void __launch_bounds__(64) tma_stream_kernel(const __grid_constant__ CUtensorMap tm, long long n_boxes, int stages,
+                                                        int* status, int box_rows, int boxes_per_stage, int slices,
+                                                        int lane_issue) {
+  extern __shared__ uint8_t mb_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mb_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * kMbBoxBytes);
+  uint64_t* empty = full + stages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (lane_issue && threadIdx.x < 32) {
+    // lane j issues box j of the stage: one warp instruction hands all boxes of a stage to the copy engine
+    const int lane = threadIdx.x;
+    int it = 0;
+    const long long n_groups = n_boxes / boxes_per_stage;
+    for (long long gi = blockIdx.x; gi < n_groups; gi += gridDim.x, ++it) {
+      const int s = it % stages;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(&empty[s], ((it / stages) & 1) ^ 1, status, 0x901) ? 1 : 0;
+        if (ok) mbar_arrive_expect_tx(&full[s], kMbBoxBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < boxes_per_stage) {
+        const long long b = gi * boxes_per_stage + lane;
+        tma_load_2d(smem + static_cast<size_t>(s) * kMbBoxBytes + static_cast<size_t>(lane) * box_rows * 128, &tm, &full[s],
+                    static_cast<int>(b % slices) * 64, static_cast<int>((b / slices) * box_rows));
+      }
+      __syncwarp();
+    }
+  } else if (!lane_issue && threadIdx.x == 0) {
+    int it = 0;
+    const long long n_groups = n_boxes / boxes_per_stage;
+    for (long long gi = blockIdx.x; gi < n_groups; gi += gridDim.x, ++it) {
+      const int s = it % stages;
+      if (!mbar_wait(&empty[s], ((it / stages) & 1) ^ 1, status, 0x901)) break;
+      mbar_arrive_expect_tx(&full[s], kMbBoxBytes);
+      for (int j = 0; j < boxes_per_stage; ++j) {
+        const long long b = gi * boxes_per_stage + j;
+        tma_load_2d(smem + static_cast<size_t>(s) * kMbBoxBytes + static_cast<size_t>(j) * box_rows * 128, &tm, &full[s],
+                    static_cast<int>(b % slices) * 64, static_cast<int>((b / slices) * box_rows));
+      }
+    }
+  } else if (threadIdx.x == 32) {
+    int it = 0;
+    const long long n_groups = n_boxes / boxes_per_stage;
+    for (long long gi = blockIdx.x; gi < n_groups; gi += gridDim.x, ++it) {
+      const int s = it % stages;
+      if (!mbar_wait(&full[s], (it / stages) & 1, status, 0x902)) break;
+      mbar_arrive(&empty[s]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) ld_stream_kernel(const uint4* __restrict__ src, long long n_vec, unsigned int* __restrict__ sink) {
+  unsigned int acc = 0;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 7 * stride < n_vec; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldg(src + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc ^= v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+  }
+  for (; i < n_vec; i += stride) {
+    const uint4 v = __ldg(src + i);
+    acc ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  if (acc == 0x9e3779b9u) sink[0] = acc;  // practically never: keeps the loads alive
+}
+
+}  // namespace sb
+
+extern "C" {
+
+// lane_issue: the boxes of a stage are issued by as many lanes of one warp at once instead of by one thread in turn.
+// Streams `bytes` (a multiple of 256 KB) from `buf` with `ctas_per_sm` CTAs per SM and `stages` 32 KB stages per CTA.
+int sb_membench_tma_stream(const void* buf, long long bytes, int stages, int ctas_per_sm, int box_rows, int slices,
+                           int lane_issue, void* stream) {
+  if (bytes <= 0 || bytes % (sb::kMbBoxBytes * 8LL) != 0 || stages < 1 || stages > 7 || ctas_per_sm < 1 || ctas_per_sm > 8)
+    return SB_ERR_ARG;
+  if (box_rows < 8 || box_rows > 256 || (256 % box_rows) != 0 || slices < 1 || slices > 8) return SB_ERR_ARG;
+  const size_t smem = static_cast<size_t>(stages) * sb::kMbBoxBytes + 1024 + 2 * 8 * 8;
+  if (smem * ctas_per_sm > 227u * 1024u) return SB_ERR_ARG;
+  const long long rows = bytes / 128 / slices;
+  const CUtensorMap* tm = sb::get_tmap_bf16_2d(buf, rows, 64LL * slices, 64LL * slices, box_rows, 64);
+  if (!tm) return SB_ERR_TMAP;
+  if (cudaFuncSetAttribute(sb::tma_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+      cudaSuccess)
+    return SB_ERR_CUDA;
+  sb::tma_stream_kernel<<<sb::sm_count() * ctas_per_sm, 64, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      *tm, bytes / (128LL * box_rows), stages, sb::device_status_ptr(), box_rows, sb::kMbBoxRows / box_rows, slices, lane_issue);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+int sb_membench_ld_stream(const void* buf, long long bytes, int ctas_per_sm, unsigned int* sink, void* stream) {
+  if (bytes <= 0 || (bytes & 15) || ctas_per_sm < 1 || ctas_per_sm > 8 || (reinterpret_cast<uintptr_t>(buf) & 15)) return SB_ERR_ARG;
+  sb::ld_stream_kernel<<<sb::sm_count() * ctas_per_sm, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(buf), bytes / 16, sink);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+}  // extern "C"
