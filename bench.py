@@ -247,6 +247,10 @@ def main() -> None:
     wall = pdist.all_reduce_max_scalar(wall, env.device)
     tokens_all = pdist.all_reduce_sum_scalar(tokens, env.device)
     gen_all = pdist.all_reduce_sum_scalar(gen_tokens, env.device)
+    # ranks of a tensor / sequence / pipeline parallel group train on one merged batch and each of them reports it:
+    # count that batch once (expert-parallel ranks keep their own data)
+    share = max(args.tp, args.sp, args.pp)
+    tokens_all, gen_all, e2e_all = tokens_all / share, gen_all / share, e2e_all / share
     K = max(1, args.steps)
     if env.is_main:
         status = _lib.status_read_clear() if torch.cuda.is_available() else 0
