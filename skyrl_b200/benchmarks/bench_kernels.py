@@ -202,23 +202,26 @@ def main() -> None:
 
         lib = _lib.kernels()
         vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        lib.sb_membench_tma_stream.argtypes = [vp, cl, ci, ci, ci, ci, ci, vp]
+        lib.sb_membench_tma_stream.argtypes = [vp, cl, ci, ci, ci, ci, ci, ci, vp]
         lib.sb_membench_ld_stream.argtypes = [vp, cl, ci, vp, vp]
         nbytes = 2 << 30
         buf = torch.empty(nbytes // 2, **bf).normal_()
         sink = torch.zeros(4, device="cuda", dtype=torch.int32)
         rows = []
         # (stages, CTAs per SM, rows per box, 128-byte columns per matrix row, boxes of a stage issued by parallel lanes)
-        for stages, ctas, box_rows, slices, lanes in ((1, 1, 256, 1, 0), (2, 1, 256, 1, 0), (3, 1, 256, 1, 0), (6, 1, 256, 1, 0),
-                                                      (1, 2, 256, 1, 0), (2, 3, 256, 1, 0), (6, 1, 32, 1, 0), (6, 1, 32, 4, 0),
-                                                      (6, 1, 128, 4, 0), (6, 1, 256, 4, 0), (3, 2, 32, 4, 0), (6, 1, 32, 4, 1),
-                                                      (6, 1, 16, 4, 1), (3, 1, 32, 4, 1), (6, 1, 64, 4, 1)):
-            def run(stages=stages, ctas=ctas, box_rows=box_rows, slices=slices, lanes=lanes):
-                _lib.check(lib.sb_membench_tma_stream(buf.data_ptr(), nbytes, stages, ctas, box_rows, slices, lanes,
+        # last field: 1 = every CTA walks a contiguous run of stages (with 128 columns: along its own 16 KB-pitch row panel,
+        # the access pattern of a GEMM streaming a K-major weight), 0 = stages dealt round-robin
+        for stages, ctas, box_rows, slices, lanes, walk in (
+                (1, 1, 256, 1, 0, 0), (2, 1, 256, 1, 0, 0), (3, 1, 256, 1, 0, 0), (6, 1, 256, 1, 0, 0), (1, 2, 256, 1, 0, 0),
+                (2, 3, 256, 1, 0, 0), (6, 1, 32, 1, 0, 0), (6, 1, 32, 4, 0, 0), (6, 1, 128, 4, 0, 0), (6, 1, 256, 4, 0, 0),
+                (3, 2, 32, 4, 0, 0), (6, 1, 32, 4, 1, 0), (6, 1, 16, 4, 1, 0), (3, 1, 32, 4, 1, 0), (6, 1, 64, 4, 1, 0),
+                (6, 1, 256, 1, 0, 1), (6, 1, 128, 128, 0, 1), (6, 1, 256, 128, 0, 1), (6, 1, 128, 128, 0, 0), (6, 1, 128, 32, 0, 1)):
+            def run(stages=stages, ctas=ctas, box_rows=box_rows, slices=slices, lanes=lanes, walk=walk):
+                _lib.check(lib.sb_membench_tma_stream(buf.data_ptr(), nbytes, stages, ctas, box_rows, slices, lanes, walk,
                                                       _lib.stream_ptr()), "membench tma")
             ms = timeit(run, a.iters)
             rows.append({"path": "tma", "stages": stages, "ctas_per_sm": ctas, "box_rows": box_rows, "columns": slices,
-                         "lane_issue": lanes, "gbs": round(nbytes / ms / 1e6, 1)})
+                         "lane_issue": lanes, "walk": walk, "gbs": round(nbytes / ms / 1e6, 1)})
         for ctas in (2, 8):
             def run(ctas=ctas):
                 _lib.check(lib.sb_membench_ld_stream(buf.data_ptr(), nbytes, ctas, sink.data_ptr(), _lib.stream_ptr()), "membench ld")

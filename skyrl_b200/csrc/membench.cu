@@ -22,7 +22,9 @@ constexpr int kMbBoxBytes = kMbBoxRows * 128;  // 32 KB
 // consecutive boxes take neighbouring columns of the same rows.
 __global__ void __launch_bounds__(64) tma_stream_kernel(const __grid_constant__ CUtensorMap tm, long long n_boxes, int stages,
                                                         int* status, int box_rows, int boxes_per_stage, int slices,
-                                                        int lane_issue) {
+                                                        int lane_issue, int walk) {
+  // walk = 1: a CTA takes a contiguous run of stages (with many columns: it walks along its own panel of rows, 128
+  // bytes of every row per box, the way a GEMM streams a K-major operand); walk = 0: stages are dealt round-robin.
   extern __shared__ uint8_t mb_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mb_smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * kMbBoxBytes);
@@ -40,7 +42,11 @@ __global__ void __launch_bounds__(64) tma_stream_kernel(const __grid_constant__ 
     const int lane = threadIdx.x;
     int it = 0;
     const long long n_groups = n_boxes / boxes_per_stage;
-    for (long long gi = blockIdx.x; gi < n_groups; gi += gridDim.x, ++it) {
+    const long long per_cta = (n_groups + gridDim.x - 1) / gridDim.x;
+    const long long g_begin = walk ? blockIdx.x * per_cta : blockIdx.x;
+    const long long g_end = walk ? (g_begin + per_cta < n_groups ? g_begin + per_cta : n_groups) : n_groups;
+    const long long g_step = walk ? 1 : gridDim.x;
+    for (long long gi = g_begin; gi < g_end; gi += g_step, ++it) {
       const int s = it % stages;
       int ok = 1;
       if (lane == 0) {
@@ -59,7 +65,11 @@ __global__ void __launch_bounds__(64) tma_stream_kernel(const __grid_constant__ 
   } else if (!lane_issue && threadIdx.x == 0) {
     int it = 0;
     const long long n_groups = n_boxes / boxes_per_stage;
-    for (long long gi = blockIdx.x; gi < n_groups; gi += gridDim.x, ++it) {
+    const long long per_cta = (n_groups + gridDim.x - 1) / gridDim.x;
+    const long long g_begin = walk ? blockIdx.x * per_cta : blockIdx.x;
+    const long long g_end = walk ? (g_begin + per_cta < n_groups ? g_begin + per_cta : n_groups) : n_groups;
+    const long long g_step = walk ? 1 : gridDim.x;
+    for (long long gi = g_begin; gi < g_end; gi += g_step, ++it) {
       const int s = it % stages;
       if (!mbar_wait(&empty[s], ((it / stages) & 1) ^ 1, status, 0x901)) break;
       mbar_arrive_expect_tx(&full[s], kMbBoxBytes);
@@ -72,7 +82,11 @@ __global__ void __launch_bounds__(64) tma_stream_kernel(const __grid_constant__ 
   } else if (threadIdx.x == 32) {
     int it = 0;
     const long long n_groups = n_boxes / boxes_per_stage;
-    for (long long gi = blockIdx.x; gi < n_groups; gi += gridDim.x, ++it) {
+    const long long per_cta = (n_groups + gridDim.x - 1) / gridDim.x;
+    const long long g_begin = walk ? blockIdx.x * per_cta : blockIdx.x;
+    const long long g_end = walk ? (g_begin + per_cta < n_groups ? g_begin + per_cta : n_groups) : n_groups;
+    const long long g_step = walk ? 1 : gridDim.x;
+    for (long long gi = g_begin; gi < g_end; gi += g_step, ++it) {
       const int s = it % stages;
       if (!mbar_wait(&full[s], (it / stages) & 1, status, 0x902)) break;
       mbar_arrive(&empty[s]);
@@ -105,10 +119,10 @@ extern "C" {
 // lane_issue: the boxes of a stage are issued by as many lanes of one warp at once instead of by one thread in turn.
 // Streams `bytes` (a multiple of 256 KB) from `buf` with `ctas_per_sm` CTAs per SM and `stages` 32 KB stages per CTA.
 int sb_membench_tma_stream(const void* buf, long long bytes, int stages, int ctas_per_sm, int box_rows, int slices,
-                           int lane_issue, void* stream) {
+                           int lane_issue, int walk, void* stream) {
   if (bytes <= 0 || bytes % (sb::kMbBoxBytes * 8LL) != 0 || stages < 1 || stages > 7 || ctas_per_sm < 1 || ctas_per_sm > 8)
     return SB_ERR_ARG;
-  if (box_rows < 8 || box_rows > 256 || (256 % box_rows) != 0 || slices < 1 || slices > 8) return SB_ERR_ARG;
+  if (box_rows < 8 || box_rows > 256 || (256 % box_rows) != 0 || slices < 1 || slices > 256) return SB_ERR_ARG;
   const size_t smem = static_cast<size_t>(stages) * sb::kMbBoxBytes + 1024 + 2 * 8 * 8;
   if (smem * ctas_per_sm > 227u * 1024u) return SB_ERR_ARG;
   const long long rows = bytes / 128 / slices;
@@ -118,7 +132,7 @@ int sb_membench_tma_stream(const void* buf, long long bytes, int stages, int cta
       cudaSuccess)
     return SB_ERR_CUDA;
   sb::tma_stream_kernel<<<sb::sm_count() * ctas_per_sm, 64, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      *tm, bytes / (128LL * box_rows), stages, sb::device_status_ptr(), box_rows, sb::kMbBoxRows / box_rows, slices, lane_issue);
+      *tm, bytes / (128LL * box_rows), stages, sb::device_status_ptr(), box_rows, sb::kMbBoxRows / box_rows, slices, lane_issue, walk);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
