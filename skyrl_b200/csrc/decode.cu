@@ -3,6 +3,9 @@
 // token-embedding gather.
 #include <curand_kernel.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "host_common.h"
 #include "ptx.cuh"
 
@@ -463,7 +466,9 @@ int sb_sample_gumbel(const void* logits, int is_bf16, long long row_stride, int 
   constexpr int kSlots = 16, kMaxRows = 4096, kMaxParts = 8;
   static sb::SamplePart* part_buf = nullptr;
   static unsigned int* counter_buf = nullptr;
-  static unsigned int next_slot = 0;
+  static std::atomic<unsigned int> next_slot{0};
+  static std::mutex alloc_mu;  // engines may be stepped from several host threads
+  std::lock_guard<std::mutex> lock(alloc_mu);
   int n_parts = 1;
   if (n <= kMaxRows && V >= 32768) {
     const int want = (4 * sb::sm_count() + n - 1) / n;
@@ -484,7 +489,7 @@ int sb_sample_gumbel(const void* logits, int is_bf16, long long row_stride, int 
   sb::SamplePart* parts = nullptr;
   unsigned int* counters = nullptr;
   if (n_parts > 1) {
-    const unsigned int slot = next_slot++ % kSlots;
+    const unsigned int slot = next_slot.fetch_add(1) % kSlots;
     parts = part_buf + static_cast<size_t>(slot) * kMaxRows * kMaxParts;
     counters = counter_buf + static_cast<size_t>(slot) * kMaxRows;
   }
