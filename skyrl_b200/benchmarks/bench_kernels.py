@@ -39,7 +39,7 @@ def timeit(fn, iters, warmup=3):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "hbm", "membench", "elementwise"])
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "elementwise"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -148,17 +148,6 @@ def main() -> None:
         fl = 2.0 * M * N * K
         out.update(m=M, n=N, k=K, emulated_ranks=R, ms=ms, tflops=fl / ms / 1e9,
                    fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
-    elif a.which == "hbm":
-        # what the memory system delivers to library kernels: copy (read + write bytes) and read-only reductions
-        nbytes = 4 << 30
-        x = torch.empty(nbytes // 4, device="cuda", dtype=torch.float32).normal_()
-        y = torch.empty_like(x)
-        ms_copy = timeit(lambda: y.copy_(x), a.iters)
-        ms_sum = timeit(lambda: x.sum(), a.iters)
-        xb = x.view(torch.bfloat16)
-        ms_max = timeit(lambda: xb.amax(), a.iters)
-        out.update(bytes=nbytes, copy_gbs=2 * nbytes / ms_copy / 1e6, read_sum_fp32_gbs=nbytes / ms_sum / 1e6,
-                   read_amax_bf16_gbs=nbytes / ms_max / 1e6)
     elif a.which == "elementwise":
         # the bandwidth-bound kernels of a step: achieved bytes / s against the measured copy bandwidth
         from skyrl_b200.ops import elementwise as ew, optim, sampling
@@ -194,40 +183,6 @@ def main() -> None:
             temp = torch.ones(256, device="cuda")
             rec("sample (gumbel + log-prob, 256 x 151936 bf16 logits)", 256 * V * 2, lambda: sampling.sample(logits, temp, 1))
         out.update(tokens=T, rows=rows)
-    elif a.which == "membench":
-        # ceiling of the TMA read stream (stages per CTA x CTAs per SM) against plain 16-byte loads, 2 GB buffer
-        import ctypes
-
-        from skyrl_b200.ops import _lib
-
-        lib = _lib.kernels()
-        vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-        lib.sb_membench_tma_stream.argtypes = [vp, cl, ci, ci, ci, ci, ci, ci, vp]
-        lib.sb_membench_ld_stream.argtypes = [vp, cl, ci, vp, vp]
-        nbytes = 2 << 30
-        buf = torch.empty(nbytes // 2, **bf).normal_()
-        sink = torch.zeros(4, device="cuda", dtype=torch.int32)
-        rows = []
-        # (stages, CTAs per SM, rows per box, 128-byte columns per matrix row, boxes of a stage issued by parallel lanes)
-        # last field: 1 = every CTA walks a contiguous run of stages (with 128 columns: along its own 16 KB-pitch row panel,
-        # the access pattern of a GEMM streaming a K-major weight), 0 = stages dealt round-robin
-        for stages, ctas, box_rows, slices, lanes, walk in (
-                (1, 1, 256, 1, 0, 0), (2, 1, 256, 1, 0, 0), (3, 1, 256, 1, 0, 0), (6, 1, 256, 1, 0, 0), (1, 2, 256, 1, 0, 0),
-                (2, 3, 256, 1, 0, 0), (6, 1, 32, 1, 0, 0), (6, 1, 32, 4, 0, 0), (6, 1, 128, 4, 0, 0), (6, 1, 256, 4, 0, 0),
-                (3, 2, 32, 4, 0, 0), (6, 1, 32, 4, 1, 0), (6, 1, 16, 4, 1, 0), (3, 1, 32, 4, 1, 0), (6, 1, 64, 4, 1, 0),
-                (6, 1, 256, 1, 0, 1), (6, 1, 128, 128, 0, 1), (6, 1, 256, 128, 0, 1), (6, 1, 128, 128, 0, 0), (6, 1, 128, 32, 0, 1)):
-            def run(stages=stages, ctas=ctas, box_rows=box_rows, slices=slices, lanes=lanes, walk=walk):
-                _lib.check(lib.sb_membench_tma_stream(buf.data_ptr(), nbytes, stages, ctas, box_rows, slices, lanes, walk,
-                                                      _lib.stream_ptr()), "membench tma")
-            ms = timeit(run, a.iters)
-            rows.append({"path": "tma", "stages": stages, "ctas_per_sm": ctas, "box_rows": box_rows, "columns": slices,
-                         "lane_issue": lanes, "walk": walk, "gbs": round(nbytes / ms / 1e6, 1)})
-        for ctas in (2, 8):
-            def run(ctas=ctas):
-                _lib.check(lib.sb_membench_ld_stream(buf.data_ptr(), nbytes, ctas, sink.data_ptr(), _lib.stream_ptr()), "membench ld")
-            ms = timeit(run, a.iters)
-            rows.append({"path": "ld.global.v4", "ctas_per_sm": ctas, "gbs": round(nbytes / ms / 1e6, 1)})
-        out.update(bytes=nbytes, rows=rows, device_status=_lib.status_read_clear())
     elif a.which == "moe":
         # one mixture-of-experts FFN layer (router, grouped gate/up GEMM, SwiGLU, grouped down GEMM, weighted combine)
         from skyrl_b200.models.moe import moe_ffn

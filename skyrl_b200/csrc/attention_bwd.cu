@@ -492,7 +492,9 @@ int sb_attn_bwd_varlen(const void* qkv, const void* out, const void* dout, const
   const CUtensorMap* tq64 = sb::get_tmap_bf16_2d(qkv, T, W, row_stride, 64);
   const CUtensorMap* tdo = sb::get_tmap_bf16_2d(dout, T, static_cast<long long>(nq) * 128, static_cast<long long>(nq) * 128, 128);
   if (!tq128 || !tq64 || !tdo) return SB_ERR_TMAP;
-  static bool attr_set = false;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
+  static bool attr_set_dev[64] = {};  // function attributes are per device
+  bool& attr_set = attr_set_dev[sb::device_index()];
   if (!attr_set) {
     if (cudaFuncSetAttribute(sb::attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::kDkvSmem) !=
             cudaSuccess ||

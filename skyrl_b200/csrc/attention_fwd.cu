@@ -317,7 +317,9 @@ int sb_attn_fwd_varlen(const void* qkv, void* out, float* lse, const int* cu_seq
   const long long W = static_cast<long long>(nq + 2 * nkv) * sb::kAttnD;
   const CUtensorMap* tm = sb::get_tmap_bf16_2d(qkv, T, W, row_stride, 128);
   if (!tm) return SB_ERR_TMAP;
-  static bool attr_set = false;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
+  static bool attr_set_dev[64] = {};  // function attributes are per device
+  bool& attr_set = attr_set_dev[sb::device_index()];
   if (!attr_set) {
     if (cudaFuncSetAttribute(sb::attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::kAttnSmem) !=
         cudaSuccess)

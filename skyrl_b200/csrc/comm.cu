@@ -93,16 +93,20 @@ __global__ void peer_adamw_push_kernel(float* __restrict__ master, float* __rest
                                        const float* __restrict__ grad, PeerPtrs params, int world, long long lo,
                                        long long n, float lr, float beta1, float beta2, float eps, float wd, float bc1,
                                        float bc2, const float* __restrict__ norm_pad, float max_norm, float grad_scale,
-                                       float* __restrict__ norm_out, int* __restrict__ skipped) {
+                                       float* __restrict__ norm_out, int* __restrict__ skipped,
+                                       const int* __restrict__ status) {
   float sq = 0.f;
   for (int r = 0; r < world; ++r) sq += norm_pad[r];
   const float norm = sqrtf(sq) * fabsf(grad_scale);
   const bool finite = isfinite(norm);
+  // a bounded wait that gave up earlier in this step (a peer never reached a barrier) means the reduced gradients
+  // may be incomplete: publish nothing, the host reads the status word after the step and raises
+  const bool broken = *reinterpret_cast<const volatile int*>(status) != 0;
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     *norm_out = norm;
-    *skipped = finite ? 0 : 1;
+    *skipped = broken ? 2 : (finite ? 0 : 1);
   }
-  if (!finite) return;  // non-finite gradient: leave parameters and moments untouched everywhere
+  if (!finite || broken) return;  // leave parameters and moments untouched everywhere
   float gs = grad_scale;
   if (max_norm > 0.f) gs *= fminf(1.f, max_norm / (norm + 1e-6f));
   const long long nv = n >> 2;
@@ -238,8 +242,10 @@ int sb_ipc_close_handle(void* p) { return cudaIpcCloseMemHandle(p) == cudaSucces
 int sb_peer_barrier(void* const* pads, int rank, int world, int channel, int epoch, unsigned long long wait_ns,
                     void* stream) {
   if (world < 1 || world > sb::kMaxPeers || channel < 0 || channel >= 8) return SB_ERR_ARG;
+  int* st = sb::device_status_ptr();
+  if (st == nullptr) return SB_ERR_CUDA;
   sb::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      sb::make_ptrs(pads, world), rank, world, channel, epoch, wait_ns, sb::device_status_ptr());
+      sb::make_ptrs(pads, world), rank, world, channel, epoch, wait_ns, st);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
@@ -263,9 +269,11 @@ int sb_peer_adamw_push(float* master, float* m, float* v, const float* grad, voi
                        float bc2, const float* norm_pad, float max_norm, float grad_scale, float* norm_out, int* skipped,
                        void* stream) {
   if (world < 1 || world > sb::kMaxPeers || (n & 3) || (lo & 3)) return SB_ERR_ARG;
+  const int* st = sb::device_status_ptr();
+  if (st == nullptr) return SB_ERR_CUDA;
   sb::peer_adamw_push_kernel<<<sb::comm_grid(n / 4, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       master, m, v, grad, sb::make_ptrs(params, world), world, lo, n, lr, beta1, beta2, eps, wd, bc1, bc2, norm_pad,
-      max_norm, grad_scale, norm_out, skipped);
+      max_norm, grad_scale, norm_out, skipped, st);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

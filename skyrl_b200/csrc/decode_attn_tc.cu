@@ -694,6 +694,7 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
   const CUtensorMap* tv = sb::get_tmap_bf16_3d(v_cache, 128, nkv, slots, 256, static_cast<uint64_t>(nkv) * 256, 64, 1,
                                                block_size);
   if (!tk || !tv) return SB_ERR_TMAP;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid(n, nkv, splits);
   const float sl2 = scale * 1.4426950408889634f;
@@ -707,14 +708,16 @@ int sb_attn_decode_paged_tc(const void* qkv, const void* k_cache, const void* v_
   const int pgrid = n_items < sb::sm_count() ? n_items : sb::sm_count();
 #define SB_DT_CASE(GV)                                                                                              \
   case GV: {                                                                                                        \
-    static bool attr = false;                                                                                       \
+    static bool attr_dev[64] = {};                                                                                  \
+    bool& attr = attr_dev[sb::device_index()];                                                                      \
     if (!attr) {                                                                                                    \
       if (cudaFuncSetAttribute(sb::attn_decode_tc_kernel<GV>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                                sb::kDtSmem) != cudaSuccess)                                                         \
         return SB_ERR_CUDA;                                                                                         \
       attr = true;                                                                                                  \
     }                                                                                                               \
-    static bool attr_p = false;                                                                                     \
+    static bool attr_p_dev[64] = {};                                                                                \
+    bool& attr_p = attr_p_dev[sb::device_index()];                                                                  \
     if (!attr_p) {                                                                                                  \
       if (cudaFuncSetAttribute(sb::attn_decode_tc_persist_kernel<GV>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                sb::kDtSmemPersist) != cudaSuccess)                                                      \

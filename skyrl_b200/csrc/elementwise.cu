@@ -536,7 +536,8 @@ int sb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define SB_NORM_BWD(NVV)                                                                                              \
   case NVV: {                                                                                                         \
-    static bool attr = false;                                                                                         \
+    static bool attr_dev[64] = {};                                                                                    \
+    bool& attr = attr_dev[sb::device_index()];                                                                        \
     if (!attr) {                                                                                                      \
       cudaFuncSetAttribute(sb::rmsnorm_bwd_warp_kernel<NVV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2048 * 4); \
       attr = true;                                                                                                    \

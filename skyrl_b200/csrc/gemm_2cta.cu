@@ -429,7 +429,9 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* bias,
   const CUtensorMap* ta = A_MN ? get_tmap_bf16_2d(A, K, M, lda, 64) : get_tmap_bf16_2d(A, M, K, lda, k2HalfM);
   const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN / 2);
   if (!ta || !tb) return SB_ERR_TMAP;
-  static bool attr_set = false;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
+  static bool attr_set_dev[64] = {};  // function attributes are per device
+  bool& attr_set = attr_set_dev[sb::device_index()];
   auto kfn = gemm2_bf16_kernel<BN, A_MN, B_MN>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)

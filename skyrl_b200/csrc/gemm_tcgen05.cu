@@ -529,7 +529,9 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   const CUtensorMap* ta = A_MN ? get_tmap_bf16_2d(A, K, M, lda, 64) : get_tmap_bf16_2d(A, M, K, lda, kBM);
   const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, K, N, ldb, 64) : get_tmap_bf16_2d(B, N, K, ldb, BN);
   if (!ta || !tb) return SB_ERR_TMAP;
-  static bool attr_set = false;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
+  static bool attr_set_dev[64] = {};  // function attributes are per device
+  bool& attr_set = attr_set_dev[sb::device_index()];
   auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
@@ -555,7 +557,9 @@ static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bia
   const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, static_cast<long long>(K) * b_groups, N, ldb, 64)
                                : get_tmap_bf16_2d(B, static_cast<long long>(N) * b_groups, K, ldb, BN);
   if (!ta || !tb) return SB_ERR_TMAP;
-  static bool attr_set = false;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
+  static bool attr_set_dev[64] = {};  // function attributes are per device
+  bool& attr_set = attr_set_dev[sb::device_index()];
   auto kfn = gemm_bf16_kernel<BN, false, B_MN, GATHER, SCATTER>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
@@ -602,7 +606,9 @@ static int launch_gemm_grouped(const void* A, const void* B, void* C, int M, int
     splits = n_groups;
   }
   if (!ta || !tb) return SB_ERR_TMAP;
-  static bool attr_set = false;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
+  static bool attr_set_dev[64] = {};  // function attributes are per device
+  bool& attr_set = attr_set_dev[sb::device_index()];
   auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)

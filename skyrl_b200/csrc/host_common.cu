@@ -121,6 +121,12 @@ int* device_status_ptr() {
   return ptrs[dev];
 }
 
+int device_index() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev < 0 ? 0 : (dev > 63 ? 63 : dev);
+}
+
 bool pdl_enabled() {
   static int v = -1;
   if (v < 0) {

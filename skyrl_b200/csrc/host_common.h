@@ -21,7 +21,8 @@ const CUtensorMap* get_tmap_bf16_2d(const void* ptr, uint64_t rows, uint64_t col
 const CUtensorMap* get_tmap_bf16_3d(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                                     uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2);
 
-int* device_status_ptr();  // per-device status word (device address)
+int* device_status_ptr();  // per-device status word (device address); nullptr when it cannot be resolved
+int device_index();        // current CUDA device clamped to [0, 63]: index of per-device "configured once" tables
 int sm_count();
 bool pdl_enabled();  // programmatic dependent launch of the decode-chain kernels (SB_PDL=0 turns it off)
 

@@ -294,7 +294,9 @@ int sb_lmhead_partials(const void* hidden, const void* W, const int* targets, vo
   const CUtensorMap* ta = sb::get_tmap_bf16_2d(hidden, T, K, ldh, sb::kLmBM);
   const CUtensorMap* tb = sb::get_tmap_bf16_2d(W, V, K, ldw, sb::kLmBN);
   if (!ta || !tb) return SB_ERR_TMAP;
-  static bool attr_set = false;
+  if (sb::device_status_ptr() == nullptr) return SB_ERR_CUDA;
+  static bool attr_set_dev[64] = {};  // function attributes are per device
+  bool& attr_set = attr_set_dev[sb::device_index()];
   if (!attr_set) {
     if (cudaFuncSetAttribute(sb::lmhead_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::kLmSmem) !=
         cudaSuccess)
@@ -344,6 +346,9 @@ int sb_lmhead_dlogits(void* logits, long long ld, int rows, int V, const int* ta
 // ---------------------------------------------------------------------------------------------------------
 #include "lmhead_noalloc.h"
 
+#include <atomic>
+#include <mutex>
+
 namespace sb {
 
 // Scratch for the per-(row, split) records of the no-alloc entry point: lives in the device image of
@@ -357,14 +362,18 @@ typedef CUresult (*NoAllocEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
 
 struct NoAllocDeviceState {
   float4* scratch = nullptr;
+  int* status = nullptr;
   bool ready = false;
+  std::mutex mu;  // serialises the one-time set-up of this device among host threads
 };
 static NoAllocDeviceState g_noalloc_state[64];
-static NoAllocEncodeFn g_noalloc_encode = nullptr;
+static std::atomic<NoAllocEncodeFn> g_noalloc_encode{nullptr};
 
 // Once per device, with that device current: resolve the scratch address and configure the kernel.
+// Safe to race from several host threads: the first one does the work under the device's mutex.
 static int noalloc_setup(int dev) {
   NoAllocDeviceState& st = g_noalloc_state[dev];
+  std::lock_guard<std::mutex> lock(st.mu);
   if (st.ready) return SB_OK;
   cudaFree(nullptr);  // bind the primary context to this thread (frees nothing, allocates nothing)
   float4* ptr = nullptr;
@@ -372,15 +381,18 @@ static int noalloc_setup(int dev) {
     return SB_ERR_CUDA;
   if (cudaFuncSetAttribute(lmhead_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLmSmem) != cudaSuccess)
     return SB_ERR_CUDA;
-  if (!g_noalloc_encode) {
+  int* status = device_status_ptr();
+  if (status == nullptr) return SB_ERR_CUDA;
+  if (!g_noalloc_encode.load()) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
         q != cudaDriverEntryPointSuccess || !fn)
       return SB_ERR_TMAP;
-    g_noalloc_encode = reinterpret_cast<NoAllocEncodeFn>(fn);
+    g_noalloc_encode.store(reinterpret_cast<NoAllocEncodeFn>(fn));
   }
   st.scratch = ptr;
+  st.status = status;
   st.ready = true;
   return SB_OK;
 }
@@ -393,7 +405,7 @@ static int noalloc_encode_2d(CUtensorMap* out, const void* ptr, uint64_t rows, u
   cuuint64_t strides[1] = {ld * 2};
   cuuint32_t box[2] = {64, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  const CUresult r = g_noalloc_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+  const CUresult r = g_noalloc_encode.load()(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                                       box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? SB_OK : SB_ERR_TMAP;
@@ -424,7 +436,7 @@ extern "C" int sb_lmhead_logprob_noalloc(const void* hidden, const void* W, cons
   const int grid = items < sb::sm_count() ? items : sb::sm_count();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   sb::lmhead_fwd_kernel<<<grid, sb::kLmThreads, sb::kLmSmem, st>>>(ta, tb, targets, scratch, T, V, K, splits, cps, 0,
-                                                                  inv_temp, sb::device_status_ptr());
+                                                                  inv_temp, sb::g_noalloc_state[dev].status);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_CUDA;
   sb::PartialSources src;
   for (int i = 0; i < 8; ++i) src.ptr[i] = i == 0 ? scratch : nullptr;

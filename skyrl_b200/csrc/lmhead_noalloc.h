@@ -25,7 +25,8 @@ extern "C" {
 // SB_ERR_ARG (1) for unsupported strides, SB_ERR_CUDA (2) / SB_ERR_TMAP (3) when a CUDA call fails.
 //
 // * The first call on each device resolves the scratch array's device address and sets the kernel's
-//   shared-memory attribute; make that first call outside of any stream capture.
+//   shared-memory attribute; make that first call outside of any stream capture.  That one-time set-up is
+//   guarded by a per-device mutex, so first calls may come from several host threads at once.
 // * All calls on a device share the one scratch array.  Two calls whose kernels overlap on the GPU (different
 //   streams, or different host threads) race on it; serialise them on one stream.
 // * Nothing in the scratch has to start at zero: each call overwrites every record it later reads, so stale

@@ -405,7 +405,8 @@ int sb_moe_plan(const void* ids, int ids_are_i64, int n, int E, int top_k, int m
   const size_t smem = sizeof(int) * (static_cast<size_t>(sb::kPlanWarps) * E + E + 1);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (ids_are_i64) {
-    static bool attr = false;
+    static bool attr_dev[64] = {};
+    bool& attr = attr_dev[sb::device_index()];
     if (!attr) {
       if (cudaFuncSetAttribute(sb::moe_plan_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, 140 * 1024) !=
           cudaSuccess)
@@ -415,7 +416,8 @@ int sb_moe_plan(const void* ids, int ids_are_i64, int n, int E, int top_k, int m
     sb::moe_plan_kernel<long long><<<1, sb::kPlanThreads, smem, st>>>(static_cast<const long long*>(ids), n, E, top_k, m_cap,
                                                                       k_off, tile_expert, row_src, slot_row);
   } else {
-    static bool attr = false;
+    static bool attr_dev[64] = {};
+    bool& attr = attr_dev[sb::device_index()];
     if (!attr) {
       if (cudaFuncSetAttribute(sb::moe_plan_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, 140 * 1024) != cudaSuccess)
         return SB_ERR_CUDA;

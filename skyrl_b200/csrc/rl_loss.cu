@@ -137,7 +137,9 @@ __global__ void group_advantage_kernel(const float* __restrict__ scores, const i
     }
 }
 
-// GAE: one thread per sequence, plain reverse scan over the R response positions of [B, R] tensors:
+// GAE: one thread per sequence, plain reverse scan over the R response positions of [B, R] tensors.  Like the
+// reference's scan (ppo_utils.py:1331-1336) it runs over every position, padded ones included (their rewards and
+// values are zero by construction); the response mask only enters the whitening that follows on the caller's side:
 //   delta_t = r_t + gamma * V_{t+1} - V_t ;  A_t = delta_t + gamma * lambda * A_{t+1} ;  ret_t = A_t + V_t
 __global__ void gae_kernel(const float* __restrict__ rewards, const float* __restrict__ values, int B, int R,
                            float gamma, float lam, float* __restrict__ adv, float* __restrict__ ret) {
@@ -183,7 +185,7 @@ int sb_group_advantage(const float* scores, const int* group_ids, int B, int num
 int sb_gae(const float* rewards, const float* values, const float* mask, int B, int R, float gamma, float lam,
            float* adv, float* ret, void* stream) {
   if (B <= 0 || R <= 0) return SB_OK;
-  (void)mask;
+  (void)mask;  // kept in the signature for callers that pass one; the scan itself is unmasked (see gae_kernel)
   sb::gae_kernel<<<(B + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(rewards, values, B, R, gamma, lam,
                                                                                       adv, ret);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;

@@ -99,14 +99,14 @@ class ShardedAdamW:
         optim_ops.sqnorm_accum(g, self._sq)
         if self.dup_ranges and not self.count_dups:
             dup = torch.zeros_like(self._sq)
-            for a, b in self.dup_ranges:  # intersect with this rank's optimizer shard
-                a2, b2 = max(a, self.lo) - self.lo, min(b, self.lo + self.shard) - self.lo
-                if b2 > a2:
-                    a4 = (a2 + 3) // 4 * 4  # the norm kernel reads 16-byte vectors
-                    if a4 > a2:
-                        dup += g[a2 : min(a4, b2)].float().pow(2).sum()
-                    if b2 > a4:
-                        optim_ops.sqnorm_accum(g[a4:b2], dup)
+            for r_lo, r_hi in self.dup_ranges:  # intersect with this rank's optimizer shard
+                s0, s1 = max(r_lo, self.lo) - self.lo, min(r_hi, self.lo + self.shard) - self.lo
+                if s1 > s0:
+                    s4 = (s0 + 3) // 4 * 4  # the norm kernel reads 16-byte vectors
+                    if s4 > s0:
+                        dup += g[s0 : min(s4, s1)].float().pow(2).sum()
+                    if s1 > s4:
+                        optim_ops.sqnorm_accum(g[s4:s1], dup)
             self._sq -= dup
         if self.world > 1:
             dist.all_reduce(self._sq, op=dist.ReduceOp.SUM, group=self.group)

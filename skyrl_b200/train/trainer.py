@@ -183,7 +183,7 @@ class PPOTrainer:
     def _old_logprobs_from_train_forward(self) -> bool:
         """True when pi_old == pi_theta at the only optimizer step of this RL step (and nothing else needs pi_old)."""
         t = self.cfg.trainer
-        single_update = (t.update_epochs_per_batch == 1 and t.train_batch_size == t.policy_mini_batch_size)
+        single_update = self.num_policy_updates_per_step() == 1
         a = t.algorithm
         return (t.b200.reuse_train_forward_for_old_logprobs and single_update and not a.use_kl_in_reward
                 and not rl.off_policy_correction_enabled_cfg(a) and a.policy_loss_type in ("regular", "dual_clip", "gspo",
@@ -274,25 +274,37 @@ class PPOTrainer:
             mean = (adv * mk).sum() / n
             var = (((adv - mean) ** 2) * mk).sum() / n
             adv = (adv - mean) * torch.rsqrt(var + 1e-8)
-        # token counts are global quantities: sum them across data-parallel ranks
-        W = self.env.world_size
+        # token counts are global quantities: sum them across the data-parallel ranks.  The ranks of one tensor /
+        # sequence / pipeline parallel group hold the same merged batch, so a sum over the world counts every batch
+        # ``tp`` times and the number of distinct data shards is ``world / tp``
+        W, tp = self.env.world_size, self._data_share()
         if a.loss_reduction == "token_mean":
-            tot = mk.sum()
+            tot = mk.sum().double().reshape(1)
             if dist.is_initialized() and W > 1:
-                tt = tot.to(self.env.device).clone()
-                dist.all_reduce(tt)
-                tot = tt.cpu()
-            mini["advantages"] = adv / tot.clamp(min=1)
+                dist.all_reduce(tot)  # host tensor: travels over the gloo side of the process group
+                tot = tot / tp
+            mini["advantages"] = adv / tot.float().clamp(min=1)
         else:
             scaled = rl.apply_loss_reduction_to_advantages_minibatch(
                 adv, mk, a.loss_reduction, t.micro_train_batch_size_per_gpu, a.max_seq_len or adv.shape[1], boundaries)
-            mini["advantages"] = scaled / W
+            mini["advantages"] = scaled / (W // tp)
         return mini
+
+    def _data_share(self) -> int:
+        """How many ranks train on the same data shard (the policy's tensor / sequence / pipeline group size)."""
+        return int(self.policy.tp_size) if self.policy is not None else 1
+
+    def num_policy_updates_per_step(self) -> int:
+        """Optimizer steps per RL step = mini-batches x epochs (reference: trainer.py:777-779)."""
+        t = self.cfg.trainer
+        return max(1, t.train_batch_size // max(1, t.policy_mini_batch_size)) * t.update_epochs_per_batch
 
     def _execute_training_step(self, role: str, batch: TrainingInputBatch) -> Dict[str, float]:
         t = self.cfg.trainer
         worker = self.policy if role == "policy" else self.critic
-        mini_prompts = (t.policy_mini_batch_size if role == "policy" else t.critic_mini_batch_size) // self.env.world_size
+        # this rank's batch holds train_batch_size / dp prompts, dp = number of distinct data shards
+        dp = max(1, self.env.world_size // self._data_share())
+        mini_prompts = (t.policy_mini_batch_size if role == "policy" else t.critic_mini_batch_size) // dp
         mini_prompts = max(1, mini_prompts)
         uids = batch.metadata["uids"]
         bounds = compute_prompt_mini_batch_boundaries(uids, mini_prompts)

@@ -60,13 +60,29 @@ def microbatch_indices(seq_lens: Sequence[int], micro_batch_size: int, max_token
     return [list(range(s, min(n, s + mbs))) for s in range(0, n, mbs)]
 
 
-def sync_num_microbatches(n_local: int, env: DistEnv) -> int:
-    """All ranks must run the same number of micro-batches (collectives inside the model); take the MAX."""
+def sync_num_microbatches(n_local: int, env: DistEnv, group=None) -> int:
+    """Ranks whose model forward contains collectives (one tensor / sequence / expert / pipeline group) must run the
+    same number of micro-batches: take the MAX over ``group``.  Reference: worker_utils.py:343-357, which pads over
+    the whole world because FSDP2 gathers parameters in every forward; here plain data-parallel ranks share nothing
+    until the optimizer step, so they are never padded (``group=None`` with no model-parallel mesh)."""
     if not dist.is_initialized() or env.world_size == 1:
         return n_local
     t = torch.tensor([n_local], device=env.device, dtype=torch.int64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return int(t.item())
+
+
+def materialize_metrics(metrics_list: List[Dict[str, Any]]) -> List[Dict[str, float]]:
+    """Per-micro-batch metric dicts may hold 0-dim device tensors; bring all of them to the host with ONE copy (one
+    device synchronisation per mini-batch instead of several per micro-batch)."""
+    slots = [(i, k) for i, m in enumerate(metrics_list) for k, v in m.items() if isinstance(v, torch.Tensor)]
+    if not slots:
+        return metrics_list
+    vals = _lib.to_host(torch.stack([metrics_list[i][k].detach().float().reshape(()) for i, k in slots])).tolist()
+    out = [dict(m) for m in metrics_list]
+    for (i, k), v in zip(slots, vals):
+        out[i][k] = float(v)
+    return out
 
 
 def reduce_metrics(metrics_list: List[Dict[str, float]]) -> Dict[str, float]:
@@ -110,6 +126,10 @@ def all_reduce_metrics(metrics: Dict[str, float], env: DistEnv) -> Dict[str, flo
         else:
             out[k] = float(sums[i]) / env.world_size
     return out
+
+
+class DeviceWaitError(RuntimeError):
+    """A kernel's bounded wait (mbarrier, peer flag, barrier epoch) ran out; see ``csrc/ptx.cuh`` for the codes."""
 
 
 # ----------------------------------------------------------------------------- worker
@@ -244,7 +264,10 @@ class ModelWorker:
             model.attach_main_grad(flat_grad)
             self.flat_grad = flat_grad
             extra = {}
-            if self.mesh is not None:
+            # sequence parallelism replicates every parameter and each rank of the group back-propagates only its
+            # token shard, so the gradient is complete only after a sum over *all* ranks: the optimizer then spans the
+            # world exactly as in plain data parallelism (fused peer transport included)
+            if self.mesh is not None and not self.sequence_parallel:
                 from ..models.tp_decoder import REPLICATED_LEAVES
 
                 if self.expert_parallel or self.pipe is not None:
@@ -262,6 +285,23 @@ class ModelWorker:
     # ------------------------------------------------------------------ helpers
     def _max_tokens(self) -> int:
         return int(self.cfg.max_tokens_per_microbatch or -1)
+
+    def _num_microbatches(self, n_local: int) -> int:
+        """Micro-batches this rank runs: its own count in plain data parallelism; the maximum over the model-parallel
+        group otherwise (its members hold the same batch, but expert-parallel members hold different ones)."""
+        if self.mesh is None:
+            return n_local
+        return sync_num_microbatches(n_local, self.env, group=self.mesh.tp_group)
+
+    def check_device_status(self, where: str) -> None:
+        """Raise when a bounded device-side wait gave up since the last check (a peer that never reached a barrier, a
+        copy that never landed).  Synchronises the device, so it is called where the host reads results anyway."""
+        if self.env.device.type != "cuda":
+            return
+        code = _lib.status_read_clear()
+        if code != 0:
+            raise DeviceWaitError(f"{self.role} worker, rank {self.env.rank}: a device-side wait timed out during {where} "
+                                  f"(status 0x{code:x}); the step's results are incomplete and nothing was published")
 
     def _seq_lens(self, batch: TrainingInputBatch) -> List[int]:
         return batch["attention_mask"].sum(1).tolist()
@@ -431,7 +471,7 @@ class ModelWorker:
         out = torch.zeros((B, R), dtype=torch.float32)
         groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_forward_batch_size_per_gpu, self._max_tokens(),
                                     getattr(self.cfg.b200, "microbatch_packing", "balanced"))
-        n_mb = sync_num_microbatches(len(groups), self.env)
+        n_mb = self._num_microbatches(len(groups))
         temp = float(self.cfg.algorithm.temperature or 1.0)
         was_ckpt = self.model.gradient_checkpointing
         self.model.gradient_checkpointing = False
@@ -493,6 +533,8 @@ class ModelWorker:
         if self.mesh is not None:
             self.model.reduce_replicated_grads()
         norm = self.optimizer.step(grad_scale=scale)
+        # the fused optimizer publishes nothing once the status word is set (csrc/comm.cu); tell the caller
+        self.check_device_status("optim_step")
         self.scheduler.step()
         self.optimizer.zero_grad()
         self.num_microbatches_accumulated = 0
@@ -629,7 +671,7 @@ class PolicyWorker(ModelWorker):
         B, R = batch["response_mask"].shape
         groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens(),
                                     getattr(self.cfg.b200, "microbatch_packing", "balanced"))
-        n_mb = sync_num_microbatches(len(groups), self.env)
+        n_mb = self._num_microbatches(len(groups))
         # number of distinct data shards (expert-parallel ranks each hold their own)
         world = self.mesh.dp_size if (self.mesh is not None and not self.expert_parallel) else self.env.world_size
         temp = float(algo.temperature or 1.0)
@@ -669,42 +711,42 @@ class PolicyWorker(ModelWorker):
                     if use_ent:
                         loss = loss - algo.entropy_loss_coef * weight * entropy_mean
                 st = stats.detach()
-                m.update(policy_loss=float(st[0]), policy_kl=float(st[2]) if use_kl else 0.0,
-                         **{"loss_metrics/clip_ratio": float(st[1] / st[3].clamp(min=1.0))})
+                m.update(policy_loss=st[0], policy_kl=st[2] if use_kl else 0.0,
+                         **{"loss_metrics/clip_ratio": st[1] / st[3].clamp(min=1.0)})
                 if entropy_mean is not None:
-                    m["policy_entropy"] = float(entropy_mean.detach())
+                    m["policy_entropy"] = entropy_mean.detach()
             else:
                 lp_grid = pv.scatter_to_grid(lp.float())
                 policy_loss, lm = loss_func(lp_grid, old_g, adv_g if adv_g is not None else torch.zeros_like(lp_grid),
                                             algo, loss_mask=mask_g, rollout_logprobs=roll_g)
                 loss = policy_loss
-                m["policy_loss"] = float(policy_loss.detach())
+                m["policy_loss"] = policy_loss.detach()
                 m.update({"loss_metrics/" + kk: float(vv) for kk, vv in lm.items()})
                 if loss_name != "cross_entropy":
                     if ent is not None:
                         ent_grid = pv.scatter_to_grid(ent.float())
                         entropy_mean = masked_mean(ent_grid, mask_g)
-                        m["policy_entropy"] = float(entropy_mean.detach())
+                        m["policy_entropy"] = entropy_mean.detach()
                         if use_ent:
                             loss = loss - algo.entropy_loss_coef * weight * entropy_mean
                     if use_kl:
                         kl = rl.compute_approx_kl(lp_grid, ref_g, loss_mask=mask_g, kl_estimator_type=algo.kl_estimator_type)
                         kl_mean = masked_mean(kl, mask_g, dim=-1).mean()
                         loss = loss + algo.kl_loss_coef * weight * kl_mean
-                        m["policy_kl"] = float(kl_mean.detach())
+                        m["policy_kl"] = kl_mean.detach()
                 if per_row_logprobs is not None and real:
                     per_row_logprobs[torch.tensor(rows, dtype=torch.long)] = lp_grid.detach().cpu()
             if not real:
                 loss = loss * 0.0
             loss.backward()
             if real:
-                m["final_loss"] = float(loss.detach())
+                m["final_loss"] = loss.detach()
                 if roll_g is not None:
                     d = (pv.scatter_to_grid(lp.detach().float()) - roll_g).abs()
-                    m["rollout_train_logprobs_abs_diff_mean"] = float(masked_mean(d, mask_g))
+                    m["rollout_train_logprobs_abs_diff_mean"] = masked_mean(d, mask_g)
                 all_metrics.append(m)
             self.num_microbatches_accumulated += 1
-        status = reduce_metrics(all_metrics)
+        status = reduce_metrics(materialize_metrics(all_metrics))
         status = all_reduce_metrics(status, self.env)
         status["policy_lr"] = self.optimizer.lr
         status["response_length"] = R
@@ -737,7 +779,7 @@ class CriticWorker(ModelWorker):
         B, R = batch["response_mask"].shape
         groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_train_batch_size_per_gpu, self._max_tokens(),
                                     getattr(self.cfg.b200, "microbatch_packing", "balanced"))
-        n_mb = sync_num_microbatches(len(groups), self.env)
+        n_mb = self._num_microbatches(len(groups))
         all_metrics = []
         for k in range(n_mb):
             real = k < len(groups)
@@ -753,10 +795,10 @@ class CriticWorker(ModelWorker):
             (loss / max(1, self.env.world_size)).backward()
             if real:
                 mk = g("loss_mask")
-                all_metrics.append({"critic_loss": float(loss.detach()), "values_mean": float(masked_mean(v_grid.detach(), mk)),
+                all_metrics.append({"critic_loss": loss.detach(), "values_mean": masked_mean(v_grid.detach(), mk),
                                     "values_clipfrac": float(clipfrac or 0.0)})
             self.num_microbatches_accumulated += 1
-        st = reduce_metrics(all_metrics)
+        st = reduce_metrics(materialize_metrics(all_metrics))
         if "critic_loss" in st and all_metrics:
             st["critic_loss"] = st["critic_loss"] / len(all_metrics)
         st = all_reduce_metrics(st, self.env)

@@ -263,24 +263,3 @@ def test_qkv_finalize_matches_unfused_rope_and_cache_write():
     assert ((kc.float() - kc2.float()).norm() / kc2.float().norm()).item() < 3e-3
     assert ((vc.float() - vc2.float()).norm() / vc2.float().norm()).item() < 3e-3
     assert kc.view(-1, nkv * D)[slots[6].item()].abs().sum() > 0
-
-
-def test_membench_streams_complete_without_timeouts():
-    """The read-stream micro-benchmark kernels (bounded mbarrier waits) finish cleanly in every mode."""
-    import ctypes
-
-    lib = _lib.kernels()
-    vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
-    lib.sb_membench_tma_stream.argtypes = [vp, cl, ci, ci, ci, ci, ci, ci, vp]
-    lib.sb_membench_ld_stream.argtypes = [vp, cl, ci, vp, vp]
-    nbytes = 64 << 20
-    buf = torch.randn(nbytes // 2, device="cuda").to(torch.bfloat16)
-    sink = torch.zeros(4, device="cuda", dtype=torch.int32)
-    for stages, ctas, box_rows, cols, lanes, walk in ((3, 1, 256, 1, 0, 0), (6, 1, 32, 4, 1, 0), (2, 2, 128, 128, 0, 1)):
-        assert lib.sb_membench_tma_stream(buf.data_ptr(), nbytes, stages, ctas, box_rows, cols, lanes, walk, _lib.stream_ptr()) == 0
-    assert lib.sb_membench_ld_stream(buf.data_ptr(), nbytes, 4, sink.data_ptr(), _lib.stream_ptr()) == 0
-    torch.cuda.synchronize()
-    assert _lib.status_read_clear() == 0
-    # argument checks: sizes that are not whole stages, too many stages for shared memory
-    assert lib.sb_membench_tma_stream(buf.data_ptr(), nbytes + 128, 3, 1, 256, 1, 0, 0, _lib.stream_ptr()) != 0
-    assert lib.sb_membench_tma_stream(buf.data_ptr(), nbytes, 7, 2, 256, 1, 0, 0, _lib.stream_ptr()) != 0

@@ -46,3 +46,14 @@ def test_gloo_two_rank_pipeline_parallel_rl_step():
     p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-llama",
               "--prompts-per-gpu", "1", "--pp", "2"], port=29636)
     assert p.returncode == 0 and "x pp2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("mode,port", [("tp", 29641), ("sp", 29642), ("ep", 29643), ("pp", 29644)])
+def test_gloo_worker_update_matches_single_rank(mode, port):
+    """forward_backward + optim_step through the worker under each model-parallel strategy: full parameters equal a
+    single-rank update on the same data, group replicas are bit-identical, one optimizer step per RL step."""
+    p = _run([os.path.join(ROOT, "tests", "mp", "worker_parity.py"), mode], port=port)
+    assert p.returncode == 0 and f"WORKER_PARITY_OK mode={mode}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
