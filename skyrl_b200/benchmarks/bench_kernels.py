@@ -37,8 +37,101 @@ def timeit(fn, iters, warmup=3):
     return tot / iters
 
 
+def load_reference_module(rel_path: str, name: str):
+    """Import one file of the unmodified reference install under ``baseline/_ref`` by path (no package import, so
+    none of the reference's heavier dependencies is pulled in)."""
+    import importlib.util
+    import os
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "baseline", "_ref", rel_path)
+    if not os.path.exists(path):
+        raise FileNotFoundError(f"{path}: install the reference into baseline/_ref first")
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _bench_lmhead(a) -> dict:
+    """Fused LM-head log-probability, forward and forward+backward, at ``--tokens`` x ``--vocab`` x ``--hidden-lm``.
+
+    ``--impl ours``: ``ops.lm_head.lm_head_logprobs`` (tcgen05 main loop, online-softmax epilogue, no logits).
+    ``--impl reference``: the reference's own kernels on the same tensors, loaded unmodified from ``baseline/_ref``:
+    its vendored Triton fused LM-head (``FusedLinearLogprobTriton``, the path ``fused_lm_head_logprob`` enables) and
+    its materialised-logits path (``logits = h @ W^T`` -> ``logprobs_from_logits`` + ``chunked_entropy_from_logits``,
+    the FSDP default).  ``--impl both`` runs all three back to back in one process and prints the ratios.
+    """
+    T, V, H = a.tokens, a.vocab, a.hidden_lm
+    g = torch.Generator(device="cuda").manual_seed(0)
+    h = (torch.randn(T, H, device="cuda", generator=g) * 0.5).to(torch.bfloat16).requires_grad_()
+    W = (torch.randn(V, H, device="cuda", generator=g) * 0.02).to(torch.bfloat16).requires_grad_()
+    tgt = torch.randint(0, V, (T,), device="cuda", generator=g)
+    gout = torch.randn(T, device="cuda", generator=g)
+    fl = 2.0 * T * V * H
+    res = {"tokens": T, "vocab": V, "hidden": H, "impl": a.impl}
+
+    def fwd_bwd(fn):
+        def run():
+            h.grad = W.grad = None
+            lp = fn(h, W)
+            lp.backward(gout)
+        return run
+
+    def record(tag, fn, check_against=None):
+        with torch.no_grad():
+            ms_f = timeit(lambda: fn(h, W), a.iters)
+        ms_fb = timeit(fwd_bwd(fn), a.iters)
+        row = {"fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9, "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3 * fl / ms_fb / 1e9,
+               "fwd_fraction_of_measured_bf16_burst": fl / ms_f / 1e9 / a.peak_tflops}
+        with torch.no_grad():
+            lp = fn(h, W).float()
+        if check_against is not None:
+            row["max_abs_diff_vs_ours"] = (lp - check_against).abs().max().item()
+        res[tag] = row
+        return lp
+
+    ours_lp = None
+    if a.impl in ("ours", "both"):
+        ours_lp = record("ours", lambda hh, ww: lm_head.lm_head_logprobs(hh, ww, tgt, 1.0)[0])
+    if a.impl in ("reference", "both"):
+        ref_fused = load_reference_module("skyrl/backends/skyrl_train/distributed/megatron/fused_linear_logprob_triton.py",
+                                          "ref_fused_linear_logprob_triton")
+        ref_tu = load_reference_module("skyrl/backends/skyrl_train/utils/torch_utils.py", "ref_torch_utils")
+        t2 = tgt.view(1, T)
+
+        def ref_triton(hh, ww):
+            return ref_fused.FusedLinearLogprobTriton.apply(hh.view(1, T, H), ww, t2, 0, V, 1024, None, False).view(T)
+
+        def ref_logits(hh, ww):
+            logits = (hh @ ww.t()).view(1, T, V)
+            lp = ref_tu.logprobs_from_logits(logits, t2, inplace_backward=True)
+            return lp.view(T)
+
+        record("reference_triton_fused", ref_triton, ours_lp)
+        if T * V * 2 <= 24 << 30:  # the materialised path needs T x V bf16 logits (+ the same again in backward)
+            record("reference_materialised_logits", ref_logits, ours_lp)
+            with torch.no_grad():
+                logits = (h @ W.t()).view(1, T, V)
+                res["reference_chunked_entropy_ms"] = timeit(lambda: ref_tu.chunked_entropy_from_logits(logits), a.iters)
+                del logits
+        else:
+            res["reference_materialised_logits"] = {"skipped": "logits would not fit the bound set for this benchmark"}
+    if a.impl == "both":
+        for tag in ("reference_triton_fused", "reference_materialised_logits"):
+            if "fwd_ms" in res.get(tag, {}):
+                res[tag]["fwd_speedup_ours"] = res[tag]["fwd_ms"] / res["ours"]["fwd_ms"]
+                res[tag]["fwd_bwd_speedup_ours"] = res[tag]["fwd_bwd_ms"] / res["ours"]["fwd_bwd_ms"]
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "both"], help="lmhead: which implementation to time")
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--hidden-lm", type=int, default=1536)
     ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "elementwise"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
@@ -206,13 +299,7 @@ def main() -> None:
                    gate_up_ms=ms_gu, gate_up_tflops=fl_gu / ms_gu / 1e9, down_ms=ms_dn, down_tflops=fl_dn / ms_dn / 1e9,
                    layer_tflops=(fl_gu + fl_dn) / ms_layer / 1e9)
     else:
-        V, H = 151936, 1536
-        h = (torch.randn(a.tokens, H, device="cuda") * 0.5).to(torch.bfloat16)
-        W = (torch.randn(V, H, device="cuda") * 0.02).to(torch.bfloat16)
-        tgt = torch.randint(0, V, (a.tokens,), device="cuda")
-        ms = timeit(lambda: lm_head.lm_head_logprobs(h, W, tgt, 1.0), a.iters)
-        fl = 2.0 * a.tokens * V * H
-        out.update(tokens=a.tokens, ms=ms, tflops=fl / ms / 1e9, fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
+        out.update(_bench_lmhead(a))
     print(json.dumps(out))
 
 

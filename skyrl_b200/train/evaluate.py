@@ -48,6 +48,17 @@ async def evaluate(eval_dataset, generator, cfg, global_step: int, tokenizer=Non
             for p, r, rew, stop in zip(out["prompt_token_ids"], out["response_ids"], out["rewards"], out["stop_reasons"]):
                 dumps.append({"prompt": tokenizer.decode(p), "response": tokenizer.decode(r),
                               "reward": float(np.sum(rew)), "stop_reason": stop})
+    if env is not None and env.world_size > 1:
+        # every rank evaluated its own slice of the set: merge the slices so that the metrics cover the whole set
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            parts = [None] * env.world_size
+            dist.all_gather_object(parts, (all_rewards, all_uids, all_src, dumps))
+            all_rewards = [x for p in parts for x in p[0]]
+            all_uids = [x for p in parts for x in p[1]]
+            all_src = [x for p in parts for x in p[2]]
+            dumps = [x for p in parts for x in p[3]]
     out_all = {"rewards": all_rewards}
     mm = get_metrics_from_generator_output(out_all, all_uids)
     metrics = {"eval/all/avg_score": mm["avg_score"], f"eval/all/pass_at_{g.eval_n_samples_per_prompt}": mm["pass_at_n"],

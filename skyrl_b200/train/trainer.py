@@ -64,6 +64,7 @@ class PPOTrainer:
         self.kl_controller = rl.get_kl_controller(cfg.trainer.algorithm) if cfg.trainer.algorithm.use_kl_in_reward else None
         self.train_iter: Optional[StatefulBatchIterator] = None
         self.callbacks: List[Any] = []
+        self.dynamic_sampler = None
         tutils.validate_cfg(cfg, self.env.world_size)
         torch.manual_seed(cfg.trainer.seed + self.env.rank)
         np.random.seed(cfg.trainer.seed + self.env.rank)
@@ -175,10 +176,58 @@ class PPOTrainer:
         self.all_metrics["generate/avg_response_length"] = batch.metadata["avg_response_length"]
         return batch
 
+    def handle_dynamic_sampling(self, out: GeneratorOutput, uids: List[str]):
+        """DAPO ``filter`` / POLARIS ``replace`` (reference: trainer.py:1584-1644). Returns
+        ``(output, uids, keep_sampling)``; with ``keep_sampling`` the caller rolls out the next prompt batch."""
+        ds = self.cfg.trainer.algorithm.dynamic_sampling
+        if self.dynamic_sampler is None:
+            from .dynamic_sampling import DynamicSampler
+
+            W = self.env.world_size
+
+            def all_done(done: bool) -> bool:
+                if not dist.is_initialized() or W == 1:
+                    return done
+                t = torch.tensor([1 if done else 0], dtype=torch.int32)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)  # host tensor: gloo side of the process group
+                return bool(t.item())
+
+            share = max(1, self.cfg.trainer.train_batch_size * self._data_share() // W)
+            self.dynamic_sampler = DynamicSampler(ds.type, share, self.cfg.generator.n_samples_per_prompt,
+                                                  ds.max_sample_batches, ds.min_replace_ratio,
+                                                  seed=self.cfg.trainer.seed + self.env.rank, all_ranks_done=all_done)
+        res = self.dynamic_sampler.handle(out, uids)
+        self.all_metrics.update(self.dynamic_sampler.metrics())
+        return res
+
     # ------------------------------------------------------------------ forward passes
     def _skip_policy_forward(self) -> bool:
+        """The old-policy forward can be skipped when the loss is anchored on the rollout log-probs and nothing else
+        reads the old ones (reference: trainer.py:1279-1304; ``cispo`` qualifies only with the rollout anchor)."""
         a = self.cfg.trainer.algorithm
-        return a.policy_loss_type in rl.LOSSES_WITHOUT_OLD_LOGPROBS and not rl.off_policy_correction_enabled_cfg(a)
+        if a.policy_loss_type == "cispo":
+            anchored = a.cispo.cispo_anchor == "rollout"
+        else:
+            anchored = a.policy_loss_type in rl.LOSSES_WITHOUT_OLD_LOGPROBS
+        return anchored and not a.use_kl_in_reward and not rl.off_policy_correction_enabled_cfg(a)
+
+    def _forward_old(self, worker, role: str, batch: TrainingInputBatch) -> torch.Tensor:
+        """Forward pass that produces "old" log-probs / values.  With ``recompute_old_logprobs_per_minibatch`` it runs
+        mini-batch by mini-batch with the training packing, so the ratio is exactly 1 at the first inner step."""
+        t = self.cfg.trainer
+        if not t.recompute_old_logprobs_per_minibatch:
+            return worker.forward(batch)["output"]
+        dp = max(1, self.env.world_size // self._data_share())
+        size = t.critic_mini_batch_size if role == "critic" else t.policy_mini_batch_size
+        bounds = compute_prompt_mini_batch_boundaries(batch.metadata["uids"], max(1, size // dp))
+        if len(bounds) <= 1 and t.micro_train_batch_size_per_gpu == t.micro_forward_batch_size_per_gpu:
+            return worker.forward(batch, train_packing=True)["output"]
+        parts = []
+        for s, e in bounds:
+            mini = batch.slice(s, e)
+            mini.metadata = dict(batch.metadata)
+            parts.append(worker.forward(mini, train_packing=True)["output"])
+        return torch.cat(parts, 0)
 
     def _old_logprobs_from_train_forward(self) -> bool:
         """True when pi_old == pi_theta at the only optimizer step of this RL step (and nothing else needs pi_old)."""
@@ -191,16 +240,16 @@ class PPOTrainer:
 
     def fwd_logprobs_values_reward(self, batch: TrainingInputBatch) -> TrainingInputBatch:
         if self.critic is not None:
-            batch["values"] = self.critic.forward(batch)["output"]
+            batch["values"] = self._forward_old(self.critic, "critic", batch)
         if self.ref is not None:
-            batch["base_action_log_probs"] = self.ref.forward(batch)["output"]
+            batch["base_action_log_probs"] = self._forward_old(self.ref, "ref", batch)
         if self._skip_policy_forward() and batch.get("rollout_logprobs") is not None:
             batch["action_log_probs"] = batch["rollout_logprobs"].clone()
         elif self._old_logprobs_from_train_forward():
             batch["action_log_probs"] = None  # filled by the worker from its own forward (identical weights)
             return batch
         else:
-            batch["action_log_probs"] = self.policy.forward(batch)["output"]
+            batch["action_log_probs"] = self._forward_old(self.policy, "policy", batch)
         if batch.get("rollout_logprobs") is not None:
             d = (batch["action_log_probs"] - batch["rollout_logprobs"]).abs()
             mk = batch["loss_mask"]
@@ -403,6 +452,13 @@ class PPOTrainer:
             out, uids = self._gather_over_tp(out, uids)
         if out.get("trajectory_ids") and len(out["response_ids"]) != len(uids):
             uids = [t.instance_id for t in out["trajectory_ids"]]  # step-wise outputs have one row per step
+        if cfg.trainer.algorithm.dynamic_sampling.type is not None:
+            out, uids, keep_sampling = self.handle_dynamic_sampling(out, uids)
+            if keep_sampling:  # not enough informative prompt groups yet: the caller supplies the next prompt batch
+                m = dict(self.all_metrics)
+                m.update({f"timing/{k}": v for k, v in self.all_timings.items()})
+                m["trainer/keep_sampling"] = 1.0
+                return m
         with Timer("postprocess", self.all_timings):
             out = self.postprocess_generator_output(out, uids)
             batch = self.convert_to_training_input(out, uids)
@@ -457,6 +513,8 @@ class PPOTrainer:
         while self.train_iter.epoch < t.epochs and not done:
             for global_batch in self.train_iter:
                 metrics = await self.train_step_async(self._local_prompts(global_batch))
+                if metrics.get("trainer/keep_sampling"):
+                    continue  # dynamic sampling wants more rollouts before this RL step can train
                 if t.eval_interval > 0 and self.eval_dataset is not None and self.global_step % t.eval_interval == 0:
                     metrics.update(await self.eval_async())
                 self._log(metrics, self.global_step)

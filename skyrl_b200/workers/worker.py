@@ -464,12 +464,17 @@ class ModelWorker:
 
     # ------------------------------------------------------------------ forward (no grad)
     @torch.no_grad()
-    def forward(self, batch: TrainingInputBatch) -> TrainingOutputBatch:
-        """Log-probabilities (policy/ref) or values (critic) on the right-aligned response grid ``[B, R]``."""
+    def forward(self, batch: TrainingInputBatch, train_packing: bool = False) -> TrainingOutputBatch:
+        """Log-probabilities (policy/ref) or values (critic) on the right-aligned response grid ``[B, R]``.
+
+        ``train_packing`` groups the rows exactly as ``forward_backward`` will (``micro_train_batch_size_per_gpu``), so
+        that the values a later training pass recomputes for the same mini-batch come from identically packed
+        micro-batches (``trainer.recompute_old_logprobs_per_minibatch``, reference: trainer.py:1244-1277)."""
         self.backload()
         B, R = batch["response_mask"].shape
         out = torch.zeros((B, R), dtype=torch.float32)
-        groups = microbatch_indices(self._seq_lens(batch), self.cfg.micro_forward_batch_size_per_gpu, self._max_tokens(),
+        mbs = self.cfg.micro_train_batch_size_per_gpu if train_packing else self.cfg.micro_forward_batch_size_per_gpu
+        groups = microbatch_indices(self._seq_lens(batch), mbs, self._max_tokens(),
                                     getattr(self.cfg.b200, "microbatch_packing", "balanced"))
         n_mb = self._num_microbatches(len(groups))
         temp = float(self.cfg.algorithm.temperature or 1.0)

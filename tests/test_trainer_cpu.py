@@ -81,3 +81,31 @@ def test_ppo_with_critic_gae(tmp_path):
     tr.build_models()
     m = tr.train_step(_prompts())
     assert "critic/critic_loss" in m and m["critic/grad_norm"] > 0 and m["policy/grad_norm"] > 0
+
+
+def test_two_minibatches_recompute_old_logprobs_with_train_packing(tmp_path):
+    """train_batch 8 / mini-batch 4: two optimizer steps; the old log-probs are computed mini-batch by mini-batch with
+    the training micro-batch size, so the first update of the step sees ratio == 1 exactly (nothing clipped)."""
+    pdist.reset_env_for_tests()
+    cfg = _cfg(tmp_path, ["trainer.policy_mini_batch_size=4", "trainer.micro_train_batch_size_per_gpu=2",
+                          "trainer.micro_forward_batch_size_per_gpu=16", "trainer.recompute_old_logprobs_per_minibatch=true",
+                          "trainer.algorithm.use_kl_loss=false"])
+    tr = PPOTrainer(cfg, tokenizer=SyntheticTokenizer(1024))
+    tr.build_models()
+    seen = []
+    orig = tr.policy.forward_backward
+
+    def spy(mini, **kw):
+        st = orig(mini, **kw)
+        seen.append((mini.batch_size, st["loss_metrics/clip_ratio"]))
+        return st
+
+    tr.policy.forward_backward = spy
+    tr.train_step(_prompts())
+    assert tr.policy.optimizer.step_count == 2 and [b for b, _ in seen] == [16, 16]
+    assert seen[0][1] == 0.0
+    # same values as one full-batch forward (fp32 on CPU: packing changes nothing beyond rounding)
+    b = tr._last_batch
+    full = tr.policy.forward(b)["output"]
+    per_mb = tr._forward_old(tr.policy, "policy", b)
+    assert torch.allclose(full, per_mb, atol=1e-5)
