@@ -48,6 +48,33 @@ __global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int world, int chan
   }
 }
 
+// Same barrier for launch sequences that are replayed from a CUDA graph: the epoch cannot be a kernel argument there
+// (it would be frozen at capture time), so it lives in device memory and every launch advances it by one.  All ranks
+// run the same launch sequence, so their counters stay equal without any exchange.
+__global__ void peer_barrier_counter_kernel(PeerPtrs pads, int rank, int world, int channel, int* epoch_counter,
+                                            unsigned long long wait_ns, int* status) {
+  __shared__ int epoch_s;
+  if (threadIdx.x == 0) {
+    epoch_s = *epoch_counter + 1;
+    *epoch_counter = epoch_s;
+  }
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  const int epoch = epoch_s;
+  __threadfence_system();
+  st_release_sys(static_cast<int*>(pads.p[t]) + channel * kMaxPeers + rank, epoch);
+  const int* mine = static_cast<const int*>(pads.p[rank]) + channel * kMaxPeers + t;
+  const unsigned long long t0 = globaltimer_ns();
+  while (ld_acquire_sys(mine) < epoch) {
+    if (globaltimer_ns() - t0 > wait_ns) {
+      atomicCAS(status, 0, 0x910 | t);
+      return;
+    }
+    __nanosleep(32);
+  }
+}
+
 // out[i] = sum_r grads[r][lo + i]; sq_partial += sum(out^2). All ranks' grads must be complete (barrier before).
 __global__ void peer_reduce_scatter_kernel(PeerPtrs grads, int world, long long lo, long long n,
                                            float* __restrict__ out, float* __restrict__ sq_partial) {
@@ -246,6 +273,16 @@ int sb_peer_barrier(void* const* pads, int rank, int world, int channel, int epo
   if (st == nullptr) return SB_ERR_CUDA;
   sb::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       sb::make_ptrs(pads, world), rank, world, channel, epoch, wait_ns, st);
+  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+}
+
+int sb_peer_barrier_counter(void* const* pads, int rank, int world, int channel, int* epoch_counter,
+                            unsigned long long wait_ns, void* stream) {
+  if (world < 1 || world > sb::kMaxPeers || channel < 0 || channel >= 8 || !epoch_counter) return SB_ERR_ARG;
+  int* st = sb::device_status_ptr();
+  if (st == nullptr) return SB_ERR_CUDA;
+  sb::peer_barrier_counter_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      sb::make_ptrs(pads, world), rank, world, channel, epoch_counter, wait_ns, st);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -274,7 +274,8 @@ class LLMEngine:
                                 a.head_dim)
         att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], self.block_tables[:n], self.ctx_lens[:n],
                                          a.num_heads, a.num_kv_heads, a.head_dim, max_ctx=self.cfg.max_model_len)
-        o = gemm.gemm_nt(att, m.p(pre + "wo"))
+        tp = self.tp_size > 1
+        o = m.row_parallel_linear(att, m.p(pre + "wo"), "prefill_o", 4) if tp else gemm.gemm_nt(att, m.p(pre + "wo"))
         x, h = ew.add_rmsnorm(x, o, m.p(pre + "ln2"), a.rms_norm_eps)
         if a.num_experts:
             from ..models.moe import moe_ffn
@@ -282,8 +283,8 @@ class LLMEngine:
             d = moe_ffn(h, m.p(pre + "router"), m.p(pre + "experts_wgu"), m.p(pre + "experts_wd"),
                         a.num_experts_per_tok, a.norm_topk_prob, layer=i)
         else:
-            gu = gemm.gemm_nt(h, m.p(pre + "wgu"))
-            d = gemm.gemm_nt(ew.swiglu(gu), m.p(pre + "wd"))
+            act = ew.swiglu(gemm.gemm_nt(h, m.p(pre + "wgu")))
+            d = m.row_parallel_linear(act, m.p(pre + "wd"), "prefill_d", 5) if tp else gemm.gemm_nt(act, m.p(pre + "wd"))
         return x, d
 
     def _splitk_linear(self, h, w, bias, n):
@@ -328,9 +329,55 @@ class LLMEngine:
         self._advance(n)
 
     @torch.no_grad()
+    def _decode_once_fused_tp(self, n: int, masked: bool) -> None:
+        """Decode step of a tensor-parallel engine (``engine/tp_model.py``): the QKV and gate/up projections are
+        column-parallel (local heads / local FFN columns, no communication); the o-proj and down-proj GEMMs store their
+        partial tiles into every rank's slot buffer from the epilogue, and after a device-side barrier the fused
+        residual-add + RMSNorm kernel sums the ``tp`` slots -- the all-reduce has no kernel of its own."""
+        from .tp_model import DECODE_CHANNELS
+
+        m, a = self.model, self.model.args
+        tp = m.tp.size
+        x = sampling.embed(m.p("embed"), self.cur_tokens[:n])
+        table = m.rope_table(self.device)
+        qkv = torch.empty((n, (a.num_heads + 2 * a.num_kv_heads) * a.head_dim), device=self.device, dtype=x.dtype)
+        pending = None
+        fused_mlp = a.intermediate_size % 128 == 0 and n >= 32 and os.environ.get("SB_DECODE_FUSED_MLP", "1") != "0"
+        for i in range(a.num_layers):
+            pre = f"layers.{i}."
+            if pending is None:
+                _, h = ew.add_rmsnorm(x, None, m.p(pre + "ln1"), a.rms_norm_eps)
+            else:
+                h = ew.add_rmsnorm_partials_(x, pending, tp, m.p(pre + "ln1"), a.rms_norm_eps)
+            part, np_ = self._splitk_linear(h, m.p(pre + "wqkv"), m._p.get(pre + "bqkv"), n)
+            ew.qkv_finalize(part, np_, self.positions[:n], table, qkv, self.k_cache[i], self.v_cache[i], self.slots[:n],
+                            a.num_heads, a.num_kv_heads, a.head_dim)
+            att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], self.block_tables[:n],
+                                             self.ctx_lens[:n], a.num_heads, a.num_kv_heads, a.head_dim,
+                                             max_ctx=self.cfg.max_model_len)
+            parts_o = m.row_parallel_partials(att, m.p(pre + "wo"), "decode_o", torch.float32, DECODE_CHANNELS[0], True)
+            h = ew.add_rmsnorm_partials_(x, parts_o, tp, m.p(pre + "ln2"), a.rms_norm_eps)
+            if fused_mlp:
+                act = gemm.gate_up_swiglu(h, m.p(pre + "wgu"), need_gu=False)[1]
+            else:
+                act = ew.swiglu(gemm.gemm_nt(h, m.p(pre + "wgu"), static_w=True))
+            pending = m.row_parallel_partials(act, m.p(pre + "wd"), "decode_d", torch.float32, DECODE_CHANNELS[1], True)
+        h = ew.add_rmsnorm_partials_(x, pending, tp, m.p("final_norm"), a.rms_norm_eps)
+        logits = gemm.gemm_nt(h, m.lm_head_weight(), static_w=True)
+        self._sample(logits, n, masked)
+        self._advance(n)
+
+    @property
+    def tp_size(self) -> int:
+        tp = getattr(self.model, "tp", None)
+        return tp.size if (tp is not None and hasattr(self.model, "row_parallel_linear")) else 1
+
+    @torch.no_grad()
     def _decode_once(self, n: int, masked: bool) -> None:
         m, a = self.model, self.model.args
-        if self.is_cuda and self.cfg.fused_decode and not a.num_experts and not a.qk_norm:
+        if self.is_cuda and self.tp_size > 1 and m.tp.fused and not a.num_experts and not a.qk_norm:
+            return self._decode_once_fused_tp(n, masked)
+        if self.is_cuda and self.cfg.fused_decode and not a.num_experts and not a.qk_norm and self.tp_size == 1:
             return self._decode_once_fused(n, masked)
         x = sampling.embed(m.p("embed"), self.cur_tokens[:n])
         delta = None

@@ -33,6 +33,7 @@ def _k():
         lib.sb_ipc_open_handle.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
         lib.sb_ipc_close_handle.argtypes = [vp]
         lib.sb_peer_barrier.argtypes = [vp, ci, ci, ci, ci, u64, vp]
+        lib.sb_peer_barrier_counter.argtypes = [vp, ci, ci, ci, vp, u64, vp]
         lib.sb_peer_reduce_scatter_f32.argtypes = [vp, ci, cl, cl, vp, vp, vp]
         lib.sb_peer_publish_scalar.argtypes = [vp, ci, ci, vp, vp]
         lib.sb_peer_adamw_push.argtypes = [vp, vp, vp, vp, vp, ci, cl, cl, cf, cf, cf, cf, cf, cf, cf, vp, cf, cf, vp, vp, vp]
@@ -109,6 +110,15 @@ class PeerContext:
         self._epoch[channel] += 1
         _lib.check(_k().sb_peer_barrier(self.signal.ptr_array(), self.rank, self.world, channel, self._epoch[channel],
                                         self.wait_ns, _lib.stream_ptr()), "sb_peer_barrier")
+
+    def barrier_replayable(self, channel: int) -> None:
+        """Device-side barrier whose epoch is kept in device memory, so the launch can be captured in a CUDA graph and
+        replayed.  A channel must be used either with this method or with ``barrier``, never with both."""
+        if getattr(self, "_epoch_dev", None) is None:
+            self._epoch_dev = torch.zeros(8, device=self.device, dtype=torch.int32)
+        _lib.check(_k().sb_peer_barrier_counter(self.signal.ptr_array(), self.rank, self.world, channel,
+                                                self._epoch_dev[channel:].data_ptr(), self.wait_ns, _lib.stream_ptr()),
+                   "sb_peer_barrier_counter")
 
     # ------------------------------------------------------------------ fused optimizer pieces
     def reduce_scatter_and_norm(self, grads: SymmTensor, out_shard: torch.Tensor, lo: int, n: int) -> None:
