@@ -96,6 +96,8 @@ def main() -> None:
     ap.add_argument("--ep", type=int, default=1, help="expert-parallel size (MoE models)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size of the training model")
     ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size of the training model")
+    ap.add_argument("--engine-tp", type=int, default=1, help="tensor-parallel size of each rollout engine (lock-step ranks, "
+                    "all-reduce in the o-proj / down-proj GEMM epilogues)")
     ap.add_argument("--reuse-train-forward", action="store_true",
                     help="take old log-probs from the training forward (exact with one optimizer update per step); "
                          "off by default so the step runs the same separate old-policy forward the reference does")
@@ -138,6 +140,7 @@ def main() -> None:
           if args.pp > 1 else []),
         *([f"trainer.policy.sequence_parallel_size={args.sp}", f"trainer.ref.sequence_parallel_size={args.sp}"]
           if args.sp > 1 else []),
+        *([f"generator.inference_engine.tensor_parallel_size={args.engine_tp}"] if args.engine_tp > 1 else []),
         f"trainer.b200.reuse_train_forward_for_old_logprobs={'true' if args.reuse_train_forward else 'false'}"])
     tok = SyntheticTokenizer(margs.vocab_size)
     trainer = PPOTrainer(cfg, tokenizer=tok, env=env)

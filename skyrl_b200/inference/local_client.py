@@ -76,7 +76,8 @@ class LocalInferenceClient(InferenceEngineInterface):
             while futs:
                 if eng.paused or eng.asleep:
                     await asyncio.sleep(0.002)
-                    continue
+                    if not getattr(eng, "lockstep", False):
+                        continue  # a tensor-parallel group keeps stepping: the step carries the resume to its ranks
 
                 def _step():
                     with self._locks[k]:

@@ -76,6 +76,7 @@ class ParallelMesh:
     dp_rank: int = 0
     tp_group: Optional[object] = None
     dp_group: Optional[object] = None
+    tp_cpu_group: Optional[object] = None  # gloo-only twin of tp_group for host-side object exchange
 
 
 _MESHES: dict = {}
@@ -94,8 +95,10 @@ def build_mesh(tp: int, env: Optional[DistEnv] = None) -> ParallelMesh:
         for g in range(W // tp):  # every rank creates every group, in the same order
             ranks = list(range(g * tp, (g + 1) * tp))
             grp = dist.new_group(ranks)
+            cpu = dist.new_group(ranks, backend="gloo")
             if r in ranks:
                 mesh.tp_group = grp
+                mesh.tp_cpu_group = cpu
         for t in range(tp):
             ranks = list(range(t, W, tp))
             grp = dist.new_group(ranks)

@@ -88,7 +88,12 @@ class PPOTrainer:
             self.critic = CriticWorker(t, model_path=t.critic.model.path or t.policy.model.path, env=self.env,
                                        seed=t.seed + 1)
         if self.inference_engine_client is None:
-            self.engine = self._build_engine(self.policy.engine_model())
+            etp = int(self.cfg.generator.inference_engine.tensor_parallel_size or 1)
+            if etp > 1 and (self.env.world_size % etp or not dist.is_initialized()):
+                raise ValueError(f"generator.inference_engine.tensor_parallel_size={etp} must divide the world size "
+                                 f"{self.env.world_size}")
+            self.engine_tp = etp
+            self.engine = self._build_engine(self.policy.engine_model(etp))
             self.inference_engine_client = LocalInferenceClient([self.engine], self.tokenizer)
         if self.generator is None:
             self.generator = SkyRLGymGenerator(self.cfg.generator, self.cfg.environment.skyrl_gym,
@@ -100,13 +105,21 @@ class PPOTrainer:
         ecfg = EngineConfig(block_size=b.kv_block_size, gpu_memory_utilization=ie.gpu_memory_utilization,
                             max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=max(ie.max_num_batched_tokens, max_len),
                             max_model_len=max_len, enable_prefix_caching=ie.enable_prefix_caching,
-                            enforce_eager=ie.enforce_eager or not b.cuda_graph_decode, seed=self.cfg.trainer.seed + self.env.rank)
+                            enforce_eager=ie.enforce_eager or not b.cuda_graph_decode,
+                            # the ranks of one tensor-parallel engine must draw the same samples
+                            seed=self.cfg.trainer.seed + self.env.rank // max(1, getattr(self, "engine_tp", 1)))
         for k, v in (ie.engine_init_kwargs or {}).items():
             if hasattr(ecfg, k):
                 setattr(ecfg, k, v)
         eos = [self.tokenizer.eos_token_id] if self.tokenizer is not None and self.tokenizer.eos_token_id is not None else []
         detok = (lambda ids: self.tokenizer.decode(ids, skip_special_tokens=False)) if self.tokenizer is not None else None
-        return LLMEngine(model, ecfg, eos_token_ids=eos, detokenize=detok)
+        eng = LLMEngine(model, ecfg, eos_token_ids=eos, detokenize=detok)
+        if getattr(self, "engine_tp", 1) > 1:
+            from ..engine.lockstep import LockstepEngine
+
+            emesh = self.policy.engine_mesh
+            eng = LockstepEngine(eng, emesh.tp_cpu_group, self.env.rank - emesh.tp_rank)
+        return eng
 
     # ------------------------------------------------------------------ data
     def _local_prompts(self, global_batch: List[Dict[str, Any]]) -> List[Dict[str, Any]]:
@@ -116,8 +129,41 @@ class PPOTrainer:
         return global_batch[r * per : (r + 1) * per]
 
     # ------------------------------------------------------------------ rollout
+    async def _generate_lockstep(self, gen_input: GeneratorInput) -> GeneratorOutput:
+        """Rollout through a tensor-parallel engine: the group's leader generates for the prompts of all its ranks
+        while the others mirror its engine steps; every rank then keeps the rows of its own prompts."""
+        emesh = self.policy.engine_mesh
+        grp, tp = emesh.tp_cpu_group, emesh.tp_size
+        parts: List[Any] = [None] * tp
+        dist.all_gather_object(parts, dict(gen_input), group=grp)
+        counts = [len(p["prompts"]) for p in parts]
+        box: List[Any] = [None]
+        if self.engine.is_leader:
+            merged = GeneratorInput()
+            for key in parts[0]:
+                vals = [p.get(key) for p in parts]
+                merged[key] = [x for v in vals for x in v] if all(isinstance(v, list) for v in vals) else vals[0]
+            try:
+                box[0] = await self.generator.generate(merged)
+            finally:
+                self.engine.end_generation()
+        else:
+            await asyncio.to_thread(self.engine.follow)
+        dist.broadcast_object_list(box, src=self.engine.leader, group=grp)
+        out = box[0]
+        n_rows, n_in = len(out["response_ids"]), sum(counts)
+        if n_rows != n_in:
+            raise NotImplementedError("step-wise trajectories are not supported with a tensor-parallel engine")
+        lo = sum(counts[: emesh.tp_rank])
+        from .dynamic_sampling import select_rows
+
+        return select_rows(out, list(range(lo, lo + counts[emesh.tp_rank])))
+
     async def generate(self, gen_input: GeneratorInput) -> GeneratorOutput:
-        out = await self.generator.generate(gen_input)
+        if getattr(self, "engine_tp", 1) > 1 and self.engine is not None:
+            out = await self._generate_lockstep(gen_input)
+        else:
+            out = await self.generator.generate(gen_input)
         n = len(out["response_ids"])
         for key in ("prompt_token_ids", "rewards", "loss_masks"):
             if len(out[key]) != n:
@@ -401,7 +447,10 @@ class PPOTrainer:
             asyncio.run(self._remote_sync.sync()) if not self._in_event_loop() else None
             return
         if self.policy is not None:
-            self.policy.refresh_engine_model()  # TP shards / LoRA adapters -> the engine's full weights
+            self.policy.refresh_engine_model()  # TP shards / LoRA adapters -> the engine's own layout
+            ms = getattr(self.policy, "last_weight_sync_ms", None)
+            if ms is not None:
+                self.all_metrics["timing/weight_sync_kernel_ms"] = float(ms)
         if hasattr(c, "increment_weight_version"):
             c.increment_weight_version()
 

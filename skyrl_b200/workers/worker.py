@@ -364,23 +364,85 @@ class ModelWorker:
         node = {"policy": cfg.policy, "ref": cfg.ref, "critic": cfg.critic}.get(self.role, cfg.policy)
         return int(getattr(node, "sequence_parallel_size", 1) or 1)
 
-    def engine_model(self) -> CausalLM:
+    def engine_model(self, engine_tp: int = 1) -> CausalLM:
         """The model object a colocated generation engine should run.  Shared with training whenever the training
-        parameters are the full weights (plain or sequence-parallel); a separate full copy when they are not
-        (tensor-parallel shards, LoRA adapters over a frozen base) -- ``refresh_engine_model`` then re-derives it."""
+        parameters are the full weights and the engine is unsharded (plain or sequence-parallel trainer); a separate
+        copy in the engine's own layout otherwise (tensor-parallel trainer shards, LoRA adapters over a frozen base, a
+        tensor-parallel engine) -- ``refresh_engine_model`` then brings it up to date after every update."""
         from ..models.lora import LoRACausalLM
 
         if getattr(self, "_engine_copy", None) is not None:
             return self._engine_copy
         if isinstance(self.model, LoRACausalLM):
+            if engine_tp > 1:
+                raise NotImplementedError("LoRA training with a tensor-parallel engine is not supported")
             self._engine_copy = CausalLM(self.model.args, device=self.env.device, dtype=self.model.base_flat_params.dtype,
                                          seed=None)
             self.model.merge_into(self._engine_copy)
             return self._engine_copy
+        dense_tp = self._dense_tp_trainer()
+        if dense_tp or (engine_tp > 1 and not self.expert_parallel and self.pipe is None):
+            self._engine_copy = self._build_engine_copy(engine_tp)
+            self.refresh_engine_model()
+            return self._engine_copy
         if self.mesh is not None and not self.sequence_parallel:
+            if engine_tp > 1:
+                raise NotImplementedError("a tensor-parallel engine needs a dense data-, tensor- or sequence-parallel trainer")
             self._engine_copy = self.full_model_copy()
             return self._engine_copy
         return getattr(self, "_plain_model", None) or self.model
+
+    def _dense_tp_trainer(self) -> bool:
+        return (self.mesh is not None and not self.sequence_parallel and not self.expert_parallel and self.pipe is None)
+
+    def _build_engine_copy(self, engine_tp: int) -> CausalLM:
+        """Engine-side weights in the engine's own tensor-parallel layout, plus the block-copy plan that fills them
+        from this rank's training shard (``weight_sync/relayout.py``).  With a tensor-parallel trainer the buffer is a
+        symmetric allocation of the trainer's TP group, so every rank of the group can push into it."""
+        from ..models.decoder import flat_numel_for
+        from ..models.tp_decoder import local_args
+        from ..parallel.dist import build_mesh
+        from ..parallel.tensor_parallel import TPGroup
+        from ..weight_sync import relayout as rlo
+
+        dev, cuda = self.env.device, self.env.device.type == "cuda"
+        dense_tp = self._dense_tp_trainer()
+        src_model = self.model if dense_tp or not hasattr(self, "_plain_model") else self._plain_model
+        full_args = src_model.full_args if dense_tp else src_model.args
+        src_tp, src_rank = (self.mesh.tp_size, self.mesh.tp_rank) if dense_tp else (1, 0)
+        dtype = src_model.flat_params.dtype
+        eargs = local_args(full_args, engine_tp) if engine_tp > 1 else full_args
+        numel = flat_numel_for(eargs)
+        sym = None
+        if dense_tp and cuda and self.tp.peer is not None:
+            sym = self.tp.peer.alloc(numel, dtype)
+            flat = sym.local
+        else:
+            flat = torch.zeros(numel, device=dev, dtype=dtype)
+        if engine_tp > 1:
+            from ..engine.tp_model import TPEngineModel
+            from ..parallel.peer import PeerContext
+
+            emesh = build_mesh(engine_tp, self.env)
+            if cuda:
+                same = dense_tp and engine_tp == src_tp
+                epeer = self.tp.peer if same else PeerContext(dev, group=emesh.tp_group)
+            else:
+                epeer = None
+            etp = TPGroup(epeer, emesh.tp_group)
+            self.engine_mesh = emesh
+            copy = TPEngineModel(full_args, etp, device=dev, dtype=dtype, flat_buffer=flat)
+        else:
+            copy = CausalLM(full_args, device=dev, dtype=dtype, seed=None, flat_buffer=flat)
+        self._relayout = None
+        self._relayout_src = (src_model, src_tp, src_rank, full_args, engine_tp)
+        if cuda:
+            base = self.env.rank - src_rank  # first global rank of this trainer TP group
+            dests = [rlo.Destination(sym.ptrs[d] if sym is not None else flat.data_ptr(), copy.offsets, engine_tp,
+                                     (base + d) % engine_tp) for d in range(src_tp)]
+            plan = rlo.build_plan(full_args, src_model.offsets, src_tp, src_rank, dests)
+            self._relayout = rlo.RelayoutPush(plan, src_model.flat_params, dests)
+        return copy
 
     def refresh_engine_model(self) -> None:
         """Bring a separate engine copy up to date with the trained parameters (no-op when the buffer is shared)."""
@@ -391,8 +453,33 @@ class ModelWorker:
             return
         if isinstance(self.model, LoRACausalLM):
             self.model.merge_into(ec)
-        else:
+            return
+        if getattr(self, "_relayout_src", None) is None:
             self.full_model_copy(into=ec)
+            return
+        src_model, src_tp, src_rank, full_args, engine_tp = self._relayout_src
+        if getattr(self, "_relayout", None) is not None:
+            # one kernel: every block this rank owns goes straight into the engine buffers that need it (peer stores);
+            # the barrier makes every rank's pushes visible before any engine of the group reads its weights
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            self._relayout.run()
+            if src_tp > 1:
+                self.tp.peer.barrier(3)
+            ev1.record()
+            ev1.synchronize()
+            self.last_weight_sync_ms = ev0.elapsed_time(ev1)
+            self.last_weight_sync_bytes = self._relayout.bytes_out
+            return
+        # host / gloo path: gather the full state, then slice it the way the engine shards it
+        from ..models.tp_decoder import shard_param
+
+        state = src_model.gather_full_state() if src_tp > 1 else dict(src_model.named_flat_views())
+        erank = self.env.rank % engine_tp
+        with torch.no_grad():
+            for name, prm in ec.named_flat_views():
+                prm.copy_(shard_param(name, state[name].detach(), full_args, engine_tp, erank) if engine_tp > 1
+                          else state[name])
 
     @staticmethod
     def _ep_size_from_cfg(cfg) -> int:

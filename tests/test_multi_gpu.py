@@ -58,3 +58,25 @@ def test_bench_two_gpus_pipeline_parallel_tiny():
     p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-tp",
               "--prompts-per-gpu", "4", "--pp", "2"], port=29623)
     assert p.returncode == 0 and "x pp2" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_engine_tensor_parallel_matches_unsharded_engine():
+    """TP=2 engine (all-reduce in the o-proj / down-proj epilogues, eager and CUDA-graph decode) vs TP=1."""
+    p = _run([os.path.join(ROOT, "tests", "mp", "engine_tp_check.py")], port=29624)
+    assert p.returncode == 0 and "ENGINE_TP_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_weight_sync_relayout_kernel_is_bit_exact():
+    p = _run([os.path.join(ROOT, "tests", "mp", "relayout_check.py")], port=29625)
+    assert p.returncode == 0 and "RELAYOUT_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_bench_two_gpus_tensor_parallel_engine_tiny():
+    """RL step with a TP=2 rollout engine, under a data-parallel and under a tensor-parallel trainer."""
+    for extra, port in ((["--engine-tp", "2"], 29626), (["--tp", "2", "--engine-tp", "2"], 29627)):
+        p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-tp",
+                  "--prompts-per-gpu", "4", *extra], port=port)
+        assert p.returncode == 0 and '"device_status": 0' in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]

@@ -57,3 +57,15 @@ def test_gloo_worker_update_matches_single_rank(mode, port):
     single-rank update on the same data, group replicas are bit-identical, one optimizer step per RL step."""
     p = _run([os.path.join(ROOT, "tests", "mp", "worker_parity.py"), mode], port=port)
     assert p.returncode == 0 and f"WORKER_PARITY_OK mode={mode}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_gloo_engine_tensor_parallel_matches_unsharded():
+    p = _run([os.path.join(ROOT, "tests", "mp", "engine_tp_check.py")], port=29645)
+    assert p.returncode == 0 and "ENGINE_TP_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_gloo_rl_step_with_tensor_parallel_engine():
+    for extra, port in ((["--engine-tp", "2"], 29646), (["--tp", "2", "--engine-tp", "2"], 29647)):
+        p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-llama",
+                  "--prompts-per-gpu", "1", *extra], port=port)
+        assert p.returncode == 0 and '"n_gpus": 2' in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
