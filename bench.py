@@ -29,6 +29,21 @@ METRIC = "rl_step_tokens_per_sec"
 MODEL = "qwen2.5-1.5b"
 PROMPTS_PER_GPU, N_SAMPLES, PROMPT_LEN, RESP_MIN, RESP_MAX = 32, 8, 512, 256, 1024
 
+# The other headline configurations.  Every entry fixes the per-GPU work (weak scaling); the parallel layout is the named
+# one when enough GPUs are present and is shrunk (and reported as such) on smaller runs.
+CONFIGS = {
+    # GRPO, Qwen2.5-1.5B, colocated sharded data parallel (the default, also selected by no --config at all)
+    2: dict(model="qwen2.5-1.5b", prompts_per_gpu=32, n=8, prompt_len=512, resp_min=256, resp_max=1024, tp=1, engine_tp=1,
+            algo="grpo"),
+    # PPO with critic and reference model, Qwen2.5-7B, TP=4 x DP=2 training, TP=2 rollout engines, vocabulary-parallel
+    # fused LM head, GAE(gamma=1, lambda=0.95), N(0, 1) reward on the last token; 128 prompts x 4 samples at 8 GPUs
+    3: dict(model="qwen2.5-7b", prompts_per_gpu=16, n=4, prompt_len=1024, resp_min=4096, resp_max=4096, tp=4, engine_tp=2,
+            algo="ppo"),
+    # GRPO, Qwen3-30B-A3B, expert parallel over all ranks; 64 prompts x 8 samples at 8 GPUs
+    4: dict(model="qwen3-30b-a3b", prompts_per_gpu=8, n=8, prompt_len=1024, resp_min=2048, resp_max=2048, tp=1, engine_tp=1,
+            algo="grpo", ep="world"),
+}
+
 
 def reference_arm() -> None:
     print(json.dumps({"impl": "reference", "unavailable":
@@ -89,14 +104,19 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--model", default=MODEL)
-    ap.add_argument("--prompts-per-gpu", type=int, default=PROMPTS_PER_GPU)
+    ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS), help="headline configuration (BASELINE numbering)")
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--prompts-per-gpu", type=int, default=None)
+    ap.add_argument("--n-samples", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--resp-len", type=int, default=None, help="fixed response length (overrides the configuration's range)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the separately timed end-to-end steps (long configurations)")
     ap.add_argument("--max-tokens-per-microbatch", type=int, default=32768)
-    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size of the training model (1 = sharded data parallel)")
-    ap.add_argument("--ep", type=int, default=1, help="expert-parallel size (MoE models)")
+    ap.add_argument("--tp", type=int, default=None, help="tensor-parallel size of the training model (1 = sharded data parallel)")
+    ap.add_argument("--ep", type=int, default=None, help="expert-parallel size (MoE models)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size of the training model")
     ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size of the training model")
-    ap.add_argument("--engine-tp", type=int, default=1, help="tensor-parallel size of each rollout engine (lock-step ranks, "
+    ap.add_argument("--engine-tp", type=int, default=None, help="tensor-parallel size of each rollout engine (lock-step ranks, "
                     "all-reduce in the o-proj / down-proj GEMM epilogues)")
     ap.add_argument("--reuse-train-forward", action="store_true",
                     help="take old log-probs from the training forward (exact with one optimizer update per step); "
@@ -120,16 +140,39 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node")
     from skyrl_b200.models.decoder import PRESETS
 
+    spec = CONFIGS[args.config]
+    args.model = args.model or spec["model"]
+    P = args.prompts_per_gpu or spec["prompts_per_gpu"]
+    n = args.n_samples or spec["n"]
+    PROMPT_LEN = args.prompt_len or spec["prompt_len"]
+    RESP_MIN, RESP_MAX = (args.resp_len, args.resp_len) if args.resp_len else (spec["resp_min"], spec["resp_max"])
+
+    def fit(want: int) -> int:  # largest power-of-two layout size <= want that divides the world
+        k = 1
+        while k * 2 <= want and world % (k * 2) == 0:
+            k *= 2
+        return k
+
+    args.tp = fit(args.tp if args.tp is not None else spec["tp"])
+    args.engine_tp = fit(args.engine_tp if args.engine_tp is not None else spec["engine_tp"])
+    args.ep = args.ep if args.ep is not None else (world if spec.get("ep") == "world" and world > 1 else 1)
+    ppo = spec["algo"] == "ppo"
     margs = PRESETS[args.model]
-    P, n = args.prompts_per_gpu, N_SAMPLES
     cfg = SkyRLTrainConfig.from_cli_overrides([
         f"trainer.policy.model.path={args.model}", f"trainer.train_batch_size={P * world}",
         f"trainer.policy_mini_batch_size={P * world}", f"generator.n_samples_per_prompt={n}",
         f"trainer.max_prompt_length={PROMPT_LEN}", f"generator.sampling_params.max_generate_length={RESP_MAX}",
-        "generator.sampling_params.temperature=1.0", "generator.batched=true", "trainer.algorithm.advantage_estimator=grpo",
-        "trainer.algorithm.use_kl_loss=false", "trainer.algorithm.policy_loss_type=regular",
+        "generator.sampling_params.temperature=1.0", "generator.batched=true",
+        *(["trainer.algorithm.advantage_estimator=gae", "trainer.algorithm.gamma=1.0", "trainer.algorithm.lambd=0.95",
+           f"trainer.critic.model.path={args.model}", f"trainer.critic_mini_batch_size={P * world}",
+           "trainer.algorithm.use_kl_loss=true", "trainer.algorithm.kl_loss_coef=0.001",
+           "trainer.critic.optimizer_config.lr=5e-6", "environment.env_class=synthetic_gaussian",
+           "trainer.b200.vocab_parallel_lm_head=true"] if ppo else
+          ["trainer.algorithm.advantage_estimator=grpo", "trainer.algorithm.use_kl_loss=false",
+           "environment.env_class=synthetic_bernoulli"]),
+        "trainer.algorithm.policy_loss_type=regular",
         "trainer.policy.optimizer_config.lr=1e-6", f"trainer.max_tokens_per_microbatch={args.max_tokens_per_microbatch}",
-        "trainer.gradient_checkpointing=false", "environment.env_class=synthetic_bernoulli",
+        "trainer.gradient_checkpointing=false",
         f"generator.inference_engine.max_num_seqs={P * n}", "generator.inference_engine.gpu_memory_utilization=0.25",
         "generator.inference_engine.enable_prefix_caching=false", "trainer.resume_mode=none", "trainer.seed=0",
         "trainer.logger=console", *(["trainer.strategy=megatron",
@@ -147,7 +190,8 @@ def main() -> None:
     trainer.build_models()
 
     g = torch.Generator().manual_seed(1234 + env.rank)
-    total_steps = args.warmup + 2 * args.steps  # warm-up, device-timed steps, then separately timed end-to-end steps
+    e2e_steps = 0 if args.no_e2e else args.steps
+    total_steps = args.warmup + args.steps + e2e_steps  # warm-up, device-timed steps, then separately timed end-to-end steps
     # all step inputs live in pinned host memory; every step copies its own slice to the device
     prompt_store = torch.randint(4, margs.vocab_size, (total_steps, P, PROMPT_LEN), generator=g, dtype=torch.int32)
     len_store = torch.randint(RESP_MIN, RESP_MAX + 1, (total_steps, P * n), generator=g, dtype=torch.int32)
@@ -242,7 +286,7 @@ def main() -> None:
     if torch.cuda.is_available():
         torch.cuda.synchronize()
     pdist.barrier()
-    wall = time.perf_counter() - t1
+    wall = max(1e-9, time.perf_counter() - t1)
     e2e_all = pdist.all_reduce_sum_scalar(e2e_tokens, env.device)
     dev_s = ev0.elapsed_time(ev1) / 1e3 if torch.cuda.is_available() else dev_wall
     clocks = sampler.stop() if env.is_main else {}
@@ -260,9 +304,11 @@ def main() -> None:
         out = {
             "metric": METRIC, "value": tokens_all / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_s * 1e3 / K, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, Bernoulli(0.5) rewards, "
-            "random-init weights)",
-            "config": {"model": args.model, "global_batch": P * n * world, "seq_len": PROMPT_LEN + RESP_MAX,
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, %s rewards, random-init weights)"
+            % ("N(0,1)" if ppo else "Bernoulli(0.5)"),
+            "config": {"model": args.model, "baseline_config": args.config, "algorithm": spec["algo"],
+                       "engine_tensor_parallel": args.engine_tp,
+                       "global_batch": P * n * world, "seq_len": PROMPT_LEN + RESP_MAX,
                        "parallelism": (f"dp{world} x ep{args.ep} (fused expert dispatch/combine)" if args.ep > 1 else
                                        f"dp{world // args.pp} x pp{args.pp} (layer stages)" if args.pp > 1 else
                                        f"dp{world // args.sp} x sp{args.sp} (Ulysses, fused projections)" if args.sp > 1 else
@@ -274,12 +320,13 @@ def main() -> None:
                        "l2_policy": "inputs larger than L2 (3.1 GB of weights, >10 GB of KV and activations per step)",
                        "phase_seconds_last_step": {k[7:]: round(v, 4) for k, v in last.items() if k.startswith("timing/")}},
             "clocks": clocks,
-            "e2e": {"value": e2e_all / wall, "timed_with": "host clock over %d further steps" % K, "unit": "tokens/s", "h2d_bytes_per_step": (_lib.H2D_BYTES - h0) / K,
-                    "d2h_bytes_per_step": (_lib.D2H_BYTES - d0) / K},
+            "e2e": {"value": (e2e_all / wall) if e2e_steps else None, "timed_with": "host clock over %d further steps" % e2e_steps, "unit": "tokens/s", "h2d_bytes_per_step": (_lib.H2D_BYTES - h0) / max(1, e2e_steps),
+                    "d2h_bytes_per_step": (_lib.D2H_BYTES - d0) / max(1, e2e_steps)},
             "gpu_launches": launches, "device_status": status, "impl": "ours",
             # trainer -> rollout weight sync: the colocated engine reads the parameter buffer the optimizer's fused
             # push just wrote, so the separate sync phase only bumps the weight version
-            "weight_sync_ms": 1e3 * float(last.get("timing/sync_weights", 0.0)),
+            "weight_sync_ms": float(last["timing/weight_sync_kernel_ms"]) if "timing/weight_sync_kernel_ms" in last
+            else 1e3 * float(last.get("timing/sync_weights", 0.0)),
         }
         print(json.dumps(out), flush=True)
     pdist.shutdown()

@@ -596,6 +596,9 @@ class B200Config(BaseConfig):
     # "full": token-budget micro-batches are filled to the budget (first-fit decreasing) and padded to exactly the
     # budget, so activation sizes repeat; "balanced": equal-load bins (the reference's packer)
     microbatch_packing: str = "full"
+    # tensor-parallel training: shard the LM head over the vocabulary (fused log-prob kernel per shard, softmax records
+    # merged across ranks through peer memory) instead of over the tokens; needs untied embeddings
+    vocab_parallel_lm_head: bool = False
 
 
 @dataclass

@@ -1,6 +1,7 @@
 """Synthetic environments for plumbing runs and benchmarks (no dataset, no external service).
 
 * ``synthetic_bernoulli``  - single turn, reward ~ Bernoulli(p) (seeded per trajectory).
+* ``synthetic_gaussian``   - single turn, reward ~ N(mean, std) (seeded per trajectory).
 * ``synthetic_even``       - single turn, reward = fraction of response token ids that are even
                               (the response text is the space-separated ids of ``SyntheticTokenizer``).
 * ``synthetic_multiturn``  - ``max_turns`` turns; every non-final turn returns an observation of
@@ -28,6 +29,20 @@ class SyntheticBernoulliEnv(BaseTextEnv):
     def step(self, action: str) -> BaseTextEnvStepOutput:
         return BaseTextEnvStepOutput(observations=[], reward=1.0 if self.rng.random() < self.p else 0.0, done=True,
                                      metadata={})
+
+
+class SyntheticGaussianEnv(BaseTextEnv):
+    def __init__(self, env_config: Any = None, extras: Dict[str, Any] | None = None):
+        super().__init__()
+        extras = extras or {}
+        self.mean, self.std = float(extras.get("mean", 0.0)), float(extras.get("std", 1.0))
+        seed = extras.get("seed", None)
+        if seed is not None:
+            seed = int(seed) * 1000003 + int(extras.get("repetition_id", 0))
+        self.rng = random.Random(seed)
+
+    def step(self, action: str) -> BaseTextEnvStepOutput:
+        return BaseTextEnvStepOutput(observations=[], reward=self.rng.gauss(self.mean, self.std), done=True, metadata={})
 
 
 class SyntheticEvenEnv(BaseTextEnv):

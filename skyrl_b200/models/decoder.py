@@ -56,6 +56,7 @@ class ModelArgs:
     model_type: str = "qwen2"
     init_std: float = 0.02
     ep_size: int = 1  # expert parallelism: this rank stores num_experts / ep_size experts (routing stays global)
+    lm_head_rows: int = 0  # vocabulary-parallel LM head: rows of the head stored on this rank (0 = the whole vocabulary)
 
     @property
     def q_dim(self) -> int:
@@ -116,6 +117,8 @@ PRESETS: Dict[str, ModelArgs] = {
     "tiny-qwen2-tp": ModelArgs(vocab_size=2048, hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
                                intermediate_size=1024, rope_theta=1e4, attention_bias=True, tie_word_embeddings=True,
                                model_type="qwen2"),
+    "tiny-llama-d128": ModelArgs(vocab_size=2048, hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
+                                 intermediate_size=1024, rope_theta=1e4, model_type="llama"),
     "tiny-moe": ModelArgs(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=2, num_kv_heads=1, head_dim=128,
                           intermediate_size=512, rope_theta=1e4, num_experts=8, num_experts_per_tok=2,
                           moe_intermediate_size=128, model_type="qwen3_moe", qk_norm=True),
@@ -158,7 +161,7 @@ def _param_specs(a: ModelArgs, with_lm_head: bool = True, value_head: bool = Fal
             specs.append((p + "wd", (a.hidden_size, a.intermediate_size)))
     specs.append(("final_norm", (a.hidden_size,)))
     if with_lm_head and not a.tie_word_embeddings and not value_head:
-        specs.append(("lm_head", (a.vocab_size, a.hidden_size)))
+        specs.append(("lm_head", (a.lm_head_rows or a.vocab_size, a.hidden_size)))
     if value_head:
         specs.append(("value_head", (8, a.hidden_size)))  # row 0 is the head; 8 rows keep GEMM alignment
     return specs

@@ -29,7 +29,12 @@ from .decoder import CausalLM, ModelArgs, _EmbeddingFn
 REPLICATED_LEAVES = ("embed", "ln1", "ln2", "final_norm", "lm_head", "q_norm", "k_norm", "value_head")
 
 
-def local_args(a: ModelArgs, tp: int) -> ModelArgs:
+def local_args(a: ModelArgs, tp: int, vocab_parallel_head: bool = False) -> ModelArgs:
+    if vocab_parallel_head:
+        if a.tie_word_embeddings or a.vocab_size % tp:
+            raise ValueError("a vocabulary-parallel LM head needs untied embeddings and a vocabulary divisible by tp "
+                             f"(tie_word_embeddings={a.tie_word_embeddings}, vocab_size={a.vocab_size}, tp={tp})")
+        return dataclasses.replace(local_args(a, tp), lm_head_rows=a.vocab_size // tp)
     if a.num_heads % tp or a.intermediate_size % tp:
         raise ValueError(f"num_heads={a.num_heads} and intermediate_size={a.intermediate_size} must divide by tp={tp}")
     if a.num_kv_heads % tp:
@@ -40,10 +45,12 @@ def local_args(a: ModelArgs, tp: int) -> ModelArgs:
                                intermediate_size=a.intermediate_size // tp)
 
 
-def shard_param(name: str, full: torch.Tensor, a: ModelArgs, tp: int, r: int) -> torch.Tensor:
+def shard_param(name: str, full: torch.Tensor, a: ModelArgs, tp: int, r: int, vocab_parallel_head: bool = False) -> torch.Tensor:
     """Rank ``r``'s slice of a full parameter (fused QKV and gate/up are sliced per component)."""
     leaf = name.split(".")[-1]
-    d = a.head_dim
+    if leaf == "lm_head" and vocab_parallel_head:
+        vs = a.vocab_size // tp
+        return full[r * vs : (r + 1) * vs]
     if leaf in ("wqkv", "bqkv"):
         q, k, v = full[: a.q_dim], full[a.q_dim : a.q_dim + a.kv_dim], full[a.q_dim + a.kv_dim :]
         qs, ks = a.q_dim // tp, a.kv_dim // tp
@@ -72,6 +79,8 @@ def unshard_param(name: str, shards: List[torch.Tensor], a: ModelArgs) -> torch.
     if leaf == "wgu":
         fs = a.intermediate_size // tp
         return torch.cat([s[:fs] for s in shards] + [s[fs:] for s in shards], 0)
+    if leaf == "lm_head" and shards[0].shape[0] * tp == a.vocab_size and tp > 1:
+        return torch.cat(shards, 0)  # vocabulary-parallel head
     return shards[0]
 
 
@@ -114,22 +123,105 @@ class _GatherRowsFn(torch.autograd.Function):
         return g[r * n : (r + 1) * n].contiguous(), None
 
 
+class _AllGatherRowsSumBwdFn(torch.autograd.Function):
+    """All-gather of row shards whose backward *sums* the ranks' gradients and keeps the local rows (the gathered
+    tensor feeds a computation that every rank continues with a different slice of the weights)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return tpm.ref_all_gather_rows(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return tpm.ref_reduce_scatter_rows(g.contiguous(), ctx.group), None
+
+
+class _AllReduceIdentityBwdFn(torch.autograd.Function):
+    """Sum (or max) over the group in forward; the gradient passes through unchanged: every rank evaluates the same
+    replicated loss, so the upstream gradient is already the full one on each rank."""
+
+    @staticmethod
+    def forward(ctx, x, group, op):
+        y = x.clone()
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(y, op=op, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None, None
+
+
+class PeerPartials:
+    """Exchange of the fused LM-head kernel's per-(row, split) softmax records between the ranks of a vocabulary-
+    parallel head: each rank's records live in symmetric memory, a device barrier publishes them, and the combine
+    kernel reads every peer's records through its pointer (16 bytes per token and split -- the whole cross-rank
+    traffic of the log-sum-exp reduction; reference: three all-reduces, model_utils.py:46-61,95-99)."""
+
+    CHANNEL = 2
+
+    def __init__(self, tp: tpm.TPGroup):
+        self.tp, self.sym = tp, None
+
+    def alloc(self, T: int, splits: int) -> torch.Tensor:
+        need = T * splits * 4
+        if self.sym is None or self.sym.local.numel() < need:
+            self.sym = self.tp.peer.alloc(max(need, 1 << 18), torch.float32)
+        return self.sym.local[:need].view(T, splits, 4)
+
+    def __call__(self, partials, splits):
+        self.tp.peer.barrier(self.CHANNEL)  # every rank's records are complete
+        return list(self.sym.ptrs)
+
+    def release(self) -> None:
+        self.tp.peer.barrier(self.CHANNEL)  # every rank has read them: the buffer may be overwritten
+
+
 class TPCausalLM(CausalLM):
     """Local shard of a tensor-parallel model; ``full_args`` describes the unsharded architecture."""
 
     def __init__(self, full_args: ModelArgs, tp: tpm.TPGroup, device="cpu", dtype=torch.bfloat16, value_head: bool = False,
-                 flat_buffer: Optional[torch.Tensor] = None, seed: Optional[int] = 0):
+                 flat_buffer: Optional[torch.Tensor] = None, seed: Optional[int] = 0, vocab_parallel_head: bool = False):
         self.full_args = full_args
         self.tp = tp
-        super().__init__(local_args(full_args, tp.size), device=device, dtype=dtype, value_head=value_head,
-                         flat_buffer=flat_buffer, seed=None)
+        # the LM head is sharded over the vocabulary only when asked for and possible (untied, divisible, no value head)
+        self.vocab_parallel_head = bool(vocab_parallel_head and not value_head and tp.size > 1
+                                        and not full_args.tie_word_embeddings and full_args.vocab_size % tp.size == 0)
+        self.replicated_leaves = tuple(x for x in REPLICATED_LEAVES if not (x == "lm_head" and self.vocab_parallel_head))
+        super().__init__(local_args(full_args, tp.size, self.vocab_parallel_head), device=device, dtype=dtype,
+                         value_head=value_head, flat_buffer=flat_buffer, seed=None)
+        self._partials = None
         if seed is not None:
             self.load_from_full(CausalLM(full_args, device="cpu", dtype=torch.float32, value_head=value_head, seed=seed))
 
     @torch.no_grad()
     def load_from_full(self, full: CausalLM) -> None:
         for name, prm in self.named_flat_views():
-            prm.copy_(shard_param(name, full.p(name).detach(), self.full_args, self.tp.size, self.tp.rank).to(prm.dtype))
+            prm.copy_(shard_param(name, full.p(name).detach(), self.full_args, self.tp.size, self.tp.rank,
+                                  self.vocab_parallel_head).to(prm.dtype))
+
+    @torch.no_grad()
+    def init_random_on_device(self, seed: int = 0) -> None:
+        """Random initialisation of large models without a host copy: every full parameter is drawn on the device from
+        a generator seeded by (seed, parameter index) -- so all ranks draw the same full tensor -- and this rank keeps
+        its slice.  The values differ from ``CausalLM.reset_parameters`` (a host generator); use ``load_from_full``
+        when the two must match."""
+        from .decoder import _param_specs
+
+        dev = self.flat_params.device
+        shapes = dict(_param_specs(self.full_args, value_head=self.has_value_head))
+        for k, (name, prm) in enumerate(self.named_flat_views()):
+            leaf = name.split(".")[-1]
+            if leaf in ("ln1", "ln2", "final_norm", "q_norm", "k_norm"):
+                prm.fill_(1.0)
+            elif leaf == "bqkv":
+                prm.zero_()
+            else:
+                g = torch.Generator(device=dev).manual_seed(seed * 1000003 + k)
+                full = torch.empty(shapes[name], device=dev, dtype=prm.dtype).normal_(0.0, self.full_args.init_std, generator=g)
+                prm.copy_(shard_param(name, full, self.full_args, self.tp.size, self.tp.rank, self.vocab_parallel_head))
+                del full
 
     @torch.no_grad()
     def gather_full_state(self) -> Dict[str, torch.Tensor]:
@@ -137,7 +229,7 @@ class TPCausalLM(CausalLM):
         out = {}
         for name, prm in self.named_flat_views():
             leaf = name.split(".")[-1]
-            if leaf in REPLICATED_LEAVES or self.tp.size == 1:
+            if leaf in self.replicated_leaves or self.tp.size == 1:
                 out[name] = prm.detach()
                 continue
             parts = [torch.empty_like(prm) for _ in range(self.tp.size)]
@@ -150,7 +242,7 @@ class TPCausalLM(CausalLM):
         if self.tp.size == 1:
             return
         for name, prm in self.named_flat_views():
-            if name.split(".")[-1] in REPLICATED_LEAVES:
+            if name.split(".")[-1] in self.replicated_leaves:
                 g = getattr(prm, "main_grad", None)
                 if g is None:
                     g = prm.grad
@@ -193,11 +285,50 @@ class TPCausalLM(CausalLM):
         """Log-probs of all ``T`` targets on every rank: each rank scores its own rows, then the rows are gathered."""
         tp = self.tp
         R = hidden_shard.shape[0]
+        if getattr(self, "vocab_parallel_head", False):
+            return self._token_logprobs_vocab_parallel(hidden_shard, targets_full, temperature, with_entropy)
         lp, ent = self.token_logprobs(hidden_shard, targets_full[tp.rank * R : (tp.rank + 1) * R], temperature, with_entropy)
         lp = _GatherRowsFn.apply(lp, tp.group)
         if ent is not None:
             ent = _GatherRowsFn.apply(ent, tp.group)
         return lp, ent
+
+    def _token_logprobs_vocab_parallel(self, hidden_shard, targets_full, temperature: float, with_entropy: bool):
+        """Vocabulary-parallel fused LM head (reference: distributed/megatron/model_utils.py:275-428 and the TP
+        epilogues of fused_linear_logprob_triton.py:478-605): every rank scores all tokens against its slice of the
+        vocabulary without materialising logits; the per-split softmax records are merged across ranks by the combine
+        kernel through peer pointers, so every rank obtains the full log-probabilities (and entropies)."""
+        from ..ops import lm_head as lm_head_ops
+
+        tp = self.tp
+        W = self.p("lm_head")
+        vs = W.shape[0]
+        h_full = _AllGatherRowsSumBwdFn.apply(hidden_shard, tp.group)
+        if tp.fused and h_full.is_cuda:
+            if self._partials is None:
+                self._partials = PeerPartials(tp)
+            return lm_head_ops.lm_head_logprobs(h_full, W, targets_full, 1.0 / temperature, with_entropy,
+                                                vocab_offset=tp.rank * vs, peer_exchange=self._partials)
+        # host / gloo reference: the same reduction written with three all-reduces
+        from ..ops import gemm
+
+        z = gemm.linear(h_full, W).float() / temperature  # weight gradient goes to the fp32 main_grad buffer
+        m = _AllReduceIdentityBwdFn.apply(z.max(-1).values.detach(), tp.group, dist.ReduceOp.MAX)
+        e = torch.exp(z - m[:, None])
+        s = _AllReduceIdentityBwdFn.apply(e.sum(-1), tp.group, dist.ReduceOp.SUM)
+        lse = m + torch.log(s)
+        t = targets_full.long() - tp.rank * vs
+        own = (t >= 0) & (t < vs)
+        zt = torch.where(own, z.gather(-1, t.clamp(0, vs - 1)[:, None]).squeeze(-1), torch.zeros_like(lse))
+        zt = _AllReduceIdentityBwdFn.apply(zt, tp.group, dist.ReduceOp.SUM)
+        lp = zt - lse
+        pz = _AllReduceIdentityBwdFn.apply((e * z).sum(-1), tp.group, dist.ReduceOp.SUM) / s
+        ent = lse - pz
+        return lp, (ent if with_entropy else ent.detach())
+
+    def values_full(self, hidden_shard: torch.Tensor) -> torch.Tensor:
+        """Value-head outputs of all ``T`` tokens on every rank (each rank scores its rows, then the rows are gathered)."""
+        return _GatherRowsFn.apply(self.values(hidden_shard), self.tp.group)
 
 
 class UlyssesCausalLM(CausalLM):
@@ -249,6 +380,7 @@ class UlyssesCausalLM(CausalLM):
         return h
 
     token_logprobs_full = TPCausalLM.token_logprobs_full
+    values_full = TPCausalLM.values_full
 
     def reduce_replicated_grads(self) -> None:  # the data-parallel reduction over all ranks already sums them
         return

@@ -59,6 +59,8 @@ def lm_head_partials(hidden: torch.Tensor, W: torch.Tensor, targets: torch.Tenso
     T, K = hidden.shape
     V = W.shape[0]
     splits = int(_k().sb_lmhead_num_splits(T, V))
+    if callable(out):
+        out = out(T, splits)  # e.g. a view into symmetric memory that the peers can read
     if out is None:
         out = torch.empty((T, splits, 4), device=hidden.device, dtype=torch.float32)
     code = _k().sb_lmhead_partials(hidden.data_ptr(), W.data_ptr(), targets.data_ptr(), out.data_ptr(), T, V, K,
@@ -85,7 +87,8 @@ class _LMHeadLogprobFn(torch.autograd.Function):
         if hidden.is_cuda:
             hidden = hidden.contiguous()
             t32 = targets.to(torch.int32).contiguous()
-            partials, splits = lm_head_partials(hidden, W, t32, inv_temp, vocab_offset)
+            partials, splits = lm_head_partials(hidden, W, t32, inv_temp, vocab_offset,
+                                                out=getattr(peer_exchange, "alloc", None))
             if peer_exchange is not None:
                 ptrs = peer_exchange(partials, splits)  # pointers to every rank's records, own included
             else:

@@ -29,13 +29,17 @@ from ..ops import _lib
 Rect = Tuple[int, int, int, int, int, int]  # full rows [r0, r1), full cols [c0, c1), local row / col of (r0, c0)
 
 
-def shard_rects(name: str, shape: Tuple[int, ...], a: ModelArgs, tp: int, r: int) -> Tuple[List[Rect], Tuple[int, int]]:
+def shard_rects(name: str, shape: Tuple[int, ...], a: ModelArgs, tp: int, r: int,
+                vocab_parallel_head: bool = False) -> Tuple[List[Rect], Tuple[int, int]]:
     """Rectangles of the full parameter held by shard ``r`` of ``tp`` and the local matrix shape ``(rows, cols)``.
     One-dimensional parameters are treated as one-column matrices."""
     leaf = name.split(".")[-1]
     rows, cols = (shape[0], int(np.prod(shape[1:]))) if len(shape) > 1 else (shape[0], 1)
     if tp == 1:
         return [(0, rows, 0, cols, 0, 0)], (rows, cols)
+    if leaf == "lm_head" and vocab_parallel_head:
+        vs = rows // tp
+        return [(r * vs, (r + 1) * vs, 0, cols, 0, 0)], (vs, cols)
     if leaf in ("wqkv", "bqkv"):
         comps = [a.q_dim, a.kv_dim, a.kv_dim]
     elif leaf == "wgu":
@@ -54,8 +58,11 @@ def shard_rects(name: str, shape: Tuple[int, ...], a: ModelArgs, tp: int, r: int
     return rects, (lbase, cols)
 
 
-def is_replicated(name: str, tp: int) -> bool:
-    return tp == 1 or name.split(".")[-1] not in ("wqkv", "bqkv", "wgu", "wo", "wd")
+def is_replicated(name: str, tp: int, vocab_parallel_head: bool = False) -> bool:
+    leaf = name.split(".")[-1]
+    if leaf == "lm_head" and vocab_parallel_head and tp > 1:
+        return False
+    return tp == 1 or leaf not in ("wqkv", "bqkv", "wgu", "wo", "wd")
 
 
 @dataclass
@@ -89,7 +96,8 @@ def full_shapes(a: ModelArgs) -> Dict[str, Tuple[int, ...]]:
 
 
 def build_plan(full_args: ModelArgs, src_offsets: Dict[str, Tuple[int, int]], src_tp: int, src_rank: int,
-               dests: Sequence[Destination], names: Optional[Sequence[str]] = None) -> List[BlockCopy]:
+               dests: Sequence[Destination], names: Optional[Sequence[str]] = None,
+               src_vocab_parallel_head: bool = False) -> List[BlockCopy]:
     """Block copies that move everything this source shard owns to every destination that needs it."""
     shapes = full_shapes(full_args)
     plan: List[BlockCopy] = []
@@ -97,9 +105,9 @@ def build_plan(full_args: ModelArgs, src_offsets: Dict[str, Tuple[int, int]], sr
         if name not in shapes:
             continue
         shape = shapes[name]
-        s_rects, (s_rows, s_cols) = shard_rects(name, shape, full_args, src_tp, src_rank)
+        s_rects, (s_rows, s_cols) = shard_rects(name, shape, full_args, src_tp, src_rank, src_vocab_parallel_head)
         s_base = src_offsets[name][0]
-        if is_replicated(name, src_tp) and src_tp > 1:
+        if is_replicated(name, src_tp, src_vocab_parallel_head) and src_tp > 1:
             # every source rank holds the whole parameter: each pushes one chunk of the rows
             rows = shape[0]
             per = -(-rows // src_tp)

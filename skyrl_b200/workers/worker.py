@@ -155,16 +155,20 @@ class ModelWorker:
             from ..parallel.peer import PeerContext
             from ..parallel.tensor_parallel import TPGroup
 
-            if value_head:
-                raise NotImplementedError("the critic runs data-parallel only; set tensor_model_parallel_size=1 for it")
             self.mesh = build_mesh(tp_size, self.env)
             tp_peer = PeerContext(dev, group=self.mesh.tp_group) if dev.type == "cuda" else None
             self.tp = TPGroup(tp_peer, self.mesh.tp_group)
             margs = resolve_model_args(model_path)
-            model = TPCausalLM(margs, self.tp, device=dev, dtype=dtype, seed=None)
-            full = build_model(model_path, device="cpu", dtype=torch.float32, seed=seed)
-            model.load_from_full(full)
-            del full
+            model = TPCausalLM(margs, self.tp, device=dev, dtype=dtype, seed=None, value_head=value_head,
+                               vocab_parallel_head=bool(getattr(cfg.b200, "vocab_parallel_lm_head", False)))
+            from ..models.decoder import PRESETS
+
+            if model_path in PRESETS and dev.type == "cuda" and model.num_parameters() * tp_size > 2_000_000_000:
+                model.init_random_on_device(seed)  # multi-billion-parameter presets: no fp32 host copy per rank
+            else:
+                full = build_model(model_path, device="cpu", dtype=torch.float32, seed=seed, value_head=value_head)
+                model.load_from_full(full)
+                del full
             peer_ctx = None  # the flat-buffer peer optimizer spans the whole world; TP uses the DP group over NCCL
         pp_size = self._pp_size_from_cfg(cfg) if (model is None and tp_size == 1) else 1
         self.pipe = None
@@ -207,8 +211,6 @@ class ModelWorker:
         use_peer = peer_ctx is not None and trainable and self.env.world_size > 1 and dev.type == "cuda"
         sp_size = self._sp_size_from_cfg(cfg) if model is None and tp_size == 1 else 1
         self.sequence_parallel = sp_size > 1
-        if self.sequence_parallel and value_head:
-            raise NotImplementedError("sequence parallelism of the critic is not supported; use sequence_parallel_size=1")
         if model is None:
             if use_peer:
                 from ..models.decoder import flat_numel_for, resolve_model_args
@@ -245,7 +247,8 @@ class ModelWorker:
                 sp_peer = PeerContext(dev, group=self.mesh.tp_group) if dev.type == "cuda" else None
                 self.tp = TPGroup(sp_peer, self.mesh.tp_group)
                 self._plain_model = model
-                model = UlyssesCausalLM(model.args, self.tp, device=dev, dtype=dtype, flat_buffer=model.flat_params, seed=None)
+                model = UlyssesCausalLM(model.args, self.tp, device=dev, dtype=dtype, flat_buffer=model.flat_params, seed=None,
+                                        value_head=value_head)
         self.model = model
         qcfg = getattr(cfg.policy.model, "fake_int4_qat", None)
         if trainable and qcfg is not None and qcfg.enabled:
@@ -273,7 +276,8 @@ class ModelWorker:
                 if self.expert_parallel or self.pipe is not None:
                     dups = model.replicated_ranges()
                 else:
-                    dups = [(o, o + n) for name, (o, n) in model.offsets.items() if name.split(".")[-1] in REPLICATED_LEAVES]
+                    rep = getattr(model, "replicated_leaves", REPLICATED_LEAVES)
+                    dups = [(o, o + n) for name, (o, n) in model.offsets.items() if name.split(".")[-1] in rep]
                 extra = dict(group=self.mesh.dp_group, transport="nccl", norm_group=self.mesh.tp_group, dup_ranges=dups,
                              count_dups=self.mesh.tp_rank == 0)
             self.optimizer = ShardedAdamW(model.flat_params, flat_grad, lr=ocfg.lr, betas=tuple(ocfg.adam_betas),
@@ -440,7 +444,8 @@ class ModelWorker:
             base = self.env.rank - src_rank  # first global rank of this trainer TP group
             dests = [rlo.Destination(sym.ptrs[d] if sym is not None else flat.data_ptr(), copy.offsets, engine_tp,
                                      (base + d) % engine_tp) for d in range(src_tp)]
-            plan = rlo.build_plan(full_args, src_model.offsets, src_tp, src_rank, dests)
+            plan = rlo.build_plan(full_args, src_model.offsets, src_tp, src_rank, dests,
+                                  src_vocab_parallel_head=bool(getattr(src_model, "vocab_parallel_head", False)))
             self._relayout = rlo.RelayoutPush(plan, src_model.flat_params, dests)
         return copy
 
@@ -549,6 +554,18 @@ class ModelWorker:
         lp, ent = self.model.token_logprobs_full(h, tgt, temp, with_entropy=with_entropy)
         return lp[pv.pred_index], (ent[pv.pred_index] if ent is not None else None)
 
+    def _pred_values(self, pv: PackedView) -> torch.Tensor:
+        """Value-head outputs at the packed batch's prediction positions, ``[n_pred]``."""
+        if self.mesh is None:
+            return self.model.values(self._hidden(pv)[pv.pred_index])
+        if self.pipe is not None or self.expert_parallel:
+            raise NotImplementedError("the critic supports data, tensor and sequence parallelism")
+        from ..models.tp_decoder import pad_packed_for_tp
+
+        ids, pos, cu, T = pad_packed_for_tp(pv.ids, pv.positions, pv.cu_seqlens, self.mesh.tp_size)
+        h = self.model(ids, pos, cu, max(pv.max_seqlen, ids.numel() - T))
+        return self.model.values_full(h)[pv.pred_index]
+
     # ------------------------------------------------------------------ forward (no grad)
     @torch.no_grad()
     def forward(self, batch: TrainingInputBatch, train_packing: bool = False) -> TrainingOutputBatch:
@@ -571,10 +588,9 @@ class ModelWorker:
             rows = groups[k] if k < len(groups) else groups[-1]  # padding micro-batch keeps collectives aligned
             pv = self._pack(batch, rows)
             if self.role == "critic":
-                h = self._hidden(pv)
-                if pv.pred_index.numel() == 0:
+                if pv.pred_index.numel() == 0 and self.mesh is None:
                     continue
-                vals = self.model.values(h[pv.pred_index])
+                vals = self._pred_values(pv)
             else:
                 if pv.pred_index.numel() == 0 and self.mesh is None:
                     self._hidden(pv)
@@ -877,14 +893,14 @@ class CriticWorker(ModelWorker):
             real = k < len(groups)
             rows = groups[k] if real else groups[-1]
             pv = self._pack(batch, rows)
-            h = self._hidden(pv)
-            v = self.model.values(h[pv.pred_index])
+            v = self._pred_values(pv)
             v_grid = pv.scatter_to_grid(v)
             g = lambda key: self._rows_to_device(batch.get(key), rows)  # noqa: E731
             loss, clipfrac = rl.ppo_critic_loss(v_grid, g("values"), g("returns"), algo, loss_mask=g("loss_mask"))
             if not real:
                 loss = loss * 0.0
-            (loss / max(1, self.env.world_size)).backward()
+            # mean over the data shards: ranks of one tensor / sequence parallel group hold the same shard
+            (loss / max(1, self.env.world_size // self.tp_size)).backward()
             if real:
                 mk = g("loss_mask")
                 all_metrics.append({"critic_loss": loss.detach(), "values_mean": masked_mean(v_grid.detach(), mk),

@@ -46,6 +46,8 @@ def main():
             for name, prm in ec.named_flat_views():
                 want = shard_param(name, full[name], fa, engine_tp, env.rank % engine_tp) if engine_tp > 1 else full[name]
                 assert torch.equal(prm, want), (trainer_tp, engine_tp, name)
+            dist.barrier()  # a peer's next push must not land while this rank still compares (in training the step
+            # structure provides this ordering: engines are idle while weights are pushed)
         assert w.last_weight_sync_ms > 0 and _lib.status_read_clear() == 0
         if env.rank == 0:
             print(f"relayout trainer_tp={trainer_tp} engine_tp={engine_tp}: {w._relayout.n_desc} block copies, "

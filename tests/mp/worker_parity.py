@@ -20,7 +20,8 @@ from skyrl_b200.parallel.sharded_optimizer import ShardedAdamW  # noqa: E402
 from skyrl_b200.train.batch import TrainingInputBatch  # noqa: E402
 from skyrl_b200.workers.worker import PolicyWorker  # noqa: E402
 
-MODELS = {"tp": "tiny-llama", "sp": "tiny-llama", "pp": "tiny-llama", "ep": "tiny-moe"}
+MODELS = {"tp": "tiny-llama", "sp": "tiny-llama", "pp": "tiny-llama", "ep": "tiny-moe", "tpv": "tiny-llama",
+          "critic_tp": "tiny-llama", "critic_sp": "tiny-llama"}
 
 
 def cfg_for(mode: str, model: str):
@@ -29,6 +30,10 @@ def cfg_for(mode: str, model: str):
         "sp": ["trainer.policy.sequence_parallel_size=2"],
         "ep": ["trainer.strategy=megatron", "trainer.policy.megatron_config.expert_model_parallel_size=2"],
         "pp": ["trainer.strategy=megatron", "trainer.policy.megatron_config.pipeline_model_parallel_size=2"],
+        "tpv": ["trainer.strategy=megatron", "trainer.policy.megatron_config.tensor_model_parallel_size=2",
+                "trainer.b200.vocab_parallel_lm_head=true"],
+        "critic_tp": ["trainer.strategy=megatron", "trainer.policy.megatron_config.tensor_model_parallel_size=2"],
+        "critic_sp": ["trainer.critic.sequence_parallel_size=2", "trainer.policy.sequence_parallel_size=2"],
         "none": [],
     }[mode]
     return SkyRLTrainConfig.from_cli_overrides([
@@ -36,6 +41,7 @@ def cfg_for(mode: str, model: str):
         "trainer.micro_train_batch_size_per_gpu=2", "generator.n_samples_per_prompt=2", "trainer.bf16=false",
         "trainer.algorithm.use_kl_loss=false", "trainer.policy.optimizer_config.lr=1e-3",
         "trainer.policy.optimizer_config.max_grad_norm=0.5", "trainer.gradient_checkpointing=false",
+        "trainer.critic.optimizer_config.lr=1e-3", "trainer.critic.optimizer_config.max_grad_norm=0.5",
         "trainer.max_tokens_per_microbatch=0", "trainer.resume_mode=none", *extra])
 
 
@@ -51,7 +57,8 @@ def make_batch(seed: int, B: int = 4, P: int = 12, R: int = 10, vocab: int = 102
     old = -torch.rand(B, R, generator=g)
     b = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "loss_mask": rmask.clone(),
                             "advantages": adv, "action_log_probs": old, "rollout_logprobs": None,
-                            "base_action_log_probs": None})
+                            "base_action_log_probs": None, "values": torch.randn(B, R, generator=g) * 0.1,
+                            "returns": torch.randn(B, R, generator=g)})
     b.metadata = {"uids": [f"u{i // 2}" for i in range(B)]}
     return b
 
@@ -80,7 +87,12 @@ def main():
     solo = [dist.new_group([r]) for r in range(2)][env.rank]
 
     # ---- model-parallel worker
-    w = PolicyWorker(cfg_for(mode, model).trainer, model_path=model, env=env, seed=0)
+    from skyrl_b200.workers.worker import CriticWorker
+
+    Worker = CriticWorker if mode.startswith("critic") else PolicyWorker
+    w = Worker(cfg_for(mode, model).trainer, model_path=model, env=env, seed=0)
+    if mode == "tpv":
+        assert w.model.vocab_parallel_head and w.model.p("lm_head").shape[0] == 512
     if mode == "ep":
         batches = [make_batch(100), make_batch(101)]  # expert-parallel ranks keep their own data
         local = batches[env.rank]
@@ -93,13 +105,13 @@ def main():
 
     # ---- single-rank reference on the same data (both ranks compute it redundantly)
     one = pdist.DistEnv(0, 0, 1, torch.device("cpu"))
-    ref = PolicyWorker(cfg_for("none", model).trainer, model_path=model, env=one, seed=0)
+    ref = Worker(cfg_for("none", model).trainer, model_path=model, env=one, seed=0)
     o = ref.optimizer
     ref.optimizer = ShardedAdamW(ref.model.flat_params, ref.flat_grad, lr=o.lr, betas=o.betas, weight_decay=o.weight_decay,
                                  max_grad_norm=o.max_grad_norm, group=solo)
     from skyrl_b200.parallel.sharded_optimizer import get_scheduler
 
-    oc = cfg_for("none", model).trainer.policy.optimizer_config
+    oc = getattr(cfg_for("none", model).trainer, "critic" if mode.startswith("critic") else "policy").optimizer_config
     ref.scheduler = get_scheduler(oc.scheduler, ref.optimizer, oc.num_warmup_steps, base_lr=oc.lr)
     for b in batches:
         if mode == "ep":  # two data shards: each contributes half of the KL / entropy weights, advantages are pre-scaled
@@ -116,7 +128,7 @@ def main():
         err = (got[k] - v).abs().max().item()
         worst = max(worst, err)
         assert err < 2e-5, (mode, k, err)
-    moved = max((want[k] - dict(PolicyWorker(cfg_for("none", model).trainer, model_path=model, env=one, seed=0)
+    moved = max((want[k] - dict(Worker(cfg_for("none", model).trainer, model_path=model, env=one, seed=0)
                                 .model.named_flat_views())[k].float()).abs().max().item() for k in list(want)[:3])
     assert moved > 1e-4, "the reference update did not move the parameters"
     # replicas inside the group are bit-identical
@@ -141,6 +153,12 @@ def main():
         calls["opt"] += 1
         return None
 
+    if mode.startswith("critic"):
+        dist.barrier()
+        if env.rank == 0:
+            print(f"WORKER_PARITY_OK mode={mode} grad_norm={gn:.6f} max_param_err={worst:.2e}")
+        pdist.shutdown()
+        return
     share = 1 if mode == "ep" else 2
     tr.policy = SimpleNamespace(tp_size=share, forward_backward=fb, optim_step=opt)
     tr.critic = None
