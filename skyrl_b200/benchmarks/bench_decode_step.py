@@ -3,6 +3,8 @@ times decode steps (CUDA-graph replay or eager), reporting ms/step, tokens/s and
 (weights + KV bytes that a step must read, over the measured copy bandwidth).
 
     python -m skyrl_b200.benchmarks.bench_decode_step --model qwen2.5-1.5b --seqs 256 --ctx 900 --steps 32
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m skyrl_b200.benchmarks.bench_decode_step \
+        --model qwen2.5-7b --seqs 128 --ctx 3000 --tp 2      # tensor-parallel engine (one rank per GPU)
 """
 
 from __future__ import annotations
@@ -26,9 +28,27 @@ def main() -> None:
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="plain GEMMs instead of split-K + fused consumers")
     ap.add_argument("--hbm-gbs", type=float, default=float(os.environ.get("SB_HBM_GBS", "6543.4")))
+    ap.add_argument("--tp", type=int, default=1, help="engine tensor-parallel size (= number of ranks launched)")
     args = ap.parse_args()
     a = PRESETS[args.model]
-    m = CausalLM(a, device="cuda", dtype=torch.bfloat16, seed=0)
+    rank = 0
+    if args.tp > 1:
+        from skyrl_b200.engine.tp_model import TPEngineModel
+        from skyrl_b200.parallel import dist as pdist
+        from skyrl_b200.parallel import tensor_parallel as tpm
+        from skyrl_b200.parallel.peer import PeerContext
+
+        env = pdist.init_distributed()
+        assert env.world_size == args.tp, "launch one rank per tensor-parallel shard"
+        rank = env.rank
+        tp = tpm.TPGroup(PeerContext(env.device), None)
+        m = TPEngineModel(a, tp, device=env.device, dtype=torch.bfloat16)
+        m.flat_params.normal_(0.0, 0.02)  # timing only: the shards need no consistent full model
+        for name, prm in m.named_flat_views():
+            if name.split(".")[-1] in ("ln1", "ln2", "final_norm"):
+                prm.data.fill_(1.0)
+    else:
+        m = CausalLM(a, device="cuda", dtype=torch.bfloat16, seed=0)
     max_len = args.ctx + args.steps * 3 + 64
     eng = LLMEngine(m, EngineConfig(block_size=32, max_num_seqs=args.seqs, max_model_len=max_len,
                                     max_num_batched_tokens=1 << 20, enforce_eager=args.eager, sync_interval=args.steps, fused_decode=not args.no_fused,
@@ -47,12 +67,20 @@ def main() -> None:
     torch.cuda.synchronize()
     ms = s.elapsed_time(e) / args.steps
     ctx_now = args.ctx + args.steps * 1.5
-    kv_bytes = args.seqs * ctx_now * 2 * a.num_layers * a.num_kv_heads * a.head_dim * 2
+    kv_bytes = args.seqs * ctx_now * 2 * a.num_layers * m.args.num_kv_heads * a.head_dim * 2  # this rank's share
     w_bytes = (m.num_parameters()) * 2
     ideal_ms = (kv_bytes + w_bytes) / (args.hbm_gbs * 1e9) * 1e3
-    print(json.dumps({"model": args.model, "seqs": args.seqs, "ctx": args.ctx, "mode": "eager" if args.eager else "graph", "fused": not args.no_fused,
-                      "ms_per_step": ms, "tokens_per_s": args.seqs / ms * 1e3, "hbm_bytes_per_step": kv_bytes + w_bytes,
-                      "roofline_ms": ideal_ms, "fraction_of_measured_hbm_roofline": ideal_ms / ms}))
+    if rank == 0:
+        print(json.dumps({"tp": args.tp, "model": args.model, "seqs": args.seqs, "ctx": args.ctx,
+                          "mode": "eager" if args.eager else "graph", "fused": not args.no_fused, "ms_per_step": ms,
+                          "tokens_per_s": args.seqs / ms * 1e3, "hbm_bytes_per_step_per_rank": kv_bytes + w_bytes,
+                          "roofline_ms": ideal_ms, "fraction_of_measured_hbm_roofline": ideal_ms / ms}))
+    if args.tp > 1:
+        from skyrl_b200.ops import _lib
+        from skyrl_b200.parallel import dist as pdist
+
+        assert _lib.status_read_clear() == 0
+        pdist.shutdown()
 
 
 if __name__ == "__main__":

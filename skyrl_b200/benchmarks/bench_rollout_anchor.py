@@ -42,7 +42,8 @@ def run_ours(args, a):
     S = args.prompts * args.n
     max_len = args.prompt_len + args.resp_max
     eng = LLMEngine(m, EngineConfig(block_size=32, max_num_seqs=S, max_model_len=max_len,
-                                    max_num_batched_tokens=max(16384, max_len), gpu_memory_utilization=0.4))
+                                    max_num_batched_tokens=max(16384, max_len), gpu_memory_utilization=0.4,
+                                    sync_interval=args.sync_interval))
     times, toks = [], []
     for r in range(args.rounds + 1):
         rows, lens = workload(a.vocab_size, args.prompts, args.n, args.prompt_len, args.resp_min, args.resp_max, 100 + r)
@@ -98,6 +99,7 @@ def main() -> None:
     ap.add_argument("--resp-min", type=int, default=256)
     ap.add_argument("--resp-max", type=int, default=1024)
     ap.add_argument("--rounds", type=int, default=3)
+    ap.add_argument("--sync-interval", type=int, default=16, help="ours: decode steps between host harvests")
     args = ap.parse_args()
     a = PRESETS[args.model]
     times, toks = (run_ours if args.impl == "ours" else run_vllm)(args, a)
@@ -106,6 +108,8 @@ def main() -> None:
            "response_len": f"uniform[{args.resp_min},{args.resp_max}]", "rounds": len(times),
            "seconds_per_round": [round(t, 4) for t in times], "generated_tokens_per_round": toks,
            "gen_tokens_per_s_mean": sum(toks) / sum(times), "gen_tokens_per_s_best": toks[best] / times[best]}
+    if args.impl == "ours":
+        out["sync_interval"] = args.sync_interval
     if args.impl == "vllm":
         import vllm
 

@@ -113,6 +113,10 @@ class EngineConfig:
     graph_batch_sizes: Sequence[int] = (8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024)
     reserve_full_length: bool = True
     fused_decode: bool = True  # split-K projections with fused partial-sum consumers on the decode path
+    # CUDA only: the host reads each interval's finish flags from a snapshot while the *next* interval of decode steps
+    # already runs, instead of draining the stream after every interval (finished sequences are retired one interval
+    # later; their rows are inactive in the meantime)
+    overlap_harvest: bool = True
 
 
 def _rt():
@@ -207,6 +211,9 @@ class LLMEngine:
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_calls": 0,
                       "graph_replays": 0, "preemptions": 0}
         self._finished: List[RequestOutput] = []
+        self._snap = None  # pending (event, finish flags, generated counts, slots covered) of the last decode interval
+        self._fetch_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        self._snap_bufs = None
 
     # ------------------------------------------------------------------ memory
     def _kv_block_bytes(self) -> int:
@@ -626,21 +633,70 @@ class LLMEngine:
         self._graphs[n] = g
         return g
 
+    def _take_snapshot(self) -> None:
+        """Enqueue (behind everything issued so far) a copy of the finish flags and token counts into pinned host
+        memory and an event that marks it complete; ``_process_snapshot`` consumes it later without draining the stream."""
+        hi = self._hi()
+        if hi == 0:
+            self._snap = None
+            return
+        S = self.cfg.max_num_seqs
+        if self._snap_bufs is None:
+            self._snap_bufs = [(torch.empty(S, dtype=torch.int32, pin_memory=True), torch.empty(S, dtype=torch.int32, pin_memory=True))
+                               for _ in range(2)]
+            self._snap_flip = 0
+        self._snap_flip ^= 1
+        fr, gc = self._snap_bufs[self._snap_flip]
+        fr[:hi].copy_(self.finish_reason[:hi], non_blocking=True)
+        gc[:hi].copy_(self.gen_count[:hi], non_blocking=True)
+        _lib.D2H_BYTES += 8 * hi
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._snap = (ev, fr, gc, hi)
+
+    def _process_snapshot(self) -> None:
+        """Retire what the pending snapshot shows as finished.  Outputs are fetched on a side stream that waits for the
+        snapshot's event only, so decode steps already enqueued behind it keep running meanwhile (finished rows are
+        inactive: nothing writes them)."""
+        snap, self._snap = self._snap, None
+        if snap is None:
+            return
+        ev, fr_t, gc_t, hi = snap
+        ev.synchronize()
+        fr, gc = fr_t[:hi].numpy(), gc_t[:hi].numpy()
+        self._harvest_from(fr, gc, hi, fetch_after=ev)
+
     def _harvest(self) -> None:
         hi = self._hi()
         if hi == 0:
             return
-        fr = _lib.to_host(self.finish_reason[:hi])
-        gc = _lib.to_host(self.gen_count[:hi])
+        self._harvest_from(_lib.to_host(self.finish_reason[:hi]), _lib.to_host(self.gen_count[:hi]), hi)
+
+    def _drain(self) -> None:
+        """Bring the host's view up to date with the device (pending snapshot, then a synchronous harvest)."""
+        if self._snap is not None:
+            self._process_snapshot()
+        self._harvest()
+
+    def _harvest_from(self, fr, gc, hi: int, fetch_after=None) -> None:
         done = [s for s in range(hi) if self._slot_req[s] is not None and int(fr[s]) != 0]
         stop_str = [s for s in range(hi) if self._slot_req[s] is not None and int(fr[s]) == 0
                     and self._slot_req[s].params.stop and self.detokenize is not None]
         fetch = done + stop_str
         if not fetch:
             return
-        idx = torch.tensor(fetch, device=self.device, dtype=torch.long)
-        toks = _lib.to_host(self.out_tokens[idx])
-        lps = _lib.to_host(self.out_logprobs[idx])
+        nmax = max(1, max(int(gc[s]) for s in fetch))
+        if fetch_after is not None:
+            # only the copies run on the side stream; every write to the slot state below stays on the main stream
+            with torch.cuda.stream(self._fetch_stream):
+                self._fetch_stream.wait_event(fetch_after)
+                idx = torch.tensor(fetch, device=self.device, dtype=torch.long)
+                toks = _lib.to_host(self.out_tokens[idx, :nmax])
+                lps = _lib.to_host(self.out_logprobs[idx, :nmax])
+        else:
+            idx = torch.tensor(fetch, device=self.device, dtype=torch.long)
+            toks = _lib.to_host(self.out_tokens[idx, :nmax])
+            lps = _lib.to_host(self.out_logprobs[idx, :nmax])
         for k, s in enumerate(fetch):
             req = self._slot_req[s]
             n = int(gc[s])
@@ -734,6 +790,21 @@ class LLMEngine:
             req = self._reqs.pop(failed[i], None)
             if req is not None:
                 self._finished.append(RequestOutput(req.rid, req.prompt, [], [], "abort", weight_version=self.weight_version))
+        if self.is_cuda and self.cfg.overlap_harvest:
+            # a snapshot that has already landed costs nothing to read: use it before deciding what to launch
+            if self._snap is not None and self._snap[0].query():
+                self._process_snapshot()
+                self._compact_slots() if any(r is not None for r in self._slot_req) else None
+            if any(r is not None for r in self._slot_req):
+                self._run_decode(self.cfg.sync_interval)  # enqueue the next interval first ...
+                self._process_snapshot()                  # ... then read the previous one while it runs
+                if any(r is not None for r in self._slot_req):
+                    self._compact_slots()
+                self._take_snapshot()
+            else:
+                self._process_snapshot()
+            out, self._finished = self._finished, []
+            return out
         self._harvest()  # requests that finished on their very first token
         if any(r is not None for r in self._slot_req):
             self._compact_slots()
@@ -767,7 +838,7 @@ class LLMEngine:
             while self.has_unfinished():
                 out.extend(self.step())
         elif mode == "abort":
-            self._harvest()
+            self._drain()
             hi = self._hi()
             gc = self.gen_count[:hi].cpu() if hi else []
             for s in range(hi):
@@ -800,6 +871,7 @@ class LLMEngine:
 
     def _requeue_running(self) -> None:
         """Move every slot's request back to the waiting queue, keeping the tokens generated so far."""
+        self._drain()
         hi = self._hi()
         if hi == 0:
             return

@@ -78,6 +78,11 @@ def get_tokenizer(name_or_path: Optional[str], vocab_size: Optional[int] = None,
             tail = str(name_or_path).rsplit("-", 1)[1]
             vocab_size = int(tail) if tail.isdigit() else None
         return SyntheticTokenizer(vocab_size or 1024)
+    import os
+
+    if vocab_size is not None and not os.path.isdir(str(name_or_path)):
+        # an architecture preset (random weights, no checkpoint directory): there is no vocabulary file to load
+        return SyntheticTokenizer(vocab_size)
     from transformers import AutoTokenizer
 
     tok = AutoTokenizer.from_pretrained(name_or_path, padding_side="left", **kw)

@@ -42,3 +42,67 @@ def test_custom_registrations_import():
     importlib.import_module("examples.algorithms.custom_policy_loss")
     assert rl.AdvantageEstimatorRegistry.get("centered_reward") is not None
     assert rl.PolicyLossRegistry.get("capped_reinforce") is not None
+
+
+# ----------------------------------------------------------------------------- executed, not only parsed
+import json  # noqa: E402
+import subprocess  # noqa: E402
+
+import pytest  # noqa: E402
+
+
+def _tiny_gsm8k(d):
+    import pandas as pd
+
+    rows = []
+    for i in range(16):
+        rows.append({"prompt": [{"role": "user", "content": f"what is {i} plus {i} ?"}], "env_class": "gsm8k",
+                     "reward_spec": {"method": "rule", "ground_truth": str(2 * i)}, "uid": f"q{i}"})
+    os.makedirs(d, exist_ok=True)
+    pd.DataFrame(rows).to_parquet(os.path.join(d, "train.parquet"))
+    pd.DataFrame(rows[:4]).to_parquet(os.path.join(d, "validation.parquet"))
+    with open(os.path.join(d, "sft.jsonl"), "w") as f:
+        for i in range(16):
+            f.write(json.dumps({"messages": [{"role": "user", "content": f"say {i}"},
+                                             {"role": "assistant", "content": f"{i} {i + 1} {i + 2}"}]}) + "\n")
+
+
+_TINY_RL = ["trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "trainer.critic_mini_batch_size=4",
+            "generator.n_samples_per_prompt=2", "trainer.max_prompt_length=64",
+            "generator.sampling_params.max_generate_length=8", "trainer.max_tokens_per_microbatch=4096",
+            "trainer.bf16=false", "trainer.gradient_checkpointing=false", "trainer.max_training_steps=1",
+            "trainer.epochs=1", "trainer.eval_interval=0", "trainer.eval_before_train=false", "trainer.ckpt_interval=0",
+            "trainer.hf_save_interval=0", "generator.inference_engine.enforce_eager=true",
+            "generator.inference_engine.max_num_seqs=16", "trainer.resume_mode=none", "trainer.logger=console"]
+
+
+@pytest.mark.parametrize("script,extra", [
+    ("examples/gsm8k/run_gsm8k_grpo.sh", []),
+    # all-zero rewards are never informative: the DAPO filter keeps sampling until it gives up after two batches
+    ("examples/algorithms/run_dapo.sh", ["trainer.algorithm.dynamic_sampling.max_sample_batches=2"]),
+    ("examples/ppo/run_ppo_gsm8k.sh", []),
+    ("examples/sft/run_sft.sh", None),
+])
+def test_example_scripts_run_on_cpu(tmp_path, script, extra):
+    """The launch scripts themselves are executed (bash, the launcher, the entry point) on a tiny preset and data."""
+    path = os.path.join(ROOT, script)
+    if not os.path.exists(path):
+        alt = sorted(glob.glob(os.path.join(ROOT, os.path.dirname(script), "*.sh")))
+        assert alt, script
+        path = alt[0]
+    data = str(tmp_path / "data")
+    _tiny_gsm8k(data)
+    env = dict(os.environ, MODEL="tiny-llama", DATA=data, NGPU="1", HOME=str(tmp_path), PYTHONPATH=ROOT,
+               CUDA_VISIBLE_DEVICES="", SFT_DATA=os.path.join(data, "sft.jsonl"), OMP_NUM_THREADS="2")
+    if extra is None:  # SFT
+        args = ["batch_size=4", "max_length=64", "max_tokens_per_microbatch=512", "num_steps=2", "bf16=false",
+                f"ckpt_path={tmp_path}/ckpt", "ckpt_interval=0"]
+    else:
+        args = _TINY_RL + [f"trainer.ckpt_path={tmp_path}/ckpt", f"trainer.export_path={tmp_path}/export",
+                           f"trainer.log_path={tmp_path}/logs"] + extra
+    p = subprocess.run(["bash", path, *args], cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    tail = p.stdout[-2500:] + p.stderr[-2500:]
+    if script.endswith("run_dapo.sh"):
+        assert p.returncode != 0 and "max_sample_batches" in tail, tail
+    else:
+        assert p.returncode == 0, tail
