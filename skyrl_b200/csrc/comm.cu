@@ -54,6 +54,8 @@ __global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int world, int chan
 __global__ void peer_barrier_counter_kernel(PeerPtrs pads, int rank, int world, int channel, int* epoch_counter,
                                             unsigned long long wait_ns, int* status) {
   __shared__ int epoch_s;
+  pdl_launch_dependents();
+  pdl_wait();  // the predecessor's stores (its peer stores included) are complete and visible before we signal
   if (threadIdx.x == 0) {
     epoch_s = *epoch_counter + 1;
     *epoch_counter = epoch_s;
@@ -281,9 +283,10 @@ int sb_peer_barrier_counter(void* const* pads, int rank, int world, int channel,
   if (world < 1 || world > sb::kMaxPeers || channel < 0 || channel >= 8 || !epoch_counter) return SB_ERR_ARG;
   int* st = sb::device_status_ptr();
   if (st == nullptr) return SB_ERR_CUDA;
-  sb::peer_barrier_counter_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      sb::make_ptrs(pads, world), rank, world, channel, epoch_counter, wait_ns, st);
-  return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+  const cudaError_t e = sb::launch_pdl(sb::peer_barrier_counter_kernel, dim3(1), dim3(32), 0,
+                                       reinterpret_cast<cudaStream_t>(stream), sb::make_ptrs(pads, world), rank, world, channel,
+                                       epoch_counter, wait_ns, st);
+  return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 
 int sb_peer_reduce_scatter_f32(void* const* grads, int world, long long lo, long long n, float* out, float* sq_partial,

@@ -397,7 +397,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                           (rel - dest * tp.seg_w[sg]));
           } else if (tp.scatter_all) {
             // all-reduce layout: every rank receives this rank's partial rows in slot my_rank
-            const long long off = tp.my_rank * tp.slot_stride + static_cast<long long>(row) * ldc + col0;
+            // (with split-K, k slice ks of rank r fills slot r * splits + ks: the consumer adds n_ranks * splits slots)
+            const long long off = (static_cast<long long>(tp.my_rank) * splits + ks) * tp.slot_stride +
+                                  static_cast<long long>(row) * ldc + col0;
 #pragma unroll 1
             for (int d = 0; d < tp.n_ranks; ++d) store_chunk(tp.dst[(tp.my_rank + d) % tp.n_ranks], off);
           } else {
@@ -551,7 +553,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
 template <int BN, bool B_MN, bool GATHER, bool SCATTER>
 static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                           long long ldb, long long ldc, int out_mode, const TpArgs& tp, cudaStream_t stream,
-                          int b_groups = 1) {
+                          int b_groups = 1, int splits = 1) {
   using Cfg = GemmCfg<BN>;
   const CUtensorMap* ta = get_tmap_bf16_2d(A, M, K, lda, kBM);
   const CUtensorMap* tb = B_MN ? get_tmap_bf16_2d(B, static_cast<long long>(K) * b_groups, N, ldb, 64)
@@ -567,7 +569,7 @@ static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bia
     attr_set = true;
   }
   const int m_blocks = (M + kBM - 1) / kBM;
-  const int tiles = m_blocks * ((N + BN - 1) / BN);
+  const int tiles = m_blocks * ((N + BN - 1) / BN) * splits;
   if (GATHER) {
     // piece counters and the ticket start at zero for every launch
     if (cudaMemsetAsync(tp.flags, 0, sizeof(unsigned int) * (m_blocks + 1), stream) != cudaSuccess) return SB_ERR_CUDA;
@@ -575,6 +577,14 @@ static int launch_gemm_tp(const void* A, const void* B, void* C, const void* bia
   // with GATHER every CTA also carries copy warps, so launch the full machine even for few tiles
   const int grid = GATHER ? sm_count() : (tiles < sm_count() ? tiles : sm_count());
   const int threads = kGemmThreads + (GATHER ? kGatherWarps * 32 : 0);
+  if (!GATHER) {
+    // scatter modes sit in the decode chain of tensor-parallel engines: let the prologue (barrier set-up, tensor
+    // memory allocation) overlap the tail of the preceding kernel; every operand access comes after pdl_wait()
+    const cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(threads), Cfg::kSmemBytes, stream, *ta, *tb, C,
+                                     reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, out_mode, splits, 0LL,
+                                     device_status_ptr(), tp, 0);
+    return e == cudaSuccess ? SB_OK : SB_ERR_CUDA;
+  }
   kfn<<<grid, threads, Cfg::kSmemBytes, stream>>>(*ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc,
                                                   out_mode, 1, 0, device_status_ptr(), tp, 0);
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
@@ -801,6 +811,34 @@ int sb_gemm_tp(const void* A, const void* B, void* C, const void* bias, int M, i
   SB_TP_CASE(256, true, false, true)
 #undef SB_TP_CASE
   return SB_ERR_ARG;
+}
+
+// Row-parallel projection of a tensor-parallel decode step: x[M, K_local] @ W[N, K_local]^T as fp32 split-K partial
+// sums stored from the epilogue into EVERY rank's slot buffer (all-reduce layout).  Slot (my_rank * splits + ks) of
+// each destination receives k slice ks; a consumer (fused residual + RMSNorm) adds the n_ranks * splits slots after a
+// barrier.  Split-K is what lets a skinny projection (M <= 256 rows) stream its weights with all SMs.
+int sb_gemm_tp_scatter_splitk(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                              void* const* outs, int n_ranks, int my_rank, long long slot_stride, int splits,
+                              void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (K & 7) || !outs) return SB_ERR_ARG;
+  if (n_ranks < 1 || n_ranks > sb::kTpMaxRanks || my_rank < 0 || my_rank >= n_ranks) return SB_ERR_ARG;
+  const int k_blocks = (K + sb::kBK - 1) / sb::kBK;
+  if (splits < 1 || splits > k_blocks) return SB_ERR_ARG;
+  const int kpb = (k_blocks + splits - 1) / splits;
+  if ((k_blocks + kpb - 1) / kpb != splits) return SB_ERR_ARG;  // an empty slice would leave its slot unwritten
+  sb::TpArgs tp{};
+  tp.n_ranks = n_ranks;
+  tp.my_rank = my_rank;
+  tp.rows_per_rank = M;
+  tp.lda = lda;
+  tp.slot_stride = slot_stride;
+  tp.scatter_all = 1;
+  for (int r = 0; r < n_ranks; ++r) {
+    if (!outs[r]) return SB_ERR_ARG;
+    tp.dst[r] = outs[r];
+  }
+  return sb::launch_gemm_tp<128, false, false, true>(A, B, nullptr, nullptr, M, N, K, lda, ldb, N, 1, tp,
+                                                     reinterpret_cast<cudaStream_t>(stream), 1, splits);
 }
 
 

@@ -355,7 +355,7 @@ class LLMEngine:
             if pending is None:
                 _, h = ew.add_rmsnorm(x, None, m.p(pre + "ln1"), a.rms_norm_eps)
             else:
-                h = ew.add_rmsnorm_partials_(x, pending, tp, m.p(pre + "ln1"), a.rms_norm_eps)
+                h = ew.add_rmsnorm_partials_(x, pending, pending.shape[0], m.p(pre + "ln1"), a.rms_norm_eps)
             part, np_ = self._splitk_linear(h, m.p(pre + "wqkv"), m._p.get(pre + "bqkv"), n)
             ew.qkv_finalize(part, np_, self.positions[:n], table, qkv, self.k_cache[i], self.v_cache[i], self.slots[:n],
                             a.num_heads, a.num_kv_heads, a.head_dim)
@@ -363,13 +363,13 @@ class LLMEngine:
                                              self.ctx_lens[:n], a.num_heads, a.num_kv_heads, a.head_dim,
                                              max_ctx=self.cfg.max_model_len)
             parts_o = m.row_parallel_partials(att, m.p(pre + "wo"), "decode_o", torch.float32, DECODE_CHANNELS[0], True)
-            h = ew.add_rmsnorm_partials_(x, parts_o, tp, m.p(pre + "ln2"), a.rms_norm_eps)
+            h = ew.add_rmsnorm_partials_(x, parts_o, parts_o.shape[0], m.p(pre + "ln2"), a.rms_norm_eps)
             if fused_mlp:
                 act = gemm.gate_up_swiglu(h, m.p(pre + "wgu"), need_gu=False)[1]
             else:
                 act = ew.swiglu(gemm.gemm_nt(h, m.p(pre + "wgu"), static_w=True))
             pending = m.row_parallel_partials(act, m.p(pre + "wd"), "decode_d", torch.float32, DECODE_CHANNELS[1], True)
-        h = ew.add_rmsnorm_partials_(x, pending, tp, m.p("final_norm"), a.rms_norm_eps)
+        h = ew.add_rmsnorm_partials_(x, pending, pending.shape[0], m.p("final_norm"), a.rms_norm_eps)
         logits = gemm.gemm_nt(h, m.lm_head_weight(), static_w=True)
         self._sample(logits, n, masked)
         self._advance(n)

@@ -66,13 +66,22 @@ class TPEngineModel(CausalLM):
         """``x_local [T, K/tp] @ w_shard^T`` stored into slot ``rank`` of every rank's buffer; returns this rank's
         ``[tp, T, N]`` view once all ranks' partials have landed (the barrier is enqueued on the stream)."""
         T, N = x_local.shape[0], w_shard.shape[0]
-        st = self.slots(tag, T, N, dtype)
-        tpm.gemm_reduce_scatter(self.tp, x_local, w_shard, _View(st, self.tp.size * T * N), T, all_ranks=True)
+        splits = 1
+        if replayable and dtype == torch.float32 and T <= 256:
+            # decode: a skinny GEMM has too few output tiles for 148 SMs; k slices fill the machine and the consumer
+            # adds tp * splits partials instead of tp
+            splits = tpm.plan_scatter_splitk(T, N, x_local.shape[1])
+        P = self.tp.size * splits
+        st = self.slots(tag, T * splits, N, dtype)
+        if splits > 1:
+            tpm.gemm_all_reduce_partials(self.tp, x_local, w_shard, _View(st, P * T * N), splits)
+        else:
+            tpm.gemm_reduce_scatter(self.tp, x_local, w_shard, _View(st, P * T * N), T, all_ranks=True)
         if replayable:
             self.tp.peer.barrier_replayable(channel)
         else:
             self.tp.peer.barrier(channel)
-        return st.local[: self.tp.size * T * N].view(self.tp.size, T, N)
+        return st.local[: P * T * N].view(P, T, N)
 
     def row_parallel_linear(self, x_local: torch.Tensor, w_shard: torch.Tensor, tag: str, channel: int) -> torch.Tensor:
         """All-reduced ``[T, N]`` output (prefill path and CPU reference)."""

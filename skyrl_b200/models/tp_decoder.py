@@ -418,6 +418,28 @@ class EPCausalLM(CausalLM):
             prm.copy_(self._shard(name, full.p(name).detach()).to(prm.dtype))
 
     @torch.no_grad()
+    def init_random_on_device(self, seed: int = 0) -> None:
+        """Random initialisation without a host copy of the full model (tens of billions of parameters): replicated
+        parameters are drawn from a generator seeded by (seed, parameter index), identical on every rank; each rank
+        draws only its own experts, from a generator that also depends on the expert's global index."""
+        dev = self.flat_params.device
+        std = self.full_args.init_std
+        el = self.full_args.num_experts // self.ep.size
+        for k, (name, prm) in enumerate(self.named_flat_views()):
+            leaf = name.split(".")[-1]
+            if leaf in ("ln1", "ln2", "final_norm", "q_norm", "k_norm"):
+                prm.fill_(1.0)
+            elif leaf == "bqkv":
+                prm.zero_()
+            elif leaf in EXPERT_LEAVES:
+                for e in range(el):
+                    g = torch.Generator(device=dev).manual_seed((seed * 1000003 + k) * 4099 + self.ep.rank * el + e)
+                    prm[e].normal_(0.0, std, generator=g)
+            else:
+                g = torch.Generator(device=dev).manual_seed(seed * 1000003 + k)
+                prm.normal_(0.0, std, generator=g)
+
+    @torch.no_grad()
     def gather_full_state(self) -> Dict[str, torch.Tensor]:
         out = {}
         for name, prm in self.named_flat_views():

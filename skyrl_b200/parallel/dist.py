@@ -108,6 +108,35 @@ def build_mesh(tp: int, env: Optional[DistEnv] = None) -> ParallelMesh:
     return mesh
 
 
+_HSDP: dict = {}
+
+
+def build_hsdp_groups(fsdp_size: int, env: Optional[DistEnv] = None):
+    """``(shard_group, replica_group)`` of a hybrid-sharded layout: runs of ``fsdp_size`` consecutive ranks shard the
+    optimizer state among themselves; ranks with the same position in different runs are replicas of each other.
+    Collective: every rank must call it (reference mesh: skyrl/backends/skyrl_train/distributed/fsdp_utils.py:254-261)."""
+    env = env or get_env()
+    if fsdp_size in _HSDP:
+        return _HSDP[fsdp_size]
+    W, r = env.world_size, env.rank
+    if fsdp_size < 1 or W % fsdp_size != 0:
+        raise ValueError(f"fsdp_size {fsdp_size} does not divide the world size {W}")
+    shard = replica = None
+    if W > 1 and dist.is_initialized():
+        for g in range(W // fsdp_size):
+            ranks = list(range(g * fsdp_size, (g + 1) * fsdp_size))
+            grp = dist.new_group(ranks)
+            if r in ranks:
+                shard = grp
+        for t in range(fsdp_size):
+            ranks = list(range(t, W, fsdp_size))
+            grp = dist.new_group(ranks)
+            if r in ranks:
+                replica = grp
+    _HSDP[fsdp_size] = (shard, replica)
+    return _HSDP[fsdp_size]
+
+
 def get_env() -> DistEnv:
     return _ENV if _ENV is not None else init_distributed()
 
@@ -145,3 +174,4 @@ def shutdown() -> None:
         dist.destroy_process_group()
     _ENV = None
     _MESHES.clear()
+    _HSDP.clear()

@@ -40,11 +40,16 @@ class ShardedAdamW:
                  eps: float = 1e-8, weight_decay: float = 0.01, max_grad_norm: float = 1.0,
                  group: Optional[dist.ProcessGroup] = None, transport: str = "auto", peer_ctx=None,
                  numel: Optional[int] = None, params_symm=None, grads_symm=None, norm_group=None,
-                 dup_ranges=None, count_dups: bool = True):
+                 dup_ranges=None, count_dups: bool = True, replica_group: Optional[dist.ProcessGroup] = None):
         """``norm_group`` / ``dup_ranges`` / ``count_dups`` serve tensor parallelism: the gradient norm is also summed
         over ``norm_group`` (the TP group), and the flat-buffer ranges listed in ``dup_ranges`` (parameters replicated
-        across that group) enter the norm on one rank only (``count_dups``)."""
+        across that group) enter the norm on one rank only (``count_dups``).
+
+        ``replica_group`` enables hybrid sharding (the reference's HSDP mesh ``ddp x fsdp``, fsdp_utils.py:254-261):
+        optimizer state is sharded over ``group`` only, and ranks that hold the same shard in different groups sum
+        their reduced gradients over ``replica_group`` before the (identical) update."""
         self.group = group
+        self.replica_group = replica_group
         self.norm_group, self.dup_ranges, self.count_dups = norm_group, list(dup_ranges or []), count_dups
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -95,6 +100,10 @@ class ShardedAdamW:
         else:
             dist.reduce_scatter_tensor(self._grad_shard, self.grads, op=dist.ReduceOp.SUM, group=self.group)
             g = self._grad_shard
+        if self.replica_group is not None and dist.get_world_size(self.replica_group) > 1:
+            if g is self.grads:
+                g = self.grads  # one-rank shard group: the whole gradient is "the shard"
+            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.replica_group)
         self._sq.zero_()
         optim_ops.sqnorm_accum(g, self._sq)
         if self.dup_ranges and not self.count_dups:

@@ -36,6 +36,7 @@ def _k():
     if not _cfg:
         vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         lib.sb_gemm_tp.argtypes = [vp, vp, vp, vp, ci, ci, ci, cl, cl, cl, ci, ci, ci, ci, vp, vp, ci, ci, ci, cl, vp, ci, vp]
+        lib.sb_gemm_tp_scatter_splitk.argtypes = [vp, vp, ci, ci, ci, cl, cl, vp, ci, ci, cl, ci, vp]
         _cfg = True
     return lib
 
@@ -121,6 +122,29 @@ def gemm_reduce_scatter(tp: TPGroup, x: torch.Tensor, w: torch.Tensor, slots: Sy
                            1 if out_fp32 else 0, 0, 2 if all_ranks else 1, None, outs, tp.size, tp.rank,
                            rows_per_rank if not all_ranks else M, rows * N, None, 0, _lib.stream_ptr())
     _lib.check(code, "sb_gemm_tp(scatter)")
+
+
+def plan_scatter_splitk(M: int, N: int, K: int, n_sm: int = 148) -> int:
+    """k slices for a skinny row-parallel projection so that (tiles x slices) covers the SMs (128-wide N tiles)."""
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    k_blocks = (K + 63) // 64
+    if tiles >= n_sm or k_blocks < 8:
+        return 1
+    splits = max(1, min(n_sm // tiles, k_blocks // 4))
+    kpb = (k_blocks + splits - 1) // splits
+    return (k_blocks + kpb - 1) // kpb  # no empty slice
+
+
+def gemm_all_reduce_partials(tp: "TPGroup", x: torch.Tensor, w: torch.Tensor, slots: SymmTensor, splits: int) -> None:
+    """``x_local @ W_shard^T`` as ``splits`` fp32 k-slice partials stored into slots ``[rank * splits, (rank + 1) *
+    splits)`` of *every* rank's ``[size * splits, M, N]`` buffer (decode path of tensor-parallel engines).  A
+    ``tp.peer`` barrier must pass before the slots are read."""
+    M, K = x.shape
+    N = w.shape[0]
+    outs = (ctypes.c_void_p * tp.size)(*slots.ptrs)
+    code = _k().sb_gemm_tp_scatter_splitk(x.data_ptr(), w.data_ptr(), M, N, K, x.stride(0), w.stride(0), outs, tp.size,
+                                          tp.rank, M * N, splits, _lib.stream_ptr())
+    _lib.check(code, "sb_gemm_tp_scatter_splitk")
 
 
 def reduce_slots(slots: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:

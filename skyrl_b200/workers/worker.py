@@ -204,9 +204,14 @@ class ModelWorker:
             ep_peer = PeerContext(dev, group=self.mesh.tp_group) if dev.type == "cuda" else None
             self.tp = TPGroup(ep_peer, self.mesh.tp_group)
             model = EPCausalLM(resolve_model_args(model_path), self.tp, device=dev, dtype=dtype, seed=None)
-            full = build_model(model_path, device="cpu", dtype=torch.float32, seed=seed)
-            model.load_from_full(full)
-            del full
+            from ..models.decoder import PRESETS
+
+            if model_path in PRESETS and dev.type == "cuda" and model.num_parameters() > 2_000_000_000:
+                model.init_random_on_device(seed)
+            else:
+                full = build_model(model_path, device="cpu", dtype=torch.float32, seed=seed)
+                model.load_from_full(full)
+                del full
             peer_ctx = None
         use_peer = peer_ctx is not None and trainable and self.env.world_size > 1 and dev.type == "cuda"
         sp_size = self._sp_size_from_cfg(cfg) if model is None and tp_size == 1 else 1
@@ -280,6 +285,15 @@ class ModelWorker:
                     dups = [(o, o + n) for name, (o, n) in model.offsets.items() if name.split(".")[-1] in rep]
                 extra = dict(group=self.mesh.dp_group, transport="nccl", norm_group=self.mesh.tp_group, dup_ranges=dups,
                              count_dups=self.mesh.tp_rank == 0)
+            node = {"policy": cfg.policy, "critic": cfg.critic}.get(self.role, cfg.policy)
+            fsdp_size = int(getattr(getattr(node, "fsdp_config", None), "fsdp_size", -1) or -1)
+            if self.mesh is None and 0 < fsdp_size < self.env.world_size and dist.is_initialized():
+                # hybrid sharding: optimizer state sharded inside groups of fsdp_size ranks, replicated across them
+                from ..parallel.dist import build_hsdp_groups
+
+                shard_g, replica_g = build_hsdp_groups(fsdp_size, self.env)
+                extra = dict(group=shard_g, replica_group=replica_g, transport="nccl")
+                peer_ctx = None
             self.optimizer = ShardedAdamW(model.flat_params, flat_grad, lr=ocfg.lr, betas=tuple(ocfg.adam_betas),
                                           weight_decay=ocfg.weight_decay, max_grad_norm=ocfg.max_grad_norm,
                                           peer_ctx=peer_ctx, params_symm=self.params_symm, grads_symm=self.grads_symm,

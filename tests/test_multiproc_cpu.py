@@ -70,3 +70,8 @@ def test_gloo_rl_step_with_tensor_parallel_engine():
         p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-llama",
                   "--prompts-per-gpu", "1", *extra], port=port)
         assert p.returncode == 0 and '"n_gpus": 2' in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_gloo_hybrid_sharded_optimizer_four_ranks():
+    p = _run([os.path.join(ROOT, "tests", "mp", "hsdp_check.py")], nproc=4, port=29651)
+    assert p.returncode == 0 and "HSDP_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
