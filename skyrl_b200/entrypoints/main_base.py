@@ -107,6 +107,7 @@ class BasePPOExp:
         tracker = self.get_tracker()
         trainer = self.get_trainer(self.cfg, tracker, self.tokenizer, self.train_dataset, self.eval_dataset, client,
                                    generator)
+        trainer.rollout_servers_in_box = bool(getattr(self, "rollout_servers_in_box", False))
         trainer.build_models()
         return trainer
 
@@ -149,9 +150,96 @@ def _resolve_override_entrypoint(cfg: SkyRLTrainConfig):
     return getattr(importlib.import_module(mod), name or "Exp")
 
 
+def split_roles(cfg: SkyRLTrainConfig) -> Optional[str]:
+    """Disaggregated placement inside one launch (``trainer.placement.colocate_all=false`` with locally run engines):
+    the first ``policy_num_gpus_per_node`` ranks train, the remaining ``num_engines`` ranks only serve rollouts.
+
+    The split happens *before* any process group exists: each side becomes its own ``torch.distributed`` world (own
+    RANK / WORLD_SIZE / MASTER_PORT; LOCAL_RANK keeps naming the physical GPU), the rollout side runs the serving
+    entry point on fixed ports and the training side talks to it like to any stand-alone server -- requests over
+    HTTP, weights by peer stores into the servers' exported parameter buffers.  Returns ``"train"``, ``"rollout"`` or
+    ``None`` (colocated / single process / external servers).  Reference topology: non-colocated placement of
+    skyrl/train/fully_async_trainer.py:392 with weight sync per worker_dispatch.py:693-707."""
+    import os
+
+    ie, pl = cfg.generator.inference_engine, cfg.trainer.placement
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if pl.colocate_all or not ie.run_engines_locally or world <= 1 or ie.external_server_urls or ie.external_proxy_url:
+        return None
+    if "SKYRL_B200_ROLE" in os.environ:  # already split (the environment was rewritten below)
+        return os.environ["SKYRL_B200_ROLE"]
+    n_train = int(pl.policy_num_gpus_per_node) * int(pl.policy_num_nodes)
+    n_roll = int(ie.num_engines) * int(ie.tensor_parallel_size or 1)
+    if n_train + n_roll != world:
+        raise ValueError(f"disaggregated placement needs policy GPUs ({n_train}) + rollout GPUs ({n_roll}) == world size "
+                         f"({world}); set trainer.placement.policy_num_gpus_per_node and generator.inference_engine.num_engines")
+    if int(ie.tensor_parallel_size or 1) != 1:
+        raise ValueError("rollout-only ranks serve unsharded engines (tensor_parallel_size=1)")
+    rank = int(os.environ.get("RANK", "0"))
+    port = int(os.environ.get("MASTER_PORT", "29500"))
+    base = int(os.environ.get("SKYRL_B200_ROLLOUT_BASE_PORT", str(port + 100)))
+    os.environ["SKYRL_B200_ROLLOUT_URLS"] = ",".join(f"http://127.0.0.1:{base + j}" for j in range(n_roll))
+    os.environ["SKYRL_B200_ROLLOUT_BASE_PORT"] = str(base)
+    if rank < n_train:
+        os.environ.update(WORLD_SIZE=str(n_train), RANK=str(rank), SKYRL_B200_ROLE="train")
+        return "train"
+    os.environ.update(WORLD_SIZE=str(n_roll), RANK=str(rank - n_train), MASTER_PORT=str(port + 1), SKYRL_B200_ROLE="rollout")
+    return "rollout"
+
+
+def _wait_for_servers(urls: List[str], timeout_s: float = 600.0) -> None:
+    import time
+    import urllib.request
+
+    t0 = time.time()
+    pending = list(urls)
+    while pending:
+        for u in list(pending):
+            try:
+                with urllib.request.urlopen(u + "/health", timeout=2) as r:
+                    if r.status == 200:
+                        pending.remove(u)
+            except Exception:
+                pass
+        if pending:
+            if time.time() - t0 > timeout_s:
+                raise TimeoutError(f"rollout servers did not come up: {pending}")
+            time.sleep(0.5)
+
+
+def _shutdown_servers(urls: List[str]) -> None:
+    import urllib.request
+
+    for u in urls:
+        try:
+            urllib.request.urlopen(urllib.request.Request(u + "/skyrl/v1/shutdown", data=b"{}", method="POST"), timeout=5)
+        except Exception:
+            pass
+
+
 def main(argv: Optional[List[str]] = None) -> None:
+    import os
+
     cfg = SkyRLTrainConfig.from_cli_overrides(sys.argv[1:] if argv is None else argv)
-    _resolve_override_entrypoint(cfg)(cfg).run()
+    role = split_roles(cfg)
+    if role == "rollout":
+        from .serve import InferenceOnlyEntrypoint
+
+        cfg.trainer.placement.colocate_all = True  # the serving entry point owns its GPU
+        InferenceOnlyEntrypoint(cfg, base_port=int(os.environ["SKYRL_B200_ROLLOUT_BASE_PORT"])).run(with_router=False)
+        return
+    urls: List[str] = []
+    if role == "train":
+        urls = os.environ["SKYRL_B200_ROLLOUT_URLS"].split(",")
+        cfg.generator.inference_engine.external_server_urls = urls
+        _wait_for_servers(urls)
+    exp = _resolve_override_entrypoint(cfg)(cfg)
+    exp.rollout_servers_in_box = role == "train"
+    try:
+        exp.run()
+    finally:
+        if role == "train" and int(os.environ.get("RANK", "0")) == 0:
+            _shutdown_servers(urls)
 
 
 if __name__ == "__main__":

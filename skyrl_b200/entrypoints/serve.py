@@ -54,7 +54,7 @@ class InferenceOnlyEntrypoint(BasePPOExp):
             self._router.stop()
         self._servers, self._router = [], None
 
-    def start(self) -> dict:
+    def start(self, with_router: bool = True) -> dict:
         """Bring the servers up and return the address record (does not block)."""
         from ..engine.llm_engine import LLMEngine
         from ..inference.local_client import LocalInferenceClient
@@ -64,8 +64,16 @@ class InferenceOnlyEntrypoint(BasePPOExp):
         from ..train.trainer import PPOTrainer
 
         t = self.cfg.trainer
-        model = build_model(t.policy.model.path, device=self.env.device,
-                            dtype=torch.bfloat16 if self.env.device.type == "cuda" else torch.float32, seed=t.seed)
+        dtype = torch.bfloat16 if self.env.device.type == "cuda" else torch.float32
+        flat, handle = None, None
+        if self.env.device.type == "cuda":
+            # the parameter buffer lives in its own allocation so that trainers on other GPUs of the machine can map it
+            # and push new weights into it (CUDA IPC; see weight_sync/remote.py, transport "peer")
+            from ..models.decoder import flat_numel_for, resolve_model_args
+            from ..parallel.peer import ipc_alloc_tensor
+
+            flat, handle, _ = ipc_alloc_tensor(flat_numel_for(resolve_model_args(t.policy.model.path)), dtype, self.env.device)
+        model = build_model(t.policy.model.path, device=self.env.device, dtype=dtype, seed=t.seed, flat_buffer=flat)
         shell = PPOTrainer.__new__(PPOTrainer)  # reuse the trainer's engine sizing rules without building workers
         shell.cfg, shell.env, shell.tokenizer = self.cfg, self.env, self.tokenizer
         engine: LLMEngine = shell._build_engine(model)
@@ -76,8 +84,15 @@ class InferenceOnlyEntrypoint(BasePPOExp):
 
         dcfg = self.cfg.generator.inference_engine.delta_weight_sync
         loader = make_weight_loader(model, engine, sync_dir=getattr(dcfg, "sync_dir", "") or None,
-                                    local_dir=getattr(dcfg, "local_checkpoint_dir", None))
-        srv = ServerThread(build_app(client, model_name=name, weight_loader=loader), host=self.host, port=port).start()
+                                    local_dir=getattr(dcfg, "local_checkpoint_dir", None), ipc_handle=handle)
+        app = build_app(client, model_name=name, weight_loader=loader)
+
+        @app.post("/skyrl/v1/shutdown")
+        async def shutdown():  # lets the trainer of a combined train + rollout launch end the rollout ranks
+            self._stop.set()
+            return {"status": "stopping"}
+
+        srv = ServerThread(app, host=self.host, port=port).start()
         self._servers.append(srv)
         rec = {"rank": self.env.rank, "server_url": srv.url}
         urls = [srv.url]
@@ -85,15 +100,15 @@ class InferenceOnlyEntrypoint(BasePPOExp):
             gathered: List[Optional[str]] = [None] * self.env.world_size
             dist.all_gather_object(gathered, srv.url)
             urls = [u for u in gathered if u]
-        if self.env.is_main:
+        if self.env.is_main and with_router:
             self._router = ServerThread(build_router_app(SessionRouter(urls)), host=self.host,
                                         port=(self.base_port + self.env.world_size) if self.base_port else 0).start()
             rec.update({"router_url": self._router.url, "server_urls": urls})
         print(json.dumps(rec), flush=True)
         return rec
 
-    def run(self) -> None:
-        self.start()
+    def run(self, with_router: bool = True) -> None:
+        self.start(with_router)
         for sig in (signal.SIGINT, signal.SIGTERM):
             try:
                 signal.signal(sig, lambda *_: self._stop.set())

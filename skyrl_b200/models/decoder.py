@@ -337,6 +337,16 @@ class CausalLM(nn.Module):
         return sum(math.prod(s) for _, s in self.specs)
 
 
+def param_offsets(args: ModelArgs, value_head: bool = False) -> Dict[str, Tuple[int, int]]:
+    """name -> (element offset, numel) of the flat parameter buffer ``CausalLM`` lays out for ``args`` (no allocation)."""
+    off, out = 0, {}
+    for name, shape in _param_specs(args, value_head=value_head):
+        n = math.prod(shape)
+        out[name] = (off, n)
+        off += _align(n)
+    return out
+
+
 def flat_numel_for(args: ModelArgs, value_head: bool = False) -> int:
     """Size (elements) of the flat parameter buffer ``CausalLM`` lays out for ``args``."""
     off = 0

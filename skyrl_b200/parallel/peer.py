@@ -60,6 +60,27 @@ class SymmTensor:
         return (ctypes.c_void_p * len(self.ptrs))(*self.ptrs)
 
 
+def ipc_alloc_tensor(numel: int, dtype: torch.dtype, device: torch.device):
+    """A device tensor in its own ``cudaMalloc`` allocation together with the CUDA IPC handle (hex string) through
+    which *another process* on the same machine can map it -- e.g. a trainer that pushes weights into a stand-alone
+    rollout server's parameter buffer.  Returns ``(tensor, handle_hex, base_pointer)``."""
+    nbytes = (numel * torch.empty(0, dtype=dtype).element_size() + 255) // 256 * 256
+    p = ctypes.c_void_p()
+    _lib.check(_k().sb_symm_alloc(nbytes, ctypes.byref(p)), "sb_symm_alloc")
+    buf = ctypes.create_string_buffer(64)
+    _lib.check(_k().sb_ipc_get_handle(p, buf), "sb_ipc_get_handle")
+    t = torch.as_tensor(_CudaArray(p.value, nbytes), device=device).view(dtype)[:numel]
+    return t, bytes(buf.raw).hex(), p.value
+
+
+def ipc_open(handle_hex: str) -> int:
+    """Map another process's allocation (see ``ipc_alloc_tensor``) into this process; returns the device pointer."""
+    q = ctypes.c_void_p()
+    raw = bytes.fromhex(handle_hex)
+    _lib.check(_k().sb_ipc_open_handle(ctypes.create_string_buffer(raw, 64), ctypes.byref(q)), "sb_ipc_open_handle")
+    return q.value
+
+
 class PeerContext:
     def __init__(self, device: torch.device, group: Optional[dist.ProcessGroup] = None, wait_seconds: float = 10.0):
         assert dist.is_initialized(), "PeerContext needs an initialised process group for the handle exchange"

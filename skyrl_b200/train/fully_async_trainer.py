@@ -216,6 +216,11 @@ class FullyAsyncPPOTrainer(PPOTrainer):
     async def sync_weights_in_flight(self) -> None:
         """pause(keep) -> transfer -> resume; in-flight requests continue on the new weights."""
         c = self.inference_engine_client
+        if self.weight_transfer is None and self.engine is None and hasattr(c, "fetch_weights"):
+            # stand-alone rollout servers (other ranks of this launch, or another machine): the remote sync helper
+            # pauses them with their requests kept, moves the weights (peer push / delta / export) and resumes them
+            await self.sync_weights_async()
+            return
         await c.pause("keep", clear_cache=self.cfg.trainer.fully_async.clear_kv_cache_on_weight_sync)
         try:
             if self.weight_transfer is not None:

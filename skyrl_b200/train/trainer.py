@@ -440,11 +440,22 @@ class PPOTrainer:
 
             if getattr(self, "_remote_sync", None) is None:
                 ie = self.cfg.generator.inference_engine
-                transport = "delta" if ie.weight_sync_backend == "delta" else "path"
+                in_box = getattr(self, "rollout_servers_in_box", False) or ie.weight_sync_backend == "peer"
+                if ie.weight_sync_backend == "delta":
+                    transport = "delta"
+                elif in_box and self.env.device.type == "cuda":
+                    transport = "peer"  # the servers' GPUs are NVLink peers: push the blocks straight into their buffers
+                else:
+                    transport = "path"
                 sd = getattr(ie.delta_weight_sync, "sync_dir", "") or None
-                self._remote_sync = RemoteWeightSync(c, self.policy.engine_model(), transport, sd, is_main=self.env.is_main)
-            self.policy.refresh_engine_model()
+                model = None if transport == "peer" else self.policy.engine_model()
+                self._remote_sync = RemoteWeightSync(c, model, transport, sd, is_main=self.env.is_main,
+                                                     peer_plan=self.policy.remote_push_plan)
+            if self._remote_sync.transport != "peer":
+                self.policy.refresh_engine_model()
             asyncio.run(self._remote_sync.sync()) if not self._in_event_loop() else None
+            if self._remote_sync.last_push_ms is not None:
+                self.all_metrics["timing/weight_sync_kernel_ms"] = float(self._remote_sync.last_push_ms)
             return
         if self.policy is not None:
             self.policy.refresh_engine_model()  # TP shards / LoRA adapters -> the engine's own layout
@@ -485,6 +496,8 @@ class PPOTrainer:
         if self.engine is None and self.policy is not None and hasattr(c, "fetch_weights"):
             self.sync_weights()  # builds the helper; the transfer itself is awaited here
             await self._remote_sync.sync()
+            if self._remote_sync.last_push_ms is not None:
+                self.all_metrics["timing/weight_sync_kernel_ms"] = float(self._remote_sync.last_push_ms)
         else:
             self.sync_weights()
 

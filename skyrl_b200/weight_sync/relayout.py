@@ -97,8 +97,12 @@ def full_shapes(a: ModelArgs) -> Dict[str, Tuple[int, ...]]:
 
 def build_plan(full_args: ModelArgs, src_offsets: Dict[str, Tuple[int, int]], src_tp: int, src_rank: int,
                dests: Sequence[Destination], names: Optional[Sequence[str]] = None,
-               src_vocab_parallel_head: bool = False) -> List[BlockCopy]:
-    """Block copies that move everything this source shard owns to every destination that needs it."""
+               src_vocab_parallel_head: bool = False, chunk_world: int = 1, chunk_rank: int = 0) -> List[BlockCopy]:
+    """Block copies that move everything this source shard owns to every destination that needs it.
+
+    ``chunk_world`` / ``chunk_rank``: this source is one of ``chunk_world`` data-parallel replicas that hold the same
+    shard; each replica then pushes only its 1 / ``chunk_world`` of every block's rows, so the replicas share the
+    link load and nothing is sent twice (disaggregated engines fed by a data-parallel trainer)."""
     shapes = full_shapes(full_args)
     plan: List[BlockCopy] = []
     for name in (names or list(src_offsets)):
@@ -114,6 +118,15 @@ def build_plan(full_args: ModelArgs, src_offsets: Dict[str, Tuple[int, int]], sr
             per = -(-per // 8) * 8  # keep 16-byte alignment for one-dimensional parameters
             lo, hi = min(rows, src_rank * per), min(rows, (src_rank + 1) * per)
             s_rects = [(lo, hi, 0, s_cols, lo, 0)] if hi > lo else []
+        if chunk_world > 1:
+            cut = []
+            for (r0, r1, c0, c1, lr, lc) in s_rects:
+                per = -(-(r1 - r0) // chunk_world)
+                per = -(-per // 8) * 8
+                lo, hi = min(r1, r0 + chunk_rank * per), min(r1, r0 + (chunk_rank + 1) * per)
+                if hi > lo:
+                    cut.append((lo, hi, c0, c1, lr + (lo - r0), lc))
+            s_rects = cut
         for di, d in enumerate(dests):
             if name not in d.offsets:
                 continue

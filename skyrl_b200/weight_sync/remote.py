@@ -8,6 +8,10 @@ server to load them, resume -- the choreography of the reference's ``save_weight
 * ``delta``  : XOR deltas against the last publication in a shared directory (``weight_sync/delta.py``); servers replay
   them into their local copy and load the result (reference: delta_strategy.py + delta_checkpoint.py).
 * ``path``   : a full HF-safetensors export that the servers read (simple, for small models and tests).
+* ``peer``   : servers on GPUs of the same NVSwitch domain export their parameter buffer through a CUDA IPC handle
+  (``/init_weight_transfer_engine``); every trainer rank maps the buffers once and pushes the blocks it owns straight
+  into them with the re-layout kernel (``weight_sync/relayout.py``) between ``pause(keep)`` and ``resume``.  No rank-0
+  funnel, no files, no per-sync handles (reference: NCCL broadcast from trainer rank 0, broadcast_strategy.py:131-183).
 
 Server side ``make_weight_loader(model, engine, ...)`` returns the callable that ``inference.server.build_app`` invokes
 for the weight verbs.
@@ -28,8 +32,10 @@ def _named_state(model) -> Dict[str, torch.Tensor]:
     return {name: prm.detach() for name, prm in model.named_flat_views()}
 
 
-def make_weight_loader(model, engine=None, sync_dir: Optional[str] = None, local_dir: Optional[str] = None) -> Callable:
-    """``loader(kind, payload)`` for ``/init_weight_transfer_engine``, ``/fetch_weights``, ``/update_weights``."""
+def make_weight_loader(model, engine=None, sync_dir: Optional[str] = None, local_dir: Optional[str] = None,
+                       ipc_handle: Optional[str] = None) -> Callable:
+    """``loader(kind, payload)`` for ``/init_weight_transfer_engine``, ``/fetch_weights``, ``/update_weights``.
+    ``ipc_handle``: CUDA IPC handle (hex) of the model's flat parameter buffer when it was allocated for export."""
     store: Dict[str, Any] = {"delta": None}
 
     def _after_load():
@@ -39,7 +45,14 @@ def make_weight_loader(model, engine=None, sync_dir: Optional[str] = None, local
     @torch.no_grad()
     def loader(kind: str, payload: Dict[str, Any]) -> Dict[str, Any]:
         if kind == "init":
-            return {"ready": True}
+            import socket
+
+            info = {"ready": True, "host": socket.gethostname(), "numel": int(model.flat_params.numel()),
+                    "dtype": str(model.flat_params.dtype).replace("torch.", ""),
+                    "device_index": model.flat_params.device.index}
+            if ipc_handle is not None:
+                info["ipc_handle"] = ipc_handle
+            return info
         if kind == "fetch_weights":
             sd = payload.get("sync_dir") or sync_dir
             if sd is None:
@@ -73,9 +86,13 @@ def make_weight_loader(model, engine=None, sync_dir: Optional[str] = None, local
 
 class RemoteWeightSync:
     def __init__(self, client, model, transport: str = "delta", sync_dir: Optional[str] = None, is_main: bool = True,
-                 pause_mode: str = "keep"):
-        if transport not in ("delta", "path"):
+                 pause_mode: str = "keep", peer_plan: Optional[Callable] = None):
+        """``peer_plan(dest_pointers) -> RelayoutPush`` builds this rank's push plan once the servers' buffers are
+        mapped (``peer`` transport only; every trainer rank takes part, rank 0 alone drives pause / resume)."""
+        if transport not in ("delta", "path", "peer"):
             raise ValueError(f"unknown remote weight transport '{transport}'")
+        self.peer_plan, self._push = peer_plan, None
+        self.last_push_ms: Optional[float] = None
         self.client, self.model, self.transport, self.is_main, self.pause_mode = client, model, transport, is_main, pause_mode
         self.sync_dir = sync_dir or os.path.join(tempfile.gettempdir(), f"skyrl_b200_sync_{os.getpid()}")
         self.publisher = DeltaPublisher(self.sync_dir) if (transport == "delta" and is_main) else None
@@ -83,6 +100,8 @@ class RemoteWeightSync:
 
     async def sync(self) -> int:
         """Publish the model's current weights and make every server load them. Returns the published version."""
+        if self.transport == "peer":
+            return await self._sync_peer()
         if not self.is_main:
             return self.version
         await self.client.pause(self.pause_mode)
@@ -106,4 +125,37 @@ class RemoteWeightSync:
                     await self.client._fanout("/update_weights", {"load_path": path})
         finally:
             await self.client.resume()  # generation always continues, also when the transfer failed
+        return self.version
+
+    async def _sync_peer(self) -> int:
+        import torch.distributed as dist
+
+        from ..parallel.peer import ipc_open
+
+        multi = dist.is_initialized() and dist.get_world_size() > 1
+        if self._push is None:
+            infos = await self.client._fanout("/init_weight_transfer_engine", {"transport": "peer"})
+            missing = [i for i, x in enumerate(infos) if not (isinstance(x, dict) and x.get("ipc_handle"))]
+            if missing:
+                raise RuntimeError(f"rollout servers {missing} did not export a parameter buffer for peer weight sync")
+            self._push = self.peer_plan([ipc_open(x["ipc_handle"]) for x in infos])
+        if self.is_main:
+            await self.client.pause(self.pause_mode)
+        try:
+            if multi:
+                dist.barrier()  # no rank writes before every server has stopped reading its weights
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            self._push.run()
+            ev1.record()
+            ev1.synchronize()  # this rank's stores have reached the engines' memory
+            self.last_push_ms = ev0.elapsed_time(ev1)
+            if multi:
+                dist.barrier()
+            self.version += 1
+            if self.is_main:
+                await self.client.collective_rpc("finish_weight_update")
+        finally:
+            if self.is_main:
+                await self.client.resume()
         return self.version

@@ -463,6 +463,27 @@ class ModelWorker:
             self._relayout = rlo.RelayoutPush(plan, src_model.flat_params, dests)
         return copy
 
+    def remote_push_plan(self, dest_ptrs: Sequence[int]):
+        """Block-copy plan from this rank's training parameters into unsharded engine buffers mapped from other
+        processes (``dest_ptrs``: device pointers valid in this process).  Tensor-parallel shards are re-laid out on
+        the way; ranks that hold the same data (data- / sequence-parallel replicas) each push a disjoint part."""
+        from ..models.decoder import param_offsets
+        from ..weight_sync import relayout as rlo
+
+        dense_tp = self._dense_tp_trainer()
+        if self.expert_parallel or self.pipe is not None:
+            raise NotImplementedError("peer weight push supports data-, sequence- and tensor-parallel trainers")
+        src_model = self.model if dense_tp or not hasattr(self, "_plain_model") else self._plain_model
+        full_args = src_model.full_args if dense_tp else src_model.args
+        src_tp, src_rank = (self.mesh.tp_size, self.mesh.tp_rank) if dense_tp else (1, 0)
+        reps, rep_rank = (self.mesh.dp_size, self.mesh.dp_rank) if dense_tp else (self.env.world_size, self.env.rank)
+        offs = param_offsets(full_args)
+        dests = [rlo.Destination(int(p), offs, 1, 0) for p in dest_ptrs]
+        plan = rlo.build_plan(full_args, src_model.offsets, src_tp, src_rank, dests,
+                              src_vocab_parallel_head=bool(getattr(src_model, "vocab_parallel_head", False)),
+                              chunk_world=reps, chunk_rank=rep_rank)
+        return rlo.RelayoutPush(plan, src_model.flat_params, dests)
+
     def refresh_engine_model(self) -> None:
         """Bring a separate engine copy up to date with the trained parameters (no-op when the buffer is shared)."""
         from ..models.lora import LoRACausalLM

@@ -66,3 +66,25 @@ def test_plan_blocks_are_vector_aligned_for_the_benchmark_models():
             for c in rl.build_plan(a, so, src_tp, r, dests):
                 assert c.cols % 8 == 0 and c.src_off % 8 == 0 and c.dst_off % 8 == 0, c
                 assert c.rows == 1 or (c.src_ld % 8 == 0 and c.dst_ld % 8 == 0), c
+
+
+@pytest.mark.parametrize("src_tp,replicas", [(1, 4), (2, 2), (1, 3)])
+def test_data_parallel_replicas_share_the_push(src_tp, replicas):
+    """Disaggregated engines fed by a data-parallel trainer: every replica pushes a disjoint part, together everything."""
+    a = PRESETS["tiny-qwen2-tp"]
+    full = CausalLM(a, device="cpu", dtype=torch.float32, seed=2)
+    srcs = [_shard_model(full, src_tp, r) for r in range(src_tp)]
+    got = [CausalLM(a, device="cpu", dtype=torch.float32, seed=None) for _ in range(2)]  # two unsharded remote engines
+    for g in got:
+        g.flat_params.fill_(float("nan"))
+    dests = [rl.Destination(0, g.offsets, 1, 0, tensor=g.flat_params) for g in got]
+    total = 0
+    for r in range(src_tp):
+        for k in range(replicas):
+            plan = rl.build_plan(a, srcs[r].offsets, src_tp, r, dests, chunk_world=replicas, chunk_rank=k)
+            rl.run_plan_reference(plan, srcs[r].flat_params, dests)
+            total += sum(c.rows * c.cols for c in plan)
+    for g in got:
+        for name, prm in g.named_flat_views():
+            assert torch.equal(prm, full.p(name)), name
+    assert total == 2 * sum(n for _, n in got[0].offsets.values())
