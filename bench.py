@@ -42,6 +42,11 @@ CONFIGS = {
     # GRPO, Qwen3-30B-A3B, expert parallel over all ranks; 64 prompts x 8 samples at 8 GPUs
     4: dict(model="qwen3-30b-a3b", prompts_per_gpu=8, n=8, prompt_len=1024, resp_min=2048, resp_max=2048, tp=1, engine_tp=1,
             algo="grpo", ep="world"),
+    # long-context multi-turn agent GRPO, disaggregated and fully asynchronous: half of the GPUs train (sharded optimizer +
+    # Ulysses sequence parallelism over all of them), the other half only roll out (one unsharded engine each), weights
+    # are pushed over NVLink into the running engines; 8 turns of 1024 generated + 512 observation tokens, env tokens
+    # masked, Bernoulli(0.3) reward at the end; 32 trajectories x 4 samples per update at 4 + 4 GPUs
+    5: dict(model="qwen2.5-7b", prompts_per_gpu=8, n=4, prompt_len=512, turns=8, turn_tokens=1024, obs_tokens=512, algo="grpo"),
 }
 
 
@@ -98,6 +103,153 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def run_disaggregated(args) -> None:
+    """Configuration 5.  The ranks of the launch split into a training world and a rollout world before any process
+    group exists (see ``entrypoints/main_base.py::split_roles``); rollout ranks serve until the trainer shuts them down."""
+    import torch
+
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.models.decoder import PRESETS
+
+    spec = CONFIGS[5]
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world < 2 or world != args.gpus:
+        raise SystemExit("--config 5 splits the launch into training and rollout ranks: it needs --gpus >= 2 under torchrun")
+    n_train = world // 2
+    n_roll = world - n_train
+    model = args.model or spec["model"]
+    margs = PRESETS[model]
+    P, n = args.prompts_per_gpu or spec["prompts_per_gpu"], args.n_samples or spec["n"]
+    turns, turn_tok, obs_tok = args.turns or spec["turns"], args.resp_len or spec["turn_tokens"], args.obs_tokens or spec["obs_tokens"]
+    plen = args.prompt_len or spec["prompt_len"]
+    max_len = plen + turns * turn_tok + (turns - 1) * (obs_tok + 4) + 64
+    sp_size = 1
+    while sp_size * 2 <= n_train and margs.num_kv_heads % (sp_size * 2) == 0:
+        sp_size *= 2
+    port = int(os.environ.get("MASTER_PORT", "29500"))
+    base = port + 100
+    urls = [f"http://127.0.0.1:{base + j}" for j in range(n_roll)]
+    W_gen = P * 2  # generation workers per training rank: one mini-batch in training, one in flight
+    cfg = SkyRLTrainConfig.from_cli_overrides([
+        f"trainer.policy.model.path={model}", f"trainer.train_batch_size={P * n_train}",
+        f"trainer.policy_mini_batch_size={P * n_train}", f"generator.n_samples_per_prompt={n}",
+        f"trainer.max_prompt_length={plen}", f"generator.sampling_params.max_generate_length={turn_tok}",
+        'generator.sampling_params.additional_kwargs={"ignore_eos": true}', "generator.sampling_params.temperature=1.0",
+        f"generator.max_turns={turns}", f"generator.max_input_length={max_len}", "generator.batched=false",
+        "generator.use_conversation_multi_turn=true", "environment.env_class=synthetic_multiturn",
+        "trainer.algorithm.advantage_estimator=grpo", "trainer.algorithm.use_kl_loss=false",
+        "trainer.algorithm.policy_loss_type=rollout_is", "trainer.policy.optimizer_config.lr=1e-6",
+        f"trainer.max_tokens_per_microbatch={args.max_tokens_per_microbatch}", "trainer.gradient_checkpointing=false",
+        f"trainer.policy.sequence_parallel_size={sp_size}", "trainer.fully_async.enabled=true",
+        "trainer.fully_async.max_staleness_steps=1", f"trainer.fully_async.num_parallel_generation_workers={W_gen}",
+        "trainer.placement.colocate_all=false", f"trainer.placement.policy_num_gpus_per_node={n_train}",
+        f"generator.inference_engine.num_engines={n_roll}", f"generator.inference_engine.max_num_seqs={4 * P * n}",
+        "generator.inference_engine.gpu_memory_utilization=0.6", "generator.inference_engine.enable_prefix_caching=true",
+        f"generator.inference_engine.max_num_batched_tokens={max(16384, max_len)}", "trainer.resume_mode=none",
+        "trainer.seed=0", "trainer.logger=console", f"trainer.max_training_steps={args.warmup + args.steps}",
+        "trainer.epochs=1000000", "trainer.ckpt_interval=0", "trainer.hf_save_interval=0", "trainer.eval_interval=0"])
+    os.environ["SKYRL_B200_ROLLOUT_BASE_PORT"] = str(base)
+    if rank >= n_train:
+        # rollout world: its rank 0 hosts the rendezvous store of that world (torchrun's agent store belongs to the
+        # full launch and stays with the training world)
+        os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
+        os.environ.update(WORLD_SIZE=str(n_roll), RANK=str(rank - n_train), MASTER_PORT=str(port + 1), SKYRL_B200_ROLE="rollout")
+        from skyrl_b200.entrypoints.serve import InferenceOnlyEntrypoint
+
+        cfg.trainer.placement.colocate_all = True
+        InferenceOnlyEntrypoint(cfg, base_port=base).run(with_router=False)
+        return
+    os.environ.update(WORLD_SIZE=str(n_train), RANK=str(rank), SKYRL_B200_ROLE="train")
+    from skyrl_b200.entrypoints.main_base import _shutdown_servers, _wait_for_servers
+    from skyrl_b200.inference.remote_client import RemoteInferenceClient
+    from skyrl_b200.ops import _lib
+    from skyrl_b200.parallel import dist as pdist
+    from skyrl_b200.train.dataset import PromptDataset
+    from skyrl_b200.train.fully_async_trainer import FullyAsyncPPOTrainer
+    from skyrl_b200.utils.tokenizer import SyntheticTokenizer
+
+    env = pdist.init_distributed()
+    tok = SyntheticTokenizer(margs.vocab_size)
+    g = torch.Generator().manual_seed(4321)
+    n_items = (args.warmup + args.steps + 4) * P * n_train * 2
+    rows = []
+    for i in range(n_items):
+        ids = torch.randint(4, margs.vocab_size, (plen,), generator=g).tolist()
+        rows.append({"prompt": [{"role": "user", "content": ids}], "prompt_token_ids": ids, "uid": f"t{i}",
+                     "env_class": "synthetic_multiturn", "max_turns": turns, "obs_tokens": obs_tok,
+                     "vocab_size": margs.vocab_size, "p": 0.3, "seed": 7919 * i + 1})
+    ds = PromptDataset(rows, None, None)
+    _wait_for_servers(urls)
+    client = RemoteInferenceClient(urls, tokenizer=tok, model_name=model)
+    trainer = FullyAsyncPPOTrainer(cfg, tokenizer=tok, train_dataset=ds, inference_engine_client=client, env=env)
+    trainer.rollout_servers_in_box = True
+    trainer.build_models()
+
+    class Clock:
+        """Step boundaries on the device clock: an event after every update, tokens from the step's metrics."""
+
+        def __init__(self):
+            self.events, self.tokens, self.gen, self.sync_ms, self.wall = [], [], [], [], []
+
+        def on_step_end(self, tr, m):
+            ev = torch.cuda.Event(enable_timing=True) if torch.cuda.is_available() else None
+            if ev is not None:
+                ev.record()
+            self.events.append(ev)
+            self.wall.append(time.perf_counter())
+            self.tokens.append(m.get("trainer/num_tokens", 0.0))
+            self.gen.append(m.get("trainer/num_generated_tokens", 0.0))
+            self.sync_ms.append(m.get("timing/weight_sync_kernel_ms", 1e3 * m.get("timing/sync_weights", 0.0)))
+            if env.is_main:
+                print("[bench] update %d: " % len(self.events) + ", ".join(f"{k[7:]}={v:.3f}" for k, v in m.items()
+                      if k.startswith("timing/")) + f", tokens={self.tokens[-1]:.0f}, staleness_max={m.get('async/staleness_max', 0):.0f}",
+                      file=sys.stderr, flush=True)
+
+        on_train_begin = on_train_end = lambda self, *a: None
+
+    clock = Clock()
+    trainer.callbacks.append(clock)
+    sampler = ClockSampler(env.local_rank)
+    if env.is_main:
+        sampler.start()
+    l0 = _lib.LAUNCH_COUNT
+    try:
+        trainer.train()
+        W, K = args.warmup, args.steps
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+            dev_s = clock.events[W - 1].elapsed_time(clock.events[W + K - 1]) / 1e3
+        else:
+            dev_s = clock.wall[W + K - 1] - clock.wall[W - 1]
+        dev_s = pdist.all_reduce_max_scalar(dev_s, env.device)
+        share = max(1, trainer.policy.tp_size)
+        tokens = pdist.all_reduce_sum_scalar(sum(clock.tokens[W : W + K]), env.device) / share
+        gen = pdist.all_reduce_sum_scalar(sum(clock.gen[W : W + K]), env.device) / share
+        clocks = sampler.stop() if env.is_main else {}
+        if env.is_main:
+            status = _lib.status_read_clear() if torch.cuda.is_available() else 0
+            print(json.dumps({
+                "metric": METRIC, "value": (tokens + gen) / dev_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": dev_s * 1e3 / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic (uniform-random token ids, Bernoulli(0.3) reward at episode end, "
+                "random-init weights)",
+                "config": {"model": model, "baseline_config": 5, "algorithm": "grpo (rollout-anchored loss), fully asynchronous",
+                           "parallelism": f"{n_train} training ranks (sharded optimizer x Ulysses sp{sp_size}) + {n_roll} "
+                           "rollout-only ranks (one unsharded engine each)", "global_batch": P * n * n_train,
+                           "trajectory": f"{turns} turns x ({turn_tok} generated + {obs_tok} observation tokens), prompt {plen}",
+                           "seq_len": max_len, "tokens_counted": "trained (prompt + response) + generated tokens of the "
+                           "updates in the timed window", "max_staleness_steps": 1,
+                           "l2_policy": "inputs larger than L2 (15 GB of weights per rank)"},
+                "clocks": clocks, "e2e": {"value": None, "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                                          "note": "the timed window is already end to end: requests and results cross HTTP"},
+                "gpu_launches": _lib.LAUNCH_COUNT - l0, "device_status": status, "impl": "ours",
+                "weight_sync_ms": float(sum(clock.sync_ms[W : W + K]) / max(1, K))}), flush=True)
+    finally:
+        if env.is_main:
+            _shutdown_servers(urls)
+        pdist.shutdown()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -111,6 +263,8 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--resp-len", type=int, default=None, help="fixed response length (overrides the configuration's range)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the separately timed end-to-end steps (long configurations)")
+    ap.add_argument("--turns", type=int, default=None, help="config 5: turns per trajectory")
+    ap.add_argument("--obs-tokens", type=int, default=None, help="config 5: observation tokens appended after every turn")
     ap.add_argument("--max-tokens-per-microbatch", type=int, default=32768)
     ap.add_argument("--tp", type=int, default=None, help="tensor-parallel size of the training model (1 = sharded data parallel)")
     ap.add_argument("--ep", type=int, default=None, help="expert-parallel size (MoE models)")
@@ -124,6 +278,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
+        return
+    if args.config == 5:
+        run_disaggregated(args)
         return
 
     import torch

@@ -215,7 +215,9 @@ class _ColumnParallelFn(torch.autograd.Function):
         dy = dy.contiguous()
         R = x_full.shape[0] // tp.size
         if tp.fused and dy.is_cuda:
-            slots = tp.slot_buffer(R, w.shape[1], torch.float32, "col_dx")
+            # bf16 slots: the partial tiles cross NVLink at 2 bytes per element (as an NCCL bf16 reduce-scatter would
+            # send them) and are added in fp32 by the slot sum
+            slots = tp.slot_buffer(R, w.shape[1], torch.bfloat16, "col_dx")
             gemm_reduce_scatter(tp, dy, w, slots, R, w_is_kn=True)
             tp.peer.barrier()
             dx = reduce_slots(slots.local.view(tp.size, R, w.shape[1]), x_full.dtype)
@@ -244,7 +246,7 @@ class _RowParallelFn(torch.autograd.Function):
         R = T // tp.size
         N = w.shape[0]
         if tp.fused and x_local.is_cuda:
-            slots = tp.slot_buffer(R, N, torch.float32, "row_y")
+            slots = tp.slot_buffer(R, N, torch.bfloat16, "row_y")
             gemm_reduce_scatter(tp, x_local.contiguous(), w, slots, R)
             tp.peer.barrier()
             y = reduce_slots(slots.local.view(tp.size, R, N), x_local.dtype)

@@ -92,8 +92,12 @@ class AsyncDataloader:
     """Shared prompt iterator for the generation workers: one item at a time under a lock, skipping uids that
     were already consumed before a restart; epochs roll over transparently."""
 
-    def __init__(self, dataset, seed: int = 42, epochs: int = 1, consumed_uids: Optional[Set[str]] = None):
+    def __init__(self, dataset, seed: int = 42, epochs: int = 1, consumed_uids: Optional[Set[str]] = None,
+                 rank: int = 0, world: int = 1):
+        """``rank`` / ``world``: every training rank feeds its own generation workers from a disjoint slice of each
+        epoch's permutation (the permutation itself is the same on all ranks)."""
         self.ds, self.seed, self.epochs = dataset, seed, epochs
+        self.rank, self.world = rank, max(1, world)
         self.epoch = 0
         self.consumed: Set[str] = set(consumed_uids or ())
         self._order = self._make_order()
@@ -103,7 +107,7 @@ class AsyncDataloader:
     def _make_order(self) -> np.ndarray:
         idx = np.arange(len(self.ds))
         np.random.default_rng(self.seed + self.epoch).shuffle(idx)
-        return idx
+        return idx[self.rank :: self.world]
 
     def epoch_uid(self, uid: str) -> str:
         return f"{self.epoch}:{uid}"
@@ -195,6 +199,13 @@ class FullyAsyncPPOTrainer(PPOTrainer):
         return groups
 
     def convert_groups_to_training_input(self, groups: List[Dict[str, Any]]) -> TrainingInputBatch:
+        if self.policy is not None and self.policy.tp_size > 1:
+            # ranks of one tensor / sequence parallel group train on one batch: the union of what each collected
+            import torch.distributed as dist
+
+            parts: List[Any] = [None] * self.policy.mesh.tp_size
+            dist.all_gather_object(parts, groups, group=self.policy.mesh.tp_group)
+            groups = [g for p in parts for g in p]
         out = concatenate_generator_outputs([g["out"] for g in groups])
         uids = [u for g in groups for u in g["uids"]]
         out = self.postprocess_generator_output(out, uids)
@@ -234,7 +245,8 @@ class FullyAsyncPPOTrainer(PPOTrainer):
         t = self.cfg.trainer
         assert self.train_dataset is not None
         self.load_checkpoints()
-        loader = AsyncDataloader(self.train_dataset, seed=t.seed, epochs=t.epochs, consumed_uids=self.consumed_uids)
+        loader = AsyncDataloader(self.train_dataset, seed=t.seed, epochs=t.epochs, consumed_uids=self.consumed_uids,
+                                 rank=self.env.rank, world=self.env.world_size)
         self._queue = asyncio.Queue(maxsize=self.B * (self.S + 1))
         self._stop, self._worker_error = False, False
         self._workers = [asyncio.create_task(self._generation_worker(loader)) for _ in range(self.W)]
@@ -254,6 +266,8 @@ class FullyAsyncPPOTrainer(PPOTrainer):
                     await self.sync_weights_in_flight()
                 for g in groups:
                     self.consumed_uids.add(g["key"])
+                self.all_metrics["trainer/num_tokens"] = float(batch["attention_mask"].sum())
+                self.all_metrics["trainer/num_generated_tokens"] = float(batch["loss_mask"].sum())
                 self.global_step += 1
                 await self.staleness.notify_capacity_change(self.global_step + 1)
                 self.staleness.check_invariant()
@@ -261,6 +275,8 @@ class FullyAsyncPPOTrainer(PPOTrainer):
                 metrics.update({f"timing/{k}": v for k, v in self.all_timings.items()})
                 metrics["trainer/global_step"] = float(self.global_step)
                 self._log(metrics, self.global_step)
+                for cb in self.callbacks:
+                    cb.on_step_end(self, metrics)
                 if t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0:
                     self.save_checkpoints()
                 if max_steps is not None and self.global_step >= max_steps:
