@@ -599,6 +599,8 @@ class B200Config(BaseConfig):
     # tensor-parallel training: shard the LM head over the vocabulary (fused log-prob kernel per shard, softmax records
     # merged across ranks through peer memory) instead of over the tokens; needs untied embeddings
     vocab_parallel_lm_head: bool = False
+    # fused peer optimizer: start each layer's gradient reduce-scatter behind the last micro-batch's backward pass
+    overlap_grad_reduce: bool = True
 
 
 @dataclass

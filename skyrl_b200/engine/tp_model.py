@@ -18,6 +18,7 @@ Without CUDA peers (CPU tests over gloo) the same methods use ``torch.distribute
 
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
@@ -67,9 +68,9 @@ class TPEngineModel(CausalLM):
         ``[tp, T, N]`` view once all ranks' partials have landed (the barrier is enqueued on the stream)."""
         T, N = x_local.shape[0], w_shard.shape[0]
         splits = 1
-        if replayable and dtype == torch.float32 and T <= 256:
-            # decode: a skinny GEMM has too few output tiles for 148 SMs; k slices fill the machine and the consumer
-            # adds tp * splits partials instead of tp
+        if replayable and dtype == torch.float32 and T <= 256 and os.environ.get("SB_TP_DECODE_SPLITK", "0") == "1":
+            # k slices would let a skinny GEMM use all SMs, but every slice's fp32 partial tile then crosses NVLink to
+            # every rank: measured at 7B, 128 sequences, the step went from 6.45 ms to 8.52 ms.  Off unless asked for.
             splits = tpm.plan_scatter_splitk(T, N, x_local.shape[1])
         P = self.tp.size * splits
         st = self.slots(tag, T * splits, N, dtype)

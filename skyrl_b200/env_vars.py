@@ -46,6 +46,14 @@ _VARS: List[EnvVar] = [
     EnvVar("SKYRL_B200_NUMA_PIN", "1", _flag, "bind each rank's host threads to the CPUs of its GPU's NUMA node"),
     EnvVar("SKYRL_B200_PEER_WAIT_S", "2.0", float, "upper bound of every wait on a peer flag inside the NVLink kernels (seconds)"),
     # ---- kernel switches (A/B measurements; defaults are the fast paths)
+    EnvVar("SB_TP_DECODE_SPLITK", "0", _flag,
+           "tensor-parallel engines: split the row-parallel decode GEMMs over k slices (more SMs, more NVLink bytes)"),
+    EnvVar("SKYRL_B200_ROLLOUT_BASE_PORT", "", str,
+           "disaggregated launch: first port of the rollout-only ranks' servers (default MASTER_PORT + 100)"),
+    EnvVar("SKYRL_B200_ROLLOUT_URLS", "", str,
+           "disaggregated launch: server URLs of the rollout ranks (written by the role split for the training ranks)"),
+    EnvVar("SKYRL_B200_ROLE", "", str, "disaggregated launch: 'train' or 'rollout' once the role split has run"),
+    EnvVar("SB_FORCE_CPU", "0", _flag, "tests: run the multi-rank engine check on CPU tensors even when GPUs exist"),
     EnvVar("SB_PDL", "1", _flag, "programmatic dependent launch between the kernels of a decode step / training layer"),
     EnvVar("SB_GEMM_PAIR", "1", _flag, "CTA-pair (cta_group::2) GEMM for large problems"),
     EnvVar("SB_FUSED_MLP", "1", _flag, "SwiGLU inside the gate/up and down-gradient GEMM epilogues (training)"),

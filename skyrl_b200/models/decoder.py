@@ -307,7 +307,11 @@ class CausalLM(nn.Module):
         """``input_ids`` / ``positions``: ``[T]``; ``cu_seqlens``: int32 ``[B+1]``. Returns hidden ``[T, H]``."""
         x = _EmbeddingFn.apply(input_ids, self.p("embed"))
         delta = None
+        ready = getattr(self, "layer_grads_ready", None)  # callable(i): every parameter gradient of layer i is final
         for i in range(self.args.num_layers):
+            if ready is not None and torch.is_grad_enabled() and x.requires_grad:
+                # the gradient of a layer's input is produced by the last backward node of that layer
+                x.register_hook(lambda g, i=i: ready(i))
             if self.gradient_checkpointing and torch.is_grad_enabled():
                 if delta is None:
                     delta = torch.zeros_like(x)

@@ -224,18 +224,22 @@ class TPCausalLM(CausalLM):
                 del full
 
     @torch.no_grad()
-    def gather_full_state(self) -> Dict[str, torch.Tensor]:
-        """Unsharded parameters on every rank (all-gather of the shards), keyed like the unsharded model."""
-        out = {}
+    def iter_full_state(self):
+        """``(name, unsharded parameter)`` one at a time (all-gather of the shards): the caller can consume each tensor
+        before the next is gathered, so the full model never exists twice."""
         for name, prm in self.named_flat_views():
             leaf = name.split(".")[-1]
             if leaf in self.replicated_leaves or self.tp.size == 1:
-                out[name] = prm.detach()
+                yield name, prm.detach()
                 continue
             parts = [torch.empty_like(prm) for _ in range(self.tp.size)]
             dist.all_gather(parts, prm.detach().contiguous(), group=self.tp.group)
-            out[name] = unshard_param(name, parts, self.full_args)
-        return out
+            yield name, unshard_param(name, parts, self.full_args)
+
+    @torch.no_grad()
+    def gather_full_state(self) -> Dict[str, torch.Tensor]:
+        """Unsharded parameters on every rank, keyed like the unsharded model."""
+        return dict(self.iter_full_state())
 
     def reduce_replicated_grads(self) -> None:
         """Sum over the TP group of the gradients of replicated parameters (each rank saw different tokens)."""
@@ -440,16 +444,18 @@ class EPCausalLM(CausalLM):
                 prm.normal_(0.0, std, generator=g)
 
     @torch.no_grad()
-    def gather_full_state(self) -> Dict[str, torch.Tensor]:
-        out = {}
+    def iter_full_state(self):
         for name, prm in self.named_flat_views():
             if name.split(".")[-1] in EXPERT_LEAVES and self.ep.size > 1:
                 parts = [torch.empty_like(prm) for _ in range(self.ep.size)]
                 dist.all_gather(parts, prm.detach().contiguous(), group=self.ep.group)
-                out[name] = torch.cat(parts, 0)
+                yield name, torch.cat(parts, 0)
             else:
-                out[name] = prm.detach()
-        return out
+                yield name, prm.detach()
+
+    @torch.no_grad()
+    def gather_full_state(self) -> Dict[str, torch.Tensor]:
+        return dict(self.iter_full_state())
 
     def replicated_ranges(self) -> List[Tuple[int, int]]:
         return [(o, o + n) for name, (o, n) in self.offsets.items() if name.split(".")[-1] not in EXPERT_LEAVES]

@@ -152,6 +152,36 @@ class PeerContext:
                                                _lib.stream_ptr()), "sb_peer_publish_scalar")
         self.barrier(1)  # all partial norms visible; everyone is done reading everyone's gradients
 
+    BUCKET_CHANNEL = 6
+
+    def reduce_scatter_bucket(self, grads: SymmTensor, out_shard: torch.Tensor, lo: int, n: int, b_lo: int, b_hi: int,
+                              first: bool) -> None:
+        """Reduce the part of flat range ``[b_lo, b_hi)`` that this rank owns (``[lo, lo + n)``) on the *current* stream:
+        a barrier (every rank has finished writing this range's gradients), then loads from every peer.  The squared
+        norm accumulates in ``_sq`` across calls (``first`` clears it)."""
+        self.barrier(self.BUCKET_CHANNEL)
+        if first:
+            self._sq.zero_()
+        a, b = max(b_lo, lo), min(b_hi, lo + n)
+        if b > a:
+            _lib.check(_k().sb_peer_reduce_scatter_f32(grads.ptr_array(), self.world, a, b - a, out_shard[a - lo :].data_ptr(),
+                                                       self._sq.data_ptr(), _lib.stream_ptr()), "sb_peer_reduce_scatter_f32")
+
+    def finish_reduce(self, grads: SymmTensor, out_shard: torch.Tensor, lo: int, n: int, remaining, first: bool) -> None:
+        """Reduce the ranges not covered by ``reduce_scatter_bucket`` calls, then publish the norm partial."""
+        self.barrier(0)
+        if first:
+            self._sq.zero_()
+        for (b_lo, b_hi) in remaining:
+            a, b = max(b_lo, lo), min(b_hi, lo + n)
+            if b > a:
+                _lib.check(_k().sb_peer_reduce_scatter_f32(grads.ptr_array(), self.world, a, b - a,
+                                                           out_shard[a - lo :].data_ptr(), self._sq.data_ptr(),
+                                                           _lib.stream_ptr()), "sb_peer_reduce_scatter_f32")
+        _lib.check(_k().sb_peer_publish_scalar(self.norm_pad.ptr_array(), self.rank, self.world, self._sq.data_ptr(),
+                                               _lib.stream_ptr()), "sb_peer_publish_scalar")
+        self.barrier(1)
+
     def adamw_and_push(self, master, m, v, grad_shard, params: SymmTensor, lo: int, n: int, lr, beta1, beta2, eps, wd,
                        step: int, max_norm: float, grad_scale: float):
         bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step

@@ -79,6 +79,8 @@ class ShardedAdamW:
         self.transport = transport
         self.peer_ctx = peer_ctx
         self.last_grad_norm: Optional[torch.Tensor] = None
+        self._buckets_done: list = []
+        self._side = torch.cuda.Stream(device=dev) if (transport == "peer" and dev.type == "cuda") else None
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()
@@ -89,7 +91,22 @@ class ShardedAdamW:
         if self.world > 1 and self.transport == "peer":
             # peer-memory path: loads from every peer's gradient buffer, AdamW, stores into every peer's parameters
             ctx = self.peer_ctx
-            ctx.reduce_scatter_and_norm(self.grads_symm, self._grad_shard, self.lo, self.shard)
+            if self._buckets_done:
+                # part of the reduce-scatter already ran behind the backward pass (``reduce_bucket``): wait for it, then
+                # reduce what is left (the embedding range and anything whose hook did not fire)
+                torch.cuda.current_stream().wait_stream(self._side)
+                done = sorted(self._buckets_done)
+                rest, cur = [], 0
+                for (a, b) in done:
+                    if a > cur:
+                        rest.append((cur, a))
+                    cur = max(cur, b)
+                if cur < self.params.numel():
+                    rest.append((cur, self.params.numel()))
+                ctx.finish_reduce(self.grads_symm, self._grad_shard, self.lo, self.shard, rest, first=False)
+                self._buckets_done = []
+            else:
+                ctx.reduce_scatter_and_norm(self.grads_symm, self._grad_shard, self.lo, self.shard)
             norm, skipped = ctx.adamw_and_push(self.master, self.exp_avg, self.exp_avg_sq, self._grad_shard,
                                                self.params_symm, self.lo, self.shard, self.lr, b1, b2, self.eps,
                                                self.weight_decay, self.step_count, self.max_grad_norm, grad_scale)
@@ -129,6 +146,23 @@ class ShardedAdamW:
             dist.all_gather_into_tensor(self.params, shard_params.clone(), group=self.group)
         self.last_grad_norm = self._norm.clone()
         return self.last_grad_norm
+
+    # ------------------------------------------------------------------ reduce-scatter behind the backward pass
+    @property
+    def can_overlap_reduce(self) -> bool:
+        return self.world > 1 and self.transport == "peer" and self._side is not None
+
+    def reduce_bucket(self, lo: int, hi: int) -> None:
+        """Gradients of flat range ``[lo, hi)`` are final on this rank (called from a backward hook during the last
+        micro-batch before ``step``): reduce this rank's part of the range on a side stream while the backward pass of
+        the earlier layers keeps running.  Every rank must call this for the same ranges in the same order."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(ev)
+            self.peer_ctx.reduce_scatter_bucket(self.grads_symm, self._grad_shard, self.lo, self.shard, lo, hi,
+                                                first=not self._buckets_done)
+        self._buckets_done.append((lo, hi))
 
     def zero_grad(self) -> None:
         self.grads.zero_()

@@ -412,7 +412,7 @@ class PPOTrainer:
                 if role == "policy":
                     pb = [(a - s, b - s) for a, b in compute_prompt_boundaries(uids[s:e])]
                     mini = self._normalize_advantages(mini, pb)
-                status = worker.forward_backward(mini)
+                status = worker.forward_backward(mini, **({"step_follows": True} if role == "policy" else {}))
                 gn = worker.optim_step()
                 if gn is not None:
                     status["grad_norm"] = float(gn)

@@ -541,12 +541,16 @@ class ModelWorker:
 
     def full_model_copy(self, into: Optional[CausalLM] = None) -> CausalLM:
         """Unsharded copy of a tensor-parallel model (collective over the TP group); ``into`` is updated in place."""
-        state = self.model.gather_full_state()
         if into is None:
             into = CausalLM(self.model.full_args, device=self.env.device, dtype=self.model.flat_params.dtype, seed=None)
         with torch.no_grad():
-            for name, prm in into.named_flat_views():
-                prm.copy_(state[name])
+            if hasattr(self.model, "iter_full_state"):
+                for name, full in self.model.iter_full_state():  # one parameter in flight at a time
+                    into.p(name).copy_(full)
+            else:
+                state = self.model.gather_full_state()
+                for name, prm in into.named_flat_views():
+                    prm.copy_(state[name])
         return into
 
     @property
@@ -791,9 +795,23 @@ class PolicyWorker(ModelWorker):
     def __init__(self, cfg, **kw):
         super().__init__(cfg, trainable=True, optimizer_cfg=cfg.policy.optimizer_config, **kw)
 
+    def _layer_buckets(self) -> List[Tuple[int, int]]:
+        """Flat gradient range of every decoder layer; the last layer's range also covers the final norm and head."""
+        m = self.model
+        L = m.args.num_layers
+        starts = [m.offsets[f"layers.{i}.ln1"][0] for i in range(L)]
+        ends = starts[1:] + [m.flat_params.numel()]
+        return list(zip(starts, ends))
+
     def forward_backward(self, batch: TrainingInputBatch, loss_fn: Optional[str] = None,
-                         loss_fn_config: Optional[dict] = None, return_per_token_outputs: bool = False) -> Dict[str, Any]:
-        """One mini-batch: micro-batch loop accumulating gradients. Advantages must already be reduction-scaled."""
+                         loss_fn_config: Optional[dict] = None, return_per_token_outputs: bool = False,
+                         step_follows: bool = False) -> Dict[str, Any]:
+        """One mini-batch: micro-batch loop accumulating gradients. Advantages must already be reduction-scaled.
+
+        ``step_follows``: the caller runs ``optim_step`` right after this call, so the gradients of a layer are final
+        as soon as the *last* micro-batch's backward pass has left that layer; with the fused peer optimizer their
+        reduce-scatter then starts behind the backward pass, layer by layer (reference behaviour: FSDP2 reduce-scatters
+        each layer's gradients inside backward, fsdp_utils.py:209-235)."""
         self.backload()
         algo = self.cfg.algorithm
         if loss_fn_config:
@@ -824,10 +842,15 @@ class PolicyWorker(ModelWorker):
             and not return_per_token_outputs
         all_metrics: List[Dict[str, float]] = []
         per_row_logprobs = torch.zeros((B, R), dtype=torch.float32) if return_per_token_outputs else None
+        overlap = (step_follows and self.mesh is None and type(self.model) is CausalLM and self.optimizer is not None
+                   and self.optimizer.can_overlap_reduce and getattr(self.cfg.b200, "overlap_grad_reduce", True))
         for k in range(n_mb):
             real = k < len(groups)
             rows = groups[k] if real else groups[-1]
             pv = self._pack(batch, rows)
+            if overlap and k == n_mb - 1:
+                buckets = self._layer_buckets()
+                self.model.layer_grads_ready = lambda i, b=buckets: self.optimizer.reduce_bucket(*b[i])
             lp, ent = self._pred_logprobs(pv, temp, with_entropy=use_ent)
             weight = len(rows) / max(1, B * world)  # KL / entropy terms: mean over the global mini-batch
             g = lambda key: self._rows_to_device(batch.get(key), rows)  # noqa: E731
@@ -882,6 +905,7 @@ class PolicyWorker(ModelWorker):
             if not real:
                 loss = loss * 0.0
             loss.backward()
+            self.model.layer_grads_ready = None
             if real:
                 m["final_loss"] = loss.detach()
                 if roll_g is not None:

@@ -144,7 +144,7 @@ def main():
     tr.cfg, tr.env = cfg_for(mode, model), env
     calls = {"fb": 0, "opt": 0, "rows": []}
 
-    def fb(mini):
+    def fb(mini, **kw):
         calls["fb"] += 1
         calls["rows"].append(mini.batch_size)
         return {}

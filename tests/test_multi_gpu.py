@@ -80,3 +80,9 @@ def test_bench_two_gpus_tensor_parallel_engine_tiny():
         p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-qwen2-tp",
                   "--prompts-per-gpu", "4", *extra], port=port)
         assert p.returncode == 0 and '"device_status": 0' in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gradient_reduce_scatter_behind_backward_matches_one_shot():
+    p = _run([os.path.join(ROOT, "tests", "mp", "overlap_check.py")], port=29628)
+    assert p.returncode == 0 and "OVERLAP_REDUCE_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
