@@ -132,7 +132,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "both"], help="lmhead: which implementation to time")
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--hidden-lm", type=int, default=1536)
-    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "elementwise"])
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "elementwise", "relayout"])
+    ap.add_argument("--layers", type=int, default=8, help="relayout: decoder layers of the Qwen2.5-1.5B-shaped source model")
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=2048)
@@ -241,6 +242,26 @@ def main() -> None:
         fl = 2.0 * M * N * K
         out.update(m=M, n=N, k=K, emulated_ranks=R, ms=ms, tflops=fl / ms / 1e9,
                    fraction_of_measured_bf16_burst=fl / ms / 1e9 / a.peak_tflops)
+    elif a.which == "relayout":
+        # weight-sync re-layout kernel on one GPU: an unsharded trainer buffer is re-sliced into the two shards of a
+        # TP=2 engine (both destination buffers local, so the copies run at HBM speed: read + write of every byte)
+        import dataclasses
+
+        from skyrl_b200.models.decoder import PRESETS, flat_numel_for, param_offsets
+        from skyrl_b200.models.tp_decoder import local_args
+        from skyrl_b200.weight_sync import relayout as rlo
+
+        args_full = dataclasses.replace(PRESETS["qwen2.5-1.5b"], num_layers=a.layers, tie_word_embeddings=False)
+        src = torch.randn(flat_numel_for(args_full), device="cuda").to(torch.bfloat16)
+        largs = local_args(args_full, 2)
+        dsts = [torch.zeros(flat_numel_for(largs), **bf) for _ in range(2)]
+        dests = [rlo.Destination(d.data_ptr(), param_offsets(largs), 2, r) for r, d in enumerate(dsts)]
+        plan = rlo.build_plan(args_full, param_offsets(args_full), 1, 0, dests)
+        push = rlo.RelayoutPush(plan, src, dests)
+        ms = timeit(push.run, a.iters)
+        moved = 2.0 * push.bytes_out  # read + write
+        out.update(layers=a.layers, block_copies=push.n_desc, work_items=push.n_items, bytes_out=push.bytes_out, ms=ms,
+                   gbs_read_plus_write=moved / ms / 1e6, fraction_of_measured_hbm=moved / ms / 1e6 / a.hbm_gbs)
     elif a.which == "elementwise":
         # the bandwidth-bound kernels of a step: achieved bytes / s against the measured copy bandwidth
         from skyrl_b200.ops import elementwise as ew, optim, sampling
