@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="plain GEMMs instead of split-K + fused consumers")
+    ap.add_argument("--mlp-block", action="store_true", help="persistent o-proj..down-proj kernel per layer")
     ap.add_argument("--hbm-gbs", type=float, default=float(os.environ.get("SB_HBM_GBS", "6543.4")))
     ap.add_argument("--tp", type=int, default=1, help="engine tensor-parallel size (= number of ranks launched)")
     args = ap.parse_args()
@@ -55,7 +56,7 @@ def main() -> None:
                 prm.data.fill_(1.0)
     max_len = args.ctx + args.steps * 3 + 64
     eng = LLMEngine(m, EngineConfig(block_size=32, max_num_seqs=args.seqs, max_model_len=max_len,
-                                    max_num_batched_tokens=1 << 20, enforce_eager=args.eager, sync_interval=args.steps, fused_decode=not args.no_fused,
+                                    max_num_batched_tokens=1 << 20, enforce_eager=args.eager, sync_interval=args.steps, fused_decode=not args.no_fused, fused_mlp_block=args.mlp_block,
                                     num_blocks=args.seqs * ((max_len + 31) // 32) + 8))
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(4, a.vocab_size, (args.seqs, args.ctx), generator=g).tolist()
@@ -76,7 +77,7 @@ def main() -> None:
     ideal_ms = (kv_bytes + w_bytes) / (args.hbm_gbs * 1e9) * 1e3
     if rank == 0:
         print(json.dumps({"tp": args.tp, "model": args.model, "seqs": args.seqs, "ctx": args.ctx,
-                          "mode": "eager" if args.eager else "graph", "fused": not args.no_fused, "ms_per_step": ms,
+                          "mode": "eager" if args.eager else "graph", "fused": not args.no_fused, "mlp_block": args.mlp_block, "ms_per_step": ms,
                           "tokens_per_s": args.seqs / ms * 1e3, "hbm_bytes_per_step_per_rank": kv_bytes + w_bytes,
                           "roofline_ms": ideal_ms, "fraction_of_measured_hbm_roofline": ideal_ms / ms}))
     if args.tp > 1:

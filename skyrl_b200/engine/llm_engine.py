@@ -113,6 +113,9 @@ class EngineConfig:
     graph_batch_sizes: Sequence[int] = (8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024)
     reserve_full_length: bool = True
     fused_decode: bool = True  # split-K projections with fused partial-sum consumers on the decode path
+    # o-proj + norm + gate/up/SwiGLU + down-proj + norm as one persistent kernel per layer (up to 256 sequences);
+    # None = follow the environment variable SB_DECODE_MLP_BLOCK (default off)
+    fused_mlp_block: Optional[bool] = None
     # CUDA only: the host reads each interval's finish flags from a snapshot while the *next* interval of decode steps
     # already runs, instead of draining the stream after every interval (finished sequences are retired one interval
     # later; their rows are inactive in the meantime)
@@ -196,6 +199,9 @@ class LLMEngine:
         self.sampled = torch.zeros(S, **i32)
         self.sampled_lp = torch.zeros(S, device=dev, dtype=torch.float32)
         self._state_ptrs = None
+        self._mlp_ws = None
+        if self.is_cuda:
+            self._mlp_block_workspace(1)  # allocate the persistent decode kernel's buffers before any graph capture
         self._graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
         self._graph_launches: Dict[int, int] = {}
         self._graph_pool = None
@@ -280,7 +286,8 @@ class LLMEngine:
         attn_ops.kv_cache_write(qkv, self.k_cache[i], self.v_cache[i], self.slots[:n], a.num_heads, a.num_kv_heads,
                                 a.head_dim)
         att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], self.block_tables[:n], self.ctx_lens[:n],
-                                         a.num_heads, a.num_kv_heads, a.head_dim, max_ctx=self.cfg.max_model_len)
+                                         a.num_heads, a.num_kv_heads, a.head_dim, max_ctx=self.cfg.max_model_len,
+                                         sinks=m._p.get(pre + "sinks"))
         tp = self.tp_size > 1
         o = m.row_parallel_linear(att, m.p(pre + "wo"), "prefill_o", 4) if tp else gemm.gemm_nt(att, m.p(pre + "wo"))
         x, h = ew.add_rmsnorm(x, o, m.p(pre + "ln2"), a.rms_norm_eps)
@@ -311,9 +318,13 @@ class LLMEngine:
         qkv = torch.empty((n, (a.num_heads + 2 * a.num_kv_heads) * a.head_dim), device=self.device, dtype=x.dtype)
         pending = None
         fused_mlp = a.intermediate_size % 128 == 0 and n >= 32 and os.environ.get("SB_DECODE_FUSED_MLP", "1") != "0"
+        block_ws = self._mlp_block_workspace(n)
+        h = None
         for i in range(a.num_layers):
             pre = f"layers.{i}."
-            if pending is None:
+            if block_ws is not None and i > 0:
+                pass  # h is the previous block kernel's output, already normed with this layer's ln1
+            elif pending is None:
                 _, h = ew.add_rmsnorm(x, None, m.p(pre + "ln1"), a.rms_norm_eps)
             else:
                 h = ew.add_rmsnorm_partials_(x, pending[0], pending[1], m.p(pre + "ln1"), a.rms_norm_eps)
@@ -323,6 +334,11 @@ class LLMEngine:
             att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], self.block_tables[:n],
                                              self.ctx_lens[:n], a.num_heads, a.num_kv_heads, a.head_dim,
                                              max_ctx=self.cfg.max_model_len)
+            if block_ws is not None:
+                nxt = m.p(f"layers.{i + 1}.ln1") if i + 1 < a.num_layers else m.p("final_norm")
+                h = ew.decode_mlp_block(att, x, m.p(pre + "wo"), m.p(pre + "ln2"), m.p(pre + "wgu"), m.p(pre + "wd"), nxt,
+                                        a.rms_norm_eps, block_ws)
+                continue
             part, np_ = self._splitk_linear(att, m.p(pre + "wo"), None, n)
             h = ew.add_rmsnorm_partials_(x, part, np_, m.p(pre + "ln2"), a.rms_norm_eps)
             if fused_mlp:  # SwiGLU in the epilogue of the CTA-pair gate/up GEMM
@@ -330,10 +346,28 @@ class LLMEngine:
             else:
                 act = ew.swiglu(gemm.gemm_nt(h, m.p(pre + "wgu"), static_w=True))
             pending = self._splitk_linear(act, m.p(pre + "wd"), None, n)
-        h = ew.add_rmsnorm_partials_(x, pending[0], pending[1], m.p("final_norm"), a.rms_norm_eps)
+        if block_ws is None:
+            h = ew.add_rmsnorm_partials_(x, pending[0], pending[1], m.p("final_norm"), a.rms_norm_eps)
         logits = gemm.gemm_nt(h, m.lm_head_weight(), static_w=True)
         self._sample(logits, n, masked)
         self._advance(n)
+
+    def _mlp_block_workspace(self, n: int):
+        """Workspace of the persistent per-layer kernel when it applies to a batch of ``n`` rows, else None."""
+        on = self.cfg.fused_mlp_block
+        if on is None:
+            on = os.environ.get("SB_DECODE_MLP_BLOCK", "0") == "1"
+        a = self.model.args
+        if not on or n > ew.DecodeMlpWorkspace.MAX_ROWS:
+            return None
+        if not ew.DecodeMlpWorkspace.supports(a.hidden_size, a.num_heads * a.head_dim, a.intermediate_size):
+            return None
+        if self._mlp_ws is None:
+            if torch.cuda.is_current_stream_capturing():
+                return None  # buffers that outlive a graph are not allocated from its pool
+            self._mlp_ws = ew.DecodeMlpWorkspace(self.cfg.max_num_seqs, a.hidden_size, a.num_heads * a.head_dim,
+                                                 a.intermediate_size, self.device, self.model.p("embed").dtype)
+        return self._mlp_ws if n <= self._mlp_ws.max_rows else None
 
     @torch.no_grad()
     def _decode_once_fused_tp(self, n: int, masked: bool) -> None:
@@ -382,9 +416,10 @@ class LLMEngine:
     @torch.no_grad()
     def _decode_once(self, n: int, masked: bool) -> None:
         m, a = self.model, self.model.args
-        if self.is_cuda and self.tp_size > 1 and m.tp.fused and not a.num_experts and not a.qk_norm:
+        plain = not a.num_experts and not a.qk_norm and not a.attention_sinks
+        if self.is_cuda and self.tp_size > 1 and m.tp.fused and plain:
             return self._decode_once_fused_tp(n, masked)
-        if self.is_cuda and self.cfg.fused_decode and not a.num_experts and not a.qk_norm and self.tp_size == 1:
+        if self.is_cuda and self.cfg.fused_decode and plain and self.tp_size == 1:
             return self._decode_once_fused(n, masked)
         x = sampling.embed(m.p("embed"), self.cur_tokens[:n])
         delta = None
@@ -530,7 +565,8 @@ class LLMEngine:
                 full[:, qd : qd + kvd] = self.k_cache[layer].view(-1, kvd)[t_full_slots]
                 full[:, qd + kvd :] = self.v_cache[layer].view(-1, kvd)[t_full_slots]
                 full[t_new_rows, :qd] = qkv[:, :qd]
-                att = attn_ops.attn_varlen(full, t_cu_full, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_len)
+                att = attn_ops.attn_varlen(full, t_cu_full, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_len,
+                                           sinks=m._p.get(f"layers.{layer}.sinks"))
                 return att[t_new_rows].contiguous()
 
             self.stats["prefix_cached_tokens"] = self.stats.get("prefix_cached_tokens", 0) + (Tf - len(ids))

@@ -48,6 +48,7 @@ class ModelArgs:
     tie_word_embeddings: bool = False
     attention_bias: bool = False  # Qwen2: bias on q/k/v projections
     qk_norm: bool = False  # Qwen3: per-head RMSNorm on q and k
+    attention_sinks: bool = False  # GPT-OSS: one learned sink logit per query head in every attention softmax
     # mixture of experts (0 experts = dense FFN)
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -83,6 +84,7 @@ class ModelArgs:
             max_position_embeddings=cfg.get("max_position_embeddings", 32768),
             tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
             attention_bias=bool(cfg.get("attention_bias", mt == "qwen2")), qk_norm=mt in ("qwen3", "qwen3_moe"),
+            attention_sinks=bool(cfg.get("attention_sinks", False)),
             num_experts=cfg.get("num_experts", 0) or 0, num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or 0,
             norm_topk_prob=bool(cfg.get("norm_topk_prob", True)), model_type=mt,
@@ -101,6 +103,8 @@ class ModelArgs:
             "tie_word_embeddings": self.tie_word_embeddings, "attention_bias": self.attention_bias,
             "hidden_act": "silu", "torch_dtype": "bfloat16",
         }  # fmt: skip
+        if self.attention_sinks:
+            cfg["attention_sinks"] = True
         if self.num_experts:
             cfg.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                        moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
@@ -114,6 +118,8 @@ PRESETS: Dict[str, ModelArgs] = {
     "tiny-qwen2-d128": ModelArgs(vocab_size=2048, hidden_size=256, num_layers=2, num_heads=2, num_kv_heads=1,
                                  head_dim=128, intermediate_size=512, rope_theta=1e4, attention_bias=True,
                                  tie_word_embeddings=True, model_type="qwen2"),
+    "tiny-sinks": ModelArgs(vocab_size=2048, hidden_size=256, num_layers=2, num_heads=2, num_kv_heads=1, head_dim=128,
+                            intermediate_size=512, rope_theta=1e4, attention_sinks=True, model_type="llama"),
     "tiny-qwen2-tp": ModelArgs(vocab_size=2048, hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
                                intermediate_size=1024, rope_theta=1e4, attention_bias=True, tie_word_embeddings=True,
                                model_type="qwen2"),
@@ -149,6 +155,8 @@ def _param_specs(a: ModelArgs, with_lm_head: bool = True, value_head: bool = Fal
         if a.qk_norm:
             specs.append((p + "q_norm", (a.head_dim,)))
             specs.append((p + "k_norm", (a.head_dim,)))
+        if a.attention_sinks:
+            specs.append((p + "sinks", (a.num_heads,)))
         specs.append((p + "wo", (a.hidden_size, a.q_dim)))
         specs.append((p + "ln2", (a.hidden_size,)))
         if a.num_experts:
@@ -238,7 +246,7 @@ class CausalLM(nn.Module):
             leaf = name.split(".")[-1]
             if leaf in ("ln1", "ln2", "final_norm", "q_norm", "k_norm"):
                 prm.fill_(1.0)
-            elif leaf == "bqkv":
+            elif leaf in ("bqkv", "sinks"):
                 prm.zero_()
             else:
                 # generate in chunks on CPU for device-independent, reproducible weights
@@ -285,7 +293,8 @@ class CausalLM(nn.Module):
         if attn_fn is not None:  # the caller supplies attention (e.g. over cached key/value prefixes)
             att = attn_fn(i, qkv)
         else:
-            att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen)
+            att = attn_ops.attn_varlen(qkv, cu, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_seqlen,
+                                       sinks=self._p.get(pre + "sinks"))
         o = gemm.linear(att, self.p(pre + "wo"))
         x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
         if a.num_experts and getattr(self, "ep", None) is not None:

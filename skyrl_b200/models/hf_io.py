@@ -74,7 +74,8 @@ def hf_names_for_layer(i: int, moe: bool) -> dict:
             "q": p + "self_attn.q_proj", "k": p + "self_attn.k_proj", "v": p + "self_attn.v_proj",
             "o": p + "self_attn.o_proj.weight", "q_norm": p + "self_attn.q_norm.weight",
             "k_norm": p + "self_attn.k_norm.weight", "gate": p + "mlp.gate_proj.weight", "up": p + "mlp.up_proj.weight",
-            "down": p + "mlp.down_proj.weight", "router": p + "mlp.gate.weight", "experts": p + "mlp.experts."}
+            "down": p + "mlp.down_proj.weight", "router": p + "mlp.gate.weight", "experts": p + "mlp.experts.",
+            "sinks": p + "self_attn.sinks"}
 
 
 def to_hf_state_dict(model) -> Dict[str, torch.Tensor]:
@@ -96,6 +97,8 @@ def to_hf_state_dict(model) -> Dict[str, torch.Tensor]:
         if a.qk_norm:
             sd[n["q_norm"]] = model.p(pre + "q_norm").detach()
             sd[n["k_norm"]] = model.p(pre + "k_norm").detach()
+        if a.attention_sinks:
+            sd[n["sinks"]] = model.p(pre + "sinks").detach()
         sd[n["o"]] = model.p(pre + "wo").detach()
         if a.num_experts:
             sd[n["router"]] = model.p(pre + "router").detach()

@@ -184,6 +184,8 @@ class TPCausalLM(CausalLM):
     def __init__(self, full_args: ModelArgs, tp: tpm.TPGroup, device="cpu", dtype=torch.bfloat16, value_head: bool = False,
                  flat_buffer: Optional[torch.Tensor] = None, seed: Optional[int] = 0, vocab_parallel_head: bool = False):
         self.full_args = full_args
+        if full_args.attention_sinks:
+            raise NotImplementedError("attention sinks are not sharded: use data parallelism for such models")
         self.tp = tp
         # the LM head is sharded over the vocabulary only when asked for and possible (untied, divisible, no value head)
         self.vocab_parallel_head = bool(vocab_parallel_head and not value_head and tp.size > 1
@@ -346,6 +348,8 @@ class UlyssesCausalLM(CausalLM):
     """
 
     def __init__(self, args: ModelArgs, sp: tpm.TPGroup, **kw):
+        if args.attention_sinks:
+            raise NotImplementedError("attention sinks are not sharded: use data parallelism for such models")
         if args.num_heads % sp.size or args.num_kv_heads % sp.size:
             raise ValueError(f"sequence_parallel_size={sp.size} must divide num_heads={args.num_heads} and "
                              f"num_kv_heads={args.num_kv_heads}")

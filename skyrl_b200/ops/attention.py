@@ -42,8 +42,10 @@ def _split(qkv, nq, nkv, D):
     return q, k, v
 
 
-def attn_varlen_ref(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: int, D: int, scale: float):
-    """fp32 PyTorch reference: returns (out [T, nq*D], lse [nq, T])."""
+def attn_varlen_ref(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: int, D: int, scale: float,
+                    sinks: torch.Tensor | None = None):
+    """fp32 PyTorch reference: returns (out [T, nq*D], lse [nq, T]).  ``sinks`` ([nq] logits): every row's softmax gets
+    one more column with that logit and a zero value vector (it only enlarges the denominator)."""
     T = qkv.shape[0]
     q, k, v = _split(qkv.float(), nq, nkv, D)
     rep = nq // nkv
@@ -61,6 +63,11 @@ def attn_varlen_ref(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: i
         L = e - s
         mask = torch.ones(L, L, dtype=torch.bool, device=qkv.device).tril()
         sc = sc.masked_fill(~mask, float("-inf"))
+        if sinks is not None:
+            sc = torch.cat([sc, sinks.float().view(nq, 1, 1).expand(nq, L, 1)], dim=-1)
+            lse[:, s:e] = torch.logsumexp(sc, dim=-1)
+            out[s:e] = (torch.softmax(sc, dim=-1)[..., :L] @ vb).transpose(0, 1)
+            continue
         lse[:, s:e] = torch.logsumexp(sc, dim=-1)
         out[s:e] = (torch.softmax(sc, dim=-1) @ vb).transpose(0, 1)
     return out.reshape(T, nq * D).to(qkv.dtype), lse
@@ -68,7 +75,7 @@ def attn_varlen_ref(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: i
 
 class _AttnVarlenFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, cu_seqlens, nq, nkv, D, scale, max_seqlen):
+    def forward(ctx, qkv, cu_seqlens, nq, nkv, D, scale, max_seqlen, sinks=None):
         T = qkv.shape[0]
         B = cu_seqlens.numel() - 1
         if qkv.is_cuda:
@@ -78,18 +85,37 @@ class _AttnVarlenFn(torch.autograd.Function):
             code = _k().sb_attn_fwd_varlen(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), cu_seqlens.data_ptr(), B, T,
                                            nq, nkv, D, qkv.stride(0), scale, _lib.stream_ptr())
             _lib.check(code, "sb_attn_fwd_varlen")
+            if sinks is not None:
+                # A sink column only enlarges the denominator: with lse' = log(exp(lse) + exp(sink)) the output is the
+                # plain one scaled by exp(lse - lse').  The backward kernels then see (out', lse') and are exact as
+                # they stand, because the sink's value vector is zero.
+                lse_s = torch.logaddexp(lse, sinks.float().view(nq, 1))
+                gate = torch.exp(lse - lse_s).t().unsqueeze(-1)  # [T, nq, 1]
+                out = (out.view(T, nq, D).float() * gate).to(qkv.dtype).view(T, nq * D)
+                lse = lse_s
         else:
-            out, lse = attn_varlen_ref(qkv, cu_seqlens, nq, nkv, D, scale)
-        ctx.save_for_backward(qkv, out, lse, cu_seqlens)
+            out, lse = attn_varlen_ref(qkv, cu_seqlens, nq, nkv, D, scale, sinks)
+        ctx.save_for_backward(qkv, out, lse, cu_seqlens, sinks)
         ctx.meta = (nq, nkv, D, scale, max_seqlen)
+        ctx.sink_main_grad = getattr(sinks, "main_grad", None) if sinks is not None else None
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, out, lse, cu = ctx.saved_tensors
+        qkv, out, lse, cu, sinks = ctx.saved_tensors
         nq, nkv, D, scale, max_seqlen = ctx.meta
         T = qkv.shape[0]
         B = cu.numel() - 1
+
+        def sink_grad(ds):
+            """fp32 gradient of the sink logits: into ``main_grad`` when the parameter has one, else returned."""
+            if ds is None:
+                return None
+            if ctx.sink_main_grad is not None:
+                ctx.sink_main_grad.add_(ds.to(ctx.sink_main_grad.dtype))
+                return None
+            return ds.to(sinks.dtype)
+
         if qkv.is_cuda:
             dout = dout.contiguous()
             dqkv = torch.empty_like(qkv)
@@ -99,20 +125,35 @@ class _AttnVarlenFn(torch.autograd.Function):
                                            dqkv.stride(0),
                                            scale, _lib.stream_ptr())
             _lib.check(code, "sb_attn_bwd_varlen")
-            return dqkv, None, None, None, None, None, None
+            ds = None
+            if sinks is not None:
+                # dS of the sink column = p_sink * (0 - delta), with delta = rowsum(dO * O) left in the workspace
+                p_sink = torch.exp(sinks.float().view(nq, 1) - lse)
+                ds = -(p_sink * delta.view(nq, T)).sum(1)
+            return dqkv, None, None, None, None, None, None, sink_grad(ds)
         with torch.enable_grad():
             x = qkv.detach().float().requires_grad_()
-            o, _ = attn_varlen_ref(x, cu, nq, nkv, D, scale)
-            (g,) = torch.autograd.grad(o, x, dout.float())
-        return g.to(qkv.dtype), None, None, None, None, None, None
+            sk = sinks.detach().float().requires_grad_() if sinks is not None else None
+            o, _ = attn_varlen_ref(x, cu, nq, nkv, D, scale, sk)
+            gs = torch.autograd.grad(o, (x,) if sk is None else (x, sk), dout.float())
+        return g_cast(gs[0], qkv), None, None, None, None, None, None, sink_grad(gs[1] if sk is not None else None)
+
+
+def g_cast(g: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+    return g.to(like.dtype)
 
 
 def attn_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: int, head_dim: int,
-                scale: float | None = None, max_seqlen: int = 0) -> torch.Tensor:
-    """Causal attention over packed sequences. ``qkv``: ``[T, (nq+2nkv)*D]`` -> ``[T, nq*D]``."""
+                scale: float | None = None, max_seqlen: int = 0, sinks: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention over packed sequences. ``qkv``: ``[T, (nq+2nkv)*D]`` -> ``[T, nq*D]``.
+
+    ``sinks`` (``[nq]`` learned logits, GPT-OSS style): an extra softmax column per head that carries no value.  The
+    reference gets it from a flex-attention score/mask patch compiled by inductor
+    (skyrl/backends/skyrl_train/patches/gptoss/flex_attn_sink.py); here the tcgen05 kernels run unchanged and the sink
+    enters through the log-sum-exp (see ``_AttnVarlenFn``)."""
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
-    return _AttnVarlenFn.apply(qkv, cu_seqlens, nq, nkv, head_dim, scale, max_seqlen)
+    return _AttnVarlenFn.apply(qkv, cu_seqlens, nq, nkv, head_dim, scale, max_seqlen, sinks)
 
 
 # ----------------------------------------------------------------------------- paged KV cache
@@ -136,7 +177,7 @@ def kv_cache_write(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     vc[slots[ok].long()] = v[ok]
 
 
-def attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale):
+def attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale, sinks=None):
     n, nq, D = q.shape
     nkv = k_cache.shape[2]
     bs = k_cache.shape[1]
@@ -151,25 +192,30 @@ def attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale):
         kk = k_cache[blocks].reshape(-1, nkv, D)[:L].float().repeat_interleave(rep, dim=1)
         vv = v_cache[blocks].reshape(-1, nkv, D)[:L].float().repeat_interleave(rep, dim=1)
         s = torch.einsum("hd,lhd->hl", q[i].float(), kk) * scale
-        out[i] = torch.einsum("hl,lhd->hd", torch.softmax(s, dim=-1), vv)
+        if sinks is not None:
+            pr = torch.softmax(torch.cat([s, sinks.float().view(nq, 1)], dim=-1), dim=-1)[:, :L]
+        else:
+            pr = torch.softmax(s, dim=-1)
+        out[i] = torch.einsum("hl,lhd->hd", pr, vv)
     return out.to(q.dtype)
 
 
 def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                       ctx_lens: torch.Tensor, nq: int, nkv: int, D: int, scale: float | None = None,
                       out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                      max_ctx: int = 0, force_simt: bool = False) -> torch.Tensor:
+                      max_ctx: int = 0, force_simt: bool = False, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """One query token per sequence against its paged KV (which already contains that token).
 
     ``qkv``: ``[n, (nq+2nkv)*D]`` (only the q heads are read); ``block_tables``: ``[n, max_blocks]`` int32;
-    ``ctx_lens``: ``[n]`` int32.  Returns ``[n, nq*D]``.
+    ``ctx_lens``: ``[n]`` int32.  Returns ``[n, nq*D]``.  With ``sinks`` (see ``attn_varlen``) the PyTorch
+    formulation runs on every device: the decode kernels do not return the log-sum-exp the sink would enter through.
     """
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     n = qkv.shape[0]
-    if not qkv.is_cuda:
-        q = qkv[:, : nq * D].view(n, nq, D)
-        return attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale).reshape(n, nq * D)
+    if not qkv.is_cuda or sinks is not None:
+        q = qkv[:, : nq * D].reshape(n, nq, D)
+        return attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale, sinks).reshape(n, nq * D)
     if out is None:
         out = torch.empty((n, nq * D), device=qkv.device, dtype=qkv.dtype)
     bs = k_cache.shape[1]

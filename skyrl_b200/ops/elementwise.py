@@ -266,3 +266,50 @@ def qkv_finalize(partials: torch.Tensor, n_part: int, pos: torch.Tensor, table: 
                  None if k_cache is None else k_cache.data_ptr(), None if v_cache is None else v_cache.data_ptr(),
                  T, nq, nkv, head_dim, _lib.stream_ptr()), "sb_qkv_finalize")
     return qkv
+
+
+# ----------------------------------------------------------------------------- persistent decode block (decode)
+class DecodeMlpWorkspace:
+    """Buffers of ``decode_mlp_block`` for up to ``max_rows`` sequences: allocated once (outside any CUDA-graph
+    capture) and shared by every layer and every batch size, because the kernel uses only a prefix of each."""
+
+    MAX_ROWS = 256
+
+    def __init__(self, max_rows: int, H: int, Q: int, F: int, device, dtype=torch.bfloat16):
+        self.max_rows = min(int(max_rows), self.MAX_ROWS)
+        self.H, self.Q, self.F = H, Q, F
+        lib = _lib.kernels()
+        lib.sb_decode_mlp_part_elems.restype = ctypes.c_longlong
+        lib.sb_decode_mlp_part_elems.argtypes = [ctypes.c_int] * 4
+        elems = int(lib.sb_decode_mlp_part_elems(self.max_rows, H, Q, F))
+        self.part = torch.empty(max(elems, 1), device=device, dtype=torch.float32)
+        self.h_mid = torch.empty((self.max_rows, H), device=device, dtype=dtype)
+        self.act = torch.empty((self.max_rows, F), device=device, dtype=dtype)
+        self.h_out = torch.empty((self.max_rows, H), device=device, dtype=dtype)
+        self.bar = torch.zeros(2, device=device, dtype=torch.int32)
+
+    @staticmethod
+    def supports(H: int, Q: int, F: int) -> bool:
+        return H % 128 == 0 and Q % 64 == 0 and F % 64 == 0 and H // 8 <= 192 * 4
+
+
+def decode_mlp_block(att: torch.Tensor, x: torch.Tensor, wo: torch.Tensor, ln_mid: torch.Tensor, wgu: torch.Tensor,
+                     wd: torch.Tensor, ln_out: torch.Tensor, eps: float, ws: DecodeMlpWorkspace) -> torch.Tensor:
+    """Attention output -> next layer's normed input in one persistent kernel (``csrc/decode_mlp.cu``):
+    ``x += att @ wo^T``; ``h = rmsnorm(x) * ln_mid``; ``x += (silu(h @ wg^T) * (h @ wu^T)) @ wd^T``; returns
+    ``rmsnorm(x) * ln_out`` (a view of the workspace).  ``x`` is updated in place.  What the unfused decode path does
+    with five kernels (two split-K GEMMs, the CTA-pair gate/up GEMM and two partial-sum consumers)."""
+    n, H = x.shape
+    Q, F = att.shape[1], wd.shape[1]
+    assert n <= ws.max_rows and (H, Q, F) == (ws.H, ws.Q, ws.F) and x.is_contiguous() and att.is_contiguous()
+    lib = _lib.kernels()
+    f = lib.sb_decode_mlp_block
+    if not getattr(f, "_configured", False):
+        vp, ci, cf, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+        f.argtypes = [vp] * 11 + [cl, vp, ci, ci, ci, ci, cf, vp]
+        f._configured = True
+    out = ws.h_out[:n]
+    _lib.check(f(att.data_ptr(), x.data_ptr(), wo.data_ptr(), ln_mid.data_ptr(), wgu.data_ptr(), wd.data_ptr(),
+                 ln_out.data_ptr(), ws.h_mid.data_ptr(), ws.act.data_ptr(), out.data_ptr(), ws.part.data_ptr(),
+                 ws.part.numel(), ws.bar.data_ptr(), n, H, Q, F, eps, _lib.stream_ptr()), "sb_decode_mlp_block")
+    return out

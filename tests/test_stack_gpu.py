@@ -140,3 +140,31 @@ def test_engine_moe_graph_decode_matches_eager():
         assert a.token_ids == b.token_ids
         assert torch.allclose(torch.tensor(a.logprobs), torch.tensor(b.logprobs), atol=1e-3)
     assert _lib.status_read_clear() == 0
+
+
+def test_attention_sinks_kernels_match_reference():
+    """Sink attention = the tcgen05 kernels unchanged + the sink folded into the log-sum-exp: forward and all three
+    gradients (qkv, sinks) against the fp32 PyTorch formulation with an explicit sink column."""
+    import math
+
+    from skyrl_b200.ops import attention as A
+
+    torch.manual_seed(0)
+    nq, nkv, D = 4, 2, 128
+    lens = [150, 37, 260]
+    cu = torch.tensor([0, 150, 187, 447], device="cuda", dtype=torch.int32)
+    T = sum(lens)
+    qkv = (torch.randn(T, (nq + 2 * nkv) * D, device="cuda") * 0.5).bfloat16().requires_grad_()
+    sinks = torch.tensor([1.0, -2.0, 3.0, 0.0], device="cuda", requires_grad=True)
+    dy = (torch.randn(T, nq * D, device="cuda") * 0.1).bfloat16()
+    out = A.attn_varlen(qkv, cu, nq, nkv, D, max_seqlen=max(lens), sinks=sinks)
+    out.backward(dy)
+    q2 = qkv.detach().float().requires_grad_()
+    s2 = sinks.detach().clone().requires_grad_()
+    ref, _ = A.attn_varlen_ref(q2, cu, nq, nkv, D, 1 / math.sqrt(D), s2)
+    ref.backward(dy.float())
+    assert (out.float() - ref).abs().max() < 2e-2
+    assert (qkv.grad.float() - q2.grad).abs().max() < 2e-2
+    assert (sinks.grad - s2.grad).abs().max() < 5e-2 * max(1.0, s2.grad.abs().max().item())
+    assert s2.grad.abs().max() > 1e-2
+    assert _lib.status_read_clear() == 0
