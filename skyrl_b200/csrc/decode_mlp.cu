@@ -10,8 +10,8 @@
 // A decode step has a few hundred rows at most, so each of these five pieces is a kernel of a few microseconds whose
 // cost is mostly its launch, its prologue (barrier set-up, tensor-memory allocation, first TMA round trip) and its
 // drain.  Here the CTAs (one per SM) stay resident: barriers, tensor memory and the TMA/MMA pipeline are set up once
-// and carried from phase to phase, and the phases are separated by a grid-wide barrier (an arrival counter and a
-// generation word in global memory) instead of a kernel boundary.
+// and carried from phase to phase, and the phases are separated by a grid-wide barrier (an arrival counter in global
+// memory) instead of a kernel boundary.
 //
 // Tiles: up to 256 rows are handled as two 128-row MMA blocks that share every weight tile, so each weight byte is
 // read from HBM exactly once per step and is used by both row blocks while it sits in shared memory.  A stage of the
@@ -30,7 +30,9 @@ constexpr int kDmThreads = 192;  // warp 0: TMA producer, warp 1: MMA issuer + T
 constexpr int kDmStages = 4;
 constexpr int kDmTile = 128 * 64 * 2;        // one [128 x 64] bf16 tile, 128-byte swizzled
 constexpr int kDmStageBytes = 3 * kDmTile;   // A rows 0..127 | A rows 128..255 | B
-constexpr int kDmSmem = kDmStages * kDmStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kDmStageLd = 36;                // words per row of an epilogue staging tile (32 + 4: conflict-free 16-byte accesses)
+constexpr int kDmStagingBytes = 4 * 32 * kDmStageLd * 4;  // one 32-row tile per epilogue warp
+constexpr int kDmSmem = kDmStages * kDmStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kDmStagingBytes;
 constexpr int kDmTmemCols = 512;             // 2 accumulator buffers x 2 row blocks x 128 columns
 constexpr int kDmMaxVec = 4;                 // hidden size <= 192 * 8 * 4
 constexpr int kDmMaxRows = 256;
@@ -47,16 +49,12 @@ struct DmArgs {
   __nv_bfloat16* act;            // [n, F] workspace: input of down-proj
   __nv_bfloat16* h_out;          // [n, H] result
   float* part;                   // [max(splits_o, splits_d), n, H] fp32 workspace
-  unsigned int* bar;             // grid barrier: [0] arrivals, [1] generation (zero before the first launch)
+  unsigned long long* bar;       // grid barrier: one 64-bit arrival counter (zero before the first launch)
+  unsigned long long* trace;     // optional [gridDim.x, 16] timestamps at the phase boundaries (profiling aid)
 };
 
 namespace {
 
-__device__ __forceinline__ unsigned int dm_ld_acquire(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ void dm_fence_proxy_async() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ float dm_tanh(float x) {
   float y;
@@ -64,31 +62,46 @@ __device__ __forceinline__ float dm_tanh(float x) {
   return y;
 }
 
-// Grid-wide barrier.  Generic-proxy stores of every thread of every CTA issued before it are visible to every thread
-// after it; TMA (async proxy) readers additionally fence on their side.  Returns false when the wait gave up.
-__device__ __forceinline__ bool dm_grid_barrier(unsigned int* bar, int* status, int code, int* s_ok) {
-  dm_fence_proxy_async();
+// Grid-wide barrier on ONE monotonically increasing 64-bit arrival counter: barrier number k of this launch is passed
+// when the counter reaches base + (k + 1) * gridDim.x.  A launch adds exactly kDmBarriers * gridDim.x, so `base` is
+// the counter rounded down to a multiple of that, whenever it is read before the launch's last barrier completes.
+// One release-add and an acquire poll per CTA: no reset, no second word.  `to_async`: the data written before the
+// barrier is read by TMA after it, so the writers also order their stores against the async proxy.
+// Returns false when the wait gave up (the counter is then inconsistent and must be zeroed by the host).
+constexpr int kDmBarriers = 4;
+
+__device__ __forceinline__ unsigned long long dm_ld_acquire64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ bool dm_grid_barrier(unsigned long long* counter, unsigned long long target, bool to_async,
+                                                int* status, int code, int* s_ok, unsigned long long* tr = nullptr) {
+  if (to_async) dm_fence_proxy_async();
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = 1;
-    const unsigned int gen = dm_ld_acquire(bar + 1);  // cannot advance before this CTA has arrived
-    __threadfence();
-    const unsigned int prev = atomicAdd(bar, 1u);
-    if (prev + 1 == gridDim.x) {
-      atomicExch(bar, 0u);
-      __threadfence();
-      atomicAdd(bar + 1, 1u);
-    } else {
+    if (tr) tr[0] = globaltimer_ns();
+    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(counter) : "memory");
+    if (tr) tr[1] = globaltimer_ns();
+    unsigned long long polls = 0;
+    if (dm_ld_acquire64(counter) < target) {
       const unsigned long long t0 = globaltimer_ns();
-      while (dm_ld_acquire(bar + 1) == gen) {
-        if (*reinterpret_cast<volatile int*>(status) != 0 || globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      while (dm_ld_acquire64(counter) < target) {
+        ++polls;
+        if ((polls & 63) == 0 &&
+            (*reinterpret_cast<volatile int*>(status) != 0 || globaltimer_ns() - t0 > kWaitTimeoutNs)) {
           atomicCAS(status, 0, code);
           ok = 0;
           break;
         }
       }
     }
-    __threadfence();
+    if (tr) {
+      tr[2] = globaltimer_ns();
+      tr[3] = polls;
+    }
     *s_ok = ok;
   }
   __syncthreads();
@@ -98,6 +111,7 @@ __device__ __forceinline__ bool dm_grid_barrier(unsigned int* bar, int* status, 
 struct DmPipe {
   uint8_t* smem;
   uint64_t *full, *empty, *tfull, *tempty;
+  uint32_t* stage;  // epilogue staging tiles
   uint32_t tmem_base;
   int it;      // k-block counter (producer and MMA thread advance it identically)
   int tcount;  // accumulator-use counter (MMA thread and epilogue warps advance it identically)
@@ -186,8 +200,13 @@ __device__ __forceinline__ void dm_gemm_phase(DmPipe& p, const CUtensorMap* tmA,
       ++p.tcount;
       if (!mbar_wait(&p.tfull[acc], aph, status, 0x704)) break;
       tc_fence_after();
+      // Each thread owns one accumulator row (32 consecutive columns per TMEM load).  Storing that straight to global
+      // memory makes every warp store touch 32 different lines; instead the 32 x 32 block goes through a padded
+      // shared-memory tile and leaves as whole 128-byte lines (8 lanes per row, 4 rows per store instruction).
+      uint32_t* stg = p.stage + (warp - 2) * (32 * kDmStageLd);
+      const int srow = lane >> 3, schunk = lane & 7;  // read side: row within a group of 4, 16-byte chunk of the row
       for (int m = 0; m < mb; ++m) {
-        const int row = m * 128 + q * 32 + lane;
+        const int row0 = m * 128 + q * 32;
         const uint32_t t_row = p.tmem_base + acc * 256 + m * 128 + (static_cast<uint32_t>(q * 32) << 16);
         if (SWIGLU) {
 #pragma unroll 1
@@ -196,36 +215,50 @@ __device__ __forceinline__ void dm_gemm_phase(DmPipe& p, const CUtensorMap* tmA,
             tmem_ld_32x32b_x32(t_row + c * 32, rg);
             tmem_ld_32x32b_x32(t_row + 64 + c * 32, ru);
             tmem_ld_wait();
-            if (row < n) {
-              // the unfused path rounds gate and up to bf16 before the activation; do the same
-              uint32_t pa[16];
+            // the unfused path rounds gate and up to bf16 before the activation; do the same
+            uint32_t pa[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const uint32_t pg = pack_bf16x2(__uint_as_float(rg[2 * j]), __uint_as_float(rg[2 * j + 1]));
-                const uint32_t pu = pack_bf16x2(__uint_as_float(ru[2 * j]), __uint_as_float(ru[2 * j + 1]));
-                const float g0 = __uint_as_float(pg << 16), g1 = __uint_as_float(pg & 0xFFFF0000u);
-                const float u0 = __uint_as_float(pu << 16), u1 = __uint_as_float(pu & 0xFFFF0000u);
-                pa[j] = pack_bf16x2(g0 * fmaf(0.5f, dm_tanh(0.5f * g0), 0.5f) * u0,
-                                    g1 * fmaf(0.5f, dm_tanh(0.5f * g1), 0.5f) * u1);
-              }
-              uint4* dst = reinterpret_cast<uint4*>(out_bf16 + static_cast<size_t>(row) * ld_out + pn * 64 + c * 32);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) dst[v] = make_uint4(pa[4 * v], pa[4 * v + 1], pa[4 * v + 2], pa[4 * v + 3]);
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t pg = pack_bf16x2(__uint_as_float(rg[2 * j]), __uint_as_float(rg[2 * j + 1]));
+              const uint32_t pu = pack_bf16x2(__uint_as_float(ru[2 * j]), __uint_as_float(ru[2 * j + 1]));
+              const float g0 = __uint_as_float(pg << 16), g1 = __uint_as_float(pg & 0xFFFF0000u);
+              const float u0 = __uint_as_float(pu << 16), u1 = __uint_as_float(pu & 0xFFFF0000u);
+              pa[j] = pack_bf16x2(g0 * fmaf(0.5f, dm_tanh(0.5f * g0), 0.5f) * u0,
+                                  g1 * fmaf(0.5f, dm_tanh(0.5f * g1), 0.5f) * u1);
             }
+            uint4* w = reinterpret_cast<uint4*>(stg + lane * kDmStageLd + c * 16);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) w[v] = make_uint4(pa[4 * v], pa[4 * v + 1], pa[4 * v + 2], pa[4 * v + 3]);
           }
+          __syncwarp();
+          // 32 rows x 64 bf16 (128 bytes per row)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + srow;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + r * kDmStageLd + schunk * 4);
+            if (row0 + r < n)
+              *reinterpret_cast<uint4*>(out_bf16 + static_cast<size_t>(row0 + r) * ld_out + pn * 64 + schunk * 8) = v;
+          }
+          __syncwarp();
         } else {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t r[32];
             tmem_ld_32x32b_x32(t_row + c * 32, r);
             tmem_ld_wait();
-            if (row < n) {
-              float4* dst = reinterpret_cast<float4*>(out_f32 + (static_cast<size_t>(ks) * n + row) * ld_out + pn * 128 + c * 32);
+            uint4* w = reinterpret_cast<uint4*>(stg + lane * kDmStageLd);
 #pragma unroll
-              for (int v = 0; v < 8; ++v)
-                dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]),
-                                     __uint_as_float(r[4 * v + 3]));
+            for (int v = 0; v < 8; ++v) w[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + srow;
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * kDmStageLd + schunk * 4);
+              if (row0 + rr < n)
+                *reinterpret_cast<uint4*>(out_f32 + (static_cast<size_t>(ks) * n + row0 + rr) * ld_out + pn * 128 + c * 32 +
+                                          schunk * 4) = v;
             }
+            __syncwarp();
           }
         }
       }
@@ -234,6 +267,8 @@ __device__ __forceinline__ void dm_gemm_phase(DmPipe& p, const CUtensorMap* tmA,
       if (lane == 0) mbar_arrive(&p.tempty[acc]);
     }
   }
+  // the single-lane roles above leave warps 0 and 1 diverged; block-wide barriers follow, which want whole warps
+  __syncwarp();
 }
 
 __device__ __forceinline__ void dm_ld_bf16x8(const __nv_bfloat16* p, float (&f)[8]) {
@@ -331,6 +366,7 @@ decode_mlp_block_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid
   p.it = 0;
   p.tcount = 0;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p.tempty + 2);
+  p.stage = reinterpret_cast<uint32_t*>(smem + kDmStages * kDmStageBytes + 256);
   const int warp = threadIdx.x >> 5;
 
   if (threadIdx.x == 0) {
@@ -359,27 +395,46 @@ decode_mlp_block_kernel(const __grid_constant__ CUtensorMap tm_att, const __grid
   tc_fence_after();
   p.tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
+  auto stamp = [&](int k) {
+    if (a.trace != nullptr && threadIdx.x == 0) a.trace[blockIdx.x * 16 + k] = globaltimer_ns();
+  };
+  const unsigned long long per_launch = static_cast<unsigned long long>(kDmBarriers) * gridDim.x;
+  const unsigned long long bar_base = (dm_ld_acquire64(a.bar) / per_launch) * per_launch;
   bool ok = true;
+  stamp(0);
   // phase 1: o-proj partials
   dm_gemm_phase<false>(p, &tm_att, &tm_wo, a.n, a.H / 128, a.Q / 64, a.splits_o, 0, a.part, nullptr, a.H, status);
-  ok = dm_grid_barrier(a.bar, status, 0x711, &s_ok);
+  __syncthreads();
+  stamp(1);
+  ok = dm_grid_barrier(a.bar, bar_base + 1ull * gridDim.x, false, status, 0x711, &s_ok,
+                       a.trace ? a.trace + blockIdx.x * 16 + 10 : nullptr);
+  stamp(2);
   // phase 2: residual add + post-attention norm
   if (ok) {
     dm_norm_phase(a.x, a.part, a.splits_o, a.ln_mid, a.h_mid, a.n, a.H, a.eps, red);
-    ok = dm_grid_barrier(a.bar, status, 0x712, &s_ok);
+    stamp(3);
+    ok = dm_grid_barrier(a.bar, bar_base + 2ull * gridDim.x, true, status, 0x712, &s_ok);
+    stamp(4);
   }
   // phase 3: gate/up with SwiGLU
   if (ok) {
     dm_gemm_phase<true>(p, &tm_hmid, &tm_wgu, a.n, a.F / 64, a.H / 64, 1, a.F, nullptr, a.act, a.F, status);
-    ok = dm_grid_barrier(a.bar, status, 0x713, &s_ok);
+    __syncthreads();
+    stamp(5);
+    ok = dm_grid_barrier(a.bar, bar_base + 3ull * gridDim.x, true, status, 0x713, &s_ok);
+    stamp(6);
   }
   // phase 4: down-proj partials
   if (ok) {
     dm_gemm_phase<false>(p, &tm_act, &tm_wd, a.n, a.H / 128, a.F / 64, a.splits_d, 0, a.part, nullptr, a.H, status);
-    ok = dm_grid_barrier(a.bar, status, 0x714, &s_ok);
+    __syncthreads();
+    stamp(7);
+    ok = dm_grid_barrier(a.bar, bar_base + 4ull * gridDim.x, false, status, 0x714, &s_ok);
+    stamp(8);
   }
   // phase 5: residual add + next norm
   if (ok) dm_norm_phase(a.x, a.part, a.splits_d, a.ln_out, a.h_out, a.n, a.H, a.eps, red);
+  stamp(9);
 
   tc_fence_before();
   __syncthreads();
@@ -409,10 +464,12 @@ long long sb_decode_mlp_part_elems(int n, int H, int Q, int F) {
 
 // One launch = o-proj + residual/norm + gate/up/SwiGLU + down-proj + residual/norm (see the top of this file).
 //   att [n, Q], x [n, H] (in place), wo [H, Q], wgu [2F, H] (gate rows then up rows), wd [H, F], ln_mid / ln_out [H],
-//   h_mid [n, H], act [n, F], h_out [n, H] bf16; part: fp32 workspace of part_elems elements; bar: two zeroed words.
+//   h_mid [n, H], act [n, F], h_out [n, H] bf16; part: fp32 workspace of part_elems elements; bar: one zeroed 64-bit word;
+//   trace: null, or [number of SMs, 16] words that receive each CTA's clock at the phase boundaries.
 int sb_decode_mlp_block(const void* att, void* x, const void* wo, const void* ln_mid, const void* wgu, const void* wd,
                         const void* ln_out, void* h_mid, void* act, void* h_out, float* part, long long part_elems,
-                        unsigned int* bar, int n, int H, int Q, int F, float eps, cudaStream_t stream) {
+                        unsigned long long* bar, int n, int H, int Q, int F, float eps, cudaStream_t stream,
+                        unsigned long long* trace) {
   using namespace sb;
   if (n < 1 || n > kDmMaxRows || H % 128 || Q % 64 || F % 64 || (H >> 3) > kDmThreads * kDmMaxVec) return SB_ERR_ARG;
   if (part == nullptr || bar == nullptr) return SB_ERR_ARG;
@@ -445,6 +502,7 @@ int sb_decode_mlp_block(const void* att, void* x, const void* wo, const void* ln
   a.h_out = reinterpret_cast<__nv_bfloat16*>(h_out);
   a.part = part;
   a.bar = bar;
+  a.trace = trace;
   const long long need = static_cast<long long>(a.splits_o > a.splits_d ? a.splits_o : a.splits_d) * n * H;
   if (part_elems < need) return SB_ERR_TOO_LARGE;
   const CUtensorMap* t_att = get_tmap_bf16_2d(att, n, Q, Q, 128);

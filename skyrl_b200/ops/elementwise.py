@@ -286,7 +286,8 @@ class DecodeMlpWorkspace:
         self.h_mid = torch.empty((self.max_rows, H), device=device, dtype=dtype)
         self.act = torch.empty((self.max_rows, F), device=device, dtype=dtype)
         self.h_out = torch.empty((self.max_rows, H), device=device, dtype=dtype)
-        self.bar = torch.zeros(2, device=device, dtype=torch.int32)
+        self.bar = torch.zeros(1, device=device, dtype=torch.int64)  # arrival counter of the grid barrier
+        self.trace = None  # set to an int64 [n_sm, 16] tensor to record per-CTA phase timestamps
 
     @staticmethod
     def supports(H: int, Q: int, F: int) -> bool:
@@ -306,10 +307,11 @@ def decode_mlp_block(att: torch.Tensor, x: torch.Tensor, wo: torch.Tensor, ln_mi
     f = lib.sb_decode_mlp_block
     if not getattr(f, "_configured", False):
         vp, ci, cf, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
-        f.argtypes = [vp] * 11 + [cl, vp, ci, ci, ci, ci, cf, vp]
+        f.argtypes = [vp] * 11 + [cl, vp, ci, ci, ci, ci, cf, vp, vp]
         f._configured = True
     out = ws.h_out[:n]
     _lib.check(f(att.data_ptr(), x.data_ptr(), wo.data_ptr(), ln_mid.data_ptr(), wgu.data_ptr(), wd.data_ptr(),
                  ln_out.data_ptr(), ws.h_mid.data_ptr(), ws.act.data_ptr(), out.data_ptr(), ws.part.data_ptr(),
-                 ws.part.numel(), ws.bar.data_ptr(), n, H, Q, F, eps, _lib.stream_ptr()), "sb_decode_mlp_block")
+                 ws.part.numel(), ws.bar.data_ptr(), n, H, Q, F, eps, _lib.stream_ptr(), _lib.ptr(ws.trace)),
+               "sb_decode_mlp_block")
     return out

@@ -48,7 +48,7 @@ def test_decode_mlp_block_matches_reference(n, dims):
         assert (h_k.float() - h_ref.float()).abs().max() < 0.08
         # the bulk must agree much better than the bf16 rounding tail
         assert (h_k.float() - h_ref.float()).abs().mean() < 4e-3
-    assert int(ws.bar[0]) == 0 and int(ws.bar[1]) == 8
+    assert int(ws.bar[0]) % (4 * torch.cuda.get_device_properties(0).multi_processor_count) == 0 and int(ws.bar[0]) > 0
 
 
 def test_engine_mlp_block_matches_split_kernels():
