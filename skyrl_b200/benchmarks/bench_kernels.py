@@ -209,6 +209,24 @@ def main() -> None:
         fl = 4.0 * a.seqs * a.nq * a.seqlen * a.seqlen * D / 2
         out.update(tokens=T, seqlen=a.seqlen, fwd_ms=ms_f, fwd_tflops=fl / ms_f / 1e9, bwd_ms=ms_b,
                    bwd_tflops=2.5 * fl / ms_b / 1e9, fwd_fraction_of_measured_bf16_burst=fl / ms_f / 1e9 / a.peak_tflops)
+        if a.impl in ("reference", "both"):
+            # anchor: the library the reference calls for this op (flash-attn varlen, model_wrapper.py:326-329), same
+            # tensors (its kernels are not part of this package's hot path: timing only)
+            from flash_attn import flash_attn_varlen_func
+
+            q, k, v = (t.detach().contiguous().requires_grad_() for t in (
+                qkv[:, : a.nq * D].view(T, a.nq, D), qkv[:, a.nq * D : (a.nq + a.nkv) * D].view(T, a.nkv, D),
+                qkv[:, (a.nq + a.nkv) * D :].view(T, a.nkv, D)))
+            fa = lambda: flash_attn_varlen_func(q, k, v, cu, cu, a.seqlen, a.seqlen, causal=True)  # noqa: E731
+            ms_rf = timeit(lambda: fa().detach(), a.iters)
+            ro = fa()
+            err = (ro.reshape(T, -1).float() - o.float()).abs().max().item()
+            ms_rb = timeit(lambda: torch.autograd.grad(ro, (q, k, v), g.view_as(ro), retain_graph=True), a.iters)
+            import flash_attn
+
+            out.update(flash_attn_version=flash_attn.__version__, ref_fwd_ms=ms_rf, ref_fwd_tflops=fl / ms_rf / 1e9,
+                       ref_bwd_ms=ms_rb, ref_bwd_tflops=2.5 * fl / ms_rb / 1e9, fwd_speedup=ms_rf / ms_f,
+                       bwd_speedup=ms_rb / ms_b, max_abs_diff_vs_flash_attn=err)
     elif a.which in ("tp_gather", "tp_scatter"):
         # Tensor-parallel GEMM modes with the ranks emulated by separate buffers of this GPU (the kernel code path --
         # copy warps reading "peer" shards, epilogue storing into "peer" slots -- is the one used across GPUs; only

@@ -113,6 +113,9 @@ class EngineConfig:
     graph_batch_sizes: Sequence[int] = (8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024)
     reserve_full_length: bool = True
     fused_decode: bool = True  # split-K projections with fused partial-sum consumers on the decode path
+    # KV cache in a fixed-address arena (driver virtual-memory management): sleep() frees the memory, the addresses and
+    # the CUDA graphs captured against them stay valid
+    kv_fixed_address: bool = True
     # o-proj + norm + gate/up/SwiGLU + down-proj + norm as one persistent kernel per layer (up to 256 sequences);
     # None = follow the environment variable SB_DECODE_MLP_BLOCK (default off)
     fused_mlp_block: Optional[bool] = None
@@ -240,6 +243,22 @@ class LLMEngine:
     def _alloc_kv(self) -> None:
         a = self.model.args
         shape = (self.num_blocks, self.cfg.block_size, a.num_kv_heads, a.head_dim)
+        self._kv_arena = None
+        if self.is_cuda and self.cfg.kv_fixed_address:
+            # one fixed-address arena for the whole cache: sleep() returns the physical memory, wake_up() maps new
+            # memory at the same address, so the decode graphs captured against the cache survive a sleep
+            from .vmm import VmmArena
+
+            per = self.num_blocks * self.cfg.block_size * a.num_kv_heads * a.head_dim * torch.empty((), dtype=self.kv_dtype).element_size()
+            per = (per + 255) // 256 * 256
+            try:
+                self._kv_arena = VmmArena(2 * a.num_layers * per, self.device)
+                self._kv_arena.wake(zero=True)
+                self.k_cache = [self._kv_arena.take(shape, self.kv_dtype) for _ in range(a.num_layers)]
+                self.v_cache = [self._kv_arena.take(shape, self.kv_dtype) for _ in range(a.num_layers)]
+                return
+            except (RuntimeError, MemoryError):
+                self._kv_arena = None  # no virtual-memory-management support here: plain allocations below
         self.k_cache = [torch.zeros(shape, device=self.device, dtype=self.kv_dtype) for _ in range(a.num_layers)]
         self.v_cache = [torch.zeros(shape, device=self.device, dtype=self.kv_dtype) for _ in range(a.num_layers)]
 
@@ -938,16 +957,22 @@ class LLMEngine:
         if tags is None or "kv_cache" in tags:
             self._requeue_running()
             self.rt.sbrt_sched_invalidate_all_kv(self.sched)
-            self.k_cache, self.v_cache = [], []
-            self._graphs.clear()
-            self._graph_pool = None
-            if self.is_cuda:
-                torch.cuda.empty_cache()
+            if getattr(self, "_kv_arena", None) is not None:
+                self._kv_arena.sleep()  # the tensors keep their addresses; the captured graphs stay
+            else:
+                self.k_cache, self.v_cache = [], []
+                self._graphs.clear()
+                self._graph_pool = None
+                if self.is_cuda:
+                    torch.cuda.empty_cache()
         self.asleep = True
 
     def wake_up(self, tags: Optional[Sequence[str]] = None) -> None:
         if tags is None or "kv_cache" in tags:
-            if not self.k_cache:
+            if getattr(self, "_kv_arena", None) is not None:
+                if not self._kv_arena.mapped:
+                    self._kv_arena.wake(zero=True)
+            elif not self.k_cache:
                 self._alloc_kv()
             self.asleep = False
         # tags == ["weights"]: nothing to map back; stay asleep until the KV cache returns

@@ -27,7 +27,7 @@ def test_example_scripts_parse():
         ov = _overrides(s)
         assert ov, s
         text = open(s).read()
-        if "entrypoints.main_sft" in text:
+        if "entrypoints.main_sft" in text or "main_sft_with_callbacks" in text:
             SFTConfig.from_cli_overrides(ov)
         else:
             SkyRLTrainConfig.from_cli_overrides(ov)
@@ -82,6 +82,11 @@ _TINY_RL = ["trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "t
     ("examples/algorithms/run_dapo.sh", ["trainer.algorithm.dynamic_sampling.max_sample_batches=2"]),
     ("examples/ppo/run_ppo_gsm8k.sh", []),
     ("examples/sft/run_sft.sh", None),
+    ("examples/callbacks/run_sft_with_callbacks.sh", None),
+    ("examples/multiply/run_multiply.sh", ["environment.env_class=multiply"]),
+    ("examples/on_policy_distillation/run_on_policy_distill.sh", []),
+    ("examples/turn_level_rewards/run_gsm8k_multi_turn.sh", ["generator.max_input_length=256"]),
+    ("examples/gptoss/run_attention_sinks_grpo.sh", ["trainer.policy.model.path=tiny-sinks"]),
 ])
 def test_example_scripts_run_on_cpu(tmp_path, script, extra):
     """The launch scripts themselves are executed (bash, the launcher, the entry point) on a tiny preset and data."""
@@ -92,7 +97,11 @@ def test_example_scripts_run_on_cpu(tmp_path, script, extra):
         path = alt[0]
     data = str(tmp_path / "data")
     _tiny_gsm8k(data)
-    env = dict(os.environ, MODEL="tiny-llama", DATA=data, NGPU="1", HOME=str(tmp_path), PYTHONPATH=ROOT,
+    if "multiply" in script:  # the example's own dataset writer
+        gen = subprocess.run(["python", os.path.join(ROOT, "examples/multiply/multiply_dataset.py"), "--out", data, "--n", "32"],
+                             cwd=ROOT, capture_output=True, text=True, timeout=120)
+        assert gen.returncode == 0, gen.stderr[-1500:]
+    env = dict(os.environ, MODEL="tiny-llama", TEACHER="tiny-llama", DATA=data, NGPU="1", HOME=str(tmp_path), PYTHONPATH=ROOT,
                CUDA_VISIBLE_DEVICES="", SFT_DATA=os.path.join(data, "sft.jsonl"), OMP_NUM_THREADS="2")
     if extra is None:  # SFT
         args = ["batch_size=4", "max_length=64", "max_tokens_per_microbatch=512", "num_steps=2", "bf16=false",

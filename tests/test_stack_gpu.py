@@ -168,3 +168,51 @@ def test_attention_sinks_kernels_match_reference():
     assert (sinks.grad - s2.grad).abs().max() < 5e-2 * max(1.0, s2.grad.abs().max().item())
     assert s2.grad.abs().max() > 1e-2
     assert _lib.status_read_clear() == 0
+
+
+def test_vmm_arena_keeps_addresses_across_sleep():
+    from skyrl_b200.engine.vmm import VmmArena
+
+    free0 = torch.cuda.mem_get_info()[0]
+    ar = VmmArena(512 << 20, "cuda")
+    a = ar.take((1024, 1024), torch.bfloat16)
+    b = ar.take((7, 3), torch.float32)
+    assert a.data_ptr() == ar.ptr and b.data_ptr() % 256 == 0 and b.data_ptr() >= a.data_ptr() + a.numel() * 2
+    a.fill_(1.5)
+    b.fill_(2.0)
+    assert float(a.float().sum()) == 1.5 * 1024 * 1024 and float(b.sum()) == 42.0
+    assert free0 - torch.cuda.mem_get_info()[0] >= 500 << 20
+    ar.sleep()
+    assert not ar.mapped and free0 - torch.cuda.mem_get_info()[0] < 64 << 20  # physical memory returned
+    ar.wake()
+    assert ar.mapped and a.data_ptr() == ar.ptr
+    assert float(a.float().abs().sum()) == 0.0  # fresh memory, zeroed by wake()
+    a.fill_(0.5)
+    assert float(a.float().sum()) == 0.5 * 1024 * 1024
+    ar.close()
+    assert free0 - torch.cuda.mem_get_info()[0] < 64 << 20
+
+
+def test_engine_sleep_wake_keeps_graphs_with_fixed_address_cache():
+    from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine, SamplingParams
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+
+    m = CausalLM(PRESETS["tiny-qwen2-d128"], device="cuda", dtype=torch.bfloat16, seed=5)
+    prompts = [torch.randint(4, 2048, (n,)).tolist() for n in (40, 7, 64)]
+    sp = SamplingParams(max_tokens=16, temperature=0.0, ignore_eos=True)
+    eng = LLMEngine(m, EngineConfig(block_size=16, max_num_seqs=8, max_model_len=256, sync_interval=4, num_blocks=4096))
+    assert eng._kv_arena is not None
+    first = eng.generate(prompts, sp)
+    graphs = dict(eng._graphs)
+    assert graphs, "decode should have been captured"
+    ptr = eng.k_cache[0].data_ptr()
+    torch.cuda.synchronize()
+    used = torch.cuda.mem_get_info()[0]
+    eng.sleep()
+    assert torch.cuda.mem_get_info()[0] - used >= eng._kv_arena.nbytes - (32 << 20)
+    eng.wake_up()
+    assert eng.k_cache[0].data_ptr() == ptr and dict(eng._graphs) == graphs  # nothing re-captured
+    again = eng.generate(prompts, sp)
+    for a, b in zip(first, again):
+        assert a.token_ids == b.token_ids
+    assert _lib.status_read_clear() == 0
