@@ -14,3 +14,4 @@ register("searchcode", "skyrl_b200.gym.envs.tool_envs:SearchCodeEnv", override=T
 register("text2sql", "skyrl_b200.gym.envs.tool_envs:Text2SQLEnv", override=True)
 register("lcb", "skyrl_b200.gym.envs.tool_envs:LiveCodeBenchEnv", override=True)
 register("rlm", "skyrl_b200.gym.envs.rlm:RLMEnv", override=True)
+register("llm_judge", "skyrl_b200.gym.envs.llm_judge:LLMJudgeEnv", override=True)

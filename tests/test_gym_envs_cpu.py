@@ -77,3 +77,53 @@ def test_registry_has_all_reference_envs():
         assert name in gym.registry_names() if hasattr(gym, "registry_names") else True
     env = gym.make("lcb", extras={"reward_spec": {"ground_truth": []}})
     assert isinstance(env, LiveCodeBenchEnv)
+
+
+def test_llm_judge_env_scores_through_a_chat_endpoint():
+    """The judge is an OpenAI-compatible endpoint; here a local stub that answers by comparing the last numbers."""
+    import json
+    import re
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    from skyrl_b200 import gym
+    from skyrl_b200.gym.envs.llm_judge import parse_score
+
+    calls = []
+
+    class H(BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            calls.append(body)
+            text = body["messages"][0]["content"]
+            gold = re.search(r"Gold answer: (\S+)", text).group(1)
+            cand = re.search(r"Candidate answer: (.*)", text).group(1)
+            if len(calls) == 1:  # first request fails: the env retries
+                self.send_response(503)
+                self.end_headers()
+                return
+            reply = "no score here" if "garbage" in cand else f"Reasoning...\nSCORE: {1 if gold in cand.split() else 0}"
+            out = json.dumps({"choices": [{"message": {"role": "assistant", "content": reply}}]}).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+
+        def log_message(self, *a):
+            pass
+
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        cfg = {"base_url": f"http://127.0.0.1:{srv.server_port}", "model": "stub", "max_retries": 3}
+        ex = {"reward_spec": {"ground_truth": "42"}, "question": "6 x 7?"}
+        good = gym.make("llm_judge", env_config=cfg, extras=ex).step("the answer is 42")
+        bad = gym.make("llm_judge", env_config=cfg, extras=ex).step("the answer is 41")
+        odd = gym.make("llm_judge", env_config=cfg, extras=ex).step("garbage")
+        assert good["reward"] == 1.0 and good["done"] and bad["reward"] == 0.0
+        assert odd["reward"] == 0.0 and odd["metadata"]["judge_parsed"] is False
+        assert calls[1]["model"] == "stub" and "Question: 6 x 7?" in calls[1]["messages"][0]["content"]
+    finally:
+        srv.shutdown()
+    assert parse_score("SCORE: 0.5 then SCORE: 3") == 1.0 and parse_score("nothing") is None
