@@ -262,6 +262,8 @@ def main() -> None:
     ap.add_argument("--n-samples", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--resp-len", type=int, default=None, help="fixed response length (overrides the configuration's range)")
+    ap.add_argument("--prefix-caching", type=int, default=0,
+                    help="engine prefix cache: the n samples of a prompt share its key/value blocks and it is prefilled once")
     ap.add_argument("--no-e2e", action="store_true", help="skip the separately timed end-to-end steps (long configurations)")
     ap.add_argument("--turns", type=int, default=None, help="config 5: turns per trajectory")
     ap.add_argument("--obs-tokens", type=int, default=None, help="config 5: observation tokens appended after every turn")
@@ -331,7 +333,8 @@ def main() -> None:
         "trainer.policy.optimizer_config.lr=1e-6", f"trainer.max_tokens_per_microbatch={args.max_tokens_per_microbatch}",
         "trainer.gradient_checkpointing=false",
         f"generator.inference_engine.max_num_seqs={P * n}", "generator.inference_engine.gpu_memory_utilization=0.25",
-        "generator.inference_engine.enable_prefix_caching=false", "trainer.resume_mode=none", "trainer.seed=0",
+        f"generator.inference_engine.enable_prefix_caching={'true' if args.prefix_caching else 'false'}",
+        "trainer.resume_mode=none", "trainer.seed=0",
         "trainer.logger=console", *(["trainer.strategy=megatron",
                                     f"trainer.policy.megatron_config.tensor_model_parallel_size={args.tp}"] if args.tp > 1 else []),
         *(["trainer.strategy=megatron", f"trainer.policy.megatron_config.expert_model_parallel_size={args.ep}"]
@@ -464,7 +467,7 @@ def main() -> None:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, %s rewards, random-init weights)"
             % ("N(0,1)" if ppo else "Bernoulli(0.5)"),
             "config": {"model": args.model, "baseline_config": args.config, "algorithm": spec["algo"],
-                       "engine_tensor_parallel": args.engine_tp,
+                       "engine_tensor_parallel": args.engine_tp, "engine_prefix_caching": bool(args.prefix_caching),
                        "global_batch": P * n * world, "seq_len": PROMPT_LEN + RESP_MAX,
                        "parallelism": (f"dp{world} x ep{args.ep} (fused expert dispatch/combine)" if args.ep > 1 else
                                        f"dp{world // args.pp} x pp{args.pp} (layer stages)" if args.pp > 1 else

@@ -3,9 +3,10 @@
 // One CTA computes a 128-row query block of one (sequence, query head).  For each 128-row KV
 // block:   S = Q K^T  (tcgen05.mma, accumulator in TMEM)  ->  softmax warps read S from TMEM,
 // keep running max / sum, write P (bf16, 128-byte swizzled) to shared memory  ->  O_blk = P V
-// (tcgen05.mma, V consumed MN-major straight from its row-major tile)  ->  softmax warps fold
-// O_blk into fp32 register accumulators.  S is double-buffered in TMEM so that S_{j+1} is
-// computed while the softmax of block j runs.  Q/K/V tiles are TMA loads from the packed
+// (tcgen05.mma, V consumed MN-major straight from its row-major tile), accumulated in TMEM over
+// all KV blocks; the softmax warps rescale that accumulator only when the reference maximum moves
+// (lazily, see the softmax role).  S is double-buffered in TMEM so that S_{j+1} is computed while
+// the softmax of block j runs.  Q/K/V tiles are TMA loads from the packed
 // [T, (nq + 2 nkv) * 128] QKV activation; nothing is unpadded or repacked on the host.
 //
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..9 = softmax
@@ -65,9 +66,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   __shared__ int s_seq, s_qblk, s_found;
   __shared__ float s_l[128];
+  __shared__ float s_half[2][2][128];  // [block parity][column half][row]: half-row maxima exchanged by a row's two threads
+  __shared__ int s_pub[2][128];        // [column half][row]: 1 + index of the last block whose half maximum is published
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 256) (&s_pub[0][0])[threadIdx.x] = 0;
 
   if (threadIdx.x == 0) {
     int seq = 0, qblk = 0;
@@ -170,7 +174,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
         for (int k = 0; k < 8; ++k) {
           const uint32_t a_off = (k >> 2) * 16384 + (k & 3) * 32;
           umma_f16(tmem_base + 256, make_smem_desc(p_base + a_off, 0, 1024),
-                   make_smem_desc(v_base + k * 2048, 16384, 1024), idesc_o, k != 0);
+                   make_smem_desc(v_base + k * 2048, 16384, 1024), idesc_o, (k != 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(o_full);
         umma_commit(&v_empty[s]);
@@ -178,30 +182,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
     }
   } else {
     // ------------------------------- softmax --------------------------------
+    // Two threads per query row, each owning 64 of the 128 score columns of a block.  Per block a thread reads its
+    // half of S once, the pair exchanges half-row maxima through shared memory (value + block counter, bounded wait),
+    // and P = exp2(s * scale - m) goes to shared memory as bf16.  O accumulates in TMEM over all blocks
+    // (the PV MMAs add into it); it is only touched here when the reference maximum m has to move: m follows the
+    // running row maximum lazily, i.e. only when the maximum grew by more than kRescaleGap (in log2 units), so that
+    // P stays below 2^kRescaleGap and the O / l rescale (a TMEM read-modify-write) is rare after the first blocks.
     const int sw = warp - 2;   // 0..7
     const int q = warp & 3;    // TMEM lane quadrant
     const int hf = sw >> 2;    // which 64 columns this thread owns
     const int r = q * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    float O[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) O[i] = 0.f;
+    const uint32_t t_o = tmem_base + 256 + hf * 64 + lane_off;
+    constexpr float kRescaleGap = 8.f;
+    float m = -INFINITY, l = 0.f;  // m: reference maximum in scaled (log2) units; l: this thread's half-row sum
     bool ok = true;
-
-    auto accumulate_o = [&](int j, float alpha) -> bool {
-      if (!mbar_wait(o_full, j & 1, status, 0x421)) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + 256 + hf * 64 + c * 32 + lane_off, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) O[c * 32 + i] = O[c * 32 + i] * alpha + __uint_as_float(v[i]);
-      }
-      return true;
-    };
 
     for (int j = 0; j < n_kv; ++j) {
       const int sb_ = j & 1;
@@ -211,70 +206,94 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
       }
       tc_fence_after();
       const bool diag = (j == qblk);
-      const uint32_t t_s = tmem_base + sb_ * 128 + lane_off;
-      float mx = m;
-      // the other half of the row only contributes to the max
+      const uint32_t t_s = tmem_base + sb_ * 128 + hf * 64 + lane_off;
+      uint32_t sv[64];
+      tmem_ld_32x32b_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+      tmem_ld_32x32b_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+      tmem_ld_wait();
+      float mx = -INFINITY;
+      if (diag) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        const int cbase = (1 - hf) * 64 + c * 32;
-        tmem_ld_32x32b_x32(t_s + cbase, v);
-        tmem_ld_wait();
+        for (int i = 0; i < 64; ++i) {
+          if (hf * 64 + i > r) sv[i] = 0xff800000u;  // -inf above the diagonal
+          mx = fmaxf(mx, __uint_as_float(sv[i]));
+        }
+      } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * scale_log2;
-          if (diag && (cbase + i > r)) s = -INFINITY;
-          mx = fmaxf(mx, s);
+        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      }
+      // row maximum = max of the two halves.  The partner thread (other column half, same row) publishes its value
+      // and then a block counter; the wait on that counter is bounded like every other wait of this kernel, so a
+      // partner that gave up cannot strand this thread.
+      {
+        volatile float* vals = &s_half[sb_][0][0];
+        volatile int* seqs = &s_pub[0][0];
+        vals[hf * 128 + r] = mx;
+        __threadfence_block();
+        seqs[hf * 128 + r] = j + 1;
+        int spins = 0;
+        while (seqs[(1 - hf) * 128 + r] < j + 1) {
+          if (++spins > (1 << 24)) {
+            atomicCAS(status, 0, 0x423);
+            ok = false;
+            break;
+          }
+        }
+        if (!ok) break;
+        __threadfence_block();
+        mx = fmaxf(mx, vals[(1 - hf) * 128 + r]) * scale_log2;
+      }
+      if (mx > m + kRescaleGap) {
+        // move the reference: everything accumulated so far shrinks by alpha (nothing to shrink on the first block)
+        const float alpha = fast_exp2(m - mx);  // m = -inf on the first block -> 0
+        l *= alpha;
+        m = mx;
+        if (j > 0) {
+          if (!mbar_wait(o_full, (j - 1) & 1, status, 0x421)) {  // PV of block j-1 has landed in O
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[16];
+            tmem_ld_32x32b_x16(t_o + c * 16, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32b_x16(t_o + c * 16, v);
+          }
+          tmem_st_wait();
         }
       }
-      float sv[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        const int cbase = hf * 64 + c * 32;
-        tmem_ld_32x32b_x32(t_s + cbase, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * scale_log2;
-          if (diag && (cbase + i > r)) s = -INFINITY;
-          sv[c * 32 + i] = s;
-          mx = fmaxf(mx, s);
-        }
-      }
-      const float alpha = fast_exp2(m - mx);  // m = -inf on the first block -> 0
+      const float neg_m = -m;
       float psum = 0.f;
-#pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        sv[i] = fast_exp2(sv[i] - mx);
-        psum += sv[i];
-      }
-      l = l * alpha + psum;
-      if (j > 0) {
-        if (!accumulate_o(j - 1, alpha_prev)) {
-          ok = false;
-          break;
-        }
-      }
-      // P (bf16) into the swizzled K-major tile: sub-tile hf, row r, eight 16-byte chunks
       uint8_t* prow = sP + hf * 16384 + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = fast_exp2(fmaf(__uint_as_float(sv[8 * c + i]), scale_log2, neg_m));
+          psum += e[i];
+        }
         uint4 o;
-        o.x = pack_bf16x2(sv[8 * c + 0], sv[8 * c + 1]);
-        o.y = pack_bf16x2(sv[8 * c + 2], sv[8 * c + 3]);
-        o.z = pack_bf16x2(sv[8 * c + 4], sv[8 * c + 5]);
-        o.w = pack_bf16x2(sv[8 * c + 6], sv[8 * c + 7]);
+        o.x = pack_bf16x2(e[0], e[1]);
+        o.y = pack_bf16x2(e[2], e[3]);
+        o.z = pack_bf16x2(e[4], e[5]);
+        o.w = pack_bf16x2(e[6], e[7]);
+        // P (bf16) into the swizzled K-major tile: sub-tile hf, row r, eight 16-byte chunks
         *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = o;
       }
+      l += psum;
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
-      m = mx;
-      alpha_prev = alpha;
     }
-    if (ok) ok = accumulate_o(n_kv - 1, alpha_prev);
+    // final O: the last PV has to land first
+    if (ok) ok = mbar_wait(o_full, (n_kv - 1) & 1, status, 0x422);
+    tc_fence_after();
     // combine the two half-row sums
     if (hf == 1) s_l[r] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -288,13 +307,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
       const float inv = 1.f / l_tot;
       __nv_bfloat16* orow = out + static_cast<size_t>(q_row0 + r) * (nq * kAttnD) + h * kAttnD + hf * 64;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint4 o;
-        o.x = pack_bf16x2(O[8 * c + 0] * inv, O[8 * c + 1] * inv);
-        o.y = pack_bf16x2(O[8 * c + 2] * inv, O[8 * c + 3] * inv);
-        o.z = pack_bf16x2(O[8 * c + 4] * inv, O[8 * c + 5] * inv);
-        o.w = pack_bf16x2(O[8 * c + 6] * inv, O[8 * c + 7] * inv);
-        reinterpret_cast<uint4*>(orow)[c] = o;
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_o + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
+          o.y = pack_bf16x2(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
+          o.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
+          o.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
+          reinterpret_cast<uint4*>(orow)[c * 4 + u] = o;
+        }
       }
       if (hf == 0 && lse) lse[static_cast<size_t>(h) * T + q_row0 + r] = (m + log2f(l_tot)) * 0.6931471805599453f;
     }

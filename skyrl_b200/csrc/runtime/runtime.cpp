@@ -19,6 +19,7 @@
 #include <numeric>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 namespace {
@@ -105,6 +106,27 @@ class BlockManager {
     queries_ += full;
     return matched;
   }
+
+  // Hash chain of every full block of `tokens` (into `hashes`) and how many leading ones are cached right now.
+  // Takes no references.
+  int probe_prefix(const int32_t* tokens, int n_tokens, uint64_t salt, std::vector<uint64_t>& hashes) const {
+    hashes.clear();
+    if (!prefix_) return 0;
+    uint64_t h = salt;
+    const int full = n_tokens / block_size_;
+    int cached = 0;
+    bool run = true;
+    for (int i = 0; i < full; ++i) {
+      h = hash_tokens(h, tokens + static_cast<size_t>(i) * block_size_, block_size_);
+      hashes.push_back(h);
+      if (run && table_.find(h) != table_.end())
+        ++cached;
+      else
+        run = false;
+    }
+    return cached;
+  }
+  bool prefix_enabled() const { return prefix_; }
 
   // Publishes the first n_full blocks of a sequence into the prefix cache.
   void register_prefix(const int32_t* tokens, int n_tokens, uint64_t salt, const int32_t* blocks, int n_blocks) {
@@ -249,12 +271,25 @@ class Scheduler {
     p.starts.clear();
     p.counts.clear();
     if (paused_) return;
-    // 1. admit waiting requests for prefill under the token budget
+    // 1. admit waiting requests for prefill under the token budget.  With the prefix cache on, a request whose next
+    // uncached block is being computed by a request admitted in this very step (same prompt sampled n times) waits
+    // one step instead of computing it again: after that step the blocks are published and it shares them.
     int budget = max_tokens_;
-    while (!waiting_.empty() && static_cast<int>(running_.size() + p.seq_ids.size()) < max_seqs_) {
-      Seq& s = seqs_[waiting_.front()];
+    std::unordered_set<uint64_t> in_flight;
+    std::vector<uint64_t> chain;
+    size_t wi = 0;
+    while (wi < waiting_.size() && static_cast<int>(running_.size() + p.seq_ids.size()) < max_seqs_) {
+      Seq& s = seqs_[waiting_[wi]];
       const int total = static_cast<int>(s.tokens.size());
-      if (s.blocks.empty() && s.num_computed == 0) {
+      const bool fresh = s.blocks.empty() && s.num_computed == 0;
+      if (fresh && bm_.prefix_enabled()) {
+        const int have = bm_.probe_prefix(s.tokens.data(), total - 1, s.salt, chain);
+        if (have < static_cast<int>(chain.size()) && in_flight.count(chain[have])) {
+          ++wi;  // a request of this step computes that block: come back when it is published
+          continue;
+        }
+      }
+      if (fresh) {
         // prefix-cache lookup; never match the whole prompt (the last token must be computed)
         std::vector<int32_t> hit(blocks_needed(total));
         const int m = bm_.match_prefix(s.tokens.data(), total - 1, s.salt, hit.data(), static_cast<int>(hit.size()));
@@ -265,20 +300,24 @@ class Scheduler {
       if (todo > budget && !p.seq_ids.empty()) break;
       const int reserve = reserve_full_ ? s.max_total : total + 1;
       if (!ensure_blocks(s, reserve, /*allow_preempt=*/false)) {
-        if (running_.empty() && p.seq_ids.empty()) {
+        if (running_.empty() && p.seq_ids.empty() && wi == 0) {
           // nothing else can make progress: this request can never fit
           s.state = FINISHED;
           failed_.push_back(s.id);
-          waiting_.pop_front();
+          waiting_.erase(waiting_.begin() + wi);
           continue;
         }
         break;
+      }
+      if (fresh && bm_.prefix_enabled()) {
+        bm_.probe_prefix(s.tokens.data(), total, s.salt, chain);
+        for (size_t i = static_cast<size_t>(s.num_cached / bm_.block_size()); i < chain.size(); ++i) in_flight.insert(chain[i]);
       }
       p.seq_ids.push_back(s.id);
       p.starts.push_back(s.num_computed);
       p.counts.push_back(todo);
       budget -= todo;
-      waiting_.pop_front();
+      waiting_.erase(waiting_.begin() + wi);
       if (budget <= 0) break;
     }
     if (!p.seq_ids.empty()) {

@@ -94,6 +94,32 @@ def use_cuda(t: torch.Tensor) -> bool:
     return t.is_cuda
 
 
+# ----------------------------------------------------------------------------- debug-mode index checks
+class IndexOutOfRange(NativeLibraryError):
+    pass
+
+
+def debug_bounds() -> bool:
+    """``SKYRL_B200_DEBUG_BOUNDS=1``: every op that hands a kernel an index tensor (token ids, cache slots, block
+    tables, targets) first checks the indices against the limit the kernel assumes.  Each check synchronises, so this
+    is a debugging mode -- the stand-in for running the kernels under a memory checker, which is closed on the shared
+    GPU pool.  The kernels themselves do not re-check: an index outside its table is never dereferenced because the
+    call raises before the launch."""
+    return os.environ.get("SKYRL_B200_DEBUG_BOUNDS", "0") == "1"
+
+
+def check_index(what: str, idx: torch.Tensor | None, limit: int, min_value: int = 0) -> None:
+    """Raise ``IndexOutOfRange`` when any element of ``idx`` lies outside ``[min_value, limit)`` (debug mode only;
+    a CUDA-graph capture in progress skips the check because it cannot synchronise)."""
+    if idx is None or idx.numel() == 0 or not debug_bounds():
+        return
+    if idx.is_cuda and torch.cuda.is_current_stream_capturing():
+        return
+    lo, hi = int(idx.min()), int(idx.max())
+    if lo < min_value or hi >= limit:
+        raise IndexOutOfRange(f"{what}: index range [{lo}, {hi}] outside [{min_value}, {limit})")
+
+
 # ----------------------------------------------------------------------------- host<->device accounting
 H2D_BYTES = 0
 D2H_BYTES = 0

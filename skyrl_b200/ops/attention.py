@@ -164,6 +164,7 @@ def kv_cache_write(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     Caches are ``[num_blocks, block_size, nkv, D]``; a slot is ``block * block_size + offset``.
     """
     T = qkv.shape[0]
+    _lib.check_index("kv_cache_write: cache slot", slots, k_cache.shape[0] * k_cache.shape[1], min_value=-(1 << 31))
     if qkv.is_cuda:
         code = _k().sb_kv_cache_write(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slots.data_ptr(), T, nq,
                                       nkv, D, qkv.stride(0), 0, _lib.stream_ptr())
@@ -213,6 +214,13 @@ def attn_decode_paged(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     n = qkv.shape[0]
+    if _lib.debug_bounds():
+        bs_ = k_cache.shape[1]
+        _lib.check_index("attn_decode_paged: context length", ctx_lens, block_tables.shape[1] * bs_ + 1)
+        if ctx_lens.numel() and not (ctx_lens.is_cuda and torch.cuda.is_current_stream_capturing()):
+            # only the table entries a sequence's context reaches are read
+            used = (torch.arange(block_tables.shape[1], device=block_tables.device)[None, :] * bs_) < ctx_lens[:, None]
+            _lib.check_index("attn_decode_paged: block table entry", block_tables[: ctx_lens.shape[0]][used], k_cache.shape[0])
     if not qkv.is_cuda or sinks is not None:
         q = qkv[:, : nq * D].reshape(n, nq, D)
         return attn_decode_paged_ref(q, k_cache, v_cache, block_tables, ctx_lens, scale, sinks).reshape(n, nq * D)

@@ -242,6 +242,9 @@ def qkv_finalize(partials: torch.Tensor, n_part: int, pos: torch.Tensor, table: 
     """Sum the fp32 partials of the fused QKV projection, rotate q/k, write bf16 ``qkv`` and scatter k/v rows
     into their paged-cache slot (one kernel for what was reduction + RoPE + cache write)."""
     T = qkv.shape[0]
+    if k_cache is not None:
+        _lib.check_index("qkv_finalize: cache slot", slots, k_cache.shape[0] * k_cache.shape[1], min_value=-(1 << 31))
+    _lib.check_index("qkv_finalize: position", pos, table.shape[0])
     if not qkv.is_cuda:
         full = partials[:n_part].sum(0).to(qkv.dtype)
         full = _rope_ref(full, pos, table, nq + nkv, head_dim, 1.0)

@@ -170,4 +170,6 @@ def lm_head_logprobs(hidden: torch.Tensor, W: torch.Tensor, targets: torch.Tenso
     ``peer_exchange`` callable that publishes the local partial records and returns the device pointers
     of every rank's records.
     """
+    if peer_exchange is None and vocab_offset == 0:  # vocabulary-parallel shards legitimately see foreign targets
+        _lib.check_index("lm_head_logprobs: target id", targets, W.shape[0])
     return _LMHeadLogprobFn.apply(hidden, W, targets, inv_temp, with_entropy, vocab_offset, peer_exchange)

@@ -83,6 +83,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: int, step_coun
 
 def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """Row gather ``table[ids]`` (no autograd; the trainer's embedding uses ``embedding`` in models)."""
+    _lib.check_index("embed: token id", ids, table.shape[0])
     if not table.is_cuda:
         return table[ids.long()]
     T, H = ids.numel(), table.shape[1]

@@ -160,3 +160,25 @@ def test_slot_compaction_keeps_outputs_and_shrinks_the_decode_batch():
     for a, b in zip(out, ref):
         assert a.token_ids == b.token_ids
     assert eng.metrics()["kv_free_blocks"] == 256 and sorted(eng._free_slots) == list(range(32))
+
+
+def test_same_prompt_sampled_n_times_is_prefilled_once():
+    """GRPO sends every prompt n times in one call.  With the prefix cache on, the scheduler admits one copy, lets it
+    publish its blocks, and the other copies share them: only their last block is computed again."""
+    m = _model()
+    torch.manual_seed(3)
+    p1, p2 = torch.randint(4, 97, (40,)).tolist(), torch.randint(4, 97, (37,)).tolist()
+    prompts = [p1] * 4 + [p2] * 3
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    res = {}
+    for caching in (False, True):
+        eng = LLMEngine(m, EngineConfig(block_size=8, max_num_seqs=8, max_model_len=64, num_blocks=128,
+                                        enable_prefix_caching=caching))
+        outs = eng.generate(prompts, sp)
+        res[caching] = ([o.token_ids for o in outs], eng.stats.get("prefix_cached_tokens", 0),
+                        eng.stats.get("prefill_tokens", None))
+        assert eng.metrics()["kv_free_blocks"] == 128
+    assert res[True][0] == res[False][0]
+    assert all(t == res[True][0][0] for t in res[True][0][:4])  # greedy copies agree
+    # p1: 39 matchable tokens -> 4 full blocks (32 tokens) shared by 3 copies; p2: 36 -> 4 blocks shared by 2 copies
+    assert res[False][1] == 0 and res[True][1] == 3 * 32 + 2 * 32

@@ -148,3 +148,29 @@ def test_env_var_registry_lists_every_variable_the_code_reads():
                 found |= set(re.findall(r'(?:environ\.get|getenv)\(\s*"((?:SB|SKYRL)_[A-Z0-9_]+)"', text))
     assert found <= names, sorted(found - names)
     assert env_vars.get("SB_PDL") is True and isinstance(env_vars.SKYRL_WORKER_NCCL_TIMEOUT_IN_S, int)
+
+
+def test_debug_bounds_mode_rejects_bad_indices_before_the_kernel(monkeypatch):
+    """SKYRL_B200_DEBUG_BOUNDS=1 stands in for a memory checker: an index outside its table raises at the op boundary."""
+    import pytest
+    import torch
+
+    from skyrl_b200.ops import _lib, attention, sampling
+
+    table = torch.randn(16, 8)
+    kc, vc = torch.zeros(4, 2, 1, 8), torch.zeros(4, 2, 1, 8)
+    qkv = torch.randn(3, 3 * 8)
+    # off: the CPU reference paths index as usual (a bad id fails inside torch, a negative slot means "skip")
+    assert sampling.embed(table, torch.tensor([0, 15])).shape == (2, 8)
+    monkeypatch.setenv("SKYRL_B200_DEBUG_BOUNDS", "1")
+    assert _lib.debug_bounds()
+    with pytest.raises(_lib.IndexOutOfRange, match="token id"):
+        sampling.embed(table, torch.tensor([0, 16]))
+    with pytest.raises(_lib.IndexOutOfRange, match="cache slot"):
+        attention.kv_cache_write(qkv, kc, vc, torch.tensor([0, 8, -1]), 1, 1, 8)
+    attention.kv_cache_write(qkv, kc, vc, torch.tensor([0, 7, -1]), 1, 1, 8)  # -1 = skip is legal
+    bt = torch.tensor([[0, 3], [1, 9]], dtype=torch.int32)
+    with pytest.raises(_lib.IndexOutOfRange, match="block table"):
+        attention.attn_decode_paged(qkv[:2], kc, vc, bt, torch.tensor([2, 4], dtype=torch.int32), 1, 1, 8)
+    # the bad entry is beyond what the second sequence's context reaches: not read, not an error
+    attention.attn_decode_paged(qkv[:2], kc, vc, bt, torch.tensor([2, 2], dtype=torch.int32), 1, 1, 8)
