@@ -262,7 +262,7 @@ def main() -> None:
     ap.add_argument("--n-samples", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--resp-len", type=int, default=None, help="fixed response length (overrides the configuration's range)")
-    ap.add_argument("--prefix-caching", type=int, default=0,
+    ap.add_argument("--prefix-caching", type=int, default=1,
                     help="engine prefix cache: the n samples of a prompt share its key/value blocks and it is prefilled once")
     ap.add_argument("--no-e2e", action="store_true", help="skip the separately timed end-to-end steps (long configurations)")
     ap.add_argument("--turns", type=int, default=None, help="config 5: turns per trajectory")

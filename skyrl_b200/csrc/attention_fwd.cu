@@ -200,9 +200,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
 
     for (int j = 0; j < n_kv; ++j) {
       const int sb_ = j & 1;
-      if (!mbar_wait(&s_full[sb_], (j >> 1) & 1, status, 0x420)) {
-        ok = false;
-        break;
+      {
+        const bool have_s = mbar_wait(&s_full[sb_], (j >> 1) & 1, status, 0x420);
+        if (!__all_sync(0xffffffffu, have_s)) {  // the whole warp stays or leaves: TMEM loads are warp-wide
+          ok = false;
+          break;
+        }
       }
       tc_fence_after();
       const bool diag = (j == qblk);
@@ -232,24 +235,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
         __threadfence_block();
         seqs[hf * 128 + r] = j + 1;
         int spins = 0;
+        bool got = true;
         while (seqs[(1 - hf) * 128 + r] < j + 1) {
           if (++spins > (1 << 24)) {
             atomicCAS(status, 0, 0x423);
-            ok = false;
+            got = false;
             break;
           }
         }
-        if (!ok) break;
+        // leave the loop as a whole warp: the TMEM loads below are warp-wide instructions
+        if (!__all_sync(0xffffffffu, got)) {
+          ok = false;
+          break;
+        }
         __threadfence_block();
         mx = fmaxf(mx, vals[(1 - hf) * 128 + r]) * scale_log2;
       }
-      if (mx > m + kRescaleGap) {
-        // move the reference: everything accumulated so far shrinks by alpha (nothing to shrink on the first block)
-        const float alpha = fast_exp2(m - mx);  // m = -inf on the first block -> 0
+      {
+        // move the reference where the row maximum outgrew it: everything accumulated so far shrinks by alpha.  The
+        // O rescale is a warp-wide TMEM read-modify-write, so the warp does it together whenever any of its rows
+        // needs it; rows that keep their reference multiply by one.
+        const bool grow = mx > m + kRescaleGap;
+        const float alpha = grow ? fast_exp2(m - mx) : 1.f;  // m = -inf on the first block -> 0
+        if (grow) m = mx;
         l *= alpha;
-        m = mx;
-        if (j > 0) {
-          if (!mbar_wait(o_full, (j - 1) & 1, status, 0x421)) {  // PV of block j-1 has landed in O
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          const bool landed = mbar_wait(o_full, (j - 1) & 1, status, 0x421);  // PV of block j-1 is in O
+          if (!__all_sync(0xffffffffu, landed)) {
             ok = false;
             break;
           }
@@ -268,23 +280,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
       }
       const float neg_m = -m;
       float psum = 0.f;
+      // exponentials first (packed in place over the scores), the shared-memory stores after the wait below
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float e0 = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), scale_log2, neg_m));
+        const float e1 = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), scale_log2, neg_m));
+        psum += e0 + e1;
+        sv[i] = pack_bf16x2(e0, e1);
+      }
+      // P is single-buffered: the PV MMA of block j-1 reads it until o_full(j-1) completes.  It was issued long before
+      // this block's exponentials were done, so the wait is normally over already.
+      if (j > 0) {
+        const bool landed = mbar_wait(o_full, (j - 1) & 1, status, 0x424);
+        if (!__all_sync(0xffffffffu, landed)) {
+          ok = false;
+          break;
+        }
+      }
+      // P (bf16) into the swizzled K-major tile: sub-tile hf, row r, eight 16-byte chunks
       uint8_t* prow = sP + hf * 16384 + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float e[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          e[i] = fast_exp2(fmaf(__uint_as_float(sv[8 * c + i]), scale_log2, neg_m));
-          psum += e[i];
-        }
-        uint4 o;
-        o.x = pack_bf16x2(e[0], e[1]);
-        o.y = pack_bf16x2(e[2], e[3]);
-        o.z = pack_bf16x2(e[4], e[5]);
-        o.w = pack_bf16x2(e[6], e[7]);
-        // P (bf16) into the swizzled K-major tile: sub-tile hf, row r, eight 16-byte chunks
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = o;
-      }
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
       l += psum;
       fence_proxy_async_smem();
       tc_fence_before();
@@ -293,6 +310,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
     }
     // final O: the last PV has to land first
     if (ok) ok = mbar_wait(o_full, (n_kv - 1) & 1, status, 0x422);
+    ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     // combine the two half-row sums
     if (hf == 1) s_l[r] = l;
@@ -303,24 +321,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
     const float l_tot = s_l[r];
-    if (ok && r < rows_valid) {
-      const float inv = 1.f / l_tot;
-      __nv_bfloat16* orow = out + static_cast<size_t>(q_row0 + r) * (nq * kAttnD) + h * kAttnD + hf * 64;
+    const float inv = 1.f / l_tot;
+    const bool store = ok && r < rows_valid;
+    __nv_bfloat16* orow = out + static_cast<size_t>(q_row0 + r) * (nq * kAttnD) + h * kAttnD + hf * 64;
+    if (ok) {  // warp-uniform: the TMEM loads are warp-wide, only the stores depend on the row
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_o + c * 32, v);
         tmem_ld_wait();
+        if (store) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 o;
-          o.x = pack_bf16x2(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
-          o.y = pack_bf16x2(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
-          o.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
-          o.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
-          reinterpret_cast<uint4*>(orow)[c * 4 + u] = o;
+          for (int u = 0; u < 4; ++u) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
+            reinterpret_cast<uint4*>(orow)[c * 4 + u] = o;
+          }
         }
       }
+    }
+    if (store) {
       if (hf == 0 && lse) lse[static_cast<size_t>(h) * T + q_row0 + r] = (m + log2f(l_tot)) * 0.6931471805599453f;
     }
   }

@@ -93,6 +93,34 @@ def test_attn_bwd(lens, nq, nkv):
         assert rel(qkv.grad[:, sl], x.grad[:, sl]) < 2e-2, name
 
 
+def test_attn_fwd_bwd_with_drifting_row_maxima():
+    """Scores whose row maximum keeps growing along the sequence (and by different amounts per row) force the forward
+    kernel to move its softmax reference after the first key/value block, for some rows of a warp and not for others:
+    the accumulator in tensor memory is rescaled mid-sequence.  Output, log-sum-exp (through the backward pass) and
+    gradients must still match the fp32 reference."""
+    torch.manual_seed(3)
+    nq, nkv, D = 4, 2, 128
+    lens = [700, 45, 260]
+    T = sum(lens)
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device="cuda") * 0.5
+    ramp = torch.linspace(0.5, 6.0, T, device="cuda")[:, None]          # keys late in a sequence score higher ...
+    rows = (1.0 + 3.0 * torch.rand(T, 1, device="cuda"))                # ... by a different factor for every query row
+    qkv[:, : nq * D] *= rows
+    qkv[:, nq * D : (nq + nkv) * D] *= ramp
+    qkv = qkv.to(torch.bfloat16).requires_grad_()
+    cu = torch.tensor([0, 700, 745, 1005], device="cuda", dtype=torch.int32)
+    out = attention.attn_varlen(qkv, cu, nq, nkv, D)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert _lib.status_read_clear() == 0
+    x = qkv.detach().float().requires_grad_()
+    ref, _ = attention.attn_varlen_ref(x, cu, nq, nkv, D, 1 / math.sqrt(D))
+    ref.backward(g.float())
+    assert rel(out, ref) < 1e-2
+    assert rel(qkv.grad, x.grad) < 3e-2
+
+
 @pytest.mark.parametrize("nq,nkv,bs", [(12, 2, 16), (28, 4, 32), (4, 4, 16)])
 def test_decode_paged(nq, nkv, bs):
     torch.manual_seed(0)
