@@ -132,7 +132,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "both"], help="lmhead: which implementation to time")
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--hidden-lm", type=int, default=1536)
-    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "elementwise", "relayout"])
+    ap.add_argument("--which", default="gemm", choices=["gemm", "decode_attn", "attn", "lmhead", "tp_gather", "tp_scatter", "moe", "elementwise", "relayout",
+                             "decode_block"])
     ap.add_argument("--layers", type=int, default=8, help="relayout: decoder layers of the Qwen2.5-1.5B-shaped source model")
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--topk", type=int, default=8)
@@ -280,6 +281,29 @@ def main() -> None:
         moved = 2.0 * push.bytes_out  # read + write
         out.update(layers=a.layers, block_copies=push.n_desc, work_items=push.n_items, bytes_out=push.bytes_out, ms=ms,
                    gbs_read_plus_write=moved / ms / 1e6, fraction_of_measured_hbm=moved / ms / 1e6 / a.hbm_gbs)
+    elif a.which == "decode_block":
+        # persistent decode block kernel (o-proj .. down-proj of one layer, Qwen2.5-1.5B shapes): one warm launch with
+        # every CTA's clock recorded at the phase boundaries; prints when the last CTA finished each phase
+        from skyrl_b200.ops import _lib
+        from skyrl_b200.ops import elementwise as ew
+
+        H, Q, F, n = 1536, 1536, 8960, a.seqs
+        g = torch.Generator(device="cuda").manual_seed(0)
+        rnd = lambda *s, scale=1.0: (torch.randn(*s, device="cuda", generator=g) * scale).to(torch.bfloat16)  # noqa: E731
+        att, x = rnd(n, Q), rnd(n, H)
+        wo, wgu, wd = rnd(H, Q, scale=Q ** -0.5), rnd(2 * F, H, scale=H ** -0.5), rnd(H, F, scale=F ** -0.5)
+        ln = torch.ones(H, **bf)
+        ws = ew.DecodeMlpWorkspace(256, H, Q, F, "cuda")
+        for _ in range(3):
+            ew.decode_mlp_block(att, x.clone(), wo, ln, wgu, wd, ln, 1e-6, ws)
+        torch.cuda.synchronize()
+        ws.trace = torch.zeros(torch.cuda.get_device_properties(0).multi_processor_count, 16, device="cuda", dtype=torch.int64)
+        ms = timeit(lambda: ew.decode_mlp_block(att, x.clone(), wo, ln, wgu, wd, ln, 1e-6, ws), a.iters)
+        t = ws.trace.cpu().double()
+        t0 = t[:, 0].min()
+        names = ["o-proj", "barrier 1", "norm", "barrier 2", "gate/up + SwiGLU", "barrier 3", "down-proj", "barrier 4", "norm"]
+        out.update(rows=n, ms_per_launch_with_clone=ms, device_status=_lib.status_read_clear(),
+                   all_ctas_done_us={nm: round(float((t[:, k + 1].max() - t0) / 1e3), 2) for k, nm in enumerate(names)})
     elif a.which == "elementwise":
         # the bandwidth-bound kernels of a step: achieved bytes / s against the measured copy bandwidth
         from skyrl_b200.ops import elementwise as ew, optim, sampling

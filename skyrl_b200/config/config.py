@@ -601,6 +601,9 @@ class B200Config(BaseConfig):
     vocab_parallel_lm_head: bool = False
     # fused peer optimizer: start each layer's gradient reduce-scatter behind the last micro-batch's backward pass
     overlap_grad_reduce: bool = True
+    # pure data parallelism: re-deal the rows of every policy mini-batch among the ranks so that all ranks train on
+    # about the same number of tokens (the summed gradient does not change; train/balance.py)
+    balance_tokens_across_ranks: bool = True
 
 
 @dataclass

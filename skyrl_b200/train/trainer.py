@@ -412,6 +412,7 @@ class PPOTrainer:
                 if role == "policy":
                     pb = [(a - s, b - s) for a, b in compute_prompt_boundaries(uids[s:e])]
                     mini = self._normalize_advantages(mini, pb)
+                    mini = self._balance_tokens(mini)
                 status = worker.forward_backward(mini, **({"step_follows": True} if role == "policy" else {}))
                 gn = worker.optim_step()
                 if gn is not None:
@@ -419,6 +420,25 @@ class PPOTrainer:
                 all_status.append({k: v for k, v in status.items() if isinstance(v, (int, float))})
         keys = set().union(*[s.keys() for s in all_status]) if all_status else set()
         return {k: float(np.mean([s[k] for s in all_status if k in s])) for k in keys}
+
+    def _balance_tokens(self, mini: TrainingInputBatch) -> TrainingInputBatch:
+        """Pure data parallelism: re-deal the mini-batch's rows so that every rank trains on about the same number of
+        tokens.  Runs after the loss reduction has been folded into the advantages, so each row carries all that its
+        loss term needs and the summed gradient is unchanged."""
+        W = self.env.world_size
+        if (W <= 1 or not dist.is_initialized() or self._data_share() != 1
+                or not getattr(self.cfg.trainer.b200, "balance_tokens_across_ranks", False)
+                or getattr(self.policy, "pipe", None) is not None):
+            return mini
+        from .balance import balance_rows_across_ranks
+
+        out, rep = balance_rows_across_ranks(mini, self.env.rank, W)
+        metrics = getattr(self, "all_metrics", None)
+        if rep is not None and metrics is not None:
+            mean = max(1.0, rep["mean_tokens"])
+            metrics["policy/token_imbalance_before"] = rep["max_tokens_before"] / mean
+            metrics["policy/token_imbalance_after"] = rep["max_tokens_after"] / mean
+        return out
 
     def train_critic_and_policy(self, batch: TrainingInputBatch) -> Dict[str, float]:
         m: Dict[str, float] = {}

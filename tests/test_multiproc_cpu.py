@@ -75,3 +75,10 @@ def test_gloo_rl_step_with_tensor_parallel_engine():
 def test_gloo_hybrid_sharded_optimizer_four_ranks():
     p = _run([os.path.join(ROOT, "tests", "mp", "hsdp_check.py")], nproc=4, port=29651)
     assert p.returncode == 0 and "HSDP_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+@pytest.mark.parametrize("nproc,port", [(2, 29661), (4, 29662)])
+def test_gloo_token_balancing_keeps_the_update_and_evens_the_loads(nproc, port):
+    p = _run([os.path.join(ROOT, "tests", "mp", "balance_check.py")], nproc=nproc, port=port)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert f"BALANCE_OK world={nproc}" in p.stdout
