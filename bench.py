@@ -271,7 +271,9 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=None, help="tensor-parallel size of the training model (1 = sharded data parallel)")
     ap.add_argument("--ep", type=int, default=None, help="expert-parallel size (MoE models)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size of the training model")
-    ap.add_argument("--sp", type=int, default=1, help="Ulysses sequence-parallel size of the training model")
+    ap.add_argument("--sp", type=int, default=1, help="sequence-parallel size of the training model")
+    ap.add_argument("--sp-backend", default="ulysses", choices=["ulysses", "context"],
+                    help="ulysses: heads exchanged by all-to-all; context: keys / values all-gathered (context parallelism)")
     ap.add_argument("--engine-tp", type=int, default=None, help="tensor-parallel size of each rollout engine (lock-step ranks, "
                     "all-reduce in the o-proj / down-proj GEMM epilogues)")
     ap.add_argument("--reuse-train-forward", action="store_true",
@@ -341,8 +343,8 @@ def main() -> None:
           if args.ep > 1 else []),
         *(["trainer.strategy=megatron", f"trainer.policy.megatron_config.pipeline_model_parallel_size={args.pp}"]
           if args.pp > 1 else []),
-        *([f"trainer.policy.sequence_parallel_size={args.sp}", f"trainer.ref.sequence_parallel_size={args.sp}"]
-          if args.sp > 1 else []),
+        *([f"trainer.policy.sequence_parallel_size={args.sp}", f"trainer.ref.sequence_parallel_size={args.sp}",
+           f"trainer.sequence_parallel_backend={args.sp_backend}"] if args.sp > 1 else []),
         *([f"generator.inference_engine.tensor_parallel_size={args.engine_tp}"] if args.engine_tp > 1 else []),
         f"trainer.b200.reuse_train_forward_for_old_logprobs={'true' if args.reuse_train_forward else 'false'}"])
     tok = SyntheticTokenizer(margs.vocab_size)
@@ -471,7 +473,8 @@ def main() -> None:
                        "global_batch": P * n * world, "seq_len": PROMPT_LEN + RESP_MAX,
                        "parallelism": (f"dp{world} x ep{args.ep} (fused expert dispatch/combine)" if args.ep > 1 else
                                        f"dp{world // args.pp} x pp{args.pp} (layer stages)" if args.pp > 1 else
-                                       f"dp{world // args.sp} x sp{args.sp} (Ulysses, fused projections)" if args.sp > 1 else
+                                       (f"dp{world // args.sp} x cp{args.sp} (context parallel, key/value all-gather)" if args.sp_backend == "context"
+                                        else f"dp{world // args.sp} x sp{args.sp} (Ulysses, fused projections)") if args.sp > 1 else
                                        f"dp{world} (sharded optimizer, colocated engine per GPU)" if args.tp == 1 else
                                        f"dp{world // args.tp} x tp{args.tp} (fused GEMM collectives, colocated engine per GPU)"),
                        "prompts_per_gpu": P, "n_samples_per_prompt": n, "prompt_len": PROMPT_LEN,

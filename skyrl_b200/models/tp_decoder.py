@@ -394,6 +394,73 @@ class UlyssesCausalLM(CausalLM):
         return
 
 
+class ContextParallelCausalLM(UlyssesCausalLM):
+    """Replicated weights, sequence-sharded activations, and attention that keeps all heads: every rank of the ``cp``
+    group owns a contiguous slice of the packed token axis and all-gathers the keys and values of the tokens before it
+    (context parallelism by key/value all-gather).  Unlike Ulysses, whose degree is bounded by the number of key/value
+    heads, the degree here is free, at the price of gathering K and V (2 x kv_dim per token and layer; small under
+    grouped-query attention).
+
+    The attention kernel takes one packed q|k|v tensor, so a rank builds the rows from the start of the first
+    sequence that reaches into its slice up to the end of its slice: K and V come from the gathered tensor, Q is zero
+    for the rows it does not own, and only its own rows of the result are kept.  The kernel therefore also walks the
+    query blocks of the foreign rows (their results are dropped); a per-sequence first-query-block argument for the
+    kernels would remove that work and is not built.  The backward pass returns the K / V gradients to their owners
+    through the reduce-scatter of the gather.  Reference: Megatron ``context_parallel_size``
+    (skyrl/backends/skyrl_train/distributed/megatron/megatron_utils.py:421-425,510-530) with ring attention from
+    TransformerEngine; selected here with ``trainer.sequence_parallel_backend=context`` (or the Megatron strategy's
+    ``context_parallel_size``).
+    """
+
+    def __init__(self, args: ModelArgs, sp: tpm.TPGroup, **kw):
+        if args.attention_sinks or args.num_experts:
+            raise NotImplementedError("context parallelism supports dense models without attention sinks")
+        self.tp = sp
+        CausalLM.__init__(self, args, **kw)
+
+    def _layer(self, i: int, x, delta, pos, cu, max_seqlen, kv_sink=None, attn_fn=None):
+        from ..ops import gemm
+
+        a, cp = self.args, self.tp
+        pre = f"layers.{i}."
+        row0, row1, first, cu_loc, max_loc = self._cp_plan
+        x, h = ew.add_rmsnorm(x, delta, self.p(pre + "ln1"), a.rms_norm_eps)
+        qkv = gemm.linear(h, self.p(pre + "wqkv"), self._p.get(pre + "bqkv"))
+        if a.qk_norm:
+            qkv = self._qk_norm(qkv, i)
+        qkv = ew.rope(qkv, pos[row0:row1], self.rope_table(qkv.device), a.num_heads + a.num_kv_heads, a.head_dim)
+        kv_all = _AllGatherRowsSumBwdFn.apply(qkv[:, a.q_dim:].contiguous(), cp.group)  # [T, 2 * kv_dim]
+        lead = row0 - first
+        q_rows = qkv[:, : a.q_dim]
+        if lead > 0:
+            q_rows = torch.cat([q_rows.new_zeros((lead, a.q_dim)), q_rows], 0)
+        full = torch.cat([q_rows, kv_all[first:row1]], 1)
+        att = attn_ops.attn_varlen(full, cu_loc, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_loc)
+        o = gemm.linear(att[lead:].contiguous(), self.p(pre + "wo"))
+        x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
+        d = gemm.linear(ew.swiglu(gemm.linear(h, self.p(pre + "wgu"))), self.p(pre + "wd"))
+        return x, d
+
+    def forward(self, input_ids, positions, cu_seqlens, max_seqlen: int = 0, kv_sink=None) -> torch.Tensor:
+        cp = self.tp
+        T = input_ids.numel()
+        R = T // cp.size
+        row0, row1 = cp.rank * R, (cp.rank + 1) * R
+        # rows [first, row1): from the start of the first sequence that reaches into this rank's slice
+        cu = [int(v) for v in cu_seqlens.tolist()]
+        first = max(c for c in cu if c <= row0)
+        bounds = [first] + [c for c in cu if first < c < row1] + [row1]
+        cu_loc = torch.tensor([b - first for b in bounds], dtype=cu_seqlens.dtype, device=cu_seqlens.device)
+        max_loc = max(b - a_ for a_, b in zip(bounds[:-1], bounds[1:]))
+        self._cp_plan = (row0, row1, first, cu_loc, max_loc)
+        x = _EmbeddingFn.apply(input_ids[row0:row1], self.p("embed"))
+        delta = None
+        for i in range(self.args.num_layers):
+            x, delta = self._layer(i, x, delta, positions, cu_seqlens, max_seqlen)
+        _, h = ew.add_rmsnorm(x, delta, self.p("final_norm"), self.args.rms_norm_eps)
+        return h
+
+
 EXPERT_LEAVES = ("experts_wgu", "experts_wd")
 
 

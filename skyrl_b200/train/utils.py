@@ -121,8 +121,9 @@ def validate_cfg(cfg, world_size: int = 1) -> None:
         t.strategy = "fsdp"
     if t.strategy not in ("fsdp", "megatron"):
         raise ValueError(f"unknown trainer.strategy '{t.strategy}' (expected fsdp or megatron)")
-    if t.sequence_parallel_backend != "ulysses":
-        raise ValueError("only sequence_parallel_backend='ulysses' is supported")
+    if t.sequence_parallel_backend not in ("ulysses", "context"):
+        raise ValueError("sequence_parallel_backend must be 'ulysses' (heads exchanged by all-to-all) or 'context' "
+                         "(keys / values all-gathered: context parallelism)")
     if a.advantage_estimator not in rl.AdvantageEstimatorRegistry.list_available():
         raise ValueError(f"unknown advantage_estimator '{a.advantage_estimator}'; available: "
                          f"{rl.AdvantageEstimatorRegistry.list_available()}")
@@ -183,14 +184,15 @@ def validate_parallel_cfg(cfg, world_size: int = 1) -> None:
                              "sequence parallelism is implied by tensor_model_parallel_size > 1")
         if pp > 1 and (tp > 1 or ep > 1):
             raise ValueError("pipeline parallelism cannot be combined with tensor or expert parallelism in this build")
-        if cp > 1:
-            raise ValueError("context_parallel_size > 1 is not supported; use Ulysses sequence parallelism (strategy=fsdp)")
+        if cp > 1 and max(tp, pp, ep) > 1:
+            raise ValueError("context parallelism cannot be combined with tensor, pipeline or expert parallelism in this build")
         if tp > 1 and ep > 1:
             raise ValueError("tensor and expert parallelism cannot be combined in this build")
         if t.policy.model.lora.rank > 0 and (tp > 1 or ep > 1 or pp > 1):
             raise ValueError("LoRA is supported with the data-parallel strategy only")
     for name, size in (("tensor_model_parallel_size", tp), ("expert_model_parallel_size", ep),
-                       ("pipeline_model_parallel_size", pp), ("policy.sequence_parallel_size", sp)):
+                       ("pipeline_model_parallel_size", pp), ("policy.sequence_parallel_size", sp),
+                       ("context_parallel_size", cp)):
         if size > 1 and world_size % size != 0:
             raise ValueError(f"{name}={size} does not divide the number of ranks ({world_size})")
         if size > 8:

@@ -252,8 +252,11 @@ class ModelWorker:
                 sp_peer = PeerContext(dev, group=self.mesh.tp_group) if dev.type == "cuda" else None
                 self.tp = TPGroup(sp_peer, self.mesh.tp_group)
                 self._plain_model = model
-                model = UlyssesCausalLM(model.args, self.tp, device=dev, dtype=dtype, flat_buffer=model.flat_params, seed=None,
-                                        value_head=value_head)
+                cls = UlyssesCausalLM
+                if self._sp_backend(cfg) == "context":
+                    from ..models.tp_decoder import ContextParallelCausalLM as cls  # noqa: N813
+                model = cls(model.args, self.tp, device=dev, dtype=dtype, flat_buffer=model.flat_params, seed=None,
+                            value_head=value_head)
         self.model = model
         qcfg = getattr(cfg.policy.model, "fake_int4_qat", None)
         if trainable and qcfg is not None and qcfg.enabled:
@@ -377,10 +380,22 @@ class ModelWorker:
         return path
 
     def _sp_size_from_cfg(self, cfg) -> int:
-        if getattr(cfg, "strategy", "fsdp") == "megatron":
-            return 1
         node = {"policy": cfg.policy, "ref": cfg.ref, "critic": cfg.critic}.get(self.role, cfg.policy)
+        if getattr(cfg, "strategy", "fsdp") == "megatron":
+            # Megatron naming: context parallelism shards the sequence (tensor / expert / pipeline sizes are handled
+            # by their own branches before this one is reached)
+            mc = getattr(node, "megatron_config", None)
+            return int(getattr(mc, "context_parallel_size", 1) or 1)
         return int(getattr(node, "sequence_parallel_size", 1) or 1)
+
+    @staticmethod
+    def _sp_backend(cfg) -> str:
+        """``ulysses`` (heads exchanged by all-to-all; degree divides the key/value heads) or ``context`` (keys and
+        values all-gathered; any degree)."""
+        if getattr(cfg, "strategy", "fsdp") == "megatron":
+            return "context"
+        b = str(getattr(cfg, "sequence_parallel_backend", "ulysses") or "ulysses").lower()
+        return "context" if b in ("context", "cp", "ring", "allgather_kv") else "ulysses"
 
     def engine_model(self, engine_tp: int = 1) -> CausalLM:
         """The model object a colocated generation engine should run.  Shared with training whenever the training

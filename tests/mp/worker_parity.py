@@ -21,7 +21,8 @@ from skyrl_b200.train.batch import TrainingInputBatch  # noqa: E402
 from skyrl_b200.workers.worker import PolicyWorker  # noqa: E402
 
 MODELS = {"tp": "tiny-llama", "sp": "tiny-llama", "pp": "tiny-llama", "ep": "tiny-moe", "tpv": "tiny-llama",
-          "critic_tp": "tiny-llama", "critic_sp": "tiny-llama"}
+          "critic_tp": "tiny-llama", "critic_sp": "tiny-llama", "cp": "tiny-llama", "cp_megatron": "tiny-llama",
+          "critic_cp": "tiny-llama"}
 
 
 def cfg_for(mode: str, model: str):
@@ -34,6 +35,10 @@ def cfg_for(mode: str, model: str):
                 "trainer.b200.vocab_parallel_lm_head=true"],
         "critic_tp": ["trainer.strategy=megatron", "trainer.policy.megatron_config.tensor_model_parallel_size=2"],
         "critic_sp": ["trainer.critic.sequence_parallel_size=2", "trainer.policy.sequence_parallel_size=2"],
+        "cp": ["trainer.policy.sequence_parallel_size=2", "trainer.sequence_parallel_backend=context"],
+        "cp_megatron": ["trainer.strategy=megatron", "trainer.policy.megatron_config.context_parallel_size=2"],
+        "critic_cp": ["trainer.critic.sequence_parallel_size=2", "trainer.policy.sequence_parallel_size=2",
+                      "trainer.sequence_parallel_backend=context"],
         "none": [],
     }[mode]
     return SkyRLTrainConfig.from_cli_overrides([
@@ -91,6 +96,8 @@ def main():
 
     Worker = CriticWorker if mode.startswith("critic") else PolicyWorker
     w = Worker(cfg_for(mode, model).trainer, model_path=model, env=env, seed=0)
+    if mode in ("cp", "cp_megatron", "critic_cp"):
+        assert type(w.model).__name__ == "ContextParallelCausalLM"
     if mode == "tpv":
         assert w.model.vocab_parallel_head and w.model.p("lm_head").shape[0] == 512
     if mode == "ep":

@@ -52,7 +52,8 @@ import pytest  # noqa: E402
 
 
 @pytest.mark.parametrize("mode,port", [("tp", 29641), ("sp", 29642), ("ep", 29643), ("pp", 29644), ("tpv", 29648),
-                                       ("critic_tp", 29649), ("critic_sp", 29650)])
+                                       ("critic_tp", 29649), ("critic_sp", 29650), ("cp", 29663),
+                                       ("cp_megatron", 29664), ("critic_cp", 29665)])
 def test_gloo_worker_update_matches_single_rank(mode, port):
     """forward_backward + optim_step through the worker under each model-parallel strategy: full parameters equal a
     single-rank update on the same data, group replicas are bit-identical, one optimizer step per RL step."""
@@ -82,3 +83,17 @@ def test_gloo_token_balancing_keeps_the_update_and_evens_the_loads(nproc, port):
     p = _run([os.path.join(ROOT, "tests", "mp", "balance_check.py")], nproc=nproc, port=port)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert f"BALANCE_OK world={nproc}" in p.stdout
+
+
+@pytest.mark.parametrize("nproc,port", [(2, 29666), (3, 29667)])
+def test_gloo_context_parallel_model_matches_plain_model(nproc, port):
+    """Key/value all-gather context parallelism: log-probs and summed weight gradients equal the plain model's, also
+    at a degree (3) that does not divide the two key/value heads."""
+    p = _run([os.path.join(ROOT, "tests", "mp", "cp_check.py")], nproc=nproc, port=port)
+    assert p.returncode == 0 and f"CP_MODEL_OK world={nproc}" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_gloo_two_rank_context_parallel_rl_step():
+    p = _run([os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "1", "--model", "tiny-llama",
+              "--prompts-per-gpu", "1", "--sp", "2", "--sp-backend", "context"], port=29668)
+    assert p.returncode == 0 and '"n_gpus": 2' in p.stdout and "context parallel" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
