@@ -150,3 +150,163 @@ def merge_stepwise_output(out: GeneratorOutput) -> GeneratorOutput:
         rollout_metrics=out.get("rollout_metrics"), rollout_expert_indices=None, env_metrics=None,
         trajectory_generation_times=None, trajectory_time_splits=None, pixel_values=None, image_grid_thw=None)
     return merged
+
+
+# ----------------------------------------------------------------------------- utilities for custom generators
+# What a hand-written generator (an agent loop that talks to the engine through chat messages) needs in order to hand
+# the trainer token ids, loss masks and rollout log-probs that are consistent with what the model saw.  Behavioural
+# reference: skyrl/train/generators/utils.py:105-182 (chat templates, generation prompt), :349-395 (overlong
+# filtering, turn counts), :567-774 (message encoding with a fixed base conversation), :783-804 (slicing).
+
+# ChatML without the "You are a helpful assistant" default that some tokenizers insert when no system message is given:
+# what a multi-turn rollout wants, because the conversation is tokenised piece by piece.
+CUSTOM_CHAT_TEMPLATES: Dict[str, str] = {
+    "chatml_no_default_system": (
+        "{% for message in messages %}"
+        "{{ '<|im_start|>' + message['role'] + '\\n' + message['content'] + '<|im_end|>' + '\\n' }}"
+        "{% endfor %}"
+        "{% if add_generation_prompt %}{{ '<|im_start|>assistant\\n' }}{% endif %}"),
+    # keeps earlier turns' <think> blocks (Qwen3's own template drops them, which changes the tokens of past turns)
+    "chatml_keep_thinking": (
+        "{% for message in messages %}"
+        "{{ '<|im_start|>' + message['role'] + '\\n' }}"
+        "{% if message['role'] == 'assistant' and message.get('reasoning_content') %}"
+        "{{ '<think>\\n' + message['reasoning_content'] + '\\n</think>\\n\\n' }}{% endif %}"
+        "{{ message['content'] + '<|im_end|>' + '\\n' }}"
+        "{% endfor %}"
+        "{% if add_generation_prompt %}{{ '<|im_start|>assistant\\n' }}{% endif %}"),
+}
+
+
+def get_custom_chat_template(chat_template_config: Optional[Any] = None) -> Optional[str]:
+    """``{"source": "name" | "file", "name_or_path": ...}`` (dict or config object) -> Jinja template text, or None to
+    keep the tokenizer's own template.  Files must be regular ``.jinja`` / ``.jinja2`` / ``.j2`` / ``.txt`` files."""
+    import os
+
+    if chat_template_config is None:
+        return None
+    get = chat_template_config.get if isinstance(chat_template_config, dict) else lambda k, d=None: getattr(chat_template_config, k, d)
+    source, name = get("source"), get("name_or_path")
+    if not source:
+        raise ValueError("chat template config needs a 'source' ('name' or 'file')")
+    if not name:
+        return None
+    if source == "name":
+        if name not in CUSTOM_CHAT_TEMPLATES:
+            raise ValueError(f"unknown chat template '{name}'; available: {sorted(CUSTOM_CHAT_TEMPLATES)}")
+        return CUSTOM_CHAT_TEMPLATES[name]
+    if source == "file":
+        path = os.path.realpath(os.path.expanduser(str(name)))
+        if not os.path.isfile(path) or os.path.splitext(path)[1].lower() not in (".jinja", ".jinja2", ".j2", ".txt"):
+            raise ValueError(f"chat template file '{name}' must be an existing .jinja / .jinja2 / .j2 / .txt file")
+        with open(path, encoding="utf-8") as f:
+            return f.read()
+    raise ValueError(f"chat template source must be 'name' or 'file', got '{source}'")
+
+
+def get_generation_prompt_ids(tokenizer, tokenizer_kwargs: Optional[Dict[str, Any]] = None) -> List[int]:
+    """Token ids the chat template appends to open an assistant turn (``<|im_start|>assistant\\n`` for ChatML): the
+    difference between templating one user message with and without the generation prompt."""
+    kw = dict(tokenizer_kwargs or {})
+    if "enable_thinking" in kw:
+        raise ValueError("enable_thinking changes the generation prompt per call: use encode_messages_subset")
+    probe = [{"role": "user", "content": ""}]
+    plain = list(tokenizer.apply_chat_template(probe, tokenize=True, **kw))
+    opened = list(tokenizer.apply_chat_template(probe, add_generation_prompt=True, tokenize=True, **kw))
+    return opened[len(plain):]
+
+
+_BASE_CONVERSATION = [{"role": "system", "content": "."}, {"role": "user", "content": "."}]
+
+
+def encode_messages_subset(messages: List[Dict[str, Any]], tokenizer, tokenizer_kwargs: Optional[Dict[str, Any]] = None) -> List[int]:
+    """Token ids of ``messages`` as they appear *inside* a longer conversation: a fixed two-message base conversation is
+    templated with and without them and the base's tokens are cut off, so a template that injects a default system
+    prompt (or a BOS token) at the start of a conversation does not inject it in the middle of a trajectory.  If the
+    last message is not an assistant message the generation prompt is *not* included."""
+    if not messages:
+        raise ValueError("messages must not be empty")
+    kw = dict(tokenizer_kwargs or {})
+    base = list(tokenizer.apply_chat_template(_BASE_CONVERSATION, add_generation_prompt=False, tokenize=True, **kw))
+    full = list(tokenizer.apply_chat_template(_BASE_CONVERSATION + list(messages), add_generation_prompt=False,
+                                              tokenize=True, **kw))
+    if full[: len(base)] != base:
+        raise ValueError("the chat template does not extend a conversation by appending tokens; give a custom template")
+    return full[len(base):]
+
+
+def get_response_ids_and_loss_mask_from_messages(messages: List[Dict[str, Any]], tokenizer,
+                                                 assistant_logprobs: Optional[List[List[float]]] = None,
+                                                 tokenizer_kwargs: Optional[Dict[str, Any]] = None):
+    """``(response_ids, loss_mask, rollout_logprobs | None)`` for the messages that follow the prompt.
+
+    Every message is encoded on its own with ``encode_messages_subset``.  Tokens of non-assistant messages are masked
+    out.  In an assistant message the generation prompt that opens the turn is masked out (the model did not produce
+    it), the tokens up to and including the end-of-turn token are trained on, and anything the template adds after
+    that token (a newline in ChatML) is masked out again.  ``assistant_logprobs[i]`` are the engine's log-probs of the
+    i-th assistant message's generated tokens: they are aligned to the trained positions (zeros elsewhere); when the
+    counts disagree by the end-of-turn token -- engines that stop *before* emitting it -- the missing entry is 0."""
+    if not messages:
+        raise ValueError("messages must not be empty")
+    gen_prompt = get_generation_prompt_ids(tokenizer, {k: v for k, v in (tokenizer_kwargs or {}).items() if k != "enable_thinking"})
+    eos = getattr(tokenizer, "eos_token_id", None)
+    ids: List[int] = []
+    mask: List[int] = []
+    lps: Optional[List[float]] = [] if assistant_logprobs is not None else None
+    a_idx = 0
+    for msg in messages:
+        cur = encode_messages_subset([msg], tokenizer, tokenizer_kwargs)
+        ids.extend(cur)
+        if msg.get("role") != "assistant":
+            mask.extend([0] * len(cur))
+            if lps is not None:
+                lps.extend([0.0] * len(cur))
+            continue
+        lead = len(gen_prompt) if cur[: len(gen_prompt)] == gen_prompt else 0
+        end = len(cur)
+        if eos is not None and eos in cur[lead:]:
+            end = len(cur) - cur[::-1].index(eos)  # one past the last end-of-turn token
+        n_train = end - lead
+        mask.extend([0] * lead + [1] * n_train + [0] * (len(cur) - end))
+        if lps is not None:
+            given = list(assistant_logprobs[a_idx]) if a_idx < len(assistant_logprobs) else []
+            if len(given) not in (n_train, n_train - 1):
+                raise ValueError(f"assistant message {a_idx}: {len(given)} log-probs for {n_train} generated tokens")
+            given = given + [0.0] * (n_train - len(given))
+            lps.extend([0.0] * lead + given + [0.0] * (len(cur) - end))
+        a_idx += 1
+    return ids, mask, lps
+
+
+def apply_overlong_filtering(loss_masks: List[List[int]], stop_reasons: List[str]) -> List[List[int]]:
+    """DAPO overlong filtering: a response that did not end by itself (stop reason other than ``stop``) is not
+    trained on at all.  Uses the engine's stop reasons, so it does not depend on a particular end-of-sequence id."""
+    if len(loss_masks) != len(stop_reasons):
+        raise ValueError("loss_masks and stop_reasons must have the same length")
+    return [list(m) if r == "stop" else [0] * len(m) for m, r in zip(loss_masks, stop_reasons)]
+
+
+def compute_turn_token_counts(loss_masks: List[List[int]]) -> List[int]:
+    """Generated tokens per assistant turn over a batch: every maximal run of non-zero loss-mask entries is one turn
+    (observation tokens are masked, so they separate the runs).  Fully masked trajectories contribute nothing."""
+    counts: List[int] = []
+    for m in loss_masks:
+        run = 0
+        for v in m:
+            if v:
+                run += 1
+            elif run:
+                counts.append(run)
+                run = 0
+        if run:
+            counts.append(run)
+    return counts
+
+
+def slice_generator_output(out: GeneratorOutput, start: int, end: int) -> GeneratorOutput:
+    """Rows ``[start, end)`` of every per-trajectory list of a generator output (scalars and ``None`` pass through)."""
+    n = len(out["response_ids"])
+    res: Dict[str, Any] = {}
+    for k, v in out.items():
+        res[k] = v[start:end] if isinstance(v, list) and len(v) == n else v
+    return res  # type: ignore[return-value]

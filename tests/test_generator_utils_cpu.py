@@ -1,0 +1,109 @@
+"""Utilities for hand-written generators: chat templates, message encoding inside a conversation, loss masks and
+log-prob alignment per message, overlong filtering, turn counts, slicing."""
+import pytest
+
+from skyrl_b200.train.generators import utils as U
+from skyrl_b200.utils.tokenizer import SyntheticTokenizer
+
+
+class _ChatMLTok:
+    """A word-level ChatML-like tokenizer that, like some real templates, injects a default system message when the
+    conversation does not start with one, and puts a newline token after the end-of-turn token."""
+
+    IM_START, IM_END, NL = 1000, 1001, 1002
+    eos_token_id = 1001
+
+    def __init__(self):
+        self.vocab = {}
+
+    def _w(self, text):
+        return [self.vocab.setdefault(w, 10 + len(self.vocab)) for w in str(text).split()]
+
+    def apply_chat_template(self, conversation, add_generation_prompt=False, tokenize=True, **kw):
+        conv = list(conversation)
+        if not conv or conv[0]["role"] != "system":
+            conv = [{"role": "system", "content": "you are a default system prompt"}] + conv
+        ids = []
+        for m in conv:
+            ids += [self.IM_START] + self._w(m["role"]) + [self.NL] + self._w(m["content"]) + [self.IM_END, self.NL]
+        if add_generation_prompt:
+            ids += [self.IM_START] + self._w("assistant") + [self.NL]
+        return ids
+
+
+def test_generation_prompt_and_subset_encoding_do_not_inject_a_default_system_message():
+    tok = _ChatMLTok()
+    gp = U.get_generation_prompt_ids(tok)
+    assert gp == [tok.IM_START] + tok._w("assistant") + [tok.NL]
+    ids = U.encode_messages_subset([{"role": "user", "content": "tool says four"}], tok)
+    assert ids == [tok.IM_START] + tok._w("user") + [tok.NL] + tok._w("tool says four") + [tok.IM_END, tok.NL]
+    assert tok._w("default")[0] not in ids
+    with pytest.raises(ValueError):
+        U.encode_messages_subset([], tok)
+    with pytest.raises(ValueError):
+        U.get_generation_prompt_ids(tok, {"enable_thinking": False})
+
+
+def test_response_ids_mask_and_logprobs_follow_the_messages():
+    tok = _ChatMLTok()
+    msgs = [{"role": "assistant", "content": "let me look"}, {"role": "user", "content": "result 4"},
+            {"role": "assistant", "content": "the answer is 4"}]
+    lp1, lp2 = [-0.1, -0.2, -0.3, -0.4], [-1.0, -1.1, -1.2, -1.3]  # second engine stopped before the end-of-turn token
+    ids, mask, lps = U.get_response_ids_and_loss_mask_from_messages(msgs, tok, [lp1, lp2])
+    assert len(ids) == len(mask) == len(lps)
+    gp = U.get_generation_prompt_ids(tok)
+    a1 = gp + tok._w("let me look") + [tok.IM_END, tok.NL]
+    assert ids[: len(a1)] == a1
+    # generation prompt masked, content + end-of-turn trained, trailing newline masked
+    assert mask[: len(a1)] == [0] * len(gp) + [1] * 4 + [0]
+    assert lps[: len(a1)] == [0.0] * len(gp) + lp1 + [0.0]
+    u = [tok.IM_START] + tok._w("user") + [tok.NL] + tok._w("result 4") + [tok.IM_END, tok.NL]
+    assert ids[len(a1): len(a1) + len(u)] == u and set(mask[len(a1): len(a1) + len(u)]) == {0}
+    tail_mask, tail_lp = mask[len(a1) + len(u):], lps[len(a1) + len(u):]
+    assert tail_mask == [0] * len(gp) + [1] * 5 + [0]
+    assert tail_lp == [0.0] * len(gp) + lp2 + [0.0] + [0.0]  # 4 given for 5 trained tokens: the end-of-turn entry is 0
+    assert U.compute_turn_token_counts([mask]) == [4, 5]
+    with pytest.raises(ValueError):
+        U.get_response_ids_and_loss_mask_from_messages(msgs, tok, [[-0.1], lp2])
+    # the synthetic tokenizer of the test suite works the same way
+    st = SyntheticTokenizer(64)
+    ids, mask, lps = U.get_response_ids_and_loss_mask_from_messages(
+        [{"role": "assistant", "content": "7 8"}, {"role": "user", "content": "9"}], st)
+    assert ids == [3, 7, 8, 1, 2, 9, 1] and mask == [0, 1, 1, 1, 0, 0, 0] and lps is None
+
+
+def test_overlong_filtering_turn_counts_and_slicing():
+    masks = [[1, 1, 0, 1], [1, 1, 1], [0, 0]]
+    assert U.apply_overlong_filtering(masks, ["stop", "length", "stop"]) == [[1, 1, 0, 1], [0, 0, 0], [0, 0]]
+    with pytest.raises(ValueError):
+        U.apply_overlong_filtering(masks, ["stop"])
+    assert U.compute_turn_token_counts(masks) == [2, 1, 3]
+    assert U.compute_turn_token_counts([[], [0, 0]]) == []
+    out = {"prompt_token_ids": [[1], [2], [3]], "response_ids": [[4], [5], [6]], "rewards": [0.0, 1.0, 0.5],
+           "loss_masks": [[1], [1], [1]], "stop_reasons": ["stop"] * 3, "rollout_metrics": {"x": 1}, "rollout_logprobs": None}
+    s = U.slice_generator_output(out, 1, 3)
+    assert s["response_ids"] == [[5], [6]] and s["rewards"] == [1.0, 0.5] and s["rollout_metrics"] == {"x": 1}
+    assert s["rollout_logprobs"] is None
+
+
+def test_custom_chat_templates_by_name_and_file(tmp_path):
+    assert U.get_custom_chat_template(None) is None
+    assert U.get_custom_chat_template({"source": "name", "name_or_path": None}) is None
+    t = U.get_custom_chat_template({"source": "name", "name_or_path": "chatml_no_default_system"})
+    assert "<|im_start|>" in t and "add_generation_prompt" in t
+    with pytest.raises(ValueError):
+        U.get_custom_chat_template({"source": "name", "name_or_path": "nope"})
+    with pytest.raises(ValueError):
+        U.get_custom_chat_template({"name_or_path": "x"})
+    f = tmp_path / "my.jinja"
+    f.write_text("{{ messages }}")
+    assert U.get_custom_chat_template({"source": "file", "name_or_path": str(f)}) == "{{ messages }}"
+    bad = tmp_path / "secrets.env"
+    bad.write_text("x")
+    with pytest.raises(ValueError):
+        U.get_custom_chat_template({"source": "file", "name_or_path": str(bad)})
+    # the named template renders through jinja the way a tokenizer would use it
+    import jinja2
+
+    txt = jinja2.Template(t).render(messages=[{"role": "user", "content": "hi"}], add_generation_prompt=True)
+    assert txt == "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
