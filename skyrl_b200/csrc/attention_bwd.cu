@@ -124,7 +124,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv128, const __grid_constant__ CUtensorMap tm_qkv64,
                     const __grid_constant__ CUtensorMap tm_do, const float* __restrict__ lse,
                     const float* __restrict__ delta, __nv_bfloat16* __restrict__ dqkv, long long dqkv_stride,
-                    const int* __restrict__ cu_seqlens, int B, int T, int nq, int nkv, float scale, int* status) {
+                    const int* __restrict__ cu_seqlens, const int* __restrict__ q_begin, int B, int T, int nq, int nkv,
+                    float scale, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -179,7 +180,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qkv128, const __grid_
   const int kv_pos0 = jblk * 64;
   const int kv_valid = min(64, seq_len - kv_pos0);
   const int nqb = (seq_len + 127) / 128;
-  const int i0 = kv_pos0 / 128;
+  // query blocks that see this key/value block: from its own block on, and not before the sequence's first query row
+  const int i0 = max(kv_pos0 / 128, q_begin ? min(nqb, max(0, q_begin[seq]) / 128) : 0);
   const int per_head = nqb - i0;
   const int n_it = rep * per_head;
   const int col_k = (nq + g) * 128, col_v = (nq + nkv + g) * 128;
@@ -308,7 +310,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv128, const __grid_constant__ CUtensorMap tm_qkv64,
                    const __grid_constant__ CUtensorMap tm_do, const float* __restrict__ lse,
                    const float* __restrict__ delta, __nv_bfloat16* __restrict__ dqkv, long long dqkv_stride,
-                   const int* __restrict__ cu_seqlens, int B, int T, int nq, int nkv, float scale, int* status) {
+                   const int* __restrict__ cu_seqlens, const int* __restrict__ q_begin, int B, int T, int nq, int nkv,
+                   float scale, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -333,6 +336,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv128, const __grid_c
     s_seq = seq;
     s_blk = s_found ? (nblk - 1 - blk) : 0;  // heavy blocks first
     s_nblk = nblk;
+    // blocks before the sequence's first query row have no dQ to compute (the caller zero-fills dqkv)
+    if (s_found && q_begin != nullptr && s_blk < min(nblk, max(0, q_begin[seq]) / 128)) s_found = 0;
     mbar_init(qdo_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1);
@@ -481,10 +486,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv128, const __grid_c
 extern "C" {
 
 // dqkv (same layout and row stride as qkv) receives dQ | dK | dV.  `delta_ws` is an fp32 workspace of
-// nq * T elements (null -> error; the caller owns all memory).
+// nq * T elements (null -> error; the caller owns all memory).  q_begin: null, or [B] int32 on device as in the
+// forward pass; the dQ rows of the skipped query blocks are not written (pass a zero-filled dqkv).
 int sb_attn_bwd_varlen(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
-                       const int* cu_seqlens, float* delta_ws, int B, int T, int nq, int nkv, int head_dim,
-                       long long row_stride, float softmax_scale, void* stream) {
+                       const int* cu_seqlens, const int* q_begin, float* delta_ws, int B, int T, int nq, int nkv,
+                       int head_dim, long long row_stride, float softmax_scale, void* stream) {
   if (head_dim != 128 || nq % nkv != 0 || T <= 0 || B <= 0 || !delta_ws) return SB_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long W = static_cast<long long>(nq + 2 * nkv) * 128;
@@ -508,12 +514,12 @@ int sb_attn_bwd_varlen(const void* qkv, const void* out, const void* dout, const
       reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta_ws, T, nq);
   dim3 g_kv((T + 63) / 64 + B, nkv);
   sb::attn_bwd_dkv_kernel<<<g_kv, sb::kBwdThreads, sb::kDkvSmem, st>>>(
-      *tq128, *tq64, *tdo, lse, delta_ws, reinterpret_cast<__nv_bfloat16*>(dqkv), row_stride, cu_seqlens, B, T, nq, nkv,
-      softmax_scale, sb::device_status_ptr());
+      *tq128, *tq64, *tdo, lse, delta_ws, reinterpret_cast<__nv_bfloat16*>(dqkv), row_stride, cu_seqlens, q_begin, B, T, nq,
+      nkv, softmax_scale, sb::device_status_ptr());
   dim3 g_q((T + 127) / 128 + B, nq);
   sb::attn_bwd_dq_kernel<<<g_q, sb::kBwdThreads, sb::kDqSmem, st>>>(
-      *tq128, *tq64, *tdo, lse, delta_ws, reinterpret_cast<__nv_bfloat16*>(dqkv), row_stride, cu_seqlens, B, T, nq, nkv,
-      softmax_scale, sb::device_status_ptr());
+      *tq128, *tq64, *tdo, lse, delta_ws, reinterpret_cast<__nv_bfloat16*>(dqkv), row_stride, cu_seqlens, q_begin, B, T, nq,
+      nkv, softmax_scale, sb::device_status_ptr());
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }
 

@@ -29,25 +29,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Locate the (sequence, q-block) of a flat block index; heavy (late) blocks first.
-__device__ __forceinline__ bool find_block(const int* __restrict__ cu, int B, int flat, int& seq, int& qblk) {
+// Locate the (sequence, q-block) of a flat block index; heavy (late) blocks first.  `q_begin` (optional): first row of
+// each sequence that carries a query; the q-blocks before it are not computed (their rows are keys / values only: a
+// cached prefix, or the part of a sequence another context-parallel rank owns).
+__device__ __forceinline__ bool find_block(const int* __restrict__ cu, const int* __restrict__ q_begin, int B, int flat,
+                                           int& seq, int& qblk) {
   int acc = 0;
   for (int b = 0; b < B; ++b) {
     const int len = cu[b + 1] - cu[b];
     const int nb = (len + kAttnBQ - 1) / kAttnBQ;
-    if (flat < acc + nb) {
+    const int first = q_begin ? min(nb, max(0, q_begin[b]) / kAttnBQ) : 0;
+    const int live = nb - first;
+    if (flat < acc + live) {
       seq = b;
       qblk = nb - 1 - (flat - acc);
       return true;
     }
-    acc += nb;
+    acc += live;
   }
   return false;
 }
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
-                const int* __restrict__ cu_seqlens, int B, int T, int nq, int nkv, float scale_log2, int* status) {
+                const int* __restrict__ cu_seqlens, const int* __restrict__ q_begin, int B, int T, int nq, int nkv,
+                float scale_log2, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -75,7 +81,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, __nv_bfloat16* __res
 
   if (threadIdx.x == 0) {
     int seq = 0, qblk = 0;
-    s_found = find_block(cu_seqlens, B, blockIdx.x, seq, qblk) ? 1 : 0;
+    s_found = find_block(cu_seqlens, q_begin, B, blockIdx.x, seq, qblk) ? 1 : 0;
     s_seq = seq;
     s_qblk = qblk;
     mbar_init(q_full, 1);
@@ -359,8 +365,10 @@ extern "C" {
 
 // qkv: packed [T, (nq + 2 nkv) * 128] bf16 (RoPE already applied), row stride `row_stride` elements.
 // out: [T, nq * 128] bf16; lse: [nq, T] fp32 (natural log) or null; cu_seqlens: [B + 1] int32 on device.
-int sb_attn_fwd_varlen(const void* qkv, void* out, float* lse, const int* cu_seqlens, int B, int T, int nq, int nkv,
-                       int head_dim, long long row_stride, float softmax_scale, void* stream) {
+// q_begin: null, or [B] int32 on device: rows of sequence b before q_begin[b] (rounded down to a 128-row block) carry
+// no query; their rows of out / lse are left untouched.
+int sb_attn_fwd_varlen(const void* qkv, void* out, float* lse, const int* cu_seqlens, const int* q_begin, int B, int T,
+                       int nq, int nkv, int head_dim, long long row_stride, float softmax_scale, void* stream) {
   if (head_dim != sb::kAttnD || nq % nkv != 0 || T <= 0 || B <= 0) return SB_ERR_ARG;
   const long long W = static_cast<long long>(nq + 2 * nkv) * sb::kAttnD;
   const CUtensorMap* tm = sb::get_tmap_bf16_2d(qkv, T, W, row_stride, 128);
@@ -376,7 +384,7 @@ int sb_attn_fwd_varlen(const void* qkv, void* out, float* lse, const int* cu_seq
   }
   dim3 grid((T + sb::kAttnBQ - 1) / sb::kAttnBQ + B, nq);
   sb::attn_fwd_kernel<<<grid, sb::kAttnThreads, sb::kAttnSmem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      *tm, reinterpret_cast<__nv_bfloat16*>(out), lse, cu_seqlens, B, T, nq, nkv,
+      *tm, reinterpret_cast<__nv_bfloat16*>(out), lse, cu_seqlens, q_begin, B, T, nq, nkv,
       softmax_scale * 1.4426950408889634f, sb::device_status_ptr());
   return cudaGetLastError() == cudaSuccess ? SB_OK : SB_ERR_CUDA;
 }

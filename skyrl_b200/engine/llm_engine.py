@@ -530,6 +530,7 @@ class LLMEngine:
         ids, pos, slot_list, cu = [], [], [], [0]
         rows = []
         full_slots: List[int] = []  # cache slot of every token (cached prefix + new), per sequence, for the prefix path
+        q_first: List[int] = []     # number of cached tokens per sequence = first row that carries a query
         new_rows_in_full: List[int] = []
         cu_full = [0]
         any_cached = False
@@ -557,6 +558,7 @@ class LLMEngine:
             slot_list.extend(all_slots[c:])
             cu.append(cu[-1] + (L - c))
             new_rows_in_full.extend(range(cu_full[-1] + c, cu_full[-1] + L))
+            q_first.append(c)
             full_slots.extend(all_slots)
             cu_full.append(cu_full[-1] + L)
         t_ids = _lib.to_device(torch.tensor(ids, dtype=torch.int32), dev)
@@ -576,6 +578,8 @@ class LLMEngine:
             t_full_slots = _lib.to_device(torch.tensor(full_slots, dtype=torch.long), dev)
             t_new_rows = _lib.to_device(torch.tensor(new_rows_in_full, dtype=torch.long), dev)
             t_cu_full = _lib.to_device(torch.tensor(cu_full, dtype=torch.int32), dev)
+            # the cached rows carry no query: the attention kernel skips the query blocks that lie entirely inside them
+            t_q_first = _lib.to_device(torch.tensor(q_first, dtype=torch.int32), dev)
             qd, kvd = a.num_heads * a.head_dim, a.num_kv_heads * a.head_dim
             Tf = len(full_slots)
 
@@ -585,7 +589,7 @@ class LLMEngine:
                 full[:, qd + kvd :] = self.v_cache[layer].view(-1, kvd)[t_full_slots]
                 full[t_new_rows, :qd] = qkv[:, :qd]
                 att = attn_ops.attn_varlen(full, t_cu_full, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_len,
-                                           sinks=m._p.get(f"layers.{layer}.sinks"))
+                                           sinks=m._p.get(f"layers.{layer}.sinks"), q_begin=t_q_first)
                 return att[t_new_rows].contiguous()
 
             self.stats["prefix_cached_tokens"] = self.stats.get("prefix_cached_tokens", 0) + (Tf - len(ids))

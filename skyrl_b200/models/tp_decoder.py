@@ -403,9 +403,9 @@ class ContextParallelCausalLM(UlyssesCausalLM):
 
     The attention kernel takes one packed q|k|v tensor, so a rank builds the rows from the start of the first
     sequence that reaches into its slice up to the end of its slice: K and V come from the gathered tensor, Q is zero
-    for the rows it does not own, and only its own rows of the result are kept.  The kernel therefore also walks the
-    query blocks of the foreign rows (their results are dropped); a per-sequence first-query-block argument for the
-    kernels would remove that work and is not built.  The backward pass returns the K / V gradients to their owners
+    for the rows it does not own, and only its own rows of the result are kept; the kernels are told where the first
+    query row of each sequence is (``q_begin``) and skip the query blocks before it, forward and backward.  The
+    backward pass returns the K / V gradients to their owners
     through the reduce-scatter of the gather.  Reference: Megatron ``context_parallel_size``
     (skyrl/backends/skyrl_train/distributed/megatron/megatron_utils.py:421-425,510-530) with ring attention from
     TransformerEngine; selected here with ``trainer.sequence_parallel_backend=context`` (or the Megatron strategy's
@@ -423,7 +423,7 @@ class ContextParallelCausalLM(UlyssesCausalLM):
 
         a, cp = self.args, self.tp
         pre = f"layers.{i}."
-        row0, row1, first, cu_loc, max_loc = self._cp_plan
+        row0, row1, first, cu_loc, max_loc, q_begin = self._cp_plan
         x, h = ew.add_rmsnorm(x, delta, self.p(pre + "ln1"), a.rms_norm_eps)
         qkv = gemm.linear(h, self.p(pre + "wqkv"), self._p.get(pre + "bqkv"))
         if a.qk_norm:
@@ -435,7 +435,8 @@ class ContextParallelCausalLM(UlyssesCausalLM):
         if lead > 0:
             q_rows = torch.cat([q_rows.new_zeros((lead, a.q_dim)), q_rows], 0)
         full = torch.cat([q_rows, kv_all[first:row1]], 1)
-        att = attn_ops.attn_varlen(full, cu_loc, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_loc)
+        att = attn_ops.attn_varlen(full, cu_loc, a.num_heads, a.num_kv_heads, a.head_dim, max_seqlen=max_loc,
+                                   q_begin=q_begin)
         o = gemm.linear(att[lead:].contiguous(), self.p(pre + "wo"))
         x, h = ew.add_rmsnorm(x, o, self.p(pre + "ln2"), a.rms_norm_eps)
         d = gemm.linear(ew.swiglu(gemm.linear(h, self.p(pre + "wgu"))), self.p(pre + "wd"))
@@ -452,7 +453,12 @@ class ContextParallelCausalLM(UlyssesCausalLM):
         bounds = [first] + [c for c in cu if first < c < row1] + [row1]
         cu_loc = torch.tensor([b - first for b in bounds], dtype=cu_seqlens.dtype, device=cu_seqlens.device)
         max_loc = max(b - a_ for a_, b in zip(bounds[:-1], bounds[1:]))
-        self._cp_plan = (row0, row1, first, cu_loc, max_loc)
+        # only the first local sequence starts with foreign rows (keys / values of earlier ranks, no queries)
+        q_begin = None
+        if row0 > first:
+            q_begin = torch.zeros(len(bounds) - 1, dtype=torch.int32, device=cu_seqlens.device)
+            q_begin[0] = row0 - first
+        self._cp_plan = (row0, row1, first, cu_loc, max_loc, q_begin)
         x = _EmbeddingFn.apply(input_ids[row0:row1], self.p("embed"))
         delta = None
         for i in range(self.args.num_layers):

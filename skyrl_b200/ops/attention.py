@@ -25,8 +25,8 @@ def _k():
     lib = _lib.kernels()
     if not _cfg_done:
         vp, ci, cf, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
-        lib.sb_attn_fwd_varlen.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, cl, cf, vp]
-        lib.sb_attn_bwd_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cl, cf, vp]
+        lib.sb_attn_fwd_varlen.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cl, cf, vp]
+        lib.sb_attn_bwd_varlen.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cl, cf, vp]
         lib.sb_kv_cache_write.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, cl, ci, vp]
         lib.sb_attn_decode_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cl, cf, vp]
         lib.sb_attn_decode_paged_tc.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, ci, cl, cf, vp]
@@ -75,15 +75,17 @@ def attn_varlen_ref(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: i
 
 class _AttnVarlenFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, cu_seqlens, nq, nkv, D, scale, max_seqlen, sinks=None):
+    def forward(ctx, qkv, cu_seqlens, nq, nkv, D, scale, max_seqlen, sinks=None, q_begin=None):
         T = qkv.shape[0]
         B = cu_seqlens.numel() - 1
         if qkv.is_cuda:
             assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and cu_seqlens.dtype == torch.int32
-            out = torch.empty((T, nq * D), device=qkv.device, dtype=qkv.dtype)
-            lse = torch.empty((nq, T), device=qkv.device, dtype=torch.float32)
-            code = _k().sb_attn_fwd_varlen(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), cu_seqlens.data_ptr(), B, T,
-                                           nq, nkv, D, qkv.stride(0), scale, _lib.stream_ptr())
+            # with q_begin the kernel leaves the rows before each sequence's first query untouched: start from zeros
+            alloc = torch.zeros if q_begin is not None else torch.empty
+            out = alloc((T, nq * D), device=qkv.device, dtype=qkv.dtype)
+            lse = alloc((nq, T), device=qkv.device, dtype=torch.float32)
+            code = _k().sb_attn_fwd_varlen(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), cu_seqlens.data_ptr(),
+                                           _lib.ptr(q_begin), B, T, nq, nkv, D, qkv.stride(0), scale, _lib.stream_ptr())
             _lib.check(code, "sb_attn_fwd_varlen")
             if sinks is not None:
                 # A sink column only enlarges the denominator: with lse' = log(exp(lse) + exp(sink)) the output is the
@@ -95,14 +97,14 @@ class _AttnVarlenFn(torch.autograd.Function):
                 lse = lse_s
         else:
             out, lse = attn_varlen_ref(qkv, cu_seqlens, nq, nkv, D, scale, sinks)
-        ctx.save_for_backward(qkv, out, lse, cu_seqlens, sinks)
+        ctx.save_for_backward(qkv, out, lse, cu_seqlens, sinks, q_begin)
         ctx.meta = (nq, nkv, D, scale, max_seqlen)
         ctx.sink_main_grad = getattr(sinks, "main_grad", None) if sinks is not None else None
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, out, lse, cu, sinks = ctx.saved_tensors
+        qkv, out, lse, cu, sinks, q_begin = ctx.saved_tensors
         nq, nkv, D, scale, max_seqlen = ctx.meta
         T = qkv.shape[0]
         B = cu.numel() - 1
@@ -118,10 +120,10 @@ class _AttnVarlenFn(torch.autograd.Function):
 
         if qkv.is_cuda:
             dout = dout.contiguous()
-            dqkv = torch.empty_like(qkv)
+            dqkv = torch.zeros_like(qkv) if q_begin is not None else torch.empty_like(qkv)
             delta = torch.empty(nq * T, device=qkv.device, dtype=torch.float32)
             code = _k().sb_attn_bwd_varlen(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-                                           dqkv.data_ptr(), cu.data_ptr(), delta.data_ptr(), B, T, nq, nkv, D,
+                                           dqkv.data_ptr(), cu.data_ptr(), _lib.ptr(q_begin), delta.data_ptr(), B, T, nq, nkv, D,
                                            dqkv.stride(0),
                                            scale, _lib.stream_ptr())
             _lib.check(code, "sb_attn_bwd_varlen")
@@ -130,13 +132,13 @@ class _AttnVarlenFn(torch.autograd.Function):
                 # dS of the sink column = p_sink * (0 - delta), with delta = rowsum(dO * O) left in the workspace
                 p_sink = torch.exp(sinks.float().view(nq, 1) - lse)
                 ds = -(p_sink * delta.view(nq, T)).sum(1)
-            return dqkv, None, None, None, None, None, None, sink_grad(ds)
+            return dqkv, None, None, None, None, None, None, sink_grad(ds), None
         with torch.enable_grad():
             x = qkv.detach().float().requires_grad_()
             sk = sinks.detach().float().requires_grad_() if sinks is not None else None
             o, _ = attn_varlen_ref(x, cu, nq, nkv, D, scale, sk)
             gs = torch.autograd.grad(o, (x,) if sk is None else (x, sk), dout.float())
-        return g_cast(gs[0], qkv), None, None, None, None, None, None, sink_grad(gs[1] if sk is not None else None)
+        return g_cast(gs[0], qkv), None, None, None, None, None, None, sink_grad(gs[1] if sk is not None else None), None
 
 
 def g_cast(g: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
@@ -144,8 +146,14 @@ def g_cast(g: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
 
 
 def attn_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: int, head_dim: int,
-                scale: float | None = None, max_seqlen: int = 0, sinks: torch.Tensor | None = None) -> torch.Tensor:
+                scale: float | None = None, max_seqlen: int = 0, sinks: torch.Tensor | None = None,
+                q_begin: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention over packed sequences. ``qkv``: ``[T, (nq+2nkv)*D]`` -> ``[T, nq*D]``.
+
+    ``q_begin`` (``[B]`` int32): the rows of sequence ``b`` before ``q_begin[b]`` only serve as keys / values (a cached
+    prefix, tokens owned by another context-parallel rank).  The CUDA kernels skip the 128-row query blocks that lie
+    entirely before it, forward and backward; the output rows there are zero and must not be used.  The PyTorch
+    reference path computes every row (the rows that matter are identical).
 
     ``sinks`` (``[nq]`` learned logits, GPT-OSS style): an extra softmax column per head that carries no value.  The
     reference gets it from a flex-attention score/mask patch compiled by inductor
@@ -153,7 +161,7 @@ def attn_varlen(qkv: torch.Tensor, cu_seqlens: torch.Tensor, nq: int, nkv: int, 
     enters through the log-sum-exp (see ``_AttnVarlenFn``)."""
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
-    return _AttnVarlenFn.apply(qkv, cu_seqlens, nq, nkv, head_dim, scale, max_seqlen, sinks)
+    return _AttnVarlenFn.apply(qkv, cu_seqlens, nq, nkv, head_dim, scale, max_seqlen, sinks, q_begin)
 
 
 # ----------------------------------------------------------------------------- paged KV cache

@@ -121,6 +121,44 @@ def test_attn_fwd_bwd_with_drifting_row_maxima():
     assert rel(qkv.grad, x.grad) < 3e-2
 
 
+def test_attn_q_begin_skips_key_value_only_rows_forward_and_backward():
+    """Rows before ``q_begin`` of a sequence serve as keys / values only (a cached prefix, another rank's tokens).  With
+    their queries zeroed and their output gradients zero, the kernels that skip those query blocks must give the same
+    output rows, dK / dV (all rows) and dQ (query rows) as the run that computes everything."""
+    torch.manual_seed(5)
+    nq, nkv, D = 4, 2, 128
+    lens, begin = [700, 260, 130, 90], [384, 0, 129, 64]   # block-aligned, none, one past a block, inside the first block
+    T = sum(lens)
+    cu = torch.tensor([0, 700, 960, 1090, 1180], device="cuda", dtype=torch.int32)
+    qb = torch.tensor(begin, device="cuda", dtype=torch.int32)
+    base = torch.randn(T, (nq + 2 * nkv) * D, device="cuda") * 0.6
+    live = torch.ones(T, dtype=torch.bool, device="cuda")
+    s0 = 0
+    for n, b in zip(lens, begin):
+        live[s0: s0 + b] = False
+        s0 += n
+    base[~live, : nq * D] = 0.0
+    g = torch.randn(T, nq * D, device="cuda").to(torch.bfloat16)
+    g[~live] = 0
+    res = []
+    for use in (False, True):
+        qkv = base.to(torch.bfloat16).requires_grad_()
+        out = attention.attn_varlen(qkv, cu, nq, nkv, D, q_begin=qb if use else None)
+        out.backward(g)
+        torch.cuda.synchronize()
+        assert _lib.status_read_clear() == 0
+        res.append((out.detach().float(), qkv.grad.float()))
+    (o0, g0), (o1, g1) = res
+    assert rel(o1[live], o0[live]) < 1e-3
+    assert rel(g1[:, nq * D:], g0[:, nq * D:]) < 5e-3                 # dK, dV of every row
+    assert rel(g1[live][:, : nq * D], g0[live][:, : nq * D]) < 5e-3   # dQ of the query rows
+    # whole skipped blocks stay zero (the first 384 rows of sequence 0 are three such blocks)
+    assert float(o1[:384].abs().max()) == 0.0 and float(g1[:384, : nq * D].abs().max()) == 0.0
+    x = base.float().requires_grad_()
+    ref, _ = attention.attn_varlen_ref(x, cu, nq, nkv, D, 1 / math.sqrt(D))
+    assert rel(o1[live], ref[live]) < 1e-2
+
+
 @pytest.mark.parametrize("nq,nkv,bs", [(12, 2, 16), (28, 4, 32), (4, 4, 16)])
 def test_decode_paged(nq, nkv, bs):
     torch.manual_seed(0)
