@@ -50,11 +50,45 @@ CONFIGS = {
 }
 
 
+def _phase_anchor(argv, timeout_s: int):
+    """Runs one kernel micro-benchmark of this repo in a child process and returns its JSON line (or the failure)."""
+    try:
+        p = subprocess.run([sys.executable, "-m", "skyrl_b200.benchmarks.bench_kernels", *argv], capture_output=True,
+                           text=True, timeout=timeout_s, cwd=os.path.dirname(os.path.abspath(__file__)))
+        for line in reversed(p.stdout.strip().splitlines()):
+            if line.startswith("{"):
+                return json.loads(line)
+        return {"error": (p.stderr or p.stdout)[-300:]}
+    except Exception as e:  # noqa: BLE001 - the reference line must be printed whatever happens here
+        return {"error": f"{type(e).__name__}: {e}"[:300]}
+
+
 def reference_arm() -> None:
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "reference installs with --no-deps into baseline/_ref but its public API cannot import here: "
-                      "ray, omegaconf, cloudpathlib, megatron-core and the pinned vllm 0.26 weight-transfer API are not "
-                      "installed and there is no network"}))
+    """No complete RL step can run through the reference here, so the arm reports ``unavailable``.  What of the
+    reference does run on this machine is timed as *phase anchors* on the same tensors as this repo's kernels and
+    attached under ``phase_anchors``: its own Triton fused LM-head kernel (and its materialised-logits path), loaded
+    unmodified from ``baseline/_ref``, and flash-attn, the library behind its training attention.  These are not a
+    reference value for the metric."""
+    out = {"impl": "reference", "unavailable":
+           "reference installs with --no-deps into baseline/_ref but its public API cannot import here: "
+           "ray, omegaconf, cloudpathlib, megatron-core and the pinned vllm 0.26 weight-transfer API are not "
+           "installed and there is no network"}
+    if int(os.environ.get("RANK", "0")) != 0:
+        return  # one line per job
+    try:
+        import torch
+
+        if torch.cuda.is_available() and os.environ.get("SKYRL_B200_REFERENCE_ANCHORS", "1") == "1":
+            out["phase_anchors"] = {
+                "note": "same tensors, CUDA events, L2 flushed between iterations; not the reference arm",
+                "fused_lm_head_logprob_T8192_V151936_H1536": _phase_anchor(
+                    ["--which", "lmhead", "--impl", "both", "--tokens", "8192", "--iters", "3"], 240),
+                "training_attention_16x8192_tokens": _phase_anchor(
+                    ["--which", "attn", "--impl", "both", "--seqs", "16", "--seqlen", "8192", "--iters", "3"], 120),
+            }
+    except Exception as e:  # noqa: BLE001
+        out["phase_anchors"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    print(json.dumps(out))
 
 
 class ClockSampler:

@@ -59,6 +59,8 @@ _VARS: List[EnvVar] = [
     EnvVar("SB_FUSED_MLP", "1", _flag, "SwiGLU inside the gate/up and down-gradient GEMM epilogues (training)"),
     EnvVar("SB_DECODE_FUSED_MLP", "1", _flag, "SwiGLU inside the gate/up GEMM epilogue (decode)"),
     EnvVar("SKYRL_B200_JUDGE_URL", "http://127.0.0.1:8000", str, "llm_judge environment: default base URL of the judge endpoint"),
+    EnvVar("SKYRL_B200_REFERENCE_ANCHORS", "1", _flag,
+           "bench.py --impl reference: time the reference's own LM-head kernel and flash-attn as phase anchors"),
     EnvVar("SKYRL_B200_DEBUG_BOUNDS", "0", _flag,
            "debug mode: check every index tensor (token ids, cache slots, block tables, targets) before the kernel launch"),
     EnvVar("SB_DECODE_MLP_BLOCK", "0", _flag,
