@@ -70,3 +70,36 @@ class DraftHead(torch.nn.Module):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         x = h.to(self.up.weight.dtype)
         return x + self.down(torch.nn.functional.silu(self.up(self.norm(x))))
+
+
+def mtp_draft_backward(draft_head, trunk_hidden: torch.Tensor, lm_head_weight: torch.Tensor, cu_seqlens: torch.Tensor,
+                       token_mask: Optional[torch.Tensor] = None, temperature: float = 1.0, scale: float = 1.0,
+                       chunk: int = 1024) -> torch.Tensor:
+    """Same loss as ``mtp_draft_loss`` (mean over the unmasked positions), evaluated and back-propagated in row chunks
+    so that only ``chunk x V`` logits of the student and of the teacher exist at a time.  Gradients (times ``scale``)
+    are accumulated into the draft head's parameters; returns the detached loss value.
+
+    ``token_mask[t]`` (optional, ``[T]``): whether position ``t`` is a trained position; the pair (student at ``t``,
+    teacher at ``t + 1``) counts when ``t + 1`` is trained and belongs to the same packed sequence."""
+    h = trunk_hidden.detach()
+    T = h.shape[0]
+    W = lm_head_weight.detach().float()
+    valid = torch.ones(T, dtype=torch.bool, device=h.device)
+    valid[(cu_seqlens[1:] - 1).long()] = False
+    m = valid[:-1]
+    if token_mask is not None:
+        m = m & token_mask[1:].bool()
+    denom = m.float().sum().clamp_min(1.0)
+    total = torch.zeros((), device=h.device, dtype=torch.float32)
+    for s in range(0, T - 1, chunk):
+        e = min(T - 1, s + chunk)
+        mk = m[s:e]
+        if not bool(mk.any()):
+            continue
+        with torch.no_grad():
+            teacher = torch.softmax((h[s + 1 : e + 1].float() @ W.t()) / temperature, -1)
+        student = torch.log_softmax((draft_head(h[s:e]).float() @ W.t()) / temperature, -1)
+        part = (-(teacher * student).sum(-1) * mk.float()).sum() / denom
+        (part * scale).backward()
+        total = total + part.detach()
+    return total

@@ -809,6 +809,76 @@ class PolicyWorker(ModelWorker):
 
     def __init__(self, cfg, **kw):
         super().__init__(cfg, trainable=True, optimizer_cfg=cfg.policy.optimizer_config, **kw)
+        self.mtp_head = self.mtp_optimizer = None
+        mcfg = getattr(cfg, "mtp", None)
+        if mcfg is not None and mcfg.enabled:
+            # Draft head for speculative decoding, trained beside the policy on detached trunk states with its own
+            # optimizer and its own gradient clipping (reference: skyrl/backends/skyrl_train/mtp/*, trainer.mtp).
+            if self.mesh is not None:
+                raise NotImplementedError("trainer.mtp.enabled is supported with the data-parallel strategy only")
+            from ..algorithms.mtp import DraftHead
+
+            torch.manual_seed(int(getattr(cfg, "seed", 0)) + 7919)  # identical initial head on every rank
+            self.mtp_head = DraftHead(self.model.args.hidden_size, dtype=torch.float32, device=self.env.device)
+            ocfg = cfg.policy.optimizer_config
+            self.mtp_optimizer = torch.optim.AdamW(self.mtp_head.parameters(), lr=ocfg.lr, betas=tuple(ocfg.adam_betas),
+                                                   weight_decay=ocfg.weight_decay)
+            self._mtp_loss_sum, self._mtp_loss_n = 0.0, 0
+
+    def _hidden(self, pv):
+        h = super()._hidden(pv)
+        if self.mtp_head is not None and torch.is_grad_enabled():
+            self._mtp_hidden = h.detach()
+        return h
+
+    def _mtp_accumulate(self, pv, mask_pred: torch.Tensor, n_mb: int) -> None:
+        """Draft-head loss of one micro-batch on the trunk states its policy forward just produced."""
+        from ..algorithms.mtp import mtp_draft_backward
+
+        h = getattr(self, "_mtp_hidden", None)
+        if h is None:
+            return
+        tok_mask = torch.zeros(h.shape[0], dtype=torch.bool, device=h.device)
+        tok_mask[pv.pred_index] = mask_pred > 0
+        loss = mtp_draft_backward(self.mtp_head, h, self.model.lm_head_weight(), pv.cu_seqlens, tok_mask,
+                                  float(self.cfg.algorithm.temperature or 1.0),
+                                  scale=float(self.cfg.mtp.loss_weight) / max(1, n_mb))
+        self._mtp_loss_sum += float(loss)
+        self._mtp_loss_n += 1
+        self._mtp_hidden = None
+
+    def optim_step(self):
+        norm = super().optim_step()
+        if self.mtp_head is not None:
+            from ..algorithms.mtp import clip_grad_norm_separately
+
+            params = [p for p in self.mtp_head.parameters() if p.grad is not None]
+            W = self.env.world_size
+            if W > 1 and dist.is_initialized():
+                for p in params:
+                    dist.all_reduce(p.grad)
+                    p.grad.div_(W)
+            gn, _ = clip_grad_norm_separately(params, float(self.cfg.policy.optimizer_config.max_grad_norm or 1.0))
+            self.mtp_optimizer.step()
+            self.mtp_optimizer.zero_grad(set_to_none=True)
+            self.last_mtp = {"mtp_loss": self._mtp_loss_sum / max(1, self._mtp_loss_n), "mtp_grad_norm": gn}
+            self._mtp_loss_sum, self._mtp_loss_n = 0.0, 0
+        return norm
+
+    def save_checkpoint(self, ckpt_dir: str, tag: Optional[str] = None, client_state: Optional[dict] = None) -> None:
+        super().save_checkpoint(ckpt_dir, tag, client_state)
+        if self.mtp_head is not None and self.env.is_main:  # the head is replicated: one copy is enough
+            torch.save({"head": self.mtp_head.state_dict(), "optim": self.mtp_optimizer.state_dict()},
+                       os.path.join(ckpt_dir, "mtp_head.pt"))
+
+    def load_checkpoint(self, ckpt_dir: str, *a, **kw):
+        out = super().load_checkpoint(ckpt_dir, *a, **kw)
+        path = os.path.join(ckpt_dir, "mtp_head.pt")
+        if self.mtp_head is not None and os.path.exists(path):
+            st = torch.load(path, map_location=self.env.device, weights_only=False)
+            self.mtp_head.load_state_dict(st["head"])
+            self.mtp_optimizer.load_state_dict(st["optim"])
+        return out
 
     def _layer_buckets(self) -> List[Tuple[int, int]]:
         """Flat gradient range of every decoder layer; the last layer's range also covers the final norm and head."""
@@ -921,6 +991,8 @@ class PolicyWorker(ModelWorker):
                 loss = loss * 0.0
             loss.backward()
             self.model.layer_grads_ready = None
+            if real and self.mtp_head is not None:
+                self._mtp_accumulate(pv, pv.gather_from_grid(mask_g), n_mb)
             if real:
                 m["final_loss"] = loss.detach()
                 if roll_g is not None:
@@ -932,6 +1004,8 @@ class PolicyWorker(ModelWorker):
         status = all_reduce_metrics(status, self.env)
         status["policy_lr"] = self.optimizer.lr
         status["response_length"] = R
+        if self.mtp_head is not None and self._mtp_loss_n:
+            status["mtp_loss"] = self._mtp_loss_sum / self._mtp_loss_n
         if per_row_logprobs is not None:
             rm = batch["response_mask"]
             lm_ = batch.get("loss_mask")

@@ -174,3 +174,75 @@ def test_debug_bounds_mode_rejects_bad_indices_before_the_kernel(monkeypatch):
         attention.attn_decode_paged(qkv[:2], kc, vc, bt, torch.tensor([2, 4], dtype=torch.int32), 1, 1, 8)
     # the bad entry is beyond what the second sequence's context reaches: not read, not an error
     attention.attn_decode_paged(qkv[:2], kc, vc, bt, torch.tensor([2, 2], dtype=torch.int32), 1, 1, 8)
+
+
+def test_mtp_draft_head_trains_beside_the_policy_without_touching_it(tmp_path):
+    """trainer.mtp.enabled: a draft head learns the trunk's next-next-token distribution on detached trunk states with
+    its own optimizer; the policy update is bit-identical to a run without it."""
+    import torch
+
+    from skyrl_b200.algorithms.mtp import DraftHead, mtp_draft_backward, mtp_draft_loss
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.parallel import dist as pdist
+    from skyrl_b200.train.batch import TrainingInputBatch
+    from skyrl_b200.workers.worker import PolicyWorker
+
+    # the chunked backward computes the same loss and gradients as the one-shot loss
+    torch.manual_seed(0)
+    head = DraftHead(16)
+    with torch.no_grad():
+        head.down.weight.normal_(0, 0.1)
+    h, W = torch.randn(23, 16), torch.randn(50, 16)
+    cu = torch.tensor([0, 9, 23])
+    mask = torch.rand(23) > 0.3
+    ref = mtp_draft_loss(head, h, W, cu, mask)
+    ref.backward()
+    g_ref = [p.grad.clone() for p in head.parameters()]
+    head.zero_grad()
+    got = mtp_draft_backward(head, h, W, cu, mask, chunk=5)
+    assert abs(float(got) - float(ref)) < 1e-5
+    for a, b in zip(g_ref, [p.grad for p in head.parameters()]):
+        assert torch.allclose(a, b, atol=1e-5)
+
+    def cfg(mtp):
+        return SkyRLTrainConfig.from_cli_overrides([
+            "trainer.policy.model.path=tiny-llama", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4",
+            "trainer.micro_train_batch_size_per_gpu=2", "generator.n_samples_per_prompt=2", "trainer.bf16=false",
+            "trainer.algorithm.use_kl_loss=false", "trainer.policy.optimizer_config.lr=1e-3",
+            "trainer.gradient_checkpointing=false", "trainer.max_tokens_per_microbatch=0", "trainer.resume_mode=none",
+            f"trainer.mtp.enabled={'true' if mtp else 'false'}", "trainer.mtp.loss_weight=1.0"])
+
+    def batch():
+        g = torch.Generator().manual_seed(5)
+        B, P, R = 4, 8, 12
+        rm = torch.ones(B, R)
+        rm[1, -3:] = 0
+        att = torch.ones(B, P + R, dtype=torch.long)
+        att[1, -3:] = 0
+        return TrainingInputBatch({"sequences": torch.randint(4, 1024, (B, P + R), generator=g), "attention_mask": att,
+                                   "response_mask": rm, "loss_mask": rm.clone(), "advantages": torch.randn(B, R, generator=g) * rm / rm.sum(),
+                                   "action_log_probs": -torch.rand(B, R, generator=g), "rollout_logprobs": None,
+                                   "base_action_log_probs": None})
+
+    pdist.reset_env_for_tests()
+    plain = PolicyWorker(cfg(False).trainer, model_path="tiny-llama", seed=0)
+    plain.forward_backward(batch())
+    plain.optim_step()
+    pdist.reset_env_for_tests()
+    w = PolicyWorker(cfg(True).trainer, model_path="tiny-llama", seed=0)
+    before = [p.detach().clone() for p in w.mtp_head.parameters()]
+    losses = []
+    for _ in range(3):
+        st = w.forward_backward(batch())
+        w.optim_step()
+        losses.append(st["mtp_loss"])
+        if len(losses) == 1:
+            assert torch.equal(w.model.flat_params, plain.model.flat_params)  # the draft loss never reaches the policy
+    assert any(not torch.equal(a, b) for a, b in zip(before, w.mtp_head.parameters()))
+    assert w.last_mtp["mtp_grad_norm"] > 0 and all(l == l and l > 0 for l in losses)
+    w.save_checkpoint(str(tmp_path / "ck"))
+    pdist.reset_env_for_tests()
+    w2 = PolicyWorker(cfg(True).trainer, model_path="tiny-llama", seed=0)
+    w2.load_checkpoint(str(tmp_path / "ck"))
+    for a, b in zip(w.mtp_head.parameters(), w2.mtp_head.parameters()):
+        assert torch.equal(a, b)
