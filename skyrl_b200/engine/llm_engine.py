@@ -80,6 +80,9 @@ class RequestOutput:
     prompt_logprobs: Optional[List[float]] = None
     num_cached_tokens: int = 0
     weight_version: int = 0
+    # mixture-of-experts models with ``EngineConfig.return_routed_experts``: expert ids chosen for every token that went
+    # through the model, ``[prompt + generated - 1, layers, top_k]`` int16 (the last generated token is never fed back)
+    routed_experts: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -96,6 +99,8 @@ class _Request:
     # tokens generated before a pause(abort)/preemption; the request is re-admitted with prompt+partial
     partial_tokens: List[int] = field(default_factory=list)
     partial_logprobs: List[float] = field(default_factory=list)
+    # routing recorded by the last prefill of this request: [prompt + partial tokens, layers, top_k] on the host
+    prefill_experts: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -113,6 +118,9 @@ class EngineConfig:
     graph_batch_sizes: Sequence[int] = (8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024)
     reserve_full_length: bool = True
     fused_decode: bool = True  # split-K projections with fused partial-sum consumers on the decode path
+    # mixture-of-experts models: return, with every output, the experts each token was routed to (router replay in the
+    # trainer).  Decode then runs without CUDA graphs and the prefix cache is bypassed (cached tokens are not routed).
+    return_routed_experts: bool = False
     # KV cache in a fixed-address arena (driver virtual-memory management): sleep() frees the memory, the addresses and
     # the CUDA graphs captured against them stay valid
     kv_fixed_address: bool = True
@@ -193,6 +201,11 @@ class LLMEngine:
         self.min_new = torch.ones(S, **i32)
         self.out_tokens = torch.zeros((S, self.out_stride), **i32)
         self.out_logprobs = torch.zeros((S, self.out_stride), device=dev, dtype=torch.float32)
+        # routing capture (mixture-of-experts only): experts of generated token j of a slot, written by the decode step
+        # that feeds it back, at [slot, j, layer * top_k + i]
+        self._record = bool(c.return_routed_experts and a.num_experts)
+        self.out_experts = (torch.zeros((S, self.out_stride, a.num_layers * a.num_experts_per_tok), device=dev,
+                                        dtype=torch.int16) if self._record else None)
         self.eos_dev = torch.tensor(self.eos_token_ids or [-1], **i32)
         self.step_counter = torch.zeros(1, device=dev, dtype=torch.int64)
         self.temperature = torch.ones(S, device=dev, dtype=torch.float32)
@@ -543,8 +556,8 @@ class LLMEngine:
             req.cached = self.rt.sbrt_sched_seq_cached(self.sched, req.sid)
             # tokens whose key/value blocks are already in the cache are not recomputed (at least one token is)
             c = min(int(req.cached), L - 1) if self.cfg.enable_prefix_caching else 0
-            if req.params.prompt_logprobs:
-                c = 0  # prompt log-probs need every position's hidden state
+            if req.params.prompt_logprobs or self._record:
+                c = 0  # prompt log-probs need every position's hidden state; routing capture every position's router
             c = (c // bs) * bs
             any_cached = any_cached or c > 0
             slot = self._free_slots.pop()
@@ -593,7 +606,16 @@ class LLMEngine:
                 return att[t_new_rows].contiguous()
 
             self.stats["prefix_cached_tokens"] = self.stats.get("prefix_cached_tokens", 0) + (Tf - len(ids))
-        h = m(t_ids, t_pos, t_cu, max_len, kv_sink=sink, attn_fn=attn_fn)
+        if self._record:
+            from ..models import router_replay
+
+            with router_replay.record_routing() as store:
+                h = m(t_ids, t_pos, t_cu, max_len, kv_sink=sink, attn_fn=attn_fn)
+            table = router_replay.stack_recorded(store).to(torch.int16).cpu()  # [tokens, layers, top_k]
+            for k, r in enumerate(reqs):
+                r.prefill_experts = table[cu[k] : cu[k + 1]].clone()
+        else:
+            h = m(t_ids, t_pos, t_cu, max_len, kv_sink=sink, attn_fn=attn_fn)
         last = h[(t_cu[1:] - 1).long()]
         if any(r.params.prompt_logprobs for r in reqs):
             tgt = torch.roll(t_ids, -1)
@@ -652,7 +674,8 @@ class LLMEngine:
         # like dense layers -- except while the routing is being recorded or replayed (those tensors live on the host side)
         from ..models import router_replay
 
-        use_graph = self.is_cuda and not self.cfg.enforce_eager and not masked and router_replay._get().mode is None
+        use_graph = (self.is_cuda and not self.cfg.enforce_eager and not masked and router_replay._get().mode is None
+                     and not self._record)
         if use_graph:
             g = self._graphs.get(n)
             if g is None:
@@ -661,6 +684,16 @@ class LLMEngine:
                 g.replay()
             _lib.LAUNCH_COUNT += steps * self._graph_launches.get(n, 0)
             self.stats["graph_replays"] += steps
+        elif self._record:
+            rows = torch.arange(n, device=self.device)
+            for _ in range(steps):
+                # the token fed by this step is generated token ``gen_count - 1`` of its slot
+                at = (self.gen_count[:n].long() - 1).clamp_(0, self.out_stride - 1)
+                live = self.active[:n].bool()
+                with router_replay.record_routing() as store:
+                    self._decode_once(n, masked)
+                tab = router_replay.stack_recorded(store).reshape(n, -1).to(torch.int16)
+                self.out_experts[rows, at] = torch.where(live[:, None], tab, self.out_experts[rows, at])
         else:
             for _ in range(steps):
                 self._decode_once(n, masked)
@@ -769,7 +802,7 @@ class LLMEngine:
 
     _SLOT_STATE = ("cur_tokens", "positions", "slots", "ctx_lens", "block_tables", "active", "finish_reason", "gen_count",
                    "max_new", "min_new", "out_tokens", "out_logprobs", "temperature", "top_k", "top_p", "min_p", "sampled",
-                   "sampled_lp")
+                   "sampled_lp", "out_experts")
 
     def _compact_slots(self) -> None:
         """Move running sequences from high slots into free low slots when that lets the decode batch drop to a
@@ -787,7 +820,8 @@ class LLMEngine:
         dst = torch.tensor(holes[: len(movers)], device=self.device, dtype=torch.long)
         for name in self._SLOT_STATE:
             t = getattr(self, name)
-            t[dst] = t[src]
+            if t is not None:
+                t[dst] = t[src]
         self.active[src] = 0
         self.finish_reason[src] = 0
         self.slots[src] = -1
@@ -802,6 +836,16 @@ class LLMEngine:
 
     def _retire(self, req: _Request, reason: str, toks: Optional[List[int]] = None,
                 lps: Optional[List[float]] = None) -> None:
+        routed = None
+        if self._record and req.prefill_experts is not None:
+            # prefill covered the prompt and the tokens generated before it; each later token but the last was fed by a
+            # decode step of this slot
+            a = self.model.args
+            fed = max(0, len(toks or []) - 1)
+            routed = req.prefill_experts
+            if fed and req.slot >= 0:
+                dec = self.out_experts[req.slot, :fed].cpu().view(fed, a.num_layers, a.num_experts_per_tok)
+                routed = torch.cat([routed, dec], 0)
         toks = req.partial_tokens + (toks or [])
         lps = req.partial_logprobs + (lps or [])
         if req.slot >= 0:
@@ -823,7 +867,7 @@ class LLMEngine:
         self._reqs.pop(req.sid, None)
         self.stats["decode_tokens"] += len(toks)
         self._finished.append(RequestOutput(req.rid, req.prompt, toks, lps, reason, req.prompt_logprobs, req.cached,
-                                            self.weight_version))
+                                            self.weight_version, routed))
 
     def step(self) -> List[RequestOutput]:
         """One scheduling round: admit + prefill what fits, then ``sync_interval`` decode steps, then harvest."""
@@ -940,6 +984,10 @@ class LLMEngine:
             if req is None:
                 continue
             n = int(gc[s])
+            if self._record and req.prefill_experts is not None and n > 1:
+                a = self.model.args
+                dec = self.out_experts[s, : n - 1].cpu().view(n - 1, a.num_layers, a.num_experts_per_tok)
+                req.prefill_experts = torch.cat([req.prefill_experts, dec], 0)
             req.partial_tokens = req.partial_tokens + self.out_tokens[s, :n].cpu().tolist()
             req.partial_logprobs = req.partial_logprobs + self.out_logprobs[s, :n].cpu().tolist()
             self.active[s] = 0

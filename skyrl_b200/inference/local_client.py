@@ -141,7 +141,9 @@ class LocalInferenceClient(InferenceEngineInterface):
             responses=[self._decode(o.token_ids) for o in outs], response_ids=[o.token_ids for o in outs],
             stop_reasons=[o.finish_reason for o in outs], response_logprobs=[o.logprobs for o in outs],
             prompt_logprobs=[o.prompt_logprobs for o in outs] if any(o.prompt_logprobs for o in outs) else None,
-            rollout_expert_indices=None, weight_versions=[o.weight_version for o in outs])
+            rollout_expert_indices=([o.routed_experts.numpy() if o.routed_experts is not None else None for o in outs]
+                                    if any(o.routed_experts is not None for o in outs) else None),
+            weight_versions=[o.weight_version for o in outs])
 
     # ------------------------------------------------------------------ control plane
     async def pause(self, mode: str = "keep", clear_cache: bool = False) -> None:

@@ -16,6 +16,7 @@ from typing import Any, Dict, List, Optional
 import aiohttp
 
 from ..env_vars import SKYRL_GENERATE_CONCURRENCY_PER_ENGINE
+from . import wire
 from .base import InferenceEngineInput, InferenceEngineInterface, InferenceEngineOutput
 
 _DATA_PLANE_RETRIES = 30
@@ -98,11 +99,13 @@ class RemoteInferenceClient(InferenceEngineInterface):
                 acc_ids += list(c["token_ids"])
                 lp = c.get("logprobs")
                 acc_lps += [x["logprob"] for x in lp["content"]] if lp else []
+                # a continuation re-submits everything generated so far, so the newest table covers the whole sequence
+                routes = wire.decode_packed_routed_experts(c["routed_experts"]) if c.get("routed_experts") else None
                 self.weight_version = max(self.weight_version, int(r.get("weight_version", 0)))
                 if c["finish_reason"] != "abort":
-                    return acc_ids, acc_lps, c["finish_reason"]
+                    return acc_ids, acc_lps, c["finish_reason"], routes
                 if budget is not None and len(acc_ids) >= budget:
-                    return acc_ids, acc_lps, "length"
+                    return acc_ids, acc_lps, "length", routes
                 await asyncio.sleep(self.backoff_s)  # server was paused with mode=abort: continue from what we have
 
     async def generate(self, input_batch: InferenceEngineInput) -> InferenceEngineOutput:
@@ -118,7 +121,8 @@ class RemoteInferenceClient(InferenceEngineInterface):
         texts = [self.tokenizer.decode(r[0], skip_special_tokens=True) if self.tokenizer is not None else "" for r in res]
         return InferenceEngineOutput(responses=texts, response_ids=[r[0] for r in res], stop_reasons=[r[2] for r in res],
                                      response_logprobs=[r[1] for r in res] if all(len(r[1]) == len(r[0]) for r in res) else None,
-                                     prompt_logprobs=None, rollout_expert_indices=None)
+                                     prompt_logprobs=None,
+                                     rollout_expert_indices=[r[3] for r in res] if any(r[3] is not None for r in res) else None)
 
     async def chat_completion(self, request_payload: Dict[str, Any]) -> Dict[str, Any]:
         return await self._post(self._target(request_payload.get("session_id")) + "/v1/chat/completions",

@@ -21,6 +21,7 @@ import threading
 import time
 from typing import Any, Dict, List, Optional
 
+from . import wire
 from .local_client import LocalInferenceClient
 
 MISSING_LOGPROB = -9999.0
@@ -74,6 +75,9 @@ def build_app(client: LocalInferenceClient, model_name: str = "policy", weight_l
             choices.append({"index": i, "token_ids": out["response_ids"][i], "finish_reason": out["stop_reasons"][i],
                             "text": out["responses"][i],
                             "logprobs": {"content": [{"logprob": lp} for lp in lps]} if lps else None})
+            routes = (out.get("rollout_expert_indices") or [None] * len(ids))[i]
+            if routes is not None:  # mixture-of-experts engine started with return_routed_experts
+                choices[-1]["routed_experts"] = wire.pack_routed_experts(routes)
         return {"id": f"gen-{int(time.time() * 1e6)}", "model": body.get("model", model_name), "choices": choices,
                 "weight_version": client.weight_version}
 

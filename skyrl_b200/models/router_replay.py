@@ -48,6 +48,43 @@ def replay_routing(indices: torch.Tensor):
         s.mode, s.replay = prev
 
 
+def set_replay(indices: Optional[torch.Tensor]) -> None:
+    """Replay ``indices`` (``[T, layers, k]``) in every forward from now until ``set_replay(None)``.  Unlike the
+    ``replay_routing`` block this also covers the layer recomputation that gradient checkpointing runs during the
+    backward pass, long after the forward call returned."""
+    s = _get()
+    s.mode, s.replay = ("replay", indices) if indices is not None else (None, None)
+
+
+PAD = -1  # rows of a replay table without recorded routing: the layer keeps its own choice there
+
+
+def pad_routes(per_sample: List[Optional[torch.Tensor]], seq_lens: List[int], width: int) -> torch.Tensor:
+    """Left-padded ``[B, width, layers, k]`` int16 batch tensor: sample ``i``'s rows sit where its ``seq_lens[i]``
+    tokens sit in the left-padded ``sequences`` tensor; tokens that were never routed at rollout time (the final
+    sampled token, text appended by the environment after the last model turn) and the padding hold ``PAD``."""
+    def as_tensor(t):
+        if t is None or isinstance(t, torch.Tensor):
+            return t
+        import numpy as np
+
+        return torch.from_numpy(np.asarray(t).astype(np.int32))  # wire tables arrive as read-only unsigned arrays
+
+    per_sample = [as_tensor(t) for t in per_sample]
+    shape = next((tuple(t.shape[1:]) for t in per_sample if t is not None and t.dim() == 3), None)
+    if shape is None:
+        raise ValueError("no sample carries routed experts")
+    out = torch.full((len(per_sample), width, *shape), PAD, dtype=torch.int16)
+    for i, (t, n) in enumerate(zip(per_sample, seq_lens)):
+        if t is None:
+            continue
+        if tuple(t.shape[1:]) != shape:
+            raise ValueError(f"sample {i}: routed experts have shape {tuple(t.shape)}, expected [*, {shape[0]}, {shape[1]}]")
+        m = min(int(n), t.shape[0])
+        out[i, width - int(n) : width - int(n) + m] = t[:m].to(torch.int16)
+    return out
+
+
 def on_route(layer: int, idx: torch.Tensor) -> Optional[torch.Tensor]:
     """Called by the MoE layer with its own top-k choice; returns the indices to use instead (replay) or ``None``."""
     s = _get()
@@ -58,7 +95,8 @@ def on_route(layer: int, idx: torch.Tensor) -> Optional[torch.Tensor]:
         r = s.replay[:, layer]
         if r.shape != idx.shape:
             raise ValueError(f"replayed routing for layer {layer} has shape {tuple(r.shape)}, expected {tuple(idx.shape)}")
-        return r.to(idx.device)
+        r = r.to(idx.device).to(idx.dtype)
+        return torch.where(r >= 0, r, idx)
     return None
 
 

@@ -57,6 +57,10 @@ def _pad_to(batch: TrainingInputBatch, keys, S: int, R: int, P_new: int, R_new: 
             out[k] = v
         elif v.shape[1] == S and k in ("sequences", "attention_mask", "position_ids"):
             out[k] = torch.nn.functional.pad(v, (P_new - (S - R), R_new - R))
+        elif k == "rollout_expert_indices":  # [B, S, layers, k]: new columns carry no recorded routing
+            out[k] = torch.nn.functional.pad(v, (0, 0, 0, 0, P_new - (S - R), R_new - R), value=-1)
+        elif k == "router_padding_mask":
+            out[k] = torch.nn.functional.pad(v, (P_new - (S - R), R_new - R), value=True)
         elif v.shape[1] == R:
             out[k] = torch.nn.functional.pad(v, (0, R_new - R))
         else:

@@ -42,6 +42,9 @@ class TrajectoryOutput:
     e2e_time: float = 0.0
     time_splits: Dict[str, float] = field(default_factory=dict)
     is_last_step: bool = True
+    # experts chosen at rollout time for the tokens of prompt + response, ``[rows <= len, layers, top_k]`` (MoE policies
+    # with ``inference_engine.enable_return_routed_experts``); rows past the recorded ones were never routed
+    rollout_expert_indices: Optional[Any] = None
 
 
 class _Trajectory:
@@ -171,6 +174,7 @@ class SkyRLGymGenerator(GeneratorInterface):
             stop_reason = "stop"
             done = False
             turn = 0
+            routes = None
             while not done:
                 ctx = traj.context
                 if len(ctx) > max_input_length:
@@ -184,6 +188,8 @@ class SkyRLGymGenerator(GeneratorInterface):
                 stop_reason = out["stop_reasons"][0]
                 lps = out.get("response_logprobs")
                 lps = list(lps[0]) if lps is not None and lps[0] is not None else None
+                # every turn re-submits the whole context, so the latest table covers all earlier turns as well
+                turn_routes = (out.get("rollout_expert_indices") or [None])[0]
                 appended_eos = False
                 stops = sp.get("stop")
                 if (stops and self.generator_cfg.append_eos_token_after_stop_str_in_multi_turn
@@ -202,6 +208,8 @@ class SkyRLGymGenerator(GeneratorInterface):
                     text = step_out["postprocessed_action"]
                     out_ids = list(self.tokenizer.encode(text, add_special_tokens=False))
                     lps = None
+                    if turn_routes is not None:
+                        turn_routes = turn_routes[: len(ctx)]  # the re-tokenised action was not what the model saw
                 obs_ids = self._obs_ids(step_out.get("observations") or [], done)
                 if step_wise:
                     gen_part = len(out_ids)
@@ -214,6 +222,8 @@ class SkyRLGymGenerator(GeneratorInterface):
                     steps.append(TrajectoryOutput(ctx, out_ids + obs_ids, rew, mask, stop_reason,
                                                   (lps + [0.0] * len(obs_ids)) if lps is not None else None,
                                                   env.get_metrics() if done else {}, is_last_step=False))
+                if turn_routes is not None:
+                    routes = turn_routes
                 traj.add_model_turn(out_ids, lps, reward, appended_eos)
                 traj.add_observation(obs_ids)
                 turn += 1
@@ -247,7 +257,7 @@ class SkyRLGymGenerator(GeneratorInterface):
             if self.generator_cfg.zero_reward_on_non_stop and stop_reason != "stop":
                 rew = [0.0] * len(rew) if isinstance(rew, list) else 0.0
             return TrajectoryOutput(traj.prompt_ids, resp, rew, mask, stop_reason, lps_all, env_metrics,
-                                    time.monotonic() - t0, splits)
+                                    time.monotonic() - t0, splits, rollout_expert_indices=routes)
         finally:
             await self.client.finish_session(session_id)
 
@@ -286,6 +296,7 @@ class SkyRLGymGenerator(GeneratorInterface):
         llm_t = time.monotonic() - t0
         res = []
         lps_all = out.get("response_logprobs")
+        routes_all = out.get("rollout_expert_indices")
         for i, env in enumerate(envs):
             step_out = env.step(out["responses"][i])
             resp = list(out["response_ids"][i])
@@ -295,7 +306,8 @@ class SkyRLGymGenerator(GeneratorInterface):
                 reward = 0.0
             res.append(TrajectoryOutput(ids[i], resp, reward, [1] * len(resp), stop,
                                         list(lps_all[i]) if lps_all is not None and lps_all[i] is not None else None,
-                                        env.get_metrics(), llm_t, {"llm": llm_t, "env": 0.0}))
+                                        env.get_metrics(), llm_t, {"llm": llm_t, "env": 0.0},
+                                        rollout_expert_indices=routes_all[i] if routes_all is not None else None))
             env.close()
         return res
 
@@ -342,6 +354,7 @@ class SkyRLGymGenerator(GeneratorInterface):
             trajectory_generation_times=[t.e2e_time for t in flat],
             trajectory_time_splits={"llm": [t.time_splits.get("llm", 0.0) for t in flat],
                                     "env": [t.time_splits.get("env", 0.0) for t in flat]},
-            rollout_expert_indices=None,
+            rollout_expert_indices=([t.rollout_expert_indices for t in flat]
+                                    if any(t.rollout_expert_indices is not None for t in flat) else None),
             is_last_step=[t.is_last_step for t in flat] if self.generator_cfg.step_wise_trajectories else None,
             env_metrics=[t.env_metrics for t in flat], pixel_values=None, image_grid_thw=None)

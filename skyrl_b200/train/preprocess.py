@@ -88,6 +88,7 @@ class PackedView:
     n_rows: int
     num_actions: int
     total_tokens: int
+    routing: Optional[torch.Tensor] = None  # [T, layers, top_k] rollout-time expert ids to replay (-1: none recorded)
 
     def scatter_to_grid(self, flat: torch.Tensor, fill: float = 0.0) -> torch.Tensor:
         """Place per-response-token values into the right-aligned ``[n_rows, R]`` grid."""

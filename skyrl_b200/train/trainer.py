@@ -106,6 +106,7 @@ class PPOTrainer:
                             max_num_seqs=ie.max_num_seqs, max_num_batched_tokens=max(ie.max_num_batched_tokens, max_len),
                             max_model_len=max_len, enable_prefix_caching=ie.enable_prefix_caching,
                             enforce_eager=ie.enforce_eager or not b.cuda_graph_decode,
+                            return_routed_experts=bool(ie.enable_return_routed_experts),
                             # the ranks of one tensor-parallel engine must draw the same samples
                             seed=self.cfg.trainer.seed + self.env.rank // max(1, getattr(self, "engine_tp", 1)))
         for k, v in (ie.engine_init_kwargs or {}).items():
@@ -215,6 +216,13 @@ class PPOTrainer:
             out.get("rollout_logprobs"), max_seq_len=self.cfg.trainer.algorithm.max_seq_len)
         batch = TrainingInputBatch({"sequences": seq, "attention_mask": att, "response_mask": rmask, "rewards": rew,
                                     "loss_mask": lmask, "rollout_logprobs": lps})
+        if out.get("rollout_expert_indices") is not None:
+            # rollout-time expert choices, aligned with ``sequences`` (reference: dataset/preprocess.py:230-273)
+            from ..models.router_replay import PAD, pad_routes
+
+            routes = pad_routes(out["rollout_expert_indices"], att.sum(1).tolist(), seq.shape[1])
+            batch["rollout_expert_indices"] = routes
+            batch["router_padding_mask"] = routes[:, :, 0, 0] == PAD
         batch.metadata = {"uids": list(uids), "response_length": rmask.shape[1],
                           "is_last_step": out.get("is_last_step"),
                           "avg_response_length": float(rmask.sum(1).float().mean()),

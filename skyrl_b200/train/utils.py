@@ -149,6 +149,10 @@ def validate_cfg(cfg, world_size: int = 1) -> None:
         raise ValueError(f"invalid dynamic_sampling.type '{a.dynamic_sampling.type}'")
     if g.step_wise_trajectories and g.batched:
         raise ValueError("step_wise_trajectories requires the non-batched generator")
+    if t.policy.megatron_config.moe_enable_routing_replay and not g.inference_engine.enable_return_routed_experts:
+        raise ValueError("rollout router replay needs generator.inference_engine.enable_return_routed_experts=true")
+    if g.inference_engine.enable_return_routed_experts and g.step_wise_trajectories:
+        raise ValueError("step_wise_trajectories does not support enable_return_routed_experts=true")
     if g.max_turns > 1 and g.batched:
         raise ValueError("generator.batched=true only supports max_turns=1")
     if t.fully_async.enabled:

@@ -144,6 +144,7 @@ class ModelWorker:
         dev = self.env.device
         dtype = torch.bfloat16 if (cfg.bf16 and dev.type == "cuda") else torch.float32
         self.params_symm = self.grads_symm = None
+        self._replay_on = False
         self.mesh = None
         self.expert_parallel = self.sequence_parallel = False
         tp_size = self._tp_size_from_cfg(cfg)
@@ -330,9 +331,27 @@ class ModelWorker:
     def _pack(self, batch: TrainingInputBatch, rows: List[int]) -> PackedView:
         idx = torch.tensor(rows, dtype=torch.long)
         b2 = self.cfg.b200
-        return pack_batch(batch["sequences"][idx], batch["attention_mask"][idx], batch["response_mask"][idx],
-                          self.env.device, pad_multiple=int(getattr(b2, "pack_pad_multiple", 0) or 0),
-                          pad_to=self._max_tokens() if getattr(b2, "microbatch_packing", "balanced") == "full" else 0)
+        pv = pack_batch(batch["sequences"][idx], batch["attention_mask"][idx], batch["response_mask"][idx],
+                        self.env.device, pad_multiple=int(getattr(b2, "pack_pad_multiple", 0) or 0),
+                        pad_to=self._max_tokens() if getattr(b2, "microbatch_packing", "balanced") == "full" else 0)
+        routes = batch.get("rollout_expert_indices")
+        if routes is not None and self._replays_routing():
+            # rollout-time expert choices of the packed tokens; the dummy tail that pads the pack keeps its own routing
+            att = batch["attention_mask"][idx].cpu().bool()
+            packed = routes[idx][att]
+            tail = int(pv.ids.numel()) - packed.shape[0]
+            if tail:
+                packed = torch.cat([packed, packed.new_full((tail, *packed.shape[1:]), -1)], 0)
+            pv.routing = _lib.to_device(packed, self.env.device)
+        return pv
+
+    def _replays_routing(self) -> bool:
+        """Router replay (reference: utils/replay_utils.py, ``megatron_config.moe_enable_routing_replay``): the policy
+        and the reference model run their mixture-of-experts layers through the experts the rollout engine chose."""
+        if self.role not in ("policy", "ref") or not self.model.args.num_experts or getattr(self, "pipe", None) is not None:
+            return False
+        node = self.cfg.policy if self.role == "policy" else self.cfg.ref
+        return bool(getattr(getattr(node, "megatron_config", None), "moe_enable_routing_replay", False))
 
     def _rows_to_device(self, t: Optional[torch.Tensor], rows: List[int]) -> Optional[torch.Tensor]:
         if t is None:
@@ -340,7 +359,21 @@ class ModelWorker:
         return _lib.to_device(t[torch.tensor(rows, dtype=torch.long)], self.env.device)
 
     def _hidden(self, pv: PackedView) -> torch.Tensor:
+        if pv.routing is not None or self._replay_on:
+            # stays set through the backward pass (checkpointed layers route again when they are recomputed); the next
+            # micro-batch replaces it and the end of the pass clears it
+            from ..models import router_replay
+
+            router_replay.set_replay(pv.routing)
+            self._replay_on = pv.routing is not None
         return self.model(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen)
+
+    def _end_replay(self) -> None:
+        if self._replay_on:
+            from ..models import router_replay
+
+            router_replay.set_replay(None)
+            self._replay_on = False
 
     # ------------------------------------------------------------------ profiling verbs (reference: worker.py:361-457)
     def start_profile(self) -> None:
@@ -598,6 +631,14 @@ class ModelWorker:
                 ids = torch.cat([ids, torch.zeros(n, dtype=ids.dtype, device=ids.device)])
                 pos = torch.cat([pos, torch.arange(n, dtype=pos.dtype, device=pos.device)])
                 cu = torch.cat([cu, torch.tensor([target], dtype=cu.dtype, device=cu.device)])
+            if pv.routing is not None or self._replay_on:
+                from ..models import router_replay
+
+                r = pv.routing
+                if r is not None and target > T:
+                    r = torch.cat([r, r.new_full((target - T, *r.shape[1:]), -1)], 0)
+                router_replay.set_replay(r)
+                self._replay_on = r is not None
             h = self.model(ids, pos, cu, max(pv.max_seqlen, target - T))
             return self.model.token_logprobs(h[pv.pred_index], pv.targets, temp, with_entropy=with_entropy)
 
@@ -654,6 +695,7 @@ class ModelWorker:
                 grid = _lib.to_host(pv.scatter_to_grid(vals.float()))
                 out[torch.tensor(rows, dtype=torch.long)] = grid
         self.model.gradient_checkpointing = was_ckpt
+        self._end_replay()
         return TrainingOutputBatch({"output": out})
 
     # ------------------------------------------------------------------ state movement (colocation)
@@ -1000,6 +1042,7 @@ class PolicyWorker(ModelWorker):
                     m["rollout_train_logprobs_abs_diff_mean"] = masked_mean(d, mask_g)
                 all_metrics.append(m)
             self.num_microbatches_accumulated += 1
+        self._end_replay()
         status = reduce_metrics(materialize_metrics(all_metrics))
         status = all_reduce_metrics(status, self.env)
         status["policy_lr"] = self.optimizer.lr
