@@ -6,7 +6,7 @@ The key names are the public contract shared with the reference
 The machinery is different: there is no OmegaConf; ``BaseConfig.from_dict`` walks the dataclass type
 hints, coerces scalars parsed from the command line with YAML rules, rejects unknown keys with the
 list of valid ones, and ``from_cli_overrides`` applies a dotlist on top of the defaults.
-Extra knobs that only exist here (engine block size, symmetric-heap sizes, fused-kernel toggles)
+Extra knobs that only exist here (engine block size, fused-kernel toggles, packing and balancing)
 live under ``trainer.b200``.
 """
 
@@ -579,14 +579,11 @@ class B200Config(BaseConfig):
     """Knobs of this implementation that the reference has no equivalent for."""
 
     kv_block_size: int = 32
-    symmetric_heap_mb: int = 0  # 0 = sized from the model
     fused_optimizer: bool = True  # reduce-scatter + AdamW + parameter push in one peer-memory kernel
-    fused_lm_head: bool = True  # tcgen05 LM-head logprob/entropy without logits
     cuda_graph_decode: bool = True
-    decode_graph_batch_sizes: List[int] = field(default_factory=lambda: [1, 2, 4, 8, 16, 32, 64, 128, 256, 512])
-    peer_memory_weight_sync: bool = True
-    nvls: bool = True
-    lm_head_bwd_chunk: int = 8192
+    # batch sizes the engine captures decode graphs for (a step runs at the smallest one that holds its live slots);
+    # empty = the engine's own ladder
+    decode_graph_batch_sizes: List[int] = field(default_factory=list)
     # With exactly one optimizer step per RL step the "old policy" is the policy being trained, so its
     # log-probabilities are the (detached) ones of the training forward pass: no separate forward is run.
     reuse_train_forward_for_old_logprobs: bool = True
@@ -688,6 +685,8 @@ class SkyRLTrainConfig(BaseConfig):
             t.algorithm.max_seq_len = g.max_input_length + g.sampling_params.max_generate_length
         if g.eval_sampling_params is None:
             g.eval_sampling_params = copy.deepcopy(g.sampling_params)
+        if t.log_example_interval > 0:  # old name of print_example_interval
+            t.print_example_interval = t.log_example_interval
         if t.ref.model.path is None:
             t.ref.model.path = t.policy.model.path
 

@@ -27,8 +27,10 @@ def calculate_per_dataset_metrics(out, uids: List[str], data_sources: List[str],
     return m
 
 
-async def evaluate(eval_dataset, generator, cfg, global_step: int, tokenizer=None, env=None) -> Dict[str, float]:
+async def evaluate(eval_dataset, generator, cfg, global_step: int, tokenizer=None, env=None, tracker=None
+                   ) -> Dict[str, float]:
     g = cfg.generator
+    first_out = None
     sp = g.eval_sampling_params.to_dict() if g.eval_sampling_params is not None else None
     bs = cfg.trainer.eval_batch_size
     items = list(eval_dataset.items)
@@ -40,6 +42,8 @@ async def evaluate(eval_dataset, generator, cfg, global_step: int, tokenizer=Non
         gi, uids = prepare_generator_input(chunk, g.eval_n_samples_per_prompt, sp, cfg.environment.env_class, "eval",
                                            global_step)
         out = await generator.generate(gi)
+        if first_out is None:
+            first_out = (out, uids)
         all_rewards.extend(out["rewards"])
         all_uids.extend(uids)
         srcs = [(it.get("env_extras") or {}).get("data_source") for it in chunk for _ in range(g.eval_n_samples_per_prompt)]
@@ -59,6 +63,22 @@ async def evaluate(eval_dataset, generator, cfg, global_step: int, tokenizer=Non
             all_uids = [x for p in parts for x in p[1]]
             all_src = [x for p in parts for x in p[2]]
             dumps = [x for p in parts for x in p[3]]
+    t = cfg.trainer
+    if first_out is not None and (env is None or env.is_main) and (t.print_example_interval > 0 or t.num_logger_eval_samples > 0):
+        # one decoded example to the log, up to ``num_logger_eval_samples`` trajectories to JSONL / the tracker's table
+        # (reference: evaluate.py:105-125)
+        import logging
+
+        from ..utils.trajectory_logging import TrajectoryLogger
+
+        tl = TrajectoryLogger(os.path.join(t.log_path, "trajectories"), tokenizer, max_rows=max(1, t.num_logger_eval_samples),
+                              tracker=tracker)
+        if t.print_example_interval > 0:
+            row = tl.rows(*first_out)[0]
+            logging.getLogger(__name__).info("eval example at step %d | reward %.3f\n--- prompt ---\n%s\n--- response ---\n%s",
+                                             global_step, row["reward"], row["prompt"], row["response"])
+        if t.num_logger_eval_samples > 0:
+            tl.log(first_out[0], global_step, "eval", first_out[1])
     out_all = {"rewards": all_rewards}
     mm = get_metrics_from_generator_output(out_all, all_uids)
     metrics = {"eval/all/avg_score": mm["avg_score"], f"eval/all/pass_at_{g.eval_n_samples_per_prompt}": mm["pass_at_n"],

@@ -17,6 +17,7 @@ prefix-cache entries.
 from __future__ import annotations
 
 import asyncio
+import logging
 import math
 import os
 import time
@@ -41,6 +42,8 @@ from .preprocess import (compute_prompt_boundaries, compute_prompt_mini_batch_bo
                          convert_prompts_responses_to_batch_tensors)
 from .tracking import Tracking
 from .utils import Timer
+
+logger = logging.getLogger(__name__)
 
 
 class PPOTrainer:
@@ -109,6 +112,8 @@ class PPOTrainer:
                             return_routed_experts=bool(ie.enable_return_routed_experts),
                             # the ranks of one tensor-parallel engine must draw the same samples
                             seed=self.cfg.trainer.seed + self.env.rank // max(1, getattr(self, "engine_tp", 1)))
+        if b.decode_graph_batch_sizes:
+            ecfg.graph_batch_sizes = tuple(sorted(int(x) for x in b.decode_graph_batch_sizes))
         for k, v in (ie.engine_init_kwargs or {}).items():
             if hasattr(ecfg, k):
                 setattr(ecfg, k, v)
@@ -551,6 +556,7 @@ class PPOTrainer:
                 return m
         with Timer("postprocess", self.all_timings):
             out = self.postprocess_generator_output(out, uids)
+            self._log_examples(out, uids)
             batch = self.convert_to_training_input(out, uids)
         with Timer("fwd_logprobs_values_reward", self.all_timings):
             batch = self.fwd_logprobs_values_reward(batch)
@@ -558,6 +564,9 @@ class PPOTrainer:
             batch = self.apply_reward_kl_penalty(batch)
         with Timer("compute_advantages_and_returns", self.all_timings):
             batch = self.compute_advantages_and_returns(batch)
+        if cfg.trainer.dump_data_batch:
+            with Timer("dump_data_batch", self.all_timings):
+                self.dump_data(batch, f"global_step_{self.global_step}_training_input")
         with Timer("train_critic_and_policy", self.all_timings):
             self.all_metrics.update(self.train_critic_and_policy(batch))
         with Timer("sync_weights", self.all_timings):
@@ -630,6 +639,37 @@ class PPOTrainer:
         for cb in self.callbacks:
             cb.on_train_end(self)
 
+    def _log_examples(self, out: GeneratorOutput, uids: List[str]) -> None:
+        """Rank 0: one decoded example every ``trainer.print_example_interval`` steps (reference: trainer.py:394-403) and
+        up to ``trainer.num_logger_train_samples`` trajectories per step as JSONL under ``{log_path}/trajectories`` and
+        as a tracker table (reference: trainer.py:405-417; ``-1`` = off)."""
+        t = self.cfg.trainer
+        if not self.env.is_main or not out.get("response_ids"):
+            return
+        every = t.print_example_interval
+        if every > 0 and self.global_step % every == 0:
+            from ..utils.trajectory_logging import TrajectoryLogger
+
+            row = TrajectoryLogger(os.path.join(t.log_path, "trajectories"), self.tokenizer, max_rows=1).rows(out, uids)[0]
+            logger.info("step %d example | reward %.3f | stop %s | %d tokens\n--- prompt ---\n%s\n--- response ---\n%s",
+                        self.global_step, row["reward"], row["stop_reason"], row["response_length"], row["prompt"],
+                        row["response"])
+        if t.num_logger_train_samples > 0:
+            from ..utils.trajectory_logging import TrajectoryLogger
+
+            TrajectoryLogger(os.path.join(t.log_path, "trajectories"), self.tokenizer, max_rows=t.num_logger_train_samples,
+                             tracker=self.tracker).log(out, self.global_step, "train", uids)
+
+    def dump_data(self, batch: TrainingInputBatch, file_name: str) -> str:
+        """``trainer.dump_data_batch``: the training batch of this rank, as the byte form that
+        ``TrainingInputBatch.from_bytes`` reads back, under ``{export_path}/dumped_data`` (reference: trainer.py:1236-1242)."""
+        d = os.path.join(self.cfg.trainer.export_path, "dumped_data")
+        os.makedirs(d, exist_ok=True)
+        path = os.path.join(d, f"{file_name}_rank{self.env.rank}.bin" if self.env.world_size > 1 else f"{file_name}.bin")
+        with open(path, "wb") as f:
+            f.write(batch.to_bytes())
+        return path
+
     def _log(self, metrics: Dict[str, float], step: int) -> None:
         if self.tracker is not None and self.env.is_main:
             self.tracker.log(metrics, step)
@@ -637,7 +677,8 @@ class PPOTrainer:
     async def eval_async(self) -> Dict[str, float]:
         from .evaluate import evaluate
 
-        return await evaluate(self.eval_dataset, self.generator, self.cfg, self.global_step, self.tokenizer, self.env)
+        return await evaluate(self.eval_dataset, self.generator, self.cfg, self.global_step, self.tokenizer, self.env,
+                              tracker=self.tracker)
 
     def eval(self) -> Dict[str, float]:
         return asyncio.run(self.eval_async())

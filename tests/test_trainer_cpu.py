@@ -109,3 +109,34 @@ def test_two_minibatches_recompute_old_logprobs_with_train_packing(tmp_path):
     full = tr.policy.forward(b)["output"]
     per_mb = tr._forward_old(tr.policy, "policy", b)
     assert torch.allclose(full, per_mb, atol=1e-5)
+
+
+def test_example_logging_trajectory_samples_and_batch_dump(tmp_path, caplog):
+    import glob
+    import json
+    import logging
+
+    from skyrl_b200.train.batch import TrainingInputBatch
+
+    pdist.reset_env_for_tests()
+    cfg = _cfg(tmp_path, ["trainer.print_example_interval=1", "trainer.num_logger_train_samples=3",
+                          "trainer.dump_data_batch=true", f"trainer.log_path={tmp_path}/logs"])
+    tr = PPOTrainer(cfg, tokenizer=SyntheticTokenizer(1024))
+    tr.build_models()
+    with caplog.at_level(logging.INFO, logger="skyrl_b200.train.trainer"):
+        tr.train_step(_prompts())
+    assert any("--- response ---" in r.getMessage() for r in caplog.records)
+    rows = [json.loads(l) for l in open(glob.glob(f"{tmp_path}/logs/trajectories/train_trajectories_step_0.jsonl")[0])]
+    assert len(rows) == 3 and all(r["response_length"] > 0 for r in rows)
+    dumped = glob.glob(f"{tmp_path}/export/dumped_data/global_step_0_training_input.bin")
+    assert len(dumped) == 1
+    back = TrainingInputBatch.from_bytes(open(dumped[0], "rb").read())
+    assert back["sequences"].shape[0] == 32 and "advantages" in back
+    # the old name of the interval still works
+    old = _cfg(tmp_path, ["trainer.log_example_interval=7"])
+    assert old.trainer.print_example_interval == 7
+    # decode-graph sizes reach the engine
+    sized = _cfg(tmp_path, ["trainer.b200.decode_graph_batch_sizes=[4,16,8]"])
+    tr2 = PPOTrainer(sized, tokenizer=SyntheticTokenizer(1024))
+    tr2.build_models()
+    assert tuple(tr2.engine.cfg.graph_batch_sizes) == (4, 8, 16)
