@@ -101,11 +101,14 @@ def datums_to_batch(datums: List[Dict[str, Any]], pad_token_id: int, role: str =
 
 
 class ModelSlot:
-    """One Tinker ``model_id``: a worker plus bookkeeping."""
+    """One Tinker ``model_id``: a worker plus bookkeeping.  ``store`` is set for LoRA models: they are tenants of an
+    ``AdapterStore`` on a worker that several model ids share (one resident base model, one adapter + optimizer state
+    per id, swapped in before every verb)."""
 
-    def __init__(self, model_id: str, worker, role: str, lora_config: Optional[dict]):
-        self.model_id, self.worker, self.role, self.lora_config = model_id, worker, role, lora_config
+    def __init__(self, model_id: str, worker, role: str, lora_config: Optional[dict], store=None):
+        self.model_id, self.worker, self.role, self.lora_config, self.store = model_id, worker, role, lora_config, store
         self.step = 0
+        self.sampler_version = 0
 
 
 class SkyRLTrainBackend:
@@ -119,7 +122,9 @@ class SkyRLTrainBackend:
         self.env = env or get_env()
         self.tokenizer = tokenizer
         self.models: Dict[str, ModelSlot] = {}
+        self._lora_hosts: Dict[tuple, Any] = {}  # (rank, alpha) -> AdapterStore whose worker holds the shared base model
         self.engine = None
+        self._engine_owner = None  # the worker whose ``engine_model()`` the engine runs
         self.client = None
         self.sampler_version = 0
         self.checkpoints_base = checkpoints_base or os.path.join(tempfile.gettempdir(), "skyrl_b200_tinker")
@@ -139,28 +144,63 @@ class SkyRLTrainBackend:
         if model_id in self.models:
             raise ValueError(f"model {model_id} already exists")
         t = self.cfg.trainer
-        if lora_config and lora_config.get("rank"):
-            t.policy.model.lora.rank = int(lora_config["rank"])
         seed = int((lora_config or {}).get("seed") or t.seed)
+        rank = int((lora_config or {}).get("rank") or 0)
         if model_role == "critic":
             w = CriticWorker(t, model_path=t.critic.model.path or self.base_model, env=self.env, seed=seed)
-        else:
-            w = PolicyWorker(t, model_path=self.base_model, env=self.env, seed=seed)
+            self.models[model_id] = ModelSlot(model_id, w, model_role, lora_config)
+            return
+        if rank > 0:
+            # LoRA models of one shape share a worker: the frozen base is resident once, each model id owns an adapter
+            # buffer, its fp32 master copy, Adam moments and pending gradients (reference: the Megatron backend's
+            # AdapterStore and the JAX backend's adapter-indexed LoRA layers)
+            from ..workers.adapter_store import AdapterStore
+
+            alpha = float((lora_config or {}).get("alpha") or t.policy.model.lora.alpha)
+            key = (rank, alpha)
+            store = self._lora_hosts.get(key)
+            if store is None:
+                import copy
+
+                tc = copy.deepcopy(t)
+                tc.policy.model.lora.rank, tc.policy.model.lora.alpha = rank, alpha
+                w = PolicyWorker(tc, model_path=self.base_model, env=self.env, seed=int(t.seed))
+                store = AdapterStore(w, max_slots=max(1, int(t.policy.model.lora.max_loras or 1), self.max_lora_models))
+                self._lora_hosts[key] = store
+            store.create(model_id, seed=seed)
+            self.models[model_id] = ModelSlot(model_id, store.worker, model_role, lora_config, store=store)
+            return
+        w = PolicyWorker(t, model_path=self.base_model, env=self.env, seed=seed)
         self.models[model_id] = ModelSlot(model_id, w, model_role, lora_config)
+
+    max_lora_models = 16  # tenants per shared base; their state lives in pinned host memory while inactive
+
+    def _activate(self, slot: ModelSlot) -> None:
+        """Bring the model id's adapter (with optimizer state and pending gradients) into its worker."""
+        if slot.store is not None:
+            slot.store.swap_to(slot.model_id)
 
     def delete_model(self, model_id: str) -> None:
         slot = self.models.pop(model_id, None)
-        if slot is not None:
-            if self.engine is not None and getattr(self.engine, "model", None) is slot.worker.model:
-                self.engine, self.client = None, None
-            del slot
-            if torch.cuda.is_available():
-                torch.cuda.empty_cache()
+        if slot is None:
+            return
+        last_user = True
+        if slot.store is not None:
+            slot.store.delete(model_id)
+            last_user = not slot.store.slots
+            if last_user:
+                self._lora_hosts = {k: v for k, v in self._lora_hosts.items() if v is not slot.store}
+        if last_user and self.engine is not None and self._engine_owner is slot.worker:
+            self.engine, self.client, self._engine_owner = None, None, None
+        del slot
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ training verbs
     def forward_backward(self, model_id: str, datums: List[dict], loss_fn: str, loss_fn_config: Optional[dict] = None,
                          forward_only: bool = False) -> Dict[str, Any]:
         slot = self.models[model_id]
+        self._activate(slot)
         batch = datums_to_batch(datums, self._pad_id(), slot.role)
         name = LOSS_ALIASES.get(loss_fn, loss_fn)
         if slot.role == "critic" or name == "ppo_critic":
@@ -210,6 +250,7 @@ class SkyRLTrainBackend:
 
     def optim_step(self, model_id: str, adam_params: Optional[dict] = None) -> Dict[str, Any]:
         slot = self.models[model_id]
+        self._activate(slot)
         ap = adam_params or {}
         opt = slot.worker.optimizer
         if "learning_rate" in ap:
@@ -236,7 +277,8 @@ class SkyRLTrainBackend:
             slot = next((s for s in self.models.values() if s.role == "policy"), None)
         if slot is None:
             raise ValueError("no policy model is loaded to sample from")
-        if self.engine is None or self.engine.model is not slot.worker.model:
+        self._activate(slot)
+        if self.engine is None or self._engine_owner is not slot.worker:
             ie = self.cfg.generator.inference_engine
             g = self.cfg.generator
             max_len = (g.max_input_length or self.cfg.trainer.max_prompt_length) + g.sampling_params.max_generate_length
@@ -248,7 +290,9 @@ class SkyRLTrainBackend:
             for k, v in (ie.engine_init_kwargs or {}).items():
                 if hasattr(ecfg, k):
                     setattr(ecfg, k, v)
-            self.engine = LLMEngine(slot.worker.model, ecfg, eos_token_ids=eos)
+            # full-parameter models are read in place; LoRA models run a merged copy that follows the active adapter
+            self.engine = LLMEngine(slot.worker.engine_model(), ecfg, eos_token_ids=eos)
+            self._engine_owner = slot.worker
         return self.engine
 
     def sample(self, prompts: List[List[int]], sampling_params: List[dict], num_samples: List[int],
@@ -269,7 +313,8 @@ class SkyRLTrainBackend:
                 flat_prompts.append(p)
                 flat_params.append(params)
                 owner.append(i)
-        outs = eng.generate(flat_prompts, flat_params, cache_salt=f"v{self.sampler_version}")
+        # cached prefixes are only shared between requests that see the same weights
+        outs = eng.generate(flat_prompts, flat_params, cache_salt=f"{model_id or ''}-v{self.sampler_version}")
         results: List[Dict[str, Any]] = [{"sequences": [], "prompt_logprobs": None, "type": "sample"} for _ in prompts]
         for o, i in zip(outs, owner):
             results[i]["sequences"].append({"tokens": list(o.token_ids), "logprobs": [float(x) for x in o.logprobs],
@@ -287,6 +332,7 @@ class SkyRLTrainBackend:
     def save_checkpoint(self, model_id: str, checkpoint_id: str) -> str:
         """Training state (parameters, optimizer shards, scheduler) as one tar archive."""
         slot = self.models[model_id]
+        self._activate(slot)
         out = self._ckpt_path(model_id, checkpoint_id, "weights")
         with tempfile.TemporaryDirectory() as tmp:
             slot.worker.save_checkpoint(tmp, tag=checkpoint_id)
@@ -299,12 +345,14 @@ class SkyRLTrainBackend:
 
     def load_checkpoint(self, model_id: str, path: str, optimizer: bool = True) -> None:
         slot = self.models[model_id]
+        self._activate(slot)
         with tempfile.TemporaryDirectory() as tmp:
             with tarfile.open(path, "r") as tar:
                 tar.extractall(tmp, filter="data")
             slot.worker.load_checkpoint(tmp, load_optimizer_states=optimizer, load_lr_scheduler_states=optimizer)
         self.sampler_version += 1
-        if self.engine is not None and self.engine.model is slot.worker.model:
+        slot.worker.refresh_engine_model()
+        if self.engine is not None and self._engine_owner is slot.worker:
             self.engine.reset_prefix_cache()
             self.engine.weight_version = self.sampler_version
 
@@ -315,6 +363,7 @@ class SkyRLTrainBackend:
         slot = self.models[model_id]
         self.sampler_version += 1
         eng = self._ensure_engine(model_id)
+        slot.worker.refresh_engine_model()  # LoRA: merge the trained adapter into the engine's copy
         eng.reset_prefix_cache()
         eng.weight_version = self.sampler_version
         if not persist or not checkpoint_id:

@@ -12,7 +12,7 @@ import torch.distributed as dist
 
 
 class AdapterSlot:
-    def __init__(self, params: torch.Tensor, optimizer) -> None:
+    def __init__(self, params: torch.Tensor, optimizer, grads: Optional[torch.Tensor] = None) -> None:
         pin = torch.cuda.is_available()
 
         def host(t: torch.Tensor) -> torch.Tensor:
@@ -23,6 +23,10 @@ class AdapterSlot:
         self.params = host(params)
         self.master, self.exp_avg, self.exp_avg_sq = host(optimizer.master), host(optimizer.exp_avg), host(optimizer.exp_avg_sq)
         self.step_count, self.lr = optimizer.step_count, optimizer.lr
+        # gradients accumulated by forward_backward calls that no optim_step has consumed yet: a tenant may be swapped
+        # out between the two (reference: adapter_store.py:113-125, ``cpu_grad_data``)
+        self.grads = host(grads) if grads is not None else None
+        self.microbatches = 0
 
 
 class AdapterStore:
@@ -51,6 +55,9 @@ class AdapterStore:
         s.exp_avg.copy_(w.optimizer.exp_avg, non_blocking=True)
         s.exp_avg_sq.copy_(w.optimizer.exp_avg_sq, non_blocking=True)
         s.step_count, s.lr = w.optimizer.step_count, w.optimizer.lr
+        if s.grads is not None:
+            s.grads.copy_(w.flat_grad, non_blocking=True)
+            s.microbatches = w.num_microbatches_accumulated
         if torch.cuda.is_available():
             torch.cuda.current_stream().synchronize()
 
@@ -70,7 +77,8 @@ class AdapterStore:
         o.exp_avg_sq.zero_()
         o.step_count = 0
         o.zero_grad()
-        self.slots[name] = AdapterSlot(w.model.flat_params, o)
+        w.num_microbatches_accumulated = 0
+        self.slots[name] = AdapterSlot(w.model.flat_params, o, getattr(w, "flat_grad", None))
         self.active = name
         self._barrier()
 
@@ -88,6 +96,10 @@ class AdapterStore:
         w.optimizer.exp_avg_sq.copy_(s.exp_avg_sq, non_blocking=True)
         w.optimizer.step_count, w.optimizer.lr = s.step_count, s.lr
         w.optimizer.zero_grad()
+        w.num_microbatches_accumulated = 0
+        if s.grads is not None:
+            w.flat_grad.copy_(s.grads, non_blocking=True)
+            w.num_microbatches_accumulated = s.microbatches
         self.active = name
         w.refresh_engine_model()
         self._barrier()

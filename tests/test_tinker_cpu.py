@@ -171,3 +171,71 @@ def test_rest_round_trip(tmp_path):
         runs = c.get("/api/v1/training_runs").json()
         assert runs["cursor"]["total_count"] == 1 and runs["training_runs"][0]["training_run_id"] == mid
         assert c.post("/api/v1/retrieve_future", json={"request_id": "99999"}).status_code == 404
+
+
+def test_lora_models_share_one_base_and_keep_their_own_state(tmp_path):
+    """Two LoRA model ids are tenants of one worker: interleaved forward_backward / optim_step calls give each the
+    result it would have had alone, pending gradients survive a swap, and sampling follows the requested id."""
+    import torch
+
+    from skyrl_b200.parallel import dist as pdist
+    from skyrl_b200.tinker.backend import SkyRLTrainBackend
+    from skyrl_b200.utils.tokenizer import SyntheticTokenizer
+
+    pdist.reset_env_for_tests()
+    ov = {"trainer.bf16": "false", "generator.sampling_params.max_generate_length": 8, "trainer.max_prompt_length": 16,
+          "generator.inference_engine.enforce_eager": "true", "generator.inference_engine.max_num_seqs": 4,
+          "trainer.policy.optimizer_config.lr": 1e-2, "trainer.policy.optimizer_config.max_grad_norm": 1e9,
+          "trainer.gradient_checkpointing": "false"}
+
+    def backend(sub):
+        return SkyRLTrainBackend("tiny-llama", ov, tokenizer=SyntheticTokenizer(1024), checkpoints_base=str(tmp_path / sub))
+
+    data_a = [_datum([5, 6, 7, 8, 9, 10]), _datum([11, 12, 13, 14])]
+    data_b = [_datum([21, 22, 23, 24, 25]), _datum([31, 32, 33])]
+    lora = lambda seed: {"rank": 4, "alpha": 8, "seed": seed}  # noqa: E731
+
+    # each model alone
+    alone = {}
+    for name, seed, data in (("a", 1, data_a), ("b", 2, data_b)):
+        be = backend("alone_" + name)
+        be.create_model(name, lora(seed))
+        be.forward_backward(name, data, "cross_entropy")
+        be.forward_backward(name, data[:1], "cross_entropy")
+        be.optim_step(name, {"learning_rate": 1e-2})
+        alone[name] = be.models[name].worker.model.flat_params.clone()
+
+    # both on one backend, calls interleaved so that every swap happens with gradients pending
+    be = backend("shared")
+    be.create_model("a", lora(1))
+    be.create_model("b", lora(2))
+    assert be.models["a"].worker is be.models["b"].worker and len(be._lora_hosts) == 1
+    be.forward_backward("a", data_a, "cross_entropy")
+    be.forward_backward("b", data_b, "cross_entropy")
+    be.forward_backward("a", data_a[:1], "cross_entropy")
+    be.forward_backward("b", data_b[:1], "cross_entropy")
+    ra = be.optim_step("a", {"learning_rate": 1e-2})
+    rb = be.optim_step("b", {"learning_rate": 1e-2})
+    assert ra["metrics"]["grad_norm"] > 0 and rb["metrics"]["grad_norm"] > 0
+    w = be.models["a"].worker
+    be._activate(be.models["a"])
+    assert torch.allclose(w.model.flat_params, alone["a"], atol=1e-6)
+    be._activate(be.models["b"])
+    assert torch.allclose(w.model.flat_params, alone["b"], atol=1e-6)
+    assert not torch.allclose(alone["a"], alone["b"])
+
+    # sampling runs the merged weights of the requested model id (greedy: different adapters, different log-probs)
+    sp = [{"max_tokens": 6, "temperature": 0.0}]
+    be.save_sampler_checkpoint("a", None, persist=False)
+    sa = be.sample([[5, 6, 7]], sp, [1], model_id="a")[0]["sequences"][0]
+    sb = be.sample([[5, 6, 7]], sp, [1], model_id="b")[0]["sequences"][0]
+    sa2 = be.sample([[5, 6, 7]], sp, [1], model_id="a")[0]["sequences"][0]
+    assert sa["tokens"] == sa2["tokens"] and sa["logprobs"] == pytest.approx(sa2["logprobs"], abs=1e-6)
+    assert sa["logprobs"] != pytest.approx(sb["logprobs"], abs=1e-7)
+
+    # deleting one tenant keeps the other and the shared worker; deleting the last one frees the host
+    be.delete_model("a")
+    assert "b" in be.models and len(be._lora_hosts) == 1
+    be.forward_backward("b", data_b, "cross_entropy")
+    be.delete_model("b")
+    assert not be._lora_hosts and be.engine is None
