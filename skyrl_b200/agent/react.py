@@ -14,6 +14,7 @@ import json
 import re
 from dataclasses import dataclass, field
 from typing import Any, Awaitable, Callable, Dict, List, Optional
+from ..utils.tokenizer import chat_template_ids
 
 _TOOL = re.compile(r"<tool>(.*?)</tool>", re.DOTALL)
 _ANSWER = re.compile(r"<answer>(.*?)</answer>", re.DOTALL)
@@ -71,7 +72,7 @@ class ReActAgent:
 
     async def run(self, task: str, session_id: Optional[str] = None) -> AgentResult:
         msgs = [{"role": "system", "content": self.system_prompt}, {"role": "user", "content": task}]
-        prompt_ids = list(self.tok.apply_chat_template(msgs, add_generation_prompt=True, tokenize=True))
+        prompt_ids = chat_template_ids(self.tok, msgs, add_generation_prompt=True)
         ctx = list(prompt_ids)
         resp, mask, lps = [], [], []
         have_lp = True
@@ -98,7 +99,7 @@ class ReActAgent:
                 stop = "no_action"
                 break
             msgs.append({"role": "user", "content": obs})
-            full = list(self.tok.apply_chat_template(msgs, add_generation_prompt=True, tokenize=True))
+            full = chat_template_ids(self.tok, msgs, add_generation_prompt=True)
             obs_ids = full[len(ctx):] if full[: len(ctx)] == ctx else list(self.tok.encode(obs))
             resp += obs_ids
             mask += [0] * len(obs_ids)  # environment tokens carry no loss

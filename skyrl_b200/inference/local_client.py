@@ -17,6 +17,7 @@ from typing import Any, Dict, List, Optional, Sequence
 from ..engine.llm_engine import LLMEngine, RequestOutput, SamplingParams
 from ..ops import _lib
 from .base import InferenceEngineInput, InferenceEngineInterface, InferenceEngineOutput
+from ..utils.tokenizer import chat_template_ids
 
 
 class _Ring:
@@ -109,7 +110,7 @@ class LocalInferenceClient(InferenceEngineInterface):
         if ids is None:
             prompts = input_batch.get("prompts")
             assert prompts is not None and self.tokenizer is not None, "need prompt_token_ids or (prompts + tokenizer)"
-            ids = [self.tokenizer.apply_chat_template(p, add_generation_prompt=True, tokenize=True) for p in prompts]
+            ids = [chat_template_ids(self.tokenizer, p, add_generation_prompt=True) for p in prompts]
         sp = SamplingParams.from_dict(input_batch.get("sampling_params"))
         sessions = input_batch.get("session_ids") or [None] * len(ids)
         salt = input_batch.get("cache_salt")

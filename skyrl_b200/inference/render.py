@@ -19,6 +19,7 @@ from typing import Any, Dict, List, NamedTuple, Optional, Sequence
 
 import numpy as np
 import torch
+from ..utils.tokenizer import chat_template_ids
 
 
 class RenderedModelInput(NamedTuple):
@@ -122,8 +123,7 @@ def render_chat(messages: List[Dict[str, Any]], tokenizer, image_token_id: Optio
         else:
             flat.append(m)
     if not images:
-        return RenderedModelInput(list(tokenizer.apply_chat_template(flat, add_generation_prompt=add_generation_prompt,
-                                                                     tokenize=True)))
+        return RenderedModelInput(chat_template_ids(tokenizer, flat, add_generation_prompt=add_generation_prompt))
     if processor is None or image_token_id is None:
         raise ValueError("messages contain images but no image processor / placeholder token id was given")
     text = tokenizer.apply_chat_template(flat, add_generation_prompt=add_generation_prompt, tokenize=False)

@@ -23,6 +23,7 @@ from typing import Any, Dict, List, Optional
 
 from . import wire
 from .local_client import LocalInferenceClient
+from ..utils.tokenizer import chat_template_ids
 
 MISSING_LOGPROB = -9999.0
 
@@ -105,7 +106,7 @@ def build_app(client: LocalInferenceClient, model_name: str = "policy", weight_l
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
         body = await request.json()
-        ids = _tok().apply_chat_template(body["messages"], add_generation_prompt=True, tokenize=True)
+        ids = chat_template_ids(_tok(), body["messages"], add_generation_prompt=True)
         sp = {k: body[k] for k in ("temperature", "top_p", "top_k", "min_p", "stop") if k in body}
         sp["max_generate_length"] = body.get("max_tokens") or body.get("max_completion_tokens") or 256
         r = await _generate({"token_ids": list(ids), "sampling_params": sp}, request.headers.get("X-Session-ID"))
@@ -119,8 +120,7 @@ def build_app(client: LocalInferenceClient, model_name: str = "policy", weight_l
     async def tokenize(request: Request):
         body = await request.json()
         if "messages" in body:
-            ids = _tok().apply_chat_template(body["messages"], add_generation_prompt=body.get("add_generation_prompt", True),
-                                             tokenize=True)
+            ids = chat_template_ids(_tok(), body["messages"], add_generation_prompt=body.get("add_generation_prompt", True))
         else:
             ids = _tok().encode(body.get("prompt", ""))
         return {"tokens": list(ids), "count": len(ids)}

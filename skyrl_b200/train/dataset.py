@@ -15,6 +15,7 @@ import os
 from typing import Any, Dict, Iterator, List, Optional, Sequence
 
 import numpy as np
+from ..utils.tokenizer import chat_template_ids
 
 
 def _read_rows(path: str) -> List[Dict[str, Any]]:
@@ -54,7 +55,7 @@ class PromptDataset:
         for i, r in enumerate(rows):
             prompt = r[prompt_key]
             if tokenizer is not None and max_prompt_length is not None and r.get("prompt_token_ids") is None:
-                n = len(tokenizer.apply_chat_template(prompt, add_generation_prompt=True, tokenize=True))
+                n = len(chat_template_ids(tokenizer, prompt, add_generation_prompt=True))
                 if n > max_prompt_length:
                     dropped += 1
                     continue

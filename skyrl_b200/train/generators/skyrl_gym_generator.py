@@ -28,6 +28,7 @@ from ... import gym as skyrl_gym
 from ...inference.base import InferenceEngineInput, InferenceEngineInterface
 from .base import GeneratorInput, GeneratorInterface, GeneratorOutput, TrajectoryID
 from .utils import get_rollout_metrics
+from ...utils.tokenizer import chat_template_ids
 
 
 @dataclass
@@ -112,14 +113,25 @@ class SkyRLGymGenerator(GeneratorInterface):
         n_workers = getattr(skyrl_gym_cfg, "max_env_workers", 32) if skyrl_gym_cfg is not None else 32
         self.env_executor = ThreadPoolExecutor(max_workers=n_workers, thread_name_prefix="env") if n_workers > 0 else None
         self.weight_version_fn = getattr(inference_engine_client, "weight_version", None)
+        # a custom chat template (generator.chat_template) switches the multi-turn loop to re-tokenising the whole chat
+        # history every turn; the assistant mask then comes from the template's {% generation %} blocks
+        from .utils import get_custom_chat_template
+
+        self.custom_chat_template = get_custom_chat_template(getattr(generator_cfg, "chat_template", None))
         if self.batched and self.max_turns > 1:
             raise ValueError("generator.batched=true only supports single-turn rollouts (max_turns=1)")
         # ids of an empty conversation: the prefix that observation tokenisation strips off
         self._base_conv = [{"role": "system", "content": ""}]
         try:
-            self._base_ids = self.tokenizer.apply_chat_template(self._base_conv, add_generation_prompt=False, tokenize=True)
+            self._base_ids = chat_template_ids(self.tokenizer, self._base_conv, add_generation_prompt=False)
         except Exception:
             self._base_conv, self._base_ids = [], []
+        # What a template writes after the end-of-turn token (ChatML: a newline) belongs in front of the next message:
+        # a sampled turn stops at its end-of-turn token, so the observation that follows has to bring those tokens
+        # along.  Cutting the base at its last end-of-turn token makes every observation start with them.
+        eos = getattr(self.tokenizer, "eos_token_id", None)
+        if eos is not None and eos in self._base_ids:
+            self._base_ids = self._base_ids[: len(self._base_ids) - self._base_ids[::-1].index(eos)]
 
     # ------------------------------------------------------------------ helpers
     async def _in_executor(self, fn, *args):
@@ -139,13 +151,13 @@ class SkyRLGymGenerator(GeneratorInterface):
         if not observations:
             if done or not self.use_conversation_multi_turn:
                 return []
-            full = self.tokenizer.apply_chat_template(self._base_conv, add_generation_prompt=True, tokenize=True)
+            full = chat_template_ids(self.tokenizer, self._base_conv, add_generation_prompt=True)
             return list(full[len(self._base_ids):])
         if not self.use_conversation_multi_turn:
             text = "".join(str(m.get("content", "")) for m in observations)
             return list(self.tokenizer.encode(text, add_special_tokens=False))
-        full = self.tokenizer.apply_chat_template(self._base_conv + list(observations), add_generation_prompt=not done,
-                                                  tokenize=True, **self.generator_cfg.chat_template_kwargs)
+        full = chat_template_ids(self.tokenizer, self._base_conv + list(observations), add_generation_prompt=not done,
+                                 **self.generator_cfg.chat_template_kwargs)
         return list(full[len(self._base_ids):])
 
     # ------------------------------------------------------------------ one episode
@@ -168,15 +180,29 @@ class SkyRLGymGenerator(GeneratorInterface):
             if prompt_token_ids is not None:
                 ids0 = list(prompt_token_ids)
             else:
-                ids0 = list(self.tokenizer.apply_chat_template(chat, add_generation_prompt=True, tokenize=True,
-                                                               **self.generator_cfg.chat_template_kwargs))
+                tkw = dict(self.generator_cfg.chat_template_kwargs)
+                if self.use_conversation_multi_turn and self.custom_chat_template:
+                    tkw["chat_template"] = self.custom_chat_template
+                ids0 = chat_template_ids(self.tokenizer, chat, add_generation_prompt=True, **tkw)
             traj = _Trajectory(ids0, track_logprobs=sp.get("logprobs", 1) is not None)
             stop_reason = "stop"
             done = False
             turn = 0
             routes = None
+            retokenize = bool(self.use_conversation_multi_turn and self.custom_chat_template)
+            if retokenize and step_wise:
+                raise ValueError("step_wise_trajectories is not supported with a custom chat template")
+            history = [dict(m) for m in chat] if isinstance(chat, list) else []
+            n_prompt_msgs = len(history)
+            last_obs: List[Dict[str, Any]] = []
+            last_reward = 0.0
+            eos_text = getattr(self.tokenizer, "eos_token", None)
             while not done:
-                ctx = traj.context
+                if retokenize:
+                    ctx = chat_template_ids(self.tokenizer, history, chat_template=self.custom_chat_template,
+                                            add_generation_prompt=True, **self.generator_cfg.chat_template_kwargs)
+                else:
+                    ctx = traj.context
                 if len(ctx) > max_input_length:
                     stop_reason = "length"
                     break
@@ -190,6 +216,8 @@ class SkyRLGymGenerator(GeneratorInterface):
                 lps = list(lps[0]) if lps is not None and lps[0] is not None else None
                 # every turn re-submits the whole context, so the latest table covers all earlier turns as well
                 turn_routes = (out.get("rollout_expert_indices") or [None])[0]
+                if turn_routes is not None and retokenize:
+                    raise ValueError("rollout expert indices cannot be kept when a custom chat template re-tokenises the history")
                 appended_eos = False
                 stops = sp.get("stop")
                 if (stops and self.generator_cfg.append_eos_token_after_stop_str_in_multi_turn
@@ -210,7 +238,23 @@ class SkyRLGymGenerator(GeneratorInterface):
                     lps = None
                     if turn_routes is not None:
                         turn_routes = turn_routes[: len(ctx)]  # the re-tokenised action was not what the model saw
+                if retokenize:
+                    # the template puts the end-of-turn token back: keep the plain text in the history
+                    msg = text[: -len(eos_text)] if eos_text and text.endswith(eos_text) else text
+                    last_obs = list(step_out.get("observations") or [])
+                    history.append({"role": "assistant", "content": msg})
+                    history.extend(last_obs)
+                    last_reward = reward
+                    turn += 1
+                    continue
                 obs_ids = self._obs_ids(step_out.get("observations") or [], done)
+                if not self.use_conversation_multi_turn and not step_wise and not done:
+                    # every turn continues one assistant message: the end-of-sequence token a turn ended on would sit in
+                    # the middle of it, so it is dropped.  The last turn keeps its own (with its sampled log-prob); if
+                    # it has none, one is appended below.
+                    if out_ids and out_ids[-1] == self.tokenizer.eos_token_id:
+                        out_ids = out_ids[:-1]
+                        lps = lps[: len(out_ids)] if lps is not None else None
                 if step_wise:
                     gen_part = len(out_ids)
                     mask = [1] * gen_part + [0] * len(obs_ids)
@@ -244,6 +288,18 @@ class SkyRLGymGenerator(GeneratorInterface):
                 for s in steps:
                     s.e2e_time, s.time_splits = time.monotonic() - t0, splits
                 return steps
+            if retokenize:
+                # response = every message after the prompt except the observations of the last step; the assistant
+                # mask comes from the template; one scalar reward (the last step's) and no rollout log-probs, because the
+                # tokens trained on are not necessarily the ones that were sampled
+                tail = history[n_prompt_msgs : len(history) - len(last_obs)]
+                enc = self.tokenizer.apply_chat_template(tail, chat_template=self.custom_chat_template,
+                                                         add_generation_prompt=False, return_dict=True,
+                                                         return_assistant_tokens_mask=True, tokenize=True,
+                                                         **self.generator_cfg.chat_template_kwargs)
+                rew_f = 0.0 if (self.generator_cfg.zero_reward_on_non_stop and stop_reason != "stop") else float(last_reward)
+                return TrajectoryOutput(ids0, list(enc["input_ids"]), rew_f, [int(x) for x in enc["assistant_masks"]],
+                                        stop_reason, None, env_metrics, time.monotonic() - t0, splits)
             per_token = self.max_turns > 1 or len(traj.turn_rewards) > 1
             resp, mask, lps_all, rew = traj.finalize(per_token_reward=per_token)
             if (not self.use_conversation_multi_turn and stop_reason != "length" and resp
@@ -252,8 +308,13 @@ class SkyRLGymGenerator(GeneratorInterface):
                 mask.append(1)
                 if lps_all is not None:
                     lps_all.append(0.0)
-                if isinstance(rew, list):
-                    rew = rew[:-1] + [0.0, rew[-1]] if rew else [0.0]
+                if isinstance(rew, list) and traj.turn_rewards:
+                    # the last turn's reward moves from its last sampled token onto the token that now ends the response
+                    r_last, idx = traj.turn_rewards[-1]
+                    rew = rew + [0.0]
+                    if idx < len(rew) - 1:
+                        rew[idx] -= r_last
+                        rew[-1] += r_last
             if self.generator_cfg.zero_reward_on_non_stop and stop_reason != "stop":
                 rew = [0.0] * len(rew) if isinstance(rew, list) else 0.0
             return TrajectoryOutput(traj.prompt_ids, resp, rew, mask, stop_reason, lps_all, env_metrics,
@@ -278,8 +339,8 @@ class SkyRLGymGenerator(GeneratorInterface):
             if prompt_token_ids is not None:
                 ids.append(list(prompt_token_ids[i]))
             else:
-                ids.append(list(self.tokenizer.apply_chat_template(chat, add_generation_prompt=True, tokenize=True,
-                                                                   **self.generator_cfg.chat_template_kwargs)))
+                ids.append(chat_template_ids(self.tokenizer, chat, add_generation_prompt=True,
+                                             **self.generator_cfg.chat_template_kwargs))
         sp = dict(sampling_params) if sampling_params is not None else self._default_sampling_params()
         sp.setdefault("max_generate_length", max_tokens)
         per_req = [e.get("sampling_params") for e in (env_extras or [])] if env_extras else None

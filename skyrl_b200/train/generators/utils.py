@@ -9,6 +9,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 import numpy as np
 
 from .base import BatchMetadata, GeneratorInput, GeneratorOutput, TrajectoryID
+from ...utils.tokenizer import chat_template_ids
 
 
 def _traj_reward(r) -> float:
@@ -160,21 +161,44 @@ def merge_stepwise_output(out: GeneratorOutput) -> GeneratorOutput:
 
 # ChatML without the "You are a helpful assistant" default that some tokenizers insert when no system message is given:
 # what a multi-turn rollout wants, because the conversation is tokenised piece by piece.
+def _chatml(assistant_body: str) -> str:
+    """ChatML template text.  ``assistant_body`` renders an assistant message's content; it sits, with the end-of-turn
+    token, inside a ``generation`` block, so that ``apply_chat_template(..., return_assistant_tokens_mask=True)`` marks
+    exactly the tokens the model produced (not the role header, not the newline after the end-of-turn token)."""
+    return ("{%- for message in messages -%}"
+            "{{- '<|im_start|>' + message['role'] + '\n' -}}"
+            "{%- if message['role'] == 'assistant' -%}"
+            "{%- generation -%}" + assistant_body + "{{- '<|im_end|>' -}}{%- endgeneration -%}"
+            "{%- else -%}"
+            "{{- message['content'] + '<|im_end|>' -}}"
+            "{%- endif -%}"
+            "{{- '\n' -}}"
+            "{%- endfor -%}"
+            "{%- if add_generation_prompt -%}{{- '<|im_start|>assistant\n' -}}{%- endif -%}")
+
+
+_KEEP = "{{- message['content'] -}}"
+# earlier assistant turns lose their <think>...</think> part (what Qwen3's own template does); the last message, if it
+# is the assistant's, keeps it
+_DROP_OLD_THINKING = ("{%- set body = message['content'] -%}"
+                      "{%- if '</think>' in body and not (loop.last and message['role'] == 'assistant') -%}"
+                      "{%- set body = body.split('</think>')[-1].lstrip('\n') -%}"
+                      "{%- endif -%}"
+                      "{{- body -}}")
+_KEEP_REASONING_FIELD = ("{%- if message.get('reasoning_content') -%}"
+                         "{{- '<think>\n' + message['reasoning_content'] + '\n</think>\n\n' -}}{%- endif -%}"
+                         "{{- message['content'] -}}")
+
+# ChatML without the "You are a helpful assistant" default that some tokenizers insert when no system message is given:
+# what a multi-turn rollout wants, because the conversation is tokenised piece by piece.  Unlike the reference's
+# templates of the same names these also honour ``add_generation_prompt``.
 CUSTOM_CHAT_TEMPLATES: Dict[str, str] = {
-    "chatml_no_default_system": (
-        "{% for message in messages %}"
-        "{{ '<|im_start|>' + message['role'] + '\\n' + message['content'] + '<|im_end|>' + '\\n' }}"
-        "{% endfor %}"
-        "{% if add_generation_prompt %}{{ '<|im_start|>assistant\\n' }}{% endif %}"),
+    "chatml_no_default_system": _chatml(_KEEP),
     # keeps earlier turns' <think> blocks (Qwen3's own template drops them, which changes the tokens of past turns)
-    "chatml_keep_thinking": (
-        "{% for message in messages %}"
-        "{{ '<|im_start|>' + message['role'] + '\\n' }}"
-        "{% if message['role'] == 'assistant' and message.get('reasoning_content') %}"
-        "{{ '<think>\\n' + message['reasoning_content'] + '\\n</think>\\n\\n' }}{% endif %}"
-        "{{ message['content'] + '<|im_end|>' + '\\n' }}"
-        "{% endfor %}"
-        "{% if add_generation_prompt %}{{ '<|im_start|>assistant\\n' }}{% endif %}"),
+    "chatml_keep_thinking": _chatml(_KEEP_REASONING_FIELD),
+    # the names the reference registers (generators/utils.py:66-102)
+    "qwen3_with_thinking": _chatml(_KEEP),
+    "qwen3_without_thinking": _chatml(_DROP_OLD_THINKING),
 }
 
 
@@ -211,8 +235,8 @@ def get_generation_prompt_ids(tokenizer, tokenizer_kwargs: Optional[Dict[str, An
     if "enable_thinking" in kw:
         raise ValueError("enable_thinking changes the generation prompt per call: use encode_messages_subset")
     probe = [{"role": "user", "content": ""}]
-    plain = list(tokenizer.apply_chat_template(probe, tokenize=True, **kw))
-    opened = list(tokenizer.apply_chat_template(probe, add_generation_prompt=True, tokenize=True, **kw))
+    plain = chat_template_ids(tokenizer, probe, **kw)
+    opened = chat_template_ids(tokenizer, probe, add_generation_prompt=True, **kw)
     return opened[len(plain):]
 
 
@@ -227,9 +251,8 @@ def encode_messages_subset(messages: List[Dict[str, Any]], tokenizer, tokenizer_
     if not messages:
         raise ValueError("messages must not be empty")
     kw = dict(tokenizer_kwargs or {})
-    base = list(tokenizer.apply_chat_template(_BASE_CONVERSATION, add_generation_prompt=False, tokenize=True, **kw))
-    full = list(tokenizer.apply_chat_template(_BASE_CONVERSATION + list(messages), add_generation_prompt=False,
-                                              tokenize=True, **kw))
+    base = chat_template_ids(tokenizer, _BASE_CONVERSATION, add_generation_prompt=False, **kw)
+    full = chat_template_ids(tokenizer, _BASE_CONVERSATION + list(messages), add_generation_prompt=False, **kw)
     if full[: len(base)] != base:
         raise ValueError("the chat template does not extend a conversation by appending tokens; give a custom template")
     return full[len(base):]

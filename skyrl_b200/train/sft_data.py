@@ -22,6 +22,7 @@ import numpy as np
 import torch
 
 from .batch import TrainingInputBatch, pad_training_input_batch
+from ..utils.tokenizer import chat_template_ids
 
 TRAIN_ON_LAST = "last_assistant_message"
 TRAIN_ON_ALL = "all_assistant_messages"
@@ -87,10 +88,7 @@ def normalize_chat_messages(messages: Sequence[dict]) -> List[dict]:
 # ----------------------------------------------------------------------------- tokenization
 def _template(tokenizer, msgs, add_generation_prompt: bool, tools=None) -> List[int]:
     kw = {"tools": tools} if tools else {}
-    ids = tokenizer.apply_chat_template(msgs, add_generation_prompt=add_generation_prompt, tokenize=True, **kw)
-    if isinstance(ids, dict):
-        ids = ids["input_ids"]
-    return list(ids)
+    return chat_template_ids(tokenizer, msgs, add_generation_prompt=add_generation_prompt, **kw)
 
 
 def tokenize_chat_example(example: dict, tokenizer, max_length: Optional[int] = None, messages_key: str = "messages",

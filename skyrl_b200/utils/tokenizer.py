@@ -71,6 +71,18 @@ class SyntheticTokenizer:
             json.dump({"vocab_size": self.vocab_size}, f)
 
 
+def chat_template_ids(tokenizer, messages, **kw) -> List[int]:
+    """Token ids of ``messages`` through the tokenizer's chat template, as a plain list.  Newer ``transformers``
+    releases return a ``BatchEncoding`` from ``apply_chat_template(tokenize=True)`` unless told otherwise; every caller
+    here wants the ids."""
+    kw["tokenize"] = True
+    kw["return_dict"] = False
+    out = tokenizer.apply_chat_template(messages, **kw)
+    if hasattr(out, "keys"):
+        out = out["input_ids"]
+    return list(out)
+
+
 def get_tokenizer(name_or_path: Optional[str], vocab_size: Optional[int] = None, **kw):
     """HF tokenizer (left padding, pad = eos if missing) or ``SyntheticTokenizer`` for ``synthetic[-N]`` names."""
     if name_or_path is None or str(name_or_path).startswith("synthetic"):
