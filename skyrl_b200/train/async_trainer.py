@@ -65,7 +65,7 @@ class OneStepOffPPOTrainer(PPOTrainer):
         await buffer.put(None)
 
     def _train_on(self, out, uids) -> Dict[str, float]:
-        out = self.postprocess_generator_output(out, uids)
+        out, uids = self.postprocess_generator_output(out, uids)
         batch = self.convert_to_training_input(out, uids)
         batch = self.fwd_logprobs_values_reward(batch)
         if self.cfg.trainer.algorithm.use_kl_in_reward and self.ref is not None:

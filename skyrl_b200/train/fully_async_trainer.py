@@ -208,7 +208,7 @@ class FullyAsyncPPOTrainer(PPOTrainer):
             groups = [g for p in parts for g in p]
         out = concatenate_generator_outputs([g["out"] for g in groups])
         uids = [u for g in groups for u in g["uids"]]
-        out = self.postprocess_generator_output(out, uids)
+        out, uids = self.postprocess_generator_output(out, uids)
         batch = self.convert_to_training_input(out, uids)
         stale = [self.staleness.current_step - g["step_at_submit"] for g in groups]
         self.all_metrics.update({"async/staleness_mean": float(np.mean(stale)), "async/staleness_max": float(max(stale)),

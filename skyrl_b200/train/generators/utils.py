@@ -333,3 +333,77 @@ def slice_generator_output(out: GeneratorOutput, start: int, end: int) -> Genera
     for k, v in out.items():
         res[k] = v[start:end] if isinstance(v, list) and len(v) == n else v
     return res  # type: ignore[return-value]
+
+
+# ----------------------------------------------------------------------------- output validation
+class GeneratorOutputError(ValueError):
+    """A generator handed the trainer rows that do not fit together."""
+
+
+def _tid(t) -> str:
+    return t.to_string() if hasattr(t, "to_string") else str(t)
+
+
+def validate_generator_output(num_prompts: int, out: GeneratorOutput, step_wise: bool = False) -> List[str]:
+    """Checks a ``GeneratorOutput`` before it is turned into tensors, so that a hand-written generator fails with a
+    message about its own output instead of an index error three layers down.  Returns warnings (conditions that are
+    legal but usually a bug, e.g. every token masked out).  Reference: trainer_utils.py:672-826 (same rules).
+
+    * at least one response; one response per prompt unless ``step_wise`` (then one per step);
+    * every per-row field (``prompt_token_ids, loss_masks, rewards, stop_reasons, rollout_logprobs, trajectory_ids,
+      is_last_step, rollout_expert_indices``), when given, has one entry per response;
+    * per row: ``len(loss_mask) == len(response)``, token-level rewards and rollout log-probs have the response's
+      length; rewards are all floats or all lists of floats, never a mixture;
+    * step-wise: ``is_last_step`` and ``trajectory_ids`` present, the last row ends a trajectory, the rows of a
+      trajectory are adjacent, and ``is_last_step`` is true exactly where the trajectory id changes."""
+    resp = out.get("response_ids")
+    if not resp:
+        raise GeneratorOutputError("the generator returned no responses")
+    n = len(resp)
+    if not step_wise and n != num_prompts:
+        raise GeneratorOutputError(f"{num_prompts} prompts but {n} responses")
+    for key in ("prompt_token_ids", "loss_masks", "rewards", "stop_reasons", "rollout_logprobs", "trajectory_ids",
+                "is_last_step", "rollout_expert_indices"):
+        v = out.get(key)
+        if isinstance(v, (list, tuple)) and len(v) != n:
+            raise GeneratorOutputError(f"'{key}' has {len(v)} entries for {n} responses")
+    masks, rewards, lps = out.get("loss_masks"), out.get("rewards"), out.get("rollout_logprobs")
+    if masks is None or rewards is None:
+        raise GeneratorOutputError("'loss_masks' and 'rewards' are required")
+    kinds = {isinstance(r, (list, tuple)) for r in rewards}
+    if len(kinds) > 1:
+        raise GeneratorOutputError("rewards mix per-trajectory floats and per-token lists")
+    per_token = kinds == {True}
+    for i, r in enumerate(resp):
+        if len(masks[i]) != len(r):
+            raise GeneratorOutputError(f"row {i}: loss mask has {len(masks[i])} entries for {len(r)} response tokens")
+        if per_token:
+            if len(rewards[i]) != len(r):
+                raise GeneratorOutputError(f"row {i}: {len(rewards[i])} token rewards for {len(r)} response tokens")
+            if not all(isinstance(x, (int, float)) and not isinstance(x, bool) for x in rewards[i]):
+                raise GeneratorOutputError(f"row {i}: token rewards must be numbers")
+        elif not isinstance(rewards[i], (int, float)) or isinstance(rewards[i], bool):
+            raise GeneratorOutputError(f"row {i}: reward must be a number or a list of numbers, got {type(rewards[i]).__name__}")
+        if lps and lps[i] is not None and len(lps[i]) != len(r):
+            raise GeneratorOutputError(f"row {i}: {len(lps[i])} rollout log-probs for {len(r)} response tokens")
+    warnings: List[str] = []
+    if not any(any(m) for m in masks):
+        warnings.append("every response token is masked out of the loss: the policy loss will be 0/0")
+    if step_wise:
+        last, tids = out.get("is_last_step"), out.get("trajectory_ids")
+        if last is None or tids is None:
+            raise GeneratorOutputError("step-wise output needs 'is_last_step' and 'trajectory_ids'")
+        if last[-1] is not True:
+            raise GeneratorOutputError("the last row must be the final step of a trajectory (is_last_step[-1] is not True)")
+        keys = [_tid(t) for t in tids]
+        done: set = set()
+        for i, k in enumerate(keys):
+            if i and k != keys[i - 1]:
+                done.add(keys[i - 1])
+                if last[i - 1] is not True:
+                    raise GeneratorOutputError(f"trajectory '{keys[i - 1]}' ends at row {i - 1} but is_last_step[{i - 1}] is not True")
+            elif i and last[i - 1] is True:
+                raise GeneratorOutputError(f"is_last_step[{i - 1}] is True but trajectory '{k}' continues at row {i}")
+            if k in done:
+                raise GeneratorOutputError(f"rows of trajectory '{k}' are not adjacent (it reappears at row {i})")
+    return warnings

@@ -37,7 +37,8 @@ from .batch import TrainingInputBatch, pad_training_input_batch
 from .dataset import PromptDataset, StatefulBatchIterator
 from .generators.base import GeneratorInput, GeneratorInterface, GeneratorOutput
 from .generators.skyrl_gym_generator import SkyRLGymGenerator
-from .generators.utils import compute_pass_at_n, get_metrics_from_generator_output, prepare_generator_input
+from .generators.utils import (compute_pass_at_n, get_metrics_from_generator_output, prepare_generator_input,
+                               validate_generator_output)
 from .preprocess import (compute_prompt_boundaries, compute_prompt_mini_batch_boundaries,
                          convert_prompts_responses_to_batch_tensors)
 from .tracking import Tracking
@@ -176,13 +177,37 @@ class PPOTrainer:
                 raise ValueError(f"generator output field '{key}' has {len(out[key])} rows, expected {n}")
         return out
 
-    def postprocess_generator_output(self, out: GeneratorOutput, uids: List[str]) -> GeneratorOutput:
-        """Scalar rewards -> last response token; metrics; optional zero-variance filter
-        (reference: trainer.py:1013-1121)."""
-        a = self.cfg.trainer.algorithm
-        rewards = out["rewards"]
+    def postprocess_generator_output(self, out: GeneratorOutput, uids: List[str],
+                                     metrics_generator_output: Optional[GeneratorOutput] = None,
+                                     metrics_uids: Optional[List[str]] = None):
+        """Scalar rewards -> last response token; reward metrics; optional merge of step-wise rows; optional
+        zero-variance filter.  Returns ``(output, uids)`` -- ``uids`` gets shorter when step-wise rows are merged
+        (reference: trainer.py:1013-1121).
+
+        The reward metrics are computed over ``metrics_generator_output`` / ``metrics_uids`` when given (a superset of
+        the trained rows: the fully-async trainer passes the groups it dropped so that the numbers stay comparable),
+        and, for step-wise rollouts, over the last step of every trajectory only."""
+        a, g = self.cfg.trainer.algorithm, self.cfg.generator
+        m_out = metrics_generator_output if metrics_generator_output is not None else out
+        m_uids = list(metrics_uids if metrics_uids is not None else uids)
+        m_rewards = list(m_out["rewards"])
+        if g.step_wise_trajectories and m_out.get("is_last_step") is not None:
+            keep = [i for i, last in enumerate(m_out["is_last_step"]) if last]
+            m_rewards, m_uids = [m_rewards[i] for i in keep], [m_uids[i] for i in keep]
+        mm = get_metrics_from_generator_output({"rewards": m_rewards}, m_uids)
+        m = {"reward/avg_raw_reward": mm["avg_score"], f"reward/avg_pass_at_{g.n_samples_per_prompt}": mm["pass_at_n"],
+             "reward/mean_positive_reward": mm["mean_positive_reward"]}
+        if g.merge_stepwise_output:
+            if not g.step_wise_trajectories:
+                raise ValueError("generator.merge_stepwise_output needs generator.step_wise_trajectories=true")
+            from .generators.utils import merge_stepwise_output
+
+            before = len(out["response_ids"])
+            out = merge_stepwise_output(out)
+            m["generate/num_seq_before_merge"], m["generate/num_seq_after_merge"] = float(before), float(len(out["response_ids"]))
+            uids = [t.instance_id for t in out["trajectory_ids"]]
         per_token: List[List[float]] = []
-        for r, resp in zip(rewards, out["response_ids"]):
+        for r, resp in zip(out["rewards"], out["response_ids"]):
             if isinstance(r, (list, tuple)):
                 per_token.append([float(x) for x in r])
             else:
@@ -190,11 +215,8 @@ class PPOTrainer:
                 if row:
                     row[-1] = float(r)
                 per_token.append(row)
-        scores = np.array([sum(r) for r in per_token], dtype=np.float64)
-        m = {"reward/avg_raw_reward": float(scores.mean()) if len(scores) else 0.0,
-             "reward/avg_pass_at_{}".format(self.cfg.generator.n_samples_per_prompt): compute_pass_at_n(per_token, uids),
-             "reward/mean_positive_reward": float(scores[scores > 0].mean()) if (scores > 0).any() else 0.0}
         if a.zero_variance_filter:
+            scores = np.array([sum(r) for r in per_token], dtype=np.float64)
             groups: Dict[str, List[int]] = {}
             for i, u in enumerate(uids):
                 groups.setdefault(u, []).append(i)
@@ -207,12 +229,12 @@ class PPOTrainer:
                         masks[i] = [0] * len(masks[i])
                     dropped += 1
             out["loss_masks"] = masks
-            m["reward/zero_variance_groups"] = float(dropped)
+            m["reward/zero_variance_groups"] = m["reward/num_zero_variance_filtered"] = float(dropped)
         out["rewards"] = per_token
         self.all_metrics.update(m)
         if out.get("rollout_metrics"):
             self.all_metrics.update(out["rollout_metrics"])
-        return out
+        return out, uids
 
     def convert_to_training_input(self, out: GeneratorOutput, uids: List[str]) -> TrainingInputBatch:
         pad_id = self.tokenizer.pad_token_id if self.tokenizer is not None and self.tokenizer.pad_token_id is not None else 0
@@ -543,6 +565,8 @@ class PPOTrainer:
                                                   cfg.environment.env_class, "train", self.global_step, prompt_token_ids)
         with Timer("generate", self.all_timings):
             out = await self.generate(gen_input)
+        for w in validate_generator_output(len(gen_input["prompts"]), out, bool(cfg.generator.step_wise_trajectories)):
+            logger.warning("generator output: %s", w)
         if self.policy is not None and self.policy.tp_size > 1:
             out, uids = self._gather_over_tp(out, uids)
         if out.get("trajectory_ids") and len(out["response_ids"]) != len(uids):
@@ -555,7 +579,7 @@ class PPOTrainer:
                 m["trainer/keep_sampling"] = 1.0
                 return m
         with Timer("postprocess", self.all_timings):
-            out = self.postprocess_generator_output(out, uids)
+            out, uids = self.postprocess_generator_output(out, uids)
             self._log_examples(out, uids)
             batch = self.convert_to_training_input(out, uids)
         with Timer("fwd_logprobs_values_reward", self.all_timings):

@@ -112,3 +112,65 @@ def test_custom_chat_templates_by_name_and_file(tmp_path):
     txt = jinja2.Template(plain).render(messages=[{"role": "user", "content": "hi"}], add_generation_prompt=True)
     assert txt == "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
     assert "generation" in t and {"qwen3_with_thinking", "qwen3_without_thinking"} <= set(U.CUSTOM_CHAT_TEMPLATES)
+
+
+def _valid_out():
+    return {"prompt_token_ids": [[1, 2, 3, 4], [5, 6], [7, 8, 9]], "response_ids": [[10, 11, 12], [13, 14], [15]],
+            "rewards": [[0.5, 0.6, 0.7], [0.8, 0.9], [1.0]], "loss_masks": [[1, 1, 0], [1, 1], [0]],
+            "stop_reasons": ["stop", "length", "stop"], "rollout_metrics": {}, "rollout_logprobs": None}
+
+
+def test_validate_generator_output_accepts_well_formed_rows_and_names_the_broken_one():
+    V, E = U.validate_generator_output, U.GeneratorOutputError
+    out = _valid_out()
+    assert V(3, out) == []
+    out["rewards"] = [0.5, 0.6, 0.7]
+    assert V(3, out) == []
+    out["rollout_logprobs"] = [[0.11, 0.12, 0.13], [0.2, 0.3], [0.4]]
+    assert V(3, out) == []
+    with pytest.raises(E, match="no responses"):
+        V(1, dict(_valid_out(), response_ids=[]))
+    with pytest.raises(E, match="3 prompts but 2 responses"):
+        V(3, {k: (v[:2] if isinstance(v, list) else v) for k, v in _valid_out().items()})
+    with pytest.raises(E, match="'stop_reasons' has 2 entries"):
+        V(3, dict(_valid_out(), stop_reasons=["stop", "stop"]))
+    with pytest.raises(E, match="row 1: loss mask has 3 entries for 2"):
+        V(3, dict(_valid_out(), loss_masks=[[1, 1, 0], [1, 1, 1], [0]]))
+    with pytest.raises(E, match="row 0: 2 token rewards for 3"):
+        V(3, dict(_valid_out(), rewards=[[0.5, 0.6], [0.8, 0.9], [1.0]]))
+    with pytest.raises(E, match="row 2: 2 rollout log-probs for 1"):
+        V(3, dict(_valid_out(), rollout_logprobs=[[0.1, 0.2, 0.3], [0.2, 0.3], [0.4, 0.5]]))
+    with pytest.raises(E, match="mix"):
+        V(3, dict(_valid_out(), rewards=[[0.5, 0.6, 0.7], 0.8, [1.0]]))
+    with pytest.raises(E, match="must be a number"):
+        V(3, dict(_valid_out(), rewards=["a", 0.1, 0.2]))
+    with pytest.raises(E, match="token rewards must be numbers"):
+        V(3, dict(_valid_out(), rewards=[[0.5, None, 0.7], [0.8, 0.9], [1.0]]))
+    assert "masked out" in V(3, dict(_valid_out(), loss_masks=[[0, 0, 0], [0, 0], [0]]))[0]
+
+
+def test_validate_step_wise_rows():
+    from skyrl_b200.train.generators.base import TrajectoryID
+
+    V, E = U.validate_generator_output, U.GeneratorOutputError
+
+    def rows(tids, last):
+        n = len(tids)
+        return {"prompt_token_ids": [[1]] * n, "response_ids": [[2]] * n, "rewards": [[0.0]] * n, "loss_masks": [[1]] * n,
+                "stop_reasons": ["stop"] * n, "rollout_logprobs": None,
+                "trajectory_ids": [TrajectoryID(t, 0) for t in tids], "is_last_step": last}
+
+    assert V(2, rows(["a", "a", "b"], [False, True, True]), step_wise=True) == []  # the prompt count is not compared
+    assert V(2, rows(["a", "b"], [True, True]), step_wise=True) == []
+    with pytest.raises(E, match="needs 'is_last_step'"):
+        V(1, dict(rows(["a"], [True]), is_last_step=None), step_wise=True)
+    with pytest.raises(E, match="'is_last_step' has 2 entries"):
+        V(1, rows(["a", "a", "b"], [True, True]), step_wise=True)
+    with pytest.raises(E, match="last row"):
+        V(1, rows(["a", "a"], [False, False]), step_wise=True)
+    with pytest.raises(E, match="not adjacent"):
+        V(1, rows(["a", "b", "a"], [True, True, True]), step_wise=True)
+    with pytest.raises(E, match="ends at row 0"):
+        V(1, rows(["a", "b"], [False, True]), step_wise=True)
+    with pytest.raises(E, match="continues at row 1"):
+        V(1, rows(["a", "a"], [True, True]), step_wise=True)

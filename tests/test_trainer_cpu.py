@@ -140,3 +140,45 @@ def test_example_logging_trajectory_samples_and_batch_dump(tmp_path, caplog):
     tr2 = PPOTrainer(sized, tokenizer=SyntheticTokenizer(1024))
     tr2.build_models()
     assert tuple(tr2.engine.cfg.graph_batch_sizes) == (4, 8, 16)
+
+
+def test_postprocess_rewards_metrics_superset_and_step_wise_merge(tmp_path):
+    from skyrl_b200.train.generators.base import TrajectoryID
+
+    pdist.reset_env_for_tests()
+    tr = PPOTrainer(_cfg(tmp_path, ["generator.n_samples_per_prompt=1"]), tokenizer=SyntheticTokenizer(1024))
+    go = {"prompt_token_ids": [[1, 2], [3, 4]], "response_ids": [[5, 6], [7, 8, 9]], "rewards": [1.0, 0.5],
+          "loss_masks": [[1, 1], [1, 1, 1]], "stop_reasons": ["stop", "stop"], "rollout_metrics": None}
+    out, uids = tr.postprocess_generator_output(go, ["u1", "u2"])
+    assert uids == ["u1", "u2"] and out["rewards"] == [[0.0, 1.0], [0.0, 0.0, 0.5]]
+    tok = {"prompt_token_ids": [[1, 2]], "response_ids": [[3, 4, 5]], "rewards": [[0.1, 0.2, 0.3]],
+           "loss_masks": [[1, 1, 1]], "stop_reasons": ["stop"], "rollout_metrics": None}
+    assert tr.postprocess_generator_output(tok, ["u1"])[0]["rewards"] == [[0.1, 0.2, 0.3]]
+    # reward metrics over a superset of the trained rows (groups the fully-async trainer dropped)
+    kept = {"prompt_token_ids": [[1]], "response_ids": [[3, 4]], "rewards": [1.0], "loss_masks": [[1, 1]],
+            "stop_reasons": ["stop"], "rollout_metrics": None}
+    union = {"prompt_token_ids": [[1]] * 3, "response_ids": [[3, 4], [5], [6]], "rewards": [1.0, 0.0, 0.0],
+             "loss_masks": [[1, 1], [1], [1]], "stop_reasons": ["stop"] * 3, "rollout_metrics": None}
+    tr.all_metrics = {}
+    out, _ = tr.postprocess_generator_output(kept, ["u1"], metrics_generator_output=union, metrics_uids=["u1", "u2", "u3"])
+    assert out["rewards"] == [[0.0, 1.0]]
+    assert tr.all_metrics["reward/avg_raw_reward"] == pytest.approx(1 / 3)
+    assert tr.all_metrics["reward/avg_pass_at_1"] == pytest.approx(1 / 3)
+
+    # step-wise rows: metrics from the last step of each trajectory; merging folds steps whose prompt extends the
+    # previous step's tokens and shortens the uid list with them
+    pdist.reset_env_for_tests()
+    sw = PPOTrainer(_cfg(tmp_path, ["generator.n_samples_per_prompt=1", "generator.batched=false",
+                                    "generator.step_wise_trajectories=true", "generator.merge_stepwise_output=true"]),
+                    tokenizer=SyntheticTokenizer(1024))
+    t = [TrajectoryID("a", 0), TrajectoryID("a", 0), TrajectoryID("b", 0)]
+    steps = {"prompt_token_ids": [[1, 2], [1, 2, 5, 6, 40], [3]], "response_ids": [[5, 6], [7], [9, 9]],
+             "rewards": [[0.0, 0.25], [1.0], [0.0, 0.0]], "loss_masks": [[1, 1], [1], [1, 1]],
+             "stop_reasons": ["stop"] * 3, "rollout_metrics": None, "rollout_logprobs": None, "trajectory_ids": t,
+             "is_last_step": [False, True, True]}
+    sw.all_metrics = {}
+    out, uids = sw.postprocess_generator_output(steps, ["a", "a", "b"])
+    assert uids == ["a", "b"] and out["response_ids"] == [[5, 6, 40, 7], [9, 9]]
+    assert out["loss_masks"] == [[1, 1, 0, 1], [1, 1]] and out["rewards"] == [[0.0, 0.25, 0.0, 1.0], [0.0, 0.0]]
+    assert sw.all_metrics["generate/num_seq_before_merge"] == 3 and sw.all_metrics["generate/num_seq_after_merge"] == 2
+    assert sw.all_metrics["reward/avg_raw_reward"] == pytest.approx(0.5)  # last steps only: (1.0 + 0.0) / 2
