@@ -15,6 +15,7 @@ from __future__ import annotations
 import copy
 import dataclasses
 import os
+import re
 import typing
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Union
@@ -26,14 +27,20 @@ class ConfigError(ValueError):
     pass
 
 
+_FLOAT_RE = re.compile(r"^[+-]?\d+(\.\d*)?[eE][+-]?\d+$")
+
+
 def _parse_scalar(text: str) -> Any:
     """Parse the right-hand side of ``key=value`` with YAML scalar/list/dict rules."""
     if text == "":
         return ""
     try:
-        return yaml.safe_load(text)
+        val = yaml.safe_load(text)
     except yaml.YAMLError:
         return text
+    if isinstance(val, str) and _FLOAT_RE.match(text.strip()):
+        return float(val)  # YAML 1.1 wants a dot in the mantissa ("1.0e-5"); people write "1e-5" (unquoted)
+    return val
 
 
 def _is_optional(tp) -> bool:
@@ -143,8 +150,16 @@ class BaseConfig:
 # ----------------------------------------------------------------------------- data / model
 @dataclass
 class DataLoaderConfig(BaseConfig):
-    num_workers: Optional[int] = None
+    num_workers: Optional[int] = None  # None: 8
     persistent_workers: bool = False
+
+    def __post_init__(self):
+        if self.num_workers is not None and self.num_workers < 0:
+            raise ConfigError("data.dataloader.num_workers must be None or >= 0")
+        if self.num_workers is None:
+            self.num_workers = 8
+        if self.persistent_workers and self.num_workers == 0:
+            raise ConfigError("data.dataloader.persistent_workers requires num_workers > 0")
 
 
 @dataclass
@@ -236,6 +251,33 @@ class TorchProfilerConfig(BaseConfig):
     with_flops: bool = False
     with_modules: bool = False
     export_type: str = "chrome_trace"
+
+    def validate(self) -> None:
+        """Nothing is checked while the profiler is off.  When on: at least one rank, a local ``save_path``, activities
+        out of cpu / cuda (any case), ``export_type`` chrome_trace or stacks (stacks needs ``with_stack``), a schedule
+        with non-negative phases and at least one active step (reference: config.py ``TorchProfilerConfig.validate``)."""
+        if not self.enable:
+            return
+        if not self.ranks:
+            raise ConfigError("torch_profiler_config.ranks must be non-empty when the profiler is enabled")
+        if not self.save_path:
+            raise ConfigError("torch_profiler_config.save_path must be set when the profiler is enabled")
+        if "://" in str(self.save_path):
+            raise ConfigError(f"torch_profiler_config.save_path must be a local path, got '{self.save_path}'")
+        if not self.activities:
+            raise ConfigError("torch_profiler_config.activities must be non-empty")
+        bad = [a for a in self.activities if str(a).lower() not in ("cpu", "cuda")]
+        if bad:
+            raise ConfigError(f"torch_profiler_config.activities: unknown {bad}; choose from ['cpu', 'cuda']")
+        if self.export_type not in ("chrome_trace", "stacks"):
+            raise ConfigError(f"torch_profiler_config.export_type must be 'chrome_trace' or 'stacks', got '{self.export_type}'")
+        if self.export_type == "stacks" and not self.with_stack:
+            raise ConfigError("torch_profiler_config.export_type='stacks' needs with_stack=true")
+        for name in ("skip_first", "wait", "warmup", "repeat"):
+            if getattr(self, name) < 0:
+                raise ConfigError(f"torch_profiler_config.{name} must be >= 0")
+        if self.active < 1:
+            raise ConfigError("torch_profiler_config.active must be >= 1")
 
 
 @dataclass
@@ -706,16 +748,25 @@ class SkyRLTrainConfig(BaseConfig):
     }
 
     @classmethod
-    def from_cli_overrides(cls, args: List[str]) -> "SkyRLTrainConfig":
-        """Build a config from ``a.b.c=value`` strings (reference: config.py:1765-1891)."""
+    def from_cli_overrides(cls, args: Union[List[str], Dict[str, Any]]) -> "SkyRLTrainConfig":
+        """Build a config from ``a.b.c=value`` strings, or from a ``{"a.b.c": value}`` mapping whose values keep their
+        Python types (``None`` stays ``None``, ``"1e-5"`` stays a string) instead of going through the text parser
+        (reference: config.py:1765-1891)."""
         tree: Dict[str, Any] = {}
-        for raw in args:
-            if raw.startswith("+"):
-                raise ConfigError(f"'+' overrides are not supported: {raw!r}; every key must already exist")
-            if "=" not in raw:
-                raise ConfigError(f"override {raw!r} is not of the form key=value")
-            key, val = raw.split("=", 1)
-            key = key.strip().lstrip("-")
+        typed = isinstance(args, dict)
+        for raw in (args.items() if typed else args):
+            if typed:
+                key, val = raw
+                raw = f"{key}=..."
+            else:
+                if "=" not in raw:
+                    if raw.startswith("+"):
+                        raise ConfigError(f"'+' overrides are not supported: {raw!r}; every key must already exist")
+                    raise ConfigError(f"override {raw!r} is not of the form key=value")
+                key, val = raw.split("=", 1)
+            if str(key).startswith("+"):
+                raise ConfigError(f"'+' overrides are not supported: {key!r}; every key must already exist")
+            key = str(key).strip().lstrip("-")
             key = cls._RENAMED.get(key, key)
             parts = key.split(".")
             node = tree
@@ -724,7 +775,7 @@ class SkyRLTrainConfig(BaseConfig):
                 if not isinstance(nxt, dict):
                     raise ConfigError(f"override {raw!r} conflicts with an earlier scalar value for '{p}'")
                 node = nxt
-            parsed = _parse_scalar(val)
+            parsed = val if typed else _parse_scalar(val)
             if parts[-1] == "strategy" and parsed == "fsdp2":
                 parsed = "fsdp"
             node[parts[-1]] = parsed
@@ -741,6 +792,29 @@ class SkyRLTrainConfig(BaseConfig):
         base["trainer"]["ref"]["model"]["path"] = None
         merged = _deep_merge(base, tree, path="")
         return cls.from_dict(merged)
+
+
+def overrides_dict_to_dotlist(overrides: Dict[str, Any]) -> List[str]:
+    """``{"a.b": value}`` -> ``["a.b=<text>"]`` such that parsing the text gives the value back: ``None`` -> ``null``,
+    booleans lower-case, containers and strings as JSON (so ``"1e-5"`` or ``"null"`` stay strings); anything JSON
+    cannot express falls back to ``str`` (reference: config.py, same name)."""
+    import json
+
+    out = []
+    for k, v in overrides.items():
+        if v is None:
+            text = "null"
+        elif isinstance(v, bool):
+            text = "true" if v else "false"
+        elif isinstance(v, (int, float)):
+            text = repr(v)
+        else:
+            try:
+                text = json.dumps(v)
+            except (TypeError, ValueError):
+                text = str(v)
+        out.append(f"{k}={text}")
+    return out
 
 
 def _deep_merge(base: Dict[str, Any], over: Dict[str, Any], path: str) -> Dict[str, Any]:

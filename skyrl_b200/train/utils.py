@@ -149,6 +149,10 @@ def validate_cfg(cfg, world_size: int = 1) -> None:
         raise ValueError(f"invalid dynamic_sampling.type '{a.dynamic_sampling.type}'")
     if g.step_wise_trajectories and g.batched:
         raise ValueError("step_wise_trajectories requires the non-batched generator")
+    for node in (t.policy, t.critic, t.ref):
+        prof = getattr(node, "torch_profiler_config", None)
+        if prof is not None:
+            prof.validate()
     if t.policy.megatron_config.moe_enable_routing_replay and not g.inference_engine.enable_return_routed_experts:
         raise ValueError("rollout router replay needs generator.inference_engine.enable_return_routed_experts=true")
     if g.inference_engine.enable_return_routed_experts and g.step_wise_trajectories:

@@ -20,9 +20,9 @@ class Profiler:
         if not self.active:
             return
         acts = []
-        if "cpu" in cfg.activities:
+        if "cpu" in [str(a).lower() for a in cfg.activities]:
             acts.append(torch.profiler.ProfilerActivity.CPU)
-        if "cuda" in cfg.activities and torch.cuda.is_available():
+        if "cuda" in [str(a).lower() for a in cfg.activities] and torch.cuda.is_available():
             acts.append(torch.profiler.ProfilerActivity.CUDA)
         self.save_path = cfg.save_path or "/tmp/skyrl-profiles"
         os.makedirs(self.save_path, exist_ok=True)

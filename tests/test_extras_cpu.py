@@ -246,3 +246,53 @@ def test_mtp_draft_head_trains_beside_the_policy_without_touching_it(tmp_path):
     w2.load_checkpoint(str(tmp_path / "ck"))
     for a, b in zip(w.mtp_head.parameters(), w2.mtp_head.parameters()):
         assert torch.equal(a, b)
+
+
+def test_config_overrides_from_dict_dotlist_round_trip_and_dataloader_rules():
+    from skyrl_b200.config.config import ConfigError, SkyRLTrainConfig, _parse_scalar, overrides_dict_to_dotlist
+
+    c = SkyRLTrainConfig.from_cli_overrides({"trainer.seed": 7, "generator.inference_engine.served_model_name": None,
+                                             "trainer.run_name": "1e-5", "trainer.policy.optimizer_config.lr": 3e-6})
+    assert c.trainer.seed == 7 and c.generator.inference_engine.served_model_name is None
+    assert c.trainer.run_name == "1e-5" and c.trainer.policy.optimizer_config.lr == 3e-6
+    for v in (None, True, False, 3, 1e-5, 2.5, "1e-5", "null", "true", [1, 2], {"a": [1, None]}, "plain text"):
+        text = overrides_dict_to_dotlist({"k": v})[0]
+        assert text.startswith("k=") and _parse_scalar(text[2:]) == v and type(_parse_scalar(text[2:])) is type(v)
+    assert overrides_dict_to_dotlist({"a": 1, "b": 2}) == ["a=1", "b=2"]
+    assert overrides_dict_to_dotlist({"k": object})[0].startswith("k=<class")
+    assert _parse_scalar("1e-6") == 1e-6 and _parse_scalar("'1e-6'") == "1e-6"
+    d = SkyRLTrainConfig.from_cli_overrides([]).data.dataloader
+    assert d.num_workers == 8 and d.persistent_workers is False
+    assert SkyRLTrainConfig.from_cli_overrides(["data.dataloader.num_workers=0"]).data.dataloader.num_workers == 0
+    assert SkyRLTrainConfig.from_cli_overrides(["data.dataloader.persistent_workers=true"]).data.dataloader.num_workers == 8
+    with pytest.raises(ConfigError, match="persistent_workers requires num_workers > 0"):
+        SkyRLTrainConfig.from_cli_overrides(["data.dataloader.num_workers=0", "data.dataloader.persistent_workers=true"])
+    with pytest.raises(ConfigError, match="num_workers must be None or >= 0"):
+        SkyRLTrainConfig.from_cli_overrides(["data.dataloader.num_workers=-1"])
+    for bad in (["+trainer.seed=1"], {"+trainer.seed": 1}):
+        with pytest.raises(ConfigError, match="not supported"):
+            SkyRLTrainConfig.from_cli_overrides(bad)
+
+
+def test_torch_profiler_config_validation():
+    from skyrl_b200.config.config import SkyRLTrainConfig, TorchProfilerConfig
+    from skyrl_b200.train.utils import validate_cfg
+
+    TorchProfilerConfig(enable=False, export_type="bogus", activities=["gpu"], ranks=[], active=0, save_path=None).validate()
+    ok = lambda **kw: TorchProfilerConfig(enable=True, **{"save_path": "/tmp/prof", **kw})  # noqa: E731
+    ok().validate()
+    ok(activities=["CPU", "CUDA"]).validate()
+    ok(export_type="stacks", with_stack=True).validate()
+    for kw, match in (({"ranks": []}, "ranks.*non-empty"), ({"save_path": None}, "save_path.*must be set"),
+                      ({"save_path": ""}, "save_path.*must be set"), ({"save_path": "s3://b/run"}, "save_path.*local path"),
+                      ({"activities": ["cpu", "gpu"]}, "activities"), ({"activities": []}, "activities.*non-empty"),
+                      ({"export_type": "bogus"}, "export_type"), ({"export_type": "stacks", "with_stack": False}, "with_stack"),
+                      ({"skip_first": -1}, "skip_first"), ({"active": 0}, "active")):
+        with pytest.raises(ValueError, match=match):
+            ok(**kw).validate()
+    cfg = SkyRLTrainConfig.from_cli_overrides(["trainer.policy.torch_profiler_config.enable=true",
+                                               "trainer.policy.torch_profiler_config.save_path=/tmp/prof",
+                                               "trainer.policy.torch_profiler_config.export_type=bogus",
+                                               "trainer.policy.model.path=tiny-llama"])
+    with pytest.raises(ValueError, match="export_type"):
+        validate_cfg(cfg)
