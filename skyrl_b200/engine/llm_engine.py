@@ -62,6 +62,11 @@ class SamplingParams:
         known = {f for f in cls.__dataclass_fields__}
         d.pop("repetition_penalty", None)
         d.pop("n", None)
+        pl = d.get("prompt_logprobs")
+        if pl is not None and not isinstance(pl, bool):
+            d["prompt_logprobs"] = True  # engines that count alternatives use 0 for "the prompt token's own log-prob"
+        elif pl is None:
+            d.pop("prompt_logprobs", None)
         return cls(**{k: v for k, v in d.items() if k in known})
 
     @property

@@ -179,6 +179,87 @@ class RemoteInferenceClient(InferenceEngineInterface):
     async def load_lora_adapter(self, lora_path: str, lora_name: str = "skyrl-lora") -> None:
         await self._fanout("/skyrl/v1/load_lora_adapter", {"lora_path": lora_path, "lora_name": lora_name})
 
+    async def unload_lora_adapter(self, lora_name: str = "skyrl-lora") -> None:
+        await self._fanout("/skyrl/v1/unload_lora_adapter", {"lora_name": lora_name})
+
+    async def pause_generation(self, clear_cache: bool = False) -> None:
+        """Freeze in-flight requests with their KV cache (``pause`` in keep mode)."""
+        await self.pause("keep", clear_cache)
+
+    async def resume_generation(self) -> None:
+        await self.resume()
+
+    # ------------------------------------------------------------------ Tinker-style sampling and text utilities
+    async def sample(self, request_payload: Dict[str, Any]) -> Dict[str, Any]:
+        """``{"json": {prompt, num_samples, sampling_params, include_prompt_logprobs | prompt_logprobs, session_id}}``
+        -> ``{"type": "sample", "sequences": [{tokens, logprobs, stop_reason}], "prompt_logprobs",
+        "topk_prompt_logprobs"}`` through ``/inference/v1/generate`` (reference: remote_inference_client.py:620-728).
+        ``prompt`` is a Tinker model input (``{"chunks": [{"tokens": [...]}]}``) or a plain id list; one request per
+        sample.  The engine scores each prompt token only, so ``topk_prompt_logprobs`` is always ``None``."""
+        body = dict(request_payload.get("json", request_payload))
+        session_id = body.get("session_id") or request_payload.get("session_id")
+        prompt = body.get("prompt") or {}
+        if isinstance(prompt, dict):
+            ids: List[int] = []
+            for ch in prompt.get("chunks", []):
+                if "tokens" not in ch:
+                    raise ValueError("sample: only token chunks are supported by this client")
+                ids.extend(int(t) for t in ch["tokens"])
+        else:
+            ids = [int(t) for t in prompt]
+        n = max(1, int(body.get("num_samples", 1)))
+        tp = body.get("sampling_params") or {}
+        want_plp = bool(body.get("include_prompt_logprobs", body.get("prompt_logprobs", False)))
+        sp: Dict[str, Any] = {}
+        for src, dst in (("max_tokens", "max_tokens"), ("temperature", "temperature"), ("top_p", "top_p"),
+                         ("top_k", "top_k"), ("stop", "stop"), ("seed", "seed")):
+            if tp.get(src) is not None:
+                sp[dst] = tp[src]
+        if want_plp:
+            sp["prompt_logprobs"] = True
+        await self._http()
+        headers = {"X-Session-ID": str(session_id)} if session_id else None
+        url = self._target(session_id) + "/inference/v1/generate"
+
+        async def one():
+            async with self._sem:
+                return await self._post(url, {"sampling_params": sp, "model": body.get("model", self.model_name),
+                                              "token_ids": ids}, headers=headers)
+
+        res = await asyncio.gather(*[one() for _ in range(n)])
+        seqs, plp = [], None
+        for r in res:
+            c = r["choices"][0]
+            lp = c.get("logprobs")
+            seqs.append({"tokens": list(c["token_ids"]), "logprobs": [x["logprob"] for x in lp["content"]] if lp else None,
+                         "stop_reason": c.get("finish_reason")})
+            if want_plp and plp is None:
+                plp = c.get("prompt_logprobs")
+        return {"type": "sample", "sequences": seqs, "prompt_logprobs": plp, "topk_prompt_logprobs": None}
+
+    async def tokenize(self, request_payload: Dict[str, Any]) -> Dict[str, Any]:
+        return await self._post(self.server_urls[0] + "/tokenize", request_payload.get("json", request_payload))
+
+    async def detokenize(self, request_payload: Dict[str, Any]) -> Dict[str, Any]:
+        return await self._post(self.server_urls[0] + "/detokenize", request_payload.get("json", request_payload))
+
+    async def render_chat_completion(self, request_payload: Dict[str, Any]) -> Dict[str, Any]:
+        """Messages -> token ids without generating (the ``/tokenize`` endpoint applied to ``messages``)."""
+        body = dict(request_payload.get("json", request_payload))
+        out = await self._post(self.server_urls[0] + "/tokenize", {"messages": body["messages"],
+                                                                  "add_generation_prompt": body.get("add_generation_prompt", True)})
+        return {"token_ids": out.get("tokens", out.get("token_ids")), "count": out.get("count")}
+
+    async def __aenter__(self) -> "RemoteInferenceClient":
+        await self._http()
+        return self
+
+    async def __aexit__(self, exc_type, exc, tb) -> None:
+        await self.teardown()
+
+    async def aclose(self) -> None:
+        await self.teardown()
+
     async def finish_session(self, session_id: Any) -> None:
         try:
             await self._post(self._target(session_id) + "/finish_session", {"session_id": str(session_id)}, retries=0)

@@ -76,6 +76,9 @@ def build_app(client: LocalInferenceClient, model_name: str = "policy", weight_l
             choices.append({"index": i, "token_ids": out["response_ids"][i], "finish_reason": out["stop_reasons"][i],
                             "text": out["responses"][i],
                             "logprobs": {"content": [{"logprob": lp} for lp in lps]} if lps else None})
+            plps = out.get("prompt_logprobs")
+            if plps and plps[i] is not None:
+                choices[-1]["prompt_logprobs"] = [None if x is None else float(x) for x in plps[i]]
             routes = (out.get("rollout_expert_indices") or [None] * len(ids))[i]
             if routes is not None:  # mixture-of-experts engine started with return_routed_experts
                 choices[-1]["routed_experts"] = wire.pack_routed_experts(routes)

@@ -137,3 +137,40 @@ def test_trainer_syncs_weights_to_stand_alone_server(tmp_path, transport):
         assert eng.weight_version >= 2 and not eng.paused
     finally:
         srv.stop()
+
+
+def test_sample_tokenize_render_and_context_manager_over_http():
+    srv, eng = _server()
+    try:
+        async def run():
+            async with RemoteInferenceClient([srv.url], tokenizer=SyntheticTokenizer(97)) as rc:
+                res = await rc.sample({"json": {"prompt": {"chunks": [{"tokens": [5, 6]}, {"tokens": [7]}]}, "num_samples": 3,
+                                                "sampling_params": {"max_tokens": 4, "temperature": 0.0},
+                                                "include_prompt_logprobs": True, "topk_prompt_logprobs": 2},
+                                       "session_id": "s"})
+                tok = await rc.tokenize({"json": {"prompt": "5 6 7"}})
+                detok = await rc.detokenize({"json": {"tokens": [5, 6, 7]}})
+                rendered = await rc.render_chat_completion({"json": {"messages": [{"role": "user", "content": "5 6"}]}})
+                await rc.pause_generation()
+                paused = eng.paused
+                await rc.resume_generation()
+                return res, tok, detok, rendered, paused, eng.paused
+
+        res, tok, detok, rendered, paused, resumed = asyncio.run(run())
+        assert res["type"] == "sample" and len(res["sequences"]) == 3 and res["topk_prompt_logprobs"] is None
+        from skyrl_b200.engine.llm_engine import SamplingParams
+
+        ref = eng.generate([[5, 6, 7]], SamplingParams(max_tokens=4, temperature=0.0, prompt_logprobs=True))[0]
+        for s in res["sequences"]:
+            assert s["tokens"] == ref.token_ids and s["stop_reason"] == "length" and len(s["logprobs"]) == 4
+        # the first prompt token has no predecessor, the others carry the model's log-prob of the token itself
+        plp = res["prompt_logprobs"]
+        assert plp[0] is None and plp[1:] == pytest.approx(ref.prompt_logprobs[1:], abs=1e-5)
+        assert tok == {"tokens": [5, 6, 7], "count": 3} and detok["prompt"] == "5 6 7"
+        assert rendered["token_ids"] == [2, 5, 6, 1, 3] and rendered["count"] == 5
+        assert paused and not resumed
+        # vLLM-style "0 alternatives" still asks for the prompt tokens' own log-probs
+        assert SamplingParams.from_dict({"prompt_logprobs": 0}).prompt_logprobs is True
+        assert SamplingParams.from_dict({"prompt_logprobs": None}).prompt_logprobs is False
+    finally:
+        srv.stop()
