@@ -180,17 +180,26 @@ class PipelinedCausalLM:
     """What a worker needs from a pipeline-parallel policy: per-token log-probs of a packed batch on *every* rank of
     the pipeline group, with a backward pass that runs through all stages.
 
-    One micro-batch travels through the stages at a time (activations forward, gradients backward, both by send/recv);
-    the last stage scores the tokens and broadcasts the log-probs, so the loss code runs identically on every stage.
-    On the last stage the log-probs are attached to the graph; on the others a zero-valued relay term carries the
-    autograd edge, so that calling ``backward()`` on the (identical) loss of every rank drives the whole chain.
-    Micro-batches are not interleaved by this wrapper: ``pipeline_forward_backward`` is the overlapped schedule for
-    callers that own the micro-batch loop."""
+    Activations travel forward and gradients backward by send / recv; the last stage scores the tokens and broadcasts
+    the log-probs, so the loss code runs identically on every stage.  On the last stage the log-probs are attached to
+    the graph; on the others a zero-valued relay term carries the autograd edge, so that calling ``backward()`` on the
+    (identical) loss of every rank drives the whole chain.  ``pred_logprobs`` moves one micro-batch through all stages;
+    the worker's training and scoring loops use the ``_begin`` / ``_end`` halves to keep all stages busy."""
 
     def __init__(self, stage: PipelineStage):
         self.stage = stage
 
     def pred_logprobs(self, ids, pos, cu, max_seqlen, pred_index, targets, temp: float = 1.0, with_entropy: bool = False):
+        return self.pred_logprobs_end(self.pred_logprobs_begin(ids, pos, cu, max_seqlen, pred_index, targets, temp,
+                                                               with_entropy))
+
+    def pred_logprobs_begin(self, ids, pos, cu, max_seqlen, pred_index, targets, temp: float = 1.0,
+                            with_entropy: bool = False):
+        """First half of ``pred_logprobs``: receive the previous stage's activations, run this stage, hand the result
+        to the next stage (the last stage scores the tokens instead).  Nothing here waits for a later stage, so a
+        caller that begins all its micro-batches before ending any keeps every stage busy: while stage ``s`` runs
+        micro-batch ``k``, stage ``s - 1`` already runs ``k + 1`` (all-forward / all-backward schedule; the backward
+        passes overlap the same way because each micro-batch's gradient hand-over is its own send / receive pair)."""
         st = self.stage
         g = st.group
         H = st.args.hidden_size
@@ -206,9 +215,23 @@ class PipelinedCausalLM:
                 x_in.register_hook(lambda gr: dist.send(gr.contiguous(), dst=prev, group=g))
         out = st.stage_forward(ids, pos, cu, max_seqlen, x_in)
         n = pred_index.numel()
-        last = _peer(g, st.pp_size - 1)
         if st.is_last:
             lp, ent = st.token_logprobs(out[pred_index], targets, temp, with_entropy=with_entropy)
+            return {"n": n, "lp": lp, "ent": ent}
+        relay = _RelayFn.apply(out, _peer(g, st.pp_rank + 1), g) if grad_on else None
+        if not grad_on:
+            dist.send(out.detach().contiguous(), dst=_peer(g, st.pp_rank + 1), group=g)
+        return {"n": n, "relay": relay}
+
+    def pred_logprobs_end(self, h):
+        """Second half: the last stage's log-probs (and entropies) reach every stage of the pipeline."""
+        st = self.stage
+        g = st.group
+        dev = st.flat_params.device
+        n = h["n"]
+        last = _peer(g, st.pp_size - 1)
+        if st.is_last:
+            lp, ent = h["lp"], h["ent"]
             # row 0: log-probs, row 1: entropies; the extra column says whether entropies were computed at all
             pack = torch.zeros((2, n + 1), device=dev, dtype=torch.float32)
             pack[0, :n] = lp.detach().float()
@@ -217,15 +240,12 @@ class PipelinedCausalLM:
                 pack[1, n] = 1.0
             dist.broadcast(pack, src=last, group=g)
             return lp, ent
-        relay = _RelayFn.apply(out, _peer(g, st.pp_rank + 1), g) if grad_on else None
-        if not grad_on:
-            dist.send(out.detach().contiguous(), dst=_peer(g, st.pp_rank + 1), group=g)
         pack = torch.empty((2, n + 1), device=dev, dtype=torch.float32)
         dist.broadcast(pack, src=last, group=g)
         lp = pack[0, :n]
         ent = pack[1, :n] if bool(pack[1, n] > 0) else None
-        if relay is not None:
-            lp = lp + relay  # numerically a no-op; gives this rank's loss a path into its stage
+        if h.get("relay") is not None:
+            lp = lp + h["relay"]  # numerically a no-op; gives this rank's loss a path into its stage
         return lp, ent
 
     @torch.no_grad()

@@ -607,6 +607,18 @@ class ModelWorker:
         each keep their own data)."""
         return self.mesh.tp_size if (self.mesh is not None and not getattr(self, "expert_parallel", False)) else 1
 
+    def _pipe_begin_all(self, batch: TrainingInputBatch, groups, n_mb: int, temp: float, with_entropy: bool = False):
+        """Pipeline parallelism: pack every micro-batch and start it through the stages before any result is collected,
+        so that stage ``s`` works on micro-batch ``k`` while stage ``s - 1`` works on ``k + 1``.  Returns the
+        ``(rows, packed view, handle)`` triples the loops finish with ``self.pipe.pred_logprobs_end``."""
+        started = []
+        for k in range(n_mb):
+            rows = groups[k] if k < len(groups) else groups[-1]
+            pv = self._pack(batch, rows)
+            started.append((rows, pv, self.pipe.pred_logprobs_begin(pv.ids, pv.positions, pv.cu_seqlens, pv.max_seqlen,
+                                                                    pv.pred_index, pv.targets, temp, with_entropy)))
+        return started
+
     def _pred_logprobs(self, pv: PackedView, temp: float, with_entropy: bool = False):
         """Log-probs (and entropies) of the packed batch's prediction positions, ``[n_pred]`` each."""
         if self.mesh is None:
@@ -679,8 +691,16 @@ class ModelWorker:
         temp = float(self.cfg.algorithm.temperature or 1.0)
         was_ckpt = self.model.gradient_checkpointing
         self.model.gradient_checkpointing = False
+        started = self._pipe_begin_all(batch, groups, n_mb, temp) if (self.pipe is not None and self.role != "critic") else None
         for k in range(n_mb):
             rows = groups[k] if k < len(groups) else groups[-1]  # padding micro-batch keeps collectives aligned
+            if started is not None:
+                _, pv, handle = started[k]
+                started[k] = None
+                vals = self.pipe.pred_logprobs_end(handle)[0]
+                if k < len(groups):
+                    out[torch.tensor(rows, dtype=torch.long)] = _lib.to_host(pv.scatter_to_grid(vals.float()))
+                continue
             pv = self._pack(batch, rows)
             if self.role == "critic":
                 if pv.pred_index.numel() == 0 and self.mesh is None:
@@ -971,14 +991,22 @@ class PolicyWorker(ModelWorker):
         per_row_logprobs = torch.zeros((B, R), dtype=torch.float32) if return_per_token_outputs else None
         overlap = (step_follows and self.mesh is None and type(self.model) is CausalLM and self.optimizer is not None
                    and self.optimizer.can_overlap_reduce and getattr(self.cfg.b200, "overlap_grad_reduce", True))
+        # pipeline parallelism: all forwards first, then loss + backward per micro-batch (activations of a stage stay
+        # alive for all micro-batches, which gradient checkpointing keeps to the layer inputs)
+        started = self._pipe_begin_all(batch, groups, n_mb, temp, use_ent) if self.pipe is not None else None
         for k in range(n_mb):
             real = k < len(groups)
             rows = groups[k] if real else groups[-1]
-            pv = self._pack(batch, rows)
-            if overlap and k == n_mb - 1:
-                buckets = self._layer_buckets()
-                self.model.layer_grads_ready = lambda i, b=buckets: self.optimizer.reduce_bucket(*b[i])
-            lp, ent = self._pred_logprobs(pv, temp, with_entropy=use_ent)
+            if started is not None:
+                _, pv, handle = started[k]
+                started[k] = None
+                lp, ent = self.pipe.pred_logprobs_end(handle)
+            else:
+                pv = self._pack(batch, rows)
+                if overlap and k == n_mb - 1:
+                    buckets = self._layer_buckets()
+                    self.model.layer_grads_ready = lambda i, b=buckets: self.optimizer.reduce_bucket(*b[i])
+                lp, ent = self._pred_logprobs(pv, temp, with_entropy=use_ent)
             weight = len(rows) / max(1, B * world)  # KL / entropy terms: mean over the global mini-batch
             g = lambda key: self._rows_to_device(batch.get(key), rows)  # noqa: E731
             mask_g, adv_g = g("loss_mask"), g("advantages")

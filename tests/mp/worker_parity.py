@@ -20,7 +20,7 @@ from skyrl_b200.parallel.sharded_optimizer import ShardedAdamW  # noqa: E402
 from skyrl_b200.train.batch import TrainingInputBatch  # noqa: E402
 from skyrl_b200.workers.worker import PolicyWorker  # noqa: E402
 
-MODELS = {"tp": "tiny-llama", "sp": "tiny-llama", "pp": "tiny-llama", "ep": "tiny-moe", "tpv": "tiny-llama",
+MODELS = {"tp": "tiny-llama", "sp": "tiny-llama", "pp": "tiny-llama", "pp_mb1": "tiny-llama", "ep": "tiny-moe", "tpv": "tiny-llama",
           "critic_tp": "tiny-llama", "critic_sp": "tiny-llama", "cp": "tiny-llama", "cp_megatron": "tiny-llama",
           "critic_cp": "tiny-llama"}
 
@@ -31,6 +31,9 @@ def cfg_for(mode: str, model: str):
         "sp": ["trainer.policy.sequence_parallel_size=2"],
         "ep": ["trainer.strategy=megatron", "trainer.policy.megatron_config.expert_model_parallel_size=2"],
         "pp": ["trainer.strategy=megatron", "trainer.policy.megatron_config.pipeline_model_parallel_size=2"],
+        # four micro-batches in flight through the two stages
+        "pp_mb1": ["trainer.strategy=megatron", "trainer.policy.megatron_config.pipeline_model_parallel_size=2",
+                   "trainer.micro_train_batch_size_per_gpu=1", "trainer.gradient_checkpointing=true"],
         "tpv": ["trainer.strategy=megatron", "trainer.policy.megatron_config.tensor_model_parallel_size=2",
                 "trainer.b200.vocab_parallel_lm_head=true"],
         "critic_tp": ["trainer.strategy=megatron", "trainer.policy.megatron_config.tensor_model_parallel_size=2"],

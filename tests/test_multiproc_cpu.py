@@ -53,7 +53,7 @@ import pytest  # noqa: E402
 
 @pytest.mark.parametrize("mode,port", [("tp", 29641), ("sp", 29642), ("ep", 29643), ("pp", 29644), ("tpv", 29648),
                                        ("critic_tp", 29649), ("critic_sp", 29650), ("cp", 29663),
-                                       ("cp_megatron", 29664), ("critic_cp", 29665)])
+                                       ("cp_megatron", 29664), ("critic_cp", 29665), ("pp_mb1", 29671)])
 def test_gloo_worker_update_matches_single_rank(mode, port):
     """forward_backward + optim_step through the worker under each model-parallel strategy: full parameters equal a
     single-rank update on the same data, group replicas are bit-identical, one optimizer step per RL step."""
