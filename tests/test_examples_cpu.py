@@ -115,3 +115,79 @@ def test_example_scripts_run_on_cpu(tmp_path, script, extra):
         assert p.returncode != 0 and "max_sample_batches" in tail, tail
     else:
         assert p.returncode == 0, tail
+
+
+def test_full_context_and_collective_check_examples_run(tmp_path):
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", HOME=str(tmp_path), MODEL="tiny-llama",
+               NGPU="1")
+    p = subprocess.run(["bash", os.path.join(ROOT, "examples/train_scripts/full_context/run_full_ctx.sh"),
+                        "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "generator.n_samples_per_prompt=2",
+                        "trainer.max_prompt_length=24", "generator.sampling_params.max_generate_length=8",
+                        "trainer.max_tokens_per_microbatch=512", "trainer.bf16=false", "num_dummy_steps=2",
+                        f"trainer.ckpt_path={tmp_path}/ckpt", f"trainer.export_path={tmp_path}/export"],
+                       cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert "step 2/2: 8 rows x 40 tokens" in p.stdout
+    p = subprocess.run(["python", "-m", "torch.distributed.run", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29689", os.path.join(ROOT, "examples/train_scripts/nccl_test.py"), "--mib", "0.5",
+                        "--iters", "2"], cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "GLOO_TEST_OK" in p.stdout, p.stdout[-1500:] + p.stderr[-1500:]
+
+
+def test_tinker_grpo_client_and_session_routing_examples(tmp_path):
+    import asyncio
+
+    import torch
+    from fastapi.testclient import TestClient
+
+    from examples.tinker.ppo.grpo_client import grpo_datum, run
+    from examples.tinker.session_based_routing.route_by_session import converse
+    from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from skyrl_b200.inference.local_client import LocalInferenceClient
+    from skyrl_b200.inference.remote_client import RemoteInferenceClient
+    from skyrl_b200.inference.server import ServerThread, build_app as build_server
+    from skyrl_b200.models.decoder import CausalLM, PRESETS
+    from skyrl_b200.parallel.dist import get_env
+    from skyrl_b200.tinker.api import build_app
+    from skyrl_b200.tinker.backend import SkyRLTrainBackend
+    from skyrl_b200.utils.tokenizer import SyntheticTokenizer
+
+    d = grpo_datum([1, 2, 3], [4, 5], [-0.1, -0.2], 0.5)
+    li = d["loss_fn_inputs"]
+    assert d["model_input"]["chunks"][0]["tokens"] == [1, 2, 3, 4] and li["target_tokens"]["data"] == [2, 3, 4, 5]
+    assert li["weights"]["data"] == [0.0, 0.0, 1.0, 1.0] and li["advantages"]["data"] == [0.0, 0.0, 0.5, 0.5]
+
+    tok = SyntheticTokenizer(1024)
+    ov = {"trainer.bf16": "false", "generator.inference_engine.max_num_seqs": 16, "trainer.max_prompt_length": 32,
+          "generator.sampling_params.max_generate_length": 16, "generator.inference_engine.enforce_eager": "true",
+          "generator.inference_engine.engine_init_kwargs": "{num_blocks: 128}", "trainer.gradient_checkpointing": "false"}
+    app = build_app(lambda base: SkyRLTrainBackend(base, ov, env=get_env(), tokenizer=tok, checkpoints_base=str(tmp_path)),
+                    supported_models=["tiny-llama"], poll_interval=0.01)
+    with TestClient(app) as c:
+        def call(path, body):
+            r = c.post(path, json=body)
+            assert r.status_code == 200, (path, r.text)
+            return r.json()
+
+        rewards = run(call, "tiny-llama", [[10 + i, 20, 30] for i in range(3)], steps=2, group=4, max_tokens=8, lr=1e-4)
+    assert len(rewards) == 2 and all(0.0 <= r <= 1.0 for r in rewards)
+
+    # two servers: every conversation stays on one of them and its turns extend one another
+    servers, engines = [], []
+    for s in range(2):
+        torch.manual_seed(s)
+        eng = LLMEngine(CausalLM(PRESETS["tiny-llama"], dtype=torch.float32, device="cpu", seed=s),
+                        EngineConfig(block_size=16, max_num_seqs=8, max_model_len=128, num_blocks=64, enforce_eager=True))
+        engines.append(eng)
+        servers.append(ServerThread(build_server(LocalInferenceClient([eng], tok))).start())
+    try:
+        async def go():
+            async with RemoteInferenceClient([s.url for s in servers]) as rc:
+                return await converse(rc, sessions=4, turns=2, max_tokens=4)
+
+        out = asyncio.run(go())
+        assert sorted(out) == [f"conv-{i}" for i in range(4)] and all(len(t) == 2 for t in out.values())
+        assert sum(e.stats["prefill_calls"] > 0 for e in engines) >= 1
+    finally:
+        for s in servers:
+            s.stop()
