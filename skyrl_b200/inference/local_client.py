@@ -58,6 +58,24 @@ class LocalInferenceClient(InferenceEngineInterface):
         self._next = 0
         self.weight_version = 0
 
+    def get_endpoint_url(self) -> str:
+        """Base URL of an OpenAI-compatible HTTP server in front of these engines (``/v1/chat/completions``,
+        ``/v1/completions``, ``/inference/v1/generate``, ``/tokenize`` ...), started in a background thread of this
+        process on first use.  It lets agent scaffolds that only speak the OpenAI protocol roll out against the
+        colocated engines (reference: ``RemoteInferenceClient.get_endpoint_url``; there the servers always exist).
+        All requests must then come through the endpoint: the engine loop lives in the server's event loop."""
+        if getattr(self, "_endpoint", None) is None:
+            from .server import ServerThread, build_app
+
+            self._endpoint = ServerThread(build_app(self, model_name=self.model_name)).start()
+        return self._endpoint.url
+
+    def close_endpoint(self) -> None:
+        ep = getattr(self, "_endpoint", None)
+        if ep is not None:
+            ep.stop()
+            self._endpoint = None
+
     # ------------------------------------------------------------------ data plane
     def _route(self, session_id: Any) -> int:
         if session_id is None or len(self.engines) == 1:

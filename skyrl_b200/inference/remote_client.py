@@ -179,6 +179,10 @@ class RemoteInferenceClient(InferenceEngineInterface):
     async def load_lora_adapter(self, lora_path: str, lora_name: str = "skyrl-lora") -> None:
         await self._fanout("/skyrl/v1/load_lora_adapter", {"lora_path": lora_path, "lora_name": lora_name})
 
+    def get_endpoint_url(self) -> str:
+        """Where OpenAI-protocol clients should connect: the router if there is one, else the first server."""
+        return self.router_url or self.server_urls[0]
+
     async def unload_lora_adapter(self, lora_name: str = "skyrl-lora") -> None:
         await self._fanout("/skyrl/v1/unload_lora_adapter", {"lora_name": lora_name})
 

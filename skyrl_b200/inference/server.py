@@ -103,8 +103,9 @@ def build_app(client: LocalInferenceClient, model_name: str = "policy", weight_l
         r = await _generate({"token_ids": ids, "sampling_params": sp}, request.headers.get("X-Session-ID"))
         c = r["choices"][0]
         return {"id": r["id"], "object": "text_completion", "model": model_name,
-                "choices": [{"index": 0, "text": c["text"], "finish_reason": c["finish_reason"], "token_ids": c["token_ids"]}],
-                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(c["token_ids"])}}
+                "choices": [{"index": 0, "text": c["text"], "finish_reason": c["finish_reason"], "token_ids": c["token_ids"],
+                             "logprobs": c["logprobs"]}],
+                "prompt_token_ids": list(ids), "usage": {"prompt_tokens": len(ids), "completion_tokens": len(c["token_ids"])}}
 
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
@@ -117,7 +118,7 @@ def build_app(client: LocalInferenceClient, model_name: str = "policy", weight_l
         return {"id": r["id"], "object": "chat.completion", "model": model_name,
                 "choices": [{"index": 0, "message": {"role": "assistant", "content": c["text"]},
                              "finish_reason": c["finish_reason"], "token_ids": c["token_ids"], "logprobs": c["logprobs"]}],
-                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(c["token_ids"])}}
+                "prompt_token_ids": list(ids), "usage": {"prompt_tokens": len(ids), "completion_tokens": len(c["token_ids"])}}
 
     @app.post("/tokenize")
     async def tokenize(request: Request):

@@ -87,6 +87,8 @@ _TINY_RL = ["trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "t
     ("examples/on_policy_distillation/run_on_policy_distill.sh", []),
     ("examples/turn_level_rewards/run_gsm8k_multi_turn.sh", ["generator.max_input_length=256"]),
     ("examples/gptoss/run_attention_sinks_grpo.sh", ["trainer.policy.model.path=tiny-sinks"]),
+    # rollouts through the OpenAI-compatible endpoint of the colocated engine
+    ("examples/train_integrations/openai_chat/run_chat_grpo.sh", []),
 ])
 def test_example_scripts_run_on_cpu(tmp_path, script, extra):
     """The launch scripts themselves are executed (bash, the launcher, the entry point) on a tiny preset and data."""

@@ -316,3 +316,87 @@ def test_chat_layout_with_a_real_fast_tokenizer_appends_observations_token_for_t
     assert trained == "A<|im_end|>B<|im_end|>"
     # the second request is the first one plus exactly the response tokens so far
     assert client.prompts[1] == tok.decode(out.prompt_ids) + "A<|im_end|>\n<|im_start|>user\nobs<|im_end|>\n<|im_start|>assistant\n"
+
+
+def _scripted_chat_server(tok, turns, rewrite_after=None):
+    """An OpenAI-style endpoint that answers the k-th request with ``turns[k]`` (token ids), templating the prompt the
+    way the real server does."""
+    from fastapi import FastAPI, Request
+
+    from skyrl_b200.inference.server import ServerThread
+    from skyrl_b200.utils.tokenizer import chat_template_ids
+
+    app, seen = FastAPI(), []
+
+    @app.post("/v1/chat/completions")
+    async def chat(request: Request):
+        body = await request.json()
+        seen.append(body)
+        ids = turns[min(len(seen) - 1, len(turns) - 1)]
+        msgs = body["messages"]
+        if rewrite_after is not None and len(seen) > rewrite_after:
+            msgs = [{"role": "system", "content": "999"}] + msgs
+        p = chat_template_ids(tok, msgs, add_generation_prompt=True)
+        return {"choices": [{"index": 0, "message": {"role": "assistant", "content": tok.decode(ids)},
+                             "finish_reason": "stop" if ids[-1] == EOS else "length", "token_ids": ids,
+                             "logprobs": {"content": [{"logprob": -0.25 * (j + 1)} for j in range(len(ids))]}}],
+                "prompt_token_ids": p}
+
+    return ServerThread(app).start(), seen
+
+
+class _Endpoint:
+    def __init__(self, url):
+        self.url = url
+
+    def get_endpoint_url(self):
+        return self.url
+
+
+def test_chat_protocol_generator_builds_trajectories_from_the_tokens_the_endpoint_reports():
+    from examples.train_integrations.openai_chat.chat_generator import ChatCompletionsGenerator
+
+    tok = SyntheticTokenizer(1024)
+    ScriptedEnv.script, ScriptedEnv.seen = [("7 8", 0.3, False), (None, 1.0, True)], []
+    srv, seen = _scripted_chat_server(tok, [[10, 11, EOS], [20, 21, EOS]])
+    try:
+        g = ChatCompletionsGenerator(_cfg(), None, _Endpoint(srv.url), tok)
+        out = asyncio.run(g.generate({"prompts": [PROMPT], "env_classes": ["scripted"], "env_extras": [{}],
+                                      "sampling_params": {"temperature": 0.0, "max_generate_length": 8}}))
+    finally:
+        srv.stop()
+    obs = [2, 7, 8, EOS, 3]
+    assert out["prompt_token_ids"] == [PROMPT_IDS]
+    assert out["response_ids"] == [[10, 11, EOS] + obs + [20, 21, EOS]]
+    assert out["loss_masks"] == [[1, 1, 1] + [0] * 5 + [1, 1, 1]]
+    assert out["rewards"][0] == pytest.approx([0, 0, 0.3] + [0] * 5 + [0, 0, 1.0])
+    assert out["rollout_logprobs"][0] == pytest.approx([-0.25, -0.5, -0.75] + [0.0] * 5 + [-0.25, -0.5, -0.75])
+    assert seen[0]["temperature"] == 0.0 and seen[0]["max_tokens"] == 8 and seen[0]["logprobs"] is True
+    assert [m["role"] for m in seen[1]["messages"]] == ["user", "assistant", "user"]
+
+    # a turn cut by the length limit has no end-of-turn token of its own: the one the template adds shows up between the
+    # turns and is context, not a sampled action
+    ScriptedEnv.script, ScriptedEnv.seen = [("7 8", 0.3, False), (None, 1.0, True)], []
+    srv, seen = _scripted_chat_server(tok, [[10, 11], [20, 21, EOS]])
+    try:
+        g = ChatCompletionsGenerator(_cfg(), None, _Endpoint(srv.url), tok)
+        out = asyncio.run(g.generate({"prompts": [PROMPT], "env_classes": ["scripted"], "env_extras": [{}]}))
+    finally:
+        srv.stop()
+    assert out["response_ids"] == [[10, 11, EOS] + obs + [20, 21, EOS]]
+    assert out["loss_masks"] == [[1, 1, 0] + [0] * 5 + [1, 1, 1]]
+    assert out["rollout_logprobs"][0] == pytest.approx([-0.25, -0.5, 0.0] + [0.0] * 5 + [-0.25, -0.5, -0.75])
+
+    # a scaffold that rewrites history (here: a system message appears from the second request on) breaks the token
+    # chain: the trajectory is rebuilt from the messages and gives up its log-probs
+    ScriptedEnv.script, ScriptedEnv.seen = [("7 8", 0.3, False), (None, 1.0, True)], []
+    srv, seen = _scripted_chat_server(tok, [[10, 11, EOS], [20, 21, EOS]], rewrite_after=1)
+    try:
+        g = ChatCompletionsGenerator(_cfg(), None, _Endpoint(srv.url), tok)
+        out = asyncio.run(g.generate({"prompts": [PROMPT], "env_classes": ["scripted"], "env_extras": [{}]}))
+    finally:
+        srv.stop()
+    assert out["rollout_logprobs"] is None
+    assert out["response_ids"] == [[3, 10, 11, EOS, 2, 7, 8, EOS, 3, 20, 21, EOS]]
+    assert out["loss_masks"] == [[0, 1, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1]]
+    assert out["rewards"] == [pytest.approx(1.3)]  # one scalar for the rebuilt trajectory
