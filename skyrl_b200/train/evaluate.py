@@ -44,9 +44,19 @@ async def evaluate(eval_dataset, generator, cfg, global_step: int, tokenizer=Non
         out = await generator.generate(gi)
         if first_out is None:
             first_out = (out, uids)
+        srcs = [(it.get("env_extras") or {}).get("data_source") for it in chunk for _ in range(g.eval_n_samples_per_prompt)]
+        if g.step_wise_trajectories and out.get("is_last_step") is not None:
+            # one row per step: score every trajectory by its last step (where the reward sits) and take the prompt uid
+            # and data source from the trajectory id (reference: evaluate.py:178-300, ``evaluate_step_wise``)
+            src_of = {t.instance_id: s for t, s in zip(gi["trajectory_ids"], srcs)} if gi.get("trajectory_ids") else {}
+            keep = [i for i, last in enumerate(out["is_last_step"]) if last]
+            tids = out.get("trajectory_ids") or []
+            uids = [tids[i].instance_id if tids else uids[min(i, len(uids) - 1)] for i in keep]
+            srcs = [src_of.get(u) for u in uids]
+            out = {k: ([v[i] for i in keep] if isinstance(v, list) and len(v) == len(out["is_last_step"]) else v)
+                   for k, v in out.items()}
         all_rewards.extend(out["rewards"])
         all_uids.extend(uids)
-        srcs = [(it.get("env_extras") or {}).get("data_source") for it in chunk for _ in range(g.eval_n_samples_per_prompt)]
         all_src.extend(srcs)
         if cfg.trainer.dump_eval_results and tokenizer is not None:
             for p, r, rew, stop in zip(out["prompt_token_ids"], out["response_ids"], out["rewards"], out["stop_reasons"]):

@@ -400,3 +400,24 @@ def test_chat_protocol_generator_builds_trajectories_from_the_tokens_the_endpoin
     assert out["response_ids"] == [[3, 10, 11, EOS, 2, 7, 8, EOS, 3, 20, 21, EOS]]
     assert out["loss_masks"] == [[0, 1, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1]]
     assert out["rewards"] == [pytest.approx(1.3)]  # one scalar for the rebuilt trajectory
+
+
+def test_step_wise_evaluation_scores_trajectories_by_their_last_step(tmp_path):
+    from types import SimpleNamespace
+
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.train.evaluate import evaluate
+
+    cfg = SkyRLTrainConfig.from_cli_overrides([
+        "generator.step_wise_trajectories=true", "generator.batched=false", "generator.max_turns=3",
+        "generator.eval_n_samples_per_prompt=2", "environment.env_class=scripted", "trainer.eval_batch_size=8",
+        f"trainer.export_path={tmp_path}", "trainer.dump_eval_results=false", "trainer.print_example_interval=0"])
+    client = ScriptedClient([[10, EOS], [20, EOS]])
+    ScriptedEnv.script, ScriptedEnv.seen = [("7", 0.0, False), (None, 1.0, True)], []
+    g = SkyRLGymGenerator(cfg.generator, None, client, SyntheticTokenizer(1024))
+    items = [{"prompt": PROMPT, "uid": f"p{i}", "env_class": "scripted", "env_extras": {"data_source": "toy"}}
+             for i in range(3)]
+    m = asyncio.run(evaluate(SimpleNamespace(items=items), g, cfg, 0, SyntheticTokenizer(1024)))
+    # 3 prompts x 2 samples, two steps each; every trajectory ends with reward 1 on its last step
+    assert m["eval/all/avg_score"] == pytest.approx(1.0) and m["eval/all/pass_at_2"] == pytest.approx(1.0)
+    assert m["eval/toy/avg_score"] == pytest.approx(1.0)
