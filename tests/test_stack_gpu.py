@@ -142,6 +142,42 @@ def test_engine_moe_graph_decode_matches_eager():
     assert _lib.status_read_clear() == 0
 
 
+def test_engine_returns_routed_experts_on_gpu_and_replay_reproduces_the_forward():
+    """Routing capture on the device path: tables have one row per fed token, agree with a full forward over the same
+    tokens (bf16 near-ties aside), and replaying them through the model gives that forward's hidden states."""
+    from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine, SamplingParams
+    from skyrl_b200.models import router_replay
+    from skyrl_b200.models.decoder import PRESETS, CausalLM
+
+    m = CausalLM(PRESETS["tiny-moe"], device="cuda", dtype=torch.bfloat16, seed=9)
+    a = m.args
+    eng = LLMEngine(m, EngineConfig(block_size=16, max_num_seqs=8, max_model_len=256, sync_interval=4, num_blocks=128,
+                                    return_routed_experts=True))
+    prompts = [torch.randint(4, 1024, (n,)).tolist() for n in (33, 5, 70)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))
+    assert eng.stats["graph_replays"] == 0  # recording runs the decode steps eagerly
+    agree, total = 0, 0
+    for p, o in zip(prompts, outs):
+        toks = p + o.token_ids[:-1]
+        r = o.routed_experts
+        assert tuple(r.shape) == (len(toks), a.num_layers, a.num_experts_per_tok) and r.dtype == torch.int16
+        assert int(r.min()) >= 0 and int(r.max()) < a.num_experts
+        ids = torch.tensor(toks, dtype=torch.int32, device="cuda")
+        pos = torch.arange(len(toks), dtype=torch.int32, device="cuda")
+        cu = torch.tensor([0, len(toks)], dtype=torch.int32, device="cuda")
+        with torch.no_grad(), router_replay.record_routing() as store:
+            h_free = m(ids, pos, cu, len(toks))
+        want = router_replay.stack_recorded(store).cpu()
+        same = (r.long().sort(-1).values == want.sort(-1).values).all(-1)
+        agree += int(same.sum())
+        total += same.numel()
+        with torch.no_grad(), router_replay.replay_routing(want.to(torch.int16).cuda()):
+            h_replay = m(ids, pos, cu, len(toks))
+        assert rel(h_replay, h_free) < 1e-3
+    assert agree / total > 0.9, (agree, total)
+    assert _lib.status_read_clear() == 0
+
+
 def test_attention_sinks_kernels_match_reference():
     """Sink attention = the tcgen05 kernels unchanged + the sink folded into the log-sum-exp: forward and all three
     gradients (qkv, sinks) against the fp32 PyTorch formulation with an explicit sink column."""
