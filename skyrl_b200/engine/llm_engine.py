@@ -679,7 +679,7 @@ class LLMEngine:
         # like dense layers -- except while the routing is being recorded or replayed (those tensors live on the host side)
         from ..models import router_replay
 
-        use_graph = (self.is_cuda and not self.cfg.enforce_eager and not masked and router_replay._get().mode is None
+        use_graph = (self.is_cuda and not self.cfg.enforce_eager and not masked and not router_replay.active()
                      and not self._record)
         if use_graph:
             g = self._graphs.get(n)

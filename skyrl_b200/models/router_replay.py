@@ -48,12 +48,20 @@ def replay_routing(indices: torch.Tensor):
         s.mode, s.replay = prev
 
 
+_persistent = {"replay": None}  # process-wide, see set_replay
+
+
 def set_replay(indices: Optional[torch.Tensor]) -> None:
     """Replay ``indices`` (``[T, layers, k]``) in every forward from now until ``set_replay(None)``.  Unlike the
     ``replay_routing`` block this also covers the layer recomputation that gradient checkpointing runs during the
-    backward pass, long after the forward call returned."""
-    s = _get()
-    s.mode, s.replay = ("replay", indices) if indices is not None else (None, None)
+    backward pass: long after the forward call returned, and on CUDA in the autograd engine's own thread -- which is
+    why this state is process-wide while the ``record_routing`` / ``replay_routing`` blocks are per thread."""
+    _persistent["replay"] = indices
+
+
+def active() -> bool:
+    """Is any recording or replay in force for the calling thread?"""
+    return _get().mode is not None or _persistent["replay"] is not None
 
 
 PAD = -1  # rows of a replay table without recorded routing: the layer keeps its own choice there
@@ -91,8 +99,8 @@ def on_route(layer: int, idx: torch.Tensor) -> Optional[torch.Tensor]:
     if s.mode == "record":
         s.store[layer] = idx.detach()
         return None
-    if s.mode == "replay":
-        r = s.replay[:, layer]
+    if s.mode == "replay" or _persistent["replay"] is not None:
+        r = (s.replay if s.mode == "replay" else _persistent["replay"])[:, layer]
         if r.shape != idx.shape:
             raise ValueError(f"replayed routing for layer {layer} has shape {tuple(r.shape)}, expected {tuple(idx.shape)}")
         r = r.to(idx.device).to(idx.dtype)

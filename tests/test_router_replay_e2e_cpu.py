@@ -124,7 +124,7 @@ def test_trainer_replays_rollout_routing_in_the_policy_passes(tmp_path, ckpt):
     finally:
         router_replay.set_replay = real
     assert seen["tables"] >= 2 and seen["forced_rows"] > 0  # the no-grad forward and the training pass both replayed
-    assert router_replay._get().mode is None                  # and nothing is left set for the next rollout
+    assert not router_replay.active()                  # and nothing is left set for the next rollout
     assert m["policy/grad_norm"] > 0
     assert m["policy/rollout_train_logprobs_abs_diff_mean"] < 1e-4
     m2 = tr.train_step(_prompts(seed=1))
@@ -166,3 +166,31 @@ def test_routed_experts_cross_the_http_wire():
         assert padded.shape[:2] == (2, 12) and (padded[0, -1] == router_replay.PAD).all()
     finally:
         srv.stop()
+
+
+def test_persistent_replay_is_seen_by_other_threads():
+    """On CUDA the backward pass (and with it the recomputation of checkpointed layers) runs in the autograd engine's
+    thread: the table set for a micro-batch must reach it, while record / replay blocks stay private to their thread."""
+    import threading
+
+    idx = torch.tensor([[1, 2], [3, 4]])
+    table = torch.tensor([[[5, 0]], [[7, 6]]], dtype=torch.int16)
+    got = {}
+
+    def other():
+        got["persistent"] = router_replay.on_route(0, idx)
+        got["active"] = router_replay.active()
+
+    router_replay.set_replay(table)
+    try:
+        t = threading.Thread(target=other)
+        t.start()
+        t.join()
+    finally:
+        router_replay.set_replay(None)
+    assert got["active"] and got["persistent"].tolist() == [[5, 0], [7, 6]]
+    with router_replay.replay_routing(table):
+        t = threading.Thread(target=other)
+        t.start()
+        t.join()
+    assert not got["active"] and got["persistent"] is None

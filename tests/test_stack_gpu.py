@@ -121,6 +121,39 @@ def test_grpo_step_on_gpu():
     ge.smoke()
 
 
+def test_moe_grpo_step_with_router_replay_on_gpu(tmp_path):
+    """One GRPO step of a mixture-of-experts policy whose training passes replay the rollout's expert choices."""
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.models import router_replay
+    from skyrl_b200.parallel import dist as pdist
+    from skyrl_b200.train.trainer import PPOTrainer
+    from skyrl_b200.utils.tokenizer import SyntheticTokenizer
+
+    pdist.reset_env_for_tests()
+    cfg = SkyRLTrainConfig.from_cli_overrides([
+        "trainer.policy.model.path=tiny-moe", "trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4",
+        "trainer.micro_train_batch_size_per_gpu=4", "trainer.micro_forward_batch_size_per_gpu=8",
+        "generator.n_samples_per_prompt=2", "generator.sampling_params.max_generate_length=24",
+        "trainer.max_prompt_length=48", "trainer.algorithm.use_kl_loss=false", "environment.env_class=synthetic_even",
+        "generator.batched=true", "generator.inference_engine.max_num_seqs=16", "trainer.seed=0",
+        "generator.inference_engine.enable_return_routed_experts=true",
+        "trainer.policy.megatron_config.moe_enable_routing_replay=true",
+        f"trainer.ckpt_path={tmp_path}/ckpt", f"trainer.export_path={tmp_path}/export", "trainer.resume_mode=none"])
+    tr = PPOTrainer(cfg, tokenizer=SyntheticTokenizer(1024))
+    tr.build_models()
+    g = torch.Generator().manual_seed(0)
+    prompts = []
+    for i in range(4):
+        ids = torch.randint(4, 1024, (40,), generator=g).tolist()
+        prompts.append({"prompt": [{"role": "user", "content": ids}], "prompt_token_ids": ids, "uid": f"p{i}"})
+    m = tr.train_step(prompts)
+    assert math.isfinite(m["policy/final_loss"]) and m["policy/grad_norm"] > 0
+    # the training pass ran through the rollout's experts: its log-probs agree with the engine's to bf16 accuracy
+    assert m["policy/rollout_train_logprobs_abs_diff_mean"] < 5e-2
+    assert not router_replay.active()
+    assert _lib.status_read_clear() == 0
+
+
 def test_engine_moe_graph_decode_matches_eager():
     """Mixture-of-experts decode replays from a CUDA graph (device-side routing plan) with the eager path's tokens."""
     from skyrl_b200.engine.llm_engine import EngineConfig, LLMEngine, SamplingParams
@@ -153,7 +186,8 @@ def test_engine_returns_routed_experts_on_gpu_and_replay_reproduces_the_forward(
     a = m.args
     eng = LLMEngine(m, EngineConfig(block_size=16, max_num_seqs=8, max_model_len=256, sync_interval=4, num_blocks=128,
                                     return_routed_experts=True))
-    prompts = [torch.randint(4, 1024, (n,)).tolist() for n in (33, 5, 70)]
+    gen = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(4, 1024, (n,), generator=gen).tolist() for n in (33, 5, 70)]
     outs = eng.generate(prompts, SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True))
     assert eng.stats["graph_replays"] == 0  # recording runs the decode steps eagerly
     agree, total = 0, 0
@@ -173,7 +207,7 @@ def test_engine_returns_routed_experts_on_gpu_and_replay_reproduces_the_forward(
         total += same.numel()
         with torch.no_grad(), router_replay.replay_routing(want.to(torch.int16).cuda()):
             h_replay = m(ids, pos, cu, len(toks))
-        assert rel(h_replay, h_free) < 1e-3
+        assert rel(h_replay, h_free) < 5e-3  # gate weights: fused router kernel vs softmax + gather, in bf16
     assert agree / total > 0.9, (agree, total)
     assert _lib.status_read_clear() == 0
 
