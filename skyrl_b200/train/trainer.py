@@ -363,7 +363,14 @@ class PPOTrainer:
         if last is not None and self.cfg.generator.step_wise_trajectories:
             # step-wise: estimate on the last step of each trajectory, broadcast to its earlier steps
             last_t = torch.tensor(last, dtype=torch.bool)
-            tids = batch.metadata["trajectory_ids"]
+            tids = batch.metadata.get("trajectory_ids")
+            if tids is None:
+                # rows of a trajectory are adjacent and end with its last step: number the trajectories by counting the
+                # last steps seen before each row
+                seen, tids = 0, []
+                for is_last in last:
+                    tids.append(seen)
+                    seen += int(bool(is_last))
             adv_l, ret_l = rl.compute_advantages_and_returns(
                 rew[last_t].to(dev), rmask[last_t].to(dev), uids[last_t.numpy()], a.advantage_estimator, a,
                 values=batch["values"][last_t].to(dev) if batch.get("values") is not None else None,

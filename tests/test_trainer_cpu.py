@@ -182,3 +182,23 @@ def test_postprocess_rewards_metrics_superset_and_step_wise_merge(tmp_path):
     assert out["loss_masks"] == [[1, 1, 0, 1], [1, 1]] and out["rewards"] == [[0.0, 0.25, 0.0, 1.0], [0.0, 0.0]]
     assert sw.all_metrics["generate/num_seq_before_merge"] == 3 and sw.all_metrics["generate/num_seq_after_merge"] == 2
     assert sw.all_metrics["reward/avg_raw_reward"] == pytest.approx(0.5)  # last steps only: (1.0 + 0.0) / 2
+
+
+def test_step_wise_advantages_follow_each_steps_own_mask(tmp_path):
+    """Intermediate and last steps have different response lengths, so their masks end at different columns: each
+    step gets its trajectory's advantage on its *own* mask (the reference's regression test for its issue 1492)."""
+    from skyrl_b200.train.batch import TrainingInputBatch
+
+    pdist.reset_env_for_tests()
+    tr = PPOTrainer(_cfg(tmp_path, ["generator.step_wise_trajectories=true", "generator.batched=false",
+                                    "trainer.algorithm.grpo_norm_by_std=false"]), tokenizer=SyntheticTokenizer(1024))
+    rm = torch.tensor([[0, 0, 1, 1, 1, 1], [0, 0, 0, 0, 0, 1], [0, 0, 0, 1, 1, 1], [0, 0, 0, 0, 1, 1]])
+    rew = torch.zeros(4, 6)
+    rew[1, -1] = 2.0
+    d = TrainingInputBatch({"sequences": torch.zeros(4, 6, dtype=torch.long), "attention_mask": torch.ones(4, 6, dtype=torch.long),
+                            "loss_mask": rm.float(), "response_mask": rm, "rewards": rew})
+    d.metadata = {"uids": ["g"] * 4, "response_length": 6, "is_last_step": [False, True, False, True]}
+    tr.all_metrics = {}
+    out = tr.compute_advantages_and_returns(d)
+    want = torch.tensor([[0, 0, 1, 1, 1, 1], [0, 0, 0, 0, 0, 1], [0, 0, 0, -1, -1, -1], [0, 0, 0, 0, -1, -1]], dtype=torch.float32)
+    assert torch.allclose(out["advantages"], want) and torch.allclose(out["returns"], want)
