@@ -623,6 +623,9 @@ class B200Config(BaseConfig):
     kv_block_size: int = 32
     fused_optimizer: bool = True  # reduce-scatter + AdamW + parameter push in one peer-memory kernel
     cuda_graph_decode: bool = True
+    # with trainer.mtp.enabled: the colocated engine drafts one token per step with the draft head being trained
+    # (decode steps then run eagerly, two rows per sequence); false keeps plain decoding and only trains the head
+    speculative_decode: bool = True
     # batch sizes the engine captures decode graphs for (a step runs at the smallest one that holds its live slots);
     # empty = the engine's own ladder
     decode_graph_batch_sizes: List[int] = field(default_factory=list)

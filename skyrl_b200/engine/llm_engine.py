@@ -126,6 +126,10 @@ class EngineConfig:
     # mixture-of-experts models: return, with every output, the experts each token was routed to (router replay in the
     # trainer).  Decode then runs without CUDA graphs and the prefix cache is bypassed (cached tokens are not routed).
     return_routed_experts: bool = False
+    # speculative decoding with a draft head on the trunk's last hidden state (``set_draft_head``): every decode step
+    # feeds the pending token and the head's guess for the one after it, and keeps the second row's result when the
+    # token sampled from the first row equals the guess.  0 = off; depths above 1 are run as 1.
+    num_speculative_tokens: int = 0
     # KV cache in a fixed-address arena (driver virtual-memory management): sleep() frees the memory, the addresses and
     # the CUDA graphs captured against them stay valid
     kv_fixed_address: bool = True
@@ -211,6 +215,11 @@ class LLMEngine:
         self._record = bool(c.return_routed_experts and a.num_experts)
         self.out_experts = (torch.zeros((S, self.out_stride, a.num_layers * a.num_experts_per_tok), device=dev,
                                         dtype=torch.int16) if self._record else None)
+        # speculative decoding: the draft head's guess for the token after ``cur_tokens`` (valid where draft_valid)
+        self.draft_head = None
+        self.draft_tokens = torch.zeros(S, **i32)
+        self.draft_valid = torch.zeros(S, **i32)
+        self._spec_counts = torch.zeros(2, device=dev, dtype=torch.int64)  # rows drafted, drafts accepted
         self.eos_dev = torch.tensor(self.eos_token_ids or [-1], **i32)
         self.step_counter = torch.zeros(1, device=dev, dtype=torch.int64)
         self.temperature = torch.ones(S, device=dev, dtype=torch.float32)
@@ -312,17 +321,21 @@ class LLMEngine:
                 self._retire(r, "abort")
 
     # ------------------------------------------------------------------ forward passes
-    def _layer_decode(self, i, x, delta, n):
+    def _layer_decode(self, i, x, delta, n, st=None):
+        """One decoder layer over one token per row.  ``st`` = (positions, slots, block_tables, ctx_lens) of the rows
+        when they are not simply the first ``n`` slots (speculative decoding feeds two rows per slot)."""
         m, a = self.model, self.model.args
         pre = f"layers.{i}."
+        pos, slots, bt, ctx = st if st is not None else (self.positions[:n], self.slots[:n], self.block_tables[:n],
+                                                         self.ctx_lens[:n])
         x, h = ew.add_rmsnorm(x, delta, m.p(pre + "ln1"), a.rms_norm_eps)
         qkv = gemm.gemm_nt(h, m.p(pre + "wqkv"), m._p.get(pre + "bqkv"))
         if a.qk_norm:
             qkv = m._qk_norm(qkv, i)
-        qkv = ew.rope_(qkv, self.positions[:n], m.rope_table(self.device), a.num_heads + a.num_kv_heads, a.head_dim)
-        attn_ops.kv_cache_write(qkv, self.k_cache[i], self.v_cache[i], self.slots[:n], a.num_heads, a.num_kv_heads,
+        qkv = ew.rope_(qkv, pos, m.rope_table(self.device), a.num_heads + a.num_kv_heads, a.head_dim)
+        attn_ops.kv_cache_write(qkv, self.k_cache[i], self.v_cache[i], slots, a.num_heads, a.num_kv_heads,
                                 a.head_dim)
-        att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], self.block_tables[:n], self.ctx_lens[:n],
+        att = attn_ops.attn_decode_paged(qkv, self.k_cache[i], self.v_cache[i], bt, ctx,
                                          a.num_heads, a.num_kv_heads, a.head_dim, max_ctx=self.cfg.max_model_len,
                                          sinks=m._p.get(pre + "sinks"))
         tp = self.tp_size > 1
@@ -466,6 +479,86 @@ class LLMEngine:
         logits = gemm.gemm_nt(h, m.lm_head_weight())
         self._sample(logits, n, masked)
         self._advance(n)
+
+    # ------------------------------------------------------------------ speculative decoding
+    def set_draft_head(self, head) -> None:
+        """``head(hidden [T, H]) -> [T, H]``: a module whose output, through the model's LM head, predicts the token
+        *after* the one the hidden state itself predicts (``algorithms/mtp.py::DraftHead``, trained beside the policy
+        with ``trainer.mtp.enabled``).  The engine keeps a reference, not a copy: a trained head drafts with its
+        current weights at the next step, so there is no drafter reload after a weight sync (reference: vLLM
+        ``speculative_config`` + drafter reload, inference_servers/vllm_worker.py)."""
+        if self.tp_size > 1:
+            raise NotImplementedError("speculative decoding is not supported by tensor-parallel engines")
+        if self._record:
+            raise NotImplementedError("speculative decoding cannot be combined with return_routed_experts")
+        self.draft_head = head
+
+    @property
+    def _spec(self) -> bool:
+        return self.draft_head is not None and self.cfg.num_speculative_tokens > 0
+
+    @torch.no_grad()
+    def _draft(self, h: torch.Tensor) -> torch.Tensor:
+        """Greedy guess of the draft head on hidden states ``h`` -> int32 token ids."""
+        w = self.model.lm_head_weight()
+        d = self.draft_head(h).to(w.dtype).contiguous()
+        return gemm.gemm_nt(d, w).float().argmax(-1).to(torch.int32)
+
+    @torch.no_grad()
+    def _decode_once_spec(self, n: int, masked: bool) -> None:
+        """One decode step over two rows per slot: row A feeds the pending token, row B the draft head's guess for the
+        next one.  The token sampled from row A is always kept; if it equals the guess, row B was computed on the right
+        input and the token sampled from it is kept too.  Sampling is from the target model's own distributions in
+        both cases, so the output distribution is exactly that of plain decoding (a greedy guess is accepted with the
+        probability the target gives it, which is also what speculative sampling's accept rule yields for a
+        deterministic draft).  The key/value entry row B wrote for a rejected guess is overwritten by the next step."""
+        m, a = self.model, self.model.args
+        bs = self.cfg.block_size
+        act = self.active[:n].bool()
+        posA = self.positions[:n]
+        # a guess is only fed where the slot may still emit two tokens (its blocks are reserved up to that length)
+        has = act & self.draft_valid[:n].bool() & ((self.gen_count[:n] + 1) < self.max_new[:n])
+        posB = torch.where(has, posA + 1, posA)
+        blk = self.block_tables[:n].gather(1, (posB // bs).long().unsqueeze(1)).squeeze(1)
+        slotB = torch.where(has, blk * bs + posB % bs, torch.full_like(blk, -1))
+        tokB = torch.where(has, self.draft_tokens[:n], self.cur_tokens[:n])
+        st = (torch.cat([posA, posB]), torch.cat([self.slots[:n], slotB]),
+              torch.cat([self.block_tables[:n], self.block_tables[:n]]), torch.cat([self.ctx_lens[:n], posB + 1]))
+        x = sampling.embed(m.p("embed"), torch.cat([self.cur_tokens[:n], tokB]))
+        delta = None
+        for i in range(a.num_layers):
+            x, delta = self._layer_decode(i, x, delta, 2 * n, st)
+        _, h = ew.add_rmsnorm(x, delta, m.p("final_norm"), a.rms_norm_eps)
+        logits = gemm.gemm_nt(h, m.lm_head_weight())
+        temp = torch.cat([self.temperature[:n], self.temperature[:n]])
+        if masked:
+            logits = _mask_logits_rows(logits, temp, torch.cat([self.top_k[:n]] * 2), torch.cat([self.top_p[:n]] * 2),
+                                       torch.cat([self.min_p[:n]] * 2))
+        tok = torch.empty(2 * n, device=self.device, dtype=torch.int32)
+        lp = torch.empty(2 * n, device=self.device)
+        if self.is_cuda:
+            sampling.sample(logits, temp.contiguous(), self.cfg.seed, self.step_counter, tok, lp)
+        else:
+            t_, l_ = sampling.sample(logits, temp, self.cfg.seed, generator=self._cpu_gen)
+            tok.copy_(t_)
+            lp.copy_(l_)
+        accepted = has & (tok[:n] == self.draft_tokens[:n])
+        # the next guess comes from the last hidden state that was computed on real tokens
+        h_last = torch.where(accepted.unsqueeze(1), h[n:], h[:n])
+        guess = self._draft(h_last)
+        rows = torch.arange(n, device=self.device)
+        self.sampled[:n] = tok[:n]
+        self.sampled_lp[:n] = lp[:n]
+        self._advance_rows(rows)
+        second = rows[accepted]
+        if second.numel():
+            self.sampled[second] = tok[n:][accepted]
+            self.sampled_lp[second] = lp[n:][accepted]
+            self._advance_rows(second)  # rows that finished on their first token are inactive and stay untouched
+        self.draft_tokens[:n] = guess
+        self.draft_valid[:n] = self.active[:n]
+        self._spec_counts[0] += has.sum()
+        self._spec_counts[1] += accepted.sum()
 
     def _sample(self, logits: torch.Tensor, n: int, masked: bool, rows: Optional[torch.Tensor] = None) -> None:
         """Samples into ``self.sampled[:n]`` / ``self.sampled_lp[:n]`` (rows = slot index of each logits row)."""
@@ -650,6 +743,9 @@ class LLMEngine:
         self._mask_slots += sum(1 for r in reqs if r.params.needs_mask)
         self._sample(logits, len(reqs), masked, rows=rows_t)
         self._advance_rows(rows_t)
+        if self._spec:
+            self.draft_tokens[rows_t] = self._draft(last.contiguous())
+            self.draft_valid[rows_t] = self.active[rows_t]
         for r in reqs:
             self.rt.sbrt_sched_mark_prefilled(self.sched, r.sid)
         self.stats["prefill_tokens"] += len(ids)
@@ -680,7 +776,7 @@ class LLMEngine:
         from ..models import router_replay
 
         use_graph = (self.is_cuda and not self.cfg.enforce_eager and not masked and not router_replay.active()
-                     and not self._record)
+                     and not self._record and not self._spec)
         if use_graph:
             g = self._graphs.get(n)
             if g is None:
@@ -689,6 +785,9 @@ class LLMEngine:
                 g.replay()
             _lib.LAUNCH_COUNT += steps * self._graph_launches.get(n, 0)
             self.stats["graph_replays"] += steps
+        elif self._spec:
+            for _ in range(steps):
+                self._decode_once_spec(n, masked)
         elif self._record:
             rows = torch.arange(n, device=self.device)
             for _ in range(steps):
@@ -807,7 +906,7 @@ class LLMEngine:
 
     _SLOT_STATE = ("cur_tokens", "positions", "slots", "ctx_lens", "block_tables", "active", "finish_reason", "gen_count",
                    "max_new", "min_new", "out_tokens", "out_logprobs", "temperature", "top_k", "top_p", "min_p", "sampled",
-                   "sampled_lp", "out_experts")
+                   "sampled_lp", "out_experts", "draft_tokens", "draft_valid")
 
     def _compact_slots(self) -> None:
         """Move running sequences from high slots into free low slots when that lets the decode batch drop to a
@@ -1048,6 +1147,10 @@ class LLMEngine:
         m["kv_usage"] = 1.0 - m["kv_free_blocks"] / max(1, self.num_blocks)
         m["prefix_hit_rate"] = self.rt.sbrt_sched_prefix_hit_rate(self.sched)
         m["weight_version"] = self.weight_version
+        if self._spec:
+            drafted, accepted = (int(x) for x in self._spec_counts.tolist())
+            m["spec_drafted"], m["spec_accepted"] = drafted, accepted
+            m["spec_acceptance_rate"] = accepted / max(1, drafted)
         return m
 
     def __del__(self):

@@ -113,6 +113,10 @@ class PPOTrainer:
                             return_routed_experts=bool(ie.enable_return_routed_experts),
                             # the ranks of one tensor-parallel engine must draw the same samples
                             seed=self.cfg.trainer.seed + self.env.rank // max(1, getattr(self, "engine_tp", 1)))
+        spec = bool(self.cfg.trainer.mtp.enabled and b.speculative_decode and getattr(self, "engine_tp", 1) == 1
+                    and not ie.enable_return_routed_experts and getattr(self.policy, "mtp_head", None) is not None)
+        if spec:
+            ecfg.num_speculative_tokens = 1  # one draft head: deeper settings of trainer.mtp.num_speculative_tokens run as 1
         if b.decode_graph_batch_sizes:
             ecfg.graph_batch_sizes = tuple(sorted(int(x) for x in b.decode_graph_batch_sizes))
         for k, v in (ie.engine_init_kwargs or {}).items():
@@ -121,6 +125,8 @@ class PPOTrainer:
         eos = [self.tokenizer.eos_token_id] if self.tokenizer is not None and self.tokenizer.eos_token_id is not None else []
         detok = (lambda ids: self.tokenizer.decode(ids, skip_special_tokens=False)) if self.tokenizer is not None else None
         eng = LLMEngine(model, ecfg, eos_token_ids=eos, detokenize=detok)
+        if spec:
+            eng.set_draft_head(self.policy.mtp_head)  # shared with the trainer: drafts follow every optimizer step
         if getattr(self, "engine_tp", 1) > 1:
             from ..engine.lockstep import LockstepEngine
 

@@ -182,3 +182,89 @@ def test_same_prompt_sampled_n_times_is_prefilled_once():
     assert all(t == res[True][0][0] for t in res[True][0][:4])  # greedy copies agree
     # p1: 39 matchable tokens -> 4 full blocks (32 tokens) shared by 3 copies; p2: 36 -> 4 blocks shared by 2 copies
     assert res[False][1] == 0 and res[True][1] == 3 * 32 + 2 * 32
+
+
+class _OracleHead(torch.nn.Module):
+    """A draft head that cannot be trained but is always right or always wrong: it ignores the hidden state and its
+    output, through the LM head, selects a fixed token."""
+
+    def __init__(self, model, token):
+        super().__init__()
+        w = model.lm_head_weight().float()
+        self.vec = w[token] / w[token].norm() ** 2 * 1e4  # the LM head scores `token` far above everything else
+
+    def forward(self, h):
+        return self.vec.to(h.dtype).expand(h.shape[0], -1)
+
+
+def _spec_engine(head_factory, **kw):
+    from skyrl_b200.algorithms.mtp import DraftHead  # noqa: F401
+    from skyrl_b200.models.decoder import PRESETS
+
+    torch.manual_seed(0)
+    m = CausalLM(PRESETS["tiny-llama"], dtype=torch.float32, device="cpu", seed=3)
+    eng = LLMEngine(m, EngineConfig(block_size=16, max_num_seqs=4, max_model_len=128, num_blocks=64, enforce_eager=True,
+                                    sync_interval=3, **kw), eos_token_ids=[])
+    if head_factory is not None:
+        eng.set_draft_head(head_factory(m))
+    return m, eng
+
+
+def test_speculative_decoding_keeps_the_greedy_output_and_counts_acceptances():
+    from skyrl_b200.algorithms.mtp import DraftHead
+
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(4, 1000, (n,), generator=g).tolist() for n in (7, 19, 33)]
+    sp = [SamplingParams(max_tokens=n, temperature=0.0, ignore_eos=True) for n in (1, 6, 11)]
+    _, plain = _spec_engine(None)
+    want = plain.generate(prompts, sp)
+
+    # an untrained head (identity: it guesses that the next token repeats) must not change a single token or log-prob
+    m, eng = _spec_engine(lambda m: DraftHead(m.args.hidden_size), num_speculative_tokens=1)
+    got = eng.generate(prompts, sp)
+    for a, b in zip(want, got):
+        assert a.token_ids == b.token_ids and a.finish_reason == b.finish_reason
+        assert torch.allclose(torch.tensor(a.logprobs), torch.tensor(b.logprobs), atol=1e-5)
+    mt = eng.metrics()
+    assert mt["spec_drafted"] > 0 and 0.0 <= mt["spec_acceptance_rate"] <= 1.0
+
+    # a head that always guesses a token the model never produces: nothing is accepted, the output is unchanged
+    never = max(set(range(4, 1000)) - {t for o in want for t in o.token_ids})
+    m, eng = _spec_engine(lambda m: _OracleHead(m, never), num_speculative_tokens=1)
+    got = eng.generate(prompts, sp)
+    assert [o.token_ids for o in got] == [o.token_ids for o in want] and eng.metrics()["spec_accepted"] == 0
+
+    # the same engine, second batch: slots are reused and still match
+    got2 = eng.generate(prompts[::-1], sp[::-1])
+    assert [o.token_ids for o in got2] == [o.token_ids for o in want][::-1]
+
+
+def test_speculative_decoding_accepts_correct_guesses_and_takes_two_tokens_per_step():
+    """A model whose final norm is zeroed gives uniform logits, so greedy decoding always emits token 0; a head that
+    always guesses 0 is always right: every step yields two tokens, limits are respected exactly, log-probs match."""
+    import math
+
+    import pytest
+
+    def zeroed(m):
+        m.p("final_norm").data.zero_()
+        return m
+
+    m0, plain = _spec_engine(None)
+    zeroed(m0)
+    prompts = [[5, 6, 7, 8], [9, 10, 11], [12, 13]]
+    sp = [SamplingParams(max_tokens=n, temperature=0.0, ignore_eos=True) for n in (9, 4, 1)]
+    want = plain.generate(prompts, sp)
+    assert all(set(o.token_ids) == {0} for o in want)
+    m, eng = _spec_engine(lambda m: _OracleHead(zeroed(m), 0), num_speculative_tokens=1)
+    got = eng.generate(prompts, sp)
+    for a, b in zip(want, got):
+        assert a.token_ids == b.token_ids and a.finish_reason == b.finish_reason == "length"
+        assert b.logprobs == pytest.approx([-math.log(m.args.vocab_size)] * len(b.token_ids), abs=1e-4)
+    mt = eng.metrics()
+    assert mt["spec_drafted"] > 0 and mt["spec_accepted"] == mt["spec_drafted"]
+    # 9 tokens: 1 from prefill, then 4 steps of two; plain decoding needs 8 steps
+    assert eng.stats["decode_steps"] < plain.stats["decode_steps"]
+    # sampled (temperature 1) outputs stay inside the vocabulary and respect the limits too
+    out = eng.generate(prompts, [SamplingParams(max_tokens=n, temperature=1.0, ignore_eos=True) for n in (9, 4, 1)])
+    assert [len(o.token_ids) for o in out] == [9, 4, 1]

@@ -202,3 +202,23 @@ def test_step_wise_advantages_follow_each_steps_own_mask(tmp_path):
     out = tr.compute_advantages_and_returns(d)
     want = torch.tensor([[0, 0, 1, 1, 1, 1], [0, 0, 0, 0, 0, 1], [0, 0, 0, -1, -1, -1], [0, 0, 0, 0, -1, -1]], dtype=torch.float32)
     assert torch.allclose(out["advantages"], want) and torch.allclose(out["returns"], want)
+
+
+def test_mtp_enabled_trainer_drafts_with_the_head_it_trains(tmp_path):
+    """trainer.mtp.enabled: the colocated engine speculates with the policy worker's own draft head (no copy, so no
+    reload after an update); the rollout log-probs still agree with the training pass."""
+    pdist.reset_env_for_tests()
+    tr = PPOTrainer(_cfg(tmp_path, ["trainer.mtp.enabled=true"]), tokenizer=SyntheticTokenizer(1024))
+    tr.build_models()
+    assert tr.engine.draft_head is tr.policy.mtp_head and tr.engine.cfg.num_speculative_tokens == 1
+    m = tr.train_step(_prompts())
+    em = tr.engine.metrics()
+    assert em["spec_drafted"] > 0 and 0.0 <= em["spec_acceptance_rate"] <= 1.0
+    assert m["policy/rollout_train_logprobs_abs_diff_mean"] < 1e-4 and m["policy/grad_norm"] > 0
+    assert 8 * 4 * 16 < m["trainer/num_generated_tokens"] <= 8 * 4 * 32
+    # switched off: the head is still trained, the engine decodes plainly
+    pdist.reset_env_for_tests()
+    tr2 = PPOTrainer(_cfg(tmp_path, ["trainer.mtp.enabled=true", "trainer.b200.speculative_decode=false"]),
+                     tokenizer=SyntheticTokenizer(1024))
+    tr2.build_models()
+    assert tr2.engine.draft_head is None and tr2.policy.mtp_head is not None
