@@ -101,7 +101,11 @@ class InferenceOnlyEntrypoint(BasePPOExp):
             dist.all_gather_object(gathered, srv.url)
             urls = [u for u in gathered if u]
         if self.env.is_main and with_router:
-            self._router = ServerThread(build_router_app(SessionRouter(urls)), host=self.host,
+            # generator.inference_engine.router_init_kwargs: policy (consistent_hash | sticky_least_loaded |
+            # round_robin) and vnodes reach the router; other names belong to the reference's router and are ignored
+            rk = {k: v for k, v in (self.cfg.generator.inference_engine.router_init_kwargs or {}).items()
+                  if k in ("policy", "vnodes")}
+            self._router = ServerThread(build_router_app(SessionRouter(urls, **rk)), host=self.host,
                                         port=(self.base_port + self.env.world_size) if self.base_port else 0).start()
             rec.update({"router_url": self._router.url, "server_urls": urls})
         print(json.dumps(rec), flush=True)

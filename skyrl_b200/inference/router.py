@@ -1,6 +1,7 @@
 """Session-affine HTTP router in front of several inference servers: consistent hashing on ``X-Session-ID``
-(C++ hash ring with virtual nodes, ``csrc/runtime/runtime.cpp``), round-robin for requests without a session,
-health-based ejection, optional prefill/decode URL lists.  Role of the Rust ``vllm-router`` wheel the reference
+(C++ hash ring with virtual nodes, ``csrc/runtime/runtime.cpp``) or ``sticky_least_loaded`` (a new session goes to
+the server with the fewest open sessions and stays there until ``/finish_session`` closes it), round-robin for
+requests without a session, health-based ejection, optional prefill/decode URL lists.  Role of the Rust ``vllm-router`` wheel the reference
 launches (skyrl/backends/skyrl_train/inference_servers/vllm_router.py:47-175)."""
 
 from __future__ import annotations
@@ -27,6 +28,11 @@ class SessionRouter:
         self.healthy = [True] * len(self.urls)
         self._rr = itertools.count()
         self.stats: Dict[str, int] = {u: 0 for u in self.urls}
+        if policy not in ("consistent_hash", "round_robin", "sticky_least_loaded"):
+            raise ValueError(f"unknown routing policy '{policy}'")
+        # sticky_least_loaded: where each open session lives, and how many open sessions each server holds
+        self.session_home: Dict[str, int] = {}
+        self.open_sessions: List[int] = [0] * len(self.urls)
 
     def pick(self, session_id: Optional[str]) -> str:
         live = [i for i, ok in enumerate(self.healthy) if ok]
@@ -34,11 +40,27 @@ class SessionRouter:
             raise RuntimeError("no healthy inference server")
         if session_id is None or self.policy == "round_robin":
             i = live[next(self._rr) % len(live)]
+        elif self.policy == "sticky_least_loaded":
+            i = self.session_home.get(session_id, -1)
+            if i < 0 or not self.healthy[i]:
+                if i >= 0:  # its server went away: the session moves (and loses its cached prefix)
+                    self.open_sessions[i] -= 1
+                i = min(live, key=lambda k: (self.open_sessions[k], k))
+                self.session_home[session_id] = i
+                self.open_sessions[i] += 1
         else:
             i = self.ring.lookup(session_id)
             if not self.healthy[i]:  # walk to the next live node deterministically
                 i = live[hash(session_id) % len(live)]
         self.stats[self.urls[i]] += 1
+        return self.urls[i]
+
+    def finish(self, session_id: Optional[str]) -> Optional[str]:
+        """The session is over: free its place (sticky_least_loaded).  Returns the URL it lived on, if any."""
+        i = self.session_home.pop(session_id, -1) if session_id is not None else -1
+        if i < 0:
+            return None
+        self.open_sessions[i] -= 1
         return self.urls[i]
 
     def mark(self, url: str, ok: bool) -> None:
@@ -77,6 +99,19 @@ def build_router_app(router: SessionRouter):
         headers = {"Content-Type": "application/json"}
         if sid:
             headers["X-Session-ID"] = sid
+        if path == "/finish_session" and router.policy == "sticky_least_loaded":
+            try:
+                sid = sid or (await request.json()).get("session_id")
+            except Exception:
+                pass
+            url = router.finish(sid)
+            if url is None:
+                return JSONResponse({"status": "ok"})
+            try:
+                async with s.post(url + path, data=body, headers=headers) as r:
+                    return JSONResponse(await r.json(), status_code=r.status)
+            except aiohttp.ClientConnectionError:
+                return JSONResponse({"status": "ok"})
         for _attempt in range(len(router.urls)):
             url = router.pick(sid)
             try:

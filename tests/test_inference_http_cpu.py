@@ -174,3 +174,50 @@ def test_sample_tokenize_render_and_context_manager_over_http():
         assert SamplingParams.from_dict({"prompt_logprobs": None}).prompt_logprobs is False
     finally:
         srv.stop()
+
+
+def test_sticky_least_loaded_balances_new_sessions_and_frees_finished_ones():
+    r = SessionRouter(["http://a", "http://b", "http://c"], policy="sticky_least_loaded")
+    first = [r.pick(f"s{i}") for i in range(3)]
+    assert sorted(first) == ["http://a", "http://b", "http://c"]        # one new session per replica
+    assert [r.pick(f"s{i}") for i in range(3)] == first and r.open_sessions == [1, 1, 1]   # sticky, not recounted
+    home0 = r.pick("s0")
+    assert r.finish("s0") == home0 and r.finish("s0") is None
+    assert r.pick("s3") == home0                                        # the freed replica is the least loaded one
+    assert r.pick("s4") in ("http://a", "http://b", "http://c") and sum(r.open_sessions) == 4
+    # a session whose server disappears moves to the least loaded live one and stays there
+    victim = r.pick("s1")
+    r.mark(victim, False)
+    moved = r.pick("s1")
+    assert moved != victim and r.pick("s1") == moved and r.open_sessions[r.urls.index(victim)] >= 0
+    assert r.pick(None) != victim                                      # session-less requests avoid it too
+    with pytest.raises(ValueError):
+        SessionRouter(["http://a"], policy="nope")
+
+
+def test_router_app_releases_sessions_on_finish():
+    srv1, eng1 = _server()
+    srv2, eng2 = _server()
+    router = SessionRouter([srv1.url, srv2.url], policy="sticky_least_loaded")
+    rt = ServerThread(build_router_app(router)).start()
+    try:
+        rc = RemoteInferenceClient([srv1.url, srv2.url], router_url=rt.url, tokenizer=SyntheticTokenizer(97))
+
+        async def run():
+            sp = {"max_generate_length": 3, "temperature": 0.0}
+            await rc.generate({"prompt_token_ids": [[5, 6], [7, 8]], "session_ids": ["x", "y"], "sampling_params": sp})
+            open_before = list(router.open_sessions)
+            await rc.generate({"prompt_token_ids": [[5, 6, 9]], "session_ids": ["x"], "sampling_params": sp})
+            still = list(router.open_sessions)
+            await rc.finish_session("x")
+            await rc.finish_session("y")
+            await rc.teardown()
+            return open_before, still
+
+        open_before, still = asyncio.run(run())
+        assert open_before == [1, 1] and still == [1, 1] and router.open_sessions == [0, 0]
+        assert eng1.stats["prefill_calls"] >= 1 and eng2.stats["prefill_calls"] >= 1
+    finally:
+        rt.stop()
+        srv1.stop()
+        srv2.stop()
