@@ -127,3 +127,34 @@ def test_llm_judge_env_scores_through_a_chat_endpoint():
     finally:
         srv.shutdown()
     assert parse_score("SCORE: 0.5 then SCORE: 3") == 1.0 and parse_score("nothing") is None
+
+
+@pytest.mark.parametrize("output,truth,expected", [
+    ("Answer: \\boxed{42}", "42", 1.0), ("Answer: 42", "42", 1.0), ("Answer: \\boxed{43}", "42", -1.0),
+    ("Answer: \\boxed{\\frac{1}{2}}", "\\frac{1}{2}", 1.0), ("Answer: \\boxed{0.5}", "\\frac{1}{2}", -1.0),
+    ("Answer: \\boxed{\\text{forty-two}}", "42", -1.0),
+    # end-of-turn tokens: a well-formed one ends the answer, a broken one becomes part of it
+    ("<|im_start|>Answer: \\boxed{42}<|im_end|>", "42", 1.0), ("<|im_start|>Answer: \\boxed{42}im_end|>", "42", -1.0),
+    ("Answer: \\boxed{42}<|eot_id|>", "42", 1.0), ("Answer: \\boxed{42}|eot_id|>", "42", -1.0),
+    # normalisation: units, thousands separators, shorthand TeX, the right-hand side of an equation
+    ("so the total is\nAnswer: 1,234 dollars", "1234", 1.0), ("Answer: x = \\frac12", "\\frac{1}{2}", 1.0),
+    ("Answer: $\\sqrt2$ cm", "\\sqrt{2}", 1.0), ("no final line at all", "42", -1.0),
+])
+def test_aime_scores_like_the_dapo_recipe(output, truth, expected):
+    """Golden cases of the reference's own environment test (skyrl-gym/tests/test_aime.py) plus normalisation cases."""
+    import skyrl_b200.gym as gym
+
+    env = gym.make("aime", env_config=None, extras={"reward_model": {"method": "rule", "ground_truth": truth}})
+    assert env.step(output)["reward"] == expected
+    # datasets written for the other environments name the field reward_spec
+    env = gym.make("aime", env_config=None, extras={"reward_spec": {"ground_truth": truth}})
+    assert env.step(output)["reward"] == expected
+
+
+@pytest.mark.parametrize("output,truth,expected", [("The answer is #### 42", "42", 1.0), ("The answer is #### 42", "43", 0.0),
+                                                    ("The answer is 42", "42", 0.0)])
+def test_gsm8k_needs_the_four_hash_format(output, truth, expected):
+    import skyrl_b200.gym as gym
+
+    env = gym.make("gsm8k", env_config=None, extras={"reward_spec": {"method": "rule", "ground_truth": truth}})
+    assert env.step(output)["reward"] == expected
