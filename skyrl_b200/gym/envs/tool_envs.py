@@ -34,11 +34,12 @@ def normalize_answer(s: str) -> str:
     return " ".join(s.split())
 
 
-def extract_tag(text: str, tag: str, last: bool = True) -> Optional[str]:
+def extract_tag(text: str, tag: str, last: bool = True, strip: bool = True) -> Optional[str]:
     m = re.findall(rf"<{tag}>(.*?)</{tag}>", text, re.DOTALL)
     if not m:
         return None
-    return (m[-1] if last else m[0]).strip()
+    out = m[-1] if last else m[0]
+    return out.strip() if strip else out
 
 
 def em_score(history: str, ground_truth: Any, format_score: float = 0.0) -> float:
@@ -74,7 +75,7 @@ class _ToolLoopEnv(BaseTextEnv):
         raise NotImplementedError
 
     def _tool_input(self, action: str) -> Any:
-        return (extract_tag(action, self.tool_tag, last=False),)
+        return (extract_tag(action, self.tool_tag, last=False, strip=False),)  # the tool sees the text as written
 
     def _wrap(self, out: str) -> str:
         return out
@@ -148,15 +149,41 @@ def _run_sql(db_file: str, sql: str, timeout_s: float = 10.0):
         conn.close()
 
 
+def verify_format_and_extract(output: str):
+    """``(valid, thoughts, solution, None)`` for a whole trajectory's text.  Valid means: exactly one ``<solution>`` and
+    one ``</solution>`` after it, no think / sql / observation tag inside the solution, at least one complete
+    ``<think>`` block somewhere, and every ``</observation>`` before the solution followed (after whitespace) by a
+    ``<think>``.  Rules of the reference's scorer (skyrl-gym/skyrl_gym/envs/sql/utils.py:21-45)."""
+    if output.count("<solution>") != 1:
+        return False, None, None, None
+    before, after = output.split("<solution>", 1)
+    if after.count("</solution>") != 1:
+        return False, None, None, None
+    solution = after.split("</solution>", 1)[0]
+    if re.search(r"</?(think|sql|observation)\b", solution, re.I):
+        return False, None, None, None
+    thoughts = re.findall(r"<think>(.*?)</think>", output, re.S)
+    if not thoughts:
+        return False, None, None, None
+    for m in re.finditer(r"</observation>", before, re.I):
+        if not before[m.end():].lstrip().lower().startswith("<think>"):
+            return False, None, None, None
+    return True, thoughts, solution.strip(), None
+
+
 def sql_score(history: str, gold_sql: str, db_file: str) -> float:
-    """1 if the last ``<solution>`` query returns the same row set as the gold query, 0 for a wrong result, -1 when the
-    format is broken (no think/solution structure)."""
-    sol = extract_tag(history, "solution")
-    if sol is None:
+    """-1 when the trajectory breaks the think / sql / solution format, else 1 if the solution query returns the same
+    row set as the gold query and 0 if not (a query that fails to run counts as a wrong result)."""
+    ok, _, sol, _ = verify_format_and_extract(history)
+    if not ok:
         return -1.0
     sol = re.sub(r"^```(?:sql)?|```$", "", sol.strip(), flags=re.MULTILINE).strip()
     try:
-        return 1.0 if _run_sql(db_file, sol) == _run_sql(db_file, gold_sql) else 0.0
+        pred = _run_sql(db_file, sol)
+    except sqlite3.Error:
+        return 0.0
+    try:
+        return 1.0 if pred == _run_sql(db_file, gold_sql) else 0.0
     except sqlite3.Error:
         return 0.0
 

@@ -22,31 +22,51 @@ class SQLCodeExecutorToolGroup(ToolGroup):
         self.db_root, self.timeout_s, self.max_rows, self.max_chars = db_file_path, timeout_s, max_rows, max_chars
         super().__init__("SQLCodeExecutorToolGroup")
 
+    INVALID_ACTION = ("Your previous action is invalid. Follow the format of outputting thinking process and sql tool, "
+                      "and try again.")
+
     @tool
     def sql(self, db_id: str, query: Optional[str], turns_left: int = 0) -> str:
-        if not query or not query.strip():
-            return "No SQL found: put the query between <sql> and </sql>."
+        """The observation the model sees next: the result table (or the error, the timeout notice, or the note that
+        no ``<sql>`` block was found) followed by a reminder of the turns left, inside one ``<observation>`` element
+        (message layout of the reference's tool, skyrl-gym/skyrl_gym/tools/sql.py:88-97)."""
+        return (f"\n\n<observation>{self._run(db_id, query)}\n"
+                f"<reminder>You have {turns_left} turns left to complete the task.</reminder></observation>\n\n")
+
+    def _run(self, db_id: str, query: Optional[str]) -> str:
+        if query is None:
+            return self.INVALID_ACTION
         db = os.path.join(self.db_root, db_id, db_id + ".sqlite")
         if not os.path.exists(db):
-            return f"Database '{db_id}' not found."
+            return f"Error executing SQL: database '{db_id}' not found, db file: {db}"
         conn = sqlite3.connect(f"file:{db}?mode=ro", uri=True, check_same_thread=False)
-        timer = threading.Timer(self.timeout_s, conn.interrupt)
+        fired = threading.Event()
+
+        def interrupt():
+            fired.set()
+            conn.interrupt()
+
+        timer = threading.Timer(self.timeout_s, interrupt)
         timer.start()
         try:
             cur = conn.execute(query)
             cols = [d[0] for d in cur.description] if cur.description else []
-            rows = cur.fetchmany(self.max_rows + 1)
+            rows = cur.fetchall()
         except sqlite3.Error as e:
-            return f"Error executing SQL: {e}\nYou have {turns_left} turns left."
+            if fired.is_set():
+                return f"SQL Timeout:\n{query}"
+            return f"Error executing SQL: {e}, db file: {db}"
         finally:
             timer.cancel()
             conn.close()
-        more = len(rows) > self.max_rows
-        lines = [" | ".join(cols)] + [" | ".join(str(v) for v in r) for r in rows[: self.max_rows]]
-        out = "\n".join(lines)[: self.max_chars]
-        if more:
-            out += f"\n... (truncated to {self.max_rows} rows)"
-        return f"<observation>\n{out}\n</observation>\nYou have {turns_left} turns left."
+
+        def table(rs):
+            return "\n".join([" | ".join(cols)] + [" | ".join(str(v) for v in r) for r in rs])
+
+        out = table(rows)
+        if len(out) > self.max_chars:
+            out = f"Truncated to {self.max_rows} lines since returned response too long: " + table(rows[: self.max_rows])
+        return out
 
 
 class SearchToolGroup(ToolGroup):

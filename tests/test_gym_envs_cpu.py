@@ -34,14 +34,25 @@ def test_text2sql_env(tmp_path):
     con.close()
     extras = {"db_id": "shop", "data": "spider", "reward_spec": {"ground_truth": "SELECT name FROM items WHERE price > 4"}}
     env = Text2SQLEnv({"db_path": str(tmp_path)}, extras)
-    out = env.step("<sql>SELECT * FROM items</sql>")
-    assert not out["done"] and "name | price" in out["observations"][0]["content"] and "turns left" in out["observations"][0]["content"]
-    out = env.step("<sql>SELEC broken</sql>")
-    assert "Error executing SQL" in out["observations"][0]["content"]
+    out = env.step("<think>look at the table</think>\n<sql>SELECT * FROM items</sql>")
+    obs = out["observations"][0]["content"]
+    assert not out["done"] and out["reward"] == 0.0 and "name | price" in obs
+    assert obs.startswith("\n\n<observation>") and "<reminder>You have 4 turns left to complete the task.</reminder></observation>" in obs
+    assert out["metadata"]["tool_input"][1] == "SELECT * FROM items"
+    out = env.step("<think>again</think><sql>SELEC broken</sql>")
+    assert "Error executing SQL" in out["observations"][0]["content"] and "3 turns left" in out["observations"][0]["content"]
+    out = env.step("<think>no query this time</think>")
+    assert "Your previous action is invalid." in out["observations"][0]["content"] and out["metadata"]["tool_input"][1] is None
     out = env.step("<think>ok</think><solution>SELECT name FROM items WHERE price >= 5</solution>")
     assert out["done"] and out["reward"] == 1.0
+    # a wrong result scores 0, a trajectory that breaks the format scores -1
     env2 = Text2SQLEnv({"db_path": str(tmp_path)}, extras)
-    assert env2.step("<solution>SELECT name FROM items</solution>")["reward"] == 0.0
+    assert env2.step("<think>t</think><solution>SELECT name FROM items</solution>")["reward"] == 0.0
+    env3 = Text2SQLEnv({"db_path": str(tmp_path)}, extras)
+    assert env3.step("<solution>SELECT name FROM items WHERE price > 4</solution>")["reward"] == -1.0
+    env4 = Text2SQLEnv({"db_path": str(tmp_path)}, extras)
+    env4.step("<sql>SELECT 1</sql>")  # the next turn does not open with <think> after the observation
+    assert env4.step("text <think>t</think><solution>SELECT name FROM items WHERE price > 4</solution>")["reward"] == -1.0
     with pytest.raises(FileNotFoundError):
         Text2SQLEnv({"db_path": str(tmp_path)}, dict(extras, db_id="nope"))
 
@@ -158,3 +169,33 @@ def test_gsm8k_needs_the_four_hash_format(output, truth, expected):
 
     env = gym.make("gsm8k", env_config=None, extras={"reward_spec": {"method": "rule", "ground_truth": truth}})
     assert env.step(output)["reward"] == expected
+
+
+@pytest.mark.parametrize("output,valid", [
+    ("<think>I need to query the database</think>\n<solution>SELECT * FROM users;</solution>", True),
+    ("<solution>SELECT * FROM users;</solution>", False),
+    ("<think>thinking</think>\n<solution>SELECT * FROM users;<solution>more text</solution>", False),
+    ("<think>thinking</think>\n<solution>SELECT * FROM users;</solution>extra</solution>", False),
+    ("<think>thinking</think>\nSELECT * FROM users;</solution>", False),
+    ("<think>thinking</think>\n<solution>SELECT * FROM users;", False),
+    ("<think>thinking</think>\nsome text<solution>", False),
+    ("<think>thinking</think>\n<solution>SELECT * FROM users; <sql>forbidden</sql></solution>", False),
+    ("<think>thinking</think>\n<solution>SELECT * FROM users; <observation>forbidden</observation></solution>", False),
+    ("<think>thinking</think>\n<solution></solution>", True),
+    ("<think>first thought</think>\n<think>second thought</think>\n<solution>SELECT * FROM users;</solution>", True),
+    ("<observation>some observation</observation>\n<think>thinking</think>\n<solution>SELECT * FROM users;</solution>", True),
+    ("<observation>some observation</observation>\nrandom text\n<think>thinking</think>\n<solution>SELECT * FROM users;</solution>", False),
+    ("some text<solution>", False), ("</solution><solution>content</solution>", False),
+    ("<solution><solution>content</solution>", False), ("some text</solution>", False), ("", False),
+    ("<solution>content without end", False),
+])
+def test_sql_trajectory_format_rules(output, valid):
+    """The cases of the reference's own test of its scorer (skyrl-gym/tests/test_sql.py)."""
+    from skyrl_b200.gym.envs.tool_envs import verify_format_and_extract
+
+    ok, thoughts, solution, _ = verify_format_and_extract(output)
+    assert ok == valid
+    if valid:
+        assert thoughts and solution is not None
+    else:
+        assert thoughts is None and solution is None
