@@ -116,24 +116,62 @@ class SearchEnv(_ToolLoopEnv):
         return em_score("".join(m["content"] for m in self.chat_history), self.ground_truth)
 
 
-class SearchCodeEnv(SearchEnv):
-    """Search plus a Python tool (``<python>`` blocks are executed, ``<search>`` blocks are retrieved)."""
+class SearchCodeEnv(BaseTextEnv):
+    """Several tools behind one calling convention: ``<tool><name>input</name></tool>`` with ``name`` one of the
+    registered tools (``search``, ``python``).  The episode ends on ``<solution>...</solution>`` or after
+    ``max_turns``; the reward is the GSM8K-style exact match of ``#### answer`` over the whole conversation.  A call
+    that cannot be parsed comes back as the observation text.  Reference: skyrl-gym/skyrl_gym/envs/searchcode/env.py."""
 
     def __init__(self, env_config: Any = None, extras: Optional[Dict[str, Any]] = None):
-        super().__init__(env_config, extras)
-        self.init_tool_groups(self.tool_groups + [PythonCodeExecutorToolGroup()])
+        super().__init__()
+        extras = extras or {}
+        assert "reward_spec" in extras, "reward_spec field is required"
+        assert "ground_truth" in extras["reward_spec"], "ground_truth is required in reward_spec field"
+        self.ground_truth = str(extras["reward_spec"]["ground_truth"])
+        self.max_turns = int(extras.get("max_turns", 2))
+        self.init_tool_groups([SearchToolGroup(_cfg(env_config, "search_url", "http://127.0.0.1:8000/retrieve"),
+                                               _cfg(env_config, "topk", 3), _cfg(env_config, "timeout", 30),
+                                               _cfg(env_config, "log_requests", False), transport=extras.get("_transport")),
+                               PythonCodeExecutorToolGroup(plain_errors=True)])
+        self.chat_history: List[Dict[str, str]] = []
+
+    def _parse_action(self, action: str):
+        block = re.search(r"<tool>(.*?)</tool>", action, re.DOTALL)
+        if not block:
+            raise ValueError("No <tool>...</tool> block found in action string.")
+        inner = re.search(r"<(\w+)>(.*?)</\1>", block.group(1).strip(), re.DOTALL)
+        if not inner:
+            raise ValueError("No valid inner tool tag found inside <tool> block.")
+        name, arg = inner.group(1), inner.group(2).strip()
+        if name not in self.tool_to_toolgroup:
+            raise ValueError(f"Tool '{name}' not found in any registered tool group.")
+        return self.tool_to_toolgroup[name], name, [arg]
+
+    def _is_done(self, action: str) -> bool:
+        return self.turns >= self.max_turns or ("<solution>" in action and "</solution>" in action)
 
     def step(self, action: str) -> BaseTextEnvStepOutput:
-        code = extract_tag(action, "python", last=False)
-        if code is not None and "<search>" not in action and not self._is_done(action):
-            self.turns += 1
-            self.chat_history.append({"role": "assistant", "content": action})
-            out = self._execute_tool("PythonCodeExecutorToolGroup", "python", (code,))
-            msg = {"role": "user", "content": "\n<information>" + out + "</information>\n"}
-            self.chat_history.append(msg)
-            return BaseTextEnvStepOutput(observations=[msg], reward=0.0, done=False,
-                                         metadata={"tool_group": "PythonCodeExecutorToolGroup", "tool_name": "python"})
-        return super().step(action)
+        from .math_utils import extract_gsm8k_answer
+
+        self.turns += 1
+        self.chat_history.append({"role": "assistant", "content": action})
+        if self._is_done(action):
+            found = extract_gsm8k_answer("\n".join(m["content"] for m in self.chat_history), "strict")
+            return BaseTextEnvStepOutput(observations=[], reward=1.0 if found == self.ground_truth else 0.0, done=True,
+                                         metadata={})
+        group = name = None
+        arg: Any = ""
+        try:
+            group, name, arg = self._parse_action(action)
+            text = self._execute_tool(group, name, arg)
+        except Exception as e:  # noqa: BLE001 - the error text is the observation
+            group = name = None
+            arg, text = "", str(e)
+        obs = [{"role": "user", "content": text}] if text else []
+        self.chat_history.extend(obs)
+        return BaseTextEnvStepOutput(observations=obs, reward=0.0, done=False,
+                                     metadata={"tool_group": group, "tool_name": name, "tool_input": arg,
+                                               "tools": [g.get_tool_names() for g in self.tool_groups]})
 
 
 def _run_sql(db_file: str, sql: str, timeout_s: float = 10.0):

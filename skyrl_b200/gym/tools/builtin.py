@@ -109,8 +109,10 @@ class SearchToolGroup(ToolGroup):
 class PythonCodeExecutorToolGroup(ToolGroup):
     """Runs a snippet in a fresh interpreter process with a time limit; returns stdout (or the error tail)."""
 
-    def __init__(self, timeout_s: float = 10.0, max_chars: int = 4000):
-        self.timeout_s, self.max_chars = timeout_s, max_chars
+    def __init__(self, timeout_s: float = 10.0, max_chars: int = 4000, plain_errors: bool = False):
+        """``plain_errors``: report like the reference's tool does (skyrl-gym/skyrl_gym/tools/python.py) -- stripped
+        stdout, or ``Error executing Python code: <stderr>`` whenever anything was written to stderr."""
+        self.timeout_s, self.max_chars, self.plain_errors = timeout_s, max_chars, plain_errors
         super().__init__("PythonCodeExecutorToolGroup")
 
     @tool
@@ -122,10 +124,17 @@ class PythonCodeExecutorToolGroup(ToolGroup):
             with open(path, "w") as f:
                 f.write(code)
             try:
-                p = subprocess.run([sys.executable, "-I", path], input=stdin, capture_output=True, text=True,
+                argv = [sys.executable, "-I", "-c", code] if self.plain_errors else [sys.executable, "-I", path]
+                p = subprocess.run(argv, input=stdin, capture_output=True, text=True,
                                    timeout=self.timeout_s, cwd=d, env={"PATH": os.environ.get("PATH", "")})
             except subprocess.TimeoutExpired:
+                if self.plain_errors:
+                    return f"Error executing Python code: Execution timed out after {self.timeout_s} seconds."
                 return f"Error: execution exceeded {self.timeout_s} s."
+        if self.plain_errors:
+            if p.stderr:
+                return ("Error executing Python code: " + p.stderr.strip())[: self.max_chars]
+            return p.stdout.strip()[: self.max_chars]
         out = p.stdout if p.returncode == 0 else (p.stdout + "\n" + p.stderr[-1500:])
         return out[: self.max_chars]
 

@@ -199,3 +199,53 @@ def test_sql_trajectory_format_rules(output, valid):
         assert thoughts and solution is not None
     else:
         assert thoughts is None and solution is None
+
+
+def test_searchcode_env_follows_the_tool_call_protocol():
+    """Cases of skyrl-gym/tests/test_searchcode.py, plus termination and scoring."""
+    import skyrl_b200.gym as gym
+
+    ex = {"reward_spec": {"method": "rule", "ground_truth": "4"}, "max_turns": 3,
+          "_transport": lambda url, payload, timeout: {"result": [[{"document": {"contents": "T\nreverse with [::-1]"}, "score": 1.0}]]}}
+    env = gym.make("searchcode", env_config=None, extras=ex)
+    assert env._parse_action("<tool><search>how to reverse a string in Python</search></tool>")[1:] == (
+        "search", ["how to reverse a string in Python"])
+    assert env._parse_action("<tool><python>print('hello')</python></tool>")[1:] == ("python", ["print('hello')"])
+    env.init([])
+    out = env.step("<tool><python>print(1 + 1)</python></tool>")
+    assert out["observations"][0]["content"] == "2" and not out["done"] and out["metadata"]["tool_name"] == "python"
+    assert out["metadata"]["tools"] == [["search"], ["python"]]
+    out = env.step("<tool><python>raise ValueError('fail')</python></tool>")
+    assert out["observations"][0]["content"] == ('Error executing Python code: Traceback (most recent call last):\n'
+                                                 '  File "<string>", line 1, in <module>\nValueError: fail')
+    out = env.step("<solution>#### 4</solution>")
+    assert out["done"] and out["reward"] == 1.0
+    # calls that cannot be parsed come back as the observation; the last turn ends the episode whatever it says
+    env = gym.make("searchcode", env_config=None, extras=dict(ex, max_turns=2))
+    out = env.step("no tool here")
+    assert out["observations"][0]["content"] == "No <tool>...</tool> block found in action string." and out["metadata"]["tool_name"] is None
+    out = env.step("<tool><bash>ls</bash></tool>")
+    assert out["done"] and out["reward"] == 0.0
+    env = gym.make("searchcode", env_config=None, extras=ex)
+    assert "not found in any registered tool group" in env.step("<tool><bash>ls</bash></tool>")["observations"][0]["content"]
+    assert "reverse with" in env.step("<tool><search>reverse</search></tool>")["observations"][0]["content"]
+
+
+def test_lcb_env_golden_cases():
+    """Cases of skyrl-gym/tests/test_lcb.py: right program, wrong logic, program that never calls its main()."""
+    import json
+
+    import skyrl_b200.gym as gym
+
+    good = ("```python\ndef main():\n    N = int(input())\n    A = list(map(int, input().split()))\n    B = sorted(A, reverse=True)\n"
+            "    second = B[1]\n    print(A.index(second) + 1)\n\nif __name__ == \"__main__\":\n    main()\n```")
+    wrong = ("```python\ndef main():\n    N = int(input())\n    A = list(map(int, input().split()))\n    print(A.index(max(A)) + 1)\n\n"
+             "if __name__ == \"__main__\":\n    main()\n```")
+    silent = ("```python\ndef main():\n    A = list(map(int, input().split()))\n    B = sorted(A, reverse=True)\n    second = B[1]\n"
+              "    print(A.index(second) + 1)\n\n# forgot to call main()\n```")
+    two = json.dumps([{"input": "4\n8 2 5 1\n", "output": "3\n", "testtype": "stdin"},
+                      {"input": "3\n3 2 1\n", "output": "2\n", "testtype": "stdin"}])
+    one = json.dumps([{"input": "4\n8 2 5 1\n", "output": "3\n", "testtype": "stdin"}])
+    for response, tests, expected in ((good, two, 1.0), (wrong, one, 0.0), (silent, one, 0.0)):
+        env = gym.make("lcb", env_config=None, extras={"reward_spec": {"method": "rule", "ground_truth": tests}})
+        assert env.step(response)["reward"] == expected
