@@ -27,7 +27,14 @@ _ALLOWED_IMPORTS = {"re", "json", "math", "collections", "itertools", "statistic
 
 
 class PersistentREPL:
-    def __init__(self, context: Any, timeout_s: float = 10.0, max_output_chars: int = 6000, tools: Optional[dict] = None):
+    """``lm_callback(prompts: list[str]) -> list[str]`` makes ``llm_query`` / ``llm_query_batched`` available to the
+    code; ``subcall_fn(prompt) -> str`` (a child agent with its own REPL) backs ``rlm_query`` / ``rlm_query_batched``,
+    which fall back to the plain calls without it.  Failures come back as ``Error: LM query failed: ...`` strings, so
+    a flaky endpoint does not kill the episode; the four names are put back after every block, so the code cannot
+    shadow them for good (reference: skyrl-gym/skyrl_gym/envs/rlm/repl.py)."""
+
+    def __init__(self, context: Any = "", timeout_s: float = 10.0, max_output_chars: int = 6000, tools: Optional[dict] = None,
+                 lm_callback=None, subcall_fn=None):
         import builtins
 
         def _imp(name, *a, **k):
@@ -43,6 +50,49 @@ class PersistentREPL:
         for name, fn in (tools or {}).items():
             self.ns[name] = fn
         self.timeout_s, self.max_output_chars = timeout_s, max_output_chars
+        self.lm_callback, self.subcall_fn = lm_callback, subcall_fn
+        self._scaffold: Dict[str, Any] = {}
+        if lm_callback is not None:
+            self._scaffold = {"llm_query": self._llm_query, "llm_query_batched": self._llm_query_batched,
+                              "rlm_query": self._rlm_query, "rlm_query_batched": self._rlm_query_batched}
+            self.ns.update(self._scaffold)
+
+    # the namespace under its reference name
+    @property
+    def globals(self) -> Dict[str, Any]:
+        return self.ns
+
+    def _llm_query_batched(self, prompts, model=None) -> List[str]:
+        prompts = [str(p) for p in prompts]
+        try:
+            out = list(self.lm_callback(prompts))
+            if len(out) != len(prompts):
+                raise ValueError(f"{len(out)} answers for {len(prompts)} prompts")
+            return [str(o) for o in out]
+        except Exception as e:  # noqa: BLE001 - reported to the model as text
+            return [f"Error: LM query failed: {e}"] * len(prompts)
+
+    def _llm_query(self, prompt, model=None) -> str:
+        return self._llm_query_batched([prompt])[0]
+
+    def _rlm_query(self, prompt, context=None) -> str:
+        if self.subcall_fn is None:
+            return self._llm_query(prompt)
+        try:
+            return str(self.subcall_fn(str(prompt)))
+        except Exception as e:  # noqa: BLE001
+            return f"Error: RLM query failed: {e}"
+
+    def _rlm_query_batched(self, prompts, context=None) -> List[str]:
+        prompts = [str(p) for p in prompts]
+        if self.subcall_fn is None:
+            return self._llm_query_batched(prompts)
+        if len(prompts) <= 1:
+            return [self._rlm_query(p) for p in prompts]
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=min(8, len(prompts))) as ex:  # children run side by side; order is kept
+            return list(ex.map(self._rlm_query, prompts))
 
     def run(self, code: str) -> str:
         buf = io.StringIO()
@@ -65,6 +115,7 @@ class PersistentREPL:
             ctypes.pythonapi.PyThreadState_SetAsyncExc(ctypes.c_ulong(t.ident), ctypes.py_object(TimeoutError))
             done.wait(1.0)
             err.append(f"TimeoutError: block exceeded {self.timeout_s} s")
+        self.ns.update(self._scaffold)  # whatever the block did to the LM helpers' names is undone
         out = buf.getvalue()
         if err:
             out += ("\n" if out else "") + err[0]
@@ -74,6 +125,12 @@ class PersistentREPL:
 
     def get(self, name: str) -> Any:
         return self.ns.get(name)
+
+    def execute(self, code: str):
+        """``run`` under the reference's name: an object with ``.stdout``."""
+        from types import SimpleNamespace
+
+        return SimpleNamespace(stdout=self.run(code))
 
 
 _REPL_BLOCK = re.compile(r"```repl\s*\n(.*?)```", re.DOTALL)
@@ -86,15 +143,69 @@ class RLMEnv(BaseTextEnv):
     ``max_turns`` (default 10), ``root_prompt``.  Reward: 1 for a normalised exact match (or containment when
     ``reward_spec.method == "contains"``), else 0."""
 
+    LM_TOOLS_NOTE = ("LM query tools available in the REPL:\n"
+                     "- `llm_query(prompt)`: one direct call to a language model, returns str\n"
+                     "- `llm_query_batched(prompts)`: several calls at once, returns list[str]\n"
+                     "- `rlm_query(prompt)`: a child agent with its own REPL works on the prompt, returns str\n"
+                     "- `rlm_query_batched(prompts)`: several child agents side by side, returns list[str]")
+
     def __init__(self, env_config: Any = None, extras: Optional[Dict[str, Any]] = None):
         super().__init__()
         extras = extras or {}
         assert "reward_spec" in extras and "ground_truth" in extras["reward_spec"], "reward_spec.ground_truth is required"
+        self.extras = extras
         self.ground_truth = extras["reward_spec"]["ground_truth"]
         self.method = extras["reward_spec"].get("method", "exact")
         self.max_turns = int(extras.get("max_turns", 10))
         self.root_prompt = extras.get("root_prompt")
-        self.repl = PersistentREPL(extras.get("context", ""), timeout_s=float(extras.get("repl_timeout_s", 10.0)))
+        # injected by the generator (``RLMGenerator``): callables, not data
+        self.lm_callback, self.subcall_fn = extras.get("lm_callback"), extras.get("subcall_fn")
+        self.depth = int(extras.get("depth", 0))
+        context = extras.get("context")
+        if context is None:
+            context = (extras.get("extra_info") or {}).get("context_text", "")
+        self._context = context
+        self._final: Optional[str] = None
+        self._reward = 0.0
+        self.repl = PersistentREPL(context, timeout_s=float(extras.get("repl_timeout_s", extras.get(
+                                       "repl_timeout", 180.0 if self.lm_callback is not None else 10.0))),
+                                   tools=self._get_repl_tools(), lm_callback=self.lm_callback, subcall_fn=self.subcall_fn)
+
+    # ------------------------------------------------------------------ hooks for task-specific subclasses
+    def _get_repl_tools(self) -> Dict[str, Any]:
+        """Extra names for the REPL (``self._context`` is set when this runs, so closures may capture it)."""
+        return {}
+
+    def _get_system_prompt(self) -> str:
+        return ("You answer a question about a long context that does not fit in your prompt. The context is the Python "
+                "variable `context` in a persistent REPL. Inspect it by writing ```repl``` code blocks (their printed "
+                "output comes back to you), keep intermediate results in variables, and finish with FINAL(answer) or "
+                "FINAL_VAR(variable_name).{custom_tools_section}")
+
+    def _get_reward(self, final_answer: str) -> float:
+        return self._score(final_answer)
+
+    def init(self, prompt):
+        """System prompt (with the LM helpers' description when a callback is present), a note on the context's type
+        and size, then the caller's messages."""
+        tools = self._get_repl_tools()
+        section = ""
+        if self.lm_callback is not None:
+            section += "\n\n" + self.LM_TOOLS_NOTE
+        if tools:
+            section += "\n\nCustom tools and data available in the REPL: " + ", ".join(f"`{k}`" for k in sorted(tools))
+        system = self._get_system_prompt().replace("{custom_tools_section}", section)
+        c = self._context
+        size = len(c) if hasattr(c, "__len__") else 0
+        meta = f"`context` is a {type(c).__name__} of length {size}."
+        if self.root_prompt is None:
+            self.root_prompt = "\n".join(str(m.get("content", "")) for m in prompt if m.get("role") == "user") or None
+        msgs = [{"role": "system", "content": system}, {"role": "user", "content": meta}]
+        return msgs + [dict(m) for m in prompt if m.get("role") != "system"], {}
+
+    def get_metrics(self) -> Dict[str, Any]:
+        return {"turns_used": self.turns, "final_value_set": self._final is not None, "final_answer": self._final,
+                "reward": self._reward, "depth": self.depth}
 
     def _score(self, answer: Optional[str]) -> float:
         if answer is None:
@@ -110,6 +221,10 @@ class RLMEnv(BaseTextEnv):
         return ("Think step by step about what to do with the REPL (it holds `context`)" + root +
                 ". Continue by writing a ```repl``` block, or finish with FINAL(...) / FINAL_VAR(name). Your next action:")
 
+    def _finish(self, answer: str) -> BaseTextEnvStepOutput:
+        self._final, self._reward = answer, float(self._get_reward(answer))
+        return BaseTextEnvStepOutput(observations=[], reward=self._reward, done=True, metadata={"final": answer})
+
     def step(self, action: str) -> BaseTextEnvStepOutput:
         self.turns += 1
         blocks = _REPL_BLOCK.findall(action)
@@ -124,10 +239,9 @@ class RLMEnv(BaseTextEnv):
                 if self.turns >= self.max_turns:
                     return BaseTextEnvStepOutput(observations=[], reward=0.0, done=True, metadata={"final": None})
                 return BaseTextEnvStepOutput(observations=[{"role": "user", "content": msg}], reward=0.0, done=False, metadata={})
-            return BaseTextEnvStepOutput(observations=[], reward=self._score(str(val)), done=True, metadata={"final": str(val)})
+            return self._finish(str(val))
         if mf is not None and not blocks:
-            ans = mf.group(1).strip()
-            return BaseTextEnvStepOutput(observations=[], reward=self._score(ans), done=True, metadata={"final": ans})
+            return self._finish(mf.group(1).strip())
         if self.turns >= self.max_turns:
             return BaseTextEnvStepOutput(observations=[], reward=0.0, done=True, metadata={"final": None})
         parts = [f"REPL output {i + 1}:\n{o}" for i, o in enumerate(outputs)] or ["No ```repl``` block found."]

@@ -160,6 +160,12 @@ class SkyRLGymGenerator(GeneratorInterface):
                                  **self.generator_cfg.chat_template_kwargs)
         return list(full[len(self._base_ids):])
 
+    def _setup_env_extras(self, env_class: str, extras: Dict[str, Any], session_id: str,
+                          sampling_params: Optional[Dict[str, Any]]) -> Dict[str, Any]:
+        """Hook for subclasses: what the environment's constructor receives (e.g. callables that let the environment
+        query the policy itself).  Runs on the event loop, before the environment exists."""
+        return extras
+
     # ------------------------------------------------------------------ one episode
     async def agent_loop(self, prompt, env_class: str, env_extras: Dict[str, Any], max_tokens: int, max_input_length: int,
                          sampling_params: Optional[Dict[str, Any]] = None, trajectory_id: Optional[TrajectoryID] = None,
@@ -169,8 +175,9 @@ class SkyRLGymGenerator(GeneratorInterface):
         extras = dict(env_extras or {})
         extras.setdefault("max_turns", self.max_turns)
         env_cfg = getattr(self.skyrl_gym_cfg, env_class, None) if self.skyrl_gym_cfg is not None else None
-        env = skyrl_gym.make(env_class, env_config=env_cfg, extras=extras)
         session_id = trajectory_id.to_string() if trajectory_id is not None else uuid4().hex
+        extras = self._setup_env_extras(env_class, extras, session_id, sampling_params)
+        env = skyrl_gym.make(env_class, env_config=env_cfg, extras=extras)
         sp = dict(sampling_params) if sampling_params is not None else self._default_sampling_params()
         sp.setdefault("max_generate_length", max_tokens)
         step_wise = bool(self.generator_cfg.step_wise_trajectories)

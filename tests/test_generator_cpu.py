@@ -421,3 +421,81 @@ def test_step_wise_evaluation_scores_trajectories_by_their_last_step(tmp_path):
     # 3 prompts x 2 samples, two steps each; every trajectory ends with reward 1 on its last step
     assert m["eval/all/avg_score"] == pytest.approx(1.0) and m["eval/all/pass_at_2"] == pytest.approx(1.0)
     assert m["eval/toy/avg_score"] == pytest.approx(1.0)
+
+
+class _TextTok(SyntheticTokenizer):
+    """Synthetic tokenizer that can carry arbitrary text: unknown strings get ids from a growing table."""
+
+    def __init__(self):
+        super().__init__(1 << 20)
+        self.table, self.back = {}, {}
+
+    def encode(self, text, add_special_tokens=False):
+        out = []
+        for line in [text]:
+            if line not in self.table:
+                i = 1000 + len(self.table)
+                self.table[line], self.back[i] = i, line
+            out.append(self.table[line])
+        return out
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(self.back.get(int(i), "") for i in ids)
+
+
+class _PolicyScript:
+    """Answers by looking at the last user text of the request: a stand-in for a policy that writes REPL code."""
+
+    weight_version = 0
+
+    def __init__(self, tok, rules):
+        self.tok, self.rules, self.requests = tok, rules, []
+
+    async def generate(self, inp):
+        outs = []
+        for ids in inp["prompt_token_ids"]:
+            text = self.tok.decode(ids)
+            self.requests.append(text)
+            reply = next(r for key, r in self.rules if key in text)
+            if callable(reply):
+                reply = reply(text)
+            outs.append(reply)
+        return {"responses": outs, "response_ids": [self.tok.encode(o) + [EOS] for o in outs],
+                "stop_reasons": ["stop"] * len(outs), "response_logprobs": None}
+
+    async def finish_session(self, sid):
+        pass
+
+
+def test_rlm_generator_lets_the_repl_query_the_policy_and_spawn_child_episodes():
+    from types import SimpleNamespace
+
+    from skyrl_b200.train.generators.rlm_generator import RLMGenerator
+
+    tok = _TextTok()
+    # the parent: turn 1 asks a sub-agent and a plain LM call, turn 2 answers with what came back
+    parent1 = "```repl\na = rlm_query('CHILD: how many legs has a spider')\nb = llm_query('PLAIN: say hi')\nprint(a, '|', b)\n```"
+    rules = [
+        ("REPL output 1:\n8 | hi there", "FINAL(8)"),                      # parent, turn 2
+        ("CHILD: how many legs has a spider\nassistant-turn-2", "never"),  # (unused)
+        ("PLAIN: say hi", "hi there"),                                      # llm_query
+        ("`context` is a str of length 33", "FINAL(8)"),                    # the child episode (its context is the prompt)
+        ("What do spiders have?", parent1),                                 # parent, turn 1
+    ]
+    client = _PolicyScript(tok, rules)
+    g = RLMGenerator(_cfg(max_turns=4), SimpleNamespace(max_env_workers=4), client, tok, max_depth=1)
+    extras = {"reward_spec": {"ground_truth": "8"}, "context": "long document about arachnids"}
+    out = asyncio.run(g.agent_loop([{"role": "user", "content": "What do spiders have?"}], "rlm", extras, 64, 4096))
+    assert out.reward == pytest.approx([0.0] * (len(out.response_ids) - 1) + [1.0]) and out.stop_reason == "stop"
+    assert g.subcall_stats == {"lm_queries": 1, "child_episodes": 1}
+    assert out.env_metrics["final_answer"] == "8" and out.env_metrics["depth"] == 0
+    # the child saw its own system prompt and context note, not the parent's document
+    child_req = next(r for r in client.requests if "`context` is a str of length 33" in r)
+    assert "CHILD: how many legs has a spider" in child_req and "arachnids" not in child_req
+    # beyond max_depth a recursive call degrades to a plain generation
+    g0 = RLMGenerator(_cfg(max_turns=4), SimpleNamespace(max_env_workers=4), _PolicyScript(tok, [
+        ("REPL output 1:\nplain answer", "FINAL(done)"), ("CHILD: q", "plain answer"),
+        ("Question?", "```repl\nprint(rlm_query('CHILD: q'))\n```")]), tok, max_depth=0)
+    out = asyncio.run(g0.agent_loop([{"role": "user", "content": "Question?"}], "rlm",
+                                    {"reward_spec": {"ground_truth": "done"}, "context": "c"}, 64, 4096))
+    assert out.env_metrics["final_answer"] == "done" and g0.subcall_stats == {"lm_queries": 1, "child_episodes": 0}

@@ -249,3 +249,76 @@ def test_lcb_env_golden_cases():
     for response, tests, expected in ((good, two, 1.0), (wrong, one, 0.0), (silent, one, 0.0)):
         env = gym.make("lcb", env_config=None, extras={"reward_spec": {"method": "rule", "ground_truth": tests}})
         assert env.step(response)["reward"] == expected
+
+
+def _lm(prompts):
+    return [f"response:{p}" for p in prompts]
+
+
+def test_repl_lm_helpers_batching_errors_and_scaffold():
+    """The cases of skyrl-gym/tests/test_rlm.py for the REPL's LM helpers."""
+    from skyrl_b200.gym.envs.rlm import PersistentREPL
+
+    bare = PersistentREPL()
+    assert not any(k in bare.globals for k in ("llm_query", "llm_query_batched", "rlm_query", "rlm_query_batched"))
+    assert "NameError" in bare.execute("r = llm_query('test')").stdout
+    repl = PersistentREPL(lm_callback=_lm)
+    assert all(k in repl.globals for k in ("llm_query", "llm_query_batched", "rlm_query", "rlm_query_batched"))
+    assert "response:hello" in repl.execute("result = llm_query('hello')\nprint(result)").stdout
+    lines = repl.execute("results = llm_query_batched(['x', 'y'])\nprint(results[0])\nprint(results[1])").stdout.strip().splitlines()
+    assert lines == ["response:x", "response:y"]
+    assert "response:fallback prompt" in repl.execute("print(rlm_query('fallback prompt'))").stdout  # no child agent given
+    repl.execute("llm_query = lambda p, m=None: 'hijacked'")
+    assert repl.globals["llm_query"] == repl._llm_query and "response:a" in repl.execute("print(llm_query('a'))").stdout
+
+    def bad(prompts):
+        raise RuntimeError("inference error")
+
+    broken = PersistentREPL(lm_callback=bad)
+    assert "Error: LM query failed" in broken.execute("print(llm_query('t'))").stdout
+    assert "Error: LM query failed" in broken.execute("print(llm_query_batched(['a', 'b']))").stdout
+    child = PersistentREPL(lm_callback=_lm, subcall_fn=lambda p, context=None: f"child_result:{p}")
+    assert "child_result:do subtask" in child.execute("print(rlm_query('do subtask'))").stdout
+    out = child.execute("rs = rlm_query_batched(['p1', 'p2', 'p3'])\nfor r in rs:\n    print(r)").stdout.strip().splitlines()
+    assert out == ["child_result:p1", "child_result:p2", "child_result:p3"]
+
+    def flaky(p, context=None):
+        if p == "bad":
+            raise RuntimeError("boom")
+        return "ok:" + p
+
+    part = PersistentREPL(lm_callback=_lm, subcall_fn=flaky).execute("print(rlm_query_batched(['a', 'bad']))").stdout
+    assert "ok:a" in part and "Error: RLM query failed: boom" in part
+
+
+def test_rlm_env_prompts_hooks_and_metrics():
+    import skyrl_b200.gym as gym
+    from skyrl_b200.gym.envs.rlm import RLMEnv
+
+    ex = {"reward_spec": {"ground_truth": "Paris"}, "max_turns": 5, "extra_info": {"context_text": "The capital of France is Paris."}}
+    q = [{"role": "user", "content": "What is the capital of France?"}]
+    msgs, _ = gym.make("rlm", extras=dict(ex)).init(q)
+    system = next(m["content"] for m in msgs if m["role"] == "system")
+    assert "llm_query" not in system and msgs[-1] == q[0] and "context" in msgs[1]["content"]
+    env = gym.make("rlm", extras=dict(ex, lm_callback=_lm, subcall_fn=lambda p, context=None: "child_result:" + p))
+    system = next(m["content"] for m in env.init(q)[0] if m["role"] == "system")
+    assert all(k in system for k in ("llm_query", "llm_query_batched", "rlm_query", "rlm_query_batched"))
+    out = env.step("Let me ask.\n\n```repl\nanswer = llm_query('What is the capital of France?')\nprint(answer)\n```")
+    assert "response:What is the capital of France?" in out["observations"][0]["content"] and out["done"] is False
+    assert "child_result:solve this subtask" in env.step("```repl\nprint(rlm_query('solve this subtask'))\n```")["observations"][0]["content"]
+    out = env.step("```repl\nimport re\nm = re.search(r'is (\\w+)\\.', context)\nans = m.group(1)\n```")
+    out = env.step("FINAL_VAR(ans)")
+    assert out["done"] and out["reward"] == 1.0
+    assert env.get_metrics() == {"turns_used": 4, "final_value_set": True, "final_answer": "Paris", "reward": 1.0, "depth": 0}
+
+    class Counting(RLMEnv):  # a task-specific subclass: own tool, own reward
+        def _get_repl_tools(self):
+            return {"count_words": lambda: len(str(self._context).split())}
+
+        def _get_reward(self, final_answer):
+            return 0.5 if final_answer == "6" else 0.0
+
+    env = Counting(extras=dict(ex))
+    assert "`count_words`" in env.init(q)[0][0]["content"]
+    env.step("```repl\nn = count_words()\n```")
+    assert env.step("FINAL_VAR(n)")["reward"] == 0.5
