@@ -77,7 +77,15 @@ class RemotePolicyWorker:
     def forward_backward(self, batch: TrainingInputBatch, **_) -> Dict[str, float]:
         a = self.cfg.trainer.algorithm
         loss = LOSS_NAMES.get(a.policy_loss_type, a.policy_loss_type)
-        cfg = {"eps_clip_low": a.eps_clip_low, "eps_clip_high": a.eps_clip_high}
+        # the service takes Tinker's names: ratio thresholds around 1 for the clipped objectives, deltas for DPPO
+        if loss in ("ppo", "gspo"):
+            cfg = {"clip_low_threshold": 1.0 - a.eps_clip_low, "clip_high_threshold": 1.0 + a.eps_clip_high}
+        elif loss == "cispo":
+            cfg = {"clip_low_threshold": 1.0 - a.cispo.cispo_eps_clip_low, "clip_high_threshold": 1.0 + a.cispo.cispo_eps_clip_high}
+        elif loss == "dppo":
+            cfg = {"delta_low": a.dppo.delta_low, "delta_high": a.dppo.delta_high}
+        else:
+            cfg = None
         # queued, not awaited: the service runs a model's requests in order, so the optimizer step can be sent behind it
         self._pending.append(self.client.forward_backward_async(batch_to_datums(batch), loss, cfg))
         return {}

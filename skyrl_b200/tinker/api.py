@@ -43,10 +43,32 @@ def _require(body: Dict[str, Any], *keys: str) -> None:
         raise HTTPException(422, f"missing field(s): {missing}")
 
 
+# what a client may tune per request (the Tinker names; the backend maps them onto the algorithm config)
+LOSS_FN_CONFIG_KEYS = {
+    "cross_entropy": set(), "importance_sampling": set(),
+    "ppo": {"clip_low_threshold", "clip_high_threshold", "value_clip"},
+    "gspo": {"clip_low_threshold", "clip_high_threshold"}, "cispo": {"clip_low_threshold", "clip_high_threshold"},
+    "ppo_critic": {"value_clip"}, "dppo": {"delta_low", "delta_high"},
+}
+
+
 def _validate_pass_input(inp: Dict[str, Any]) -> None:
     _require(inp, "data", "loss_fn")
     if inp["loss_fn"] not in LOSS_FNS:
         raise HTTPException(422, f"loss_fn must be one of {LOSS_FNS}")
+    cfg = inp.get("loss_fn_config")
+    if cfg:
+        if not isinstance(cfg, dict):
+            raise HTTPException(422, "loss_fn_config must be an object of numbers")
+        allowed = LOSS_FN_CONFIG_KEYS[inp["loss_fn"]]
+        bad = sorted(set(cfg) - allowed)
+        if bad and allowed:
+            raise HTTPException(422, f"Invalid loss_fn_config keys for loss_fn='{inp['loss_fn']}': {bad}. "
+                                     f"Allowed keys: {sorted(allowed)}.")
+        if bad:
+            raise HTTPException(422, f"loss_fn='{inp['loss_fn']}' does not accept loss_fn_config keys. Received: {bad}.")
+        if any(isinstance(v, bool) or not isinstance(v, (int, float)) for v in cfg.values()):
+            raise HTTPException(422, "loss_fn_config values must be numbers")
     if not isinstance(inp["data"], list) or not inp["data"]:
         raise HTTPException(422, "data must be a non-empty list of datums")
     for d in inp["data"]:

@@ -196,6 +196,34 @@ class SkyRLTrainBackend:
         if torch.cuda.is_available():
             torch.cuda.empty_cache()
 
+    @staticmethod
+    def normalize_loss_fn_config(loss_fn: str, cfg: Optional[dict]) -> Optional[dict]:
+        """Tinker's per-request knobs -> fields of the algorithm config (reference: skyrl_train_backend.py:840-872).
+        Ratio thresholds are given around 1 (``clip_low_threshold=0.9`` means ``eps_clip_low=0.1``); DPPO's deltas and
+        CISPO's clips live in their nested sections; anything else (``value_clip``) keeps its name."""
+        if not cfg:
+            return None
+        out = dict(cfg)
+        lo, hi = out.pop("clip_low_threshold", None), out.pop("clip_high_threshold", None)
+        if loss_fn == "cispo":
+            nested = {}
+            if lo is not None:
+                nested["cispo_eps_clip_low"] = 1.0 - float(lo)
+            if hi is not None:
+                nested["cispo_eps_clip_high"] = float(hi) - 1.0
+            if nested:
+                out["cispo"] = nested
+        else:
+            if lo is not None:
+                out["eps_clip_low"] = 1.0 - float(lo)
+            if hi is not None:
+                out["eps_clip_high"] = float(hi) - 1.0
+        if loss_fn == "dppo":
+            nested = {k: float(out.pop(k)) for k in ("delta_low", "delta_high") if k in out}
+            if nested:
+                out["dppo"] = nested
+        return out or None
+
     # ------------------------------------------------------------------ training verbs
     def forward_backward(self, model_id: str, datums: List[dict], loss_fn: str, loss_fn_config: Optional[dict] = None,
                          forward_only: bool = False) -> Dict[str, Any]:
@@ -203,12 +231,24 @@ class SkyRLTrainBackend:
         self._activate(slot)
         batch = datums_to_batch(datums, self._pad_id(), slot.role)
         name = LOSS_ALIASES.get(loss_fn, loss_fn)
+        loss_fn_config = self.normalize_loss_fn_config(loss_fn, loss_fn_config)
+        if slot.role == "critic" and loss_fn not in ("ppo", "ppo_critic"):
+            raise ValueError(f"critic models take loss_fn 'ppo' or 'ppo_critic', got '{loss_fn}'")
+        if slot.role != "critic" and loss_fn == "ppo_critic":
+            raise ValueError("loss_fn 'ppo_critic' is only valid for critic models")
         if slot.role == "critic" or name == "ppo_critic":
             if forward_only:
                 vals = slot.worker.forward(batch)["output"]
                 outs = self._per_row(vals, batch, "values")
                 return {"loss_fn_output_type": "values", "loss_fn_outputs": outs, "metrics": {}}
-            st = slot.worker.forward_backward(batch)
+            algo = slot.worker.cfg.algorithm
+            keep = algo.value_clip
+            if loss_fn_config and "value_clip" in loss_fn_config:
+                algo.value_clip = float(loss_fn_config["value_clip"])
+            try:
+                st = slot.worker.forward_backward(batch)
+            finally:
+                algo.value_clip = keep
             return {"loss_fn_output_type": "scalar", "loss_fn_outputs": [], "metrics": self._metrics(st)}
         if forward_only:
             lp = slot.worker.forward(batch)["output"]

@@ -966,7 +966,16 @@ class PolicyWorker(ModelWorker):
 
             algo = copy.deepcopy(algo)
             for k, v in loss_fn_config.items():
-                setattr(algo, k, v)
+                if not hasattr(algo, k):
+                    raise ValueError(f"loss_fn_config: the algorithm config has no field '{k}'")
+                if isinstance(v, dict):  # nested section (dppo, cispo, sapo ...): set its fields
+                    node = getattr(algo, k)
+                    for kk, vv in v.items():
+                        if not hasattr(node, kk):
+                            raise ValueError(f"loss_fn_config: '{k}' has no field '{kk}'")
+                        setattr(node, kk, vv)
+                else:
+                    setattr(algo, k, v)
         loss_name = loss_fn or algo.policy_loss_type
         loss_name = {"ppo": "regular"}.get(loss_name, loss_name)
         if loss_name != algo.policy_loss_type:

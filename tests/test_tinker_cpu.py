@@ -239,3 +239,55 @@ def test_lora_models_share_one_base_and_keep_their_own_state(tmp_path):
     be.forward_backward("b", data_b, "cross_entropy")
     be.delete_model("b")
     assert not be._lora_hosts and be.engine is None
+
+
+def test_loss_fn_config_keys_are_validated_and_mapped_onto_the_algorithm_config():
+    from fastapi import HTTPException
+
+    from skyrl_b200.tinker.api import _validate_pass_input
+
+    N = SkyRLTrainBackend.normalize_loss_fn_config
+    assert N("ppo", {"clip_low_threshold": 0.9, "clip_high_threshold": 1.25}) == pytest.approx({"eps_clip_low": 0.1, "eps_clip_high": 0.25})
+    assert N("gspo", {"clip_high_threshold": 1.0004}) == pytest.approx({"eps_clip_high": 0.0004})
+    assert N("dppo", {"delta_low": 0.2, "delta_high": 0.3}) == {"dppo": {"delta_low": 0.2, "delta_high": 0.3}}
+    got = N("cispo", {"clip_low_threshold": 0.0, "clip_high_threshold": 5.0})
+    assert got == {"cispo": {"cispo_eps_clip_low": 1.0, "cispo_eps_clip_high": 4.0}}
+    assert N("ppo_critic", {"value_clip": 0.2}) == {"value_clip": 0.2} and N("ppo", None) is None and N("ppo", {}) is None
+
+    datum = _datum([1, 2, 3, 4])
+    datum["loss_fn_inputs"].update({"logprobs": {"data": [-1.0] * 3}, "advantages": {"data": [0.5] * 3}})
+    ok = lambda fn, cfg: _validate_pass_input({"data": [datum], "loss_fn": fn, "loss_fn_config": cfg})  # noqa: E731
+    ok("ppo", {"clip_low_threshold": 0.9, "clip_high_threshold": 1.1})
+    ok("ppo", {"value_clip": 0.2})
+    ok("ppo_critic", {"value_clip": 0.2})
+    ok("dppo", {"delta_low": 0.2, "delta_high": 0.2})
+    for fn, cfg, msg in (("dppo", {"clip_low_threshold": 0.9}, "Invalid loss_fn_config keys"),
+                         ("ppo", {"clip_ratio": 0.2}, "Invalid loss_fn_config keys"),
+                         ("cross_entropy", {"clip_low_threshold": 0.9}, "does not accept loss_fn_config keys"),
+                         ("ppo", {"value_clip": "x"}, "must be numbers")):
+        with pytest.raises(HTTPException) as e:
+            ok(fn, cfg)
+        assert e.value.status_code == 422 and msg in e.value.detail
+
+
+def test_backend_applies_tinker_clip_thresholds(tmp_path):
+    """The sampled tokens are far less likely under the model than the given log-probs say (ratio near 0) and their
+    advantages are negative: a tight lower threshold clips them (no gradient), a lower threshold of 0 does not."""
+    from skyrl_b200.parallel import dist as pdist
+
+    pdist.reset_env_for_tests()
+    ov = {"trainer.bf16": "false", "trainer.gradient_checkpointing": "false", "trainer.policy.optimizer_config.max_grad_norm": 1e9}
+    be = SkyRLTrainBackend("tiny-llama", ov, tokenizer=SyntheticTokenizer(1024), checkpoints_base=str(tmp_path))
+    be.create_model("m", None)
+    toks = [5, 6, 7, 8, 9, 10]
+    d = _datum(toks)
+    n = len(toks) - 1
+    d["loss_fn_inputs"].update({"logprobs": {"data": [-0.05] * n, "dtype": "float32", "shape": [n]},      # far from the
+                                "advantages": {"data": [-1.0] * n, "dtype": "float32", "shape": [n]}})      # model's own
+    be.forward_backward("m", [d], "ppo", {"clip_low_threshold": 0.999, "clip_high_threshold": 1.001})
+    tight = float(be.optim_step("m", {"learning_rate": 0.0})["metrics"]["grad_norm"])
+    be.forward_backward("m", [d], "ppo", {"clip_low_threshold": 0.0, "clip_high_threshold": 1e9})
+    loose = float(be.optim_step("m", {"learning_rate": 0.0})["metrics"]["grad_norm"])
+    assert loose > 0 and tight < 1e-3 * loose
+    with pytest.raises(ValueError, match="only valid for critic"):
+        be.forward_backward("m", [d], "ppo_critic", None)
