@@ -92,3 +92,28 @@ def test_delta_publish_fetch_replay_and_recovery(tmp_path):
     fresh = LocalCheckpointStore(sync, str(tmp_path / "local2"))
     with pytest.raises(Exception):
         fresh.fetch(1)
+
+
+def test_delta_publish_of_unchanged_weights_still_advances_the_version(tmp_path):
+    m = _model(3)
+    sync = str(tmp_path / "sync")
+    pub = DeltaPublisher(sync)
+    pub.publish_base(hf_io.to_hf_state_dict(m))
+    d = pub.publish(hf_io.to_hf_state_dict(m))
+    man = json.load(open(os.path.join(d, "manifest.json")))
+    assert d.endswith("delta-00000001") and not any(e["changed"] for e in man["tensors"])
+    store = LocalCheckpointStore(sync, str(tmp_path / "local"))
+    assert store.fetch(1) == 1
+    want = hf_io.to_hf_state_dict(m)
+    assert all(torch.equal(t, want[k]) for k, t in store.state_dict().items())
+    # a late joiner replays every version it missed
+    with torch.no_grad():
+        m.p("final_norm").mul_(1.5)
+    pub.publish(hf_io.to_hf_state_dict(m))
+    with torch.no_grad():
+        m.p("layers.0.wo").add_(0.25)
+    pub.publish(hf_io.to_hf_state_dict(m))
+    late = LocalCheckpointStore(sync, str(tmp_path / "late"))
+    assert late.fetch(3) == 3
+    want = hf_io.to_hf_state_dict(m)
+    assert all(torch.equal(t, want[k]) for k, t in late.state_dict().items())
