@@ -52,6 +52,24 @@ def entropy_from_logits(logits: torch.Tensor) -> torch.Tensor:
     return -(lp.exp() * lp).sum(-1)
 
 
-def chunked_entropy_from_logits(logits: torch.Tensor, chunk: int = 1024) -> torch.Tensor:
-    out = [entropy_from_logits(logits[:, i : i + chunk]) for i in range(0, logits.shape[1], chunk)]
-    return torch.cat(out, dim=1)
+def chunked_entropy_from_logits(logits: torch.Tensor, chunk: int = 1024, attention_mask: Optional[torch.Tensor] = None,
+                                requires_grad: bool = False) -> torch.Tensor:
+    """Entropy of every position of ``[B, S, V]`` logits, ``chunk`` positions at a time; positions with
+    ``attention_mask == 0`` get 0 (reference: utils/torch_utils.py ``chunked_entropy_from_logits``).  The training
+    path never calls this -- the fused LM-head kernel yields the entropy without logits -- it is here for code written
+    against logits."""
+    if attention_mask is not None and tuple(attention_mask.shape) != tuple(logits.shape[:2]):
+        raise ValueError(f"attention_mask shape {tuple(attention_mask.shape)} does not match logits shape {tuple(logits.shape[:2])}")
+    with torch.set_grad_enabled(requires_grad):
+        out = torch.cat([entropy_from_logits(logits[:, i : i + chunk]) for i in range(0, logits.shape[1], chunk)], dim=1)
+    return out * attention_mask.to(out.dtype) if attention_mask is not None else out
+
+
+def chunked_cross_entropy_from_log_probs(logprobs: torch.Tensor, chunk: int = 1024, requires_grad: bool = False) -> torch.Tensor:
+    """``-sum_v p_v log p_v`` per position from ``[B, S, V]`` log-probabilities (same role as above)."""
+    with torch.set_grad_enabled(requires_grad):
+        parts = []
+        for i in range(0, logprobs.shape[1], chunk):
+            lp = logprobs[:, i : i + chunk].float()
+            parts.append(-(lp.exp() * lp).sum(-1))
+        return torch.cat(parts, dim=1)

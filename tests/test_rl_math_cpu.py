@@ -432,3 +432,24 @@ def test_off_policy_correction_composes_and_feeds_ppo_loss():
     cfg.off_policy_correction.geo_mask_high = 1.1  # now every sequence is rejected
     got, _ = rl.ppo_policy_loss(lp, old, adv, cfg, loss_mask=mask, rollout_logprobs=roll)
     assert float(got) == 0.0
+
+
+def test_chunked_entropy_helpers_for_code_written_against_logits():
+    import math
+
+    from skyrl_b200.utils.torch_utils import chunked_cross_entropy_from_log_probs, chunked_entropy_from_logits
+
+    logits = torch.tensor([[[1.0, 2.0, 3.0, 4.0], [1.0, 0.0, 0.0, 0.0], [0.0, 0.0, 0.0, 0.0]],
+                           [[0.0, 0.0, 0.0, 0.0], [1.0, 2.0, 3.0, 4.0], [4.0, 3.0, 2.0, 1.0]]])
+    for got in (chunked_entropy_from_logits(logits, chunk=2), chunked_cross_entropy_from_log_probs(torch.log_softmax(logits, -1), chunk=2)):
+        assert got.shape == (2, 3) and torch.allclose(got[0, 2], torch.tensor(math.log(4.0)), atol=1e-4)
+        assert torch.allclose(got[1, 0], torch.tensor(math.log(4.0)), atol=1e-4) and torch.allclose(got[0, 0], got[1, 1])
+    x = torch.randn(2, 4, 4)
+    mask = torch.tensor([[1, 1, 1, 1], [1, 1, 0, 0]], dtype=torch.float32)
+    masked, free = chunked_entropy_from_logits(x, attention_mask=mask), chunked_entropy_from_logits(x)
+    assert masked[1, 2] == 0 and masked[1, 3] == 0 and torch.allclose(masked[0], free[0]) and torch.allclose(masked[1, :2], free[1, :2])
+    for bad in (torch.ones(3, 4), torch.ones(2, 5)):
+        with pytest.raises(ValueError, match="does not match logits shape"):
+            chunked_entropy_from_logits(x, attention_mask=bad)
+    y = torch.randn(1, 3, 5, requires_grad=True)
+    assert not chunked_entropy_from_logits(y).requires_grad and chunked_entropy_from_logits(y, requires_grad=True).requires_grad
