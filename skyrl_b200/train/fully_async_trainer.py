@@ -183,7 +183,12 @@ class FullyAsyncPPOTrainer(PPOTrainer):
                 raise
 
     def _zero_variance(self, out) -> bool:
-        scores = [float(np.sum(r)) if isinstance(r, (list, tuple)) else float(r) for r in out["rewards"]]
+        """All *live* trajectories of the group (those with a non-zero loss mask) earned the same total reward, within
+        the tolerance: nothing to learn from.  A single live trajectory is kept (reference: fully_async_trainer.py
+        ``_should_keep_group``)."""
+        masks = out.get("loss_masks") or [[1]] * len(out["rewards"])
+        scores = [float(np.sum(r)) if isinstance(r, (list, tuple)) else float(r)
+                  for r, m in zip(out["rewards"], masks) if any(m)]
         return len(scores) > 1 and (max(scores) - min(scores)) <= self.cfg.trainer.algorithm.zero_variance_filter_tol
 
     async def _collect_mini_batch(self) -> Optional[List[Dict[str, Any]]]:

@@ -126,3 +126,19 @@ def test_one_step_off_trainer_overlaps_generation_and_training(tmp_path):
     assert tr.global_step == 3
     assert not torch.equal(tr.policy.model.flat_params, before)
     assert torch.equal(tr.engine.model.flat_params, tr.policy.model.flat_params)  # last sync published the weights
+
+
+def test_zero_variance_group_filter_ignores_masked_trajectories():
+    from types import SimpleNamespace
+
+    def zv(tol, rewards, masks):
+        fake = SimpleNamespace(cfg=SimpleNamespace(trainer=SimpleNamespace(algorithm=SimpleNamespace(zero_variance_filter_tol=tol))))
+        return FullyAsyncPPOTrainer._zero_variance(fake, {"rewards": rewards, "loss_masks": masks})
+
+    assert zv(0.0, [1.0, 1.0], [[1], [1]]) is True          # nothing to learn from: dropped
+    assert zv(0.0, [1.0, 0.0], [[1], [1]]) is False
+    assert zv(0.0, [1.0], [[1]]) is False                    # a single trajectory is kept
+    assert zv(0.0, [1.0, 1.0, 0.0], [[1], [1], [0]]) is True  # the masked one does not count
+    assert zv(1e-6, [0.6667, 0.66670001], [[1], [1]]) is True
+    assert zv(0.0, [[0.0, 1.0], [1.0, 0.0]], [[1, 1], [1, 1]]) is True   # token-level rewards: compared by their sums
+    assert zv(0.0, [[0.0, 1.0], [0.0, 0.0]], [[1, 1], [1, 1]]) is False
