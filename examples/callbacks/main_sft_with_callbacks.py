@@ -14,29 +14,36 @@ from skyrl_b200.train.sft_trainer import SFTTrainer
 
 
 class PerplexityLogger(TrainingCallback):
-    """Adds exp(loss) to the step metrics and prints a running minimum on the main rank."""
+    """Adds exp(loss) to what goes to the tracker and prints a running minimum on the main rank."""
 
     def __init__(self):
         self.best = float("inf")
 
-    def on_step_end(self, trainer, metrics=None, control=None):
-        if not metrics or "loss" not in metrics:
+    def on_log(self, trainer, callback_input, control):
+        logs = callback_input.logs or {}
+        if "train/loss" not in logs:
             return
-        ppl = math.exp(min(20.0, float(metrics["loss"])))
-        metrics["perplexity"] = ppl
+        ppl = math.exp(min(20.0, float(logs["train/loss"])))
+        logs["train/perplexity"] = ppl  # in place: the trainer commits this dict
         self.best = min(self.best, ppl)
         if trainer.env.is_main:
-            print(f"[callback] step {metrics.get('step', '?')}: perplexity {ppl:.3f} (best {self.best:.3f})", flush=True)
+            print(f"[callback] step {callback_input.global_step}/{callback_input.total_steps}: perplexity {ppl:.3f} "
+                  f"(best {self.best:.3f})", flush=True)
 
 
 class StopAtLoss(TrainingCallback):
     def __init__(self, target: float):
         self.target = target
 
-    def on_step_end(self, trainer, metrics=None, control=None):
-        if metrics and float(metrics.get("loss", float("inf"))) <= self.target and control is not None:
+    def on_step_end(self, trainer, callback_input, control):
+        m = callback_input.metrics or {}
+        if float(m.get("train/loss", float("inf"))) <= self.target:
             control.should_save = True
             control.should_stop = True
+
+    def on_save(self, trainer, callback_input, control):
+        if trainer.env.is_main:
+            print(f"[callback] checkpoint written to {callback_input.ckpt_path}", flush=True)
 
 
 if __name__ == "__main__":

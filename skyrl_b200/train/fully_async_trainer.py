@@ -279,9 +279,13 @@ class FullyAsyncPPOTrainer(PPOTrainer):
                 metrics = dict(self.all_metrics)
                 metrics.update({f"timing/{k}": v for k, v in self.all_timings.items()})
                 metrics["trainer/global_step"] = float(self.global_step)
+                ctl = self.callbacks.fire("on_step_end", self, metrics=metrics)
+                want_save = ctl.should_save
+                ctl.reset()
+                self.callbacks.fire("on_log", self, logs=metrics)
                 self._log(metrics, self.global_step)
-                for cb in self.callbacks:
-                    cb.on_step_end(self, metrics)
+                if want_save and not (t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0):
+                    self.save_checkpoints()
                 if t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0:
                     self.save_checkpoints()
                 if max_steps is not None and self.global_step >= max_steps:

@@ -263,20 +263,22 @@ class SFTTrainer:
         self.sampler = self.build_train_sampler(examples)
         self.global_step = self.load_checkpoint()
         total = self._resolve_num_steps(len(self.sampler))
-        self.callbacks.fire("on_train_begin", self)
+        self.total_steps, self.steps_per_epoch, self.epoch = total, len(self.sampler), self.sampler.epoch
+        self.callbacks.fire("on_train_start", self)
         if c.eval_before_train and self.global_step == 0:
             ev = self.run_eval()
             if ev:
                 self._log(ev, 0)
         done = self.global_step >= total
         while not done:
-            self.callbacks.fire("on_epoch_begin", self, epoch=self.sampler.epoch)
+            self.epoch = self.sampler.epoch
+            self.callbacks.fire("on_epoch_start", self)
             for idx in self.sampler:
                 t0 = time.perf_counter()
                 batch = sft_data.collate_sft_examples([examples[i] for i in idx], self.collator, c.batch_size,
                                                       pad_to_batch_size=not c.use_sequence_packing)
                 t_collate = time.perf_counter() - t0
-                self.callbacks.fire("on_step_begin", self)
+                self.callbacks.fire("on_step_start", self, batch=batch)
                 r = self.train_step(batch, self.global_step + 1)
                 self.global_step += 1
                 dt = time.perf_counter() - t0
@@ -285,23 +287,25 @@ class SFTTrainer:
                         "train/tokens_per_second": float(batch["attention_mask"].sum()) / dt,
                         "timing/step": dt, "timing/collate": t_collate,
                         **{f"timing/{k}": v for k, v in r["timings"].items()}}
-                ctl = self.callbacks.fire("on_step_end", self, metrics=last)
-                want_eval = (c.eval_interval > 0 and self.global_step % c.eval_interval == 0) or ctl.should_evaluate
-                if want_eval:
+                ctl = self.callbacks.fire("on_step_end", self, batch=batch, metrics=last)
+                # the flags are read once per step, here; what later events of this step set counts for the next step
+                want_save, want_eval_flag, stop = ctl.should_save, ctl.should_evaluate, ctl.should_stop
+                ctl.reset()
+                if (c.eval_interval > 0 and self.global_step % c.eval_interval == 0) or want_eval_flag:
+                    self.callbacks.fire("on_eval_start", self)
                     ev = self.run_eval()
                     last.update(ev)
-                    self.callbacks.fire("on_evaluate", self, metrics=ev)
+                    self.callbacks.fire("on_eval_end", self, metrics=ev)
+                self.callbacks.fire("on_log", self, logs=last)
                 self._log(last, self.global_step)
-                if (c.ckpt_interval > 0 and self.global_step % c.ckpt_interval == 0) or ctl.should_save:
+                if (c.ckpt_interval > 0 and self.global_step % c.ckpt_interval == 0) or want_save:
                     self.save_checkpoint()
                 if c.hf_save_interval > 0 and self.global_step % c.hf_save_interval == 0:
                     self.save_hf_model()
-                stop = getattr(ctl, "should_stop", False)
-                ctl.reset()
                 if self.global_step >= total or stop:
                     done = True
                     break
-            self.callbacks.fire("on_epoch_end", self, epoch=self.sampler.epoch)
+            self.callbacks.fire("on_epoch_end", self)
         if c.ckpt_interval > 0 and c.ckpt_path:
             self.save_checkpoint()
         self.callbacks.fire("on_train_end", self)
@@ -325,7 +329,7 @@ class SFTTrainer:
         if self.env.is_main:
             tutils.write_latest(c.ckpt_path, self.global_step)
             tutils.cleanup_old_checkpoints(c.ckpt_path, c.max_ckpts_to_keep, self.global_step)
-        self.callbacks.fire("on_save", self, path=d)
+        self.callbacks.fire("on_save", self, ckpt_path=d)
         return d
 
     def load_checkpoint(self) -> int:

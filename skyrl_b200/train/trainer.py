@@ -34,6 +34,7 @@ from ..parallel.dist import DistEnv, get_env
 from ..workers.worker import CriticWorker, PolicyWorker, RefWorker
 from . import utils as tutils
 from .batch import TrainingInputBatch, pad_training_input_batch
+from .callbacks import CallbackHandler
 from .dataset import PromptDataset, StatefulBatchIterator
 from .generators.base import GeneratorInput, GeneratorInterface, GeneratorOutput
 from .generators.skyrl_gym_generator import SkyRLGymGenerator
@@ -67,7 +68,7 @@ class PPOTrainer:
         self.all_timings: Dict[str, float] = {}
         self.kl_controller = rl.get_kl_controller(cfg.trainer.algorithm) if cfg.trainer.algorithm.use_kl_in_reward else None
         self.train_iter: Optional[StatefulBatchIterator] = None
-        self.callbacks: List[Any] = []
+        self.callbacks = CallbackHandler([])  # add with trainer.callbacks.add(cb) (or append: it is list-like enough)
         self.dynamic_sampler = None
         tutils.validate_cfg(cfg, self.env.world_size)
         torch.manual_seed(cfg.trainer.seed + self.env.rank)
@@ -640,30 +641,39 @@ class PPOTrainer:
         total = t.epochs * len(self.train_iter)
         if t.max_training_steps is not None:
             total = min(total, t.max_training_steps)
-        for cb in self.callbacks:
-            cb.on_train_begin(self)
+        self.total_steps, self.steps_per_epoch, self.epoch = total, len(self.train_iter), self.train_iter.epoch
+        self.callbacks.fire("on_train_start", self)
         self.policy.start_profile()
         if getattr(t.policy, "record_memory", False):
             self.policy.record_memory_history(True)
         done = False
         while self.train_iter.epoch < t.epochs and not done:
+            self.epoch = self.train_iter.epoch
+            self.callbacks.fire("on_epoch_start", self)
             for global_batch in self.train_iter:
+                self.callbacks.fire("on_step_start", self, batch=global_batch)
                 metrics = await self.train_step_async(self._local_prompts(global_batch))
                 if metrics.get("trainer/keep_sampling"):
                     continue  # dynamic sampling wants more rollouts before this RL step can train
-                if t.eval_interval > 0 and self.eval_dataset is not None and self.global_step % t.eval_interval == 0:
-                    metrics.update(await self.eval_async())
+                ctl = self.callbacks.fire("on_step_end", self, batch=getattr(self, "_last_batch", None), metrics=metrics)
+                want_save, want_eval, stop = ctl.should_save, ctl.should_evaluate, ctl.should_stop
+                ctl.reset()
+                if self.eval_dataset is not None and (want_eval or (t.eval_interval > 0 and self.global_step % t.eval_interval == 0)):
+                    self.callbacks.fire("on_eval_start", self)
+                    ev = await self.eval_async()
+                    metrics.update(ev)
+                    self.callbacks.fire("on_eval_end", self, metrics=ev)
+                self.callbacks.fire("on_log", self, logs=metrics)
                 self._log(metrics, self.global_step)
                 self.policy.profile_step()  # one profiler step per RL step
-                for cb in self.callbacks:
-                    cb.on_step_end(self, metrics)
-                if t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0:
+                if want_save or (t.ckpt_interval > 0 and self.global_step % t.ckpt_interval == 0):
                     self.save_checkpoints()
                 if t.hf_save_interval > 0 and self.global_step % t.hf_save_interval == 0:
                     self.save_models()
-                if self.global_step >= total:
+                if self.global_step >= total or stop:
                     done = True
                     break
+            self.callbacks.fire("on_epoch_end", self)
             if t.update_ref_every_epoch and self.ref is not None:
                 self.update_ref_with_policy()
         if t.ckpt_interval > 0:
@@ -673,8 +683,7 @@ class PPOTrainer:
             print(summary)
         if getattr(t.policy, "record_memory", False):
             self.policy.dump_memory_snapshot(os.path.join(t.log_path, "memory_snapshots"), f"step{self.global_step}")
-        for cb in self.callbacks:
-            cb.on_train_end(self)
+        self.callbacks.fire("on_train_end", self)
 
     def _log_examples(self, out: GeneratorOutput, uids: List[str]) -> None:
         """Rank 0: one decoded example every ``trainer.print_example_interval`` steps (reference: trainer.py:394-403) and
@@ -742,6 +751,7 @@ class PPOTrainer:
         if self.env.is_main:
             tutils.write_latest(t.ckpt_path, self.global_step)
             tutils.cleanup_old_checkpoints(t.ckpt_path, t.max_ckpts_to_keep, self.global_step)
+        self.callbacks.fire("on_save", self, ckpt_path=d)
 
     def load_checkpoints(self) -> int:
         d = tutils.resolve_resume_path(self.cfg.trainer)

@@ -108,3 +108,44 @@ def test_dummy_run(tok, tmp_path):
                                         "dummy_run_full_ctx=true", "dummy_run_max_steps=2", f"log_path={tmp_path}"])
     out = SFTTrainer(cfg, tokenizer=tok).setup().train()
     assert out["train/tokens_per_second"] > 0
+
+
+def test_sft_loop_fires_reference_style_callbacks(tok, tmp_path):
+    """Event names, argument order and per-event fields of the reference's callback interface; control flags set in
+    on_step_end are honoured in the same step (an evaluation after step 1, a checkpoint and a stop after step 2)."""
+    from skyrl_b200.train.callbacks import EVENTS, TrainingCallback
+
+    class Rec(TrainingCallback):
+        seen = []
+
+    rec = Rec()
+    for name in EVENTS:
+        def handler(trainer, ci, control, name=name):
+            rec.seen.append((name, ci.global_step, ci.ckpt_path is not None, ci.metrics is not None, ci.batch is not None))
+            if name == "on_step_end" and ci.global_step == 1:
+                control.should_evaluate = True
+            if name == "on_step_end" and ci.global_step == 2:
+                control.should_save = True
+                control.should_stop = True
+            if name == "on_log":
+                ci.logs["custom/x"] = 7.0
+
+        setattr(rec, name, handler)
+    cfg = SFTConfig.from_cli_overrides([
+        "model.path=tiny-qwen2-d128", "batch_size=8", "micro_train_batch_size_per_gpu=4", "num_steps=6",
+        "optimizer_config.lr=1e-3", f"ckpt_path={tmp_path}/ckpt", "ckpt_interval=0", "disable_cache=true", "bf16=false",
+        f"log_path={tmp_path}/logs", "sampler=sequential", "eval_interval=0", "eval_before_train=false"])
+    ex = _examples(tok)
+    tr = SFTTrainer(cfg, tokenizer=tok, train_examples=ex, eval_examples=[("held", ex[:8])]).setup()
+    tr.add_callback(rec)
+    last = tr.train()
+    names = [e[0] for e in rec.seen]
+    assert names == ["on_train_start", "on_epoch_start",
+                     "on_step_start", "on_step_end", "on_eval_start", "on_eval_end", "on_log",
+                     "on_step_start", "on_step_end", "on_log", "on_save",
+                     "on_epoch_end", "on_train_end"]
+    assert tr.global_step == 2 and last["custom/x"] == 7.0 and "eval/held/loss" not in last
+    ev = next(e for e in rec.seen if e[0] == "on_eval_end")
+    assert ev[1] == 1 and ev[3]
+    assert next(e for e in rec.seen if e[0] == "on_save")[2] and next(e for e in rec.seen if e[0] == "on_step_start")[4]
+    assert os.path.isdir(os.path.join(str(tmp_path), "ckpt", "global_step_2", "policy"))

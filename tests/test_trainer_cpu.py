@@ -222,3 +222,67 @@ def test_mtp_enabled_trainer_drafts_with_the_head_it_trains(tmp_path):
                      tokenizer=SyntheticTokenizer(1024))
     tr2.build_models()
     assert tr2.engine.draft_head is None and tr2.policy.mtp_head is not None
+
+
+class _Recorder:
+    """Records every event with the fields that were set, and asks for a save + stop after the second step."""
+
+    def __init__(self):
+        from skyrl_b200.train.callbacks import EVENTS
+
+        self.events = []
+        for name in EVENTS:
+            setattr(self, name, self._make(name))
+
+    def _make(self, name):
+        def handler(trainer, ci, control):
+            self.events.append((name, ci.global_step, ci.epoch, sorted(k for k in ("batch", "metrics", "logs", "ckpt_path")
+                                                                         if getattr(ci, k) is not None)))
+            if name == "on_log":
+                ci.logs["custom/from_callback"] = 1.0
+            if name == "on_step_end" and ci.global_step == 2:
+                control.should_save = True
+                control.should_stop = True
+
+        return handler
+
+
+def test_rl_training_loop_fires_callbacks_in_order_and_honours_control(tmp_path):
+    import pandas as pd
+
+    from skyrl_b200.train.dataset import PromptDataset
+
+    pdist.reset_env_for_tests()
+    rows = [{"prompt": [{"role": "user", "content": f"{10 + i} {20 + i}"}], "env_class": "synthetic_even", "uid": f"q{i}"}
+            for i in range(16)]
+    path = str(tmp_path / "train.parquet")
+    pd.DataFrame(rows).to_parquet(path)
+    cfg = _cfg(tmp_path, ["trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "generator.n_samples_per_prompt=2",
+                          "trainer.epochs=3", "trainer.eval_interval=0", "trainer.eval_before_train=false",
+                          "trainer.ckpt_interval=0", "trainer.hf_save_interval=0", "generator.sampling_params.max_generate_length=8"])
+    tok = SyntheticTokenizer(1024)
+    logged = []
+
+    class Tracker:
+        def log(self, metrics, step):
+            logged.append((step, dict(metrics)))
+
+        def finish(self):
+            pass
+
+    tr = PPOTrainer(cfg, tracker=Tracker(), tokenizer=tok, train_dataset=PromptDataset([path], tok, 64))
+    rec = _Recorder()
+    tr.callbacks.add(rec)
+    tr.build_models()
+    tr.train()
+    names = [e[0] for e in rec.events]
+    assert names == ["on_train_start", "on_epoch_start",
+                     "on_step_start", "on_step_end", "on_log",
+                     "on_step_start", "on_step_end", "on_log", "on_save",   # the callback asked for a checkpoint and a stop
+                     "on_epoch_end", "on_train_end"]
+    by = {(n, s): f for n, s, _, f in rec.events}
+    assert by[("on_step_start", 0)] == ["batch"] and by[("on_step_end", 1)] == ["batch", "metrics"]
+    assert by[("on_log", 2)] == ["logs"] and by[("on_save", 2)] == ["ckpt_path"]
+    assert tr.global_step == 2 and os.path.isdir(os.path.join(cfg.trainer.ckpt_path, "global_step_2"))
+    assert [s for s, _ in logged] == [1, 2] and all(m["custom/from_callback"] == 1.0 for _, m in logged)
+    assert tr.total_steps == 12 and tr.steps_per_epoch == 4
