@@ -68,6 +68,9 @@ class PPOTrainer:
         self.all_timings: Dict[str, float] = {}
         self.kl_controller = rl.get_kl_controller(cfg.trainer.algorithm) if cfg.trainer.algorithm.use_kl_in_reward else None
         self.train_iter: Optional[StatefulBatchIterator] = None
+        from ..workers.dispatch import WorkerDispatch
+
+        self.dispatch = WorkerDispatch(self)  # the reference's worker verbs by role name (trainer.dispatch.forward(...))
         self.callbacks = CallbackHandler([])  # add with trainer.callbacks.add(cb) (or append: it is list-like enough)
         self.dynamic_sampler = None
         tutils.validate_cfg(cfg, self.env.world_size)
@@ -715,6 +718,10 @@ class PPOTrainer:
         with open(path, "wb") as f:
             f.write(batch.to_bytes())
         return path
+
+    def init_weight_sync_state(self) -> None:
+        """Kept for trainer subclasses written against the reference: there is no state to set up here."""
+        self.dispatch.init_weight_sync_state(self.inference_engine_client)
 
     def _log(self, metrics: Dict[str, float], step: int) -> None:
         if self.tracker is not None and self.env.is_main:

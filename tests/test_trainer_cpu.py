@@ -286,3 +286,34 @@ def test_rl_training_loop_fires_callbacks_in_order_and_honours_control(tmp_path)
     assert tr.global_step == 2 and os.path.isdir(os.path.join(cfg.trainer.ckpt_path, "global_step_2"))
     assert [s for s, _ in logged] == [1, 2] and all(m["custom/from_callback"] == 1.0 for _, m in logged)
     assert tr.total_steps == 12 and tr.steps_per_epoch == 4
+
+
+def test_dispatch_facade_offers_the_reference_worker_verbs(tmp_path):
+    import asyncio
+
+    pdist.reset_env_for_tests()
+    tr = PPOTrainer(_cfg(tmp_path), tokenizer=SyntheticTokenizer(1024))
+    tr.build_models()
+    d = tr.dispatch
+    assert d.has("policy") and d.has("ref") and not d.has("critic") and d.dp_size("policy") == 1 and d.get_lcm_dp_size() == 1
+    tr.train_step(_prompts())
+    batch = tr._last_batch
+    lp = d.forward("policy", batch)["output"]
+    assert lp.shape == batch["response_mask"].shape
+    w0 = tr.policy.model.flat_params.clone()
+    d.set_lr("policy", 1e-4)
+    assert tr.policy.get_lr() == 1e-4
+    st = d.forward_backward("policy", batch, loss_fn="regular", loss_fn_config={"eps_clip_low": 0.1})
+    assert "final_loss" in st and d.optim_step("policy") is not None and not torch.equal(w0, tr.policy.model.flat_params)
+    v = tr.engine.weight_version
+    tr.init_weight_sync_state()
+    asyncio.run(d.save_weights_for_sampler())
+    assert tr.engine.weight_version == v + 1
+    d.set_algorithm_config("policy", eps_clip_high=0.3)
+    assert tr.policy.cfg.algorithm.eps_clip_high == 0.3
+    d.save_checkpoint("policy", str(tmp_path / "p"))
+    d.load_checkpoint("policy", str(tmp_path / "p"))
+    with pytest.raises(ValueError, match="no 'critic' worker"):
+        d.forward("critic", batch)
+    with pytest.raises(ValueError, match="unknown model role"):
+        d.optim_step("reward")
