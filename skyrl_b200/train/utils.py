@@ -136,6 +136,20 @@ def validate_cfg(cfg, world_size: int = 1) -> None:
         raise ValueError(f"invalid kl_estimator_type '{a.kl_estimator_type}'")
     if a.use_kl_in_reward and a.use_kl_loss:
         raise ValueError("use_kl_in_reward and use_kl_loss are mutually exclusive")
+    if t.max_training_steps is not None and t.max_training_steps <= 0:
+        raise ValueError(f"max_training_steps must be > 0, got {t.max_training_steps}")
+    lp = g.sampling_params.logprobs
+    if lp is not None and (isinstance(lp, bool) or not isinstance(lp, int) or lp > 1 or lp < 0):
+        raise ValueError(f"`logprobs` if set should be 0 or 1 (both return only the chosen token's logprob), got {lp!r}")
+    if g.max_input_length is not None and g.max_input_length < t.max_prompt_length:
+        raise ValueError(f"generator.max_input_length ({g.max_input_length}) must be at least trainer.max_prompt_length "
+                         f"({t.max_prompt_length})")
+    if t.mtp.enabled and t.mtp.num_speculative_tokens < 1:
+        raise ValueError("trainer.mtp.num_speculative_tokens must be >= 1 when trainer.mtp.enabled")
+    if t.update_epochs_per_batch < 1:
+        raise ValueError("trainer.update_epochs_per_batch must be >= 1")
+    if g.n_samples_per_prompt < 1 or g.eval_n_samples_per_prompt < 1:
+        raise ValueError("generator.n_samples_per_prompt and eval_n_samples_per_prompt must be >= 1")
     if a.advantage_estimator == "gae" and t.critic.model.path is None:
         raise ValueError("advantage_estimator='gae' needs a critic: set trainer.critic.model.path")
     if a.use_tis:

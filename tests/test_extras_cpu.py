@@ -296,3 +296,20 @@ def test_torch_profiler_config_validation():
                                                "trainer.policy.model.path=tiny-llama"])
     with pytest.raises(ValueError, match="export_type"):
         validate_cfg(cfg)
+
+
+def test_validate_cfg_rejects_out_of_range_knobs():
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.train.utils import validate_cfg
+
+    base = ["trainer.policy.model.path=tiny-llama"]
+    validate_cfg(SkyRLTrainConfig.from_cli_overrides(base))
+    for extra, match in ((["trainer.max_training_steps=0"], "max_training_steps must be > 0"),
+                         (["generator.sampling_params.logprobs=2"], "should be 0 or 1"),
+                         (["generator.max_input_length=100", "trainer.max_prompt_length=512"], "must be at least"),
+                         (["trainer.mtp.enabled=true", "trainer.mtp.num_speculative_tokens=0"], "num_speculative_tokens"),
+                         (["trainer.update_epochs_per_batch=0"], "update_epochs_per_batch"),
+                         (["generator.n_samples_per_prompt=0"], "n_samples_per_prompt")):
+        with pytest.raises(ValueError, match=match):
+            validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + extra))
+    validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + ["generator.sampling_params.logprobs=null", "trainer.max_training_steps=3"]))
