@@ -39,20 +39,35 @@ def get_rollout_metrics(responses: Sequence[Sequence[int]], rewards: Sequence[Un
     return m
 
 
+def _outcome(r) -> float:
+    """What decides whether a trajectory "passed": its scalar reward, or the reward on its last token (the outcome
+    reward of a token-level list; earlier entries are shaping terms)."""
+    if isinstance(r, (list, tuple)):
+        if not len(r):
+            raise ValueError("token-level rewards must be non-empty lists")
+        return float(r[-1])
+    return float(r)
+
+
 def compute_pass_at_n(rewards: Sequence[Union[float, Sequence[float]]], uids: Sequence[str]) -> float:
-    """Fraction of prompts with at least one trajectory of positive total reward."""
+    """Fraction of prompts with at least one trajectory whose outcome reward is positive."""
     best: Dict[str, float] = {}
     for r, u in zip(rewards, uids):
-        best[u] = max(best.get(u, float("-inf")), _traj_reward(r))
+        best[u] = max(best.get(u, float("-inf")), _outcome(r))
     return float(np.mean([1.0 if v > 0 else 0.0 for v in best.values()])) if best else 0.0
 
 
 def get_metrics_from_generator_output(out: GeneratorOutput, uids: Sequence[str]) -> Dict[str, float]:
+    """``avg_score``: mean total reward per trajectory; ``pass_at_n``: see ``compute_pass_at_n``;
+    ``mean_positive_reward``: mean over *all* trajectories of their positive reward mass (``max(r, 0)``, summed over
+    tokens for token-level rewards).  Definitions of the reference (generators/utils.py:184-232)."""
     rewards = out["rewards"]
+    if not len(rewards):
+        raise ValueError("`rewards` must be a non-empty list")
     scores = [_traj_reward(r) for r in rewards]
-    pos = [s for s in scores if s > 0]
-    return {"avg_score": float(np.mean(scores)) if scores else 0.0, "pass_at_n": compute_pass_at_n(rewards, uids),
-            "mean_positive_reward": float(np.mean(pos)) if pos else 0.0}
+    pos = [float(sum(max(float(x), 0.0) for x in r)) if isinstance(r, (list, tuple)) else max(float(r), 0.0) for r in rewards]
+    return {"avg_score": float(np.mean(scores)), "pass_at_n": compute_pass_at_n(rewards, uids),
+            "mean_positive_reward": float(np.mean(pos))}
 
 
 def prepare_generator_input(prompts: List[Any], n_samples_per_prompt: int, sampling_params: Optional[Dict[str, Any]],

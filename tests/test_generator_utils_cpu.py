@@ -174,3 +174,27 @@ def test_validate_step_wise_rows():
         V(1, rows(["a", "b"], [False, True]), step_wise=True)
     with pytest.raises(E, match="continues at row 1"):
         V(1, rows(["a", "a"], [True, True]), step_wise=True)
+
+
+@pytest.mark.parametrize("rewards,avg,pass_n,pos", [
+    ([1.0, 2.0], 1.5, 1.0, 1.5),
+    ([[1.0, 0.0], [0.0, 1.0]], 1.0, 0.5, 1.0),     # token-level: the last token's reward decides the pass
+    ([-1.0, 2.0], 0.5, 0.5, 1.0),                  # positive mass averaged over all trajectories
+    ([[1.0, -1.0], [-0.5, 0.5]], 0.0, 0.5, 0.75),
+])
+def test_reward_metrics_follow_the_reference_definitions(rewards, avg, pass_n, pos):
+    m = U.get_metrics_from_generator_output({"rewards": rewards}, ["a", "b"])
+    assert (m["avg_score"], m["pass_at_n"], m["mean_positive_reward"]) == pytest.approx((avg, pass_n, pos))
+    with pytest.raises(ValueError):
+        U.get_metrics_from_generator_output({"rewards": []}, [])
+
+
+@pytest.mark.parametrize("masks,stops,want", [
+    ([[1, 1, 0, 1], [0, 1, 1, 1], [1, 0, 1]], ["stop"] * 3, [[1, 1, 0, 1], [0, 1, 1, 1], [1, 0, 1]]),
+    ([[1, 1, 0, 1], [0, 1, 1, 1], [1, 0, 1]], ["length"] * 3, [[0] * 4, [0] * 4, [0] * 3]),
+    ([[1, 1], [1, 0, 1], [0, 1, 1, 1]], ["length", "abort", "cancelled"], [[0, 0], [0, 0, 0], [0, 0, 0, 0]]),
+    ([], [], []),
+])
+def test_overlong_filtering_cases_of_the_reference(masks, stops, want):
+    before = [list(m) for m in masks]
+    assert U.apply_overlong_filtering(masks, stops) == want and masks == before  # the input is not modified
