@@ -35,10 +35,15 @@ def select_rows(out: GeneratorOutput, idx: Sequence[int]) -> GeneratorOutput:
     for k, v in out.items():
         if k in _ROW_KEYS and isinstance(v, list):
             res[k] = [v[i] for i in idx]
+        elif k == "trajectory_time_splits" and isinstance(v, dict):
+            res[k] = {name: [times[i] for i in idx] for name, times in v.items()}  # per-trajectory lists by name
         else:
             res[k] = v
     if res.get("response_ids") is not None and res.get("rewards") is not None:
-        res["rollout_metrics"] = get_rollout_metrics(res["response_ids"], res["rewards"], res.get("env_metrics"))
+        res["rollout_metrics"] = get_rollout_metrics(res["response_ids"], res["rewards"], res.get("env_metrics"),
+                                                     loss_masks=res.get("loss_masks"),
+                                                     trajectory_completion_times=res.get("trajectory_generation_times"),
+                                                     trajectory_time_splits=res.get("trajectory_time_splits"))
     return res
 
 

@@ -16,26 +16,61 @@ def _traj_reward(r) -> float:
     return float(sum(r)) if isinstance(r, (list, tuple)) else float(r)
 
 
+def _time_stats(m: Dict[str, float], name: str, times) -> None:
+    if times is None or len(times) == 0:
+        return
+    a = np.asarray(times, dtype=np.float64)
+    m[f"generate/trajectory_time_{name}_mean"] = float(a.mean())
+    m[f"generate/trajectory_time_{name}_p90"] = float(np.percentile(a, 90))
+    m[f"generate/trajectory_time_{name}_max"] = float(a.max())
+
+
 def get_rollout_metrics(responses: Sequence[Sequence[int]], rewards: Sequence[Union[float, Sequence[float]]],
                         env_metrics: Optional[Sequence[Dict[str, Any]]] = None,
-                        env_classes: Optional[Sequence[str]] = None) -> Dict[str, float]:
+                        env_classes: Optional[Sequence[str]] = None, loss_masks: Optional[Sequence[Sequence[int]]] = None,
+                        trajectory_completion_times: Optional[Sequence[float]] = None,
+                        trajectory_time_splits: Optional[Dict[str, Sequence[float]]] = None) -> Dict[str, float]:
+    """Token statistics of a rollout batch (all tokens; with ``loss_masks`` also the model-generated ones and the
+    lengths of the individual turns = runs of trained tokens), trajectory time statistics (mean / p90 / max of the
+    end-to-end times, of every named split, and of the remainder ``other``), and the environments' own numeric
+    metrics, averaged -- per environment class when ``env_classes`` is given (reference: generators/utils.py:411-520,
+    same metric names)."""
     lens = np.array([len(r) for r in responses], dtype=np.float64) if len(responses) else np.zeros(1)
     scores = np.array([_traj_reward(r) for r in rewards], dtype=np.float64) if len(rewards) else np.zeros(1)
-    pos, nonpos = lens[scores > 0], lens[scores <= 0]
+    pos, zero = lens[scores > 0], lens[scores == 0]
     m = {
         "generate/min_num_tokens": float(lens.min()), "generate/max_num_tokens": float(lens.max()),
         "generate/avg_num_tokens": float(lens.mean()), "generate/std_num_tokens": float(lens.std()),
         "generate/avg_tokens_non_zero_rewards": float(pos.mean()) if len(pos) else 0.0,
-        "generate/avg_tokens_zero_rewards": float(nonpos.mean()) if len(nonpos) else 0.0,
+        "generate/avg_tokens_zero_rewards": float(zero.mean()) if len(zero) else 0.0,
     }  # fmt: skip
+    if loss_masks is not None and len(loss_masks):
+        own = np.array([sum(1 for x in mk if x) for mk in loss_masks], dtype=np.float64)
+        m.update({"generate/avg_assistant_tokens": float(own.mean()), "generate/min_assistant_tokens": float(own.min()),
+                  "generate/max_assistant_tokens": float(own.max()), "generate/std_assistant_tokens": float(own.std())})
+        turns = compute_turn_token_counts([list(mk) for mk in loss_masks])
+        if turns:
+            t = np.array(turns, dtype=np.float64)
+            m.update({"generate/tokens_per_turn_mean": float(t.mean()), "generate/tokens_per_turn_std": float(t.std()),
+                      "generate/tokens_per_turn_max": float(t.max())})
+    _time_stats(m, "completion", trajectory_completion_times)
+    for name, times in (trajectory_time_splits or {}).items():
+        _time_stats(m, name, times)
+    n_t = len(trajectory_completion_times) if trajectory_completion_times is not None else 0
+    if n_t and trajectory_time_splits and all(len(v) == n_t for v in trajectory_time_splits.values()):
+        other = np.asarray(trajectory_completion_times, dtype=np.float64).copy()
+        for times in trajectory_time_splits.values():
+            other -= np.asarray(times, dtype=np.float64)  # what no split accounts for: templating, tokenisation, queueing
+        _time_stats(m, "other", other)
     if env_metrics:
         agg: Dict[str, List[float]] = defaultdict(list)
-        for em in env_metrics:
+        for i, em in enumerate(env_metrics):
+            cls = env_classes[i] if env_classes is not None and i < len(env_classes) else None
             for k, v in (em or {}).items():
                 if isinstance(v, (int, float, bool)):
-                    agg[k].append(float(v))
+                    agg[f"environment/{cls}/{k}" if cls else f"environment/{k}"].append(float(v))
         for k, v in agg.items():
-            m[f"environment/{k}"] = float(np.mean(v))
+            m[k] = float(np.mean(v))
     return m
 
 
@@ -109,10 +144,21 @@ def concatenate_generator_outputs(outputs: List[GeneratorOutput]) -> GeneratorOu
             res[key] = None
         else:
             res[key] = [x for v in vals for x in v]
-    res["rollout_metrics"] = get_rollout_metrics(res["response_ids"], res["rewards"], res.get("env_metrics"))
-    res["rollout_expert_indices"] = None
+    # per-component times: lists are joined per name; a chunk without them makes the whole field None
+    splits = [o.get("trajectory_time_splits") for o in outputs]
+    if any(sp is None for sp in splits):
+        res["trajectory_time_splits"] = None
+    else:
+        names = list(splits[0])
+        res["trajectory_time_splits"] = {k: [x for sp in splits for x in sp.get(k, [])] for k in names}
+    routes = [o.get("rollout_expert_indices") for o in outputs]
+    res["rollout_expert_indices"] = None if any(r is None for r in routes) else [x for r in routes for x in r]
+    # aggregates are recomputed over the joined rows, never combined from the chunks' aggregates
+    res["rollout_metrics"] = get_rollout_metrics(res["response_ids"], res["rewards"], res.get("env_metrics"),
+                                                 loss_masks=res.get("loss_masks"),
+                                                 trajectory_completion_times=res.get("trajectory_generation_times"),
+                                                 trajectory_time_splits=res.get("trajectory_time_splits"))
     res["pixel_values"] = res["image_grid_thw"] = None
-    res["trajectory_time_splits"] = first.get("trajectory_time_splits")
     return res
 
 

@@ -198,3 +198,49 @@ def test_reward_metrics_follow_the_reference_definitions(rewards, avg, pass_n, p
 def test_overlong_filtering_cases_of_the_reference(masks, stops, want):
     before = [list(m) for m in masks]
     assert U.apply_overlong_filtering(masks, stops) == want and masks == before  # the input is not modified
+
+
+def test_rollout_metrics_assistant_tokens_turns_and_time_splits():
+    import numpy as np
+
+    out1 = {"prompt_token_ids": [[1, 2], [3, 4]], "response_ids": [[1, 2], [3, 4]], "rewards": [1.0, 2.0],
+            "loss_masks": [[1, 1], [1, 1]], "stop_reasons": ["stop", "stop"], "rollout_logprobs": [[0.1, 0.2], [0.3, 0.4]]}
+    out2 = {"prompt_token_ids": [[5, 6, 7], [8]], "response_ids": [[5, 6, 7], [8]], "rewards": [2.0, 3.0],
+            "loss_masks": [[1, 1, 1], [1]], "stop_reasons": ["stop", "stop"], "rollout_logprobs": [[0.5, 0.6, 0.7], [0.8]]}
+    cat = U.concatenate_generator_outputs([out1, out2])
+    assert cat["response_ids"] == [[1, 2], [3, 4], [5, 6, 7], [8]] and cat["rewards"] == [1.0, 2.0, 2.0, 3.0]
+    assert cat["rollout_logprobs"] == [[0.1, 0.2], [0.3, 0.4], [0.5, 0.6, 0.7], [0.8]]
+    want = {"generate/min_num_tokens": 1, "generate/max_num_tokens": 3, "generate/avg_num_tokens": 2.0,
+            "generate/std_num_tokens": np.std([2, 2, 3, 1]), "generate/avg_tokens_non_zero_rewards": 2.0,
+            "generate/avg_tokens_zero_rewards": 0, "generate/avg_assistant_tokens": 2.0, "generate/min_assistant_tokens": 1,
+            "generate/max_assistant_tokens": 3, "generate/std_assistant_tokens": np.std([2, 2, 3, 1]),
+            "generate/tokens_per_turn_mean": 2.0, "generate/tokens_per_turn_std": np.std([2, 2, 3, 1]),
+            "generate/tokens_per_turn_max": 3}
+    assert cat["rollout_metrics"].keys() == want.keys()
+    for k, v in want.items():
+        assert cat["rollout_metrics"][k] == pytest.approx(v), k
+
+    m = U.get_rollout_metrics([[1, 2]] * 4, [1.0] * 4, trajectory_completion_times=[10.0, 20.0, 30.0, 40.0],
+                              trajectory_time_splits={"llm": [4.0, 8.0, 12.0, 16.0], "env": [5.0, 10.0, 15.0, 20.0]})
+    assert m["generate/trajectory_time_llm_mean"] == 10.0 and m["generate/trajectory_time_llm_max"] == 16.0
+    assert m["generate/trajectory_time_llm_p90"] == pytest.approx(np.percentile([4.0, 8.0, 12.0, 16.0], 90))
+    assert m["generate/trajectory_time_env_mean"] == 12.5 and m["generate/trajectory_time_completion_max"] == 40.0
+    assert m["generate/trajectory_time_other_mean"] == pytest.approx(2.5) and m["generate/trajectory_time_other_max"] == pytest.approx(4.0)
+
+    def timed(times, splits):
+        n = len(times)
+        return {"prompt_token_ids": [[1]] * n, "response_ids": [[1, 2]] * n, "rewards": [1.0] * n, "loss_masks": [[1, 1]] * n,
+                "stop_reasons": ["stop"] * n, "rollout_logprobs": None, "trajectory_generation_times": times,
+                "trajectory_time_splits": splits}
+
+    both = U.concatenate_generator_outputs([timed([10.0, 20.0], {"llm": [4.0, 8.0], "env": [5.0, 10.0]}),
+                                            timed([30.0, 40.0], {"llm": [12.0, 16.0], "env": [15.0, 20.0]})])
+    assert both["trajectory_time_splits"] == {"llm": [4.0, 8.0, 12.0, 16.0], "env": [5.0, 10.0, 15.0, 20.0]}
+    assert both["rollout_metrics"]["generate/trajectory_time_llm_p90"] == pytest.approx(np.percentile([4.0, 8.0, 12.0, 16.0], 90))
+    assert both["rollout_metrics"]["generate/trajectory_time_other_mean"] == pytest.approx(2.5)
+    part = U.concatenate_generator_outputs([timed([10.0], {"llm": [4.0], "env": [5.0]}), timed([30.0], None)])
+    assert part["trajectory_time_splits"] is None and "generate/trajectory_time_llm_mean" not in part["rollout_metrics"]
+    # environment metrics: averaged, per class when the classes are known
+    m = U.get_rollout_metrics([[1]] * 2, [0.0, 1.0], env_metrics=[{"turns": 2}, {"turns": 4}], env_classes=["a", "b"])
+    assert m["environment/a/turns"] == 2.0 and m["environment/b/turns"] == 4.0
+    assert U.get_rollout_metrics([[1]] * 2, [0.0, 1.0], env_metrics=[{"turns": 2}, {"turns": 4}])["environment/turns"] == 3.0
