@@ -392,7 +392,10 @@ def slice_generator_output(out: GeneratorOutput, start: int, end: int) -> Genera
     n = len(out["response_ids"])
     res: Dict[str, Any] = {}
     for k, v in out.items():
-        res[k] = v[start:end] if isinstance(v, list) and len(v) == n else v
+        if k == "trajectory_time_splits" and isinstance(v, dict):
+            res[k] = {name: (t[start:end] if len(t) == n else t) for name, t in v.items()}
+        else:
+            res[k] = v[start:end] if isinstance(v, list) and len(v) == n else v
     return res  # type: ignore[return-value]
 
 
