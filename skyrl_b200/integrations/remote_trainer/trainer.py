@@ -77,7 +77,7 @@ class RemotePolicyWorker:
     def forward_backward(self, batch: TrainingInputBatch, **_) -> Dict[str, float]:
         a = self.cfg.trainer.algorithm
         loss = LOSS_NAMES.get(a.policy_loss_type, a.policy_loss_type)
-        # the service takes Tinker's names: ratio thresholds around 1 for the clipped objectives, deltas for DPPO
+        # the service takes Tinker's names: ratio thresholds centred on one for the clipped objectives, deltas for DPPO
         if loss in ("ppo", "gspo"):
             cfg = {"clip_low_threshold": 1.0 - a.eps_clip_low, "clip_high_threshold": 1.0 + a.eps_clip_high}
         elif loss == "cispo":

@@ -199,7 +199,7 @@ class SkyRLTrainBackend:
     @staticmethod
     def normalize_loss_fn_config(loss_fn: str, cfg: Optional[dict]) -> Optional[dict]:
         """Tinker's per-request knobs -> fields of the algorithm config (reference: skyrl_train_backend.py:840-872).
-        Ratio thresholds are given around 1 (``clip_low_threshold=0.9`` means ``eps_clip_low=0.1``); DPPO's deltas and
+        Ratio thresholds are centred on one (``clip_low_threshold=0.9`` means ``eps_clip_low=0.1``); DPPO's deltas and
         CISPO's clips live in their nested sections; anything else (``value_clip``) keeps its name."""
         if not cfg:
             return None
