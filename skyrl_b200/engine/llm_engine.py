@@ -60,7 +60,9 @@ class SamplingParams:
         extra = d.pop("additional_kwargs", None) or {}
         d.update(extra)
         known = {f for f in cls.__dataclass_fields__}
-        d.pop("repetition_penalty", None)
+        rp = d.pop("repetition_penalty", None)
+        if rp is not None and float(rp) != 1.0:
+            raise ValueError(f"repetition_penalty={rp} is not supported by this engine (only 1.0: no penalty)")
         d.pop("n", None)
         pl = d.get("prompt_logprobs")
         if pl is not None and not isinstance(pl, bool):

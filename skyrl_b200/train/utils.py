@@ -144,6 +144,10 @@ def validate_cfg(cfg, world_size: int = 1) -> None:
     if g.max_input_length is not None and g.max_input_length < t.max_prompt_length:
         raise ValueError(f"generator.max_input_length ({g.max_input_length}) must be at least trainer.max_prompt_length "
                          f"({t.max_prompt_length})")
+    for name, sp in (("sampling_params", g.sampling_params), ("eval_sampling_params", g.eval_sampling_params)):
+        if sp is not None and float(sp.repetition_penalty) != 1.0:
+            raise ValueError(f"generator.{name}.repetition_penalty={sp.repetition_penalty}: the built-in engine applies no "
+                             "repetition penalty; leave it at 1.0")
     if t.mtp.enabled and t.mtp.num_speculative_tokens < 1:
         raise ValueError("trainer.mtp.num_speculative_tokens must be >= 1 when trainer.mtp.enabled")
     if t.update_epochs_per_batch < 1:

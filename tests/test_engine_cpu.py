@@ -268,3 +268,17 @@ def test_speculative_decoding_accepts_correct_guesses_and_takes_two_tokens_per_s
     # sampled (temperature 1) outputs stay inside the vocabulary and respect the limits too
     out = eng.generate(prompts, [SamplingParams(max_tokens=n, temperature=1.0, ignore_eos=True) for n in (9, 4, 1)])
     assert [len(o.token_ids) for o in out] == [9, 4, 1]
+
+
+def test_unsupported_sampling_knobs_are_rejected_not_ignored():
+    import pytest
+
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.train.utils import validate_cfg
+
+    assert SamplingParams.from_dict({"repetition_penalty": 1.0, "max_generate_length": 5}).max_tokens == 5
+    with pytest.raises(ValueError, match="repetition_penalty"):
+        SamplingParams.from_dict({"repetition_penalty": 1.2})
+    with pytest.raises(ValueError, match="repetition_penalty"):
+        validate_cfg(SkyRLTrainConfig.from_cli_overrides(["trainer.policy.model.path=tiny-llama",
+                                                          "generator.sampling_params.repetition_penalty=1.1"]))
