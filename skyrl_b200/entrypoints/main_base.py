@@ -89,7 +89,12 @@ class BasePPOExp:
         return SkyRLGymGenerator(cfg.generator, cfg.environment.skyrl_gym, inference_engine_client, tokenizer)
 
     def get_trainer(self, cfg, tracker, tokenizer, train_dataset, eval_dataset, inference_engine_client, generator):
-        if cfg.trainer.fully_async.enabled:
+        if cfg.trainer.fully_async.enabled and cfg.trainer.fully_async.simulate_training:
+            # rollout-side dry run: generation, staleness control and weight-sync pacing are real, training is a timed stub
+            from ..train.fully_async_trainer import FullyAsyncTrainerSim
+
+            cls = FullyAsyncTrainerSim
+        elif cfg.trainer.fully_async.enabled:
             from ..train.fully_async_trainer import FullyAsyncPPOTrainer
 
             cls = FullyAsyncPPOTrainer

@@ -148,6 +148,16 @@ def validate_cfg(cfg, world_size: int = 1) -> None:
         if sp is not None and float(sp.repetition_penalty) != 1.0:
             raise ValueError(f"generator.{name}.repetition_penalty={sp.repetition_penalty}: the built-in engine applies no "
                              "repetition penalty; leave it at 1.0")
+    ie = g.inference_engine
+    for key in ("pipeline_parallel_size", "expert_parallel_size"):
+        if int(getattr(ie, key) or 1) != 1:
+            raise ValueError(f"generator.inference_engine.{key}={getattr(ie, key)}: the built-in engine shards by tensor "
+                             "parallelism only (tensor_parallel_size); use more engines for more throughput")
+    if int(ie.data_parallel_size or 1) != 1:
+        raise ValueError("generator.inference_engine.data_parallel_size: engine replicas are counted by num_engines here "
+                         "(one per GPU when colocated); leave data_parallel_size at 1")
+    if ie.enable_pd or int(ie.num_prefill or 0) > 0:
+        raise ValueError("prefill/decode disaggregation (enable_pd, num_prefill) is not available")
     if t.mtp.enabled and t.mtp.num_speculative_tokens < 1:
         raise ValueError("trainer.mtp.num_speculative_tokens must be >= 1 when trainer.mtp.enabled")
     if t.update_epochs_per_batch < 1:

@@ -756,13 +756,43 @@ class ModelWorker:
             scale = 1.0 / self.num_microbatches_accumulated  # reference: worker.py:1513-1537
         if self.mesh is not None:
             self.model.reduce_replicated_grads()
+        frozen = self._frozen_ranges()
+        kept = []
+        if frozen:
+            # frozen parameters: no gradient (so they do not count in the clipping norm either) and, because AdamW's
+            # weight decay would still shrink them, their values -- working copy and fp32 master -- put back afterwards
+            o = self.optimizer
+            for lo, hi in frozen:
+                self.flat_grad[lo:hi].zero_()
+                m0, m1 = max(lo, o.lo), min(hi, o.lo + o.shard)
+                kept.append((lo, hi, self.model.flat_params[lo:hi].clone(), m0, m1,
+                             o.master[m0 - o.lo : m1 - o.lo].clone() if m1 > m0 else None))
         norm = self.optimizer.step(grad_scale=scale)
+        for lo, hi, p, m0, m1, mast in kept:
+            self.model.flat_params[lo:hi].copy_(p)
+            if mast is not None:
+                self.optimizer.master[m0 - self.optimizer.lo : m1 - self.optimizer.lo].copy_(mast)
         # the fused optimizer publishes nothing once the status word is set (csrc/comm.cu); tell the caller
         self.check_device_status("optim_step")
         self.scheduler.step()
         self.optimizer.zero_grad()
         self.num_microbatches_accumulated = 0
         return norm
+
+    def _frozen_ranges(self) -> List[Tuple[int, int]]:
+        """Flat-buffer ranges that training must not move: the routers of a mixture-of-experts policy under
+        ``megatron_config.freeze_moe_router`` (reference: megatron_worker.py, same key)."""
+        if getattr(self, "_frozen_cache", None) is not None:
+            return self._frozen_cache
+        out: List[Tuple[int, int]] = []
+        node = getattr(self.cfg, self.role, None) if self.role in ("policy", "critic") else None
+        if (node is not None and getattr(getattr(node, "megatron_config", None), "freeze_moe_router", False)
+                and getattr(self.model.args, "num_experts", 0) and hasattr(self.model, "offsets")):
+            for name, (off, n) in self.model.offsets.items():
+                if name.endswith(".router"):
+                    out.append((off, off + n))
+        self._frozen_cache = out
+        return out
 
     def set_lr(self, lr: float) -> None:
         self.optimizer.set_lr(lr)

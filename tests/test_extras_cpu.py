@@ -313,3 +313,16 @@ def test_validate_cfg_rejects_out_of_range_knobs():
         with pytest.raises(ValueError, match=match):
             validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + extra))
     validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + ["generator.sampling_params.logprobs=null", "trainer.max_training_steps=3"]))
+
+
+def test_validate_cfg_rejects_engine_layouts_the_engine_does_not_have():
+    from skyrl_b200.config.config import SkyRLTrainConfig
+    from skyrl_b200.train.utils import validate_cfg
+
+    base = ["trainer.policy.model.path=tiny-llama"]
+    for extra, match in ((["generator.inference_engine.pipeline_parallel_size=2"], "pipeline_parallel_size"),
+                         (["generator.inference_engine.expert_parallel_size=4"], "expert_parallel_size"),
+                         (["generator.inference_engine.data_parallel_size=2"], "num_engines"),
+                         (["generator.inference_engine.enable_pd=true"], "disaggregation")):
+        with pytest.raises(ValueError, match=match):
+            validate_cfg(SkyRLTrainConfig.from_cli_overrides(base + extra))

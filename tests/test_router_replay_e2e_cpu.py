@@ -194,3 +194,22 @@ def test_persistent_replay_is_seen_by_other_threads():
         t.start()
         t.join()
     assert not got["active"] and got["persistent"] is None
+
+
+def test_freeze_moe_router_keeps_the_routers_and_trains_the_rest(tmp_path):
+    pdist.reset_env_for_tests()
+    cfg = _cfg(tmp_path, ["trainer.policy.megatron_config.freeze_moe_router=true",
+                          "trainer.policy.optimizer_config.weight_decay=0.1", "trainer.policy.optimizer_config.lr=1e-3"])
+    tr = PPOTrainer(cfg, tokenizer=SyntheticTokenizer(1024))
+    tr.build_models()
+    m = tr.policy.model
+    routers = {n: m.p(n).detach().clone() for n in m.offsets if n.endswith(".router")}
+    experts = m.p("layers.0.experts_wgu").detach().clone()
+    assert routers
+    out = tr.train_step(_prompts())
+    assert out["policy/grad_norm"] > 0
+    for n, w in routers.items():
+        assert torch.equal(m.p(n), w), n                          # not even weight decay touched them
+    assert not torch.equal(m.p("layers.0.experts_wgu"), experts)  # everything else trains
+    lo, n_ = m.offsets["layers.0.router"]
+    assert torch.equal(tr.policy.optimizer.master[lo : lo + n_], routers["layers.0.router"].float().reshape(-1))
