@@ -414,7 +414,9 @@ class SkyRLGymGenerator(GeneratorInterface):
             eos = self.tokenizer.eos_token_id
             masks = [[0] * len(m) if (not r or r[-1] != eos) else m for m, r in zip(masks, responses)]
         has_lp = all(t.rollout_logprobs is not None for t in flat) and len(flat) > 0
-        metrics = get_rollout_metrics(responses, rewards, [t.env_metrics for t in flat], env_classes=None, loss_masks=masks,
+        # one environment class per row (step-wise rollouts have several rows per trajectory)
+        flat_classes = [env_classes[i] for i, o in enumerate(outs) for _ in (o if isinstance(o, list) else [o])]
+        metrics = get_rollout_metrics(responses, rewards, [t.env_metrics for t in flat], env_classes=flat_classes, loss_masks=masks,
                                       trajectory_completion_times=[t.e2e_time for t in flat],
                                       trajectory_time_splits={"llm": [t.time_splits.get("llm", 0.0) for t in flat],
                                                               "env": [t.time_splits.get("env", 0.0) for t in flat]})

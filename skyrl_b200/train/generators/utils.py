@@ -16,6 +16,29 @@ def _traj_reward(r) -> float:
     return float(sum(r)) if isinstance(r, (list, tuple)) else float(r)
 
 
+def _aggregate_env_metrics(env_class: Optional[str], rows: List[Dict[str, Any]]) -> Dict[str, float]:
+    """The environment class's own ``aggregate_metrics`` when the class is registered (an environment may want a sum or
+    a maximum rather than a mean); the mean of every numeric entry otherwise."""
+    if env_class is not None:
+        try:
+            from ...gym.registration import _load, registry
+
+            spec = registry.get(env_class)
+            agg = getattr(_load(spec.entry_point), "aggregate_metrics", None) if spec is not None else None
+            if agg is not None:
+                out = agg(rows)
+                if out:
+                    return {k: float(v) for k, v in out.items() if isinstance(v, (int, float, bool))}
+        except Exception:  # noqa: BLE001 - metrics must never break a rollout
+            pass
+    acc: Dict[str, List[float]] = defaultdict(list)
+    for em in rows:
+        for k, v in em.items():
+            if isinstance(v, (int, float, bool)):
+                acc[k].append(float(v))
+    return {k: float(np.mean(v)) for k, v in acc.items()}
+
+
 def _time_stats(m: Dict[str, float], name: str, times) -> None:
     if times is None or len(times) == 0:
         return
@@ -33,8 +56,8 @@ def get_rollout_metrics(responses: Sequence[Sequence[int]], rewards: Sequence[Un
     """Token statistics of a rollout batch (all tokens; with ``loss_masks`` also the model-generated ones and the
     lengths of the individual turns = runs of trained tokens), trajectory time statistics (mean / p90 / max of the
     end-to-end times, of every named split, and of the remainder ``other``), and the environments' own numeric
-    metrics, averaged -- per environment class when ``env_classes`` is given (reference: generators/utils.py:411-520,
-    same metric names)."""
+    metrics under ``environment/<name>``, aggregated per environment class by the class's own ``aggregate_metrics``
+    when ``env_classes`` is given and averaged otherwise (reference: generators/utils.py:411-508, same metric names)."""
     lens = np.array([len(r) for r in responses], dtype=np.float64) if len(responses) else np.zeros(1)
     scores = np.array([_traj_reward(r) for r in rewards], dtype=np.float64) if len(rewards) else np.zeros(1)
     pos, zero = lens[scores > 0], lens[scores == 0]
@@ -63,14 +86,12 @@ def get_rollout_metrics(responses: Sequence[Sequence[int]], rewards: Sequence[Un
             other -= np.asarray(times, dtype=np.float64)  # what no split accounts for: templating, tokenisation, queueing
         _time_stats(m, "other", other)
     if env_metrics:
-        agg: Dict[str, List[float]] = defaultdict(list)
+        by_class: Dict[Optional[str], List[Dict[str, Any]]] = defaultdict(list)
         for i, em in enumerate(env_metrics):
-            cls = env_classes[i] if env_classes is not None and i < len(env_classes) else None
-            for k, v in (em or {}).items():
-                if isinstance(v, (int, float, bool)):
-                    agg[f"environment/{cls}/{k}" if cls else f"environment/{k}"].append(float(v))
-        for k, v in agg.items():
-            m[k] = float(np.mean(v))
+            by_class[env_classes[i] if env_classes is not None and i < len(env_classes) else None].append(em or {})
+        for cls, rows in by_class.items():
+            for k, v in _aggregate_env_metrics(cls, rows).items():
+                m[f"environment/{k}"] = v
     return m
 
 

@@ -240,7 +240,17 @@ def test_rollout_metrics_assistant_tokens_turns_and_time_splits():
     assert both["rollout_metrics"]["generate/trajectory_time_other_mean"] == pytest.approx(2.5)
     part = U.concatenate_generator_outputs([timed([10.0], {"llm": [4.0], "env": [5.0]}), timed([30.0], None)])
     assert part["trajectory_time_splits"] is None and "generate/trajectory_time_llm_mean" not in part["rollout_metrics"]
-    # environment metrics: averaged, per class when the classes are known
-    m = U.get_rollout_metrics([[1]] * 2, [0.0, 1.0], env_metrics=[{"turns": 2}, {"turns": 4}], env_classes=["a", "b"])
-    assert m["environment/a/turns"] == 2.0 and m["environment/b/turns"] == 4.0
+    # environment metrics: a registered class aggregates its own episodes (here: a maximum), others are averaged
+    import skyrl_b200.gym as gym
+    from skyrl_b200.gym.envs.base_text_env import BaseTextEnv
+
+    class MaxTurns(BaseTextEnv):
+        @staticmethod
+        def aggregate_metrics(metrics):
+            return {"turns": max(m["turns"] for m in metrics), "episodes": len(metrics)}
+
+    gym.register("max_turns_env", MaxTurns, override=True)
+    m = U.get_rollout_metrics([[1]] * 3, [0.0, 1.0, 0.0], env_metrics=[{"turns": 2}, {"turns": 4}, {"steps": 6}],
+                              env_classes=["max_turns_env", "max_turns_env", "not_registered"])
+    assert m["environment/turns"] == 4.0 and m["environment/episodes"] == 2.0 and m["environment/steps"] == 6.0
     assert U.get_rollout_metrics([[1]] * 2, [0.0, 1.0], env_metrics=[{"turns": 2}, {"turns": 4}])["environment/turns"] == 3.0
