@@ -89,6 +89,8 @@ _TINY_RL = ["trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "t
     ("examples/gptoss/run_attention_sinks_grpo.sh", ["trainer.policy.model.path=tiny-sinks"]),
     # rollouts through the OpenAI-compatible endpoint of the colocated engine
     ("examples/train_integrations/openai_chat/run_chat_grpo.sh", []),
+    # a draft head trained beside the policy, used by the engine for speculative decoding
+    ("examples/spec_decode/run_mtp_spec_decode.sh", []),
 ])
 def test_example_scripts_run_on_cpu(tmp_path, script, extra):
     """The launch scripts themselves are executed (bash, the launcher, the entry point) on a tiny preset and data."""
