@@ -91,6 +91,9 @@ _TINY_RL = ["trainer.train_batch_size=4", "trainer.policy_mini_batch_size=4", "t
     ("examples/train_integrations/openai_chat/run_chat_grpo.sh", []),
     # a draft head trained beside the policy, used by the engine for speculative decoding
     ("examples/spec_decode/run_mtp_spec_decode.sh", []),
+    # REPL environment whose code may query the policy; the generator injects the callbacks
+    ("examples/rlm/run_rlm_recursive.sh", ["generator.max_turns=2", "generator.max_input_length=512",
+                                           "environment.skyrl_gym.max_env_workers=4"]),
 ])
 def test_example_scripts_run_on_cpu(tmp_path, script, extra):
     """The launch scripts themselves are executed (bash, the launcher, the entry point) on a tiny preset and data."""
@@ -101,6 +104,14 @@ def test_example_scripts_run_on_cpu(tmp_path, script, extra):
         path = alt[0]
     data = str(tmp_path / "data")
     _tiny_gsm8k(data)
+    if "rlm" in script:  # rows with a context document for the REPL
+        import pandas as pd
+
+        rows = [{"prompt": [{"role": "user", "content": f"which number follows {i} ?"}], "env_class": "rlm",
+                 "context": f"the number after {i} is {i + 1}", "reward_spec": {"method": "contains", "ground_truth": str(i + 1)},
+                 "uid": f"r{i}"} for i in range(16)]
+        pd.DataFrame(rows).to_parquet(os.path.join(data, "train.parquet"))
+        pd.DataFrame(rows[:4]).to_parquet(os.path.join(data, "validation.parquet"))
     if "multiply" in script:  # the example's own dataset writer
         gen = subprocess.run(["python", os.path.join(ROOT, "examples/multiply/multiply_dataset.py"), "--out", data, "--n", "32"],
                              cwd=ROOT, capture_output=True, text=True, timeout=120)
